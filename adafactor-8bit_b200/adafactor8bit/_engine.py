@@ -1,0 +1,270 @@
+"""Launch plans: the layer between the optimizer class and the C ABI.
+
+A plan owns the device-side tables of one multi-tensor launch (tensor
+descriptors, per-tensor dynamic scalars, per-block partial sums) and their
+pinned host mirrors.  Each step the optimizer refreshes the host mirror
+(gradient pointers and the step's scalars change) and the plan enqueues the
+passes on the current CUDA stream.
+"""
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+from . import _native as N
+
+_GRAD_DT = {torch.float32: N.F32, torch.bfloat16: N.BF16}
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def dynamic_map(total_bits):
+    """The signed dynamic-map codebook of the d8 / d4 momentum formats, built
+    with the same torch float32 operations as the reference so that both produce
+    identical tables on the same host (_create_dynamic_map, optimizer.py:416-441;
+    8 bits use 7 exponent bits, 4 bits use 3, optimizer.py:122-123)."""
+    exp_bits = 7 if total_bits == 8 else 3
+    mantissa_bits = total_bits - 1
+    values = []
+    for i in range(exp_bits):
+        edges = torch.linspace(0.1, 1, int(2 ** (i + mantissa_bits - exp_bits) + 1), dtype=torch.float32)
+        centres = (edges[:-1] + edges[1:]) / 2.0
+        magnitude = 10 ** (-(exp_bits - 1) + i)
+        values += (magnitude * centres).tolist() + (-magnitude * centres).tolist()
+    extra = 2 ** (mantissa_bits - exp_bits) - 1
+    if extra > 0:
+        edges = torch.linspace(0.1, 1, extra + 1, dtype=torch.float32)
+        centres = (edges[:-1] + edges[1:]) / 2.0
+        values += centres.tolist() + (-centres).tolist()
+    values += [0, 1.0]
+    if len(values) != 2 ** total_bits:
+        raise AssertionError("dynamic map has the wrong number of entries")
+    return np.asarray(sorted(values), dtype=np.float32)
+
+
+_QMAP_DEVICES = set()
+
+# When set to a list, every kernel launch appends (name, parameters covered,
+# start event, end event), recorded on the launch stream.  Used by bench.py to
+# time individual kernels inside its timed region; None disables it.
+LAUNCH_LOG = None
+_MODE_NAMES = {N.MODE_NOCLIP: "noclip", N.MODE_SUMSQ: "sumsq", N.MODE_APPLY: "apply", N.MODE_SUMSQ_M: "sumsq_m"}
+
+
+def ensure_qmap(device):
+    """Upload both codebooks to `device` once (optimizer.py:109-133)."""
+    device = torch.device(device)
+    if device in _QMAP_DEVICES:
+        return
+    m8 = np.ascontiguousarray(dynamic_map(8))
+    m4 = np.ascontiguousarray(dynamic_map(4))
+    with torch.cuda.device(device):
+        rc = N.lib().af8_set_qmap(m8.ctypes.data, m4.ctypes.data, torch.cuda.current_stream().cuda_stream)
+        N.check(rc, "af8_set_qmap")
+        torch.cuda.current_stream().synchronize()   # the host arrays die with this frame
+    _QMAP_DEVICES.add(device)
+
+
+class _PinnedRing:
+    """A small ring of pinned host buffers.  A buffer is reused only after the
+    copy that read it has completed on the device."""
+
+    def __init__(self, nbytes, depth=3):
+        self.bufs = [torch.empty(max(nbytes, 16), dtype=torch.uint8, pin_memory=True) for _ in range(depth)]
+        self.events = [None] * depth
+        self.i = 0
+
+    def next(self):
+        self.i = (self.i + 1) % len(self.bufs)
+        ev = self.events[self.i]
+        if ev is not None:
+            ev.synchronize()
+        return self.bufs[self.i]
+
+    def mark(self, stream):
+        ev = self.events[self.i]
+        if ev is None:
+            ev = torch.cuda.Event()
+            self.events[self.i] = ev
+        ev.record(stream)
+
+
+class FullrankKey(tuple):
+    """(grad_dtype, v_fmt, m_fmt, block, m_block, use_adam_denom, momentum_only, negate)"""
+
+
+class FullrankPlan:
+    """One multi-tensor launch group of the full-rank path: all tensors share
+    the kernel configuration `key`; per-tensor scalars live in the table."""
+
+    def __init__(self, device, grad_dtype, v_fmt, m_fmt, block, m_block, use_adam_denom,
+                 momentum_only, negate, params, states):
+        self.device = torch.device(device)
+        self.params = list(params)
+        self.states = list(states)
+        n = len(self.params)
+        self.n = n
+        self.cfg = N.FullrankCfg()
+        self.cfg.param_dtype = N.F32
+        self.cfg.grad_dtype = _GRAD_DT[grad_dtype]
+        self.cfg.v_fmt = N.V_FMT[v_fmt]
+        self.cfg.m_fmt = N.M_FMT[m_fmt]
+        self.cfg.block = int(block)
+        self.cfg.m_block = int(m_block) if m_block else 0
+        # the momentum-only rule exists only with momentum and always normalises
+        # with rsqrt(max(v, eps_sq)) (optimizer.py:893-896)
+        momentum_only = bool(momentum_only) and m_fmt is not None
+        self.cfg.use_adam_denom = int(bool(use_adam_denom) and not momentum_only)
+        self.cfg.momentum_only = int(momentum_only)
+        self.cfg.negate_grad = int(bool(negate))
+        self.cfg.v_floor = -126.0     # optimizer.py:299 (default min_log_floor)
+        if m_fmt in ("d8", "d4"):
+            ensure_qmap(self.device)
+        self.numel = np.array([p.numel() for p in self.params], dtype=np.int64)
+        self.nblocks = (self.numel + block - 1) // block
+        self.first_block = np.concatenate([[0], np.cumsum(self.nblocks)[:-1]]).astype(np.int64)
+        self.total_blocks = int(self.nblocks.sum())
+        self.total_numel = int(self.numel.sum())
+
+        self.d_table = torch.empty(n * N.FULLRANK_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+        self.d_dyn = torch.zeros(n * N.DYN_SCALARS.itemsize, dtype=torch.uint8, device=self.device)
+        self.d_norm = torch.empty(n * N.NORM_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+        self.d_sumsq = None
+        self.h_table = _PinnedRing(n * N.FULLRANK_TENSOR.itemsize)
+        self.h_norm = _PinnedRing(n * N.NORM_TENSOR.itemsize)
+        self._static = None
+        for p in self.params:
+            if p.dtype != torch.float32:
+                raise RuntimeError("the full-rank kernels update fp32 parameters only")
+            if not p.is_contiguous():
+                raise RuntimeError("parameters must be contiguous")
+
+    # -- table ---------------------------------------------------------------
+    def _static_fields(self):
+        """Pointers and sizes that only change when a state tensor is replaced."""
+        t = np.zeros(self.n, dtype=N.FULLRANK_TENSOR)
+        for i, (p, st) in enumerate(zip(self.params, self.states)):
+            t["param"][i] = p.data_ptr()
+            t["v_q"][i] = _ptr(st.get("variance_q"))
+            t["v_scale"][i] = _ptr(st.get("variance_scale"))
+            t["v_min_log"][i] = _ptr(st.get("variance_min_log"))
+            t["v_f32"][i] = _ptr(st.get("variance"))
+            t["m_q"][i] = _ptr(st.get("m_q"))
+            t["m_scale"][i] = _ptr(st.get("m_scale"))
+            t["m_f32"][i] = _ptr(st.get("m"))
+        t["numel"] = self.numel
+        t["first_block"] = self.first_block
+        return t
+
+    def invalidate(self):
+        self._static = None
+
+    def fill_table(self, grads, scalars):
+        """scalars: dict of per-tensor float32 arrays (or python floats) named as
+        the table fields."""
+        if self._static is None:
+            self._static = self._static_fields()
+        buf = self.h_table.next()
+        table = buf.numpy()[: self.n * N.FULLRANK_TENSOR.itemsize].view(N.FULLRANK_TENSOR)
+        table[:] = self._static
+        table["grad"] = [g.data_ptr() for g in grads]
+        for k in ("decay", "alpha", "v_w", "v_keep", "v_eps_add", "m_w", "eps_gradsq", "eps_denom", "eps_sq"):
+            table[k] = scalars[k]
+        return buf, table
+
+    # -- launches ------------------------------------------------------------
+    def kernel_name(self, mode):
+        c = self.cfg
+        fast = (c.v_fmt == N.V_AL8 and c.m_fmt == N.M_UF8 and c.block == 2048 and c.m_block == 256
+                and c.use_adam_denom and not c.momentum_only and mode != N.MODE_SUMSQ_M)
+        return ("fullrank_fast_" if fast else "fullrank_generic_") + _MODE_NAMES[mode]
+
+    def _step(self, mode, host_buf, stream):
+        self.cfg.mode = mode
+        log = LAUNCH_LOG
+        if log is not None:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+        rc = N.lib().af8_fullrank_step(
+            ctypes.byref(self.cfg), host_buf.data_ptr() if host_buf is not None else None,
+            self.d_table.data_ptr(), self.n, self.total_blocks, self.d_dyn.data_ptr(),
+            self.d_sumsq.data_ptr() if self.d_sumsq is not None else None, stream.cuda_stream)
+        N.check(rc, "af8_fullrank_step")
+        if log is not None:
+            e1.record(stream)
+            log.append((self.kernel_name(mode), self.total_numel, e0, e1))
+        if host_buf is not None:
+            self.h_table.mark(stream)
+
+    def _finalize(self, table, pre_div_mode, d, fira, fira_margin, stream):
+        buf = self.h_norm.next()
+        nt = buf.numpy()[: self.n * N.NORM_TENSOR.itemsize].view(N.NORM_TENSOR)
+        nt["first_block"] = self.first_block
+        nt["n_blocks"] = self.nblocks
+        nt["pre_div_mode"] = pre_div_mode
+        nt["alpha"] = table["alpha"]
+        sqrt_n = np.sqrt(self.numel.astype(np.float64))
+        nt["sqrt_n"] = sqrt_n.astype(np.float32)
+        nt["d"] = np.float32(d)
+        use_clip = d > 0 and pre_div_mode == 0
+        nt["clip_div"] = (sqrt_n * d).astype(np.float32) if use_clip else np.float32(0.0)
+        nt["fira_margin1"] = np.float32(1.0 + fira_margin)
+        if fira and pre_div_mode != 1:
+            for i, st in enumerate(self.states):
+                prev = st.get("fira_prev_norm")
+                if prev is None:
+                    prev = torch.zeros((), dtype=torch.float32, device=self.device)
+                    st["fira_prev_norm"] = prev
+                    nt["fira_has_prev"][i] = 0
+                else:
+                    nt["fira_has_prev"][i] = 1
+                nt["fira_prev"][i] = prev.data_ptr()
+        else:
+            nt["fira_prev"] = 0
+            nt["fira_has_prev"] = 0
+        self.d_norm.copy_(buf[: self.d_norm.numel()], non_blocking=True)
+        self.h_norm.mark(stream)
+        rc = N.lib().af8_norm_finalize(self.d_norm.data_ptr(), self.n, self.d_sumsq.data_ptr(),
+                                       self.d_dyn.data_ptr(), stream.cuda_stream)
+        N.check(rc, "af8_norm_finalize")
+
+    def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, stream=None):
+        """One optimizer step for every tensor of the plan
+        (_dispatch_cuda_clip's pass structure, optimizer.py:1048-1077)."""
+        stream = stream or torch.cuda.current_stream(self.device)
+        buf, table = self.fill_table(grads, scalars)
+        mom_only = bool(self.cfg.momentum_only)
+        clip_first = d > 0                      # a statistic of the raw update is needed
+        if not (fira or clip_first):
+            self._step(N.MODE_NOCLIP, buf, stream)
+            return
+        if self.d_sumsq is None:
+            self.d_sumsq = torch.empty(self.total_blocks, dtype=torch.float32, device=self.device)
+        if not mom_only:
+            self._step(N.MODE_SUMSQ, buf, stream)
+            self._finalize(table, 0, d, fira, fira_margin, stream)
+            self._step(N.MODE_APPLY, None, stream)
+            return
+        # momentum-only rule (optimizer.py:894-901): clip the normalised gradient
+        # first, then limit the norm of the momentum that is applied with d = 0
+        pending = buf
+        if clip_first:
+            self._step(N.MODE_SUMSQ, pending, stream)
+            pending = None
+            self._finalize(table, 1, d, False, fira_margin, stream)
+        else:
+            self.d_dyn.view(torch.float32).view(self.n, 8)[:, 2] = 1.0   # pre_div
+        if fira:
+            self._step(N.MODE_SUMSQ_M, pending, stream)
+            pending = None
+            self._finalize(table, 2, 0.0, True, fira_margin, stream)
+        self._step(N.MODE_APPLY, pending, stream)
+
+    def norms(self):
+        """Update norms measured by the last two-pass step (one per tensor)."""
+        dyn = self.d_dyn.cpu().numpy().view(N.DYN_SCALARS)
+        return dyn["norm"].copy()

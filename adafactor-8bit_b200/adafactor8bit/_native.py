@@ -1,0 +1,116 @@
+"""ctypes binding of libaf8 (include/af8.h): the only way this package reaches
+the GPU.  There is no fallback: if the library is missing or a call fails, a
+RuntimeError is raised.
+
+The table structs of the C ABI are mirrored as numpy structured dtypes so that
+a whole table can be filled with vectorised assignments.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_DEFAULT_LIB = os.path.join(os.path.dirname(_HERE), "lib", "libaf8.so")
+
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA = 0, 1, 2, 3
+F32, BF16, F16 = 0, 1, 2
+V_FP32, V_AL8, V_AL16 = 0, 8, 16
+M_NONE, M_UF8, M_UF4, M_D8, M_D4, M_FP32 = 0, 1, 2, 3, 4, 5
+MODE_NOCLIP, MODE_SUMSQ, MODE_APPLY, MODE_SUMSQ_M = 0, 1, 2, 3
+
+V_FMT = {"fp32": V_FP32, "al8": V_AL8, "al16": V_AL16}
+M_FMT = {None: M_NONE, "uf8": M_UF8, "uf4": M_UF4, "d8": M_D8, "d4": M_D4, "fp32": M_FP32}
+
+_P = np.uint64   # device / host pointers inside tables
+
+FULLRANK_TENSOR = np.dtype([
+    ("param", _P), ("grad", _P), ("v_q", _P), ("v_scale", _P), ("v_min_log", _P), ("v_f32", _P),
+    ("m_q", _P), ("m_scale", _P), ("m_f32", _P),
+    ("numel", np.int64), ("first_block", np.int64),
+    ("decay", np.float32), ("alpha", np.float32), ("v_w", np.float32), ("v_keep", np.float32),
+    ("v_eps_add", np.float32), ("m_w", np.float32), ("eps_gradsq", np.float32),
+    ("eps_denom", np.float32), ("eps_sq", np.float32), ("reserved", np.float32),
+], align=True)
+assert FULLRANK_TENSOR.itemsize == 128
+
+DYN_SCALARS = np.dtype([
+    ("step", np.float32), ("fira", np.float32), ("pre_div", np.float32), ("zero", np.float32),
+    ("norm", np.float32), ("reserved", np.float32, (3,)),
+], align=True)
+assert DYN_SCALARS.itemsize == 32
+
+NORM_TENSOR = np.dtype([
+    ("first_block", np.int64), ("n_blocks", np.int64), ("fira_prev", _P),
+    ("fira_has_prev", np.int32), ("pre_div_mode", np.int32),
+    ("alpha", np.float32), ("clip_div", np.float32), ("sqrt_n", np.float32), ("d", np.float32),
+    ("fira_margin1", np.float32), ("reserved", np.float32),
+], align=True)
+assert NORM_TENSOR.itemsize == 56
+
+
+class FullrankCfg(ctypes.Structure):
+    _fields_ = [
+        ("param_dtype", ctypes.c_int32), ("grad_dtype", ctypes.c_int32),
+        ("v_fmt", ctypes.c_int32), ("m_fmt", ctypes.c_int32),
+        ("block", ctypes.c_int32), ("m_block", ctypes.c_int32),
+        ("use_adam_denom", ctypes.c_int32), ("momentum_only", ctypes.c_int32),
+        ("negate_grad", ctypes.c_int32), ("mode", ctypes.c_int32),
+        ("v_floor", ctypes.c_float), ("reserved", ctypes.c_int32),
+    ]
+
+
+_c_p = ctypes.c_void_p
+_c_i = ctypes.c_int32
+_c_l = ctypes.c_int64
+_c_f = ctypes.c_float
+
+# name -> (restype, argtypes); every symbol that include/af8.h declares
+PROTOTYPES = {
+    "af8_version": (_c_i, []),
+    "af8_last_error": (ctypes.c_char_p, []),
+    "af8_set_qmap": (_c_i, [_c_p, _c_p, _c_p]),
+    "af8_fullrank_step": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
+    "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
+    "af8_al_dequant": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_i, _c_i, _c_p, _c_p]),
+    "af8_al_quant": (_c_i, [_c_p, _c_l, _c_i, _c_i, _c_f, _c_p, _c_p, _c_p, _c_p]),
+    "af8_m_dequant": (_c_i, [_c_p, _c_p, _c_l, _c_i, _c_i, _c_p, _c_p]),
+    "af8_m_quant": (_c_i, [_c_p, _c_l, _c_i, _c_i, _c_p, _c_p, _c_p]),
+}
+
+_lib = None
+
+
+def library_path():
+    return os.environ.get("AF8_LIBRARY", _DEFAULT_LIB)
+
+
+def lib():
+    """Load libaf8.so once.  Raises RuntimeError when it cannot be loaded."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"libaf8.so not found at {path}; build it with "
+                f"`python adafactor-8bit_b200/build.py` (this package has no CPU or PyTorch fallback)")
+        try:
+            handle = ctypes.CDLL(path)
+        except OSError as e:  # missing libcudart and the like
+            raise RuntimeError(f"cannot load {path}: {e}") from e
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc, what):
+    if rc != OK:
+        msg = lib().af8_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed (code {rc}): {msg}")
+
+
+def version():
+    return lib().af8_version()

@@ -1,0 +1,452 @@
+"""`Adafactor8Bit`: the reference's optimizer class, served by libaf8.
+
+The constructor signature, the argument checks, `param_groups`, the per-
+parameter state keys / dtypes and the two extra `state_dict` entries are those
+of the reference (adafactor8bit/optimizer.py:1313-1467), so code written for
+the reference runs unchanged.  What differs is how a step executes: the
+reference walks the parameters one by one and issues 1-8 kernels (or ~25 torch
+ops) per tensor; here the parameters of a group are sorted into launch plans
+and every plan runs one multi-tensor kernel per pass.
+
+There is no PyTorch or CPU path in this class: parameters must live on a CUDA
+device and libaf8.so must be loadable.  `use_cuda_kernel` is accepted for
+compatibility and ignored.
+"""
+import logging
+import math
+from typing import Any, Dict, Iterable, Optional, Tuple, Union
+
+import numpy as np
+import torch
+from torch import Tensor
+from torch.optim import Optimizer
+
+from . import _native as N
+from ._engine import FullrankPlan
+
+__all__ = ["Adafactor8Bit"]
+
+logger = logging.getLogger(__name__)
+
+_FLOOR = 1.17549435e-38                                   # optimizer.py:23
+_M_TYPES = ("uf4", "uf8", "d4", "d8", "fp32")              # optimizer.py:24
+_V_TYPES = ("al8", "al16", "fp32")                         # optimizer.py:25
+f32 = np.float32
+
+
+def _pad_to(n, block):
+    return (block - n % block) % block
+
+
+def _new_al_state(state, prefix, shape, block, device, fmt):
+    """Zero-initialised AL state (optimizer.py:389-401): codes 0, scale 1, min_log 0."""
+    numel = int(math.prod(shape)) if not isinstance(shape, int) else shape
+    if fmt == "fp32":
+        state[prefix] = torch.zeros(shape, dtype=torch.float32, device=device)
+        return
+    pad = _pad_to(numel, block)
+    nblocks = (numel + pad) // block
+    state[prefix + "_q"] = torch.zeros(numel + pad, dtype=torch.uint8 if fmt == "al8" else torch.int16, device=device)
+    state[prefix + "_scale"] = torch.ones(nblocks, dtype=torch.float32, device=device)
+    state[prefix + "_min_log"] = torch.zeros(nblocks, dtype=torch.float32, device=device)
+    state[prefix + "_shape"] = shape
+    state[prefix + "_pad"] = pad
+
+
+def _new_m_state(state, numel, m_block, fmt, device, shape, prefix="m"):
+    """Zero momentum (optimizer.py:574-590): the code of 0.0 with scale 1."""
+    if fmt == "fp32":
+        state[prefix] = torch.zeros(shape, dtype=torch.float32, device=device)
+    else:
+        padded = ((numel + m_block - 1) // m_block) * m_block
+        if fmt in ("uf4", "d4"):
+            fill, count = (0x88 if fmt == "uf4" else 0x77), padded // 2
+        else:
+            fill, count = (128 if fmt == "uf8" else 127), padded
+        state[prefix + "_q"] = torch.full((count,), fill, dtype=torch.uint8, device=device)
+        state[prefix + "_scale"] = torch.ones(padded // m_block, dtype=torch.float32, device=device)
+        state["m_block_size"] = m_block
+    state["m_quant_type"] = fmt
+
+
+class Adafactor8Bit(Optimizer):
+    """Memory-efficient optimizer family (Adafactor, AdamW, RMSprop, CAME, APOLLO)
+    over block-quantised states.  See the reference's class docstring
+    (optimizer.py:1177-1311) for the meaning of every argument; names, defaults
+    and validation are identical."""
+
+    def __init__(
+        self,
+        params: Iterable[Union[Tensor, Dict[str, Any]]],
+        lr: float = 1e-2,
+        beta1: Optional[float] = None,
+        beta2: Optional[float] = None,
+        beta2_decay: Optional[float] = -0.8,
+        beta3: Optional[float] = None,
+        eps_came: float = 1e-16,
+        eps: Tuple[Optional[float], float] = (1e-30, 1e-3),
+        weight_decay: float = 0.0,
+        d: float = 1.0,
+        maximize: bool = False,
+        relative_step: bool = True,
+        scale_parameter: bool = True,
+        factored: bool = True,
+        quantize: bool = True,
+        block_size: int = 2048,
+        m_block_size: int = 256,
+        m_quant_type: str = "uf8",
+        v_quant_type: str = "al8",
+        c_quant_type: Optional[str] = None,
+        min_8bit_size: int = 4096,
+        use_cuda_kernel: bool = True,
+        stochastic_round_writeback: bool = False,
+        apollo_rank: int = 0,
+        apollo_update_proj_gap: int = 200,
+        apollo_scale_type: str = "channel",
+        apollo_scale: float = 1.0,
+        apollo_scale_front: bool = False,
+        apollo_eps: float = 1e-6,
+        apollo_factorize: bool = False,
+        apollo_cache_proj: bool = False,
+        enable_fira_for_apollo: bool = True,
+        scale_weight_decay: bool = True,
+        enable_fira_for_adafactor: bool = False,
+        fira_margin: float = 0.01,
+        lag_norm: bool = False,
+        momentum_only_1d: Optional[bool] = None,
+        bias_correction: Optional[bool] = None,
+        warmup_multiplier: float = 0.0,
+    ):
+        # argument checks, in the reference's order (optimizer.py:1362-1432)
+        if lr < 0.0:
+            raise ValueError(f"Invalid lr: {lr}, must be >= 0.0")
+        if beta1 is not None and not (0.0 <= beta1 < 1.0):
+            raise ValueError(f"Invalid beta1: {beta1}, must be in [0.0, 1.0)")
+        if beta2_decay is not None and beta2_decay > 0.0:
+            raise ValueError(f"Invalid beta2_decay: {beta2_decay}, must be <= 0.0")
+        if beta2 is None and beta2_decay is None:
+            if relative_step:
+                raise ValueError("When `beta2` and `beta2_decay` are both None, `relative_step` must be False. "
+                                 "Please set `relative_step=False` for standard SGD, or specify "
+                                 "`beta2`/`beta2_decay` to use adaptive optimizers.")
+            if apollo_rank > 0:
+                raise ValueError("APOLLO requires a second-moment estimate (`beta2` or `beta2_decay`), "
+                                 "but both are currently None.")
+            if beta3 is not None:
+                raise ValueError("CAME (`beta3`) requires both `beta1` and `beta2`, but `beta2` is currently None.")
+        eps1, eps2 = eps
+        if eps1 is None:
+            eps1 = 1e-30
+        if eps1 < 0.0:
+            raise ValueError(f"Invalid eps1: {eps1}, must be >= 0.0")
+        if eps2 < 0.0:
+            raise ValueError(f"Invalid eps2: {eps2}, must be >= 0.0")
+        if d < 0.0:
+            raise ValueError(f"Invalid d: {d}, must be >= 0.0. d=0 disables RMS clipping.")
+        if weight_decay < 0.0:
+            raise ValueError(f"Invalid weight_decay: {weight_decay}, must be >= 0.0")
+        if beta2 is not None and not (0.0 <= beta2 < 1.0):
+            raise ValueError(f"Invalid beta2: {beta2}, must be in [0.0, 1.0)")
+        if quantize and (block_size < 128 or block_size % 128 != 0):
+            raise ValueError(f"block_size must be >= 128 and a multiple of 128, but got {block_size}.")
+        if m_block_size < 32 or m_block_size % 4 != 0:
+            raise ValueError(f"m_block_size must be a multiple of 4 and >= 32, but got {m_block_size}.")
+        if m_quant_type not in _M_TYPES:
+            raise ValueError(f"m_quant_type must be one of {_M_TYPES}, got '{m_quant_type}'.")
+        if v_quant_type not in _V_TYPES:
+            raise ValueError(f"v_quant_type must be one of {_V_TYPES}, got '{v_quant_type}'.")
+        if c_quant_type is not None and c_quant_type not in _V_TYPES:
+            raise ValueError(f"c_quant_type must be one of {_V_TYPES} or None, got '{c_quant_type}'.")
+        if quantize and beta1 is not None and m_quant_type != "fp32" and block_size % m_block_size != 0:
+            raise ValueError("For the fused 1D kernel, block_size must be a multiple of m_block_size "
+                             f"(got block_size={block_size}, m_block_size={m_block_size}).")
+        if apollo_rank > 0 and apollo_scale_type not in ("channel", "tensor"):
+            raise ValueError(f"apollo_scale_type must be 'channel' or 'tensor', got {apollo_scale_type}.")
+        if apollo_scale < 0.0:
+            raise ValueError(f"Invalid apollo_scale: {apollo_scale}, must be >= 0.0")
+        if fira_margin < 0.0:
+            raise ValueError(f"Invalid fira_margin: {fira_margin}, must be >= 0.0")
+        if beta3 is not None:
+            if not (0.0 <= beta3 < 1.0):
+                raise ValueError(f"Invalid beta3: {beta3}, must be in [0.0, 1.0)")
+            if beta1 is None:
+                raise ValueError("CAME (beta3) strictly requires momentum (beta1) to compute update instability.")
+            if apollo_rank == 0 and not factored:
+                raise ValueError("CAME (beta3) requires factored=True (2D row/col factorization). "
+                                 "It is not supported for 1D full-rank paths.")
+
+        defaults = dict(
+            lr=lr, beta1=beta1, beta2=beta2, beta2_decay=beta2_decay, beta3=beta3, eps_came=eps_came,
+            eps=eps, weight_decay=weight_decay, d=d, maximize=maximize,
+            relative_step=relative_step, scale_parameter=scale_parameter, factored=factored,
+            quantize=quantize, block_size=block_size, m_block_size=m_block_size,
+            m_quant_type=m_quant_type, v_quant_type=v_quant_type, c_quant_type=c_quant_type,
+            min_8bit_size=min_8bit_size, use_cuda_kernel=use_cuda_kernel,
+            stochastic_round_writeback=stochastic_round_writeback,
+            apollo_rank=apollo_rank, apollo_update_proj_gap=apollo_update_proj_gap,
+            apollo_scale_type=apollo_scale_type, apollo_scale=apollo_scale,
+            apollo_scale_front=apollo_scale_front, apollo_eps=apollo_eps,
+            apollo_factorize=apollo_factorize, apollo_cache_proj=apollo_cache_proj,
+            enable_fira_for_apollo=enable_fira_for_apollo,
+            scale_weight_decay=scale_weight_decay,
+            enable_fira_for_adafactor=enable_fira_for_adafactor, fira_margin=fira_margin,
+            lag_norm=lag_norm, momentum_only_1d=momentum_only_1d, bias_correction=bias_correction,
+            warmup_multiplier=warmup_multiplier,
+        )
+        super().__init__(params, defaults)
+        self._apollo_seed_counter = 1          # optimizer.py:1460-1461
+        self._sr_seed_counter = 1
+        self._plans = {}
+
+    # ------------------------------------------------------------------
+    # checkpointing (optimizer.py:1463-1553)
+    # ------------------------------------------------------------------
+    def state_dict(self):
+        sd = super().state_dict()
+        sd["_apollo_seed_counter"] = self._apollo_seed_counter
+        sd["_sr_seed_counter"] = self._sr_seed_counter
+        return sd
+
+    def load_state_dict(self, state_dict):
+        state_dict = dict(state_dict)
+        self._apollo_seed_counter = state_dict.pop("_apollo_seed_counter", self._apollo_seed_counter)
+        self._sr_seed_counter = state_dict.pop("_sr_seed_counter", self._sr_seed_counter)
+        # torch's loader casts floating-point state to the parameter's dtype and
+        # moves everything to its device; remember the saved dtypes and restore
+        # them afterwards (the reference does the same, optimizer.py:1482-1539)
+        saved = {idx: {k: v.dtype for k, v in st.items() if isinstance(v, Tensor)}
+                 for idx, st in state_dict["state"].items()}
+        saved_vals = {idx: {k: v for k, v in st.items() if isinstance(v, Tensor)}
+                      for idx, st in state_dict["state"].items()}
+        super().load_state_dict(state_dict)
+        idx_of = {}
+        i = 0
+        for g in self.param_groups:
+            for p in g["params"]:
+                idx_of[p] = i
+                i += 1
+        keys = list(saved.keys())
+        for p, st in self.state.items():
+            idx = idx_of.get(p)
+            src = saved.get(idx, saved.get(str(idx)))
+            if src is None:
+                continue
+            vals = saved_vals.get(idx, saved_vals.get(str(idx)))
+            for k, dt in src.items():
+                if k in st and isinstance(st[k], Tensor) and st[k].dtype != dt:
+                    st[k] = vals[k].to(device=p.device, dtype=dt).clone()
+            if "step" in st and isinstance(st["step"], Tensor):
+                st["step"] = int(st["step"].item())
+        del keys
+        self._plans.clear()
+
+    def update_norms(self):
+        """Norms of the updates measured by the last step's statistic passes, one
+        per tensor of every launch plan (zeros where no norm was needed).  Reads
+        them back from the device, so it synchronises."""
+        out = [plan.norms() for plan in self._plans.values()]
+        return np.concatenate(out) if out else np.zeros(0, dtype=np.float32)
+
+    # ------------------------------------------------------------------
+    # lazy state creation (first-step branch of _init_group, optimizer.py:1711-1773)
+    # ------------------------------------------------------------------
+    def _create_state(self, p, grad, group):
+        state = self.state[p]
+        numel = p.numel()
+        use_quant = group.get("quantize", True) and not (numel < group.get("min_8bit_size", 4096))
+        block = group.get("block_size", 2048)
+        m_block = group.get("m_block_size", 256)
+        vqt = group.get("v_quant_type", "al8")
+        cqt = group.get("c_quant_type") or vqt
+        mqt = group.get("m_quant_type", "uf8")
+        beta1, beta3 = group.get("beta1"), group.get("beta3")
+        sgd = group.get("beta2") is None and group.get("beta2_decay") is None
+        if "step" not in state:
+            state["step"] = 0
+        state["is_quantized"] = use_quant
+        state["block_size"] = block
+        state["v_quant_type"] = vqt
+        state["c_quant_type"] = cqt
+        dev = p.device
+        v_fmt = vqt if use_quant else "fp32"
+        c_fmt = cqt if use_quant else "fp32"
+        m_fmt = mqt if use_quant else "fp32"
+        if sgd:
+            if beta1 is not None:
+                _new_m_state(state, numel, m_block, m_fmt, dev, p.shape)
+        elif group.get("apollo_rank", 0) > 0 and grad.dim() >= 2:
+            seed = self._apollo_seed_counter
+            self._apollo_seed_counter += 1
+            gap = group.get("apollo_update_proj_gap", 200)
+            state.update(apollo_seed=seed, apollo_rank=group["apollo_rank"],
+                         apollo_factorize=group.get("apollo_factorize", False), beta3=beta3,
+                         apollo_update_proj_gap=gap, last_proj_step=-gap,
+                         apollo_proj_matrix_T=None, m_quant_type=mqt)
+            for k in ("v_low_q", "v_low_scale", "v_low_min_log", "v_low_shape", "v_low_pad", "v_low"):
+                state[k] = None
+        elif grad.dim() >= 2 and group.get("factored", True):
+            shape = grad.shape
+            r_shape = list(shape[:-2]) + [shape[-2], 1]
+            c_shape = list(shape[:-2]) + [1, shape[-1]]
+            _new_al_state(state, "row_var", r_shape, block, dev, v_fmt)
+            _new_al_state(state, "col_var", c_shape, block, dev, v_fmt)
+            if beta1 is not None:
+                _new_m_state(state, numel, m_block, m_fmt, dev, p.shape)
+            if beta3 is not None:
+                _new_al_state(state, "conf_row", r_shape, block, dev, c_fmt)
+                _new_al_state(state, "conf_col", c_shape, block, dev, c_fmt)
+        else:
+            _new_al_state(state, "variance", grad.shape, block, dev, v_fmt)
+            if beta1 is not None:
+                _new_m_state(state, numel, m_block, m_fmt, dev, p.shape)
+        return state
+
+    # ------------------------------------------------------------------
+    # per-step host scalars (optimizer.py:1957-2040, 832-856)
+    # ------------------------------------------------------------------
+    @staticmethod
+    def _step_scalars(group, step):
+        """Scalars of one parameter at step `step` that do not depend on tensor
+        contents, rounded to binary32 where the reference's 0-d tensors round."""
+        eps1, eps2 = group["eps"]
+        if eps1 is None:
+            eps1 = 1e-30
+        beta1, beta2, beta3 = group.get("beta1"), group["beta2"], group.get("beta3")
+        factored = group.get("factored", True)
+        adam = (not factored) and beta2 is not None and beta3 is None
+        eps_denom = eps1 if adam else 0.0
+        eps_gradsq = 0.0 if adam else eps1
+        relative = group["relative_step"]
+        if beta2 is not None:
+            beta_val = 1.0 - beta2
+        elif group["beta2_decay"] is not None:
+            beta_val = math.pow(step, group["beta2_decay"])
+        else:
+            beta_val = 0.0
+        lr = float(group["lr"])
+        rho = f32(min(lr, 1.0 / math.sqrt(step)) if relative else lr)
+        bc_mul = None      # multiplies alpha
+        bc_div = None      # divides alpha
+        if beta1 is not None and not relative and not (beta2 is None and group["beta2_decay"] is None):
+            apply_bc = adam if group.get("bias_correction") is None else group["bias_correction"]
+            if apply_bc:
+                bc1 = 1.0 - beta1 ** step
+                if beta2 is not None:
+                    bc2 = 1.0 - beta2 ** step
+                    bc_mul = f32(math.sqrt(bc2) / bc1)
+                    if adam:
+                        eps_denom = eps1 * math.sqrt(bc2)
+                else:
+                    bc_div = f32(bc1)
+        return dict(eps1=eps1, eps2=eps2, adam=adam, beta_val=beta_val, rho=rho,
+                    bc_mul=bc_mul, bc_div=bc_div, eps_denom=eps_denom, eps_gradsq=eps_gradsq,
+                    eps_sq=max(eps1 * eps1, _FLOOR))
+
+    @staticmethod
+    def _alpha_decay(group, sc):
+        """alpha and the weight-decay factor when alpha does not depend on the
+        parameter's RMS (scale_parameter=False)."""
+        alpha = sc["rho"]
+        if sc["bc_mul"] is not None:
+            alpha = f32(alpha * sc["bc_mul"])
+        elif sc["bc_div"] is not None:
+            alpha = f32(alpha / sc["bc_div"])
+        wd = group["weight_decay"]
+        if wd != 0:
+            mult = alpha if group.get("scale_weight_decay", True) else sc["rho"]
+            decay = f32(f32(1.0) - f32(mult * f32(wd)))
+        else:
+            decay = f32(1.0)
+        return alpha, decay
+
+    # ------------------------------------------------------------------
+    # step
+    # ------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        N.lib()   # fail loudly when the CUDA library is missing
+        for gi, group in enumerate(self.param_groups):
+            entries = []
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if not p.is_cuda:
+                    raise RuntimeError("Adafactor8Bit (B200 build) only updates CUDA parameters; "
+                                       "there is no CPU path")
+                state = self.state[p]
+                if len(state) == 0 or "is_quantized" not in state:
+                    state = self._create_state(p, p.grad, group)
+                entries.append((p, p.grad, state))
+            if entries:
+                self._run_group(gi, group, entries)
+        return loss
+
+    def _run_group(self, gi, group, entries):
+        apollo_rank = group.get("apollo_rank", 0)
+        factored = group.get("factored", True)
+        sgd = group["beta2"] is None and group["beta2_decay"] is None
+        fullrank = {}
+        for p, g, st in entries:
+            if sgd:
+                raise NotImplementedError("the SGD preset is not available in this build")
+            if apollo_rank > 0 and "apollo_seed" in st:
+                raise NotImplementedError("the APOLLO path is not available in this build")
+            if g.dim() >= 2 and factored:
+                raise NotImplementedError("the factored path is not available in this build")
+            quant = st.get("is_quantized", False)
+            v_fmt = st.get("v_quant_type", "al8") if quant else "fp32"
+            if group.get("beta1") is not None:
+                m_fmt = st.get("m_quant_type", "uf8")
+                if "m" in st:
+                    m_fmt = "fp32"
+                m_block = st.get("m_block_size", group.get("m_block_size", 256))
+            else:
+                m_fmt, m_block = None, 0
+            key = (p.device, g.dtype, v_fmt, m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block)
+            fullrank.setdefault(key, []).append((p, g, st))
+        for key, items in fullrank.items():
+            self._run_fullrank(gi, group, key, items)
+
+    def _run_fullrank(self, gi, group, key, items):
+        device, gdtype, v_fmt, m_fmt, block, m_block = key
+        sc0 = self._step_scalars(group, 1)
+        momentum_only = group.get("momentum_only_1d")
+        if momentum_only is None:
+            momentum_only = not sc0["adam"]
+        ids = tuple(id(p) for p, _, _ in items)
+        pkey = (gi, "fullrank", key, bool(momentum_only), bool(group["maximize"]))
+        plan = self._plans.get(pkey)
+        if plan is None or plan.ids != ids:
+            plan = FullrankPlan(device, gdtype, v_fmt, m_fmt, block, m_block, sc0["adam"], momentum_only,
+                                group["maximize"], [p for p, _, _ in items], [s for _, _, s in items])
+            plan.ids = ids
+            self._plans[pkey] = plan
+        if group["scale_parameter"]:
+            raise NotImplementedError("scale_parameter=True is not available in this build")
+        n = len(items)
+        cols = {k: np.empty(n, dtype=f32) for k in
+                ("decay", "alpha", "v_w", "v_keep", "v_eps_add", "m_w", "eps_gradsq", "eps_denom", "eps_sq")}
+        cache = {}
+        grads = []
+        for i, (p, g, st) in enumerate(items):
+            step = st["step"] + 1
+            st["step"] = step
+            vals = cache.get(step)
+            if vals is None:
+                sc = self._step_scalars(group, step)
+                alpha, decay = self._alpha_decay(group, sc)
+                bv = sc["beta_val"]
+                vals = (decay, alpha, f32(bv), f32(1.0 - bv), f32(bv * sc["eps_gradsq"]),
+                        f32(1.0 - group["beta1"]) if group.get("beta1") is not None else f32(0.0),
+                        f32(sc["eps_gradsq"]), f32(sc["eps_denom"]), f32(sc["eps_sq"]))
+                cache[step] = vals
+            for k, v in zip(cols, vals):
+                cols[k][i] = v
+            grads.append(g if g.is_contiguous() else g.contiguous())
+        with torch.cuda.device(device):
+            plan.run(grads, cols, d=float(group["d"]), fira=bool(group.get("enable_fira_for_adafactor", False)),
+                     fira_margin=float(group.get("fira_margin", 0.01)))

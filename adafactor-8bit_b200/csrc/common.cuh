@@ -1,0 +1,170 @@
+// Shared host/device helpers of libaf8: error reporting, exactly rounded
+// scalar primitives and warp/block reductions.
+//
+// Arithmetic contract.  The optimizer whose results this library must
+// reproduce runs as a sequence of torch CPU ops, each of which rounds once to
+// binary32 (reference: adafactor8bit/optimizer.py, pure-PyTorch path).  Every
+// device function here therefore uses the explicitly rounded intrinsics
+// (__fadd_rn, __fmul_rn, __fdiv_rn, __fsqrt_rn, __fmaf_rn), which the compiler
+// never contracts or replaces by approximations, and the library is compiled
+// with -fmad=false, without --use_fast_math and without flush-to-zero.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <math.h>
+
+#include "../../include/af8.h"
+
+namespace af8 {
+
+// ---------------------------------------------------------------------------
+// host: error reporting
+// ---------------------------------------------------------------------------
+inline char *error_buffer()
+{
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+inline int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define AF8_CUDA_TRY(expr)                                                          \
+    do {                                                                            \
+        cudaError_t e__ = (expr);                                                   \
+        if (e__ != cudaSuccess)                                                     \
+            return af8::fail(AF8_ERR_CUDA, "%s failed: %s", #expr,                  \
+                             cudaGetErrorString(e__));                              \
+    } while (0)
+
+inline int sm_count()
+{
+    static thread_local int cached_dev = -1;
+    static thread_local int cached_sms = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached_dev = dev;
+        cached_sms = n;
+    }
+    return cached_sms;
+}
+
+// ---------------------------------------------------------------------------
+// device: scalar primitives
+// ---------------------------------------------------------------------------
+// log2(1e-38f), the value torch.log2 returns for every element that
+// clamp(min=1e-38) lifted (optimizer.py:309-310).
+#define AF8_LOG2_TINY (-126.23327f)
+#define AF8_TINY 1e-38f
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+
+// Tensor.lerp_(end, w) as ATen computes it (optimizer.py:698, 2119).
+__device__ __forceinline__ float lerp_t(float s, float e, float w)
+{
+    float d = __fsub_rn(e, s);
+    return (fabsf(w) < 0.5f) ? __fmaf_rn(w, d, s) : __fmaf_rn(__fsub_rn(w, 1.0f), d, e);
+}
+
+// Correctly rounded log2 of a positive finite float: evaluated in binary64
+// (error below 1 ulp of binary64) and rounded once.
+__device__ __forceinline__ float log2_cr(float x) { return __double2float_rn(log2((double)x)); }
+
+// Correctly rounded 2^x.
+__device__ __forceinline__ float exp2_cr(float x) { return __double2float_rn(exp2((double)x)); }
+
+// torch.rsqrt on CPU: one rounded sqrt, then one rounded reciprocal.
+__device__ __forceinline__ float rsqrt_t(float x) { return __frcp_rn(__fsqrt_rn(x)); }
+
+// log2 of a second-moment value as _log_quantize_nonneg sees it
+// (optimizer.py:308-310): values below 1e-38 (zero included) are lifted to 1e-38.
+__device__ __forceinline__ float al_log2(float v) { return (v > AF8_TINY) ? log2_cr(v) : AF8_LOG2_TINY; }
+
+// AL dequantisation of one code (optimizer.py:341-349).  qm1 = levels - 2.
+__device__ __forceinline__ float al_decode(uint32_t code, float scale, float min_log, float qm1)
+{
+    if (code == 0) return 0.0f;
+    float t = __fmul_rn((float)(code - 1), scale);
+    t = __fdiv_rn(t, qm1);
+    t = __fadd_rn(t, min_log);
+    return exp2_cr(t);
+}
+
+// Block range of _log_quantize_nonneg from the reduced extrema
+// (optimizer.py:315-318).  mn = min of log2 over non-zero elements (+inf if
+// none), mx = max over all elements.
+__device__ __forceinline__ void al_range(float mn, float mx, float floor_log, float &min_log, float &scale)
+{
+    mn = fmaxf(mn, floor_log);
+    if (mn >= mx) mn = __fsub_rn(mx, 1.0f);
+    float s = __fsub_rn(mx, mn);
+    scale = fmaxf(s, 1e-12f);
+    min_log = mn;
+}
+
+// AL code of one element (optimizer.py:320-321).  l = al_log2(v).
+__device__ __forceinline__ uint32_t al_encode(float v, float l, float min_log, float scale, float qm1, int qmax)
+{
+    if (v == 0.0f) return 0u;
+    float t = __fdiv_rn(__fsub_rn(l, min_log), scale);
+    t = __fmul_rn(t, qm1);
+    int q = __float2int_rn(t) + 1;   // round half to even, like torch.round
+    q = max(1, min(q, qmax));
+    return (uint32_t)q;
+}
+
+// UF8 / UF4 code of one element (optimizer.py:512, 518).  a = block absmax >= 1e-12.
+__device__ __forceinline__ uint32_t uf8_encode(float m, float a)
+{
+    float t = __fmul_rn(__fdiv_rn(m, a), 128.0f);
+    int q = __float2int_rn(t);
+    q = max(-128, min(q, 127));
+    return (uint32_t)(q + 128);
+}
+
+__device__ __forceinline__ uint32_t uf4_encode(float m, float a)
+{
+    float t = __fmul_rn(__fdiv_rn(m, a), 8.0f);
+    int q = __float2int_rn(t);
+    q = max(-8, min(q, 7));
+    return (uint32_t)(q + 8);
+}
+
+// ---------------------------------------------------------------------------
+// device: reductions
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float warp_max(float x)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+    return x;
+}
+
+__device__ __forceinline__ float warp_min(float x)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x = fminf(x, __shfl_xor_sync(0xffffffffu, x, o));
+    return x;
+}
+
+__device__ __forceinline__ float warp_sum(float x)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x = __fadd_rn(x, __shfl_xor_sync(0xffffffffu, x, o));
+    return x;
+}
+
+}  // namespace af8

@@ -1,0 +1,224 @@
+// Host side of the full-rank step: argument validation, kernel selection and
+// launch (af8_fullrank_step), and the per-tensor norm / Fira / clip finaliser
+// (af8_norm_finalize).
+#pragma once
+
+#include "common.cuh"
+#include "fullrank_fast.cuh"
+#include "fullrank_generic.cuh"
+
+namespace af8 {
+
+// ---------------------------------------------------------------------------
+// norm finaliser: one CTA per tensor
+// ---------------------------------------------------------------------------
+// Reduces the tensor's per-block partial sums in a fixed order in binary64,
+// then evaluates on one thread what the reference computes with 0-d tensors:
+// _compute_fira_scale (optimizer.py:760-782), the clip denominators of
+// _apply_fira_pytorch / _safe_rms_denom (optimizer.py:805-806, 859-863) and
+// -alpha/denom (optimizer.py:874); in pre_div_mode 1 the RMS clip of the
+// momentum-only rule (optimizer.py:897-899).
+__global__ void __launch_bounds__(256)
+norm_finalize_kernel(const af8_norm_tensor *tensors, const float *block_sumsq, af8_dyn_scalars *dyn)
+{
+    __shared__ double s_acc[256];
+    const af8_norm_tensor T = tensors[blockIdx.x];
+    const int tid = threadIdx.x;
+    double acc = 0.0;
+    for (int64_t i = tid; i < T.n_blocks; i += 256) acc += (double)block_sumsq[T.first_block + i];
+    s_acc[tid] = acc;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (tid < o) s_acc[tid] += s_acc[tid + o];
+        __syncthreads();
+    }
+    if (tid != 0) return;
+
+    float norm = __double2float_rn(sqrt(s_acc[0]));
+    af8_dyn_scalars out = dyn[blockIdx.x];
+    out.norm = norm;
+    if (T.pre_div_mode == 1) {
+        const float rms = __fdiv_rn(norm, T.sqrt_n);
+        float cf = __fdiv_rn(rms, T.d);
+        cf = (cf >= 1.0f || isnan(cf)) ? cf : 1.0f;
+        out.pre_div = cf;
+        out.step = -T.alpha;
+        out.fira = 1.0f;
+        out.zero = 0.0f;
+        dyn[blockIdx.x] = out;
+        return;
+    }
+    float fs = 1.0f;
+    float zero = 0.0f;
+    if (T.fira_prev != nullptr) {
+        if (!isfinite(norm)) { zero = 1.0f; norm = 0.0f; }       // optimizer.py:798-800
+        if (T.fira_has_prev) {
+            const float fp = *T.fira_prev;
+            const bool reset = fp < 1e-6f;                          // optimizer.py:774
+            const float ratio = __fdiv_rn(norm, __fadd_rn(fp, 1e-8f));
+            const float lim = __fdiv_rn(fmaxf(ratio, T.fira_margin1), T.fira_margin1);
+            fs = reset ? 1.0f : __frcp_rn(lim);                     // optimizer.py:777
+            *T.fira_prev = reset ? norm : __fmul_rn(norm, fs);      // optimizer.py:778
+        } else {
+            *T.fira_prev = norm;                                    // optimizer.py:780-781
+        }
+    }
+    float denom = 1.0f;
+    if (T.clip_div > 0.0f) {
+        const float x = __fdiv_rn(norm, T.clip_div);
+        denom = (x >= 1.0f || isnan(x)) ? x : 1.0f;
+    }
+    out.step = __fdiv_rn(-T.alpha, denom);
+    out.fira = fs;
+    out.zero = zero;
+    if (T.pre_div_mode != 2) out.pre_div = 1.0f;
+    dyn[blockIdx.x] = out;
+}
+
+// ---------------------------------------------------------------------------
+// launch helpers
+// ---------------------------------------------------------------------------
+template <typename K>
+inline int persistent_grid(K kernel, int threads, size_t smem, int64_t total_blocks, int *grid_out)
+{
+    int per_sm = 0;
+    AF8_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
+    if (per_sm < 1) return fail(AF8_ERR_CUDA, "kernel does not fit on an SM (threads=%d smem=%zu)", threads, smem);
+    int64_t g = (int64_t)per_sm * sm_count();
+    if (g > total_blocks) g = total_blocks;
+    *grid_out = (int)g;
+    return AF8_OK;
+}
+
+template <typename GradT, int MODE>
+inline int launch_fast(const FullrankLaunch &L, cudaStream_t st)
+{
+    int grid = 0;
+    int rc = persistent_grid(fullrank_fast_kernel<GradT, MODE>, FAST_THREADS, 0, L.total_blocks, &grid);
+    if (rc) return rc;
+    fullrank_fast_kernel<GradT, MODE><<<grid, FAST_THREADS, 0, st>>>(L);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+template <typename GradT, int MODE>
+inline int launch_generic(const FullrankLaunch &L, const GenericCfg &C, cudaStream_t st)
+{
+    const size_t smem = (size_t)2 * C.block * sizeof(float);
+    auto kernel = fullrank_generic_kernel<GradT, MODE>;
+    if (smem > 48 * 1024)
+        AF8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int grid = 0;
+    int rc = persistent_grid(kernel, GEN_THREADS, smem, L.total_blocks, &grid);
+    if (rc) return rc;
+    kernel<<<grid, GEN_THREADS, smem, st>>>(L, C);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+template <typename GradT>
+inline int dispatch_mode(bool fast, int mode, const FullrankLaunch &L, const GenericCfg &C, cudaStream_t st)
+{
+    switch (mode) {
+    case AF8_MODE_NOCLIP:
+        return fast ? launch_fast<GradT, AF8_MODE_NOCLIP>(L, st) : launch_generic<GradT, AF8_MODE_NOCLIP>(L, C, st);
+    case AF8_MODE_SUMSQ:
+        return fast ? launch_fast<GradT, AF8_MODE_SUMSQ>(L, st) : launch_generic<GradT, AF8_MODE_SUMSQ>(L, C, st);
+    case AF8_MODE_APPLY:
+        return fast ? launch_fast<GradT, AF8_MODE_APPLY>(L, st) : launch_generic<GradT, AF8_MODE_APPLY>(L, C, st);
+    default:
+        return launch_generic<GradT, AF8_MODE_SUMSQ_M>(L, C, st);
+    }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int validate_fullrank_table(const af8_fullrank_cfg &c, const af8_fullrank_tensor *T, int n, int64_t total_blocks)
+{
+    int64_t next = 0;
+    const bool v_quant = c.v_fmt != AF8_V_FP32;
+    const bool has_m = c.m_fmt != AF8_M_NONE;
+    const bool m_quant = has_m && c.m_fmt != AF8_M_FP32;
+    for (int i = 0; i < n; ++i) {
+        const af8_fullrank_tensor &t = T[i];
+        if (t.numel <= 0) return fail(AF8_ERR_INVALID, "tensor %d: numel must be positive", i);
+        if (t.first_block != next) return fail(AF8_ERR_INVALID, "tensor %d: first_block %lld, expected %lld", i, (long long)t.first_block, (long long)next);
+        next += (t.numel + c.block - 1) / c.block;
+        if (!t.param || !t.grad) return fail(AF8_ERR_INVALID, "tensor %d: null param or grad", i);
+        if (!aligned16(t.param) || !aligned16(t.grad)) return fail(AF8_ERR_INVALID, "tensor %d: param and grad must be 16-byte aligned", i);
+        if (v_quant) {
+            if (!t.v_q || !t.v_scale || !t.v_min_log) return fail(AF8_ERR_INVALID, "tensor %d: null quantised V state", i);
+            if (!aligned16(t.v_q)) return fail(AF8_ERR_INVALID, "tensor %d: v_q must be 16-byte aligned", i);
+        } else if (!t.v_f32) {
+            return fail(AF8_ERR_INVALID, "tensor %d: null fp32 V state", i);
+        }
+        if (m_quant) {
+            if (!t.m_q || !t.m_scale) return fail(AF8_ERR_INVALID, "tensor %d: null quantised M state", i);
+            if (!aligned16(t.m_q)) return fail(AF8_ERR_INVALID, "tensor %d: m_q must be 16-byte aligned", i);
+        } else if (has_m && !t.m_f32) {
+            return fail(AF8_ERR_INVALID, "tensor %d: null fp32 M state", i);
+        }
+    }
+    if (next != total_blocks) return fail(AF8_ERR_INVALID, "total_blocks is %lld but the table holds %lld blocks", (long long)total_blocks, (long long)next);
+    return AF8_OK;
+}
+
+}  // namespace af8
+
+extern "C" int af8_fullrank_step(const af8_fullrank_cfg *cfg, const af8_fullrank_tensor *host_tensors,
+                                 af8_fullrank_tensor *dev_tensors, int32_t n_tensors, int64_t total_blocks,
+                                 const af8_dyn_scalars *dyn, float *block_sumsq, void *stream)
+{
+    using namespace af8;
+    if (!cfg || !dev_tensors) return fail(AF8_ERR_INVALID, "af8_fullrank_step: null cfg or table");
+    if (n_tensors <= 0 || total_blocks <= 0) return fail(AF8_ERR_INVALID, "af8_fullrank_step: empty launch (n_tensors=%d, total_blocks=%lld)", n_tensors, (long long)total_blocks);
+    const af8_fullrank_cfg &c = *cfg;
+    if (c.param_dtype != AF8_F32) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: only fp32 parameters are supported");
+    if (c.grad_dtype != AF8_F32 && c.grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: gradients must be fp32 or bf16");
+    if (c.v_fmt != AF8_V_FP32 && c.v_fmt != AF8_V_AL8 && c.v_fmt != AF8_V_AL16) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad v_fmt %d", c.v_fmt);
+    if (c.m_fmt < AF8_M_NONE || c.m_fmt > AF8_M_FP32) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad m_fmt %d", c.m_fmt);
+    if (c.block < 128 || c.block % 128 != 0) return fail(AF8_ERR_INVALID, "af8_fullrank_step: block must be a multiple of 128, >= 128 (got %d)", c.block);
+    if (c.block > GEN_MAX_BLOCK) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: block %d exceeds the supported maximum %d", c.block, GEN_MAX_BLOCK);
+    const bool m_quant = c.m_fmt != AF8_M_NONE && c.m_fmt != AF8_M_FP32;
+    if (m_quant && (c.m_block < 32 || c.m_block % 4 != 0 || c.block % c.m_block != 0))
+        return fail(AF8_ERR_INVALID, "af8_fullrank_step: m_block must be a multiple of 4, >= 32 and divide block (got %d, block %d)", c.m_block, c.block);
+    if (c.mode < AF8_MODE_NOCLIP || c.mode > AF8_MODE_SUMSQ_M) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad mode %d", c.mode);
+    if ((c.mode == AF8_MODE_APPLY || c.mode == AF8_MODE_SUMSQ_M) && !dyn) return fail(AF8_ERR_INVALID, "af8_fullrank_step: this mode needs dyn");
+    if ((c.mode == AF8_MODE_SUMSQ || c.mode == AF8_MODE_SUMSQ_M) && !block_sumsq) return fail(AF8_ERR_INVALID, "af8_fullrank_step: this mode needs block_sumsq");
+    if (c.mode == AF8_MODE_SUMSQ_M && !(c.momentum_only && c.m_fmt != AF8_M_NONE)) return fail(AF8_ERR_INVALID, "af8_fullrank_step: SUMSQ_M needs the momentum-only rule");
+    if (c.momentum_only && c.use_adam_denom) return fail(AF8_ERR_INVALID, "af8_fullrank_step: momentum_only excludes the Adam denominator");
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (host_tensors) {
+        int rc = validate_fullrank_table(c, host_tensors, n_tensors, total_blocks);
+        if (rc) return rc;
+        AF8_CUDA_TRY(cudaMemcpyAsync(dev_tensors, host_tensors, sizeof(af8_fullrank_tensor) * (size_t)n_tensors, cudaMemcpyHostToDevice, st));
+    }
+
+    FullrankLaunch L;
+    L.tensors = dev_tensors;
+    L.dyn = dyn;
+    L.block_sumsq = block_sumsq;
+    L.total_blocks = total_blocks;
+    L.n_tensors = n_tensors;
+    L.negate_grad = c.negate_grad ? 1 : 0;
+    L.v_floor = c.v_floor;
+    GenericCfg C{c.v_fmt, c.m_fmt, c.block, c.m_block, c.use_adam_denom ? 1 : 0, c.momentum_only ? 1 : 0};
+
+    const bool fast = c.v_fmt == AF8_V_AL8 && c.m_fmt == AF8_M_UF8 && c.block == FAST_VBLOCK &&
+                      c.m_block == FAST_MBLOCK && c.use_adam_denom && !c.momentum_only &&
+                      c.mode != AF8_MODE_SUMSQ_M;
+    if (c.grad_dtype == AF8_BF16) return dispatch_mode<bf16_tag>(fast, c.mode, L, C, st);
+    return dispatch_mode<float>(fast, c.mode, L, C, st);
+}
+
+extern "C" int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors, const float *block_sumsq,
+                                 af8_dyn_scalars *dyn, void *stream)
+{
+    using namespace af8;
+    if (!tensors || !block_sumsq || !dyn) return fail(AF8_ERR_INVALID, "af8_norm_finalize: null argument");
+    if (n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_norm_finalize: n_tensors must be positive");
+    norm_finalize_kernel<<<n_tensors, 256, 0, static_cast<cudaStream_t>(stream)>>>(tensors, block_sumsq, dyn);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}

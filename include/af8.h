@@ -1,0 +1,221 @@
+/*
+ * af8.h -- C ABI of libaf8: the fused optimizer step over block-quantised
+ * states (AL8/AL16 second moments, UF8/UF4/d8/d4 momentum) for NVIDIA B200
+ * (sm_100a).
+ *
+ * The library replaces the reference's pybind11 module `adafactor8bit_cuda`
+ * (kernels.cu:3088-3151).  Where the reference passes torch::Tensor objects and
+ * launches one kernel per parameter tensor, this ABI takes raw device
+ * pointers, 64-bit sizes and a stream, and every step entry point works on a
+ * whole TABLE of tensors in one launch.
+ *
+ * Conventions
+ *   - every function returns AF8_OK (0) or an AF8_ERR_* code; af8_last_error()
+ *     returns the message of the calling thread's last failure;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and
+ *     no entry point synchronises the device;
+ *   - the caller owns all memory; the library keeps nothing between calls
+ *     except the two dynamic-map codebooks in constant memory;
+ *   - tensor tables (`af8_*_tensor` arrays) live in DEVICE memory; they are
+ *     filled on the host and copied by the caller;
+ *   - the current device must be the one that owns the pointers.
+ */
+#ifndef AF8_H
+#define AF8_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AF8_VERSION 1
+
+#if defined(__GNUC__)
+#define AF8_API __attribute__((visibility("default")))
+#else
+#define AF8_API
+#endif
+
+/* return codes */
+enum {
+    AF8_OK = 0,
+    AF8_ERR_INVALID = 1,      /* bad argument (null pointer, size, enum, alignment) */
+    AF8_ERR_UNSUPPORTED = 2,  /* valid request that this build has no kernel for */
+    AF8_ERR_CUDA = 3          /* a CUDA runtime call or a kernel launch failed */
+};
+
+/* element types of parameters and gradients */
+enum { AF8_F32 = 0, AF8_BF16 = 1, AF8_F16 = 2 };
+
+/* second-moment / confidence state formats (v_quant_type, c_quant_type;
+ * optimizer.py:25) */
+enum { AF8_V_FP32 = 0, AF8_V_AL8 = 8, AF8_V_AL16 = 16 };
+
+/* momentum state formats (m_quant_type; optimizer.py:24); NONE = beta1 is None */
+enum { AF8_M_NONE = 0, AF8_M_UF8 = 1, AF8_M_UF4 = 2, AF8_M_D8 = 3, AF8_M_D4 = 4, AF8_M_FP32 = 5 };
+
+/* pass selection; mirrors the reference's NOCLIP / NORM / APPLY kernel modes
+ * (_dispatch_cuda_clip, optimizer.py:1048-1077) */
+enum {
+    AF8_MODE_NOCLIP = 0,  /* single pass: update states and parameters */
+    AF8_MODE_SUMSQ = 1,   /* first pass: per-block sum of squares of the update, no writes
+                             to states or parameters */
+    AF8_MODE_APPLY = 2,   /* second pass: as NOCLIP, scaled by af8_dyn_scalars */
+    AF8_MODE_SUMSQ_M = 3  /* momentum-only rule, second statistic pass: sum of squares of
+                             the new momentum (reads af8_dyn_scalars.pre_div), no writes */
+};
+
+AF8_API int af8_version(void);
+AF8_API const char *af8_last_error(void);
+
+/* Upload the signed dynamic-map codebooks (256 and 16 sorted entries) used by
+ * the d8 / d4 momentum formats to the current device.
+ * Replaces set_qmap (kernels.cu:32-37, optimizer.py:109-133). */
+AF8_API int af8_set_qmap(const float *host_map8, const float *host_map4, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Full-rank step: AdamW / RMSprop / unfactored Adafactor                    */
+/* ------------------------------------------------------------------------ */
+
+/* Per-tensor scalars that a first pass produces on the device and the APPLY
+ * pass consumes (written by af8_norm_finalize). */
+typedef struct af8_dyn_scalars {
+    float step;       /* -alpha / denom: multiplier of the update in p += step*u */
+    float fira;       /* Fira scale applied to the update before `step` */
+    float pre_div;    /* divisor of u_t before the momentum EMA (momentum-only path) */
+    float zero;       /* non-zero: the update norm was not finite, use a zero update */
+    float norm;       /* the norm that was measured (diagnostic, read by tests) */
+    float reserved[3];
+} af8_dyn_scalars;
+
+/* One parameter tensor of a full-rank launch.  The V state is padded to a
+ * multiple of `block`, the M state to a multiple of `m_block`, exactly as the
+ * reference allocates them (optimizer.py:389-401, 574-590). */
+typedef struct af8_fullrank_tensor {
+    void *param;            /* numel elements of cfg.param_dtype */
+    const void *grad;       /* numel elements of cfg.grad_dtype */
+    void *v_q;              /* AL8: uint8, AL16: uint16 codes; NULL for fp32 V */
+    float *v_scale;         /* one per V block */
+    float *v_min_log;       /* one per V block */
+    float *v_f32;           /* fp32 V state (cfg.v_fmt == AF8_V_FP32) */
+    uint8_t *m_q;           /* momentum codes (4-bit formats: two per byte) */
+    float *m_scale;         /* one per M block */
+    float *m_f32;           /* fp32 momentum (cfg.m_fmt == AF8_M_FP32) */
+    int64_t numel;
+    int64_t first_block;    /* index of this tensor's first V block in the launch */
+    /* host scalars of this step, rounded to binary32 as the reference's 0-d
+     * tensors are (optimizer.py:2009-2040) */
+    float decay;            /* 1 - wd_mult*wd; 1.0 when weight_decay == 0 */
+    float alpha;            /* step size with bias correction folded in */
+    float v_w;              /* second-moment EMA weight beta_val */
+    float v_keep;           /* float(1 - beta_val), used by the fp32 V state */
+    float v_eps_add;        /* float(beta_val * eps_for_grad_sq), fp32 V state */
+    float m_w;              /* float(1 - beta1) */
+    float eps_gradsq;       /* added to g*g (0 in Adam mode) */
+    float eps_denom;        /* added to sqrt(v) in Adam mode */
+    float eps_sq;           /* floor of v outside Adam mode */
+    float reserved;
+} af8_fullrank_tensor;
+
+/* Launch-wide configuration: everything that selects a kernel variant. */
+typedef struct af8_fullrank_cfg {
+    int32_t param_dtype;    /* AF8_F32 */
+    int32_t grad_dtype;     /* AF8_F32 or AF8_BF16 */
+    int32_t v_fmt;          /* AF8_V_* */
+    int32_t m_fmt;          /* AF8_M_* */
+    int32_t block;          /* V block size: multiple of 128, >= 128 */
+    int32_t m_block;        /* M block size: multiple of 4, >= 32, divides block */
+    int32_t use_adam_denom; /* 1: u = m/(sqrt(v)+eps); 0: u = m*rsqrt(max(v,eps_sq)) */
+    int32_t momentum_only;  /* 1: momentum is the EMA of the normalised gradient */
+    int32_t negate_grad;    /* maximize */
+    int32_t mode;           /* AF8_MODE_* */
+    float v_floor;          /* lower clamp of a block's min_log (-126 on this path) */
+    int32_t reserved;
+} af8_fullrank_cfg;
+
+/* One fused pass over every tensor of the table.
+ *   host_tensors  optional host copy of the table (n_tensors entries).  When it
+ *                 is not NULL the library validates it (pointer alignment,
+ *                 ascending first_block, block count) and enqueues its copy
+ *                 into dev_tensors on `stream` before the launch; the host
+ *                 memory must stay unchanged until that copy has run.  When it
+ *                 is NULL, dev_tensors must already hold a valid table.
+ *   dev_tensors   device array of n_tensors entries, first_block ascending
+ *   total_blocks  sum over tensors of ceil(numel / cfg.block)
+ *   dyn           device array of n_tensors entries; read in the APPLY and
+ *                 SUMSQ_M modes, may be NULL in the other modes
+ *   block_sumsq   device array of total_blocks floats; written in the SUMSQ
+ *                 modes (one partial sum per V block), may be NULL otherwise
+ * Pointers of quantised states, parameters and gradients must be 16-byte
+ * aligned.
+ * Replaces fused_update_1d_{noclip,norm,apply}, fused_update_1d_vonly_* and
+ * fused_update_1d_full_* (kernels.cu:826-990, 1100-1255, 1374-1515) and the
+ * separate weight-decay pass (optimizer.py:2039). */
+AF8_API int af8_fullrank_step(const af8_fullrank_cfg *cfg,
+                      const af8_fullrank_tensor *host_tensors,
+                      af8_fullrank_tensor *dev_tensors, int32_t n_tensors,
+                      int64_t total_blocks, const af8_dyn_scalars *dyn,
+                      float *block_sumsq, void *stream);
+
+/* Per-tensor description for af8_norm_finalize. */
+typedef struct af8_norm_tensor {
+    int64_t first_block;    /* first entry of block_sumsq that belongs to the tensor */
+    int64_t n_blocks;
+    float *fira_prev;       /* device scalar: previous limited norm (state key
+                               "fira_prev_norm"); NULL when the limiter is off */
+    int32_t fira_has_prev;  /* 0 on the first limited step of this tensor */
+    int32_t pre_div_mode;   /* 0: write step/fira/zero and pre_div = 1
+                               1: write pre_div = max((norm/sqrt_n)/d, 1), step = -alpha,
+                                  fira = 1 (clip of the momentum-only rule,
+                                  optimizer.py:897-899)
+                               2: as 0 but leave pre_div untouched */
+    float alpha;            /* numerator of `step` */
+    float clip_div;         /* float(sqrt(numel)*d); <= 0 disables clipping */
+    float sqrt_n;           /* float(sqrt(numel)) */
+    float d;
+    float fira_margin1;     /* float(1 + fira_margin) */
+    float reserved;
+} af8_norm_tensor;
+
+/* Reduce the per-block partial sums of each tensor (fixed order, binary64),
+ * take the norm, run the Fira norm-growth limiter and the RMS clip on it and
+ * write af8_dyn_scalars for the APPLY pass.  One launch for all tensors.
+ * Replaces fira_scalar (kernels.cu:3029-3084) and the host-side tensor
+ * arithmetic of _apply_fira_cuda / _safe_rms_denom (optimizer.py:785-793,
+ * 859-863). */
+AF8_API int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors,
+                      const float *block_sumsq, af8_dyn_scalars *dyn,
+                      void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Stand-alone codecs (state migration, checkpoint conversion, tests)        */
+/* ------------------------------------------------------------------------ */
+
+/* AL8/AL16 -> fp32.  Replaces dequantize_log_nonneg (kernels.cu:2613-2632). */
+AF8_API int af8_al_dequant(const void *q, const float *scale, const float *min_log,
+                   int64_t numel, int32_t block, int32_t bits, float *out,
+                   void *stream);
+
+/* fp32 -> AL8/AL16 with fresh per-block ranges; q holds ceil(numel/block)*block
+ * codes.  Replaces the quantise half of fused_log_quantize_lerp
+ * (kernels.cu:482-517) and _log_quantize_nonneg (optimizer.py:299-325). */
+AF8_API int af8_al_quant(const float *x, int64_t numel, int32_t block, int32_t bits,
+                 float floor_log, void *q, float *scale, float *min_log,
+                 void *stream);
+
+/* momentum codes -> fp32.  Replaces dequantize_dynamic (kernels.cu:2585-2590)
+ * and _dequantize_uniform_pytorch (optimizer.py:522-532). */
+AF8_API int af8_m_dequant(const uint8_t *q, const float *scale, int64_t numel,
+                  int32_t m_block, int32_t m_fmt, float *out, void *stream);
+
+/* fp32 -> momentum codes.  Replaces the quantise half of
+ * fused_m_quantize_lerp (kernels.cu:574-588) and _m_quantize
+ * (optimizer.py:547-552). */
+AF8_API int af8_m_quant(const float *m, int64_t numel, int32_t m_block, int32_t m_fmt,
+                uint8_t *q, float *scale, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AF8_H */

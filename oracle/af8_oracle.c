@@ -1,0 +1,559 @@
+/*
+ * af8_oracle.c -- CPU restatement of the reference optimizer's pure-PyTorch
+ * numerics (adafactor8bit/optimizer.py, the path taken with
+ * use_cuda_kernel=False).
+ *
+ * THIS FILE IS TEST INFRASTRUCTURE.  It is the checker that the CUDA library
+ * is compared against and the CPU baseline that the benchmark times.  Nothing
+ * in the shipped package may call it.
+ *
+ * Every function cites the reference lines it follows, as
+ * "optimizer.py:<first>-<last>".
+ *
+ * Arithmetic conventions (they restate what torch's CPU kernels compute):
+ *   - all tensor arithmetic is IEEE binary32 with one rounding per torch op;
+ *     this file must be compiled with -ffp-contract=off and without fast-math
+ *     so that the only fused multiply-adds are the explicit fmaf() calls;
+ *   - Tensor.lerp_(end, w)      = w < 0.5 ? fma(w, end-x, x)
+ *                                         : fma(w-1, end-x, end)
+ *   - Tensor.add_(u, alpha=s)   = fma(s, u, x)
+ *   - Tensor.addcmul_(a,b,value=s) = fma(fl(s*a), b, x)
+ *   - torch.round               = round-half-to-even (rintf in the default
+ *                                 rounding mode)
+ *   - torch.rsqrt(x)            = fl(1 / fl(sqrt(x)))
+ *   - torch.log2 / torch.pow(2, x) are restated as the correctly rounded
+ *     functions (evaluated in binary64, rounded once to binary32).  torch's own
+ *     vector math differs from that by one ulp on a small share of inputs,
+ *     which is inside the parity tolerances and is measured by the golden
+ *     fixture tests.
+ *   - full-tensor reductions (norms, means) accumulate in binary64 and round
+ *     once; torch's float accumulation order is not reproduced.
+ *
+ * Parity status: pinned against outputs of the reference itself, produced by
+ * tests/golden/gen_golden.py (which imports the reference package) and stored
+ * as fixtures under tests/golden/.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <float.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define AF8O_API __attribute__((visibility("default")))
+
+/* optimizer.py:23 */
+#define LOG_QUANT_FLOOR 1.17549435e-38f
+
+/* state formats */
+enum { AF8O_V_FP32 = 0, AF8O_V_AL8 = 8, AF8O_V_AL16 = 16 };
+enum { AF8O_M_NONE = 0, AF8O_M_UF8 = 1, AF8O_M_UF4 = 2, AF8O_M_D8 = 3, AF8O_M_D4 = 4, AF8O_M_FP32 = 5 };
+enum { AF8O_G_F32 = 0, AF8O_G_BF16 = 1 };
+
+AF8O_API int af8o_num_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+AF8O_API void af8o_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+/* ------------------------------------------------------------------ */
+/* scalar primitives                                                   */
+/* ------------------------------------------------------------------ */
+static inline float bf16_to_f32(uint16_t h)
+{
+    uint32_t u = ((uint32_t)h) << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+static inline float log2_cr(float x) { return (float)log2((double)x); }
+static inline float pow2_cr(float x) { return (float)exp2((double)x); }
+static inline float rsqrt_t(float x) { return 1.0f / sqrtf(x); }
+
+/* Tensor.lerp_ (optimizer.py:698, 2119, 2234) */
+static inline float lerp_t(float s, float e, float w)
+{
+    float d = e - s;
+    return (fabsf(w) < 0.5f) ? fmaf(w, d, s) : fmaf(w - 1.0f, d, e);
+}
+
+static inline float load_grad(const void *g, int dtype, int64_t i, int negate)
+{
+    float x = (dtype == AF8O_G_BF16) ? bf16_to_f32(((const uint16_t *)g)[i])
+                                     : ((const float *)g)[i];
+    return negate ? -x : x;
+}
+
+/* ------------------------------------------------------------------ */
+/* AL codec: adaptive log-space, code 0 reserved for exact zero        */
+/* ------------------------------------------------------------------ */
+
+/* One block of _log_quantize_nonneg (optimizer.py:299-325).  x holds the
+ * `valid` real elements of the block; the remaining block-valid elements are
+ * the zero padding that torch.nn.functional.pad appends (optimizer.py:303-305). */
+static void al_quant_block(const float *x, int64_t valid, int64_t block,
+                           float floor_log, int bits, void *q_out,
+                           float *scale_out, float *min_log_out)
+{
+    const float qm1 = (bits == 16) ? 65534.0f : 254.0f;  /* q_max - 1 */
+    const float qmax = (bits == 16) ? 65535.0f : 255.0f;
+    const float l_zero = log2_cr(1e-38f);                 /* clamp(min=1e-38) */
+    float mn = INFINITY, mx = -INFINITY;
+    for (int64_t i = 0; i < block; ++i) {
+        float v = (i < valid) ? x[i] : 0.0f;
+        int is_zero = (v == 0.0f);
+        float vs = (v < 1e-38f) ? 1e-38f : v;             /* optimizer.py:309 */
+        float l = (vs == 1e-38f) ? l_zero : log2_cr(vs);  /* optimizer.py:310 */
+        if (!is_zero && l < mn) mn = l;                   /* optimizer.py:312 */
+        if (l > mx) mx = l;                               /* optimizer.py:313 */
+    }
+    if (mn < floor_log) mn = floor_log;                   /* optimizer.py:315 */
+    if (mn >= mx) mn = mx - 1.0f;                         /* optimizer.py:316 */
+    float scale = mx - mn;                                /* optimizer.py:318 */
+    if (scale < 1e-12f) scale = 1e-12f;
+    for (int64_t i = 0; i < block; ++i) {
+        float v = (i < valid) ? x[i] : 0.0f;
+        float code;
+        if (v == 0.0f) {
+            code = 0.0f;                                  /* optimizer.py:321 */
+        } else {
+            float vs = (v < 1e-38f) ? 1e-38f : v;
+            float l = (vs == 1e-38f) ? l_zero : log2_cr(vs);
+            float t = (l - mn) / scale;                   /* optimizer.py:320 */
+            t = t * qm1;
+            code = rintf(t) + 1.0f;
+            if (code < 1.0f) code = 1.0f;
+            if (code > qmax) code = qmax;
+        }
+        if (bits == 16) ((uint16_t *)q_out)[i] = (uint16_t)code;
+        else ((uint8_t *)q_out)[i] = (uint8_t)code;
+    }
+    *scale_out = scale;
+    *min_log_out = mn;
+}
+
+/* _log_quantize_nonneg over a whole flattened tensor (optimizer.py:299-325).
+ * q has nblocks*block entries, scale/min_log have nblocks entries. */
+AF8O_API int af8o_al_quantize(const float *x, int64_t n, int64_t block,
+                              float floor_log, int bits, void *q, float *scale,
+                              float *min_log)
+{
+    if (block <= 0 || (bits != 8 && bits != 16)) return 1;
+    int64_t nblocks = (n + block - 1) / block;
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nblocks; ++b) {
+        int64_t start = b * block;
+        int64_t valid = n - start < block ? n - start : block;
+        void *qb = (bits == 16) ? (void *)((uint16_t *)q + start)
+                                : (void *)((uint8_t *)q + start);
+        al_quant_block(x + start, valid, block, floor_log, bits, qb, scale + b,
+                       min_log + b);
+    }
+    return 0;
+}
+
+/* one element of _log_dequantize_nonneg (optimizer.py:341-349) */
+static inline float al_deq1(uint32_t code, float scale, float min_log, float qm1)
+{
+    if (code == 0) return 0.0f;                           /* optimizer.py:349 */
+    float t = ((float)code - 1.0f) * scale;               /* optimizer.py:347 */
+    t = t / qm1;
+    t = t + min_log;
+    return pow2_cr(t);                                    /* optimizer.py:348 */
+}
+
+/* _log_dequantize_nonneg (optimizer.py:328-353); writes n values. */
+AF8O_API int af8o_al_dequantize(const void *q, const float *scale,
+                                const float *min_log, int64_t n, int64_t block,
+                                int bits, float *out)
+{
+    if (block <= 0 || (bits != 8 && bits != 16)) return 1;
+    const float qm1 = (bits == 16) ? 65534.0f : 254.0f;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        int64_t b = i / block;
+        uint32_t code = (bits == 16) ? ((const uint16_t *)q)[i]
+                                     : ((const uint8_t *)q)[i];
+        out[i] = al_deq1(code, scale[b], min_log[b], qm1);
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------ */
+/* momentum codecs                                                     */
+/* ------------------------------------------------------------------ */
+
+/* block absmax with the 1e-12 floor (optimizer.py:462, 510) */
+static float m_block_absmax(const float *m, int64_t valid)
+{
+    float a = 0.0f;
+    for (int64_t i = 0; i < valid; ++i) {
+        float t = fabsf(m[i]);
+        if (t > a) a = t;
+    }
+    return a < 1e-12f ? 1e-12f : a;
+}
+
+/* _quantize_uniform_pytorch, 8-bit branch (optimizer.py:518) */
+static inline uint8_t uf8_q1(float m, float a)
+{
+    float t = m / a;
+    t = t * 128.0f;
+    t = rintf(t);
+    if (t < -128.0f) t = -128.0f;
+    if (t > 127.0f) t = 127.0f;
+    return (uint8_t)(t + 128.0f);
+}
+
+/* _quantize_uniform_pytorch, 4-bit branch (optimizer.py:512) */
+static inline uint8_t uf4_q1(float m, float a)
+{
+    float t = m / a;
+    t = t * 8.0f;
+    t = rintf(t);
+    if (t < -8.0f) t = -8.0f;
+    if (t > 7.0f) t = 7.0f;
+    return (uint8_t)(t + 8.0f);
+}
+
+/* _quantize_dynamic_pytorch for one element (optimizer.py:463-473).
+ * map is sorted ascending with L entries. */
+static inline uint8_t dyn_q1(float m, float a, const float *map, int L)
+{
+    float x = m / a;
+    int lo = 0, hi = L;                 /* torch.searchsorted, side="left" */
+    while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (map[mid] < x) lo = mid + 1; else hi = mid;
+    }
+    int idx = lo > L - 1 ? L - 1 : lo;
+    int prev = idx - 1 < 0 ? 0 : idx - 1;
+    float cd = fabsf(x - map[idx]);
+    float pd = fabsf(x - map[prev]);
+    if (pd < cd) idx = prev;
+    int os = (x > 0.0f) - (x < 0.0f);
+    int ms = (map[idx] > 0.0f) - (map[idx] < 0.0f);
+    int flip = (os != ms) && (os != 0);
+    int out = idx;
+    if (flip && os > 0 && idx < L - 1) out = idx + 1;
+    if (flip && os < 0 && out > 0 && idx > 0) out = out - 1;
+    return (uint8_t)out;
+}
+
+/* _m_quantize (optimizer.py:547-552).  n real elements, padded with zeros to
+ * a multiple of `block`.  8-bit formats write nblocks*block bytes, 4-bit
+ * formats nblocks*block/2 bytes with the even element in the high nibble
+ * (optimizer.py:513-515, 477-479).  map is only read for d8 / d4. */
+AF8O_API int af8o_m_quantize(const float *m, int64_t n, int64_t block, int fmt,
+                             const float *map, uint8_t *q, float *scale)
+{
+    if (block <= 0 || (block & 1)) return 1;
+    if (fmt < AF8O_M_UF8 || fmt > AF8O_M_D4) return 1;
+    int64_t nblocks = (n + block - 1) / block;
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nblocks; ++b) {
+        int64_t start = b * block;
+        int64_t valid = n - start < block ? n - start : block;
+        float a = m_block_absmax(m + start, valid);
+        scale[b] = a;
+        for (int64_t i = 0; i < block; i += 2) {
+            float x0 = (i < valid) ? m[start + i] : 0.0f;
+            float x1 = (i + 1 < valid) ? m[start + i + 1] : 0.0f;
+            switch (fmt) {
+            case AF8O_M_UF8:
+                q[start + i] = uf8_q1(x0, a);
+                q[start + i + 1] = uf8_q1(x1, a);
+                break;
+            case AF8O_M_D8:
+                q[start + i] = dyn_q1(x0, a, map, 256);
+                q[start + i + 1] = dyn_q1(x1, a, map, 256);
+                break;
+            case AF8O_M_UF4:
+                q[(start + i) >> 1] = (uint8_t)((uf4_q1(x0, a) << 4) | uf4_q1(x1, a));
+                break;
+            default: /* AF8O_M_D4 */
+                q[(start + i) >> 1] =
+                    (uint8_t)((dyn_q1(x0, a, map, 16) << 4) | dyn_q1(x1, a, map, 16));
+                break;
+            }
+        }
+    }
+    return 0;
+}
+
+static inline float m_deq1(const uint8_t *q, const float *scale, int64_t i,
+                           int64_t block, int fmt, const float *map)
+{
+    float s = scale[i / block];
+    switch (fmt) {
+    case AF8O_M_UF8:   /* optimizer.py:528-531 */
+        return ((float)q[i] - 128.0f) * (s / 128.0f);
+    case AF8O_M_UF4: { /* optimizer.py:524-531 */
+        uint8_t byte = q[i >> 1];
+        uint8_t nib = (i & 1) ? (byte & 0x0F) : (byte >> 4);
+        return ((float)nib - 8.0f) * (s / 8.0f);
+    }
+    case AF8O_M_D8:    /* optimizer.py:489-498 */
+        return map[q[i]] * s;
+    default: {         /* AF8O_M_D4 */
+        uint8_t byte = q[i >> 1];
+        uint8_t nib = (i & 1) ? (byte & 0x0F) : (byte >> 4);
+        return map[nib] * s;
+    }
+    }
+}
+
+/* _m_dequantize (optimizer.py:555-560) */
+AF8O_API int af8o_m_dequantize(const uint8_t *q, const float *scale, int64_t n,
+                               int64_t block, int fmt, const float *map,
+                               float *out)
+{
+    if (block <= 0) return 1;
+    if (fmt < AF8O_M_UF8 || fmt > AF8O_M_D4) return 1;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = m_deq1(q, scale, i, block, fmt, map);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ */
+/* Fira norm-growth limiter on one scalar (optimizer.py:760-782)       */
+/* ------------------------------------------------------------------ */
+AF8O_API float af8o_fira_scale(float norm, float margin_plus_one, int *has_prev,
+                               float *prev)
+{
+    if (!isfinite(norm)) norm = 0.0f;                    /* optimizer.py:768-769 */
+    float fs;
+    if (*has_prev) {
+        float fp = *prev;
+        int is_reset = fp < 1e-6f;                       /* optimizer.py:774 */
+        float ratio = norm / (fp + 1e-8f);               /* optimizer.py:775 */
+        float lim = (ratio < margin_plus_one ? margin_plus_one : ratio) /
+                    margin_plus_one;                     /* optimizer.py:776 */
+        fs = is_reset ? 1.0f : 1.0f / lim;               /* optimizer.py:777 */
+        *prev = is_reset ? norm : norm * fs;             /* optimizer.py:778 */
+    } else {
+        fs = 1.0f;                                       /* optimizer.py:780-781 */
+        *prev = norm;
+        *has_prev = 1;
+    }
+    return fs;
+}
+
+/* sqrt(sum x^2) accumulated in binary64; stands in for
+ * torch.linalg.vector_norm (optimizer.py:797, 827, 851, 861, 898). */
+static float norm2_f64(const float *x, int64_t n)
+{
+    double acc = 0.0;
+#pragma omp parallel for reduction(+ : acc) schedule(static)
+    for (int64_t i = 0; i < n; ++i) acc += (double)x[i] * (double)x[i];
+    return (float)sqrt(acc);
+}
+
+AF8O_API float af8o_norm2(const float *x, int64_t n) { return norm2_f64(x, n); }
+
+/* ------------------------------------------------------------------ */
+/* full-rank step ("1D" path): AdamW / RMSprop / unfactored Adafactor   */
+/* ------------------------------------------------------------------ */
+
+/* Host-computed scalars arrive already rounded to binary32 the way the
+ * reference's 0-d tensors and Python floats are when they meet a tensor. */
+typedef struct {
+    int64_t numel;
+    int64_t block;        /* V block size (state["block_size"]) */
+    int64_t m_block;      /* M block size (state["m_block_size"]) */
+    int32_t grad_dtype;   /* AF8O_G_* */
+    int32_t v_fmt;        /* AF8O_V_* */
+    int32_t m_fmt;        /* AF8O_M_*; AF8O_M_NONE when beta1 is None */
+    int32_t negate_grad;  /* maximize (optimizer.py:1973-1974) */
+    int32_t use_adam_denom;
+    int32_t momentum_only;
+    int32_t fira;
+    int32_t has_decay;
+    float decay;          /* 1 - wd_mult*wd (optimizer.py:2034-2039) */
+    float alpha;          /* optimizer.py:2018-2030 */
+    float v_w;            /* beta_val as the lerp weight (optimizer.py:2012-2017) */
+    float v_keep;         /* float(1.0 - beta_val), fp32-state path (optimizer.py:2187) */
+    float v_eps_add;      /* float(beta_val*eps_for_grad_sq) (optimizer.py:2189) */
+    float m_w;            /* float(1.0 - beta1) (optimizer.py:698) */
+    float eps_gradsq;     /* optimizer.py:1967 */
+    float eps_denom;      /* optimizer.py:1966, 2028 */
+    float eps_sq;         /* optimizer.py:1961 */
+    float d;              /* clip threshold, 0 disables */
+    float sqrt_n;         /* float(math.sqrt(numel)) */
+    float clip_div;       /* float(math.sqrt(numel)*d) (optimizer.py:862) */
+    float fira_margin1;   /* float(1.0 + fira_margin) */
+    float v_floor;        /* min_log floor, -126 on this path (optimizer.py:299) */
+} af8o_fullrank_cfg;
+
+/* _apply_update_pytorch (optimizer.py:866-881) with _apply_fira_pytorch
+ * (optimizer.py:796-810) and _safe_rms_denom (optimizer.py:859-863).
+ * u is consumed (scaled in place).  Returns the update norm it measured, or
+ * -1 when no norm was needed. */
+static float apply_update(float *p, float *u, int64_t n, float alpha, float d,
+                          float clip_div, int fira, float margin1,
+                          int *fira_has_prev, float *fira_prev)
+{
+    float denom = 1.0f;
+    float norm = -1.0f;
+    if (fira) {
+        norm = norm2_f64(u, n);                          /* optimizer.py:797 */
+        if (!isfinite(norm)) {                           /* optimizer.py:798-800 */
+            memset(u, 0, (size_t)n * sizeof(float));
+            norm = 0.0f;
+        }
+        float fs = af8o_fira_scale(norm, margin1, fira_has_prev, fira_prev);
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) u[i] = u[i] * fs; /* optimizer.py:803 */
+        if (d > 0.0f) {                                  /* optimizer.py:805-806 */
+            denom = norm / clip_div;
+            if (denom < 1.0f) denom = 1.0f;
+        }
+    } else if (d > 0.0f) {                               /* optimizer.py:860-862 */
+        norm = norm2_f64(u, n);
+        denom = norm / clip_div;
+        if (!(denom >= 1.0f)) denom = (denom != denom) ? denom : 1.0f;
+    }
+    float s = -alpha / denom;                            /* optimizer.py:874 */
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) p[i] = fmaf(s, u[i], p[i]);
+    return norm;
+}
+
+/* _update_param_8bit, full-rank branch without the SGD mode
+ * (optimizer.py:1957-2040 prologue scalars are inputs; 2076-2194 body) plus
+ * _fallback_1d_update (optimizer.py:886-917) and _m_ema_pytorch
+ * (optimizer.py:690-700).
+ *
+ * Quantised states are updated in place: v_q/v_scale/v_min_log (AL8/AL16,
+ * nblocks*block codes) or v_f32; m_q/m_scale (n padded to m_block) or m_f32.
+ * map is the dynamic codebook for d8/d4 (else NULL).
+ * norm_out receives the update norm measured for clipping / Fira (or -1). */
+AF8O_API int af8o_fullrank_step(const af8o_fullrank_cfg *c, float *p,
+                                const void *grad, void *v_q, float *v_scale,
+                                float *v_min_log, float *v_f32, uint8_t *m_q,
+                                float *m_scale, float *m_f32, const float *map,
+                                int *fira_has_prev, float *fira_prev,
+                                float *norm_out)
+{
+    const int64_t n = c->numel;
+    const int has_m = c->m_fmt != AF8O_M_NONE;
+    const int m_quant = has_m && c->m_fmt != AF8O_M_FP32;
+    const int v_quant = c->v_fmt != AF8O_V_FP32;
+    float *g = (float *)malloc((size_t)(n ? n : 1) * sizeof(float));
+    float *v = v_quant ? (float *)malloc((size_t)(n ? n : 1) * sizeof(float)) : v_f32;
+    float *u = (float *)malloc((size_t)(n ? n : 1) * sizeof(float));
+    if (!g || !v || !u) { free(g); if (v_quant) free(v); free(u); return 2; }
+
+    /* grad upcast (optimizer.py:1997), weight decay as its own pass
+     * (optimizer.py:2039) */
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        g[i] = load_grad(grad, c->grad_dtype, i, c->negate_grad);
+        if (c->has_decay) p[i] = p[i] * c->decay;
+    }
+
+    if (v_quant) {
+        /* optimizer.py:2117-2121 */
+        af8o_al_dequantize(v_q, v_scale, v_min_log, n, c->block, c->v_fmt, v);
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float g2 = g[i] * g[i];
+            g2 = g2 + c->eps_gradsq;
+            v[i] = lerp_t(v[i], g2, c->v_w);
+        }
+        af8o_al_quantize(v, n, c->block, c->v_floor, c->v_fmt, v_q, v_scale, v_min_log);
+    } else {
+        /* optimizer.py:2186-2189 */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float t = v[i] * c->v_keep;
+            t = fmaf(c->v_w * g[i], g[i], t);
+            if (c->eps_gradsq > 0.0f) t = t + c->v_eps_add;
+            v[i] = t;
+        }
+    }
+
+    float norm = -1.0f;
+    int rc = 0;
+    if (has_m) {
+        /* m_temp before the EMA: dequantised state or the fp32 state */
+        float *m = m_quant ? u : m_f32;
+        if (m_quant) af8o_m_dequantize(m_q, m_scale, n, c->m_block, c->m_fmt, map, m);
+        if (c->momentum_only) {
+            /* optimizer.py:894-901 */
+            float *ut = g;  /* grad_fp32 * inv_std, reuse g */
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < n; ++i) {
+                float vc = v[i] < c->eps_sq ? c->eps_sq : v[i];
+                ut[i] = g[i] * rsqrt_t(vc);
+            }
+            if (c->d > 0.0f) {
+                float rms = norm2_f64(ut, n) / c->sqrt_n;
+                float cf = rms / c->d;
+                if (cf < 1.0f) cf = 1.0f;
+#pragma omp parallel for schedule(static)
+                for (int64_t i = 0; i < n; ++i) ut[i] = ut[i] / cf;
+            }
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < n; ++i) m[i] = lerp_t(m[i], ut[i], c->m_w);
+            if (m_quant) rc = af8o_m_quantize(m, n, c->m_block, c->m_fmt, map, m_q, m_scale);
+            float *upd = u;
+            if (!m_quant) memcpy(u, m, (size_t)n * sizeof(float));
+            norm = apply_update(p, upd, n, c->alpha, 0.0f, c->clip_div, c->fira,
+                                c->fira_margin1, fira_has_prev, fira_prev);
+        } else {
+            /* optimizer.py:903-910 */
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < n; ++i) m[i] = lerp_t(m[i], g[i], c->m_w);
+            if (m_quant) rc = af8o_m_quantize(m, n, c->m_block, c->m_fmt, map, m_q, m_scale);
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < n; ++i) {
+                float inv;
+                if (c->use_adam_denom) {
+                    float den = sqrtf(v[i]) + c->eps_denom;
+                    inv = 1.0f / den;
+                } else {
+                    float vc = v[i] < c->eps_sq ? c->eps_sq : v[i];
+                    inv = rsqrt_t(vc);
+                }
+                u[i] = m[i] * inv;
+            }
+            norm = apply_update(p, u, n, c->alpha, c->d, c->clip_div, c->fira,
+                                c->fira_margin1, fira_has_prev, fira_prev);
+        }
+    } else {
+        /* optimizer.py:911-917 */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            if (c->use_adam_denom) {
+                float den = sqrtf(v[i]) + c->eps_denom;
+                u[i] = g[i] / den;
+            } else {
+                float vc = v[i] < c->eps_sq ? c->eps_sq : v[i];
+                u[i] = g[i] * rsqrt_t(vc);
+            }
+        }
+        norm = apply_update(p, u, n, c->alpha, c->d, c->clip_div, c->fira,
+                            c->fira_margin1, fira_has_prev, fira_prev);
+    }
+    if (norm_out) *norm_out = norm;
+    free(g);
+    if (v_quant) free(v);
+    free(u);
+    return rc;
+}

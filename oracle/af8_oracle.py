@@ -1,0 +1,408 @@
+"""ctypes front end of the CPU oracle (af8_oracle.c) plus the host-side scalar
+logic of the reference's per-parameter update, restated with numpy float32.
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
+benchmark's CPU-baseline leg.  The shipped package never imports this module.
+
+The state of one parameter is a plain dict that uses the reference's own key
+names (optimizer.py:1711-1773): ``step``, ``variance_q`` / ``variance_scale`` /
+``variance_min_log`` or ``variance``; ``m_q`` / ``m_scale`` or ``m``;
+``row_var_*`` / ``col_var_*`` / ``conf_row_*`` / ``conf_col_*``;
+``fira_prev_norm``.  Arrays are numpy; AL16 codes are uint16 (the reference
+stores the same bit pattern in int16, optimizer.py:323-324).
+"""
+import ctypes
+import math
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_BUILD = os.path.join(_HERE, "_build")
+_LIB_PATH = os.path.join(_BUILD, "libaf8_oracle.so")
+_SRC = os.path.join(_HERE, "af8_oracle.c")
+
+LOG_QUANT_FLOOR = 1.17549435e-38  # optimizer.py:23
+
+V_FMT = {"fp32": 0, "al8": 8, "al16": 16}
+M_FMT = {None: 0, "uf8": 1, "uf4": 2, "d8": 3, "d4": 4, "fp32": 5}
+G_F32, G_BF16 = 0, 1
+
+f32 = np.float32
+c_f = ctypes.c_float
+c_i = ctypes.c_int32
+c_l = ctypes.c_int64
+c_p = ctypes.c_void_p
+
+
+def build(force=False):
+    """Compile af8_oracle.c into oracle/_build/libaf8_oracle.so with gcc."""
+    os.makedirs(_BUILD, exist_ok=True)
+    if (not force and os.path.exists(_LIB_PATH)
+            and os.path.getmtime(_LIB_PATH) >= os.path.getmtime(_SRC)):
+        return _LIB_PATH
+    cmd = ["gcc", "-O2", "-fopenmp", "-ffp-contract=off", "-fno-fast-math",
+           "-fvisibility=hidden", "-shared", "-fPIC", "-o", _LIB_PATH, _SRC, "-lm"]
+    subprocess.run(cmd, check=True)
+    return _LIB_PATH
+
+
+class FullrankCfg(ctypes.Structure):
+    _fields_ = [
+        ("numel", c_l), ("block", c_l), ("m_block", c_l),
+        ("grad_dtype", c_i), ("v_fmt", c_i), ("m_fmt", c_i), ("negate_grad", c_i),
+        ("use_adam_denom", c_i), ("momentum_only", c_i), ("fira", c_i), ("has_decay", c_i),
+        ("decay", c_f), ("alpha", c_f), ("v_w", c_f), ("v_keep", c_f), ("v_eps_add", c_f),
+        ("m_w", c_f), ("eps_gradsq", c_f), ("eps_denom", c_f), ("eps_sq", c_f),
+        ("d", c_f), ("sqrt_n", c_f), ("clip_div", c_f), ("fira_margin1", c_f),
+        ("v_floor", c_f),
+    ]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = build() if os.path.exists(_SRC) else _LIB_PATH
+        _lib = ctypes.CDLL(path)
+        _lib.af8o_fira_scale.restype = c_f
+        _lib.af8o_fira_scale.argtypes = [c_f, c_f, ctypes.POINTER(c_i), ctypes.POINTER(c_f)]
+        _lib.af8o_norm2.restype = c_f
+        _lib.af8o_norm2.argtypes = [c_p, c_l]
+        _lib.af8o_al_quantize.argtypes = [c_p, c_l, c_l, c_f, c_i, c_p, c_p, c_p]
+        _lib.af8o_al_dequantize.argtypes = [c_p, c_p, c_p, c_l, c_l, c_i, c_p]
+        _lib.af8o_m_quantize.argtypes = [c_p, c_l, c_l, c_i, c_p, c_p, c_p]
+        _lib.af8o_m_dequantize.argtypes = [c_p, c_p, c_l, c_l, c_i, c_p, c_p]
+        _lib.af8o_fullrank_step.argtypes = [ctypes.POINTER(FullrankCfg)] + [c_p] * 10 + [
+            ctypes.POINTER(c_i), ctypes.POINTER(c_f), ctypes.POINTER(c_f)]
+    return _lib
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(c_p)
+
+
+def num_threads():
+    return lib().af8o_num_threads()
+
+
+def set_num_threads(n):
+    lib().af8o_set_num_threads(int(n))
+
+
+# ---------------------------------------------------------------------------
+# codecs
+# ---------------------------------------------------------------------------
+def al_quantize(x, block, bits=8, floor_log=-126.0):
+    """_log_quantize_nonneg (optimizer.py:299-325) -> (q, scale, min_log, pad)."""
+    x = np.ascontiguousarray(x, dtype=f32).reshape(-1)
+    n = x.size
+    nblocks = (n + block - 1) // block
+    q = np.zeros(nblocks * block, dtype=np.uint16 if bits == 16 else np.uint8)
+    scale = np.zeros(nblocks, dtype=f32)
+    min_log = np.zeros(nblocks, dtype=f32)
+    rc = lib().af8o_al_quantize(_ptr(x), n, block, floor_log, bits, _ptr(q), _ptr(scale), _ptr(min_log))
+    assert rc == 0
+    return q, scale, min_log, nblocks * block - n
+
+
+def al_dequantize(q, scale, min_log, n, bits=8):
+    """_log_dequantize_nonneg (optimizer.py:328-353)."""
+    q = np.ascontiguousarray(q).reshape(-1)
+    block = q.size // scale.size
+    out = np.empty(n, dtype=f32)
+    rc = lib().af8o_al_dequantize(_ptr(q), _ptr(scale), _ptr(min_log), n, block, bits, _ptr(out))
+    assert rc == 0
+    return out
+
+
+def dynamic_map(total_bits):
+    """_create_dynamic_map(signed=True, ...) (optimizer.py:416-441) for the two
+    codebooks the reference uses (optimizer.py:122-123): 8 bits with 7 exponent
+    bits, 4 bits with 3 exponent bits."""
+    max_exponent_bits = 7 if total_bits == 8 else 3
+    non_sign_bits = total_bits - 1
+    additional_items = 2 ** (non_sign_bits - max_exponent_bits) - 1
+    data = []
+
+    def linspace32(n):
+        # torch.linspace(0.1, 1, n, dtype=float32): symmetric evaluation from
+        # both ends with a float32 step.
+        start, end = f32(0.1), f32(1.0)
+        step = f32((end - start) / f32(n - 1))
+        out = np.empty(n, dtype=f32)
+        half = n // 2
+        for i in range(n):
+            out[i] = start + step * f32(i) if i < half else end - step * f32(n - i - 1)
+        return out
+
+    for i in range(max_exponent_bits):
+        fraction_items = int(2 ** (i + non_sign_bits - max_exponent_bits) + 1)
+        b = linspace32(fraction_items)
+        means = (b[:-1] + b[1:]) / f32(2.0)
+        mult = f32(10 ** (-(max_exponent_bits - 1) + i))
+        data += [float(v) for v in (mult * means)]
+        data += [float(v) for v in (-mult * means)]
+    if additional_items > 0:
+        b = linspace32(additional_items + 1)
+        means = (b[:-1] + b[1:]) / f32(2.0)
+        data += [float(v) for v in means]
+        data += [float(v) for v in (-means)]
+    data.append(0.0)
+    data.append(1.0)
+    assert len(data) == 2 ** total_bits
+    data.sort()
+    return np.asarray(data, dtype=f32)
+
+
+_MAPS = {}
+
+
+def set_dynamic_map(bits, values):
+    """Use `values` (the codebook a caller built on this host) instead of the
+    numpy restatement above, which can differ from torch.linspace by an ulp."""
+    arr = np.ascontiguousarray(values, dtype=f32)
+    assert arr.size == 2 ** bits
+    _MAPS[bits] = arr
+
+
+def _map_for(fmt):
+    if fmt in ("d8", "d4"):
+        bits = 8 if fmt == "d8" else 4
+        if bits not in _MAPS:
+            _MAPS[bits] = dynamic_map(bits)
+        return _MAPS[bits]
+    return None
+
+
+def m_quantize(m, block, fmt="uf8"):
+    """_m_quantize (optimizer.py:547-552) -> (q, scale)."""
+    m = np.ascontiguousarray(m, dtype=f32).reshape(-1)
+    n = m.size
+    nblocks = (n + block - 1) // block
+    nbytes = nblocks * block // (2 if fmt in ("uf4", "d4") else 1)
+    q = np.zeros(nbytes, dtype=np.uint8)
+    scale = np.zeros(nblocks, dtype=f32)
+    mp = _map_for(fmt)
+    rc = lib().af8o_m_quantize(_ptr(m), n, block, M_FMT[fmt], _ptr(mp), _ptr(q), _ptr(scale))
+    assert rc == 0
+    return q, scale
+
+
+def m_dequantize(q, scale, n, block, fmt="uf8"):
+    """_m_dequantize (optimizer.py:555-560)."""
+    out = np.empty(n, dtype=f32)
+    mp = _map_for(fmt)
+    rc = lib().af8o_m_dequantize(_ptr(q), _ptr(scale), n, block, M_FMT[fmt], _ptr(mp), _ptr(out))
+    assert rc == 0
+    return out
+
+
+def fira_scale(norm, margin, prev):
+    """_compute_fira_scale (optimizer.py:760-782) -> (scale, new_prev)."""
+    has = c_i(0 if prev is None else 1)
+    pv = c_f(0.0 if prev is None else float(prev))
+    fs = lib().af8o_fira_scale(float(f32(norm)), float(f32(1.0 + margin)), ctypes.byref(has), ctypes.byref(pv))
+    return f32(fs), f32(pv.value)
+
+
+# ---------------------------------------------------------------------------
+# hyper-parameters and state initialisation
+# ---------------------------------------------------------------------------
+# constructor defaults (optimizer.py:1313-1360)
+DEFAULTS = dict(
+    lr=1e-2, beta1=None, beta2=None, beta2_decay=-0.8, beta3=None, eps_came=1e-16,
+    eps=(1e-30, 1e-3), weight_decay=0.0, d=1.0, maximize=False,
+    relative_step=True, scale_parameter=True, factored=True,
+    quantize=True, block_size=2048, m_block_size=256, m_quant_type="uf8",
+    v_quant_type="al8", c_quant_type=None, min_8bit_size=4096,
+    apollo_rank=0, apollo_update_proj_gap=200, apollo_scale_type="channel",
+    apollo_scale=1.0, apollo_scale_front=False, apollo_eps=1e-6,
+    apollo_factorize=False, apollo_cache_proj=False, enable_fira_for_apollo=True,
+    scale_weight_decay=True, enable_fira_for_adafactor=False, fira_margin=0.01,
+    lag_norm=False, momentum_only_1d=None, bias_correction=None,
+)
+
+
+def hyper(**kw):
+    hp = dict(DEFAULTS)
+    hp.update(kw)
+    return hp
+
+
+def _init_al(state, prefix, numel, block, fmt):
+    """_init_v_state (optimizer.py:389-401)."""
+    if fmt == "fp32":
+        state[prefix] = np.zeros(numel, dtype=f32)
+        return
+    pad = (block - numel % block) % block
+    nblocks = (numel + pad) // block
+    state[prefix + "_q"] = np.zeros(numel + pad, dtype=np.uint8 if fmt == "al8" else np.uint16)
+    state[prefix + "_scale"] = np.ones(nblocks, dtype=f32)
+    state[prefix + "_min_log"] = np.zeros(nblocks, dtype=f32)
+    state[prefix + "_pad"] = pad
+
+
+def _init_m(state, numel, m_block, fmt, prefix="m"):
+    """_m_init_state (optimizer.py:574-590)."""
+    if fmt == "fp32":
+        state[prefix] = np.zeros(numel, dtype=f32)
+    else:
+        padded = ((numel + m_block - 1) // m_block) * m_block
+        if fmt in ("uf4", "d4"):
+            state[prefix + "_q"] = np.full(padded // 2, 0x88 if fmt == "uf4" else 0x77, dtype=np.uint8)
+        else:
+            state[prefix + "_q"] = np.full(padded, 128 if fmt == "uf8" else 127, dtype=np.uint8)
+        state[prefix + "_scale"] = np.ones(padded // m_block, dtype=f32)
+        state["m_block_size"] = m_block
+    state["m_quant_type"] = fmt
+
+
+def init_state(shape, hp):
+    """First-step branch of _init_group (optimizer.py:1711-1773) for the
+    non-SGD paths."""
+    shape = tuple(shape)
+    numel = int(np.prod(shape)) if shape else 1
+    use_quant = hp["quantize"] and not (numel < hp["min_8bit_size"])
+    vqt = hp["v_quant_type"]
+    cqt = hp["c_quant_type"] or vqt
+    st = {"step": 0, "is_quantized": use_quant, "block_size": hp["block_size"],
+          "v_quant_type": vqt, "c_quant_type": cqt, "shape": shape}
+    use_apollo = hp["apollo_rank"] > 0 and len(shape) >= 2
+    factored = len(shape) >= 2 and hp["factored"]
+    v_fmt = vqt if use_quant else "fp32"
+    c_fmt = cqt if use_quant else "fp32"
+    m_fmt = hp["m_quant_type"] if use_quant else "fp32"
+    if use_apollo:
+        st["apollo"] = True
+        st["m_quant_type"] = hp["m_quant_type"]
+        return st
+    if factored:
+        R, C = shape[-2], shape[-1]
+        batch = numel // (R * C)
+        assert batch == 1, "oracle covers 2-D factored tensors"
+        _init_al(st, "row_var", R, hp["block_size"], v_fmt)
+        _init_al(st, "col_var", C, hp["block_size"], v_fmt)
+        if hp["beta1"] is not None:
+            _init_m(st, numel, hp["m_block_size"], m_fmt)
+        if hp["beta3"] is not None:
+            _init_al(st, "conf_row", R, hp["block_size"], c_fmt)
+            _init_al(st, "conf_col", C, hp["block_size"], c_fmt)
+    else:
+        _init_al(st, "variance", numel, hp["block_size"], v_fmt)
+        if hp["beta1"] is not None:
+            _init_m(st, numel, hp["m_block_size"], m_fmt)
+    return st
+
+
+def _grad_args(g):
+    g = np.ascontiguousarray(g)
+    if g.dtype == np.uint16:
+        return g, G_BF16
+    assert g.dtype == f32
+    return g, G_F32
+
+
+def prologue(p, state, hp):
+    """Per-step host scalars of _update_param_8bit (optimizer.py:1957-2040) and
+    _compute_alpha (optimizer.py:832-856), rounded to float32 where the
+    reference's 0-d float32 tensors round."""
+    eps1, eps2 = hp["eps"]
+    if eps1 is None:
+        eps1 = 1e-30
+    beta1, beta2, beta3 = hp["beta1"], hp["beta2"], hp["beta3"]
+    factored = hp["factored"]
+    eps_sq = max(eps1 * eps1, LOG_QUANT_FLOOR)
+    use_adam_denom = (not factored) and (beta2 is not None) and (beta3 is None)
+    eps_for_denom = eps1 if use_adam_denom else 0.0
+    eps_for_grad_sq = eps1 if not use_adam_denom else 0.0
+    momentum_only = hp["momentum_only_1d"]
+    if momentum_only is None:
+        momentum_only = not use_adam_denom
+    step = state["step"] + 1
+    state["step"] = step
+    beta_val = 1.0 - beta2 if beta2 is not None else math.pow(step, hp["beta2_decay"])
+    lr = hp["lr"]
+    rho = f32(min(lr, 1.0 / math.sqrt(step)) if hp["relative_step"] else lr)
+    if hp["scale_parameter"]:
+        n = p.size
+        rms = f32(lib().af8o_norm2(_ptr(p), n)) / f32(math.sqrt(n))
+        alpha = f32(max(rms, f32(eps2))) * rho
+    else:
+        alpha = rho
+    if beta1 is not None and not hp["relative_step"]:
+        apply_bc = use_adam_denom if hp["bias_correction"] is None else hp["bias_correction"]
+        if apply_bc:
+            bc1 = 1.0 - beta1 ** step
+            if beta2 is not None:
+                bc2 = 1.0 - beta2 ** step
+                alpha = f32(alpha * f32(math.sqrt(bc2) / bc1))
+                if use_adam_denom:
+                    eps_for_denom = eps1 * math.sqrt(bc2)
+            else:
+                alpha = f32(alpha / f32(bc1))
+    decay = None
+    if hp["weight_decay"] != 0:
+        wd_mult = alpha if hp["scale_weight_decay"] else rho
+        decay = f32(f32(1.0) - f32(wd_mult * f32(hp["weight_decay"])))
+    return dict(step=step, beta_val=beta_val, alpha=f32(alpha), rho=rho, decay=decay,
+                eps1=eps1, eps_sq=eps_sq, use_adam_denom=use_adam_denom,
+                eps_for_denom=eps_for_denom, eps_for_grad_sq=eps_for_grad_sq,
+                momentum_only=momentum_only)
+
+
+def fullrank_step(p, g, state, hp, sc=None):
+    """Full-rank branch of _update_param_8bit (optimizer.py:2076-2194).
+    p: float32 array updated in place; g: float32, or uint16 holding bf16 bits."""
+    assert p.dtype == f32 and p.flags.c_contiguous
+    if sc is None:
+        sc = prologue(p, state, hp)
+    n = p.size
+    g, gdt = _grad_args(g)
+    quant = state["is_quantized"]
+    vqt = state["v_quant_type"] if quant else "fp32"
+    has_m = hp["beta1"] is not None
+    mqt = (state.get("m_quant_type", "uf8") if has_m else None)
+    cfg = FullrankCfg()
+    cfg.numel = n
+    cfg.block = state["block_size"]
+    cfg.m_block = state.get("m_block_size", hp["m_block_size"])
+    cfg.grad_dtype = gdt
+    cfg.v_fmt = V_FMT[vqt]
+    cfg.m_fmt = M_FMT[mqt]
+    cfg.negate_grad = int(bool(hp["maximize"]))
+    cfg.use_adam_denom = int(sc["use_adam_denom"])
+    cfg.momentum_only = int(sc["momentum_only"])
+    cfg.fira = int(bool(hp["enable_fira_for_adafactor"]))
+    cfg.has_decay = int(sc["decay"] is not None)
+    cfg.decay = float(sc["decay"]) if sc["decay"] is not None else 1.0
+    cfg.alpha = float(sc["alpha"])
+    cfg.v_w = float(f32(sc["beta_val"]))
+    cfg.v_keep = float(f32(1.0 - sc["beta_val"]))
+    cfg.v_eps_add = float(f32(sc["beta_val"] * sc["eps_for_grad_sq"]))
+    cfg.m_w = float(f32(1.0 - hp["beta1"])) if has_m else 0.0
+    cfg.eps_gradsq = float(f32(sc["eps_for_grad_sq"]))
+    cfg.eps_denom = float(f32(sc["eps_for_denom"]))
+    cfg.eps_sq = float(f32(sc["eps_sq"]))
+    cfg.d = float(f32(hp["d"]))
+    cfg.sqrt_n = float(f32(math.sqrt(n)))
+    cfg.clip_div = float(f32(math.sqrt(n) * hp["d"]))
+    cfg.fira_margin1 = float(f32(1.0 + hp["fira_margin"]))
+    cfg.v_floor = -126.0
+    has_prev = c_i(1 if "fira_prev_norm" in state else 0)
+    prev = c_f(float(state.get("fira_prev_norm", 0.0)))
+    norm = c_f(-1.0)
+    rc = lib().af8o_fullrank_step(
+        ctypes.byref(cfg), _ptr(p.reshape(-1)), _ptr(g.reshape(-1)),
+        _ptr(state.get("variance_q")), _ptr(state.get("variance_scale")),
+        _ptr(state.get("variance_min_log")), _ptr(state.get("variance")),
+        _ptr(state.get("m_q")), _ptr(state.get("m_scale")), _ptr(state.get("m")),
+        _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev), ctypes.byref(norm))
+    if rc != 0:
+        raise RuntimeError(f"af8o_fullrank_step failed with {rc}")
+    if has_prev.value:
+        state["fira_prev_norm"] = f32(prev.value)
+    return float(norm.value)

@@ -1,0 +1,144 @@
+"""Case definitions and seeded input generators shared by the golden-vector
+generator (gen_golden.py, which runs the reference) and by the parity tests.
+
+Everything here is plain numpy so that the same inputs can be rebuilt on a
+machine that has neither the reference nor a GPU.  Each fixture stores a digest
+of the inputs it was generated from; a test that rebuilds different bytes
+fails instead of comparing against the wrong vectors.
+"""
+import hashlib
+
+import numpy as np
+
+f32 = np.float32
+
+
+def f32_to_bf16_bits(x):
+    """Round-to-nearest-even float32 -> bfloat16, returned as uint16 bit patterns."""
+    u = np.ascontiguousarray(x, dtype=f32).view(np.uint32).astype(np.uint64)
+    rounded = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return rounded.astype(np.uint16)
+
+
+def bf16_bits_to_f32(h):
+    return (h.astype(np.uint32) << 16).view(f32)
+
+
+def make_param(shape, seed, std=0.02):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return (rng.standard_normal(shape, dtype=np.float64) * std).astype(f32)
+
+
+def make_grad(shape, seed, step, spec):
+    """spec keys: dist ('normal' | 'rowscale'), std, zero_frac, dtype ('f32' | 'bf16'),
+    spike_step / spike_mult (optional)."""
+    rng = np.random.Generator(np.random.PCG64([seed, step]))
+    g = rng.standard_normal(shape, dtype=np.float64) * spec["std"]
+    if spec.get("dist") == "rowscale" and len(shape) >= 2:
+        rows = rng.standard_normal(shape[:-1] + (1,), dtype=np.float64)
+        g = g * np.exp(rows)
+    elif spec.get("dist") == "rowscale":
+        g = g * np.exp(rng.standard_normal((), dtype=np.float64))
+    zf = spec.get("zero_frac", 0.0)
+    if zf > 0:
+        g = np.where(rng.random(shape) < zf, 0.0, g)
+    if spec.get("spike_step") == step:
+        g = g * spec.get("spike_mult", 100.0)
+    g = g.astype(f32)
+    if spec.get("dtype", "f32") == "bf16":
+        return f32_to_bf16_bits(g)
+    return g
+
+
+def digest(arrays):
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+_ADAMW = dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=None, factored=False,
+              relative_step=False, scale_parameter=False, scale_weight_decay=False,
+              d=0.0, eps=(1e-8, 1e-3))
+_CAME = dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=0.9999, factored=True,
+             relative_step=False, scale_parameter=False, scale_weight_decay=False,
+             d=1.0, eps_came=1e-16)
+_RMSPROP = dict(beta1=None, beta2=0.99, beta2_decay=None, beta3=None, factored=False,
+                relative_step=False, scale_parameter=False, scale_weight_decay=False,
+                d=0.0, eps=(1e-8, 1e-3))
+_APOLLO = dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=None, factored=False,
+               relative_step=False, scale_parameter=False, scale_weight_decay=False,
+               d=0.0, eps=(1e-6, 1e-3), apollo_eps=1e-6, apollo_factorize=False,
+               apollo_scale_type="channel", apollo_scale=1.0, apollo_scale_front=False,
+               apollo_cache_proj=True, enable_fira_for_apollo=True)
+
+_G_CFG0 = dict(dist="normal", std=1e-2, zero_frac=0.01, dtype="f32")
+_G_HEAVY = dict(dist="rowscale", std=1e-3, zero_frac=0.005, dtype="bf16")
+_G_BF16 = dict(dist="rowscale", std=1e-3, zero_frac=0.0, dtype="bf16")
+
+# name -> dict(shapes, hp, grad, steps, seed)
+CASES = {
+    # AdamW UF8 (block 256) / AL8 (block 2048), fp32 grads with 1 % exact zeros.
+    "adamw_uf8_al8": dict(shapes=[(64, 200), (4096,)], steps=10, seed=11, grad=_G_CFG0,
+                          hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048,
+                                  m_block_size=256, m_quant_type="uf8", v_quant_type="al8")),
+    # same optimizer + Fira limiter, bf16 heavy-tailed grads, x100 spike on step 5.
+    "adamw_fira_bf16": dict(shapes=[(96, 200), (2048,)], steps=10, seed=12,
+                            grad=dict(_G_HEAVY, spike_step=5, spike_mult=100.0),
+                            hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048,
+                                    m_block_size=256, m_quant_type="uf8", v_quant_type="al8",
+                                    enable_fira_for_adafactor=True, fira_margin=0.01)),
+    # other state formats on the full-rank path.
+    "adamw_uf4_al16": dict(shapes=[(40, 130)], steps=4, seed=13, grad=_G_CFG0,
+                           hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=1024,
+                                   m_block_size=128, m_quant_type="uf4", v_quant_type="al16")),
+    "adamw_d8_al8": dict(shapes=[(40, 130)], steps=4, seed=14, grad=_G_CFG0,
+                         hp=dict(_ADAMW, lr=1e-3, block_size=2048, m_block_size=256,
+                                 m_quant_type="d8", v_quant_type="al8")),
+    "adamw_d4_al8": dict(shapes=[(40, 130)], steps=4, seed=15, grad=_G_CFG0,
+                         hp=dict(_ADAMW, lr=1e-3, block_size=2048, m_block_size=256,
+                                 m_quant_type="d4", v_quant_type="al8")),
+    "adamw_fp32m_al8": dict(shapes=[(40, 130)], steps=4, seed=16, grad=_G_CFG0,
+                            hp=dict(_ADAMW, lr=1e-3, block_size=2048, m_block_size=256,
+                                    m_quant_type="fp32", v_quant_type="al8")),
+    "rmsprop_al8": dict(shapes=[(40, 130)], steps=4, seed=17, grad=_G_CFG0,
+                        hp=dict(_RMSPROP, lr=1e-3, block_size=256)),
+    # unfactored Adafactor (relative step, parameter scaling, clip d=1).
+    "adafactor_unfactored": dict(shapes=[(40, 130), (300,)], steps=4, seed=18, grad=_G_HEAVY,
+                                 hp=dict(factored=False, block_size=256)),
+    # factored Adafactor, constructor defaults, AL8 block 256, no momentum.
+    "adafactor_factored": dict(shapes=[(320, 192), (64, 384), (2048,)], steps=10, seed=19,
+                               grad=_G_HEAVY, hp=dict(block_size=256)),
+    # factored Adafactor with quantised momentum.
+    "adafactor_factored_m": dict(shapes=[(128, 256)], steps=4, seed=20, grad=_G_HEAVY,
+                                 hp=dict(block_size=256, beta1=0.9, relative_step=False,
+                                         lr=1e-3)),
+    # CAME: UF8 momentum, AL16 second moment and confidence, block 2048.
+    "came_al16": dict(shapes=[(320, 192), (64, 384), (4096,)], steps=10, seed=21, grad=_G_BF16,
+                      hp=dict(_CAME, lr=1e-4, m_quant_type="uf8", v_quant_type="al16",
+                              c_quant_type="al16", block_size=2048)),
+    # APOLLO rank 32, projection refreshed every 3 steps, UF8/AL8 low-rank states.
+    "apollo_r32": dict(shapes=[(256, 128), (64, 384), (4096,)], steps=8, seed=22,
+                       grad=dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="bf16"),
+                       hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=32,
+                               apollo_update_proj_gap=3, m_quant_type="uf8",
+                               v_quant_type="al8", block_size=2048)),
+}
+
+
+def case_inputs(name):
+    """-> (params0, grads[step][i]) for a case, steps numbered from 1."""
+    c = CASES[name]
+    params = [make_param(s, c["seed"] * 1000 + i) for i, s in enumerate(c["shapes"])]
+    grads = {}
+    for t in range(1, c["steps"] + 1):
+        grads[t] = [make_grad(s, c["seed"] * 1000 + 500 + i, t, c["grad"])
+                    for i, s in enumerate(c["shapes"])]
+    return params, grads
+
+
+def inputs_digest(params, grads):
+    arrays = list(params)
+    for t in sorted(grads):
+        arrays += grads[t]
+    return digest(arrays)

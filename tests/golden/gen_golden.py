@@ -1,0 +1,89 @@
+"""Generate the golden fixtures in this directory by running the REFERENCE
+optimizer (its pure-PyTorch path, use_cuda_kernel=False) on the seeded inputs
+of cases.py.
+
+Run it where the reference checkout is available:
+
+    python tests/golden/gen_golden.py --reference /path/to/reference [case ...]
+
+It writes one ``<case>.npz`` per case.  Keys: ``digest`` (sha256 of the inputs),
+``t<step>_p<i>_param`` and ``t<step>_p<i>_<state key>`` for every tensor-valued
+state entry after that step.  Arrays of 50 000 elements or more are stored only
+after steps 1, 2 and the last one; smaller ones after every step.
+"""
+import argparse
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import cases  # noqa: E402
+
+BIG = 50000
+
+
+def run_case(name, out_dir):
+    import torch
+    from adafactor8bit import Adafactor8Bit
+
+    c = cases.CASES[name]
+    params0, grads = cases.case_inputs(name)
+    out = {"digest": np.array(cases.inputs_digest(params0, grads))}
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy())) for p in params0]
+    for p in params:
+        p.grad_dtype = None  # allow bf16 grads on fp32 parameters
+    opt = Adafactor8Bit(params, use_cuda_kernel=False, **c["hp"])
+    steps = c["steps"]
+    for t in range(1, steps + 1):
+        for p, g in zip(params, grads[t]):
+            if g.dtype == np.uint16:
+                p.grad = torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(p.shape)
+            else:
+                p.grad = torch.from_numpy(g.copy())
+        opt.step()
+        keep_big = t in (1, 2, steps)
+        for i, p in enumerate(params):
+            entries = {"param": p.detach()}
+            for k, v in opt.state[p].items():
+                if isinstance(v, torch.Tensor):
+                    entries[k] = v
+            for k, v in entries.items():
+                a = v.detach().cpu().contiguous()
+                if a.dtype == torch.int16:
+                    a = a.view(torch.uint16) if hasattr(torch, "uint16") else a
+                a = a.numpy().reshape(-1) if a.dim() != 0 else a.numpy().reshape(1)
+                if a.dtype == np.int16:
+                    a = a.view(np.uint16)
+                if a.size >= BIG and not keep_big:
+                    continue
+                if k == "apollo_proj_matrix_T":
+                    # keep the matrix only when it changed (refresh steps)
+                    prev = out.get(f"_lastP_{i}")
+                    if prev is not None and np.array_equal(prev, a):
+                        continue
+                    out[f"_lastP_{i}"] = a.copy()
+                out[f"t{t}_p{i}_{k}"] = a.copy()
+    out = {k: v for k, v in out.items() if not k.startswith("_lastP_")}
+    path = os.path.join(out_dir, name + ".npz")
+    np.savez_compressed(path, **out)
+    print(f"{name}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference",
+                    help="directory that contains the reference's adafactor8bit package")
+    ap.add_argument("cases", nargs="*")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    import torch
+    torch.manual_seed(0)
+    names = args.cases or list(cases.CASES)
+    for name in names:
+        run_case(name, HERE)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,45 @@
+"""Drive the CPU oracle through a case of tests/golden/cases.py."""
+import numpy as np
+
+import af8_oracle as o
+import cases
+
+FULLRANK_CASES = ["adamw_uf8_al8", "adamw_fira_bf16", "adamw_uf4_al16", "adamw_d8_al8", "adamw_d4_al8",
+                  "adamw_fp32m_al8", "rmsprop_al8", "adafactor_unfactored"]
+
+
+def load_golden(name):
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(cases.__file__)), name + ".npz")
+    return np.load(path)
+
+
+class OracleRun:
+    def __init__(self, name):
+        self.name = name
+        self.case = cases.CASES[name]
+        self.hp = o.hyper(**self.case["hp"])
+        self.params0, self.grads = cases.case_inputs(name)
+        self.params = [p.copy() for p in self.params0]
+        self.states = [o.init_state(p.shape, self.hp) for p in self.params]
+        self.t = 0
+
+    def step_param(self, i, p, g, st):
+        shape = p.shape
+        if self.hp["apollo_rank"] > 0 and len(shape) >= 2:
+            return o.apollo_step(p, g, st, self.hp)
+        if len(shape) >= 2 and self.hp["factored"]:
+            return o.factored_step(p, g, st, self.hp)
+        return o.fullrank_step(p.reshape(-1), g.reshape(-1), st, self.hp)
+
+    def step(self):
+        self.t += 1
+        norms = []
+        for i, (p, st) in enumerate(zip(self.params, self.states)):
+            norms.append(self.step_param(i, p, self.grads[self.t][i], st))
+        return norms
+
+
+def golden_entries(gold, t, i):
+    pre = f"t{t}_p{i}_"
+    return {k[len(pre):]: gold[k] for k in gold.files if k.startswith(pre)}

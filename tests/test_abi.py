@@ -1,0 +1,63 @@
+"""The C-ABI library loads and exports every symbol that include/af8.h declares.
+No compute call is made, so this runs without a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "af8.h")).read()
+    return sorted(set(re.findall(r"AF8_API\s+[A-Za-z_ ]+?\**\s*\*?(af8_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    names = declared_symbols()
+    for must in ("af8_version", "af8_last_error", "af8_fullrank_step", "af8_norm_finalize", "af8_set_qmap"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from adafactor8bit import _native
+    path = _native.library_path()
+    if not os.path.exists(path):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("af8_build", os.path.join(ROOT, "adafactor-8bit_b200", "build.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build()
+    handle = ctypes.CDLL(path)
+    for name in declared_symbols():
+        assert hasattr(handle, name), f"libaf8.so does not export {name}"
+    # the Python binding knows the same set
+    assert sorted(_native.PROTOTYPES) == declared_symbols()
+
+
+def test_version_and_error_string():
+    from adafactor8bit import _native
+    assert _native.version() == 1
+    assert isinstance(_native.lib().af8_last_error(), bytes)
+
+
+def test_struct_sizes_match_header():
+    from adafactor8bit import _native
+    assert _native.FULLRANK_TENSOR.itemsize == 128
+    assert _native.DYN_SCALARS.itemsize == 32
+    assert _native.NORM_TENSOR.itemsize == 56
+    assert ctypes.sizeof(_native.FullrankCfg) == 48
+
+
+def test_bad_arguments_are_rejected_without_a_gpu():
+    from adafactor8bit import _native
+    lib = _native.lib()
+    cfg = _native.FullrankCfg()
+    cfg.block = 100   # not a multiple of 128
+    rc = lib.af8_fullrank_step(ctypes.byref(cfg), None, ctypes.c_void_p(16), 1, 1, None, None, None)
+    assert rc == _native.ERR_INVALID
+    assert b"block" in lib.af8_last_error()
+    with pytest.raises(RuntimeError):
+        _native.check(rc, "af8_fullrank_step")
+    assert lib.af8_fullrank_step(None, None, None, 0, 0, None, None, None) == _native.ERR_INVALID

@@ -1,0 +1,164 @@
+"""Parity of the CUDA full-rank path (through the optimizer class and the C
+ABI) with the CPU oracle and with the reference's golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import parity
+from oracle_runner import FULLRANK_CASES, OracleRun, golden_entries, load_golden
+
+pytestmark = pytest.mark.gpu
+
+CODE_KEYS = ("variance_q", "m_q")
+RANGE_KEYS = ("variance_scale", "variance_min_log", "m_scale")
+
+
+def to_cuda_grad(g, shape):
+    if g.dtype == np.uint16:
+        return torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(shape).cuda()
+    return torch.from_numpy(g.copy()).reshape(shape).cuda()
+
+
+def state_np(st, key):
+    v = st[key]
+    a = v.detach().cpu()
+    if a.dtype == torch.int16:
+        return a.numpy().view(np.uint16).reshape(-1)
+    return a.numpy().reshape(-1)
+
+
+def make_optimizer(run):
+    from adafactor8bit import Adafactor8Bit
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).cuda()) for p in run.params0]
+    for p in params:
+        p.grad_dtype = None
+    return params, Adafactor8Bit(params, **run.case["hp"])
+
+
+def compare_state(name, t, i, st_gpu, st_cpu, p_gpu, p_cpu, strict):
+    """strict: both sides started this step from identical state."""
+    mfmt = st_cpu.get("m_quant_type")
+    for key in CODE_KEYS:
+        if key not in st_cpu:
+            continue
+        a, b = state_np(st_gpu, key), np.asarray(st_cpu[key]).reshape(-1)
+        if key == "m_q" and mfmt in ("uf4", "d4"):
+            a, b = parity.unpack_nibbles(a), parity.unpack_nibbles(b)
+        parity.assert_codes(a, b, f"{name} t{t} p{i} {key}", al16=(b.dtype == np.uint16),
+                            zero_reserved=(key != "m_q"))
+    for key in RANGE_KEYS:
+        if key in st_cpu:
+            parity.assert_ranges(state_np(st_gpu, key), st_cpu[key], f"{name} t{t} p{i} {key}",
+                                 max_ulp=1 if strict else 4)
+    for key in ("variance", "m"):
+        if key in st_cpu:
+            assert parity.rel_l2(state_np(st_gpu, key), st_cpu[key]) <= 1e-6, f"{name} t{t} p{i} {key}"
+    parity.assert_params(p_gpu.detach().cpu().numpy(), p_cpu, f"{name} t{t} p{i} param")
+
+
+@pytest.mark.parametrize("name", FULLRANK_CASES)
+def test_free_running_matches_oracle_and_golden(name, oracle):
+    from adafactor8bit import _engine
+    run = OracleRun(name)
+    if run.hp["m_quant_type"] in ("d8", "d4"):
+        for bits in (8, 4):
+            oracle.set_dynamic_map(bits, _engine.dynamic_map(bits))
+    gold = load_golden(name)
+    assert str(gold["digest"]) == cases.inputs_digest(run.params0, run.grads)
+    params, opt = make_optimizer(run)
+    steps = run.case["steps"]
+    for t in range(1, steps + 1):
+        for p, g in zip(params, run.grads[t]):
+            p.grad = to_cuda_grad(g, p.shape)
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            compare_state(name, t, i, opt.state[p], run.states[i], p, run.params[i], strict=False)
+            if "fira_prev_norm" in run.states[i]:
+                a = float(opt.state[p]["fira_prev_norm"].item())
+                b = float(run.states[i]["fira_prev_norm"])
+                assert abs(a - b) <= 2e-6 * abs(b), f"{name} t{t} p{i} fira_prev_norm {a} vs {b}"
+    # and against what the reference itself produced
+    for i, p in enumerate(params):
+        ref = golden_entries(gold, steps, i)
+        parity.assert_params(p.detach().cpu().numpy(), ref["param"], f"{name} final p{i} vs reference")
+        for key in CODE_KEYS:
+            if key in ref:
+                a, b = state_np(opt.state[p], key), ref[key]
+                if key == "m_q" and run.states[i].get("m_quant_type") in ("uf4", "d4"):
+                    a, b = parity.unpack_nibbles(a), parity.unpack_nibbles(b)
+                parity.assert_codes(a, b, f"{name} final p{i} {key} vs reference",
+                                    al16=(b.dtype == np.uint16), zero_reserved=(key != "m_q"))
+
+
+@pytest.mark.parametrize("name", ["adamw_uf8_al8", "adamw_fira_bf16", "adamw_uf4_al16"])
+def test_teacher_forced_step_matches_oracle(name, oracle):
+    """Each step starts from the oracle's state on both sides: block ranges must
+    then agree to 1 ulp and codes to the +-1 rule."""
+    run = OracleRun(name)
+    params, opt = make_optimizer(run)
+    for t in range(1, run.case["steps"] + 1):
+        for p, g in zip(params, run.grads[t]):
+            p.grad = to_cuda_grad(g, p.shape)
+        if t > 1:   # overwrite the GPU state and parameters with the oracle's
+            for i, p in enumerate(params):
+                st = opt.state[p]
+                p.data.copy_(torch.from_numpy(run.params[i]).reshape(p.shape))
+                for key, val in run.states[i].items():
+                    if isinstance(val, np.ndarray) and key in st and isinstance(st[key], torch.Tensor):
+                        src = torch.from_numpy(val.view(np.int16) if val.dtype == np.uint16 else val)
+                        st[key].copy_(src.reshape(st[key].shape))
+                if "fira_prev_norm" in run.states[i]:
+                    st["fira_prev_norm"].fill_(float(run.states[i]["fira_prev_norm"]))
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            compare_state(name, t, i, opt.state[p], run.states[i], p, run.params[i], strict=True)
+
+
+def test_block_edge_cases(oracle):
+    """All-zero gradients, a constant block, one block plus a one-element tail, and
+    a tensor shorter than one momentum block."""
+    from adafactor8bit import Adafactor8Bit
+    hp = dict(cases.CASES["adamw_uf8_al8"]["hp"], min_8bit_size=1)
+    shapes = [(2048,), (2049,), (4096 + 255,), (100,), (6144,)]
+    rng = np.random.default_rng(3)
+    p0 = [rng.standard_normal(s).astype(np.float32) * 0.02 for s in shapes]
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).cuda()) for p in p0]
+    opt = Adafactor8Bit(params, **hp)
+    ohp = oracle.hyper(**hp)
+    ostates = [oracle.init_state(s, ohp) for s in shapes]
+    oparams = [p.copy() for p in p0]
+    for t in range(1, 4):
+        grads = []
+        for k, s in enumerate(shapes):
+            g = rng.standard_normal(s).astype(np.float32) * 1e-2
+            if k == 0:
+                g[:] = 0.0 if t < 3 else 1e-3          # all-zero block, then a constant block
+            if k == 4:
+                g[2048:4096] = 0.0                      # an all-zero block between live ones
+            grads.append(g)
+        for p, g in zip(params, grads):
+            p.grad = torch.from_numpy(g).cuda()
+        opt.step()
+        torch.cuda.synchronize()
+        for i in range(len(shapes)):
+            oracle.fullrank_step(oparams[i], grads[i], ostates[i], ohp)
+            compare_state("edges", t, i, opt.state[params[i]], ostates[i], params[i], oparams[i], strict=False)
+    st0 = opt.state[params[0]]
+    assert int(st0["variance_q"].max()) == 255 and int(st0["variance_q"].min()) == 255   # constant block
+    st4 = opt.state[params[4]]
+    assert int(st4["variance_q"][2048:4096].max()) == 0                                   # exact zeros kept
+    assert abs(float(st4["variance_min_log"][1]) + 127.23327) < 1e-4
+
+
+def test_cpu_parameters_are_refused():
+    from adafactor8bit import Adafactor8Bit
+    p = torch.nn.Parameter(torch.zeros(8, 8))
+    opt = Adafactor8Bit([p], **cases.CASES["adamw_uf8_al8"]["hp"])
+    p.grad = torch.ones(8, 8)
+    with pytest.raises(RuntimeError):
+        opt.step()
