@@ -135,7 +135,11 @@ class FullrankPlan:
         self.d_sumsq = None
         self.h_table = _PinnedRing(n * N.FULLRANK_TENSOR.itemsize)
         self.h_norm = _PinnedRing(n * N.NORM_TENSOR.itemsize)
+        self.h_scale = None
+        self.d_scale = None
+        self.d_chunks = None
         self._static = None
+        self._alpha_on_device = False
         for p in self.params:
             if p.dtype != torch.float32:
                 raise RuntimeError("the full-rank kernels update fp32 parameters only")
@@ -207,6 +211,11 @@ class FullrankPlan:
         nt["n_blocks"] = self.nblocks
         nt["pre_div_mode"] = pre_div_mode
         nt["alpha"] = table["alpha"]
+        if self._alpha_on_device:
+            nt["alpha_dev"] = (self.d_table.data_ptr() + np.arange(self.n, dtype=np.uint64) * np.uint64(N.FULLRANK_TENSOR.itemsize)
+                               + np.uint64(N.FULLRANK_TENSOR.fields["alpha"][1]))
+        else:
+            nt["alpha_dev"] = 0
         sqrt_n = np.sqrt(self.numel.astype(np.float64))
         nt["sqrt_n"] = sqrt_n.astype(np.float32)
         nt["d"] = np.float32(d)
@@ -232,11 +241,47 @@ class FullrankPlan:
                                        self.d_dyn.data_ptr(), stream.cuda_stream)
         N.check(rc, "af8_norm_finalize")
 
-    def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, stream=None):
+    def _param_scale(self, buf, scale, stream):
+        """Upload the table, then let the device fill alpha / decay from the
+        parameters' RMS (scale_parameter=True, optimizer.py:850-853)."""
+        chunk = N.lib().af8_scale_chunk()
+        nchunks = (self.numel + chunk - 1) // chunk
+        if self.h_scale is None:
+            self.h_scale = _PinnedRing(self.n * N.SCALE_TENSOR.itemsize)
+            self.d_scale = torch.empty(self.n * N.SCALE_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+            self.d_chunks = torch.empty(int(nchunks.sum()), dtype=torch.float32, device=self.device)
+        rc = N.lib().af8_fullrank_upload(ctypes.byref(self.cfg), buf.data_ptr(), self.d_table.data_ptr(), self.n,
+                                         self.total_blocks, stream.cuda_stream)
+        N.check(rc, "af8_fullrank_upload")
+        self.h_table.mark(stream)
+        hb = self.h_scale.next()
+        t = hb.numpy()[: self.n * N.SCALE_TENSOR.itemsize].view(N.SCALE_TENSOR)
+        t["param"] = [p.data_ptr() for p in self.params]
+        t["numel"] = self.numel
+        t["first_chunk"] = np.concatenate([[0], np.cumsum(nchunks)[:-1]])
+        t["sqrt_n"] = np.sqrt(self.numel.astype(np.float64)).astype(np.float32)
+        for k in ("rho", "eps2", "bc", "weight_decay", "bc_mode", "scale_weight_decay"):
+            t[k] = scale[k]
+        rc = N.lib().af8_param_scale(hb.data_ptr(), self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(),
+                                     self.d_table.data_ptr(), N.FULLRANK_TENSOR.itemsize,
+                                     N.FULLRANK_TENSOR.fields["alpha"][1], N.FULLRANK_TENSOR.fields["decay"][1],
+                                     stream.cuda_stream)
+        N.check(rc, "af8_param_scale")
+        self.h_scale.mark(stream)
+        if LAUNCH_LOG is not None:
+            pass
+
+    def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None):
         """One optimizer step for every tensor of the plan
-        (_dispatch_cuda_clip's pass structure, optimizer.py:1048-1077)."""
+        (_dispatch_cuda_clip's pass structure, optimizer.py:1048-1077).
+        scale: per-tensor inputs of af8_param_scale when alpha depends on the
+        parameter RMS; the table's alpha / decay are then produced on the device."""
         stream = stream or torch.cuda.current_stream(self.device)
         buf, table = self.fill_table(grads, scalars)
+        self._alpha_on_device = scale is not None
+        if scale is not None:
+            self._param_scale(buf, scale, stream)
+            buf = None
         mom_only = bool(self.cfg.momentum_only)
         clip_first = d > 0                      # a statistic of the raw update is needed
         if not (fira or clip_first):

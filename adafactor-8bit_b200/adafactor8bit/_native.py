@@ -44,9 +44,17 @@ NORM_TENSOR = np.dtype([
     ("first_block", np.int64), ("n_blocks", np.int64), ("fira_prev", _P),
     ("fira_has_prev", np.int32), ("pre_div_mode", np.int32),
     ("alpha", np.float32), ("clip_div", np.float32), ("sqrt_n", np.float32), ("d", np.float32),
-    ("fira_margin1", np.float32), ("reserved", np.float32),
+    ("fira_margin1", np.float32), ("reserved", np.float32), ("alpha_dev", _P),
 ], align=True)
-assert NORM_TENSOR.itemsize == 56
+assert NORM_TENSOR.itemsize == 64
+
+SCALE_TENSOR = np.dtype([
+    ("param", _P), ("numel", np.int64), ("first_chunk", np.int64),
+    ("sqrt_n", np.float32), ("rho", np.float32), ("eps2", np.float32), ("bc", np.float32),
+    ("weight_decay", np.float32), ("bc_mode", np.int32), ("scale_weight_decay", np.int32),
+    ("reserved", np.int32),
+], align=True)
+assert SCALE_TENSOR.itemsize == 56
 
 
 class FullrankCfg(ctypes.Structure):
@@ -71,7 +79,10 @@ PROTOTYPES = {
     "af8_last_error": (ctypes.c_char_p, []),
     "af8_set_qmap": (_c_i, [_c_p, _c_p, _c_p]),
     "af8_fullrank_step": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
+    "af8_fullrank_upload": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
+    "af8_param_scale": (_c_i, [_c_p, _c_p, _c_i, _c_p, _c_p, _c_l, _c_l, _c_l, _c_p]),
+    "af8_scale_chunk": (_c_i, []),
     "af8_al_dequant": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_i, _c_i, _c_p, _c_p]),
     "af8_al_quant": (_c_i, [_c_p, _c_l, _c_i, _c_i, _c_f, _c_p, _c_p, _c_p, _c_p]),
     "af8_m_dequant": (_c_i, [_c_p, _c_p, _c_l, _c_i, _c_i, _c_p, _c_p]),

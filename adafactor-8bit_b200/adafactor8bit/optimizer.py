@@ -425,9 +425,12 @@ class Adafactor8Bit(Optimizer):
                                 group["maximize"], [p for p, _, _ in items], [s for _, _, s in items])
             plan.ids = ids
             self._plans[pkey] = plan
-        if group["scale_parameter"]:
-            raise NotImplementedError("scale_parameter=True is not available in this build")
         n = len(items)
+        scale = None
+        if group["scale_parameter"]:
+            scale = {k: np.zeros(n, dtype=f32) for k in ("rho", "eps2", "bc", "weight_decay")}
+            scale["bc_mode"] = np.zeros(n, dtype=np.int32)
+            scale["scale_weight_decay"] = np.full(n, int(bool(group.get("scale_weight_decay", True))), dtype=np.int32)
         cols = {k: np.empty(n, dtype=f32) for k in
                 ("decay", "alpha", "v_w", "v_keep", "v_eps_add", "m_w", "eps_gradsq", "eps_denom", "eps_sq")}
         cache = {}
@@ -446,7 +449,16 @@ class Adafactor8Bit(Optimizer):
                 cache[step] = vals
             for k, v in zip(cols, vals):
                 cols[k][i] = v
+            if scale is not None:
+                sc = self._step_scalars(group, step)
+                scale["rho"][i] = sc["rho"]
+                scale["eps2"][i] = f32(sc["eps2"])
+                scale["weight_decay"][i] = f32(group["weight_decay"])
+                if sc["bc_mul"] is not None:
+                    scale["bc"][i], scale["bc_mode"][i] = sc["bc_mul"], 1
+                elif sc["bc_div"] is not None:
+                    scale["bc"][i], scale["bc_mode"][i] = sc["bc_div"], 2
             grads.append(g if g.is_contiguous() else g.contiguous())
         with torch.cuda.device(device):
             plan.run(grads, cols, d=float(group["d"]), fira=bool(group.get("enable_fira_for_adafactor", False)),
-                     fira_margin=float(group.get("fira_margin", 0.01)))
+                     fira_margin=float(group.get("fira_margin", 0.01)), scale=scale)

@@ -21,7 +21,7 @@ NVCC_FLAGS = [
     # exact IEEE arithmetic: no contraction, no approximate division / sqrt, no flush to zero
     "-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-    "-shared", "-cudart", "shared",
+    "-shared", "-cudart", "static",
 ]
 
 

@@ -6,6 +6,7 @@
 #include "fullrank_generic.cuh"
 #include "fullrank_api.cuh"
 #include "codec.cuh"
+#include "scale.cuh"
 
 extern "C" int af8_version(void) { return AF8_VERSION; }
 

@@ -35,6 +35,7 @@ norm_finalize_kernel(const af8_norm_tensor *tensors, const float *block_sumsq, a
     if (tid != 0) return;
 
     float norm = __double2float_rn(sqrt(s_acc[0]));
+    const float alpha = T.alpha_dev ? *T.alpha_dev : T.alpha;
     af8_dyn_scalars out = dyn[blockIdx.x];
     out.norm = norm;
     if (T.pre_div_mode == 1) {
@@ -42,7 +43,7 @@ norm_finalize_kernel(const af8_norm_tensor *tensors, const float *block_sumsq, a
         float cf = __fdiv_rn(rms, T.d);
         cf = (cf >= 1.0f || isnan(cf)) ? cf : 1.0f;
         out.pre_div = cf;
-        out.step = -T.alpha;
+        out.step = -alpha;
         out.fira = 1.0f;
         out.zero = 0.0f;
         dyn[blockIdx.x] = out;
@@ -68,7 +69,7 @@ norm_finalize_kernel(const af8_norm_tensor *tensors, const float *block_sumsq, a
         const float x = __fdiv_rn(norm, T.clip_div);
         denom = (x >= 1.0f || isnan(x)) ? x : 1.0f;
     }
-    out.step = __fdiv_rn(-T.alpha, denom);
+    out.step = __fdiv_rn(-alpha, denom);
     out.fira = fs;
     out.zero = zero;
     if (T.pre_div_mode != 2) out.pre_div = 1.0f;
@@ -210,6 +211,20 @@ extern "C" int af8_fullrank_step(const af8_fullrank_cfg *cfg, const af8_fullrank
                       c.mode != AF8_MODE_SUMSQ_M;
     if (c.grad_dtype == AF8_BF16) return dispatch_mode<bf16_tag>(fast, c.mode, L, C, st);
     return dispatch_mode<float>(fast, c.mode, L, C, st);
+}
+
+extern "C" int af8_fullrank_upload(const af8_fullrank_cfg *cfg, const af8_fullrank_tensor *host_tensors,
+                                   af8_fullrank_tensor *dev_tensors, int32_t n_tensors, int64_t total_blocks,
+                                   void *stream)
+{
+    using namespace af8;
+    if (!cfg || !host_tensors || !dev_tensors) return fail(AF8_ERR_INVALID, "af8_fullrank_upload: null argument");
+    if (n_tensors <= 0 || cfg->block < 128 || cfg->block % 128 != 0) return fail(AF8_ERR_INVALID, "af8_fullrank_upload: bad sizes");
+    int rc = validate_fullrank_table(*cfg, host_tensors, n_tensors, total_blocks);
+    if (rc) return rc;
+    AF8_CUDA_TRY(cudaMemcpyAsync(dev_tensors, host_tensors, sizeof(af8_fullrank_tensor) * (size_t)n_tensors,
+                                 cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return AF8_OK;
 }
 
 extern "C" int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors, const float *block_sumsq,

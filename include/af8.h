@@ -158,6 +158,15 @@ AF8_API int af8_fullrank_step(const af8_fullrank_cfg *cfg,
                       int64_t total_blocks, const af8_dyn_scalars *dyn,
                       float *block_sumsq, void *stream);
 
+/* Validate a host table and enqueue its copy into dev_tensors without
+ * launching a kernel.  Use it when the device table must be patched (see
+ * af8_param_scale) before af8_fullrank_step runs with host_tensors == NULL.
+ * No counterpart in the reference, which passes scalars per launch. */
+AF8_API int af8_fullrank_upload(const af8_fullrank_cfg *cfg,
+                                const af8_fullrank_tensor *host_tensors,
+                                af8_fullrank_tensor *dev_tensors, int32_t n_tensors,
+                                int64_t total_blocks, void *stream);
+
 /* Per-tensor description for af8_norm_finalize. */
 typedef struct af8_norm_tensor {
     int64_t first_block;    /* first entry of block_sumsq that belongs to the tensor */
@@ -176,6 +185,8 @@ typedef struct af8_norm_tensor {
     float d;
     float fira_margin1;     /* float(1 + fira_margin) */
     float reserved;
+    const float *alpha_dev; /* when not NULL: device location of alpha (overrides `alpha`);
+                               used when af8_param_scale computed it on the device */
 } af8_norm_tensor;
 
 /* Reduce the per-block partial sums of each tensor (fixed order, binary64),
@@ -187,6 +198,42 @@ typedef struct af8_norm_tensor {
 AF8_API int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors,
                       const float *block_sumsq, af8_dyn_scalars *dyn,
                       void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Parameter-scaled step size                                                */
+/* ------------------------------------------------------------------------ */
+
+/* One tensor of af8_param_scale. */
+typedef struct af8_scale_tensor {
+    const float *param;
+    int64_t numel;
+    int64_t first_chunk;        /* running sum of ceil(numel / af8_scale_chunk()) */
+    float sqrt_n;               /* float(sqrt(numel)) */
+    float rho;                  /* relative or fixed learning rate of this step */
+    float eps2;                 /* lower bound of the parameter RMS */
+    float bc;                   /* bias-correction factor, see bc_mode */
+    float weight_decay;         /* 0 disables */
+    int32_t bc_mode;            /* 0: none, 1: alpha *= bc, 2: alpha /= bc */
+    int32_t scale_weight_decay; /* 1: decay uses alpha, 0: decay uses rho */
+    int32_t reserved;
+} af8_scale_tensor;
+
+/* alpha = max(||p|| / sqrt(n), eps2) * rho (then bias correction) and
+ * decay = 1 - mult * weight_decay for every tensor, written into the float
+ * fields at alpha_offset / decay_offset of row i of a device table whose rows
+ * are table_stride bytes apart (for af8_fullrank_tensor: stride 128, offsets of
+ * `alpha` and `decay`).  chunk_sumsq is scratch: one float per chunk of
+ * af8_scale_chunk() parameters, summed over the tensors.
+ * Replaces the torch.linalg.vector_norm pass of _compute_alpha with
+ * scale_parameter=True (optimizer.py:850-853) and the 0-d tensor arithmetic
+ * after it (optimizer.py:2020-2039). */
+AF8_API int af8_param_scale(const af8_scale_tensor *host_tensors,
+                            af8_scale_tensor *dev_tensors, int32_t n_tensors,
+                            float *chunk_sumsq, void *dev_table, int64_t table_stride,
+                            int64_t alpha_offset, int64_t decay_offset, void *stream);
+
+/* Number of parameters per partial sum of af8_param_scale. */
+AF8_API int af8_scale_chunk(void);
 
 /* ------------------------------------------------------------------------ */
 /* Stand-alone codecs (state migration, checkpoint conversion, tests)        */

@@ -46,7 +46,8 @@ def test_struct_sizes_match_header():
     from adafactor8bit import _native
     assert _native.FULLRANK_TENSOR.itemsize == 128
     assert _native.DYN_SCALARS.itemsize == 32
-    assert _native.NORM_TENSOR.itemsize == 56
+    assert _native.NORM_TENSOR.itemsize == 64
+    assert _native.SCALE_TENSOR.itemsize == 56
     assert ctypes.sizeof(_native.FullrankCfg) == 48
 
 
