@@ -557,3 +557,206 @@ AF8O_API int af8o_fullrank_step(const af8o_fullrank_cfg *c, float *p,
     free(u);
     return rc;
 }
+
+/* ------------------------------------------------------------------ */
+/* factored step ("2D" path): Adafactor and CAME                       */
+/* ------------------------------------------------------------------ */
+
+/* A small second-moment / confidence state of n elements: quantised
+ * (q/scale/min_log, fmt 8 or 16) or fp32 (f32, fmt 0). */
+typedef struct {
+    void *q;
+    float *scale;
+    float *min_log;
+    float *f32;
+    int64_t n;
+    int32_t fmt;
+    int32_t pad_;
+} af8o_small_state;
+
+typedef struct {
+    int64_t rows, cols;
+    int64_t block;        /* AL block of the row / col / conf states */
+    int64_t m_block;
+    int32_t grad_dtype;
+    int32_t m_fmt;        /* AF8O_M_NONE when beta1 is None */
+    int32_t came;         /* beta3 is not None */
+    int32_t negate_grad;
+    int32_t fira;
+    int32_t has_decay;
+    float decay;
+    float alpha;
+    float v_w;            /* beta_val */
+    float m_w;            /* float(1 - beta1) */
+    float c_w;            /* float(1 - beta3) */
+    float eps1;
+    float eps_came;
+    float d;
+    float sqrt_n;         /* float(sqrt(rows*cols)) */
+    float clip_div;       /* float(sqrt(rows*cols)*d) */
+    float fira_margin1;
+    float v_floor;
+} af8o_factored_cfg;
+
+/* deq -> lerp_ -> requant of one small state (optimizer.py:2232-2238,
+ * 937-946), or lerp_ of the fp32 state (optimizer.py:2248-2251).
+ * out receives the un-requantised values. */
+static void small_state_ema(af8o_small_state *s, const float *new_vals, float w,
+                            int64_t block, float floor_log, float *out)
+{
+    const int64_t n = s->n;
+    if (s->fmt == AF8O_V_FP32) {
+        for (int64_t i = 0; i < n; ++i) {
+            s->f32[i] = lerp_t(s->f32[i], new_vals[i], w);
+            out[i] = s->f32[i];
+        }
+        return;
+    }
+    af8o_al_dequantize(s->q, s->scale, s->min_log, n, block, s->fmt, out);
+    for (int64_t i = 0; i < n; ++i) out[i] = lerp_t(out[i], new_vals[i], w);
+    af8o_al_quantize(out, n, block, floor_log, s->fmt, s->q, s->scale, s->min_log);
+}
+
+/* row means and column means of x[R][C], binary64 accumulation
+ * (Tensor.mean(dim=-1) / mean(dim=-2), optimizer.py:2222-2223, 933-934) */
+static void row_col_means(const float *x, int64_t R, int64_t C, float *rmean, float *cmean)
+{
+    double *cs = (double *)calloc((size_t)C, sizeof(double));
+#pragma omp parallel
+    {
+        double *local = (double *)calloc((size_t)C, sizeof(double));
+#pragma omp for schedule(static)
+        for (int64_t i = 0; i < R; ++i) {
+            double rs = 0.0;
+            const float *row = x + i * C;
+            for (int64_t j = 0; j < C; ++j) { rs += (double)row[j]; local[j] += (double)row[j]; }
+            rmean[i] = (float)(rs / (double)C);
+        }
+#pragma omp critical
+        for (int64_t j = 0; j < C; ++j) cs[j] += local[j];
+        free(local);
+    }
+    for (int64_t j = 0; j < C; ++j) cmean[j] = (float)(cs[j] / (double)R);
+    free(cs);
+}
+
+static float mean_f64(const float *x, int64_t n)
+{
+    double a = 0.0;
+    for (int64_t i = 0; i < n; ++i) a += (double)x[i];
+    return (float)(a / (double)n);
+}
+
+/* _update_param_8bit, factored branch on the pure-PyTorch route
+ * (optimizer.py:2202-2253 statistics, 2394-2399 / 2543-2549 dispatch),
+ * _factored_inv_std (optimizer.py:818-821), _compute_ut_clipped
+ * (optimizer.py:824-829) and _fallback_2d_update (optimizer.py:920-970). */
+AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void *grad,
+                                af8o_small_state *row_var, af8o_small_state *col_var,
+                                af8o_small_state *conf_row, af8o_small_state *conf_col,
+                                uint8_t *m_q, float *m_scale, float *m_f32, const float *map,
+                                int *fira_has_prev, float *fira_prev, float *norm_out)
+{
+    const int64_t R = c->rows, C = c->cols, n = R * C;
+    const int has_m = c->m_fmt != AF8O_M_NONE;
+    const int m_quant = has_m && c->m_fmt != AF8O_M_FP32;
+    float *g = (float *)malloc((size_t)n * sizeof(float));
+    float *u = (float *)malloc((size_t)n * sizeof(float));
+    float *rmean = (float *)malloc((size_t)R * sizeof(float));
+    float *cmean = (float *)malloc((size_t)C * sizeof(float));
+    float *row = (float *)malloc((size_t)R * sizeof(float));
+    float *col = (float *)malloc((size_t)C * sizeof(float));
+    float *inv_r = (float *)malloc((size_t)R * sizeof(float));
+    float *inv_c = (float *)malloc((size_t)C * sizeof(float));
+    if (!g || !u || !rmean || !cmean || !row || !col || !inv_r || !inv_c) return 2;
+
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        g[i] = load_grad(grad, c->grad_dtype, i, c->negate_grad);
+        if (c->has_decay) p[i] = p[i] * c->decay;          /* optimizer.py:2039 */
+        u[i] = g[i] * g[i];                                /* optimizer.py:2221 */
+    }
+    row_col_means(u, R, C, rmean, cmean);                  /* optimizer.py:2222-2223 */
+    for (int64_t i = 0; i < R; ++i) rmean[i] = rmean[i] + c->eps1;
+    for (int64_t j = 0; j < C; ++j) cmean[j] = cmean[j] + c->eps1;
+
+    /* optimizer.py:2232-2238 / 2248-2252 */
+    small_state_ema(row_var, rmean, c->v_w, c->block, c->v_floor, row);
+    small_state_ema(col_var, cmean, c->v_w, c->block, c->v_floor, col);
+    float rm = mean_f64(row, R);
+    if (rm < c->eps1) rm = c->eps1;
+    for (int64_t i = 0; i < R; ++i) inv_r[i] = rsqrt_t(row[i] / rm);   /* optimizer.py:819 */
+    for (int64_t j = 0; j < C; ++j) inv_c[j] = rsqrt_t(col[j]);        /* optimizer.py:820 */
+
+    float norm = -1.0f;
+    int rc = 0;
+    if (c->came && has_m) {
+        /* optimizer.py:928-956 */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float t = g[i] * inv_r[i / C];                 /* optimizer.py:825 */
+            g[i] = t * inv_c[i % C];
+        }
+        if (c->d > 0.0f) {                                 /* optimizer.py:826-828 */
+            float rms = norm2_f64(g, n) / c->sqrt_n;
+            float cf = rms / c->d;
+            if (cf < 1.0f) cf = 1.0f;
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < n; ++i) g[i] = g[i] / cf;
+        }
+        float *m = m_quant ? u : m_f32;
+        if (m_quant) af8o_m_dequantize(m_q, m_scale, n, c->m_block, c->m_fmt, map, m);
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) m[i] = lerp_t(m[i], g[i], c->m_w);
+        if (m_quant) rc = af8o_m_quantize(m, n, c->m_block, c->m_fmt, map, m_q, m_scale);
+        /* res = (U - M)^2 + eps_came, in place in U (optimizer.py:932) */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float t = g[i] - m[i];
+            t = t * t;
+            g[i] = t + c->eps_came;
+        }
+        row_col_means(g, R, C, rmean, cmean);              /* optimizer.py:933-934 */
+        small_state_ema(conf_row, rmean, c->c_w, c->block, c->v_floor, row);   /* optimizer.py:937-946 */
+        small_state_ema(conf_col, cmean, c->c_w, c->block, c->v_floor, col);
+        float cm = mean_f64(row, R);                       /* optimizer.py:948 */
+        if (cm < c->eps1) cm = c->eps1;
+        for (int64_t i = 0; i < R; ++i) inv_r[i] = rsqrt_t(row[i] / cm);
+        for (int64_t j = 0; j < C; ++j) inv_c[j] = rsqrt_t(col[j]);
+        if (!m_quant) memcpy(u, m, (size_t)n * sizeof(float));
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {                  /* optimizer.py:952, 955 */
+            float t = u[i] * inv_r[i / C];
+            u[i] = t * inv_c[i % C];
+        }
+        norm = apply_update(p, u, n, c->alpha, 0.0f, c->clip_div, c->fira, c->fira_margin1,
+                            fira_has_prev, fira_prev);
+    } else if (has_m) {
+        /* optimizer.py:958-965 */
+        float *m = m_quant ? u : m_f32;
+        if (m_quant) af8o_m_dequantize(m_q, m_scale, n, c->m_block, c->m_fmt, map, m);
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) m[i] = lerp_t(m[i], g[i], c->m_w);
+        if (m_quant) rc = af8o_m_quantize(m, n, c->m_block, c->m_fmt, map, m_q, m_scale);
+        if (!m_quant) memcpy(u, m, (size_t)n * sizeof(float));
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float t = u[i] * inv_r[i / C];
+            u[i] = t * inv_c[i % C];
+        }
+        norm = apply_update(p, u, n, c->alpha, c->d, c->clip_div, c->fira, c->fira_margin1,
+                            fira_has_prev, fira_prev);
+    } else {
+        /* optimizer.py:967-970 */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float t = g[i] * inv_r[i / C];
+            u[i] = t * inv_c[i % C];
+        }
+        norm = apply_update(p, u, n, c->alpha, c->d, c->clip_div, c->fira, c->fira_margin1,
+                            fira_has_prev, fira_prev);
+    }
+    if (norm_out) *norm_out = norm;
+    free(g); free(u); free(rmean); free(cmean); free(row); free(col); free(inv_r); free(inv_c);
+    return rc;
+}

@@ -406,3 +406,96 @@ def fullrank_step(p, g, state, hp, sc=None):
     if has_prev.value:
         state["fira_prev_norm"] = f32(prev.value)
     return float(norm.value)
+
+
+# ---------------------------------------------------------------------------
+# factored path
+# ---------------------------------------------------------------------------
+class SmallState(ctypes.Structure):
+    _fields_ = [("q", c_p), ("scale", c_p), ("min_log", c_p), ("f32", c_p), ("n", c_l),
+                ("fmt", c_i), ("pad_", c_i)]
+
+
+class FactoredCfg(ctypes.Structure):
+    _fields_ = [
+        ("rows", c_l), ("cols", c_l), ("block", c_l), ("m_block", c_l),
+        ("grad_dtype", c_i), ("m_fmt", c_i), ("came", c_i), ("negate_grad", c_i),
+        ("fira", c_i), ("has_decay", c_i),
+        ("decay", c_f), ("alpha", c_f), ("v_w", c_f), ("m_w", c_f), ("c_w", c_f),
+        ("eps1", c_f), ("eps_came", c_f), ("d", c_f), ("sqrt_n", c_f), ("clip_div", c_f),
+        ("fira_margin1", c_f), ("v_floor", c_f),
+    ]
+
+
+def _small(state, prefix, n, fmt):
+    s = SmallState()
+    s.n = n
+    s.fmt = V_FMT[fmt]
+    if fmt == "fp32":
+        s.f32 = _ptr(state[prefix])
+    else:
+        s.q = _ptr(state[prefix + "_q"])
+        s.scale = _ptr(state[prefix + "_scale"])
+        s.min_log = _ptr(state[prefix + "_min_log"])
+    return s
+
+
+def factored_step(p, g, state, hp, sc=None):
+    """Factored branch of _update_param_8bit (optimizer.py:2202-2552, pure route)."""
+    assert p.dtype == f32 and p.ndim == 2 and p.flags.c_contiguous
+    lib_ = lib()
+    if not hasattr(lib_, "_factored_ready"):
+        lib_.af8o_factored_step.argtypes = [ctypes.POINTER(FactoredCfg), c_p, c_p] + \
+            [ctypes.POINTER(SmallState)] * 4 + [c_p, c_p, c_p, c_p, ctypes.POINTER(c_i),
+                                                ctypes.POINTER(c_f), ctypes.POINTER(c_f)]
+        lib_._factored_ready = True
+    if sc is None:
+        sc = prologue(p, state, hp)
+    R, C = p.shape
+    n = R * C
+    g, gdt = _grad_args(g)
+    quant = state["is_quantized"]
+    vqt = state["v_quant_type"] if quant else "fp32"
+    cqt = state["c_quant_type"] if quant else "fp32"
+    has_m = hp["beta1"] is not None
+    mqt = state.get("m_quant_type", "uf8") if has_m else None
+    came = hp["beta3"] is not None and has_m
+    cfg = FactoredCfg()
+    cfg.rows, cfg.cols = R, C
+    cfg.block = state["block_size"]
+    cfg.m_block = state.get("m_block_size", hp["m_block_size"])
+    cfg.grad_dtype = gdt
+    cfg.m_fmt = M_FMT[mqt]
+    cfg.came = int(came)
+    cfg.negate_grad = int(bool(hp["maximize"]))
+    cfg.fira = int(bool(hp["enable_fira_for_adafactor"]))
+    cfg.has_decay = int(sc["decay"] is not None)
+    cfg.decay = float(sc["decay"]) if sc["decay"] is not None else 1.0
+    cfg.alpha = float(sc["alpha"])
+    cfg.v_w = float(f32(sc["beta_val"]))
+    cfg.m_w = float(f32(1.0 - hp["beta1"])) if has_m else 0.0
+    cfg.c_w = float(f32(1.0 - hp["beta3"])) if came else 0.0
+    cfg.eps1 = float(f32(sc["eps1"]))
+    cfg.eps_came = float(f32(hp["eps_came"]))
+    cfg.d = float(f32(hp["d"]))
+    cfg.sqrt_n = float(f32(math.sqrt(n)))
+    cfg.clip_div = float(f32(math.sqrt(n) * hp["d"]))
+    cfg.fira_margin1 = float(f32(1.0 + hp["fira_margin"]))
+    cfg.v_floor = -126.0
+    row = _small(state, "row_var", R, vqt)
+    col = _small(state, "col_var", C, vqt)
+    crow = _small(state, "conf_row", R, cqt) if came else SmallState()
+    ccol = _small(state, "conf_col", C, cqt) if came else SmallState()
+    has_prev = c_i(1 if "fira_prev_norm" in state else 0)
+    prev = c_f(float(state.get("fira_prev_norm", 0.0)))
+    norm = c_f(-1.0)
+    rc = lib_.af8o_factored_step(
+        ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), ctypes.byref(row), ctypes.byref(col),
+        ctypes.byref(crow), ctypes.byref(ccol), _ptr(state.get("m_q")), _ptr(state.get("m_scale")),
+        _ptr(state.get("m")), _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev),
+        ctypes.byref(norm))
+    if rc != 0:
+        raise RuntimeError(f"af8o_factored_step failed with {rc}")
+    if has_prev.value:
+        state["fira_prev_norm"] = f32(prev.value)
+    return float(norm.value)
