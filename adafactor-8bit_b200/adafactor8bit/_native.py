@@ -81,6 +81,8 @@ PROTOTYPES = {
     "af8_fullrank_step": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
     "af8_fullrank_upload": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
+    "af8_fullrank_limited_step_noalloc": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_f, _c_i, _c_f, _c_p, _c_i, _c_p, _c_p]),
+    "af8_noalloc_max_numel": (_c_l, [_c_i]),
     "af8_param_scale": (_c_i, [_c_p, _c_p, _c_i, _c_p, _c_p, _c_l, _c_l, _c_l, _c_p]),
     "af8_scale_chunk": (_c_i, []),
     "af8_al_dequant": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_i, _c_i, _c_p, _c_p]),

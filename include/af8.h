@@ -200,6 +200,54 @@ AF8_API int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors,
                       void *stream);
 
 /* ------------------------------------------------------------------------ */
+/* Step without caller-provided working memory                               */
+/* ------------------------------------------------------------------------ */
+
+/* The limited full-rank step (statistic pass, norm / Fira / clip scalars, apply
+ * pass) for ONE tensor, using no memory besides the tensor's own parameter,
+ * gradient and states.  It has no counterpart in the reference.
+ *
+ * It exists for callers that cannot come up with device buffers when they
+ * step: a foreign-language binding that only forwards pointers it was given
+ * and has no device allocator, or a process in which a framework's allocator
+ * already holds the whole GPU, so that an extra cudaMalloc would fail or stall.
+ * The descriptor row, the per-tensor scalars and the per-block partial sums
+ * that af8_fullrank_step takes from the caller live here in a 1 MiB array that
+ * is part of the library image (each GPU that loads the library holds one copy
+ * until the process ends).  The call performs no cudaMalloc / cudaFree and uses
+ * no allocating library routine.
+ *
+ *   cfg          as for af8_fullrank_step; cfg->mode is ignored and the
+ *                momentum-only rule is not covered
+ *   host_tensor  HOST pointer to one filled af8_fullrank_tensor (first_block is
+ *                ignored); passed to the device as a kernel argument
+ *   clip_d       RMS clip threshold d (0 disables)
+ *   fira         non-zero: run the Fira norm-growth limiter with fira_margin1 =
+ *                float(1 + fira_margin); fira_prev is the device scalar that holds the previous limited
+ *                norm (read when fira_has_prev != 0, always written)
+ *   norm_out     optional device float that receives the measured update norm
+ *
+ * Limit: at most af8_noalloc_max_numel(cfg->block) elements (262,080 V blocks:
+ * 536,739,840 elements at block 2048); larger tensors are rejected with
+ * AF8_ERR_UNSUPPORTED and a message that names the limit.
+ *
+ * The first call on each device resolves the array's device address (which can
+ * load the library's device code); make that first call outside any stream
+ * capture.  All calls on a device share the one array and it keeps the previous
+ * call's contents; the call itself clears what it needs cleared.  Two calls
+ * whose GPU work can overlap (different streams, different threads) race on
+ * the array: serialise them on one stream or with events. */
+AF8_API int af8_fullrank_limited_step_noalloc(const af8_fullrank_cfg *cfg,
+                                              const af8_fullrank_tensor *host_tensor,
+                                              float clip_d, int32_t fira, float fira_margin1,
+                                              float *fira_prev, int32_t fira_has_prev,
+                                              float *norm_out, void *stream);
+
+/* Largest tensor the call above accepts for a V block size (0 for an invalid
+ * block size). */
+AF8_API int64_t af8_noalloc_max_numel(int32_t block);
+
+/* ------------------------------------------------------------------------ */
 /* Parameter-scaled step size                                                */
 /* ------------------------------------------------------------------------ */
 

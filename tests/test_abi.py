@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def declared_symbols():
     text = open(os.path.join(ROOT, "include", "af8.h")).read()
-    return sorted(set(re.findall(r"AF8_API\s+[A-Za-z_ ]+?\**\s*\*?(af8_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"AF8_API\s+[A-Za-z0-9_ ]+?\**\s*\*?(af8_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_header_declares_entry_points():
