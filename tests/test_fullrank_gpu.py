@@ -162,3 +162,44 @@ def test_cpu_parameters_are_refused():
     p.grad = torch.ones(8, 8)
     with pytest.raises(RuntimeError):
         opt.step()
+
+
+@pytest.mark.parametrize("kind", ["normal_f32", "rowscale_bf16", "narrow_range", "spiky"])
+def test_large_tensor_codes_are_exact(kind, oracle):
+    """Millions of elements through the specialised kernel: its estimate-then-verify
+    code path must reproduce the exact sequence on every element, not just within
+    the +-1 allowance."""
+    from adafactor8bit import Adafactor8Bit
+    hp = dict(cases.CASES["adamw_uf8_al8"]["hp"])
+    shape = (1024, 2048)
+    rng = np.random.default_rng(hash(kind) % 2 ** 31)
+    p0 = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    param = torch.nn.Parameter(torch.from_numpy(p0.copy()).cuda())
+    param.grad_dtype = None
+    opt = Adafactor8Bit([param], **hp)
+    ohp = oracle.hyper(**hp)
+    ost = oracle.init_state(shape, ohp)
+    op = p0.copy()
+    for t in range(1, 5):
+        if kind == "normal_f32":
+            g = (rng.standard_normal(shape) * 1e-2).astype(np.float32)
+            g[rng.random(shape) < 0.01] = 0.0
+        elif kind == "rowscale_bf16":
+            g = cases.make_grad(shape, 31337, t, cases._G_HEAVY)
+        elif kind == "narrow_range":
+            g = (1e-3 * (1.0 + 1e-4 * rng.standard_normal(shape))).astype(np.float32)
+        else:
+            g = (rng.standard_normal(shape) * 1e-4).astype(np.float32)
+            g[rng.random(shape) < 1e-3] *= 1e4
+            g[:, :7] = 0.0
+        param.grad = to_cuda_grad(g, shape)
+        opt.step()
+        oracle.fullrank_step(op.reshape(-1), g.reshape(-1), ost, ohp)
+        torch.cuda.synchronize()
+        st = opt.state[param]
+        for key in ("variance_q", "m_q"):
+            s = parity.code_stats(state_np(st, key), ost[key])
+            assert s["neq"] == 0, f"{kind} step {t} {key}: {s}"
+        for key in RANGE_KEYS:
+            assert int(parity.ulp_diff(state_np(st, key), ost[key]).max()) == 0, f"{kind} step {t} {key}"
+        parity.assert_params(param.detach().cpu().numpy(), op, f"{kind} step {t} param", tol=1e-6)
