@@ -77,6 +77,7 @@ _c_f = ctypes.c_float
 PROTOTYPES = {
     "af8_version": (_c_i, []),
     "af8_last_error": (ctypes.c_char_p, []),
+    "af8_device_status": (_c_i, [ctypes.POINTER(ctypes.c_int32), _c_p]),
     "af8_set_qmap": (_c_i, [_c_p, _c_p, _c_p]),
     "af8_fullrank_step": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
     "af8_fullrank_upload": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p]),
@@ -123,6 +124,13 @@ def check(rc, what):
     if rc != OK:
         msg = lib().af8_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{what} failed (code {rc}): {msg}")
+
+
+def device_status(stream=None):
+    """Synchronise `stream` (a raw cudaStream_t or None) and return the sticky device error flag."""
+    out = ctypes.c_int32(0)
+    check(lib().af8_device_status(ctypes.byref(out), stream), "af8_device_status")
+    return out.value
 
 
 def version():

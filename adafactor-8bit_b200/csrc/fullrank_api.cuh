@@ -95,6 +95,9 @@ template <typename GradT, int MODE>
 inline int launch_fast(const FullrankLaunch &L, cudaStream_t st)
 {
     int grid = 0;
+    // the two-stage ring needs up to 43 KB per CTA: ask for the large shared-memory carve-out
+    AF8_CUDA_TRY(cudaFuncSetAttribute(fullrank_fast_kernel<GradT, MODE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      (int)cudaSharedmemCarveoutMaxShared));
     int rc = persistent_grid(fullrank_fast_kernel<GradT, MODE>, FAST_THREADS, 0, L.total_blocks, &grid);
     if (rc) return rc;
     fullrank_fast_kernel<GradT, MODE><<<grid, FAST_THREADS, 0, st>>>(L);
@@ -224,6 +227,18 @@ extern "C" int af8_fullrank_upload(const af8_fullrank_cfg *cfg, const af8_fullra
     if (rc) return rc;
     AF8_CUDA_TRY(cudaMemcpyAsync(dev_tensors, host_tensors, sizeof(af8_fullrank_tensor) * (size_t)n_tensors,
                                  cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return AF8_OK;
+}
+
+extern "C" int af8_device_status(int32_t *status_out, void *stream)
+{
+    using namespace af8;
+    if (!status_out) return fail(AF8_ERR_INVALID, "af8_device_status: null output");
+    int v = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    AF8_CUDA_TRY(cudaMemcpyFromSymbolAsync(&v, g_device_error, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
+    AF8_CUDA_TRY(cudaStreamSynchronize(st));
+    *status_out = v;
     return AF8_OK;
 }
 

@@ -10,12 +10,20 @@
 // Work decomposition.  The launch covers a table of tensors; the unit of work
 // is one V block (2048 consecutive elements of one tensor).  A persistent grid
 // walks the flat block space with a grid stride.  One CTA of 256 threads owns a
-// block; thread t owns elements [8t, 8t+8), so warp w owns exactly M block w of
-// the V block and the momentum absmax is a pure warp reduction.  All global
-// accesses of full blocks are 64- or 128-bit wide and contiguous across a warp.
-// Everything a thread needs between the load and the requantisation stays in
-// registers; shared memory only holds the 256-entry AL8 decode table of the
-// block, the tensor descriptor and the cross-warp extrema.
+// block; warp w owns elements [256w, 256w+256), i.e. exactly M block w, so the
+// momentum absmax is a pure warp reduction.  Lane l of the warp owns the two
+// 4-element groups at 256w+4l and 256w+128+4l: every shared-memory read and
+// every global store of a warp is one contiguous 128/256/512-byte run.
+//
+// Data movement.  The parameter, gradient and both code arrays of a full block
+// are brought into a two-stage shared-memory ring by bulk asynchronous copies
+// (cp.async.bulk, completion on an mbarrier).  While block i is being processed
+// the copies of block i+1 of the same tensor are already in flight, and the
+// 256-entry AL8 decode table of block i+1 is computed while warp 0 derives the
+// range of block i.  Tail blocks (fewer than 2048 real elements) and the first
+// block a CTA touches in a tensor take a plain-load path.  Every wait on an
+// mbarrier is bounded; a wait that runs out raises the device error flag that
+// af8_device_status() reports and the CTA stops without further stores.
 //
 // Instruction budget.  At 14-16 bytes per parameter the HBM roofline leaves
 // roughly 60 issue slots per parameter, so exact IEEE arithmetic is spent only
@@ -150,179 +158,408 @@ __device__ __forceinline__ float lerp_sel(float s, float e, float w, float wm1)
     return SMALL_W ? __fmaf_rn(w, d, s) : __fmaf_rn(wm1, d, e);
 }
 
+// ---------------------------------------------------------------------------
+// device error flag, mbarrier and bulk-copy helpers
+// ---------------------------------------------------------------------------
+// Set (never cleared by kernels) when a bounded wait ran out.  Read back by
+// af8_device_status().
+__device__ int g_device_error = 0;
+constexpr int DEVERR_COPY_TIMEOUT = 1;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Wait for a phase of the barrier for at most two seconds of wall time (a block's
+// copies take microseconds).  Returns false when the time ran out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity)
+{
+    uint64_t t0 = 0;
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 0xffu) == 0xffu) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) return false;
+        }
+    }
+}
+// global -> shared bulk copy of `bytes` (multiple of 16, both addresses 16-byte
+// aligned); completion is signalled on `bar` as transaction bytes.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <typename T> struct GradBytes { static constexpr int value = 4; };
+template <> struct GradBytes<bf16_tag> { static constexpr int value = 2; };
+
+// ---------------------------------------------------------------------------
+// EMAs and update of a thread's 8 elements
+// ---------------------------------------------------------------------------
+struct StepScalars {
+    float decay, v_w, v_wm1, m_w, m_wm1, eps_g, eps_d, step_mul, fira;
+    bool zero_upd;
+};
+
+template <int MODE, bool SMALL_W, bool TAIL>
+__device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], const uint32_t (&mq)[2],
+                                           const uint32_t (&vq)[2], const float *tab, float mc,
+                                           const StepScalars &S, int nva, int nvb, float (&v)[8], float (&m)[8],
+                                           float &acc)
+{
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t vcode = __byte_perm(vq[j >> 2], 0u, 0x4440u | (uint32_t)(j & 3));
+        const float gj = g[j];
+        // second moment (optimizer.py:2117-2119)
+        const float g2 = __fadd_rn(__fmul_rn(gj, gj), S.eps_g);
+        const float v_old = tab[vcode];
+        // momentum (optimizer.py:528-531, 698)
+        const float m_old = __fmul_rn(byte_minus_128(mq[j >> 2], j & 3), mc);
+        float vj = lerp_sel<SMALL_W>(v_old, g2, S.v_w, S.v_wm1);
+        float mj = lerp_sel<SMALL_W>(m_old, gj, S.m_w, S.m_wm1);
+        const bool real = !TAIL || ((j < 4) ? (j < nva) : (j - 4 < nvb));
+        if (TAIL && !real) { vj = 0.0f; mj = 0.0f; }
+        v[j] = vj; m[j] = mj;
+        // update from the un-requantised v and m (optimizer.py:905, 909); feeds the parameter only
+        float u = __fmul_rn(mj, rcp_approx(__fadd_rn(sqrt_approx(vj), S.eps_d)));
+        if (TAIL && !real) u = 0.0f;                             // padding (0 * inf when eps is 0)
+        if (MODE == AF8_MODE_SUMSQ) {
+            acc = __fmaf_rn(u, u, acc);                          // padding contributes m = 0
+        } else {
+            float pj = __fmul_rn(p[j], S.decay);                 // optimizer.py:2039
+            const float us = (MODE == AF8_MODE_APPLY) ? __fmul_rn(u, S.fira) : u;   // optimizer.py:803
+            if (!(MODE == AF8_MODE_APPLY && S.zero_upd))         // non-finite norm: zero update (optimizer.py:798-800)
+                pj = __fmaf_rn(S.step_mul, us, pj);              // optimizer.py:874
+            p[j] = pj;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
 template <typename GradT, int MODE>
 __global__ void __launch_bounds__(FAST_THREADS, 3)
 fullrank_fast_kernel(const FullrankLaunch L)
 {
+    constexpr int GB = GradBytes<GradT>::value;
+    constexpr bool NEED_P = MODE != AF8_MODE_SUMSQ;
+    constexpr int P_OFF = 0;
+    constexpr int G_OFF = NEED_P ? FAST_VBLOCK * 4 : 0;
+    constexpr int MQ_OFF = G_OFF + FAST_VBLOCK * GB;
+    constexpr int VQ_OFF = MQ_OFF + FAST_VBLOCK;
+    constexpr int STAGE_BYTES = VQ_OFF + FAST_VBLOCK;
+
+    __shared__ __align__(128) unsigned char s_stage[2][STAGE_BYTES];
+    __shared__ __align__(8) uint64_t s_full[2];
     __shared__ af8_fullrank_tensor sT;
-    __shared__ float s_tab[256];
-    __shared__ float s_red[3][FAST_WARPS];
+    __shared__ float s_tab[2][256];
+    __shared__ uint32_t s_redmin[FAST_WARPS];
+    __shared__ uint32_t s_redmax[FAST_WARPS];
+    __shared__ float s_redsum[2][FAST_WARPS];
     __shared__ VRange s_vr;
+    __shared__ int s_abort;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    int cur_t = -1;
+    const int oa = warp * FAST_MBLOCK + lane * 4;   // first 4-element group of this thread
+    const int ob = oa + 128;                         // second group
 
-    for (int64_t blk = blockIdx.x; blk < L.total_blocks; blk += gridDim.x) {
-        // ---- locate the tensor (uniform over the CTA) ----
-        int t = cur_t;
-        if (t < 0) {
-            t = find_tensor(L.tensors, L.n_tensors, blk);
-        } else {
-            while (t + 1 < L.n_tensors && __ldg(&L.tensors[t + 1].first_block) <= blk) ++t;
-        }
-        __syncthreads();  // previous iteration is done with sT, s_tab, s_red, s_vr
-        if (t != cur_t) {
+    if (tid == 0) {
+        mbar_init(&s_full[0], 1);
+        mbar_init(&s_full[1], 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    int cur_t = -1;
+    int64_t cur_first = 0, cur_end = 0;      // block range of the current tensor
+    uint32_t phase = 0;                      // bit s: parity to wait for on stage s
+    bool staged = false;                     // this iteration's copies and table were issued last iteration
+    float nsc = 0.f, nml = 0.f, nms = 0.f;   // prefetched range of the next block (v_scale, v_min_log, m_scale)
+    float mscale_cur = 0.f;
+    int n = 0;
+
+    for (int64_t blk = blockIdx.x; blk < L.total_blocks; blk += gridDim.x, ++n) {
+        // ---- tensor change (rare, uniform over the CTA) ----
+        if (cur_t < 0 || blk >= cur_end) {
+            int t = cur_t;
+            if (t < 0) {
+                t = find_tensor(L.tensors, L.n_tensors, blk);
+            } else {
+                while (t + 1 < L.n_tensors && __ldg(&L.tensors[t + 1].first_block) <= blk) ++t;
+            }
+            __syncthreads();
             if (tid < (int)(sizeof(af8_fullrank_tensor) / 4))
                 reinterpret_cast<uint32_t *>(&sT)[tid] =
                     __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
+            __syncthreads();
             cur_t = t;
+            cur_first = sT.first_block;
+            cur_end = cur_first + (sT.numel + FAST_VBLOCK - 1) / FAST_VBLOCK;
+            staged = false;
         }
-        __syncthreads();
-
-        const int64_t b = blk - sT.first_block;       // V block index inside the tensor
+        const int64_t b = blk - cur_first;            // V block index inside the tensor
         const int64_t base = b * FAST_VBLOCK;         // first element of the block
         const int64_t rem = sT.numel - base;          // real elements from base on (> 0)
         const bool full = rem >= FAST_VBLOCK;
-        const int e0 = tid * FAST_EPT;
-        const bool m_exists = (int64_t)warp * FAST_MBLOCK < rem;  // this warp's M block is allocated
+        const int stage = n & 1;
+        const int64_t blk_next = blk + gridDim.x;
+        const int64_t b_next = blk_next - cur_first;
+        // the next block is prefetched when it is a full block of the same tensor
+        const bool next_staged = blk_next < cur_end && (sT.numel - b_next * FAST_VBLOCK) >= FAST_VBLOCK;
 
-        // ---- loads ----
-        float p[FAST_EPT], g[FAST_EPT];
+        // ---- issue the bulk copies (one thread) ----
+        if (tid == 0) {
+            const unsigned char *gp = static_cast<const unsigned char *>(sT.grad);
+            const unsigned char *pp = static_cast<const unsigned char *>(sT.param);
+            const unsigned char *vp = static_cast<const unsigned char *>(sT.v_q);
+            fence_proxy_async();
+            if (full && !staged) {
+                mbar_expect_tx(&s_full[stage], STAGE_BYTES);
+                if (NEED_P) bulk_g2s(s_stage[stage] + P_OFF, pp + base * 4, FAST_VBLOCK * 4, &s_full[stage]);
+                bulk_g2s(s_stage[stage] + G_OFF, gp + base * GB, FAST_VBLOCK * GB, &s_full[stage]);
+                bulk_g2s(s_stage[stage] + MQ_OFF, sT.m_q + base, FAST_VBLOCK, &s_full[stage]);
+                bulk_g2s(s_stage[stage] + VQ_OFF, vp + base, FAST_VBLOCK, &s_full[stage]);
+            }
+            if (next_staged) {
+                const int64_t nb = b_next * FAST_VBLOCK;
+                mbar_expect_tx(&s_full[stage ^ 1], STAGE_BYTES);
+                if (NEED_P) bulk_g2s(s_stage[stage ^ 1] + P_OFF, pp + nb * 4, FAST_VBLOCK * 4, &s_full[stage ^ 1]);
+                bulk_g2s(s_stage[stage ^ 1] + G_OFF, gp + nb * GB, FAST_VBLOCK * GB, &s_full[stage ^ 1]);
+                bulk_g2s(s_stage[stage ^ 1] + MQ_OFF, sT.m_q + nb, FAST_VBLOCK, &s_full[stage ^ 1]);
+                bulk_g2s(s_stage[stage ^ 1] + VQ_OFF, vp + nb, FAST_VBLOCK, &s_full[stage ^ 1]);
+            }
+        }
+        // ---- ranges of this block (if not prefetched) and of the next one ----
+        const bool m_exists = (int64_t)warp * FAST_MBLOCK < rem;   // this warp's M block is allocated
+        if (!staged) {
+            const float sc = __ldg(sT.v_scale + b);
+            const float ml = __ldg(sT.v_min_log + b);
+            mscale_cur = m_exists ? __ldg(sT.m_scale + b * (FAST_VBLOCK / FAST_MBLOCK) + warp) : 0.0f;
+            s_tab[stage][tid] = al_decode((uint32_t)tid, sc, ml, 254.0f);   // optimizer.py:341-349
+            __syncthreads();
+        }
+        if (next_staged) {
+            nsc = __ldg(sT.v_scale + b_next);
+            nml = __ldg(sT.v_min_log + b_next);
+            nms = __ldg(sT.m_scale + b_next * (FAST_VBLOCK / FAST_MBLOCK) + warp);
+        }
+        const float mc = __fdiv_rn(mscale_cur, 128.0f);            // fl(m_scale / 128) (optimizer.py:531)
+
+        // ---- this thread's raw inputs ----
+        float p[8], g[8];
         uint32_t mq[2], vq[2];
-        float *pptr = static_cast<float *>(sT.param) + base + e0;
-        {
-            const uint2 vv = __ldcs(reinterpret_cast<const uint2 *>(static_cast<const uint8_t *>(sT.v_q) + base + e0));
-            vq[0] = vv.x; vq[1] = vv.y;
-        }
-        if (m_exists) {
-            const uint2 mm = __ldcs(reinterpret_cast<const uint2 *>(sT.m_q + base + e0));
-            mq[0] = mm.x; mq[1] = mm.y;
-        } else {
-            mq[0] = mq[1] = 0x80808080u;
-        }
+        int nva = 4, nvb = 4;
+        float *pa = static_cast<float *>(sT.param) + base + oa;
+        float *pb = static_cast<float *>(sT.param) + base + ob;
         if (full) {
-            if (MODE != AF8_MODE_SUMSQ) {
-                const float4 a = *reinterpret_cast<const float4 *>(pptr);
-                const float4 c = *reinterpret_cast<const float4 *>(pptr + 4);
+            if (!mbar_wait_bounded(&s_full[stage], (phase >> stage) & 1u)) {
+                s_abort = 1;
+                atomicExch(&g_device_error, DEVERR_COPY_TIMEOUT);
+            }
+            phase ^= 1u << stage;
+            const unsigned char *st = s_stage[stage];
+            if (NEED_P) {
+                const float4 a = *reinterpret_cast<const float4 *>(st + P_OFF + oa * 4);
+                const float4 c = *reinterpret_cast<const float4 *>(st + P_OFF + ob * 4);
                 p[0] = a.x; p[1] = a.y; p[2] = a.z; p[3] = a.w;
                 p[4] = c.x; p[5] = c.y; p[6] = c.z; p[7] = c.w;
             }
-            GradLoad<GradT>::load8(sT.grad, base + e0, g);
+            if (GB == 4) {
+                const float4 a = *reinterpret_cast<const float4 *>(st + G_OFF + oa * 4);
+                const float4 c = *reinterpret_cast<const float4 *>(st + G_OFF + ob * 4);
+                g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w;
+                g[4] = c.x; g[5] = c.y; g[6] = c.z; g[7] = c.w;
+            } else {
+                const uint2 a = *reinterpret_cast<const uint2 *>(st + G_OFF + oa * 2);
+                const uint2 c = *reinterpret_cast<const uint2 *>(st + G_OFF + ob * 2);
+                g[0] = __uint_as_float(a.x << 16); g[1] = __uint_as_float(a.x & 0xffff0000u);
+                g[2] = __uint_as_float(a.y << 16); g[3] = __uint_as_float(a.y & 0xffff0000u);
+                g[4] = __uint_as_float(c.x << 16); g[5] = __uint_as_float(c.x & 0xffff0000u);
+                g[6] = __uint_as_float(c.y << 16); g[7] = __uint_as_float(c.y & 0xffff0000u);
+            }
+            mq[0] = *reinterpret_cast<const uint32_t *>(st + MQ_OFF + oa);
+            mq[1] = *reinterpret_cast<const uint32_t *>(st + MQ_OFF + ob);
+            vq[0] = *reinterpret_cast<const uint32_t *>(st + VQ_OFF + oa);
+            vq[1] = *reinterpret_cast<const uint32_t *>(st + VQ_OFF + ob);
         } else {
+            // tail block: guarded plain loads; the V state is padded to the block, the M
+            // state only to its own 256-element blocks
+            nva = (int)max((int64_t)0, min((int64_t)4, rem - oa));
+            nvb = (int)max((int64_t)0, min((int64_t)4, rem - ob));
+            const uint8_t *vp = static_cast<const uint8_t *>(sT.v_q) + base;
+            vq[0] = *reinterpret_cast<const uint32_t *>(vp + oa);
+            vq[1] = *reinterpret_cast<const uint32_t *>(vp + ob);
+            mq[0] = m_exists ? *reinterpret_cast<const uint32_t *>(sT.m_q + base + oa) : 0x80808080u;
+            mq[1] = m_exists ? *reinterpret_cast<const uint32_t *>(sT.m_q + base + ob) : 0x80808080u;
 #pragma unroll
-            for (int j = 0; j < FAST_EPT; ++j) {
-                const bool ok = e0 + j < rem;
-                p[j] = (ok && MODE != AF8_MODE_SUMSQ) ? pptr[j] : 0.0f;
-                g[j] = ok ? GradLoad<GradT>::load1(sT.grad, base + e0 + j) : 0.0f;
+            for (int j = 0; j < 8; ++j) {
+                const int e = (j < 4) ? oa + j : ob + j - 4;
+                const bool ok = (j < 4) ? (j < nva) : (j - 4 < nvb);
+                p[j] = (ok && NEED_P) ? static_cast<const float *>(sT.param)[base + e] : 0.0f;
+                g[j] = ok ? GradLoad<GradT>::load1(sT.grad, base + e) : 0.0f;
             }
         }
-
-        // ---- AL8 decode table of this block: 255 powers of two (optimizer.py:341-349) ----
-        {
-            const float sc = __ldg(sT.v_scale + b);
-            const float ml = __ldg(sT.v_min_log + b);
-            s_tab[tid] = al_decode((uint32_t)tid, sc, ml, 254.0f);
+        if (L.negate_grad) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] = -g[j];
         }
-        // fl(m_scale / 128) (optimizer.py:531)
-        const float mc = m_exists ? __fdiv_rn(__ldg(sT.m_scale + b * (FAST_VBLOCK / FAST_MBLOCK) + warp), 128.0f) : 0.0f;
-        __syncthreads();
 
-        const float decay = sT.decay, v_w = sT.v_w, m_w = sT.m_w;
-        const float eps_g = sT.eps_gradsq, eps_d = sT.eps_denom;
-        float step_mul, fira = 1.0f;
+        // ---- scalars of the step ----
+        StepScalars S;
+        S.decay = sT.decay; S.v_w = sT.v_w; S.m_w = sT.m_w;
+        S.v_wm1 = __fsub_rn(S.v_w, 1.0f); S.m_wm1 = __fsub_rn(S.m_w, 1.0f);
+        S.eps_g = sT.eps_gradsq; S.eps_d = sT.eps_denom;
+        S.fira = 1.0f; S.zero_upd = false;
         if (MODE == AF8_MODE_APPLY) {
             const af8_dyn_scalars ds = L.dyn[cur_t];
-            step_mul = ds.step;
-            fira = (ds.zero != 0.0f) ? 0.0f : ds.fira;     // a non-finite norm zeroes the update (optimizer.py:798-800)
-            if (ds.zero != 0.0f) step_mul = 0.0f;
+            S.step_mul = ds.step; S.fira = ds.fira; S.zero_upd = ds.zero != 0.0f;
         } else {
-            step_mul = -sT.alpha;
+            S.step_mul = -sT.alpha;
         }
 
         // ---- EMAs and update: everything that reaches a state is exact ----
-        float v[FAST_EPT], m[FAST_EPT];
+        float v[8], m[8];
         float acc = 0.0f;
-        const bool small_w = fabsf(v_w) < 0.5f && fabsf(m_w) < 0.5f;   // ATen's lerp has two forms
-        const float v_wm1 = __fsub_rn(v_w, 1.0f), m_wm1 = __fsub_rn(m_w, 1.0f);
+        const bool small_w = fabsf(S.v_w) < 0.5f && fabsf(S.m_w) < 0.5f;   // ATen's lerp has two forms
+        if (small_w) {
+            if (full) ema_update<MODE, true, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
+            else ema_update<MODE, true, true>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
+        } else {
 #pragma unroll
-        for (int j = 0; j < FAST_EPT; ++j) {
-            const bool real = full || (e0 + j < rem);
-            const uint32_t vcode = (vq[j >> 2] >> (8 * (j & 3))) & 0xffu;
-            const float gj = L.negate_grad ? -g[j] : g[j];
-            // second moment (optimizer.py:2117-2119)
-            const float g2 = __fadd_rn(__fmul_rn(gj, gj), eps_g);
-            const float v_old = s_tab[vcode];
-            // momentum (optimizer.py:528-531, 698)
-            const float m_old = __fmul_rn(byte_minus_128(mq[j >> 2], j & 3), mc);
-            float vj, mj;
-            if (small_w) {
-                vj = lerp_sel<true>(v_old, g2, v_w, v_wm1);
-                mj = lerp_sel<true>(m_old, gj, m_w, m_wm1);
-            } else {
-                vj = lerp_t(v_old, g2, v_w);
-                mj = lerp_t(m_old, gj, m_w);
-            }
-            if (!real) { vj = 0.0f; mj = 0.0f; }
-            v[j] = vj; m[j] = mj;
-            // update from the un-requantised v and m (optimizer.py:905, 909); feeds the parameter only
-            const float u = __fmul_rn(mj, rcp_approx(__fadd_rn(sqrt_approx(vj), eps_d)));
-            if (MODE == AF8_MODE_SUMSQ) {
-                acc = __fmaf_rn(u, u, acc);                       // padding contributes m = 0
-            } else {
-                const float us = (MODE == AF8_MODE_APPLY) ? __fmul_rn(u, fira) : u;   // optimizer.py:803
-                const float p1 = __fmul_rn(p[j], decay);          // optimizer.py:2039
-                p[j] = (MODE == AF8_MODE_APPLY && step_mul == 0.0f) ? p1 : __fmaf_rn(step_mul, us, p1);   // optimizer.py:874
+            for (int j = 0; j < 8; ++j) {   // general lerp (weights >= 0.5): rare, kept simple
+                const bool real = (j < 4) ? (j < nva) : (j - 4 < nvb);
+                const uint32_t vcode = (vq[j >> 2] >> (8 * (j & 3))) & 0xffu;
+                const float g2 = __fadd_rn(__fmul_rn(g[j], g[j]), S.eps_g);
+                float vj = lerp_t(s_tab[stage][vcode], g2, S.v_w);
+                float mj = lerp_t(__fmul_rn(byte_minus_128(mq[j >> 2], j & 3), mc), g[j], S.m_w);
+                if (!real) { vj = 0.0f; mj = 0.0f; }
+                v[j] = vj; m[j] = mj;
+                float u = __fmul_rn(mj, rcp_approx(__fadd_rn(sqrt_approx(vj), S.eps_d)));
+                if (!real) u = 0.0f;
+                if (MODE == AF8_MODE_SUMSQ) {
+                    acc = __fmaf_rn(u, u, acc);
+                } else {
+                    float pj = __fmul_rn(p[j], S.decay);
+                    const float us = (MODE == AF8_MODE_APPLY) ? __fmul_rn(u, S.fira) : u;
+                    if (!(MODE == AF8_MODE_APPLY && S.zero_upd)) pj = __fmaf_rn(S.step_mul, us, pj);
+                    p[j] = pj;
+                }
             }
         }
 
         if (MODE == AF8_MODE_SUMSQ) {
             acc = warp_sum(acc);
-            if (lane == 0) s_red[2][warp] = acc;
+            if (lane == 0) s_redsum[stage][warp] = acc;
+            if (next_staged) s_tab[stage ^ 1][tid] = al_decode((uint32_t)tid, nsc, nml, 254.0f);
             __syncthreads();
+            if (s_abort) {   // a copy never completed: give the one still in flight a bounded chance, then stop
+                if (next_staged) mbar_wait_bounded(&s_full[stage ^ 1], (phase >> (stage ^ 1)) & 1u);
+                break;
+            }
             if (tid == 0) {
                 float s = 0.0f;
 #pragma unroll
-                for (int w = 0; w < FAST_WARPS; ++w) s = __fadd_rn(s, s_red[2][w]);
+                for (int w = 0; w < FAST_WARPS; ++w) s = __fadd_rn(s, s_redsum[stage][w]);
                 L.block_sumsq[blk] = s;
             }
+            staged = next_staged;
+            mscale_cur = nms;
             continue;
+        }
+
+        // ---- block extrema of v as integers: for v >= 0 the bit patterns order like the
+        //      values, and bits-1 sends the excluded zeros to the top (optimizer.py:312-313) ----
+        {
+            uint32_t umin = 0xffffffffu, umax = 0u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t bits = __float_as_uint(v[j]);
+                umin = min(umin, bits - 1u);
+                umax = max(umax, bits);
+            }
+            umin = __reduce_min_sync(0xffffffffu, umin);
+            umax = __reduce_max_sync(0xffffffffu, umax);
+            if (lane == 0) { s_redmin[warp] = umin; s_redmax[warp] = umax; }
+        }
+        __syncthreads();                     // ---- D ----
+        if (s_abort) {       // a copy never completed: give the one still in flight a bounded chance, then stop
+            if (next_staged) mbar_wait_bounded(&s_full[stage ^ 1], (phase >> (stage ^ 1)) & 1u);
+            break;
+        }
+
+        // ---- warp 0: exact log2 of the two extreme values only (optimizer.py:308-318) ----
+        if (warp == 0) {
+            uint32_t umin = lane < FAST_WARPS ? s_redmin[lane] : 0xffffffffu;
+            uint32_t umax = lane < FAST_WARPS ? s_redmax[lane] : 0u;
+            umin = __reduce_min_sync(0xffffffffu, umin);
+            umax = __reduce_max_sync(0xffffffffu, umax);
+            if (lane == 0) {
+                const float mn = (umin == 0xffffffffu) ? INFINITY : al_log2(__uint_as_float(umin + 1u));
+                const float mx = al_log2(__uint_as_float(umax));
+                VRange r;
+                al_range(mn, mx, L.v_floor, r.min_log, r.scale);
+                r.k = __fdiv_rn(254.0f, r.scale);
+                r.c = -__fmul_rn(r.min_log, r.k);
+                // error bound of the estimate in code units: the hardware log2, the roundings
+                // of the estimate and those of the exact sequence it must agree with
+                const float lmax = fmaxf(fmaxf(fabsf(r.min_log), fabsf(mx)), 1.0f);
+                const float err = __fmaf_rn(__fmul_rn(lmax, LG2_REL_BOUND), r.k, 2.0e-4f);
+                r.thr = 0.5f - err;
+                s_vr = r;
+                sT.v_scale[b] = r.scale;
+                sT.v_min_log[b] = r.min_log;
+            }
         }
 
         // ---- parameter store ----
         if (full) {
-            *reinterpret_cast<float4 *>(pptr) = make_float4(p[0], p[1], p[2], p[3]);
-            *reinterpret_cast<float4 *>(pptr + 4) = make_float4(p[4], p[5], p[6], p[7]);
+            *reinterpret_cast<float4 *>(pa) = make_float4(p[0], p[1], p[2], p[3]);
+            *reinterpret_cast<float4 *>(pb) = make_float4(p[4], p[5], p[6], p[7]);
         } else {
 #pragma unroll
-            for (int j = 0; j < FAST_EPT; ++j)
-                if (e0 + j < rem) pptr[j] = p[j];
-        }
-
-        // ---- block extrema of v (log2 is monotone, so they locate min_log and max_log) ----
-        {
-            float vmin = INFINITY, vmax = 0.0f;
-#pragma unroll
-            for (int j = 0; j < FAST_EPT; ++j) {
-                vmin = fminf(vmin, v[j] != 0.0f ? v[j] : INFINITY);
-                vmax = fmaxf(vmax, v[j]);
+            for (int j = 0; j < 4; ++j) {
+                if (j < nva) pa[j] = p[j];
+                if (j < nvb) pb[j] = p[j + 4];
             }
-            vmin = warp_min(vmin);
-            vmax = warp_max(vmax);
-            if (lane == 0) { s_red[0][warp] = vmin; s_red[1][warp] = vmax; }
         }
 
         // ---- momentum requantisation: one warp = one M block (optimizer.py:510, 518) ----
         {
-            float am = 0.0f;
+            uint32_t ab = 0u;
 #pragma unroll
-            for (int j = 0; j < FAST_EPT; ++j) am = fmaxf(am, fabsf(m[j]));
-            am = fmaxf(warp_max(am), 1e-12f);
+            for (int j = 0; j < 8; ++j) ab = max(ab, __float_as_uint(fabsf(m[j])));
+            const float am = fmaxf(__uint_as_float(__reduce_max_sync(0xffffffffu, ab)), 1e-12f);
             const float ra = __frcp_rn(am);
-            uint32_t raw[FAST_EPT];
+            uint32_t raw[8];
 #pragma unroll
-            for (int j = 0; j < FAST_EPT; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 // IEEE m / am from the correctly rounded reciprocal and one residual step
                 float q = __fmul_rn(m[j], ra);
                 const float r = __fmaf_rn(-q, am, m[j]);
@@ -336,69 +573,51 @@ fullrank_fast_kernel(const FullrankLaunch L)
             const uint32_t o0 = __byte_perm(__byte_perm(raw[0], raw[1], 0x0040), __byte_perm(raw[2], raw[3], 0x0040), 0x5410) ^ 0x80808080u;
             const uint32_t o1 = __byte_perm(__byte_perm(raw[4], raw[5], 0x0040), __byte_perm(raw[6], raw[7], 0x0040), 0x5410) ^ 0x80808080u;
             if (m_exists) {
-                __stcs(reinterpret_cast<uint2 *>(sT.m_q + base + e0), make_uint2(o0, o1));
+                *reinterpret_cast<uint32_t *>(sT.m_q + base + oa) = o0;
+                *reinterpret_cast<uint32_t *>(sT.m_q + base + ob) = o1;
                 if (lane == 0) sT.m_scale[b * (FAST_VBLOCK / FAST_MBLOCK) + warp] = am;
             }
         }
 
-        // ---- block range: exact log2 of the two extreme values only (optimizer.py:308-318) ----
-        __syncthreads();
-        if (warp == 0) {
-            float vmin = lane < FAST_WARPS ? s_red[0][lane] : INFINITY;
-            float vmax = lane < FAST_WARPS ? s_red[1][lane] : 0.0f;
-            vmin = warp_min(vmin);
-            vmax = warp_max(vmax);
-            if (lane == 0) {
-                const float mn = (vmin == INFINITY) ? INFINITY : al_log2(vmin);
-                const float mx = al_log2(vmax);
-                VRange r;
-                al_range(mn, mx, L.v_floor, r.min_log, r.scale);
-                r.k = __fdiv_rn(254.0f, r.scale);
-                r.c = -__fmul_rn(r.min_log, r.k);
-                // error bound of the estimate in code units: the hardware log2 (taken as
-                // 2^-21 relative and absolute, twice its specified bound), the roundings of
-                // the estimate itself and of the exact sequence it must agree with
-                const float lmax = fmaxf(fmaxf(fabsf(r.min_log), fabsf(mx)), 1.0f);
-                const float err = __fmaf_rn(__fmul_rn(lmax, LG2_REL_BOUND), r.k, 2.0e-4f);
-                r.thr = 0.5f - err;
-                s_vr = r;
-                sT.v_scale[b] = r.scale;
-                sT.v_min_log[b] = r.min_log;
-            }
-        }
-        __syncthreads();
+        // ---- decode table of the next block, while warp 0 finishes the range ----
+        if (next_staged) s_tab[stage ^ 1][tid] = al_decode((uint32_t)tid, nsc, nml, 254.0f);
+        __syncthreads();                     // ---- E ----
 
         // ---- second-moment codes ----
         {
             const VRange r = s_vr;
-            int kk[FAST_EPT];
+            int kk[8];
             uint32_t ambiguous = 0;
 #pragma unroll
-            for (int j = 0; j < FAST_EPT; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 const float le = lg2_approx(fmaxf(v[j], AF8_TINY));
                 const float te = __fmaf_rn(le, r.k, r.c);
                 const float s = __fadd_rn(te, AF8_MAGIC_F + 1.0f);          // rint(te) + 1 in the low bits
                 const float rf = __fsub_rn(s, AF8_MAGIC_F + 1.0f);
-                if (!(fabsf(__fsub_rn(te, rf)) <= r.thr) && (v[j] != 0.0f)) ambiguous |= 1u << j;
+                if (!(fabsf(__fsub_rn(te, rf)) <= r.thr)) ambiguous |= 1u << j;
                 kk[j] = __float_as_int(s);
             }
             if (__any_sync(0xffffffffu, ambiguous != 0)) {
                 // rare: redo the codes in doubt with the exact sequence
 #pragma unroll
-                for (int j = 0; j < FAST_EPT; ++j)
+                for (int j = 0; j < 8; ++j)
                     if (ambiguous & (1u << j))
                         kk[j] = AF8_MAGIC_I + (int)al_encode(v[j], al_log2(v[j]), r.min_log, r.scale, 254.0f, 255);
             }
-            uint32_t raw[FAST_EPT];
+            uint32_t raw[8];
 #pragma unroll
-            for (int j = 0; j < FAST_EPT; ++j) {
-                int k = max(AF8_MAGIC_I + 1, min(kk[j], AF8_MAGIC_I + 255));
+            for (int j = 0; j < 8; ++j) {
+                const int k = max(AF8_MAGIC_I + 1, min(kk[j], AF8_MAGIC_I + 255));
                 raw[j] = (v[j] == 0.0f) ? (uint32_t)AF8_MAGIC_I : (uint32_t)k;   // code 0 is reserved for exact zero
             }
             const uint32_t o0 = __byte_perm(__byte_perm(raw[0], raw[1], 0x0040), __byte_perm(raw[2], raw[3], 0x0040), 0x5410);
             const uint32_t o1 = __byte_perm(__byte_perm(raw[4], raw[5], 0x0040), __byte_perm(raw[6], raw[7], 0x0040), 0x5410);
-            __stcs(reinterpret_cast<uint2 *>(static_cast<uint8_t *>(sT.v_q) + base + e0), make_uint2(o0, o1));
+            uint8_t *vp = static_cast<uint8_t *>(sT.v_q) + base;
+            *reinterpret_cast<uint32_t *>(vp + oa) = o0;
+            *reinterpret_cast<uint32_t *>(vp + ob) = o1;
         }
+        staged = next_staged;
+        mscale_cur = nms;
     }
 }
 

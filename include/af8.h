@@ -69,6 +69,13 @@ enum {
 AF8_API int af8_version(void);
 AF8_API const char *af8_last_error(void);
 
+/* Device-side health: waits inside the kernels (on asynchronous copies) are
+ * bounded; a wait that ran out sets a sticky flag on the device instead of
+ * hanging.  This call synchronises `stream` and returns the flag of the current
+ * device in *status_out: 0 = healthy, 1 = an asynchronous copy never completed
+ * (results of that launch are invalid).  No counterpart in the reference. */
+AF8_API int af8_device_status(int32_t *status_out, void *stream);
+
 /* Upload the signed dynamic-map codebooks (256 and 16 sorted entries) used by
  * the d8 / d4 momentum formats to the current device.
  * Replaces set_qmap (kernels.cu:32-37, optimizer.py:109-133). */

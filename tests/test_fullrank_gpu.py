@@ -203,3 +203,8 @@ def test_large_tensor_codes_are_exact(kind, oracle):
         for key in RANGE_KEYS:
             assert int(parity.ulp_diff(state_np(st, key), ost[key]).max()) == 0, f"{kind} step {t} {key}"
         parity.assert_params(param.detach().cpu().numpy(), op, f"{kind} step {t} param", tol=1e-6)
+
+
+def test_device_status_is_clean_after_the_runs_above():
+    from adafactor8bit import _native
+    assert _native.device_status(torch.cuda.current_stream().cuda_stream) == 0
