@@ -33,8 +33,20 @@ def sources():
     return out
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, extra=(), out=None):
+    """extra: additional nvcc arguments (e.g. -D macros for tuning builds);
+    out: alternative output path (the default library is left untouched)."""
     os.makedirs(LIB_DIR, exist_ok=True)
+    if out is not None:
+        nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+        cmd = [nvcc] + NVCC_FLAGS + list(extra) + (["-Xptxas", "-v"] if verbose else []) + [
+            "-I", INCLUDE, "-o", out, os.path.join(CSRC, "af8_lib.cu")]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed building " + out)
+        return out
     if not force and os.path.exists(LIB):
         newest = max(os.path.getmtime(s) for s in sources())
         if os.path.getmtime(LIB) >= newest:

@@ -23,7 +23,8 @@
 // range of block i.  Tail blocks (fewer than 2048 real elements) and the first
 // block a CTA touches in a tensor take a plain-load path.  Every wait on an
 // mbarrier is bounded; a wait that runs out raises the device error flag that
-// af8_device_status() reports and the CTA stops without further stores.
+// af8_device_status() reports, the threads skip the stores of that block and
+// the CTA stops at its next block-wide barrier.
 //
 // Instruction budget.  At 14-16 bytes per parameter the HBM roofline leaves
 // roughly 60 issue slots per parameter, so exact IEEE arithmetic is spent only
@@ -108,23 +109,24 @@ template <> struct GradLoad<bf16_tag> {
     }
 };
 
-// hardware approximations, used only where the result does not reach a stored state
+// hardware approximations (flush-to-zero forms: one MUFU instruction each, no
+// subnormal fix-up code), used only where the result does not reach a stored state
 __device__ __forceinline__ float sqrt_approx(float x)
 {
     float y;
-    asm("sqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 __device__ __forceinline__ float rcp_approx(float x)
 {
     float y;
-    asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 __device__ __forceinline__ float lg2_approx(float x)
 {
     float y;
-    asm("lg2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
@@ -150,6 +152,11 @@ struct __align__(16) VRange {
     float thr;       // an estimate is trusted when |t - rint(t)| <= thr
     float pad[3];
 };
+
+// Blackwell packed binary32 arithmetic: one instruction works on a pair of floats held in
+// a 64-bit register; each component rounds exactly like the scalar *_rn operation.
+__device__ __forceinline__ float2 bc2(float x) { return make_float2(x, x); }
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(bc2(-1.0f), b, a); }   // a - b, one rounding
 
 template <bool SMALL_W>
 __device__ __forceinline__ float lerp_sel(float s, float e, float w, float wm1)
@@ -223,46 +230,67 @@ struct StepScalars {
     bool zero_upd;
 };
 
-template <int MODE, bool SMALL_W, bool TAIL>
+template <int MODE, bool HAS_EPSG, bool TAIL>
 __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], const uint32_t (&mq)[2],
                                            const uint32_t (&vq)[2], const float *tab, float mc,
                                            const StepScalars &S, int nva, int nvb, float (&v)[8], float (&m)[8],
                                            float &acc)
 {
+    const float2 w_v = bc2(S.v_w), w_m = bc2(S.m_w), mc2 = bc2(mc), eps_d2 = bc2(S.eps_d);
+    const float2 decay2 = bc2(S.decay), step2 = bc2(S.step_mul), fira2 = bc2(S.fira);
+    float2 acc2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t vcode = __byte_perm(vq[j >> 2], 0u, 0x4440u | (uint32_t)(j & 3));
-        const float gj = g[j];
+    for (int j = 0; j < 8; j += 2) {
+        const uint32_t c0 = __byte_perm(vq[j >> 2], 0u, 0x4440u | (uint32_t)(j & 3));
+        const uint32_t c1 = __byte_perm(vq[j >> 2], 0u, 0x4440u | (uint32_t)((j + 1) & 3));
+        const float2 gj = make_float2(g[j], g[j + 1]);
         // second moment (optimizer.py:2117-2119)
-        const float g2 = __fadd_rn(__fmul_rn(gj, gj), S.eps_g);
-        const float v_old = tab[vcode];
-        // momentum (optimizer.py:528-531, 698)
-        const float m_old = __fmul_rn(byte_minus_128(mq[j >> 2], j & 3), mc);
-        float vj = lerp_sel<SMALL_W>(v_old, g2, S.v_w, S.v_wm1);
-        float mj = lerp_sel<SMALL_W>(m_old, gj, S.m_w, S.m_wm1);
-        const bool real = !TAIL || ((j < 4) ? (j < nva) : (j - 4 < nvb));
-        if (TAIL && !real) { vj = 0.0f; mj = 0.0f; }
-        v[j] = vj; m[j] = mj;
+        float2 g2 = __fmul2_rn(gj, gj);
+        if (HAS_EPSG) g2 = __fadd2_rn(g2, bc2(S.eps_g));          // 0 in Adam mode (optimizer.py:1967)
+        const float2 v_old = make_float2(tab[c0], tab[c1]);
+        float2 vj = __ffma2_rn(w_v, sub2(g2, v_old), v_old);
+        // momentum (optimizer.py:528-531, 698): (byte - 128) * fl(scale / 128), then lerp
+        const float2 mb = make_float2(__uint_as_float(__byte_perm(mq[j >> 2], 0x4b000000u, 0x7540u | (uint32_t)(j & 3))),
+                                      __uint_as_float(__byte_perm(mq[j >> 2], 0x4b000000u, 0x7540u | (uint32_t)((j + 1) & 3))));
+        const float2 m_old = __fmul2_rn(__fadd2_rn(mb, bc2(-8388736.0f)), mc2);
+        float2 mj = __ffma2_rn(w_m, sub2(gj, m_old), m_old);
+        bool real0 = true, real1 = true;
+        if (TAIL) {
+            real0 = (j < 4) ? (j < nva) : (j - 4 < nvb);
+            real1 = (j < 4) ? (j + 1 < nva) : (j - 3 < nvb);
+            if (!real0) { vj.x = 0.0f; mj.x = 0.0f; }
+            if (!real1) { vj.y = 0.0f; mj.y = 0.0f; }
+        }
+        v[j] = vj.x; v[j + 1] = vj.y; m[j] = mj.x; m[j + 1] = mj.y;
         // update from the un-requantised v and m (optimizer.py:905, 909); feeds the parameter only
-        float u = __fmul_rn(mj, rcp_approx(__fadd_rn(sqrt_approx(vj), S.eps_d)));
-        if (TAIL && !real) u = 0.0f;                             // padding (0 * inf when eps is 0)
+        const float2 den = __fadd2_rn(make_float2(sqrt_approx(vj.x), sqrt_approx(vj.y)), eps_d2);
+        float2 u = __fmul2_rn(mj, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
+        if (TAIL) {                                               // padding (0 * inf when eps is 0)
+            if (!real0) u.x = 0.0f;
+            if (!real1) u.y = 0.0f;
+        }
         if (MODE == AF8_MODE_SUMSQ) {
-            acc = __fmaf_rn(u, u, acc);                          // padding contributes m = 0
+            acc2 = __ffma2_rn(u, u, acc2);                        // padding contributes m = 0
         } else {
-            float pj = __fmul_rn(p[j], S.decay);                 // optimizer.py:2039
-            const float us = (MODE == AF8_MODE_APPLY) ? __fmul_rn(u, S.fira) : u;   // optimizer.py:803
-            if (!(MODE == AF8_MODE_APPLY && S.zero_upd))         // non-finite norm: zero update (optimizer.py:798-800)
-                pj = __fmaf_rn(S.step_mul, us, pj);              // optimizer.py:874
-            p[j] = pj;
+            float2 pj = __fmul2_rn(make_float2(p[j], p[j + 1]), decay2);     // optimizer.py:2039
+            if (MODE == AF8_MODE_APPLY) u = __fmul2_rn(u, fira2);             // optimizer.py:803
+            if (!(MODE == AF8_MODE_APPLY && S.zero_upd))          // non-finite norm: zero update (optimizer.py:798-800)
+                pj = __ffma2_rn(step2, u, pj);                    // optimizer.py:874
+            p[j] = pj.x; p[j + 1] = pj.y;
         }
     }
+    if (MODE == AF8_MODE_SUMSQ) acc = __fadd_rn(acc2.x, acc2.y);
 }
 
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
+#ifndef AF8_FAST_MIN_CTAS
+#define AF8_FAST_MIN_CTAS 3
+#endif
+
 template <typename GradT, int MODE>
-__global__ void __launch_bounds__(FAST_THREADS, 3)
+__global__ void __launch_bounds__(FAST_THREADS, AF8_FAST_MIN_CTAS)
 fullrank_fast_kernel(const FullrankLaunch L)
 {
     constexpr int GB = GradBytes<GradT>::value;
@@ -370,17 +398,21 @@ fullrank_fast_kernel(const FullrankLaunch L)
             nml = __ldg(sT.v_min_log + b_next);
             nms = __ldg(sT.m_scale + b_next * (FAST_VBLOCK / FAST_MBLOCK) + warp);
         }
-        const float mc = __fdiv_rn(mscale_cur, 128.0f);            // fl(m_scale / 128) (optimizer.py:531)
+        // fl(m_scale / 128) (optimizer.py:531): a power-of-two divisor, so the product is the
+        // same number (m_scale >= 1e-12 keeps it far from the subnormal range)
+        const float mc = __fmul_rn(mscale_cur, 0.0078125f);
 
         // ---- this thread's raw inputs ----
         float p[8], g[8];
         uint32_t mq[2], vq[2];
         int nva = 4, nvb = 4;
+        bool bad = false;
         float *pa = static_cast<float *>(sT.param) + base + oa;
         float *pb = static_cast<float *>(sT.param) + base + ob;
         if (full) {
             if (!mbar_wait_bounded(&s_full[stage], (phase >> stage) & 1u)) {
-                s_abort = 1;
+                bad = true;      // this thread stores nothing for the block
+                s_abort = 1;     // and the CTA stops at the next block-wide barrier
                 atomicExch(&g_device_error, DEVERR_COPY_TIMEOUT);
             }
             phase ^= 1u << stage;
@@ -449,8 +481,12 @@ fullrank_fast_kernel(const FullrankLaunch L)
         float acc = 0.0f;
         const bool small_w = fabsf(S.v_w) < 0.5f && fabsf(S.m_w) < 0.5f;   // ATen's lerp has two forms
         if (small_w) {
-            if (full) ema_update<MODE, true, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
-            else ema_update<MODE, true, true>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
+            if (full) {
+                if (S.eps_g == 0.0f) ema_update<MODE, false, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
+                else ema_update<MODE, true, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
+            } else {
+                ema_update<MODE, true, true>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
+            }
         } else {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {   // general lerp (weights >= 0.5): rare, kept simple
@@ -508,11 +544,9 @@ fullrank_fast_kernel(const FullrankLaunch L)
             umax = __reduce_max_sync(0xffffffffu, umax);
             if (lane == 0) { s_redmin[warp] = umin; s_redmax[warp] = umax; }
         }
-        __syncthreads();                     // ---- D ----
-        if (s_abort) {       // a copy never completed: give the one still in flight a bounded chance, then stop
-            if (next_staged) mbar_wait_bounded(&s_full[stage ^ 1], (phase >> (stage ^ 1)) & 1u);
-            break;
-        }
+        // ---- D: only warp 0 consumes the extrema; the other warps signal and move on ----
+        if (warp == 0) asm volatile("bar.sync 1, %0;" ::"n"(FAST_THREADS) : "memory");
+        else asm volatile("bar.arrive 1, %0;" ::"n"(FAST_THREADS) : "memory");
 
         // ---- warp 0: exact log2 of the two extreme values only (optimizer.py:308-318) ----
         if (warp == 0) {
@@ -520,9 +554,13 @@ fullrank_fast_kernel(const FullrankLaunch L)
             uint32_t umax = lane < FAST_WARPS ? s_redmax[lane] : 0u;
             umin = __reduce_min_sync(0xffffffffu, umin);
             umax = __reduce_max_sync(0xffffffffu, umax);
+            // lane 0 takes the log of the minimum, lane 1 of the maximum
+            float lg = (lane == 0) ? ((umin == 0xffffffffu) ? INFINITY : al_log2(__uint_as_float(umin + 1u)))
+                                   : ((lane == 1) ? al_log2(__uint_as_float(umax)) : 0.0f);
+            const float mx_l = __shfl_sync(0xffffffffu, lg, 1);
             if (lane == 0) {
-                const float mn = (umin == 0xffffffffu) ? INFINITY : al_log2(__uint_as_float(umin + 1u));
-                const float mx = al_log2(__uint_as_float(umax));
+                const float mn = lg;
+                const float mx = mx_l;
                 VRange r;
                 al_range(mn, mx, L.v_floor, r.min_log, r.scale);
                 r.k = __fdiv_rn(254.0f, r.scale);
@@ -532,6 +570,9 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 const float lmax = fmaxf(fmaxf(fabsf(r.min_log), fabsf(mx)), 1.0f);
                 const float err = __fmaf_rn(__fmul_rn(lmax, LG2_REL_BOUND), r.k, 2.0e-4f);
                 r.thr = 0.5f - err;
+                // absurd range (NaN / inf) or a floor below the normal range, where the estimate's
+                // clamp of subnormal values would not match: exact path for all
+                if (!(r.k >= 1.0f) || L.v_floor < -126.0f) r.thr = -1.0f;
                 s_vr = r;
                 sT.v_scale[b] = r.scale;
                 sT.v_min_log[b] = r.min_log;
@@ -539,7 +580,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
         }
 
         // ---- parameter store ----
-        if (full) {
+        if (bad) {
+        } else if (full) {
             *reinterpret_cast<float4 *>(pa) = make_float4(p[0], p[1], p[2], p[3]);
             *reinterpret_cast<float4 *>(pb) = make_float4(p[4], p[5], p[6], p[7]);
         } else {
@@ -552,27 +594,29 @@ fullrank_fast_kernel(const FullrankLaunch L)
 
         // ---- momentum requantisation: one warp = one M block (optimizer.py:510, 518) ----
         {
-            uint32_t ab = 0u;
+            float amx = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ab = max(ab, __float_as_uint(fabsf(m[j])));
-            const float am = fmaxf(__uint_as_float(__reduce_max_sync(0xffffffffu, ab)), 1e-12f);
-            const float ra = __frcp_rn(am);
+            for (int j = 0; j < 8; ++j) amx = fmaxf(amx, fabsf(m[j]));
+            // non-negative floats order like their bit patterns: one REDUX instead of a shuffle tree
+            const float am = fmaxf(__uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amx))), 1e-12f);
+            const float2 ra2 = bc2(__frcp_rn(am)), nam2 = bc2(-am);
             uint32_t raw[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 8; j += 2) {
                 // IEEE m / am from the correctly rounded reciprocal and one residual step
-                float q = __fmul_rn(m[j], ra);
-                const float r = __fmaf_rn(-q, am, m[j]);
-                q = __fmaf_rn(r, ra, q);
-                // round(q * 128) (the product is exact), clamp to [-128, 127]
-                int k = __float_as_int(__fmaf_rn(q, 128.0f, AF8_MAGIC_F));
-                k = max(AF8_MAGIC_I - 128, min(k, AF8_MAGIC_I + 127));
-                raw[j] = (uint32_t)k;
+                const float2 mj = make_float2(m[j], m[j + 1]);
+                float2 q = __fmul2_rn(mj, ra2);
+                const float2 r = __ffma2_rn(q, nam2, mj);
+                q = __ffma2_rn(r, ra2, q);
+                // round(q * 128) (the product is exact); |q| <= 1, so only +128 needs the clamp to 127
+                const float2 kf = __ffma2_rn(q, bc2(128.0f), bc2(AF8_MAGIC_F));
+                raw[j] = (uint32_t)min(__float_as_int(kf.x), AF8_MAGIC_I + 127);
+                raw[j + 1] = (uint32_t)min(__float_as_int(kf.y), AF8_MAGIC_I + 127);
             }
             // low bytes hold k mod 256; k + 128 is that byte with its top bit flipped
             const uint32_t o0 = __byte_perm(__byte_perm(raw[0], raw[1], 0x0040), __byte_perm(raw[2], raw[3], 0x0040), 0x5410) ^ 0x80808080u;
             const uint32_t o1 = __byte_perm(__byte_perm(raw[4], raw[5], 0x0040), __byte_perm(raw[6], raw[7], 0x0040), 0x5410) ^ 0x80808080u;
-            if (m_exists) {
+            if (m_exists && !bad) {
                 *reinterpret_cast<uint32_t *>(sT.m_q + base + oa) = o0;
                 *reinterpret_cast<uint32_t *>(sT.m_q + base + ob) = o1;
                 if (lane == 0) sT.m_scale[b * (FAST_VBLOCK / FAST_MBLOCK) + warp] = am;
@@ -582,38 +626,50 @@ fullrank_fast_kernel(const FullrankLaunch L)
         // ---- decode table of the next block, while warp 0 finishes the range ----
         if (next_staged) s_tab[stage ^ 1][tid] = al_decode((uint32_t)tid, nsc, nml, 254.0f);
         __syncthreads();                     // ---- E ----
+        if (s_abort) {       // a copy never completed: give the one still in flight a bounded chance, then stop
+            if (next_staged) mbar_wait_bounded(&s_full[stage ^ 1], (phase >> (stage ^ 1)) & 1u);
+            break;
+        }
 
         // ---- second-moment codes ----
         {
             const VRange r = s_vr;
             int kk[8];
-            uint32_t ambiguous = 0;
+            float dd[8];
+            float dmax = 0.0f;
+            const float2 k2 = bc2(r.k), c2 = bc2(r.c), mg2 = bc2(AF8_MAGIC_F + 1.0f), nmg2 = bc2(-(AF8_MAGIC_F + 1.0f));
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float le = lg2_approx(fmaxf(v[j], AF8_TINY));
-                const float te = __fmaf_rn(le, r.k, r.c);
-                const float s = __fadd_rn(te, AF8_MAGIC_F + 1.0f);          // rint(te) + 1 in the low bits
-                const float rf = __fsub_rn(s, AF8_MAGIC_F + 1.0f);
-                if (!(fabsf(__fsub_rn(te, rf)) <= r.thr)) ambiguous |= 1u << j;
-                kk[j] = __float_as_int(s);
+            for (int j = 0; j < 8; j += 2) {
+                // zeros and subnormal values estimate as 2^-126: at or below every stored min_log
+                const float2 le = make_float2(lg2_approx(fmaxf(v[j], 1.17549435e-38f)),
+                                              lg2_approx(fmaxf(v[j + 1], 1.17549435e-38f)));
+                const float2 te = __ffma2_rn(le, k2, c2);
+                const float2 sm = __fadd2_rn(te, mg2);             // rint(te) + 1 in the low bits
+                const float2 rf = __fadd2_rn(sm, nmg2);
+                const float2 d = sub2(te, rf);                     // distance to the chosen integer
+                dd[j] = d.x; dd[j + 1] = d.y;
+                dmax = fmaxf(dmax, fmaxf(fabsf(d.x), fabsf(d.y)));
+                kk[j] = __float_as_int(sm.x); kk[j + 1] = __float_as_int(sm.y);
             }
-            if (__any_sync(0xffffffffu, ambiguous != 0)) {
+            if (__any_sync(0xffffffffu, !(dmax <= r.thr))) {
                 // rare: redo the codes in doubt with the exact sequence
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
-                    if (ambiguous & (1u << j))
+                    if (!(fabsf(dd[j]) <= r.thr))
                         kk[j] = AF8_MAGIC_I + (int)al_encode(v[j], al_log2(v[j]), r.min_log, r.scale, 254.0f, 255);
             }
             uint32_t raw[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const int k = max(AF8_MAGIC_I + 1, min(kk[j], AF8_MAGIC_I + 255));
-                raw[j] = (v[j] == 0.0f) ? (uint32_t)AF8_MAGIC_I : (uint32_t)k;   // code 0 is reserved for exact zero
+                // t <= 254 for every element of the block, so only the lower clamp can bind
+                // (values below the min_log floor); code 0 is reserved for exact zero
+                const int k = max(kk[j], AF8_MAGIC_I + 1);
+                raw[j] = (v[j] == 0.0f) ? (uint32_t)AF8_MAGIC_I : (uint32_t)k;
             }
             const uint32_t o0 = __byte_perm(__byte_perm(raw[0], raw[1], 0x0040), __byte_perm(raw[2], raw[3], 0x0040), 0x5410);
             const uint32_t o1 = __byte_perm(__byte_perm(raw[4], raw[5], 0x0040), __byte_perm(raw[6], raw[7], 0x0040), 0x5410);
             uint8_t *vp = static_cast<uint8_t *>(sT.v_q) + base;
-            *reinterpret_cast<uint32_t *>(vp + oa) = o0;
+            *reinterpret_cast<uint32_t *>(vp + oa) = o0;       // (not reached after a failed wait: the CTA left at E)
             *reinterpret_cast<uint32_t *>(vp + ob) = o1;
         }
         staged = next_staged;

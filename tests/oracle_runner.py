@@ -43,3 +43,22 @@ class OracleRun:
 def golden_entries(gold, t, i):
     pre = f"t{t}_p{i}_"
     return {k[len(pre):]: gold[k] for k in gold.files if k.startswith(pre)}
+
+
+FACTORED_CASES = ["adafactor_factored", "adafactor_factored_m", "came_al16"]
+STATE_ARRAY_KEYS = ("variance_q", "variance_scale", "variance_min_log", "variance", "m_q", "m_scale", "m",
+                    "row_var_q", "row_var_scale", "row_var_min_log", "row_var", "col_var_q", "col_var_scale",
+                    "col_var_min_log", "col_var", "conf_row_q", "conf_row_scale", "conf_row_min_log", "conf_row",
+                    "conf_col_q", "conf_col_scale", "conf_col_min_log", "conf_col")
+
+
+def state_from_golden(entries, hp, shape, step):
+    """Oracle state of one parameter rebuilt from a fixture snapshot (after `step` steps)."""
+    st = o.init_state(shape, hp)
+    st["step"] = step
+    for k in STATE_ARRAY_KEYS:
+        if k in entries and k in st:
+            st[k] = np.ascontiguousarray(entries[k]).astype(st[k].dtype).reshape(st[k].shape).copy()
+    if "fira_prev_norm" in entries:
+        st["fira_prev_norm"] = np.float32(entries["fira_prev_norm"].reshape(-1)[0])
+    return st
