@@ -83,6 +83,38 @@ __device__ __forceinline__ float lerp_t(float s, float e, float w)
 // (error below 1 ulp of binary64) and rounded once.
 __device__ __forceinline__ float log2_cr(float x) { return __double2float_rn(log2((double)x)); }
 
+// The same function with a short dependency chain, for the few calls that sit on a
+// critical path (block extrema, codes in doubt): table-driven argument reduction in
+// binary64.  x = 2^e * m with m in [0.75, 1.5); with c_j the nearest of 97 centres
+// 0.75 + j/128 and inv_j = double(1/c_j):  log2(x) = e - log2(inv_j) + log2(1 + r),
+// r = m*inv_j - 1 (one fma, |r| < 2^-7.5), log2(1 + r) by its Taylor series through
+// r^7.  The table stores -log2(inv_j) for the stored inv_j, so the identity is exact;
+// the centre c_32 = 1 has inv = 1 and a zero table entry, which keeps the result
+// relatively accurate around x = 1.  Error about 2^-52 relative before the final
+// rounding, like the library routine.  x must be positive and finite.
+__constant__ double2 c_log2_tab[97] = {
+#include "log2_table.inc"
+};
+
+__device__ __forceinline__ float log2_cr_fast(float x)
+{
+    const double xd = (double)x;
+    const int hi = __double2hiint(xd);
+    const int e = (hi - 0x3fe80000) >> 20;                 // 0x3fe80000: high word of 0.75
+    const double m = __hiloint2double(hi - (e << 20), __double2loint(xd));
+    const int j = __double2int_rn((m - 0.75) * 128.0);
+    const double2 t = c_log2_tab[j];
+    const double r = fma(m, t.x, -1.0);
+    double p = 0x1.a61762a7adedap-3;        //  1/(7 ln 2)
+    p = fma(p, r, -0x1.ec709dc3a03fep-3);   // -1/(6 ln 2)
+    p = fma(p, r, 0x1.2776c50ef9bfep-2);    //  1/(5 ln 2)
+    p = fma(p, r, -0x1.71547652b82fep-2);   // -1/(4 ln 2)
+    p = fma(p, r, 0x1.ec709dc3a03fep-2);    //  1/(3 ln 2)
+    p = fma(p, r, -0x1.71547652b82fep-1);   // -1/(2 ln 2)
+    p = fma(p, r, 0x1.71547652b82fep+0);    //  1/ln 2
+    return __double2float_rn(fma(p, r, (double)e + t.y));
+}
+
 // Correctly rounded 2^x.
 __device__ __forceinline__ float exp2_cr(float x) { return __double2float_rn(exp2((double)x)); }
 
@@ -92,6 +124,7 @@ __device__ __forceinline__ float rsqrt_t(float x) { return __frcp_rn(__fsqrt_rn(
 // log2 of a second-moment value as _log_quantize_nonneg sees it
 // (optimizer.py:308-310): values below 1e-38 (zero included) are lifted to 1e-38.
 __device__ __forceinline__ float al_log2(float v) { return (v > AF8_TINY) ? log2_cr(v) : AF8_LOG2_TINY; }
+__device__ __forceinline__ float al_log2_fast(float v) { return (v > AF8_TINY) ? log2_cr_fast(v) : AF8_LOG2_TINY; }
 
 // AL dequantisation of one code (optimizer.py:341-349).  qm1 = levels - 2.
 __device__ __forceinline__ float al_decode(uint32_t code, float scale, float min_log, float qm1)

@@ -286,7 +286,7 @@ __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], c
 // the kernel
 // ---------------------------------------------------------------------------
 #ifndef AF8_FAST_MIN_CTAS
-#define AF8_FAST_MIN_CTAS 3
+#define AF8_FAST_MIN_CTAS 4
 #endif
 
 template <typename GradT, int MODE>
@@ -555,8 +555,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
             umin = __reduce_min_sync(0xffffffffu, umin);
             umax = __reduce_max_sync(0xffffffffu, umax);
             // lane 0 takes the log of the minimum, lane 1 of the maximum
-            float lg = (lane == 0) ? ((umin == 0xffffffffu) ? INFINITY : al_log2(__uint_as_float(umin + 1u)))
-                                   : ((lane == 1) ? al_log2(__uint_as_float(umax)) : 0.0f);
+            float lg = (lane == 0) ? ((umin == 0xffffffffu) ? INFINITY : al_log2_fast(__uint_as_float(umin + 1u)))
+                                   : ((lane == 1) ? al_log2_fast(__uint_as_float(umax)) : 0.0f);
             const float mx_l = __shfl_sync(0xffffffffu, lg, 1);
             if (lane == 0) {
                 const float mn = lg;
@@ -656,7 +656,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     if (!(fabsf(dd[j]) <= r.thr))
-                        kk[j] = AF8_MAGIC_I + (int)al_encode(v[j], al_log2(v[j]), r.min_log, r.scale, 254.0f, 255);
+                        kk[j] = AF8_MAGIC_I + (int)al_encode(v[j], al_log2_fast(v[j]), r.min_log, r.scale, 254.0f, 255);
             }
             uint32_t raw[8];
 #pragma unroll
