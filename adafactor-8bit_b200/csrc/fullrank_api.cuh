@@ -94,13 +94,17 @@ inline int persistent_grid(K kernel, int threads, size_t smem, int64_t total_blo
 template <typename GradT, int MODE>
 inline int launch_fast(const FullrankLaunch &L, cudaStream_t st)
 {
-    int grid = 0;
-    // the two-stage ring needs up to 43 KB per CTA: ask for the large shared-memory carve-out
-    AF8_CUDA_TRY(cudaFuncSetAttribute(fullrank_fast_kernel<GradT, MODE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    using Ring = FastRing<GradT, MODE>;
+    auto kernel = fullrank_fast_kernel<GradT, MODE>;
+    // the ring lives in dynamic shared memory (up to 48-60 KB per CTA): opt in and ask for
+    // the large shared-memory carve-out
+    AF8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring::SMEM_BYTES));
+    AF8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                       (int)cudaSharedmemCarveoutMaxShared));
-    int rc = persistent_grid(fullrank_fast_kernel<GradT, MODE>, FAST_THREADS, 0, L.total_blocks, &grid);
+    int grid = 0;
+    int rc = persistent_grid(kernel, FAST_THREADS, Ring::SMEM_BYTES, L.total_blocks, &grid);
     if (rc) return rc;
-    fullrank_fast_kernel<GradT, MODE><<<grid, FAST_THREADS, 0, st>>>(L);
+    kernel<<<grid, FAST_THREADS, Ring::SMEM_BYTES, st>>>(L);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }

@@ -288,21 +288,45 @@ __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], c
 #ifndef AF8_FAST_MIN_CTAS
 #define AF8_FAST_MIN_CTAS 4
 #endif
+#ifndef AF8_FAST_STAGES_UPDATE
+#define AF8_FAST_STAGES_UPDATE 2      /* ring depth of the NOCLIP / APPLY passes, bf16 gradients */
+#endif
+#ifndef AF8_FAST_STAGES_UPDATE_F32
+#define AF8_FAST_STAGES_UPDATE_F32 2  /* the same with fp32 gradients (20 KB per slot) */
+#endif
+#ifndef AF8_FAST_STAGES_STAT
+#define AF8_FAST_STAGES_STAT 2        /* ring depth of the SUMSQ pass (8-12 KB per slot) */
+#endif
+
+// Measured on B200 (TinyLlama set): depths 2 / 3 / 4 / 6 change the pass times by a few
+// per cent in the wrong direction (fewer resident CTAs), so the default stays at 2.
+// Ring geometry of one kernel variant: byte offsets inside a slot and the slot count.
+template <typename GradT, int MODE> struct FastRing {
+    static constexpr int GB = GradBytes<GradT>::value;
+    static constexpr bool NEED_P = MODE != AF8_MODE_SUMSQ;
+    static constexpr int P_OFF = 0;
+    static constexpr int G_OFF = NEED_P ? FAST_VBLOCK * 4 : 0;
+    static constexpr int MQ_OFF = G_OFF + FAST_VBLOCK * GB;
+    static constexpr int VQ_OFF = MQ_OFF + FAST_VBLOCK;
+    static constexpr int STAGE_BYTES = VQ_OFF + FAST_VBLOCK;
+    static constexpr int NST = NEED_P ? (GB == 2 ? AF8_FAST_STAGES_UPDATE : AF8_FAST_STAGES_UPDATE_F32) : AF8_FAST_STAGES_STAT;
+    static constexpr int SMEM_BYTES = NST * STAGE_BYTES;
+    static_assert(NST >= 2 && NST <= 8, "ring depth");
+};
 
 template <typename GradT, int MODE>
 __global__ void __launch_bounds__(FAST_THREADS, AF8_FAST_MIN_CTAS)
 fullrank_fast_kernel(const FullrankLaunch L)
 {
-    constexpr int GB = GradBytes<GradT>::value;
-    constexpr bool NEED_P = MODE != AF8_MODE_SUMSQ;
-    constexpr int P_OFF = 0;
-    constexpr int G_OFF = NEED_P ? FAST_VBLOCK * 4 : 0;
-    constexpr int MQ_OFF = G_OFF + FAST_VBLOCK * GB;
-    constexpr int VQ_OFF = MQ_OFF + FAST_VBLOCK;
-    constexpr int STAGE_BYTES = VQ_OFF + FAST_VBLOCK;
+    using Ring = FastRing<GradT, MODE>;
+    constexpr int GB = Ring::GB;
+    constexpr bool NEED_P = Ring::NEED_P;
+    constexpr int P_OFF = Ring::P_OFF, G_OFF = Ring::G_OFF, MQ_OFF = Ring::MQ_OFF, VQ_OFF = Ring::VQ_OFF;
+    constexpr int STAGE_BYTES = Ring::STAGE_BYTES;
+    constexpr int NST = Ring::NST;
 
-    __shared__ __align__(128) unsigned char s_stage[2][STAGE_BYTES];
-    __shared__ __align__(8) uint64_t s_full[2];
+    extern __shared__ __align__(128) unsigned char s_ring[];     // NST slots of STAGE_BYTES
+    __shared__ __align__(8) uint64_t s_full[NST];
     __shared__ af8_fullrank_tensor sT;
     __shared__ float s_tab[2][256];
     __shared__ uint32_t s_redmin[FAST_WARPS];
@@ -318,8 +342,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
     const int ob = oa + 128;                         // second group
 
     if (tid == 0) {
-        mbar_init(&s_full[0], 1);
-        mbar_init(&s_full[1], 1);
+        for (int k = 0; k < NST; ++k) mbar_init(&s_full[k], 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -327,8 +350,9 @@ fullrank_fast_kernel(const FullrankLaunch L)
 
     int cur_t = -1;
     int64_t cur_first = 0, cur_end = 0;      // block range of the current tensor
-    uint32_t phase = 0;                      // bit s: parity to wait for on stage s
-    bool staged = false;                     // this iteration's copies and table were issued last iteration
+    uint32_t phase = 0;                      // bit k: parity to wait for on ring slot k
+    int ahead = 0;                           // consecutive blocks from the current one whose copies are in flight
+    bool staged = false;                     // this block's decode table and ranges were prepared last iteration
     float nsc = 0.f, nml = 0.f, nms = 0.f;   // prefetched range of the next block (v_scale, v_min_log, m_scale)
     float mscale_cur = 0.f;
     int n = 0;
@@ -350,40 +374,44 @@ fullrank_fast_kernel(const FullrankLaunch L)
             cur_t = t;
             cur_first = sT.first_block;
             cur_end = cur_first + (sT.numel + FAST_VBLOCK - 1) / FAST_VBLOCK;
-            staged = false;
+            staged = false;                          // (ahead is 0 here: copies never cross a tensor)
         }
         const int64_t b = blk - cur_first;            // V block index inside the tensor
         const int64_t base = b * FAST_VBLOCK;         // first element of the block
         const int64_t rem = sT.numel - base;          // real elements from base on (> 0)
         const bool full = rem >= FAST_VBLOCK;
-        const int stage = n & 1;
+        const int stage = n & 1;                      // decode-table / partial-sum buffer of this block
+        const int slot = n % NST;                     // ring slot of this block
         const int64_t blk_next = blk + gridDim.x;
         const int64_t b_next = blk_next - cur_first;
-        // the next block is prefetched when it is a full block of the same tensor
-        const bool next_staged = blk_next < cur_end && (sT.numel - b_next * FAST_VBLOCK) >= FAST_VBLOCK;
+        // blocks blk, blk+G, ... that are full blocks of this tensor get their copies issued ahead
+        int want = 0;
+#pragma unroll
+        for (int k = 0; k < NST; ++k) {
+            const int64_t bk = b + (int64_t)k * gridDim.x;
+            if (want == k && blk + (int64_t)k * gridDim.x < cur_end && sT.numel - bk * FAST_VBLOCK >= FAST_VBLOCK) want = k + 1;
+        }
+        const bool next_staged = want >= 2;           // the next block gets its table and ranges prepared here
 
         // ---- issue the bulk copies (one thread) ----
-        if (tid == 0) {
+        if (tid == 0 && ahead < want) {
             const unsigned char *gp = static_cast<const unsigned char *>(sT.grad);
             const unsigned char *pp = static_cast<const unsigned char *>(sT.param);
             const unsigned char *vp = static_cast<const unsigned char *>(sT.v_q);
             fence_proxy_async();
-            if (full && !staged) {
-                mbar_expect_tx(&s_full[stage], STAGE_BYTES);
-                if (NEED_P) bulk_g2s(s_stage[stage] + P_OFF, pp + base * 4, FAST_VBLOCK * 4, &s_full[stage]);
-                bulk_g2s(s_stage[stage] + G_OFF, gp + base * GB, FAST_VBLOCK * GB, &s_full[stage]);
-                bulk_g2s(s_stage[stage] + MQ_OFF, sT.m_q + base, FAST_VBLOCK, &s_full[stage]);
-                bulk_g2s(s_stage[stage] + VQ_OFF, vp + base, FAST_VBLOCK, &s_full[stage]);
-            }
-            if (next_staged) {
-                const int64_t nb = b_next * FAST_VBLOCK;
-                mbar_expect_tx(&s_full[stage ^ 1], STAGE_BYTES);
-                if (NEED_P) bulk_g2s(s_stage[stage ^ 1] + P_OFF, pp + nb * 4, FAST_VBLOCK * 4, &s_full[stage ^ 1]);
-                bulk_g2s(s_stage[stage ^ 1] + G_OFF, gp + nb * GB, FAST_VBLOCK * GB, &s_full[stage ^ 1]);
-                bulk_g2s(s_stage[stage ^ 1] + MQ_OFF, sT.m_q + nb, FAST_VBLOCK, &s_full[stage ^ 1]);
-                bulk_g2s(s_stage[stage ^ 1] + VQ_OFF, vp + nb, FAST_VBLOCK, &s_full[stage ^ 1]);
+            for (int k = ahead; k < want; ++k) {
+                const int64_t nb = (b + (int64_t)k * gridDim.x) * FAST_VBLOCK;
+                const int sl = (n + k) % NST;
+                unsigned char *dst = s_ring + sl * STAGE_BYTES;
+                mbar_expect_tx(&s_full[sl], STAGE_BYTES);
+                if (NEED_P) bulk_g2s(dst + P_OFF, pp + nb * 4, FAST_VBLOCK * 4, &s_full[sl]);
+                bulk_g2s(dst + G_OFF, gp + nb * GB, FAST_VBLOCK * GB, &s_full[sl]);
+                bulk_g2s(dst + MQ_OFF, sT.m_q + nb, FAST_VBLOCK, &s_full[sl]);
+                bulk_g2s(dst + VQ_OFF, vp + nb, FAST_VBLOCK, &s_full[sl]);
             }
         }
+        const int in_flight = want;                   // copies outstanding now, this block included
+        ahead = want > 0 ? want - 1 : 0;              // ... as seen from the next block
         // ---- ranges of this block (if not prefetched) and of the next one ----
         const bool m_exists = (int64_t)warp * FAST_MBLOCK < rem;   // this warp's M block is allocated
         if (!staged) {
@@ -410,13 +438,13 @@ fullrank_fast_kernel(const FullrankLaunch L)
         float *pa = static_cast<float *>(sT.param) + base + oa;
         float *pb = static_cast<float *>(sT.param) + base + ob;
         if (full) {
-            if (!mbar_wait_bounded(&s_full[stage], (phase >> stage) & 1u)) {
+            if (!mbar_wait_bounded(&s_full[slot], (phase >> slot) & 1u)) {
                 bad = true;      // this thread stores nothing for the block
                 s_abort = 1;     // and the CTA stops at the next block-wide barrier
                 atomicExch(&g_device_error, DEVERR_COPY_TIMEOUT);
             }
-            phase ^= 1u << stage;
-            const unsigned char *st = s_stage[stage];
+            phase ^= 1u << slot;
+            const unsigned char *st = s_ring + slot * STAGE_BYTES;
             if (NEED_P) {
                 const float4 a = *reinterpret_cast<const float4 *>(st + P_OFF + oa * 4);
                 const float4 c = *reinterpret_cast<const float4 *>(st + P_OFF + ob * 4);
@@ -515,8 +543,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
             if (lane == 0) s_redsum[stage][warp] = acc;
             if (next_staged) s_tab[stage ^ 1][tid] = al_decode((uint32_t)tid, nsc, nml, 254.0f);
             __syncthreads();
-            if (s_abort) {   // a copy never completed: give the one still in flight a bounded chance, then stop
-                if (next_staged) mbar_wait_bounded(&s_full[stage ^ 1], (phase >> (stage ^ 1)) & 1u);
+            if (s_abort) {   // a copy never completed: give the ones still in flight a bounded chance, then stop
+                for (int k = 1; k < in_flight; ++k) mbar_wait_bounded(&s_full[(n + k) % NST], (phase >> ((n + k) % NST)) & 1u);
                 break;
             }
             if (tid == 0) {
@@ -626,8 +654,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
         // ---- decode table of the next block, while warp 0 finishes the range ----
         if (next_staged) s_tab[stage ^ 1][tid] = al_decode((uint32_t)tid, nsc, nml, 254.0f);
         __syncthreads();                     // ---- E ----
-        if (s_abort) {       // a copy never completed: give the one still in flight a bounded chance, then stop
-            if (next_staged) mbar_wait_bounded(&s_full[stage ^ 1], (phase >> (stage ^ 1)) & 1u);
+        if (s_abort) {       // a copy never completed: give the ones still in flight a bounded chance, then stop
+            for (int k = 1; k < in_flight; ++k) mbar_wait_bounded(&s_full[(n + k) % NST], (phase >> ((n + k) % NST)) & 1u);
             break;
         }
 
