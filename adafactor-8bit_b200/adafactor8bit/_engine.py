@@ -210,6 +210,7 @@ class FullrankPlan:
         nt["first_block"] = self.first_block
         nt["n_blocks"] = self.nblocks
         nt["pre_div_mode"] = pre_div_mode
+        nt["partials_f64"] = 0
         nt["alpha"] = table["alpha"]
         if self._alpha_on_device:
             nt["alpha_dev"] = (self.d_table.data_ptr() + np.arange(self.n, dtype=np.uint64) * np.uint64(N.FULLRANK_TENSOR.itemsize)
@@ -311,5 +312,230 @@ class FullrankPlan:
 
     def norms(self):
         """Update norms measured by the last two-pass step (one per tensor)."""
+        dyn = self.d_dyn.cpu().numpy().view(N.DYN_SCALARS)
+        return dyn["norm"].copy()
+
+
+def _small_state_fields(row, st, prefix, fmt, block):
+    """Fill one af8_small_state of a table row from the optimizer state dict."""
+    row["fmt"] = N.V_FMT[fmt]
+    row["block"] = int(block)
+    if fmt == "fp32":
+        row["f32"] = st[prefix].data_ptr()
+    else:
+        row["q"] = st[prefix + "_q"].data_ptr()
+        row["scale"] = st[prefix + "_scale"].data_ptr()
+        row["min_log"] = st[prefix + "_min_log"].data_ptr()
+
+
+class FactoredPlan:
+    """One multi-tensor launch group of the factored path (2-D tensors with row /
+    column second moments; optionally momentum; optionally CAME confidence)."""
+
+    def __init__(self, device, grad_dtype, m_fmt, m_block, came, negate, params, states, v_fmts, c_fmts):
+        self.device = torch.device(device)
+        self.params, self.states = list(params), list(states)
+        self.n = n = len(self.params)
+        self.came = bool(came)
+        self.cfg = N.FactoredCfg()
+        self.cfg.param_dtype = N.F32
+        self.cfg.grad_dtype = _GRAD_DT[grad_dtype]
+        self.cfg.m_fmt = N.M_FMT[m_fmt]
+        self.cfg.m_block = int(m_block) if m_block else 0
+        self.cfg.came = int(self.came)
+        self.cfg.negate_grad = int(bool(negate))
+        self.cfg.v_floor = -126.0
+        if m_fmt in ("d8", "d4"):
+            ensure_qmap(self.device)
+        for p in self.params:
+            if p.dtype != torch.float32 or not p.is_contiguous() or p.dim() != 2:
+                raise RuntimeError("the factored kernels update contiguous 2-D fp32 parameters")
+        self.rows = np.array([p.shape[0] for p in self.params], dtype=np.int64)
+        self.cols = np.array([p.shape[1] for p in self.params], dtype=np.int64)
+        self.numel = self.rows * self.cols
+        self.total_numel = int(self.numel.sum())
+        lib = N.lib()
+        m_quant = m_fmt not in (None, "fp32")
+        self.chunk = lib.af8_factored_chunk(self.cfg.m_block if m_quant else 0)
+        tr, tc = lib.af8_factored_tile_rows(), lib.af8_factored_tile_cols()
+        self.nchunks = (self.numel + self.chunk - 1) // self.chunk
+        ntiles = ((self.rows + tr - 1) // tr) * ((self.cols + tc - 1) // tc)
+        self.first_chunk = np.concatenate([[0], np.cumsum(self.nchunks)[:-1]]).astype(np.int64)
+        self.first_tile = np.concatenate([[0], np.cumsum(ntiles)[:-1]]).astype(np.int64)
+        self.total_chunks = int(self.nchunks.sum())
+        rc = int((self.rows + self.cols).sum())
+        self.d_sums = torch.empty(rc, dtype=torch.float64, device=self.device)
+        self.d_inv = torch.empty(rc * (2 if self.came else 1), dtype=torch.float32, device=self.device)
+        self.d_table = torch.empty(n * N.FACTORED_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+        self.d_dyn = torch.zeros(n * N.DYN_SCALARS.itemsize, dtype=torch.uint8, device=self.device)
+        self.d_norm = torch.empty(n * N.NORM_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+        self.d_sumsq = torch.empty(self.total_chunks, dtype=torch.float64, device=self.device)
+        self.h_table = _PinnedRing(n * N.FACTORED_TENSOR.itemsize)
+        self.h_norm = _PinnedRing(n * N.NORM_TENSOR.itemsize)
+        self.h_scale = self.d_scale = self.d_chunks = None
+        self.v_fmts, self.c_fmts = list(v_fmts), list(c_fmts)
+        self._static = None
+        self._alpha_on_device = False
+
+    def _static_fields(self):
+        t = np.zeros(self.n, dtype=N.FACTORED_TENSOR)
+        off = 0
+        sums, inv = self.d_sums.data_ptr(), self.d_inv.data_ptr()
+        half = int((self.rows + self.cols).sum())
+        for i, (p, st) in enumerate(zip(self.params, self.states)):
+            R, C = int(self.rows[i]), int(self.cols[i])
+            t["param"][i] = p.data_ptr()
+            t["m_q"][i] = _ptr(st.get("m_q"))
+            t["m_scale"][i] = _ptr(st.get("m_scale"))
+            t["m_f32"][i] = _ptr(st.get("m"))
+            t["row_sum"][i] = sums + 8 * off
+            t["col_sum"][i] = sums + 8 * (off + R)
+            t["inv_row"][i] = inv + 4 * off
+            t["inv_col"][i] = inv + 4 * (off + R)
+            if self.came:
+                t["inv_row_conf"][i] = inv + 4 * (half + off)
+                t["inv_col_conf"][i] = inv + 4 * (half + off + R)
+            block = st.get("block_size", 2048)
+            _small_state_fields(t["row_var"][i:i + 1], st, "row_var", self.v_fmts[i], block)
+            _small_state_fields(t["col_var"][i:i + 1], st, "col_var", self.v_fmts[i], block)
+            if self.came:
+                _small_state_fields(t["conf_row"][i:i + 1], st, "conf_row", self.c_fmts[i], block)
+                _small_state_fields(t["conf_col"][i:i + 1], st, "conf_col", self.c_fmts[i], block)
+            off += R + C
+        t["rows"], t["cols"] = self.rows, self.cols
+        t["first_chunk"], t["first_tile"] = self.first_chunk, self.first_tile
+        return t
+
+    def kernel_name(self, what):
+        return "factored_" + what
+
+    def _log(self, name, fn, stream):
+        log = LAUNCH_LOG
+        if log is None:
+            fn()
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        fn()
+        e1.record(stream)
+        log.append((self.kernel_name(name), self.total_numel, e0, e1))
+
+    def _stats(self, mode, host_buf, stream):
+        self.cfg.mode = mode
+        lib = N.lib()
+        self._log("stats_gradsq" if mode == N.FSTAT_GRADSQ else "stats_residual", lambda: N.check(
+            lib.af8_factored_stats(ctypes.byref(self.cfg), self.d_table.data_ptr(), host_buf.data_ptr(), self.n,
+                                   self.d_dyn.data_ptr(), stream.cuda_stream), "af8_factored_stats"), stream)
+
+    def _small(self, conf, stream):
+        lib = N.lib()
+        self._log("small_conf" if conf else "small_var", lambda: N.check(
+            lib.af8_factored_small(ctypes.byref(self.cfg), self.d_table.data_ptr(), self.n, int(conf),
+                                   stream.cuda_stream), "af8_factored_small"), stream)
+
+    def _update(self, mode, use_dyn, stream):
+        self.cfg.mode = mode
+        lib = N.lib()
+        name = {N.FUPD_SUMSQ_U: "sumsq_u", N.FUPD_SUMSQ: "sumsq", N.FUPD_APPLY: "apply"}[mode]
+        self._log(name, lambda: N.check(
+            lib.af8_factored_update(ctypes.byref(self.cfg), self.d_table.data_ptr(), self.n, self.total_chunks,
+                                    self.d_dyn.data_ptr() if use_dyn else None, self.d_sumsq.data_ptr(),
+                                    stream.cuda_stream), "af8_factored_update"), stream)
+
+    def _finalize(self, table, pre_div_mode, d, fira, fira_margin, stream):
+        buf = self.h_norm.next()
+        nt = buf.numpy()[: self.n * N.NORM_TENSOR.itemsize].view(N.NORM_TENSOR)
+        nt["first_block"] = self.first_chunk
+        nt["n_blocks"] = self.nchunks
+        nt["pre_div_mode"] = pre_div_mode
+        nt["partials_f64"] = 1
+        nt["alpha"] = table["alpha"]
+        if self._alpha_on_device:
+            nt["alpha_dev"] = (self.d_table.data_ptr() + np.arange(self.n, dtype=np.uint64) * np.uint64(N.FACTORED_TENSOR.itemsize)
+                               + np.uint64(N.FACTORED_TENSOR.fields["alpha"][1]))
+        else:
+            nt["alpha_dev"] = 0
+        sqrt_n = np.sqrt(self.numel.astype(np.float64))
+        nt["sqrt_n"] = sqrt_n.astype(np.float32)
+        nt["d"] = np.float32(d)
+        nt["clip_div"] = (sqrt_n * d).astype(np.float32) if (d > 0 and pre_div_mode == 0) else np.float32(0.0)
+        nt["fira_margin1"] = np.float32(1.0 + fira_margin)
+        if fira and pre_div_mode != 1:
+            for i, st in enumerate(self.states):
+                prev = st.get("fira_prev_norm")
+                if prev is None:
+                    prev = torch.zeros((), dtype=torch.float32, device=self.device)
+                    st["fira_prev_norm"] = prev
+                    nt["fira_has_prev"][i] = 0
+                else:
+                    nt["fira_has_prev"][i] = 1
+                nt["fira_prev"][i] = prev.data_ptr()
+        else:
+            nt["fira_prev"] = 0
+            nt["fira_has_prev"] = 0
+        self.d_norm.copy_(buf[: self.d_norm.numel()], non_blocking=True)
+        self.h_norm.mark(stream)
+        N.check(N.lib().af8_norm_finalize(self.d_norm.data_ptr(), self.n, self.d_sumsq.data_ptr(),
+                                          self.d_dyn.data_ptr(), stream.cuda_stream), "af8_norm_finalize")
+
+    def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None):
+        """One optimizer step for every tensor of the plan (optimizer.py:2202-2552)."""
+        stream = stream or torch.cuda.current_stream(self.device)
+        if self._static is None:
+            self._static = self._static_fields()
+        buf = self.h_table.next()
+        table = buf.numpy()[: self.n * N.FACTORED_TENSOR.itemsize].view(N.FACTORED_TENSOR)
+        table[:] = self._static
+        table["grad"] = [g.data_ptr() for g in grads]
+        for k in ("decay", "alpha", "v_w", "m_w", "c_w", "eps1", "eps_came"):
+            table[k] = scalars[k]
+        lib = N.lib()
+        N.check(lib.af8_factored_upload(ctypes.byref(self.cfg), buf.data_ptr(), self.d_table.data_ptr(), self.n,
+                                        stream.cuda_stream), "af8_factored_upload")
+        self.h_table.mark(stream)
+        self._alpha_on_device = scale is not None
+        if scale is not None:
+            self._param_scale(scale, stream)
+        self._stats(N.FSTAT_GRADSQ, buf, stream)
+        self._small(False, stream)
+        if self.came:
+            # clip of U (optimizer.py:826-828); d == 0 means no clip: an infinite threshold gives divisor 1
+            self._update(N.FUPD_SUMSQ_U, False, stream)
+            self._finalize(table, 1, d if d > 0 else float("inf"), False, fira_margin, stream)
+            self._stats(N.FSTAT_RESIDUAL, buf, stream)
+            self._small(True, stream)
+            if fira:                                    # the final update is applied with d = 0 (optimizer.py:953)
+                self._update(N.FUPD_SUMSQ, True, stream)
+                self._finalize(table, 2, 0.0, True, fira_margin, stream)
+            self._update(N.FUPD_APPLY, True, stream)
+        elif fira or d > 0:
+            self._update(N.FUPD_SUMSQ, False, stream)
+            self._finalize(table, 0, d, fira, fira_margin, stream)
+            self._update(N.FUPD_APPLY, True, stream)
+        else:
+            self._update(N.FUPD_APPLY, False, stream)
+
+    def _param_scale(self, scale, stream):
+        chunk = N.lib().af8_scale_chunk()
+        nchunks = (self.numel + chunk - 1) // chunk
+        if self.h_scale is None:
+            self.h_scale = _PinnedRing(self.n * N.SCALE_TENSOR.itemsize)
+            self.d_scale = torch.empty(self.n * N.SCALE_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+            self.d_chunks = torch.empty(int(nchunks.sum()), dtype=torch.float32, device=self.device)
+        hb = self.h_scale.next()
+        t = hb.numpy()[: self.n * N.SCALE_TENSOR.itemsize].view(N.SCALE_TENSOR)
+        t["param"] = [p.data_ptr() for p in self.params]
+        t["numel"] = self.numel
+        t["first_chunk"] = np.concatenate([[0], np.cumsum(nchunks)[:-1]])
+        t["sqrt_n"] = np.sqrt(self.numel.astype(np.float64)).astype(np.float32)
+        for k in ("rho", "eps2", "bc", "weight_decay", "bc_mode", "scale_weight_decay"):
+            t[k] = scale[k]
+        self._log("param_scale", lambda: N.check(N.lib().af8_param_scale(
+            hb.data_ptr(), self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(), self.d_table.data_ptr(),
+            N.FACTORED_TENSOR.itemsize, N.FACTORED_TENSOR.fields["alpha"][1], N.FACTORED_TENSOR.fields["decay"][1],
+            stream.cuda_stream), "af8_param_scale"), stream)
+        self.h_scale.mark(stream)
+
+    def norms(self):
         dyn = self.d_dyn.cpu().numpy().view(N.DYN_SCALARS)
         return dyn["norm"].copy()

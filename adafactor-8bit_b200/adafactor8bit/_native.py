@@ -44,9 +44,25 @@ NORM_TENSOR = np.dtype([
     ("first_block", np.int64), ("n_blocks", np.int64), ("fira_prev", _P),
     ("fira_has_prev", np.int32), ("pre_div_mode", np.int32),
     ("alpha", np.float32), ("clip_div", np.float32), ("sqrt_n", np.float32), ("d", np.float32),
-    ("fira_margin1", np.float32), ("reserved", np.float32), ("alpha_dev", _P),
+    ("fira_margin1", np.float32), ("partials_f64", np.int32), ("alpha_dev", _P),
 ], align=True)
 assert NORM_TENSOR.itemsize == 64
+
+SMALL_STATE = np.dtype([
+    ("q", _P), ("scale", _P), ("min_log", _P), ("f32", _P), ("fmt", np.int32), ("block", np.int32),
+], align=True)
+assert SMALL_STATE.itemsize == 40
+
+FACTORED_TENSOR = np.dtype([
+    ("param", _P), ("grad", _P), ("m_q", _P), ("m_scale", _P), ("m_f32", _P),
+    ("row_sum", _P), ("col_sum", _P), ("inv_row", _P), ("inv_col", _P),
+    ("inv_row_conf", _P), ("inv_col_conf", _P),
+    ("row_var", SMALL_STATE), ("col_var", SMALL_STATE), ("conf_row", SMALL_STATE), ("conf_col", SMALL_STATE),
+    ("rows", np.int64), ("cols", np.int64), ("first_chunk", np.int64), ("first_tile", np.int64),
+    ("decay", np.float32), ("alpha", np.float32), ("v_w", np.float32), ("m_w", np.float32),
+    ("c_w", np.float32), ("eps1", np.float32), ("eps_came", np.float32), ("reserved", np.float32),
+], align=True)
+assert FACTORED_TENSOR.itemsize == 312
 
 SCALE_TENSOR = np.dtype([
     ("param", _P), ("numel", np.int64), ("first_chunk", np.int64),
@@ -68,6 +84,17 @@ class FullrankCfg(ctypes.Structure):
     ]
 
 
+class FactoredCfg(ctypes.Structure):
+    _fields_ = [
+        ("param_dtype", ctypes.c_int32), ("grad_dtype", ctypes.c_int32), ("m_fmt", ctypes.c_int32),
+        ("m_block", ctypes.c_int32), ("came", ctypes.c_int32), ("negate_grad", ctypes.c_int32),
+        ("mode", ctypes.c_int32), ("v_floor", ctypes.c_float),
+    ]
+
+
+FSTAT_GRADSQ, FSTAT_RESIDUAL = 0, 1
+FUPD_SUMSQ_U, FUPD_SUMSQ, FUPD_APPLY = 0, 1, 2
+
 _c_p = ctypes.c_void_p
 _c_i = ctypes.c_int32
 _c_l = ctypes.c_int64
@@ -81,6 +108,13 @@ PROTOTYPES = {
     "af8_set_qmap": (_c_i, [_c_p, _c_p, _c_p]),
     "af8_fullrank_step": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
     "af8_fullrank_upload": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p]),
+    "af8_factored_chunk": (_c_i, [_c_i]),
+    "af8_factored_tile_rows": (_c_i, []),
+    "af8_factored_tile_cols": (_c_i, []),
+    "af8_factored_upload": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_p, _c_i, _c_p]),
+    "af8_factored_stats": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_p, _c_i, _c_p, _c_p]),
+    "af8_factored_small": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_i, _c_p]),
+    "af8_factored_update": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
     "af8_fullrank_limited_step_noalloc": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_f, _c_i, _c_f, _c_p, _c_i, _c_p, _c_p]),
     "af8_noalloc_max_numel": (_c_l, [_c_i]),

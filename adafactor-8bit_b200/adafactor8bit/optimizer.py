@@ -22,7 +22,7 @@ from torch import Tensor
 from torch.optim import Optimizer
 
 from . import _native as N
-from ._engine import FullrankPlan
+from ._engine import FactoredPlan, FullrankPlan
 
 __all__ = ["Adafactor8Bit"]
 
@@ -389,27 +389,82 @@ class Adafactor8Bit(Optimizer):
         apollo_rank = group.get("apollo_rank", 0)
         factored = group.get("factored", True)
         sgd = group["beta2"] is None and group["beta2_decay"] is None
-        fullrank = {}
+        fullrank, factored_items = {}, {}
         for p, g, st in entries:
             if sgd:
                 raise NotImplementedError("the SGD preset is not available in this build")
             if apollo_rank > 0 and "apollo_seed" in st:
                 raise NotImplementedError("the APOLLO path is not available in this build")
-            if g.dim() >= 2 and factored:
-                raise NotImplementedError("the factored path is not available in this build")
             quant = st.get("is_quantized", False)
-            v_fmt = st.get("v_quant_type", "al8") if quant else "fp32"
             if group.get("beta1") is not None:
-                m_fmt = st.get("m_quant_type", "uf8")
-                if "m" in st:
-                    m_fmt = "fp32"
+                m_fmt = "fp32" if "m" in st else st.get("m_quant_type", "uf8")
                 m_block = st.get("m_block_size", group.get("m_block_size", 256))
             else:
                 m_fmt, m_block = None, 0
+            if g.dim() >= 2 and factored:
+                if g.dim() != 2:
+                    raise NotImplementedError("factored tensors with more than two dimensions are not available in this build")
+                came = group.get("beta3") is not None and group.get("beta1") is not None
+                key = (p.device, g.dtype, m_fmt, m_block, came)
+                factored_items.setdefault(key, []).append((p, g, st))
+                continue
+            v_fmt = st.get("v_quant_type", "al8") if quant else "fp32"
             key = (p.device, g.dtype, v_fmt, m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block)
             fullrank.setdefault(key, []).append((p, g, st))
         for key, items in fullrank.items():
             self._run_fullrank(gi, group, key, items)
+        for key, items in factored_items.items():
+            self._run_factored(gi, group, key, items)
+
+    def _scale_inputs(self, group, n):
+        scale = {k: np.zeros(n, dtype=f32) for k in ("rho", "eps2", "bc", "weight_decay")}
+        scale["bc_mode"] = np.zeros(n, dtype=np.int32)
+        scale["scale_weight_decay"] = np.full(n, int(bool(group.get("scale_weight_decay", True))), dtype=np.int32)
+        return scale
+
+    def _fill_scale(self, scale, i, group, sc):
+        scale["rho"][i] = sc["rho"]
+        scale["eps2"][i] = f32(sc["eps2"])
+        scale["weight_decay"][i] = f32(group["weight_decay"])
+        if sc["bc_mul"] is not None:
+            scale["bc"][i], scale["bc_mode"][i] = sc["bc_mul"], 1
+        elif sc["bc_div"] is not None:
+            scale["bc"][i], scale["bc_mode"][i] = sc["bc_div"], 2
+
+    def _run_factored(self, gi, group, key, items):
+        device, gdtype, m_fmt, m_block, came = key
+        ids = tuple(id(p) for p, _, _ in items)
+        pkey = (gi, "factored", key, bool(group["maximize"]))
+        plan = self._plans.get(pkey)
+        if plan is None or plan.ids != ids:
+            v_fmts = [(st.get("v_quant_type", "al8") if st.get("is_quantized", False) else "fp32") for _, _, st in items]
+            c_fmts = [(st.get("c_quant_type", st.get("v_quant_type", "al8")) if st.get("is_quantized", False) else "fp32")
+                      for _, _, st in items]
+            plan = FactoredPlan(device, gdtype, m_fmt, m_block, came, group["maximize"],
+                                [p for p, _, _ in items], [s for _, _, s in items], v_fmts, c_fmts)
+            plan.ids = ids
+            self._plans[pkey] = plan
+        n = len(items)
+        scale = self._scale_inputs(group, n) if group["scale_parameter"] else None
+        cols = {k: np.empty(n, dtype=f32) for k in ("decay", "alpha", "v_w", "m_w", "c_w", "eps1", "eps_came")}
+        grads = []
+        for i, (p, g, st) in enumerate(items):
+            step = st["step"] + 1
+            st["step"] = step
+            sc = self._step_scalars(group, step)
+            alpha, decay = self._alpha_decay(group, sc)
+            cols["decay"][i], cols["alpha"][i] = decay, alpha
+            cols["v_w"][i] = f32(sc["beta_val"])
+            cols["m_w"][i] = f32(1.0 - group["beta1"]) if group.get("beta1") is not None else f32(0.0)
+            cols["c_w"][i] = f32(1.0 - group["beta3"]) if group.get("beta3") is not None else f32(0.0)
+            cols["eps1"][i] = f32(sc["eps1"])
+            cols["eps_came"][i] = f32(group.get("eps_came", 1e-16))
+            if scale is not None:
+                self._fill_scale(scale, i, group, sc)
+            grads.append(g if g.is_contiguous() else g.contiguous())
+        with torch.cuda.device(device):
+            plan.run(grads, cols, d=float(group["d"]), fira=bool(group.get("enable_fira_for_adafactor", False)),
+                     fira_margin=float(group.get("fira_margin", 0.01)), scale=scale)
 
     def _run_fullrank(self, gi, group, key, items):
         device, gdtype, v_fmt, m_fmt, block, m_block = key

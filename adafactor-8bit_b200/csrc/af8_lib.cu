@@ -7,6 +7,7 @@
 #include "fullrank_api.cuh"
 #include "codec.cuh"
 #include "scale.cuh"
+#include "factored.cuh"
 #include "noalloc.cuh"
 
 extern "C" int af8_version(void) { return AF8_VERSION; }

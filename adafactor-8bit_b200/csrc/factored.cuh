@@ -1,0 +1,502 @@
+// Factored step for 2-D tensors: Adafactor (row / column second moments) and
+// CAME (confidence-guided, with momentum).
+//
+// Reference semantics: _update_param_8bit factored branch on the pure-PyTorch
+// route (optimizer.py:2202-2253 statistics and small-state EMAs, 2394-2399 and
+// 2543-2549 dispatch), _factored_inv_std (optimizer.py:818-821),
+// _compute_ut_clipped (optimizer.py:824-829), _fallback_2d_update
+// (optimizer.py:920-970).
+//
+// Three kernels, each launched once for a whole table of tensors:
+//   factored_stats_kernel   row and column sums of g*g, or of CAME's residual
+//                           (U - M)^2 + eps, over 64 x 256 tiles.  Every product
+//                           is rounded to binary32 as torch does and then
+//                           accumulated in binary64, so the binary32 means do not
+//                           depend on the order of accumulation.
+//   factored_small_kernel   one CTA per tensor: means, EMA into the (tiny) row /
+//                           column AL states with exact requantisation, mean of
+//                           the row state, inverse-std vectors.
+//   factored_update_kernel  flat chunks aligned to momentum blocks: the update
+//                           itself, its sum of squares, the parameter write and
+//                           the momentum requantisation.
+#pragma once
+
+#include "common.cuh"
+#include "fullrank_fast.cuh"
+#include "fullrank_generic.cuh"
+
+namespace af8 {
+
+constexpr int FSTAT_ROWS = 64;
+constexpr int FSTAT_COLS = 256;
+constexpr int FUPD_THREADS = 256;
+
+struct FactoredLaunch {
+    const af8_factored_tensor *tensors;
+    const af8_dyn_scalars *dyn;
+    double *block_sumsq;
+    int64_t total_units;
+    int32_t n_tensors;
+    int32_t grad_dtype, m_fmt, m_block, came, negate_grad, mode;
+    float v_floor;
+};
+
+__device__ __forceinline__ int find_factored_tile(const af8_factored_tensor *t, int n, int64_t id)
+{
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (__ldg(&t[mid].first_tile) <= id) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+__device__ __forceinline__ int find_factored_chunk(const af8_factored_tensor *t, int n, int64_t id)
+{
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (__ldg(&t[mid].first_chunk) <= id) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float load_grad_any(const void *g, int dtype, int64_t i)
+{
+    return dtype == AF8_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t *>(g)[i])
+                             : static_cast<const float *>(g)[i];
+}
+
+// momentum before the EMA (optimizer.py:694-697): dequantised codes or the fp32 state
+__device__ __forceinline__ float m_old_at(const af8_factored_tensor &T, int m_fmt, int m_block, int64_t flat)
+{
+    if (m_fmt == AF8_M_FP32) return T.m_f32[flat];
+    return m_decode(T.m_q, __ldg(T.m_scale + flat / m_block), flat, m_fmt);
+}
+
+// U = g * inv_row * inv_col, then the RMS clip divisor (optimizer.py:825-828)
+__device__ __forceinline__ float u_clipped(float g, float ir, float ic, float pre_div)
+{
+    float u = __fmul_rn(__fmul_rn(g, ir), ic);
+    if (pre_div != 1.0f) u = __fdiv_rn(u, pre_div);
+    return u;
+}
+
+// ---------------------------------------------------------------------------
+// statistics
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+factored_stats_kernel(const FactoredLaunch L)
+{
+    __shared__ double s_col[FSTAT_COLS];
+    __shared__ af8_factored_tensor sT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
+        const int t = find_factored_tile(L.tensors, L.n_tensors, id);
+        __syncthreads();
+        if (tid < (int)(sizeof(af8_factored_tensor) / 4))
+            reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
+        s_col[tid] = 0.0;
+        __syncthreads();
+        const int64_t R = sT.rows, C = sT.cols;
+        const int64_t ntc = (C + FSTAT_COLS - 1) / FSTAT_COLS;
+        const int64_t local = id - sT.first_tile;
+        const int64_t r0 = (local / ntc) * FSTAT_ROWS;
+        const int64_t c0 = (local % ntc) * FSTAT_COLS;
+        float pre_div = 1.0f;
+        if (L.mode == AF8_FSTAT_RESIDUAL) pre_div = L.dyn[t].pre_div;
+
+        double cacc[FSTAT_COLS / 32];
+        float icv[FSTAT_COLS / 32];
+#pragma unroll
+        for (int k = 0; k < FSTAT_COLS / 32; ++k) {
+            cacc[k] = 0.0;
+            const int64_t c = c0 + lane + 32 * k;
+            icv[k] = (L.mode == AF8_FSTAT_RESIDUAL && c < C) ? sT.inv_col[c] : 0.0f;
+        }
+        for (int rr = warp; rr < FSTAT_ROWS; rr += 8) {
+            const int64_t r = r0 + rr;
+            if (r >= R) break;
+            const float ir = (L.mode == AF8_FSTAT_RESIDUAL) ? sT.inv_row[r] : 0.0f;
+            double racc = 0.0;
+#pragma unroll
+            for (int k = 0; k < FSTAT_COLS / 32; ++k) {
+                const int64_t c = c0 + lane + 32 * k;
+                if (c < C) {
+                    const int64_t flat = r * C + c;
+                    float g = load_grad_any(sT.grad, L.grad_dtype, flat);
+                    if (L.negate_grad) g = -g;
+                    float x;
+                    if (L.mode == AF8_FSTAT_GRADSQ) {
+                        x = __fmul_rn(g, g);                                         // optimizer.py:2221
+                    } else {
+                        const float u = u_clipped(g, ir, icv[k], pre_div);           // optimizer.py:929
+                        const float m = lerp_t(m_old_at(sT, L.m_fmt, L.m_block, flat), u, sT.m_w);   // optimizer.py:930
+                        const float df = __fsub_rn(u, m);
+                        x = __fadd_rn(__fmul_rn(df, df), sT.eps_came);               // optimizer.py:932
+                    }
+                    const double xd = (double)x;
+                    racc += xd;
+                    cacc[k] += xd;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) racc += __shfl_xor_sync(0xffffffffu, racc, o);
+            if (lane == 0) atomicAdd(sT.row_sum + r, racc);
+        }
+#pragma unroll
+        for (int k = 0; k < FSTAT_COLS / 32; ++k) atomicAdd(&s_col[lane + 32 * k], cacc[k]);
+        __syncthreads();
+        if (c0 + tid < C) atomicAdd(sT.col_sum + c0 + tid, s_col[tid]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// small states
+// ---------------------------------------------------------------------------
+// EMA + requantisation of one small state of n elements (optimizer.py:2232-2238,
+// 937-946, 2248-2251).  `out` receives the un-requantised values.  Returns this
+// thread's partial sum of the values (binary64) for the mean of the row state.
+__device__ double small_state_ema(const af8_small_state &S, const double *sums, double count, int64_t n,
+                                  float eps_add, float w, float floor_log, float *out, float *s_l, float (*s_red)[8])
+{
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    double acc = 0.0;
+    if (S.fmt == AF8_V_FP32) {
+        for (int64_t i = tid; i < n; i += blockDim.x) {
+            const float nv = __fadd_rn(__double2float_rn(sums[i] / count), eps_add);
+            const float v = lerp_t(S.f32[i], nv, w);
+            S.f32[i] = v;
+            out[i] = v;
+            acc += (double)v;
+        }
+        return acc;
+    }
+    const int bits = S.fmt;
+    const float qm1 = bits == 16 ? 65534.0f : 254.0f;
+    const int qmax = bits == 16 ? 65535 : 255;
+    const int block = S.block;
+    const int64_t nblocks = (n + block - 1) / block;
+    for (int64_t b = 0; b < nblocks; ++b) {
+        const float sc = S.scale[b], ml = S.min_log[b];
+        float mn = INFINITY, mx = -INFINITY;
+        __syncthreads();
+        for (int i = tid; i < block; i += blockDim.x) {
+            const int64_t e = b * block + i;
+            float v = 0.0f;                                       // padding re-enters as zeros (optimizer.py:303-305)
+            if (e < n) {
+                const uint32_t code = bits == 16 ? static_cast<const uint16_t *>(S.q)[e] : static_cast<const uint8_t *>(S.q)[e];
+                const float nv = __fadd_rn(__double2float_rn(sums[e] / count), eps_add);
+                v = lerp_t(al_decode(code, sc, ml, qm1), nv, w);
+                out[e] = v;
+                acc += (double)v;
+            }
+            const float l = al_log2(v);
+            if (v != 0.0f) mn = fminf(mn, l);
+            mx = fmaxf(mx, l);
+            s_l[i] = (v != 0.0f) ? l : -INFINITY;
+        }
+        mn = warp_min(mn);
+        mx = warp_max(mx);
+        if (lane == 0) { s_red[0][warp] = mn; s_red[1][warp] = mx; }
+        __syncthreads();
+        for (int w8 = 0; w8 < 8; ++w8) { mn = fminf(mn, s_red[0][w8]); mx = fmaxf(mx, s_red[1][w8]); }
+        float min_log, scale;
+        al_range(mn, mx, floor_log, min_log, scale);
+        for (int i = tid; i < block; i += blockDim.x) {
+            const float l = s_l[i];
+            const uint32_t code = (l == -INFINITY) ? 0u : al_encode(1.0f, l, min_log, scale, qm1, qmax);
+            const int64_t e = b * block + i;
+            if (bits == 16) static_cast<uint16_t *>(S.q)[e] = (uint16_t)code;
+            else static_cast<uint8_t *>(S.q)[e] = (uint8_t)code;
+        }
+        if (tid == 0) { S.scale[b] = scale; S.min_log[b] = min_log; }
+    }
+    return acc;
+}
+
+__global__ void __launch_bounds__(256)
+factored_small_kernel(const af8_factored_tensor *tensors, int conf, float floor_log)
+{
+    extern __shared__ float s_l[];
+    __shared__ float s_red[2][8];
+    __shared__ double s_acc[256];
+    const af8_factored_tensor T = tensors[blockIdx.x];
+    const int tid = threadIdx.x;
+    const af8_small_state &SR = conf ? T.conf_row : T.row_var;
+    const af8_small_state &SC = conf ? T.conf_col : T.col_var;
+    float *inv_r = conf ? T.inv_row_conf : T.inv_row;
+    float *inv_c = conf ? T.inv_col_conf : T.inv_col;
+    const float w = conf ? T.c_w : T.v_w;
+    const float eps_add = conf ? 0.0f : T.eps1;                 // optimizer.py:2222-2223 vs 933-934
+
+    const double part = small_state_ema(SR, T.row_sum, (double)T.cols, T.rows, eps_add, w, floor_log, inv_r, s_l, s_red);
+    small_state_ema(SC, T.col_sum, (double)T.rows, T.cols, eps_add, w, floor_log, inv_c, s_l, s_red);
+
+    // mean of the row state, clamped (optimizer.py:2236, 948)
+    s_acc[tid] = part;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (tid < o) s_acc[tid] += s_acc[tid + o];
+        __syncthreads();
+    }
+    float rm = __double2float_rn(s_acc[0] / (double)T.rows);
+    if (rm < T.eps1) rm = T.eps1;
+    // inverse std vectors (optimizer.py:818-821)
+    for (int64_t i = tid; i < T.rows; i += blockDim.x) inv_r[i] = rsqrt_t(__fdiv_rn(inv_r[i], rm));
+    for (int64_t j = tid; j < T.cols; j += blockDim.x) inv_c[j] = rsqrt_t(inv_c[j]);
+}
+
+// ---------------------------------------------------------------------------
+// update
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(FUPD_THREADS)
+factored_update_kernel(const FactoredLaunch L, int chunk)
+{
+    extern __shared__ float s_m[];                 // new momentum of the chunk (quantised formats)
+    __shared__ af8_factored_tensor sT;
+    __shared__ double s_acc[FUPD_THREADS / 32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool has_m = L.m_fmt != AF8_M_NONE;
+    const bool m_quant = has_m && L.m_fmt != AF8_M_FP32;
+    const bool writes = L.mode == AF8_FUPD_APPLY;
+
+    for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
+        const int t = find_factored_chunk(L.tensors, L.n_tensors, id);
+        __syncthreads();
+        if (tid < (int)(sizeof(af8_factored_tensor) / 4))
+            reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
+        __syncthreads();
+        const int64_t C = sT.cols, numel = sT.rows * sT.cols;
+        const int64_t base = (id - sT.first_chunk) * chunk;
+        const int valid = (int)min((int64_t)chunk, numel - base);
+        float pre_div = 1.0f, step_mul = -sT.alpha, fira = 1.0f;
+        bool zero_upd = false;
+        if (L.dyn != nullptr) {
+            const af8_dyn_scalars ds = L.dyn[t];
+            if (L.came) pre_div = ds.pre_div;
+            if (writes) { step_mul = ds.step; fira = ds.fira; zero_upd = ds.zero != 0.0f; }
+        }
+        if (L.mode == AF8_FUPD_SUMSQ_U) pre_div = 1.0f;           // the clip divisor is what this pass measures
+
+        int64_t row = (base + tid) / C;
+        int64_t col = (base + tid) - row * C;
+        double acc = 0.0;
+        float *param = static_cast<float *>(sT.param);
+        for (int i = tid; i < chunk; i += FUPD_THREADS) {
+            float mj = 0.0f;
+            if (i < valid) {
+                const int64_t flat = base + i;
+                float g = load_grad_any(sT.grad, L.grad_dtype, flat);
+                if (L.negate_grad) g = -g;
+                const float ir = sT.inv_row[row], ic = sT.inv_col[col];
+                float u;
+                if (L.came) {
+                    const float uc = u_clipped(g, ir, ic, pre_div);                  // optimizer.py:929
+                    if (L.mode == AF8_FUPD_SUMSQ_U) {
+                        u = uc;
+                    } else {
+                        mj = lerp_t(m_old_at(sT, L.m_fmt, L.m_block, flat), uc, sT.m_w);   // optimizer.py:930
+                        u = __fmul_rn(__fmul_rn(mj, sT.inv_row_conf[row]), sT.inv_col_conf[col]);   // optimizer.py:952
+                    }
+                } else if (has_m) {
+                    mj = lerp_t(m_old_at(sT, L.m_fmt, L.m_block, flat), g, sT.m_w);        // optimizer.py:959
+                    u = __fmul_rn(__fmul_rn(mj, ir), ic);                                  // optimizer.py:961
+                } else {
+                    u = __fmul_rn(__fmul_rn(g, ir), ic);                                   // optimizer.py:968-969
+                }
+                if (!writes) {
+                    acc += (double)__fmul_rn(u, u);
+                } else {
+                    if (!m_quant && has_m) sT.m_f32[flat] = mj;
+                    float pj = __fmul_rn(param[flat], sT.decay);                           // optimizer.py:2039
+                    if (!zero_upd) pj = __fmaf_rn(step_mul, __fmul_rn(u, fira), pj);       // optimizer.py:803, 874
+                    param[flat] = pj;
+                }
+            }
+            if (writes && m_quant) s_m[i] = mj;
+            col += FUPD_THREADS;
+            while (col >= C) { col -= C; ++row; }
+        }
+        if (!writes) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) s_acc[warp] = acc;
+            __syncthreads();
+            if (tid == 0) {
+                double s = 0.0;
+                for (int w = 0; w < FUPD_THREADS / 32; ++w) s += s_acc[w];
+                L.block_sumsq[id] = s;
+            }
+            continue;
+        }
+        if (m_quant) {
+            __syncthreads();
+            const bool four_bit = (L.m_fmt == AF8_M_UF4 || L.m_fmt == AF8_M_D4);
+            const int subs = chunk / L.m_block;
+            for (int sb = warp; sb < subs; sb += FUPD_THREADS / 32) {
+                const int s0 = sb * L.m_block;
+                if (s0 >= valid) break;
+                float am = 0.0f;
+                for (int i = lane; i < L.m_block; i += 32) am = fmaxf(am, fabsf(s_m[s0 + i]));
+                am = fmaxf(warp_max(am), 1e-12f);
+                if (four_bit) {
+                    for (int i = lane * 2; i < L.m_block; i += 64)
+                        sT.m_q[(base + s0 + i) >> 1] = (uint8_t)((m_encode(s_m[s0 + i], am, L.m_fmt) << 4) | m_encode(s_m[s0 + i + 1], am, L.m_fmt));
+                } else {
+                    for (int i = lane; i < L.m_block; i += 32)
+                        sT.m_q[base + s0 + i] = (uint8_t)m_encode(s_m[s0 + i], am, L.m_fmt);
+                }
+                if (lane == 0) sT.m_scale[(base + s0) / L.m_block] = am;
+            }
+        }
+    }
+}
+
+inline int factored_chunk_for(int m_block)
+{
+    if (m_block <= 0) return 2048;
+    int k = 2048 / m_block;
+    if (k < 1) k = 1;
+    return k * m_block;
+}
+
+inline int validate_factored(const af8_factored_cfg &c, const af8_factored_tensor *T, int n)
+{
+    const bool has_m = c.m_fmt != AF8_M_NONE;
+    const bool m_quant = has_m && c.m_fmt != AF8_M_FP32;
+    const int chunk = factored_chunk_for(m_quant ? c.m_block : 0);
+    int64_t next_chunk = 0, next_tile = 0;
+    for (int i = 0; i < n; ++i) {
+        const af8_factored_tensor &t = T[i];
+        if (t.rows <= 0 || t.cols <= 0) return fail(AF8_ERR_INVALID, "factored tensor %d: empty shape", i);
+        if (t.rows * t.cols >= ((int64_t)1 << 40)) return fail(AF8_ERR_UNSUPPORTED, "factored tensor %d: too large", i);
+        if (!t.param || !t.grad || !t.row_sum || !t.col_sum || !t.inv_row || !t.inv_col)
+            return fail(AF8_ERR_INVALID, "factored tensor %d: null pointer", i);
+        if (c.came && (!t.inv_row_conf || !t.inv_col_conf)) return fail(AF8_ERR_INVALID, "factored tensor %d: CAME needs the confidence vectors", i);
+        if (m_quant && (!t.m_q || !t.m_scale)) return fail(AF8_ERR_INVALID, "factored tensor %d: null quantised momentum", i);
+        if (c.m_fmt == AF8_M_FP32 && !t.m_f32) return fail(AF8_ERR_INVALID, "factored tensor %d: null fp32 momentum", i);
+        if (t.first_chunk != next_chunk) return fail(AF8_ERR_INVALID, "factored tensor %d: first_chunk %lld, expected %lld", i, (long long)t.first_chunk, (long long)next_chunk);
+        if (t.first_tile != next_tile) return fail(AF8_ERR_INVALID, "factored tensor %d: first_tile %lld, expected %lld", i, (long long)t.first_tile, (long long)next_tile);
+        next_chunk += (t.rows * t.cols + chunk - 1) / chunk;
+        next_tile += ((t.rows + FSTAT_ROWS - 1) / FSTAT_ROWS) * ((t.cols + FSTAT_COLS - 1) / FSTAT_COLS);
+        const af8_small_state *ss[4] = {&t.row_var, &t.col_var, &t.conf_row, &t.conf_col};
+        for (int k = 0; k < (c.came ? 4 : 2); ++k) {
+            const af8_small_state &s = *ss[k];
+            if (s.fmt == AF8_V_FP32) {
+                if (!s.f32) return fail(AF8_ERR_INVALID, "factored tensor %d: null fp32 small state %d", i, k);
+            } else if (s.fmt == AF8_V_AL8 || s.fmt == AF8_V_AL16) {
+                if (!s.q || !s.scale || !s.min_log) return fail(AF8_ERR_INVALID, "factored tensor %d: null quantised small state %d", i, k);
+                if (s.block < 128 || s.block % 128 != 0 || s.block > GEN_MAX_BLOCK) return fail(AF8_ERR_INVALID, "factored tensor %d: bad block %d of small state %d", i, s.block, k);
+            } else {
+                return fail(AF8_ERR_INVALID, "factored tensor %d: bad format %d of small state %d", i, s.fmt, k);
+            }
+        }
+    }
+    return AF8_OK;
+}
+
+inline int check_factored_cfg(const af8_factored_cfg *cfg, const char *who)
+{
+    if (!cfg) return fail(AF8_ERR_INVALID, "%s: null cfg", who);
+    if (cfg->param_dtype != AF8_F32) return fail(AF8_ERR_UNSUPPORTED, "%s: only fp32 parameters are supported", who);
+    if (cfg->grad_dtype != AF8_F32 && cfg->grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "%s: gradients must be fp32 or bf16", who);
+    if (cfg->m_fmt < AF8_M_NONE || cfg->m_fmt > AF8_M_FP32) return fail(AF8_ERR_INVALID, "%s: bad m_fmt %d", who, cfg->m_fmt);
+    const bool m_quant = cfg->m_fmt != AF8_M_NONE && cfg->m_fmt != AF8_M_FP32;
+    if (m_quant && (cfg->m_block < 32 || cfg->m_block % 4 != 0 || cfg->m_block > 2048)) return fail(AF8_ERR_INVALID, "%s: bad m_block %d", who, cfg->m_block);
+    if (cfg->came && cfg->m_fmt == AF8_M_NONE) return fail(AF8_ERR_INVALID, "%s: CAME needs momentum", who);
+    return AF8_OK;
+}
+
+inline FactoredLaunch make_factored_launch(const af8_factored_cfg &c, const af8_factored_tensor *dev, int n,
+                                           int64_t units, const af8_dyn_scalars *dyn, double *sumsq)
+{
+    FactoredLaunch L;
+    L.tensors = dev; L.dyn = dyn; L.block_sumsq = sumsq; L.total_units = units; L.n_tensors = n;
+    L.grad_dtype = c.grad_dtype; L.m_fmt = c.m_fmt; L.m_block = c.m_block > 0 ? c.m_block : 256;
+    L.came = c.came ? 1 : 0; L.negate_grad = c.negate_grad ? 1 : 0; L.mode = c.mode; L.v_floor = c.v_floor;
+    return L;
+}
+
+}  // namespace af8
+
+extern "C" int32_t af8_factored_chunk(int32_t m_block) { return af8::factored_chunk_for(m_block); }
+extern "C" int32_t af8_factored_tile_rows(void) { return af8::FSTAT_ROWS; }
+extern "C" int32_t af8_factored_tile_cols(void) { return af8::FSTAT_COLS; }
+
+extern "C" int af8_factored_upload(const af8_factored_cfg *cfg, const af8_factored_tensor *host_tensors,
+                                   af8_factored_tensor *dev_tensors, int32_t n_tensors, void *stream)
+{
+    using namespace af8;
+    int rc = check_factored_cfg(cfg, "af8_factored_upload");
+    if (rc) return rc;
+    if (!host_tensors || !dev_tensors || n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_factored_upload: null or empty table");
+    rc = validate_factored(*cfg, host_tensors, n_tensors);
+    if (rc) return rc;
+    AF8_CUDA_TRY(cudaMemcpyAsync(dev_tensors, host_tensors, sizeof(af8_factored_tensor) * (size_t)n_tensors,
+                                 cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return AF8_OK;
+}
+
+extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                                  const af8_factored_tensor *host_tensors, int32_t n_tensors,
+                                  const af8_dyn_scalars *dyn, void *stream)
+{
+    using namespace af8;
+    int rc = check_factored_cfg(cfg, "af8_factored_stats");
+    if (rc) return rc;
+    if (!dev_tensors || !host_tensors || n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_factored_stats: null or empty table");
+    if (cfg->mode != AF8_FSTAT_GRADSQ && cfg->mode != AF8_FSTAT_RESIDUAL) return fail(AF8_ERR_INVALID, "af8_factored_stats: bad mode %d", cfg->mode);
+    if (cfg->mode == AF8_FSTAT_RESIDUAL && (!cfg->came || !dyn)) return fail(AF8_ERR_INVALID, "af8_factored_stats: the residual needs CAME and dyn");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int64_t tiles = 0;
+    for (int i = 0; i < n_tensors; ++i) {
+        const af8_factored_tensor &t = host_tensors[i];
+        AF8_CUDA_TRY(cudaMemsetAsync(t.row_sum, 0, sizeof(double) * (size_t)t.rows, st));
+        AF8_CUDA_TRY(cudaMemsetAsync(t.col_sum, 0, sizeof(double) * (size_t)t.cols, st));
+        tiles += ((t.rows + FSTAT_ROWS - 1) / FSTAT_ROWS) * ((t.cols + FSTAT_COLS - 1) / FSTAT_COLS);
+    }
+    FactoredLaunch L = make_factored_launch(*cfg, dev_tensors, n_tensors, tiles, dyn, nullptr);
+    int64_t grid = (int64_t)sm_count() * 6;
+    if (grid > tiles) grid = tiles;
+    factored_stats_kernel<<<(int)grid, 256, 0, st>>>(L);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+extern "C" int af8_factored_small(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                                  int32_t n_tensors, int32_t conf, void *stream)
+{
+    using namespace af8;
+    int rc = check_factored_cfg(cfg, "af8_factored_small");
+    if (rc) return rc;
+    if (!dev_tensors || n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_factored_small: null or empty table");
+    if (conf && !cfg->came) return fail(AF8_ERR_INVALID, "af8_factored_small: confidence states exist only with CAME");
+    const size_t smem = sizeof(float) * GEN_MAX_BLOCK;
+    factored_small_kernel<<<n_tensors, 256, smem, static_cast<cudaStream_t>(stream)>>>(dev_tensors, conf, cfg->v_floor);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                                   int32_t n_tensors, int64_t total_chunks, const af8_dyn_scalars *dyn,
+                                   double *block_sumsq, void *stream)
+{
+    using namespace af8;
+    int rc = check_factored_cfg(cfg, "af8_factored_update");
+    if (rc) return rc;
+    if (!dev_tensors || n_tensors <= 0 || total_chunks <= 0) return fail(AF8_ERR_INVALID, "af8_factored_update: null or empty table");
+    if (cfg->mode < AF8_FUPD_SUMSQ_U || cfg->mode > AF8_FUPD_APPLY) return fail(AF8_ERR_INVALID, "af8_factored_update: bad mode %d", cfg->mode);
+    if (cfg->mode != AF8_FUPD_APPLY && !block_sumsq) return fail(AF8_ERR_INVALID, "af8_factored_update: this mode needs block_sumsq");
+    if (cfg->mode == AF8_FUPD_SUMSQ_U && !cfg->came) return fail(AF8_ERR_INVALID, "af8_factored_update: SUMSQ_U is a CAME pass");
+    if (cfg->came && cfg->mode != AF8_FUPD_SUMSQ_U && !dyn) return fail(AF8_ERR_INVALID, "af8_factored_update: CAME passes need dyn");
+    const bool m_quant = cfg->m_fmt != AF8_M_NONE && cfg->m_fmt != AF8_M_FP32;
+    const int chunk = factored_chunk_for(m_quant ? cfg->m_block : 0);
+    FactoredLaunch L = make_factored_launch(*cfg, dev_tensors, n_tensors, total_chunks, dyn, block_sumsq);
+    const size_t smem = sizeof(float) * (size_t)chunk;
+    int64_t grid = (int64_t)sm_count() * 6;
+    if (grid > total_chunks) grid = total_chunks;
+    factored_update_kernel<<<(int)grid, FUPD_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(L, chunk);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}

@@ -19,13 +19,19 @@ namespace af8 {
 // -alpha/denom (optimizer.py:874); in pre_div_mode 1 the RMS clip of the
 // momentum-only rule (optimizer.py:897-899).
 __global__ void __launch_bounds__(256)
-norm_finalize_kernel(const af8_norm_tensor *tensors, const float *block_sumsq, af8_dyn_scalars *dyn)
+norm_finalize_kernel(const af8_norm_tensor *tensors, const void *block_sumsq, af8_dyn_scalars *dyn)
 {
     __shared__ double s_acc[256];
     const af8_norm_tensor T = tensors[blockIdx.x];
     const int tid = threadIdx.x;
     double acc = 0.0;
-    for (int64_t i = tid; i < T.n_blocks; i += 256) acc += (double)block_sumsq[T.first_block + i];
+    if (T.partials_f64) {
+        const double *ps = static_cast<const double *>(block_sumsq);
+        for (int64_t i = tid; i < T.n_blocks; i += 256) acc += ps[T.first_block + i];
+    } else {
+        const float *ps = static_cast<const float *>(block_sumsq);
+        for (int64_t i = tid; i < T.n_blocks; i += 256) acc += (double)ps[T.first_block + i];
+    }
     s_acc[tid] = acc;
     __syncthreads();
     for (int o = 128; o > 0; o >>= 1) {
@@ -246,7 +252,7 @@ extern "C" int af8_device_status(int32_t *status_out, void *stream)
     return AF8_OK;
 }
 
-extern "C" int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors, const float *block_sumsq,
+extern "C" int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors, const void *block_sumsq,
                                  af8_dyn_scalars *dyn, void *stream)
 {
     using namespace af8;

@@ -140,7 +140,7 @@ extern "C" int af8_fullrank_limited_step_noalloc(const af8_fullrank_cfg *cfg, co
     nrow.d = clip_d;
     nrow.clip_div = clip_d > 0.0f ? (float)(sqrt_n * (double)clip_d) : 0.0f;
     nrow.fira_margin1 = fira_margin1;
-    nrow.reserved = 0.0f;
+    nrow.partials_f64 = 0;
     nrow.alpha_dev = nullptr;
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);

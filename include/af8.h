@@ -191,7 +191,8 @@ typedef struct af8_norm_tensor {
     float sqrt_n;           /* float(sqrt(numel)) */
     float d;
     float fira_margin1;     /* float(1 + fira_margin) */
-    float reserved;
+    int32_t partials_f64;   /* 0: block_sumsq holds floats (full-rank passes); 1: doubles
+                               (factored passes) */
     const float *alpha_dev; /* when not NULL: device location of alpha (overrides `alpha`);
                                used when af8_param_scale computed it on the device */
 } af8_norm_tensor;
@@ -203,8 +204,110 @@ typedef struct af8_norm_tensor {
  * arithmetic of _apply_fira_cuda / _safe_rms_denom (optimizer.py:785-793,
  * 859-863). */
 AF8_API int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors,
-                      const float *block_sumsq, af8_dyn_scalars *dyn,
-                      void *stream);
+                              const void *block_sumsq, af8_dyn_scalars *dyn,
+                              void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* Factored step: Adafactor and CAME on 2-D tensors                          */
+/* ------------------------------------------------------------------------ */
+
+/* A small per-row or per-column state: AL8/AL16 codes with per-block ranges,
+ * or fp32 (optimizer.py:389-401: keys <prefix>_q/_scale/_min_log or <prefix>). */
+typedef struct af8_small_state {
+    void *q;            /* uint8 (AL8) / uint16 (AL16) codes, padded to `block`; NULL for fp32 */
+    float *scale;
+    float *min_log;
+    float *f32;         /* fp32 state when fmt == AF8_V_FP32 */
+    int32_t fmt;        /* AF8_V_* */
+    int32_t block;      /* AL block size of this state */
+} af8_small_state;
+
+/* One 2-D tensor (rows x cols, row-major) of a factored launch. */
+typedef struct af8_factored_tensor {
+    void *param;                /* fp32 */
+    const void *grad;           /* fp32 or bf16 */
+    uint8_t *m_q;               /* momentum codes over the flattened tensor, or NULL */
+    float *m_scale;
+    float *m_f32;               /* fp32 momentum, or NULL */
+    double *row_sum;            /* rows doubles: scratch, filled by af8_factored_stats */
+    double *col_sum;            /* cols doubles: scratch */
+    float *inv_row;             /* rows floats: rsqrt(row_var / mean) of the second moment */
+    float *inv_col;             /* cols floats: rsqrt(col_var) */
+    float *inv_row_conf;        /* CAME: the same for the confidence states */
+    float *inv_col_conf;
+    af8_small_state row_var, col_var;      /* second-moment states */
+    af8_small_state conf_row, conf_col;    /* CAME confidence states */
+    int64_t rows, cols;
+    int64_t first_chunk;        /* running sum of ceil(rows*cols / chunk) (update passes) */
+    int64_t first_tile;         /* running sum of stat tiles (af8_factored_stats) */
+    float decay;                /* 1 - wd_mult*wd, 1.0 without weight decay */
+    float alpha;
+    float v_w;                  /* second-moment EMA weight beta_val */
+    float m_w;                  /* float(1 - beta1) */
+    float c_w;                  /* float(1 - beta3) */
+    float eps1;
+    float eps_came;
+    float reserved;
+} af8_factored_tensor;
+
+enum {
+    AF8_FSTAT_GRADSQ = 0,     /* row / column sums of g*g (optimizer.py:2221-2223) */
+    AF8_FSTAT_RESIDUAL = 1    /* CAME: sums of (U - M)^2 + eps_came (optimizer.py:932-934) */
+};
+
+enum {
+    AF8_FUPD_SUMSQ_U = 0,     /* per-chunk sum of squares of U = g*inv_row*inv_col (CAME clip,
+                                 optimizer.py:826-828) or of the final update (d-clip / Fira) */
+    AF8_FUPD_SUMSQ = 1,       /* per-chunk sum of squares of the final update */
+    AF8_FUPD_APPLY = 2        /* write parameters (and momentum codes), scaled by af8_dyn_scalars */
+};
+
+typedef struct af8_factored_cfg {
+    int32_t param_dtype;    /* AF8_F32 */
+    int32_t grad_dtype;     /* AF8_F32 or AF8_BF16 */
+    int32_t m_fmt;          /* AF8_M_*; AF8_M_NONE when beta1 is None */
+    int32_t m_block;
+    int32_t came;           /* 1: CAME (needs momentum) */
+    int32_t negate_grad;
+    int32_t mode;           /* AF8_FSTAT_* for af8_factored_stats, AF8_FUPD_* for af8_factored_update */
+    float v_floor;          /* min_log floor of the AL requantisation (-126) */
+} af8_factored_cfg;
+
+/* Number of flattened elements per work unit of af8_factored_update for a
+ * momentum block size (a multiple of m_block, at most 2048). */
+AF8_API int32_t af8_factored_chunk(int32_t m_block);
+/* Rows and columns per tile of af8_factored_stats. */
+AF8_API int32_t af8_factored_tile_rows(void);
+AF8_API int32_t af8_factored_tile_cols(void);
+
+/* Validate a host table and copy it to the device (as af8_fullrank_upload). */
+AF8_API int af8_factored_upload(const af8_factored_cfg *cfg, const af8_factored_tensor *host_tensors,
+                                af8_factored_tensor *dev_tensors, int32_t n_tensors, void *stream);
+
+/* Row and column sums in binary64 for every tensor: zeroes row_sum / col_sum,
+ * then accumulates.  RESIDUAL mode reads dyn[i].pre_div (the clip divisor of U).
+ * Replaces compute_factored_sums (kernels.cu:1946-1956) and fused_came_pass1
+ * (kernels.cu:2223-2242). */
+AF8_API int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                               const af8_factored_tensor *host_tensors, int32_t n_tensors,
+                               const af8_dyn_scalars *dyn, void *stream);
+
+/* Per tensor: means from the sums, EMA into the row / column states (second
+ * moment when conf == 0, CAME confidence when conf != 0), requantisation, and
+ * the inverse-std vectors inv_row / inv_col (or inv_*_conf).
+ * Replaces fused_log_quantize_lerp on the small states and the torch glue
+ * around it (optimizer.py:2226-2252, 2289-2294, 818-821). */
+AF8_API int af8_factored_small(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                               int32_t n_tensors, int32_t conf, void *stream);
+
+/* One pass over all elements in chunks.  block_sumsq: one DOUBLE per chunk
+ * (SUMSQ modes; set af8_norm_tensor.partials_f64 when finalising them).  dyn: per-tensor scalars (pre_div always read when cfg->came,
+ * step / fira / zero in APPLY mode).
+ * Replaces fused_update_2d_*, compute_ut_rms and fused_came_pass2*
+ * (kernels.cu:1651-1917, 1986-2000, 2244-2405). */
+AF8_API int af8_factored_update(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                                int32_t n_tensors, int64_t total_chunks, const af8_dyn_scalars *dyn,
+                                double *block_sumsq, void *stream);
 
 /* ------------------------------------------------------------------------ */
 /* Step without caller-provided working memory                               */

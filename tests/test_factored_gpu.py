@@ -1,0 +1,69 @@
+"""Parity of the CUDA factored path (Adafactor, CAME) with the CPU oracle and the
+reference's golden vectors, through the optimizer class."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import parity
+from oracle_runner import FACTORED_CASES, OracleRun, golden_entries, load_golden
+from test_fullrank_gpu import make_optimizer, state_np, to_cuda_grad
+
+pytestmark = pytest.mark.gpu
+
+CODE_KEYS = ("row_var_q", "col_var_q", "conf_row_q", "conf_col_q", "variance_q", "m_q")
+RANGE_KEYS = ("row_var_scale", "row_var_min_log", "col_var_scale", "col_var_min_log", "conf_row_scale",
+              "conf_row_min_log", "conf_col_scale", "conf_col_min_log", "variance_scale", "variance_min_log", "m_scale")
+F32_KEYS = ("row_var", "col_var", "conf_row", "conf_col", "variance", "m")
+
+
+def compare(name, t, i, st_gpu, st_cpu, p_gpu, p_cpu, param_tol):
+    for key in CODE_KEYS:
+        if key in st_cpu:
+            a, b = state_np(st_gpu, key), np.asarray(st_cpu[key]).reshape(-1)
+            parity.assert_codes(a, b, f"{name} t{t} p{i} {key}", al16=(b.dtype == np.uint16),
+                                zero_reserved=(key != "m_q"))
+    for key in RANGE_KEYS:
+        if key in st_cpu:
+            parity.assert_ranges(state_np(st_gpu, key), st_cpu[key], f"{name} t{t} p{i} {key}", max_ulp=4)
+    for key in F32_KEYS:
+        if key in st_cpu:
+            assert parity.rel_l2(state_np(st_gpu, key), st_cpu[key]) <= 1e-6, f"{name} t{t} p{i} {key}"
+    parity.assert_params(p_gpu.detach().cpu().numpy(), p_cpu, f"{name} t{t} p{i} param", tol=param_tol)
+
+
+@pytest.mark.parametrize("name", FACTORED_CASES)
+def test_factored_free_running_matches_oracle(name, oracle):
+    run = OracleRun(name)
+    params, opt = make_optimizer(run)
+    steps = run.case["steps"]
+    for t in range(1, steps + 1):
+        for p, g in zip(params, run.grads[t]):
+            p.grad = to_cuda_grad(g, p.shape)
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            compare(name, t, i, opt.state[p], run.states[i], p, run.params[i], param_tol=2e-6)
+    from adafactor8bit import _native
+    assert _native.device_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+@pytest.mark.parametrize("name", ["adafactor_factored", "adafactor_factored_m"])
+def test_factored_matches_reference_golden(name, oracle):
+    run = OracleRun(name)
+    gold = load_golden(name)
+    params, opt = make_optimizer(run)
+    steps = run.case["steps"]
+    for t in range(1, steps + 1):
+        for p, g in zip(params, run.grads[t]):
+            p.grad = to_cuda_grad(g, p.shape)
+        opt.step()
+    torch.cuda.synchronize()
+    for i, p in enumerate(params):
+        ref = golden_entries(gold, steps, i)
+        parity.assert_params(p.detach().cpu().numpy(), ref["param"], f"{name} final p{i} vs reference", tol=1e-6)
+        for key in CODE_KEYS:
+            if key in ref:
+                parity.assert_codes(state_np(opt.state[p], key), ref[key], f"{name} final p{i} {key} vs reference",
+                                    al16=(ref[key].dtype == np.uint16), zero_reserved=(key != "m_q"))
