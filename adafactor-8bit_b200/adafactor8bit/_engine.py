@@ -539,3 +539,113 @@ class FactoredPlan:
     def norms(self):
         dyn = self.d_dyn.cpu().numpy().view(N.DYN_SCALARS)
         return dyn["norm"].copy()
+
+
+class ApolloPlan:
+    """APOLLO tensors of one parameter group (optimizer.py:2587-3084): per-tensor
+    projection, one batched low-rank state update (the full-rank kernel run on the
+    projected gradients), per-tensor scaling and write-back."""
+
+    def __init__(self, device, grad_dtype, v_fmt, m_fmt, block, m_block, negate, params, states, rank):
+        self.device = torch.device(device)
+        self.params, self.states = list(params), list(states)
+        self.n = len(self.params)
+        self.grad_dtype = _GRAD_DT[grad_dtype]
+        self.v_fmt, self.m_fmt, self.block, self.m_block = v_fmt, m_fmt, int(block), int(m_block) if m_block else 0
+        self.negate = int(bool(negate))
+        self.rank = int(rank)
+        for p in self.params:
+            if p.dtype != torch.float32 or not p.is_contiguous() or p.dim() != 2:
+                raise RuntimeError("the APOLLO kernels update contiguous 2-D fp32 parameters")
+        self.rows = [int(p.shape[0]) for p in self.params]
+        self.cols = [int(p.shape[1]) for p in self.params]
+        self.nch = [max(r, c) for r, c in zip(self.rows, self.cols)]
+        self.nl = [n * self.rank for n in self.nch]
+        self.total_numel = int(sum(r * c for r, c in zip(self.rows, self.cols)))
+        dev = self.device
+        self.g_low = [torch.empty(n, dtype=torch.float32, device=dev) for n in self.nl]
+        self.upd = [torch.zeros(n, dtype=torch.float32, device=dev) for n in self.nl]
+        self.chan_g2 = [torch.empty(n, dtype=torch.float64, device=dev) for n in self.nch]
+        self.sf = [torch.empty(n, dtype=torch.float32, device=dev) for n in self.nch]
+        self.sums = torch.zeros(3 * self.n, dtype=torch.float64, device=dev)
+        self.out = torch.zeros(4 * self.n, dtype=torch.float32, device=dev)
+        self._low_plans = {}
+
+    def _low_plan(self, idx):
+        """Full-rank plan over the projected space for the tensors `idx` (they share the
+        first-step status, which selects the min_log floor)."""
+        key = tuple(idx)
+        plan = self._low_plans.get(key)
+        if plan is None:
+            fake_states = []
+            for i in idx:
+                st = self.states[i]
+                fs = {}
+                for src, dst in (("v_low_q", "variance_q"), ("v_low_scale", "variance_scale"),
+                                 ("v_low_min_log", "variance_min_log"), ("v_low", "variance"),
+                                 ("m_low_q", "m_q"), ("m_low_scale", "m_scale"), ("m_low", "m")):
+                    if st.get(src) is not None:
+                        fs[dst] = st[src]
+                fake_states.append(fs)
+            plan = FullrankPlan(self.device, torch.float32, self.v_fmt, self.m_fmt, self.block, self.m_block,
+                                True, False, False, [self.upd[i] for i in idx], fake_states)
+            self._low_plans[key] = plan
+        return plan
+
+    def run(self, grads, pts, per_tensor, lowrank_scalars, first_flags, floor_later, stream=None):
+        """per_tensor: list of dicts with the ApolloScalarsIn fields, decay, has_decay and the
+        device scalar `fira_prev` (or None).  lowrank_scalars: v_w, m_w, apollo_eps."""
+        stream = stream or torch.cuda.current_stream(self.device)
+        lib = N.lib()
+        s = stream.cuda_stream
+        log = LAUNCH_LOG
+        ev = None
+        if log is not None:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record(stream)
+        for i in range(self.n):
+            N.check(lib.af8_apollo_project(grads[i].data_ptr(), self.grad_dtype, self.negate, pts[i].data_ptr(),
+                                           self.rows[i], self.cols[i], self.rank, self.g_low[i].data_ptr(),
+                                           self.chan_g2[i].data_ptr(), s), "af8_apollo_project")
+        if log is not None:
+            ev[1].record(stream)
+        for first in (True, False):
+            idx = [i for i in range(self.n) if bool(first_flags[i]) == first]
+            if not idx:
+                continue
+            plan = self._low_plan(idx)
+            plan.cfg.v_floor = -126.0 if first else float(floor_later)
+            k = len(idx)
+            cols = dict(decay=np.zeros(k, np.float32), alpha=np.full(k, -1.0, np.float32),
+                        v_w=np.full(k, lowrank_scalars["v_w"], np.float32),
+                        v_keep=np.full(k, lowrank_scalars["v_keep"], np.float32), v_eps_add=np.zeros(k, np.float32),
+                        m_w=np.full(k, lowrank_scalars["m_w"], np.float32), eps_gradsq=np.zeros(k, np.float32),
+                        eps_denom=np.full(k, lowrank_scalars["apollo_eps"], np.float32),
+                        eps_sq=np.full(k, 1.17549435e-38, np.float32))
+            for i in idx:
+                self.upd[i].zero_()
+            plan.run([self.g_low[i] for i in idx], cols, d=0.0, fira=False)
+        if log is not None:
+            ev[2].record(stream)
+        for i in range(self.n):
+            t = per_tensor[i]
+            sin = N.ApolloScalarsIn()
+            for k in ("alpha", "bc", "d", "clip_div", "fira_margin1", "sqrt_scale"):
+                setattr(sin, k, float(t[k]))
+            for k in ("bc_mode", "fira", "fira_has_prev", "scale_tensor", "scale_front"):
+                setattr(sin, k, int(t[k]))
+            prev = t.get("fira_prev")
+            N.check(lib.af8_apollo_scales(self.upd[i].data_ptr(), self.g_low[i].data_ptr(), self.chan_g2[i].data_ptr(),
+                                          self.rows[i], self.cols[i], self.rank, ctypes.byref(sin), self.sf[i].data_ptr(),
+                                          self.sums.data_ptr() + 24 * i, prev.data_ptr() if prev is not None else None,
+                                          self.out.data_ptr() + 16 * i, s), "af8_apollo_scales")
+            N.check(lib.af8_apollo_apply(self.params[i].data_ptr(), grads[i].data_ptr(), self.grad_dtype, self.negate,
+                                         self.sf[i].data_ptr(), self.out.data_ptr() + 16 * i, self.rows[i], self.cols[i],
+                                         ctypes.byref(sin), float(t["decay"]), int(t["has_decay"]), s), "af8_apollo_apply")
+        if log is not None:
+            ev[3].record(stream)
+            log.append(("apollo_project", self.total_numel, ev[0], ev[1]))
+            log.append(("apollo_scales_apply", self.total_numel, ev[2], ev[3]))
+
+    def norms(self):
+        return self.out.cpu().numpy().reshape(self.n, 4)[:, 2].copy()

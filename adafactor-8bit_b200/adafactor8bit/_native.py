@@ -92,6 +92,15 @@ class FactoredCfg(ctypes.Structure):
     ]
 
 
+class ApolloScalarsIn(ctypes.Structure):
+    _fields_ = [
+        ("alpha", ctypes.c_float), ("bc", ctypes.c_float), ("d", ctypes.c_float), ("clip_div", ctypes.c_float),
+        ("fira_margin1", ctypes.c_float), ("sqrt_scale", ctypes.c_float),
+        ("bc_mode", ctypes.c_int32), ("fira", ctypes.c_int32), ("fira_has_prev", ctypes.c_int32),
+        ("scale_tensor", ctypes.c_int32), ("scale_front", ctypes.c_int32), ("reserved", ctypes.c_int32),
+    ]
+
+
 FSTAT_GRADSQ, FSTAT_RESIDUAL = 0, 1
 FUPD_SUMSQ_U, FUPD_SUMSQ, FUPD_APPLY = 0, 1, 2
 
@@ -115,6 +124,11 @@ PROTOTYPES = {
     "af8_factored_stats": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_p, _c_i, _c_p, _c_p]),
     "af8_factored_small": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_i, _c_p]),
     "af8_factored_update": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
+    "af8_apollo_project": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_l, _c_l, _c_l, _c_p, _c_p, _c_p]),
+    "af8_apollo_scales": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn), _c_p, _c_p, _c_p,
+                                 _c_p, _c_p]),
+    "af8_apollo_apply": (_c_i, [_c_p, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn),
+                                _c_f, _c_i, _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
     "af8_fullrank_limited_step_noalloc": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_f, _c_i, _c_f, _c_p, _c_i, _c_p, _c_p]),
     "af8_noalloc_max_numel": (_c_l, [_c_i]),

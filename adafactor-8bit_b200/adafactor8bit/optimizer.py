@@ -22,9 +22,14 @@ from torch import Tensor
 from torch.optim import Optimizer
 
 from . import _native as N
-from ._engine import FactoredPlan, FullrankPlan
+from ._engine import ApolloPlan, FactoredPlan, FullrankPlan
 
 __all__ = ["Adafactor8Bit"]
+
+# Device on which APOLLO's random projections are drawn.  None follows the reference
+# (the gradient's device, optimizer.py:139-149, so the values depend on the device type);
+# "cpu" draws the CPU generator's values, which is what CPU-side checkers reproduce.
+APOLLO_RNG_DEVICE = None
 
 logger = logging.getLogger(__name__)
 
@@ -389,12 +394,15 @@ class Adafactor8Bit(Optimizer):
         apollo_rank = group.get("apollo_rank", 0)
         factored = group.get("factored", True)
         sgd = group["beta2"] is None and group["beta2_decay"] is None
-        fullrank, factored_items = {}, {}
+        fullrank, factored_items, apollo_items = {}, {}, []
         for p, g, st in entries:
             if sgd:
                 raise NotImplementedError("the SGD preset is not available in this build")
             if apollo_rank > 0 and "apollo_seed" in st:
-                raise NotImplementedError("the APOLLO path is not available in this build")
+                if g.dim() != 2:
+                    raise NotImplementedError("APOLLO tensors with more than two dimensions are not available in this build")
+                apollo_items.append((p, g, st))
+                continue
             quant = st.get("is_quantized", False)
             if group.get("beta1") is not None:
                 m_fmt = "fp32" if "m" in st else st.get("m_quant_type", "uf8")
@@ -415,6 +423,136 @@ class Adafactor8Bit(Optimizer):
             self._run_fullrank(gi, group, key, items)
         for key, items in factored_items.items():
             self._run_factored(gi, group, key, items)
+        if apollo_items:
+            self._run_apollo(gi, group, apollo_items)
+
+    # ------------------------------------------------------------------
+    # APOLLO (optimizer.py:2557-3084)
+    # ------------------------------------------------------------------
+    @staticmethod
+    def _stable_randn(shape, seed, device):
+        gen = torch.Generator(device=device).manual_seed(int(seed))           # optimizer.py:139-149
+        return torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
+
+    @staticmethod
+    def _next_seed(seed, adv=0xF):
+        gen = torch.Generator().manual_seed(int(seed))                         # optimizer.py:152-155
+        return torch.randint(0, torch.iinfo(torch.int64).max, (adv,), generator=gen).tolist()[-1]
+
+    def _projection(self, state, shape, step, device, cache_proj):
+        """Transposed projection matrix of this step (_get_apollo_proj_matrix, optimizer.py:2557-2584)."""
+        rank = int(state["apollo_rank"])
+        gap = int(state["apollo_update_proj_gap"])
+        refresh = (step - int(state.get("last_proj_step", -gap))) >= gap
+        cached = state.get("apollo_proj_matrix_T") if cache_proj else state.get("_proj_T")
+        if not refresh and cached is not None:
+            return cached
+        if refresh:
+            state["current_proj_seed"] = int(state["apollo_seed"])
+            state["apollo_seed"] = self._next_seed(state["current_proj_seed"])
+            state["last_proj_step"] = step
+        R, C = shape
+        m_shape = (rank, C) if R >= C else (R, rank)
+        seed = state.get("current_proj_seed", state["apollo_seed"])
+        rng_dev = APOLLO_RNG_DEVICE if APOLLO_RNG_DEVICE is not None else device
+        proj = self._stable_randn(m_shape, seed, rng_dev) / math.sqrt(rank)
+        proj_t = proj.T.contiguous().to(device)
+        if cache_proj:
+            state["apollo_proj_matrix_T"] = proj_t
+        else:
+            state["_proj_T"] = proj_t      # same values the reference would regenerate each step
+        return proj_t
+
+    def _run_apollo(self, gi, group, items):
+        if group["scale_parameter"]:
+            raise NotImplementedError("APOLLO with scale_parameter=True is not available in this build")
+        if group.get("apollo_factorize", False) or group.get("beta3") is not None:
+            raise NotImplementedError("apollo_factorize and APOLLO+CAME are not available in this build")
+        rank = int(group["apollo_rank"])
+        beta1, beta2 = group.get("beta1"), group["beta2"]
+        block = group.get("block_size", 2048)
+        m_block = group.get("m_block_size", 256)
+        device = items[0][0].device
+        quant0 = items[0][2].get("is_quantized", False)
+        v_fmt = items[0][2].get("v_quant_type", "al8") if quant0 else "fp32"
+        m_fmt = ((items[0][2].get("m_quant_type", "uf8") if quant0 else "fp32") if beta1 is not None else None)
+        if v_fmt == "fp32" or m_fmt == "fp32":
+            raise NotImplementedError("APOLLO with fp32 low-rank states is not available in this build")
+        ids = tuple(id(p) for p, _, _ in items)
+        pkey = (gi, "apollo", items[0][1].dtype, v_fmt, m_fmt, rank, bool(group["maximize"]))
+        plan = self._plans.get(pkey)
+        first_flags, pts, per_tensor, grads = [], [], [], []
+        apollo_eps = group.get("apollo_eps", 1e-6)
+        # low-rank states are created on the tensor's first step (optimizer.py:2763-2779, 2916-2917)
+        for p, g, st in items:
+            quant = st.get("is_quantized", False)
+            if quant != quant0:
+                raise NotImplementedError("APOLLO tensors of one group must share the quantisation setting")
+            R, C = p.shape
+            nl = max(R, C) * rank
+            first = st.get("v_low_q") is None and st.get("v_low") is None
+            first_flags.append(first)
+            if first:
+                tmp = {}
+                _new_al_state(tmp, "v_low", (nl,), st.get("block_size", block), p.device, v_fmt)
+                for k in ("v_low_q", "v_low_scale", "v_low_min_log", "v_low_shape", "v_low_pad", "v_low"):
+                    if k in tmp:
+                        st[k] = tmp[k]
+                if v_fmt != "fp32":
+                    st["v_low_shape"] = torch.Size([nl])
+            if beta1 is not None and st.get("m_low_q") is None and st.get("m_low") is None:
+                tmp = {}
+                _new_m_state(tmp, nl, st.get("m_block_size", m_block), m_fmt, p.device, (nl,), prefix="m_low")
+                tmp.pop("m_quant_type", None)
+                st.update(tmp)
+        if plan is None or plan.ids != ids:
+            plan = ApolloPlan(device, items[0][1].dtype, v_fmt, m_fmt, block, m_block, group["maximize"],
+                              [p for p, _, _ in items], [s for _, _, s in items], rank)
+            plan.ids = ids
+            self._plans[pkey] = plan
+        step_any = None
+        for p, g, st in items:
+            step = st["step"] + 1
+            st["step"] = step
+            step_any = step
+            sc = self._step_scalars(group, step)
+            R, C = p.shape
+            pts.append(self._projection(st, (R, C), step, p.device, group.get("apollo_cache_proj", False)))
+            alpha = sc["rho"]
+            wd = group["weight_decay"]
+            decay = f32(f32(1.0) - f32(alpha * f32(wd))) if wd != 0 else f32(1.0)      # optimizer.py:3007-3009
+            t = dict(alpha=alpha, bc=1.0, bc_mode=0, d=f32(group["d"]), clip_div=f32(math.sqrt(R * C) * group["d"]),
+                     fira_margin1=f32(1.0 + group.get("fira_margin", 0.01)),
+                     sqrt_scale=f32(math.sqrt(group.get("apollo_scale", 1.0))),
+                     fira=bool(group.get("enable_fira_for_apollo", True)),
+                     scale_tensor=group.get("apollo_scale_type", "channel") == "tensor",
+                     scale_front=bool(group.get("apollo_scale_front", False)), decay=decay, has_decay=wd != 0)
+            if beta1 is not None and not group["relative_step"]:                       # optimizer.py:3015-3023
+                apply_bc = True if group.get("bias_correction") is None else group["bias_correction"]
+                if apply_bc:
+                    bc1 = 1.0 - beta1 ** step
+                    if beta2 is not None:
+                        t["bc"], t["bc_mode"] = f32(math.sqrt(1.0 - beta2 ** step) / bc1), 1
+                    else:
+                        t["bc"], t["bc_mode"] = f32(bc1), 2
+            if t["fira"]:
+                prev = st.get("scaled_grad_norm_prev")
+                t["fira_has_prev"] = prev is not None
+                if prev is None:
+                    prev = torch.zeros((), dtype=torch.float32, device=p.device)
+                    st["scaled_grad_norm_prev"] = prev
+                t["fira_prev"] = prev
+            else:
+                t["fira_has_prev"] = False
+            per_tensor.append(t)
+            grads.append(g if g.is_contiguous() else g.contiguous())
+        sc = self._step_scalars(group, step_any)
+        bv = sc["beta_val"]
+        low = dict(v_w=f32(bv), v_keep=f32(1.0 - bv), m_w=f32(1.0 - beta1) if beta1 is not None else f32(0.0),
+                   apollo_eps=f32(apollo_eps))
+        floor_later = math.log2(max(apollo_eps * apollo_eps, _FLOOR))                  # optimizer.py:2766-2767
+        with torch.cuda.device(device):
+            plan.run(grads, pts, per_tensor, low, first_flags, floor_later)
 
     def _scale_inputs(self, group, n):
         scale = {k: np.zeros(n, dtype=f32) for k in ("rho", "eps2", "bc", "weight_decay")}

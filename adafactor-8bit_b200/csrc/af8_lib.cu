@@ -8,6 +8,7 @@
 #include "codec.cuh"
 #include "scale.cuh"
 #include "factored.cuh"
+#include "apollo.cuh"
 #include "noalloc.cuh"
 
 extern "C" int af8_version(void) { return AF8_VERSION; }

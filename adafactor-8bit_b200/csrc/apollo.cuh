@@ -1,0 +1,355 @@
+// APOLLO: Adam statistics kept in a randomly projected low-rank space, applied to
+// the full gradient through per-channel (or per-tensor) scaling factors.
+//
+// Reference semantics: _update_param_apollo without factorisation and without
+// CAME (optimizer.py:2587-3084).  The step of one tensor G (rows x cols) is
+//   1. g_low = G @ Pt ("right", rows >= cols, Pt is cols x rank) or Pt @ G
+//      ("left", Pt is rank x rows)                        optimizer.py:2678-2681
+//   2. EMA + requantisation of the low-rank V (AL) and M (UF/dynamic) states
+//      over the flattened g_low, update_low = m / (sqrt(v) + eps)
+//                                                         optimizer.py:2763-2959
+//   3. scaling factor per channel = ||update_low|| / (||g_low|| + 1e-8), global
+//      norm sqrt(sum ||G_channel||^2 * factor^2)          optimizer.py:2961-2988
+//   4. Fira limiter on that norm, clip, bias correction   optimizer.py:2990-3023
+//   5. p = p*decay + (update_scale * G) * final_scale      optimizer.py:3073-3079
+// Step 2 is the full-rank kernel run on g_low (its "parameter" output, with decay
+// 0 and step 1, is update_low); this file holds steps 1, 3, 4 and 5.
+#pragma once
+
+#include "common.cuh"
+#include "fullrank_fast.cuh"
+
+namespace af8 {
+
+// gradient element with the reference's nan_to_num and maximize handling
+// (optimizer.py:2601-2606)
+__device__ __forceinline__ float apollo_grad(const void *g, int dtype, int64_t i, int negate)
+{
+    float x = dtype == AF8_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t *>(g)[i]) : static_cast<const float *>(g)[i];
+    if (!isfinite(x)) x = 0.0f;
+    return negate ? -x : x;
+}
+
+// ---------------------------------------------------------------------------
+// 1. projection: C[M x N] = A[M x K] * B[K x N], A or B being the gradient.
+//    Register-tiled SIMT kernel: 64 x 64 tile per CTA, 4 x 4 per thread, K step 16.
+//    Products of two binary32 numbers are exact in binary64 and the accumulation runs in
+//    binary64, so every output is the correctly rounded dot product whatever the order of
+//    summation: the low-rank states that are quantised from it do not depend on tiling.
+//    (A tensor-core version with a three-term bf16 split of Pt is the faster route for
+//    bf16 gradients; its binary32 accumulation moves codes next to a block minimum.)
+// ---------------------------------------------------------------------------
+constexpr int PJ_TM = 64, PJ_TN = 64, PJ_TK = 16;
+
+// GRAD_IS_A: A is the gradient (right side: A = G, B = Pt); else B is the gradient (left: A = Pt, B = G)
+template <bool GRAD_IS_A>
+__global__ void __launch_bounds__(256)
+apollo_project_kernel(const void *grad, int grad_dtype, int negate, const float *pt, float *out, int M, int N, int K)
+{
+    __shared__ float sA[PJ_TK][PJ_TM + 1];
+    __shared__ float sB[PJ_TK][PJ_TN + 1];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * PJ_TM, n0 = blockIdx.x * PJ_TN;
+    double acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
+
+    for (int k0 = 0; k0 < K; k0 += PJ_TK) {
+        // A tile: 64 rows x 16 k; B tile: 16 k x 64 cols (1024 elements each, 4 per thread)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int idx = tid + e * 256;
+            {   // A[m][k], row-major M x K
+                const int mm = idx / PJ_TK, kk = idx % PJ_TK;
+                const int m = m0 + mm, k = k0 + kk;
+                float v = 0.0f;
+                if (m < M && k < K)
+                    v = GRAD_IS_A ? apollo_grad(grad, grad_dtype, (int64_t)m * K + k, negate) : pt[(int64_t)m * K + k];
+                sA[kk][mm] = v;
+            }
+            {   // B[k][n], row-major K x N
+                const int kk = idx / PJ_TN, nn = idx % PJ_TN;
+                const int k = k0 + kk, n = n0 + nn;
+                float v = 0.0f;
+                if (k < K && n < N)
+                    v = GRAD_IS_A ? pt[(int64_t)k * N + n] : apollo_grad(grad, grad_dtype, (int64_t)k * N + n, negate);
+                sB[kk][nn] = v;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < PJ_TK; ++kk) {
+            double a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = (double)sA[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = (double)sB[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+            if (m < M && n < N) out[(int64_t)m * N + n] = __double2float_rn(acc[i][j]);
+        }
+}
+
+// squared channel norms of G in binary64: per row (right) or per column (left)
+__global__ void __launch_bounds__(256)
+apollo_channel_sumsq_kernel(const void *grad, int grad_dtype, int64_t rows, int64_t cols, int right, double *chan)
+{
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (right) {
+        for (int64_t r = (int64_t)blockIdx.x * 8 + warp; r < rows; r += (int64_t)gridDim.x * 8) {
+            double a = 0.0;
+            for (int64_t c = lane; c < cols; c += 32) {
+                const float x = apollo_grad(grad, grad_dtype, r * cols + c, 0);
+                a += (double)__fmul_rn(x, x);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            if (lane == 0) chan[r] = a;
+        }
+    } else {
+        // one thread per column, a block of rows per CTA, combined with binary64 atomics
+        const int64_t c = (int64_t)blockIdx.x * 256 + tid;
+        const int64_t r0 = (int64_t)blockIdx.y * 256;
+        if (c < cols) {
+            double a = 0.0;
+            const int64_t r1 = min(rows, r0 + 256);
+            for (int64_t r = r0; r < r1; ++r) {
+                const float x = apollo_grad(grad, grad_dtype, r * cols + c, 0);
+                a += (double)__fmul_rn(x, x);
+            }
+            atomicAdd(chan + c, a);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// 3. scaling factors and the global norm
+// ---------------------------------------------------------------------------
+// One warp per channel: ||update_low|| / (||g_low|| + 1e-8) over the channel's `rank`
+// entries (contiguous for "right", stride cols for "left"), then sum of ||G_ch||^2 * sf^2.
+__global__ void __launch_bounds__(256)
+apollo_scales_kernel(const float *upd, const float *g_low, const double *chan_g2, int64_t nch, int64_t rank,
+                     int right, int front, float sqrt_scale, float *sf, double *total)
+{
+    __shared__ double s_part[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    double local = 0.0;
+    for (int64_t ch = (int64_t)blockIdx.x * 8 + warp; ch < nch; ch += (int64_t)gridDim.x * 8) {
+        double nu = 0.0, ng = 0.0;
+        for (int64_t k = lane; k < rank; k += 32) {
+            const int64_t idx = right ? ch * rank + k : k * nch + ch;
+            const float u = upd[idx], g = g_low[idx];
+            nu += (double)__fmul_rn(u, u);
+            ng += (double)__fmul_rn(g, g);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            nu += __shfl_xor_sync(0xffffffffu, nu, o);
+            ng += __shfl_xor_sync(0xffffffffu, ng, o);
+        }
+        if (lane == 0) {
+            float s = __fdiv_rn(__double2float_rn(sqrt(nu)), __fadd_rn(__double2float_rn(sqrt(ng)), 1e-8f));   // optimizer.py:2964
+            if (front) s = __fmul_rn(s, sqrt_scale);                       // optimizer.py:2969-2971
+            sf[ch] = s;
+            const float nG = __double2float_rn(sqrt(chan_g2[ch]));
+            local += (double)__fmul_rn(__fmul_rn(nG, nG), __fmul_rn(s, s));   // optimizer.py:2975-2982
+        }
+    }
+    if (lane == 0) s_part[warp] = local;
+    __syncthreads();
+    if (tid == 0) {
+        double s = 0.0;
+        for (int w = 0; w < 8; ++w) s += s_part[w];
+        atomicAdd(total, s);
+    }
+}
+
+// tensor-wide scaling (apollo_scale_type == "tensor", optimizer.py:2966, 2984-2988):
+// sums[0..2] hold sum(update_low^2), sum(g_low^2), sum(G^2)
+__global__ void __launch_bounds__(256)
+apollo_tensor_sums_kernel(const float *upd, const float *g_low, int64_t nl, const double *chan_g2, int64_t nch, double *sums)
+{
+    __shared__ double s_part[3][8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    double a = 0.0, b = 0.0, c = 0.0;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + tid; i < nl; i += (int64_t)gridDim.x * 256) {
+        a += (double)__fmul_rn(upd[i], upd[i]);
+        b += (double)__fmul_rn(g_low[i], g_low[i]);
+    }
+    for (int64_t i = (int64_t)blockIdx.x * 256 + tid; i < nch; i += (int64_t)gridDim.x * 256) c += chan_g2[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+        c += __shfl_xor_sync(0xffffffffu, c, o);
+    }
+    if (lane == 0) { s_part[0][warp] = a; s_part[1][warp] = b; s_part[2][warp] = c; }
+    __syncthreads();
+    if (tid < 3) {
+        double s = 0.0;
+        for (int w = 0; w < 8; ++w) s += s_part[tid][w];
+        atomicAdd(sums + tid, s);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// 4. scalar chain of one tensor (one thread)
+// ---------------------------------------------------------------------------
+__global__ void apollo_finalize_kernel(const af8_apollo_scalars_in in, const double *sums, float *sf_tensor,
+                                       float *fira_prev, af8_apollo_scalars *out)
+{
+    float norm, s_tensor = 0.0f;
+    if (in.scale_tensor) {
+        s_tensor = __fdiv_rn(__double2float_rn(sqrt(sums[0])), __fadd_rn(__double2float_rn(sqrt(sums[1])), 1e-8f));
+        if (in.scale_front) s_tensor = __fmul_rn(s_tensor, in.sqrt_scale);
+        norm = __fmul_rn(__double2float_rn(sqrt(sums[2])), s_tensor);       // optimizer.py:2988
+        *sf_tensor = s_tensor;
+    } else {
+        norm = __fsqrt_rn(__double2float_rn(sums[0]));                      // optimizer.py:2982
+    }
+    float fs = 1.0f;
+    if (in.fira) {                                                          // optimizer.py:760-782, 2990-2994
+        float nn = isfinite(norm) ? norm : 0.0f;
+        if (in.fira_has_prev) {
+            const float fp = *fira_prev;
+            const bool reset = fp < 1e-6f;
+            const float ratio = __fdiv_rn(nn, __fadd_rn(fp, 1e-8f));
+            const float lim = __fdiv_rn(fmaxf(ratio, in.fira_margin1), in.fira_margin1);
+            fs = reset ? 1.0f : __frcp_rn(lim);
+            *fira_prev = reset ? nn : __fmul_rn(nn, fs);
+        } else {
+            *fira_prev = nn;
+        }
+    }
+    float denom = 1.0f;
+    if (in.d > 0.0f) {                                                      // optimizer.py:3003-3005
+        const float x = __fdiv_rn(norm, in.clip_div);
+        denom = (x >= 1.0f || isnan(x)) ? x : 1.0f;
+    }
+    float us = __fdiv_rn(-in.alpha, denom);                                 // optimizer.py:3013
+    if (in.bc_mode == 1) us = __fmul_rn(us, in.bc);                         // optimizer.py:3021
+    else if (in.bc_mode == 2) us = __fdiv_rn(us, in.bc);                    // optimizer.py:3023
+    out->update_scale = us;
+    out->fira = fs;
+    out->norm = norm;
+    out->reserved = 0.0f;
+}
+
+// ---------------------------------------------------------------------------
+// 5. apply: p = p*decay + (us*G) * final_scale[channel]
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, const float *sf,
+                    const af8_apollo_scalars *sc, int64_t rows, int64_t cols, int right, int scale_tensor,
+                    int fira, int front, float sqrt_scale, float decay, int has_decay)
+{
+    const float us = sc->update_scale, fs = sc->fira;
+    const int64_t n = rows * cols;
+    for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * 1024) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int64_t idx = i + e;
+            if (idx >= n) break;
+            const float g = apollo_grad(grad, grad_dtype, idx, negate);
+            float f = scale_tensor ? sf[0] : (right ? sf[idx / cols] : sf[idx % cols]);
+            if (fira) f = __fmul_rn(f, fs);                                  // optimizer.py:2994
+            if (!front) f = __fmul_rn(f, sqrt_scale);                        // optimizer.py:3000
+            float pv = param[idx];
+            if (has_decay) pv = __fmul_rn(pv, decay);                        // optimizer.py:3075
+            if (scale_tensor) pv = __fmaf_rn(__fmul_rn(us, f), g, pv);       // optimizer.py:3079
+            else pv = __fmaf_rn(__fmul_rn(us, g), f, pv);                    // optimizer.py:3077
+            param[idx] = pv;
+        }
+    }
+}
+
+}  // namespace af8
+
+extern "C" int af8_apollo_project(const void *grad, int32_t grad_dtype, int32_t negate, const float *pt,
+                                  int64_t rows, int64_t cols, int64_t rank, float *g_low, double *chan_g2,
+                                  void *stream)
+{
+    using namespace af8;
+    if (!grad || !pt || !g_low || !chan_g2) return fail(AF8_ERR_INVALID, "af8_apollo_project: null argument");
+    if (rows <= 0 || cols <= 0 || rank <= 0 || rows >= (1 << 30) || cols >= (1 << 30) || rank > 4096)
+        return fail(AF8_ERR_INVALID, "af8_apollo_project: bad shape %lld x %lld, rank %lld", (long long)rows, (long long)cols, (long long)rank);
+    if (grad_dtype != AF8_F32 && grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_project: gradients must be fp32 or bf16");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int right = rows >= cols;
+    if (right) {
+        dim3 grid((unsigned)((rank + PJ_TN - 1) / PJ_TN), (unsigned)((rows + PJ_TM - 1) / PJ_TM));
+        apollo_project_kernel<true><<<grid, 256, 0, st>>>(grad, grad_dtype, negate, pt, g_low, (int)rows, (int)rank, (int)cols);
+    } else {
+        dim3 grid((unsigned)((cols + PJ_TN - 1) / PJ_TN), (unsigned)((rank + PJ_TM - 1) / PJ_TM));
+        apollo_project_kernel<false><<<grid, 256, 0, st>>>(grad, grad_dtype, negate, pt, g_low, (int)rank, (int)cols, (int)rows);
+    }
+    AF8_CUDA_TRY(cudaGetLastError());
+    if (right) {
+        int64_t g = (rows + 7) / 8;
+        if (g > 148 * 16) g = 148 * 16;
+        apollo_channel_sumsq_kernel<<<(int)g, 256, 0, st>>>(grad, grad_dtype, rows, cols, 1, chan_g2);
+    } else {
+        AF8_CUDA_TRY(cudaMemsetAsync(chan_g2, 0, sizeof(double) * (size_t)cols, st));
+        dim3 grid((unsigned)((cols + 255) / 256), (unsigned)((rows + 255) / 256));
+        apollo_channel_sumsq_kernel<<<grid, 256, 0, st>>>(grad, grad_dtype, rows, cols, 0, chan_g2);
+    }
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+extern "C" int af8_apollo_scales(const float *upd, const float *g_low, const double *chan_g2, int64_t rows,
+                                 int64_t cols, int64_t rank, const af8_apollo_scalars_in *in, float *sf,
+                                 double *sums, float *fira_prev, af8_apollo_scalars *out, void *stream)
+{
+    using namespace af8;
+    if (!upd || !g_low || !chan_g2 || !in || !sf || !sums || !out) return fail(AF8_ERR_INVALID, "af8_apollo_scales: null argument");
+    if (in->fira && !fira_prev) return fail(AF8_ERR_INVALID, "af8_apollo_scales: the limiter needs fira_prev");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int right = rows >= cols;
+    const int64_t nch = right ? rows : cols;
+    AF8_CUDA_TRY(cudaMemsetAsync(sums, 0, sizeof(double) * 3, st));
+    if (in->scale_tensor) {
+        const int64_t nl = nch * rank;
+        int64_t g = (nl + 255) / 256;
+        if (g > 148 * 8) g = 148 * 8;
+        apollo_tensor_sums_kernel<<<(int)g, 256, 0, st>>>(upd, g_low, nl, chan_g2, nch, sums);
+    } else {
+        int64_t g = (nch + 7) / 8;
+        if (g > 148 * 16) g = 148 * 16;
+        apollo_scales_kernel<<<(int)g, 256, 0, st>>>(upd, g_low, chan_g2, nch, rank, right, in->scale_front, in->sqrt_scale, sf, sums);
+    }
+    AF8_CUDA_TRY(cudaGetLastError());
+    apollo_finalize_kernel<<<1, 1, 0, st>>>(*in, sums, sf, fira_prev, out);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+extern "C" int af8_apollo_apply(void *param, const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
+                                const af8_apollo_scalars *scalars, int64_t rows, int64_t cols,
+                                const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *stream)
+{
+    using namespace af8;
+    if (!param || !grad || !sf || !scalars || !in) return fail(AF8_ERR_INVALID, "af8_apollo_apply: null argument");
+    if (grad_dtype != AF8_F32 && grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_apply: gradients must be fp32 or bf16");
+    const int64_t n = rows * cols;
+    int64_t g = (n + 1023) / 1024;
+    if (g > 148 * 16) g = 148 * 16;
+    apollo_apply_kernel<<<(int)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<float *>(param), grad, grad_dtype, negate, sf, scalars, rows, cols, rows >= cols ? 1 : 0,
+        in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}

@@ -310,6 +310,62 @@ AF8_API int af8_factored_update(const af8_factored_cfg *cfg, const af8_factored_
                                 double *block_sumsq, void *stream);
 
 /* ------------------------------------------------------------------------ */
+/* APOLLO: low-rank projected statistics                                     */
+/* ------------------------------------------------------------------------ */
+
+/* Host scalars of one tensor's APOLLO step (optimizer.py:2990-3023). */
+typedef struct af8_apollo_scalars_in {
+    float alpha;            /* alpha_t */
+    float bc;               /* float(sqrt(bc2)/bc1) (bc_mode 1) or float(bc1) (bc_mode 2) */
+    float d;                /* clip threshold, 0 disables */
+    float clip_div;         /* float(sqrt(numel)*d) */
+    float fira_margin1;     /* float(1 + fira_margin) */
+    float sqrt_scale;       /* float(sqrt(apollo_scale)) */
+    int32_t bc_mode;        /* 0 none, 1 multiply, 2 divide */
+    int32_t fira;           /* enable_fira_for_apollo */
+    int32_t fira_has_prev;  /* 0 on the tensor's first limited step */
+    int32_t scale_tensor;   /* apollo_scale_type == "tensor" */
+    int32_t scale_front;    /* apollo_scale_front */
+    int32_t reserved;
+} af8_apollo_scalars_in;
+
+/* Device scalars produced by af8_apollo_scales and consumed by af8_apollo_apply. */
+typedef struct af8_apollo_scalars {
+    float update_scale;     /* -alpha/denom with bias correction */
+    float fira;             /* Fira scale */
+    float norm;             /* the global norm that was limited */
+    float reserved;
+} af8_apollo_scalars;
+
+/* g_low = G @ Pt (rows >= cols; Pt is cols x rank, g_low rows x rank) or Pt @ G
+ * (Pt is rank x rows, g_low rank x cols), every output being the correctly
+ * rounded dot product, and chan_g2 = squared norm of every channel of G (rows
+ * when rows >= cols, else columns) in binary64.  Non-finite gradient entries
+ * count as zero (optimizer.py:2606).
+ * Replaces torch.matmul (optimizer.py:2678-2681) and the channel norms
+ * (optimizer.py:2975-2979). */
+AF8_API int af8_apollo_project(const void *grad, int32_t grad_dtype, int32_t negate, const float *pt,
+                               int64_t rows, int64_t cols, int64_t rank, float *g_low, double *chan_g2,
+                               void *stream);
+
+/* Scaling factors sf[channel] = ||update_low|| / (||g_low|| + 1e-8) (one entry
+ * for the tensor-wide variant), the global norm, the Fira limiter, the clip
+ * and the bias correction.  sums: 3 doubles of scratch.  fira_prev: device
+ * scalar of the state key "scaled_grad_norm_prev".
+ * Replaces compute_apollo_norms (kernels.cu:2441-2453), fira_scalar and the
+ * torch glue of optimizer.py:2961-3023. */
+AF8_API int af8_apollo_scales(const float *upd, const float *g_low, const double *chan_g2, int64_t rows,
+                              int64_t cols, int64_t rank, const af8_apollo_scalars_in *in, float *sf,
+                              double *sums, float *fira_prev, af8_apollo_scalars *out, void *stream);
+
+/* p = p*decay + (update_scale * G) * (sf[channel] * fira * sqrt_scale) for fp32
+ * parameters.  Replaces the apollo_apply_* kernels (kernels.cu:2834-3000) and the
+ * torch mul_/addcmul_ write-back (optimizer.py:3073-3079). */
+AF8_API int af8_apollo_apply(void *param, const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
+                             const af8_apollo_scalars *scalars, int64_t rows, int64_t cols,
+                             const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *stream);
+
+/* ------------------------------------------------------------------------ */
 /* Step without caller-provided working memory                               */
 /* ------------------------------------------------------------------------ */
 

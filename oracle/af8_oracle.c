@@ -760,3 +760,167 @@ AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void
     free(g); free(u); free(rmean); free(cmean); free(row); free(col); free(inv_r); free(inv_c);
     return rc;
 }
+
+/* ------------------------------------------------------------------ */
+/* APOLLO: low-rank projected Adam statistics, channel-wise scaling     */
+/* ------------------------------------------------------------------ */
+typedef struct {
+    int64_t rows, cols, rank;
+    int64_t block, m_block;
+    int32_t grad_dtype;
+    int32_t v_fmt;          /* AF8O_V_* of v_low */
+    int32_t m_fmt;          /* AF8O_M_* of m_low; NONE when beta1 is None */
+    int32_t negate_grad;
+    int32_t first_step;     /* v_low does not exist yet (optimizer.py:2763) */
+    int32_t scale_tensor;   /* apollo_scale_type == "tensor" */
+    int32_t scale_front;
+    int32_t fira;
+    int32_t has_decay;
+    float decay;
+    float alpha;            /* alpha_t */
+    float bc;               /* float(sqrt(bc2)/bc1), or bc1 when bc_mode == 2 */
+    int32_t bc_mode;        /* 0 none, 1 multiply, 2 divide (optimizer.py:3015-3023) */
+    float v_w;              /* beta_val */
+    float m_w;              /* float(1 - beta1) */
+    float apollo_eps;
+    float sqrt_scale;       /* float(sqrt(apollo_scale)) */
+    float d;
+    float clip_div;         /* float(sqrt(numel)*d) */
+    float fira_margin1;
+    float v_floor_first;    /* -126 */
+    float v_floor_later;    /* log2(max(apollo_eps^2, FLT_MIN)) (optimizer.py:2766-2767) */
+} af8o_apollo_cfg;
+
+/* _update_param_apollo without factorisation and without CAME
+ * (optimizer.py:2587-3084): projection (2678-2681), low-rank V (2763-2799) and M
+ * (2906-2953) states, update_low (2959), scaling factor (2961-2966), global norm
+ * (2973-2988), Fira (2990-2996), write-back for fp32 parameters (3073-3079).
+ * pt is proj_matrix_T: (cols, rank) when rows >= cols ("right"), else (rank, rows). */
+AF8O_API int af8o_apollo_step(const af8o_apollo_cfg *c, float *p, const void *grad, const float *pt,
+                              void *v_q, float *v_scale, float *v_min_log, float *v_f32,
+                              uint8_t *m_q, float *m_scale, float *m_f32, const float *map,
+                              int *fira_has_prev, float *fira_prev, float *norm_out)
+{
+    const int64_t R = c->rows, C = c->cols, r = c->rank, n = R * C;
+    const int right = R >= C;                                /* optimizer.py:2662 */
+    const int64_t LR = right ? R : r, LC = right ? r : C, nl = LR * LC;
+    const int has_m = c->m_fmt != AF8O_M_NONE;
+    const int m_quant = has_m && c->m_fmt != AF8O_M_FP32;
+    const int v_quant = c->v_fmt != AF8O_V_FP32;
+    float *G = (float *)malloc((size_t)n * sizeof(float));
+    float *gl = (float *)malloc((size_t)nl * sizeof(float));
+    float *v = (float *)malloc((size_t)nl * sizeof(float));
+    float *m = (float *)malloc((size_t)nl * sizeof(float));
+    const int64_t nch = right ? R : C;                       /* channels */
+    float *sf = (float *)malloc((size_t)nch * sizeof(float));
+    if (!G || !gl || !v || !m || !sf) return 2;
+
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {                        /* optimizer.py:2601-2606 */
+        float x = load_grad(grad, c->grad_dtype, i, c->negate_grad);
+        G[i] = isfinite(x) ? x : 0.0f;
+    }
+    /* optimizer.py:2678-2681, binary64 accumulation */
+    if (right) {
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < R; ++i)
+            for (int64_t k = 0; k < r; ++k) {
+                double a = 0.0;
+                for (int64_t j = 0; j < C; ++j) a += (double)G[i * C + j] * (double)pt[j * r + k];
+                gl[i * r + k] = (float)a;
+            }
+    } else {
+#pragma omp parallel for schedule(static)
+        for (int64_t k = 0; k < r; ++k)
+            for (int64_t j = 0; j < C; ++j) {
+                double a = 0.0;
+                for (int64_t i = 0; i < R; ++i) a += (double)pt[k * R + i] * (double)G[i * C + j];
+                gl[k * C + j] = (float)a;
+            }
+    }
+    /* low-rank second moment */
+    if (c->first_step) {                                     /* optimizer.py:2770-2779 */
+        for (int64_t i = 0; i < nl; ++i) { float t = gl[i] * gl[i]; v[i] = t * c->v_w; }
+        if (v_quant) af8o_al_quantize(v, nl, c->block, c->v_floor_first, c->v_fmt, v_q, v_scale, v_min_log);
+        else memcpy(v_f32, v, (size_t)nl * sizeof(float));
+    } else if (v_quant) {                                    /* optimizer.py:2788-2795 */
+        af8o_al_dequantize(v_q, v_scale, v_min_log, nl, c->block, c->v_fmt, v);
+        for (int64_t i = 0; i < nl; ++i) v[i] = lerp_t(v[i], gl[i] * gl[i], c->v_w);
+        af8o_al_quantize(v, nl, c->block, c->v_floor_later, c->v_fmt, v_q, v_scale, v_min_log);
+    } else {                                                 /* optimizer.py:2797-2799 */
+        for (int64_t i = 0; i < nl; ++i) { v_f32[i] = lerp_t(v_f32[i], gl[i] * gl[i], c->v_w); v[i] = v_f32[i]; }
+    }
+    /* low-rank momentum and update_low (optimizer.py:2906-2959) */
+    int rc = 0;
+    if (has_m) {
+        if (m_quant) {
+            af8o_m_dequantize(m_q, m_scale, nl, c->m_block, c->m_fmt, map, m);
+            for (int64_t i = 0; i < nl; ++i) m[i] = lerp_t(m[i], gl[i], c->m_w);
+            rc = af8o_m_quantize(m, nl, c->m_block, c->m_fmt, map, m_q, m_scale);
+        } else {
+            for (int64_t i = 0; i < nl; ++i) { m_f32[i] = lerp_t(m_f32[i], gl[i], c->m_w); m[i] = m_f32[i]; }
+        }
+    } else {
+        memcpy(m, gl, (size_t)nl * sizeof(float));
+    }
+    for (int64_t i = 0; i < nl; ++i) m[i] = m[i] / (sqrtf(v[i]) + c->apollo_eps);   /* update_low in m */
+
+    /* scaling factor (optimizer.py:2961-2966) and squared channel norms of G (2975-2979) */
+    double total = 0.0;
+    float norm_unscaled = 0.0f;
+    if (!c->scale_tensor) {
+        for (int64_t ch = 0; ch < nch; ++ch) {
+            double nu = 0.0, ng = 0.0, nG = 0.0;
+            if (right) {
+                for (int64_t k = 0; k < r; ++k) { nu += (double)m[ch * r + k] * m[ch * r + k]; ng += (double)gl[ch * r + k] * gl[ch * r + k]; }
+                for (int64_t j = 0; j < C; ++j) nG += (double)G[ch * C + j] * G[ch * C + j];
+            } else {
+                for (int64_t k = 0; k < r; ++k) { nu += (double)m[k * C + ch] * m[k * C + ch]; ng += (double)gl[k * C + ch] * gl[k * C + ch]; }
+                for (int64_t i = 0; i < R; ++i) nG += (double)G[i * C + ch] * G[i * C + ch];
+            }
+            float s = (float)sqrt(nu) / ((float)sqrt(ng) + 1e-8f);
+            if (c->scale_front) s = s * c->sqrt_scale;        /* optimizer.py:2969-2971 */
+            sf[ch] = s;
+            float nGf = (float)sqrt(nG);
+            float nG2 = nGf * nGf;                            /* vector_norm(...).square() */
+            float s2 = s * s;
+            total += (double)(nG2 * s2);
+        }
+        norm_unscaled = sqrtf((float)total);                  /* optimizer.py:2982 */
+    } else {
+        float s = norm2_f64(m, nl) / (norm2_f64(gl, nl) + 1e-8f);
+        if (c->scale_front) s = s * c->sqrt_scale;
+        for (int64_t ch = 0; ch < nch; ++ch) sf[ch] = s;
+        norm_unscaled = norm2_f64(G, n) * s;                  /* optimizer.py:2988 */
+    }
+    float fs = 1.0f;
+    if (c->fira) fs = af8o_fira_scale(norm_unscaled, c->fira_margin1, fira_has_prev, fira_prev);   /* optimizer.py:2990-2994 */
+    for (int64_t ch = 0; ch < nch; ++ch) {
+        float f = c->fira ? sf[ch] * fs : sf[ch];
+        if (!c->scale_front) f = f * c->sqrt_scale;           /* optimizer.py:2999-3000 */
+        sf[ch] = f;
+    }
+    float denom = 1.0f;
+    if (c->d > 0.0f) { denom = norm_unscaled / c->clip_div; if (denom < 1.0f) denom = 1.0f; }   /* optimizer.py:3003-3005 */
+    float us = -c->alpha / denom;                             /* optimizer.py:3013 */
+    if (c->bc_mode == 1) us = us * c->bc; else if (c->bc_mode == 2) us = us / c->bc;
+    /* fp32 parameters (optimizer.py:3074-3079) */
+    if (!c->scale_tensor) {
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float pv = c->has_decay ? p[i] * c->decay : p[i];
+            float f = right ? sf[i / C] : sf[i % C];
+            p[i] = fmaf(us * G[i], f, pv);
+        }
+    } else {
+        float a = us * sf[0];
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float pv = c->has_decay ? p[i] * c->decay : p[i];
+            p[i] = fmaf(a, G[i], pv);
+        }
+    }
+    if (norm_out) *norm_out = norm_unscaled;
+    free(G); free(gl); free(v); free(m); free(sf);
+    return rc;
+}

@@ -277,8 +277,10 @@ def init_state(shape, hp):
     c_fmt = cqt if use_quant else "fp32"
     m_fmt = hp["m_quant_type"] if use_quant else "fp32"
     if use_apollo:
-        st["apollo"] = True
-        st["m_quant_type"] = hp["m_quant_type"]
+        # optimizer.py:1726-1739; the seed is assigned by the caller in first-step order
+        gap = hp["apollo_update_proj_gap"]
+        st.update(apollo_seed=None, apollo_rank=hp["apollo_rank"], apollo_update_proj_gap=gap,
+                  last_proj_step=-gap, apollo_proj_matrix_T=None, m_quant_type=hp["m_quant_type"])
         return st
     if factored:
         R, C = shape[-2], shape[-1]
@@ -498,4 +500,137 @@ def factored_step(p, g, state, hp, sc=None):
         raise RuntimeError(f"af8o_factored_step failed with {rc}")
     if has_prev.value:
         state["fira_prev_norm"] = f32(prev.value)
+    return float(norm.value)
+
+
+# ---------------------------------------------------------------------------
+# APOLLO
+# ---------------------------------------------------------------------------
+class ApolloCfg(ctypes.Structure):
+    _fields_ = [
+        ("rows", c_l), ("cols", c_l), ("rank", c_l), ("block", c_l), ("m_block", c_l),
+        ("grad_dtype", c_i), ("v_fmt", c_i), ("m_fmt", c_i), ("negate_grad", c_i), ("first_step", c_i),
+        ("scale_tensor", c_i), ("scale_front", c_i), ("fira", c_i), ("has_decay", c_i),
+        ("decay", c_f), ("alpha", c_f), ("bc", c_f), ("bc_mode", c_i), ("v_w", c_f), ("m_w", c_f),
+        ("apollo_eps", c_f), ("sqrt_scale", c_f), ("d", c_f), ("clip_div", c_f), ("fira_margin1", c_f),
+        ("v_floor_first", c_f), ("v_floor_later", c_f),
+    ]
+
+
+def stable_randn(shape, seed):
+    """stable_randn on the CPU generator (optimizer.py:139-149)."""
+    import torch
+    gen = torch.Generator(device="cpu").manual_seed(int(seed))
+    return torch.randn(tuple(shape), generator=gen, device="cpu", dtype=torch.float32)
+
+
+def next_seed(seed, adv=0xF):
+    """next_seed (optimizer.py:152-155)."""
+    import torch
+    gen = torch.Generator().manual_seed(int(seed))
+    return torch.randint(0, torch.iinfo(torch.int64).max, (adv,), generator=gen).tolist()[-1]
+
+
+def apollo_projection(state, shape, step, rank, gap):
+    """_get_apollo_proj_matrix (optimizer.py:2557-2584) -> proj_matrix_T as a numpy array."""
+    last = int(state.get("last_proj_step", -gap))
+    refresh = (step - last) >= gap
+    if not refresh and state.get("apollo_proj_matrix_T") is not None:
+        return state["apollo_proj_matrix_T"]
+    if refresh:
+        state["current_proj_seed"] = int(state["apollo_seed"])
+        state["apollo_seed"] = next_seed(state["current_proj_seed"])
+        state["last_proj_step"] = step
+    R, C = shape
+    m_shape = (rank, C) if R >= C else (R, rank)
+    seed = state.get("current_proj_seed", state["apollo_seed"])
+    proj = stable_randn(m_shape, seed) / math.sqrt(rank)
+    pt = proj.T.contiguous().numpy().copy()
+    state["apollo_proj_matrix_T"] = pt
+    return pt
+
+
+def apollo_step(p, g, state, hp):
+    """_update_param_apollo (optimizer.py:2587-3084) for 2-D fp32 parameters, without
+    factorisation and without CAME."""
+    assert p.dtype == f32 and p.ndim == 2 and p.flags.c_contiguous
+    lib_ = lib()
+    if not hasattr(lib_, "_apollo_ready"):
+        lib_.af8o_apollo_step.argtypes = [ctypes.POINTER(ApolloCfg)] + [c_p] * 11 + [
+            ctypes.POINTER(c_i), ctypes.POINTER(c_f), ctypes.POINTER(c_f)]
+        lib_._apollo_ready = True
+    R, C = p.shape
+    n = R * C
+    rank = int(hp["apollo_rank"])
+    step = state["step"] + 1
+    state["step"] = step
+    beta1, beta2 = hp["beta1"], hp["beta2"]
+    beta_val = 1.0 - beta2 if beta2 is not None else math.pow(step, hp["beta2_decay"])
+    lr = hp["lr"]
+    rho = f32(min(lr, 1.0 / math.sqrt(step)) if hp["relative_step"] else lr)
+    if hp["scale_parameter"]:
+        rms = f32(lib_.af8o_norm2(_ptr(p), n)) / f32(math.sqrt(n))
+        alpha = f32(max(rms, f32(hp["eps"][1]))) * rho
+    else:
+        alpha = rho
+    pt = apollo_projection(state, (R, C), step, rank, int(hp["apollo_update_proj_gap"]))
+    g, gdt = _grad_args(g)
+    quant = state["is_quantized"]
+    vqt = state["v_quant_type"] if quant else "fp32"
+    has_m = beta1 is not None
+    mqt = (state.get("m_quant_type", "uf8") if quant else "fp32") if has_m else None
+    nl = max(R, C) * rank
+    block = state["block_size"]
+    m_block = state.get("m_block_size", hp["m_block_size"])
+    first = state.get("v_low_q") is None and state.get("v_low") is None
+    if first:
+        if vqt == "fp32":
+            state["v_low"] = np.zeros(nl, dtype=f32)
+        else:
+            _init_al(state, "v_low", nl, block, vqt)
+    if has_m and state.get("m_low_q") is None and state.get("m_low") is None:
+        _init_m(state, nl, m_block, mqt, prefix="m_low")
+    cfg = ApolloCfg()
+    cfg.rows, cfg.cols, cfg.rank, cfg.block, cfg.m_block = R, C, rank, block, m_block
+    cfg.grad_dtype, cfg.v_fmt, cfg.m_fmt = gdt, V_FMT[vqt], M_FMT[mqt]
+    cfg.negate_grad = int(bool(hp["maximize"]))
+    cfg.first_step = int(first)
+    cfg.scale_tensor = int(hp["apollo_scale_type"] == "tensor")
+    cfg.scale_front = int(bool(hp["apollo_scale_front"]))
+    cfg.fira = int(bool(hp["enable_fira_for_apollo"]))
+    wd = hp["weight_decay"]
+    cfg.has_decay = int(wd != 0)
+    mult = alpha if hp["scale_weight_decay"] else rho
+    cfg.decay = float(f32(f32(1.0) - f32(mult * f32(wd)))) if wd != 0 else 1.0
+    cfg.alpha = float(alpha)
+    cfg.bc_mode, cfg.bc = 0, 1.0
+    if has_m and not hp["relative_step"]:
+        apply_bc = True if hp["bias_correction"] is None else hp["bias_correction"]
+        if apply_bc:
+            bc1 = 1.0 - beta1 ** step
+            if beta2 is not None:
+                cfg.bc_mode, cfg.bc = 1, float(f32(math.sqrt(1.0 - beta2 ** step) / bc1))
+            else:
+                cfg.bc_mode, cfg.bc = 2, float(f32(bc1))
+    cfg.v_w = float(f32(beta_val))
+    cfg.m_w = float(f32(1.0 - beta1)) if has_m else 0.0
+    cfg.apollo_eps = float(f32(hp["apollo_eps"]))
+    cfg.sqrt_scale = float(f32(math.sqrt(hp["apollo_scale"])))
+    cfg.d = float(f32(hp["d"]))
+    cfg.clip_div = float(f32(math.sqrt(n) * hp["d"]))
+    cfg.fira_margin1 = float(f32(1.0 + hp["fira_margin"]))
+    cfg.v_floor_first = -126.0
+    cfg.v_floor_later = float(f32(math.log2(max(hp["apollo_eps"] * hp["apollo_eps"], LOG_QUANT_FLOOR))))
+    has_prev = c_i(1 if "scaled_grad_norm_prev" in state else 0)
+    prev = c_f(float(state.get("scaled_grad_norm_prev", 0.0)))
+    norm = c_f(-1.0)
+    rc = lib_.af8o_apollo_step(
+        ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), _ptr(pt),
+        _ptr(state.get("v_low_q")), _ptr(state.get("v_low_scale")), _ptr(state.get("v_low_min_log")),
+        _ptr(state.get("v_low")), _ptr(state.get("m_low_q")), _ptr(state.get("m_low_scale")), _ptr(state.get("m_low")),
+        _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev), ctypes.byref(norm))
+    if rc != 0:
+        raise RuntimeError(f"af8o_apollo_step failed with {rc}")
+    if has_prev.value:
+        state["scaled_grad_norm_prev"] = f32(prev.value)
     return float(norm.value)

@@ -22,6 +22,11 @@ class OracleRun:
         self.params0, self.grads = cases.case_inputs(name)
         self.params = [p.copy() for p in self.params0]
         self.states = [o.init_state(p.shape, self.hp) for p in self.params]
+        seed = 1                                 # optimizer-level counter (optimizer.py:1460, 1727-1728)
+        for st in self.states:
+            if "apollo_seed" in st:
+                st["apollo_seed"] = seed
+                seed += 1
         self.t = 0
 
     def step_param(self, i, p, g, st):
