@@ -57,6 +57,31 @@ WORKLOADS = {
         shapes=lambda: llama_shapes(22, 2048, 5632, 256, 32000), grad="bf16", bytes_per_param=14,
         hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
                 m_quant_type="uf8", v_quant_type="al8")),
+    # factored Adafactor, constructor defaults (relative step, parameter scaling, clip d=1),
+    # AL8 second moment in blocks of 256, no momentum: TinyLlama-1.1B
+    "tinyllama_adafactor": dict(
+        shapes=lambda: llama_shapes(22, 2048, 5632, 256, 32000), grad="bf16", bytes_per_param=10,
+        hp=dict(block_size=256)),
+    # CAME: UF8 momentum, AL16 second moment and confidence (block 2048): Llama-2-7B shapes
+    "llama2_7b_came": dict(
+        shapes=lambda: llama_shapes(32, 4096, 11008, 4096, 32000), grad="bf16", bytes_per_param=12,
+        hp=dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=0.9999, factored=True, relative_step=False,
+                scale_parameter=False, scale_weight_decay=False, d=1.0, eps_came=1e-16, lr=1e-4,
+                m_quant_type="uf8", v_quant_type="al16", c_quant_type="al16", block_size=2048)),
+    # APOLLO rank 256 on the attention / MLP matrices, AdamW-style fallback elsewhere: Llama-3-8B shapes
+    "llama3_8b_apollo": dict(
+        shapes=lambda: llama_shapes(32, 4096, 14336, 1024, 128256), grad="bf16", bytes_per_param=10,
+        apollo_targets=("q", "k", "v", "o", "gate", "up", "down"),
+        hp=dict(_ADAMW, eps=(1e-6, 1e-3), lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
+                m_quant_type="uf8", v_quant_type="al8", apollo_rank=256, apollo_update_proj_gap=200,
+                apollo_eps=1e-6, apollo_cache_proj=True, enable_fira_for_apollo=True)),
+    # the same optimizer on one Llama-3-8B layer (small case for tests and profiler captures)
+    "llama3_layer_apollo": dict(
+        shapes=lambda: llama_shapes(1, 4096, 14336, 1024, 128256)[1:-2], grad="bf16", bytes_per_param=10,
+        apollo_targets=("q", "k", "v", "o", "gate", "up", "down"),
+        hp=dict(_ADAMW, eps=(1e-6, 1e-3), lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
+                m_quant_type="uf8", v_quant_type="al8", apollo_rank=256, apollo_update_proj_gap=200,
+                apollo_eps=1e-6, apollo_cache_proj=True, enable_fira_for_apollo=True)),
     # one TinyLlama decoder layer (44 M parameters): the small case used for profiler captures
     "tinyllama_layer_adamw": dict(
         shapes=lambda: llama_shapes(1, 2048, 5632, 256, 32000)[1:-2], grad="bf16", bytes_per_param=14,
@@ -69,6 +94,21 @@ WORKLOADS = {
                 m_quant_type="uf8", v_quant_type="al8")),
 }
 DEFAULT_WORKLOAD = "tinyllama_adamw_fira"
+
+
+def make_groups(wl, named_params):
+    """Parameter groups of a workload: APOLLO workloads route the target matrices to the
+    low-rank path and everything else to the AdamW-style fallback (what the reference's
+    build_param_groups(preset="apollo") produces); the others use one group."""
+    targets = wl.get("apollo_targets")
+    if not targets:
+        return [dict(params=[p for _, p in named_params])]
+    main = [p for n, p in named_params if n in targets]
+    rest = [p for n, p in named_params if n not in targets]
+    groups = [dict(params=main)]
+    if rest:
+        groups.append(dict(params=rest, apollo_rank=0))
+    return groups
 
 
 def load_peaks():
@@ -146,7 +186,9 @@ def cpu_reference_run(workload, steps, warmup, budget_params=24_000_000):
     hp = o.hyper(**wl["hp"])
     shapes = wl["shapes"]()
     # sample: one of each distinct shape, in order, until the budget is spent
-    seen, sample, total = set(), [], 0
+    seen, sample, sample_names, total = set(), [], [], 0
+    if wl.get("apollo_targets"):
+        budget_params = min(budget_params, 6_000_000)      # the CPU projection costs 2*rank flops per parameter
     for name, shp in shapes:
         if shp in seen:
             continue
@@ -159,16 +201,31 @@ def cpu_reference_run(workload, steps, warmup, budget_params=24_000_000):
         if n == 0 or total + n > budget_params * 1.05:
             continue
         sample.append(shp)
+        sample_names.append(name)
         total += n
     spec = dict(dist="rowscale", std=1e-3, zero_frac=0.005, dtype="bf16" if wl["grad"] == "bf16" else "f32")
     params = [cases.make_param(s, 100 + i) for i, s in enumerate(sample)]
-    states = [o.init_state(s, hp) for s in sample]
+    targets = wl.get("apollo_targets")
+    hps = [hp if (not targets or nm in targets) else dict(hp, apollo_rank=0) for nm in sample_names]
+    states = [o.init_state(s, h) for s, h in zip(sample, hps)]
+    for k, st in enumerate(states):
+        if "apollo_seed" in st:
+            st["apollo_seed"] = k + 1
     grads = [cases.make_grad(s, 200 + i, 1, spec) for i, s in enumerate(sample)]
+
+    def one(p, g, st, h):
+        if h["apollo_rank"] > 0 and p.ndim == 2:
+            o.apollo_step(p, g, st, h)
+        elif p.ndim == 2 and h["factored"]:
+            o.factored_step(p, g, st, h)
+        else:
+            o.fullrank_step(p.reshape(-1), g.reshape(-1), st, h)
+
     times = []
     for it in range(warmup + steps):
         t0 = time.perf_counter()
-        for p, g, st in zip(params, grads, states):
-            o.fullrank_step(p.reshape(-1), g.reshape(-1), st, hp)
+        for p, g, st, h in zip(params, grads, states, hps):
+            one(p, g, st, h)
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
@@ -217,7 +274,7 @@ def make_grad_set(torch, shapes, dtype, seed, device):
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
-    from adafactor8bit import Adafactor8Bit, _engine
+    from adafactor8bit import Adafactor8Bit, ShardedAdafactor8Bit, _engine
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -230,23 +287,32 @@ def run_gpu_arm(args):
     wl = WORKLOADS[args.workload]
     shapes = wl["shapes"]()
     gdtype = torch.bfloat16 if wl["grad"] == "bf16" else torch.float32
-    if world > 1:
-        # replicas only at this stage: every rank steps the full parameter set
-        pass
     gen = torch.Generator(device=device).manual_seed(1234)
-    params = []
-    for _, shp in shapes:
+    named = []
+    for name, shp in shapes:
         p = torch.nn.Parameter(torch.randn(shp, generator=gen, device=device) * 0.02)
         p.grad_dtype = None
-        params.append(p)
+        named.append((name, p))
+    params = [p for _, p in named]
     n_params = sum(p.numel() for p in params)
-    opt = Adafactor8Bit(params, **wl["hp"])
+    groups = make_groups(wl, named)
+    if world > 1:
+        # ZeRO-1: whole tensors are owned by ranks; each rank updates its tensors, then one
+        # in-place all-gather of the flat parameter buffer (strong scaling: the job is fixed)
+        opt = ShardedAdafactor8Bit(groups, **wl["hp"])
+        owned = [i for i, o in enumerate(opt.owner) if o == opt.rank]
+    else:
+        opt = Adafactor8Bit(groups, **wl["hp"])
+        owned = list(range(len(params)))
+    inner = opt.inner if world > 1 else opt
+    # synthetic gradients only for the tensors this rank updates
     n_sets = 3
-    grad_sets = [make_grad_set(torch, shapes, gdtype, 77 + s, device) for s in range(n_sets)]
+    own_shapes = [shapes[i] for i in owned]
+    grad_sets = [make_grad_set(torch, own_shapes, gdtype, 77 + s_, device) for s_ in range(n_sets)]
 
     def set_grads(k):
-        for p, g in zip(params, grad_sets[k % n_sets]):
-            p.grad = g
+        for i, g in zip(owned, grad_sets[k % n_sets]):
+            params[i].grad = g
 
     def barrier():
         if world > 1:
@@ -262,22 +328,33 @@ def run_gpu_arm(args):
     # ---- timed region: inputs resident in HBM ----
     _engine.LAUNCH_LOG = []
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    evs = []
     with ClockSampler(local) as clocks:
         barrier()
         ev0.record()
         for k in range(args.steps):
             set_grads(k)
-            opt.step()
+            if world > 1:
+                opt.local_step()
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                opt.gather()
+                e2 = torch.cuda.Event(enable_timing=True)
+                e2.record()
+                evs.append((e, e2))
+            else:
+                opt.step()
         ev1.record()
         barrier()
     ms = ev0.elapsed_time(ev1) / args.steps
+    gather_ms = sum(a.elapsed_time(b) for a, b in evs) / max(1, len(evs)) if evs else 0.0
     log = _engine.LAUNCH_LOG
     _engine.LAUNCH_LOG = None
     if world > 1:
-        t = torch.tensor([ms], device=device)
+        t = torch.tensor([ms, gather_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    value = n_params * world / (ms * 1e-3) / 1e9
+        ms, gather_ms = float(t[0].item()), float(t[1].item())
+    value = n_params / (ms * 1e-3) / 1e9
 
     # ---- per-kernel durations inside the timed region (events on the launch stream) ----
     per_kernel = {}
@@ -290,7 +367,19 @@ def run_gpu_arm(args):
     if per_kernel:
         dom = max(per_kernel, key=lambda k: per_kernel[k][0])
         tot_ms, launches, units = per_kernel[dom]
-        bpp = wl["bytes_per_param"] if dom.endswith(("apply", "noclip")) else {"bf16": 4, "f32": 6}[wl["grad"]]
+        gb = {"bf16": 2, "f32": 4}[wl["grad"]]
+        if dom.startswith("fullrank") and dom.endswith(("apply", "noclip")):
+            bpp = gb + 8 + 4                      # grad + param r/w + M and V codes r/w
+        elif dom.startswith("fullrank"):
+            bpp = gb + 2                          # statistic pass: grad + both codes
+        elif dom == "factored_apply":
+            bpp = gb + 8 + (2 if inner.param_groups[0].get("beta1") is not None else 0)
+        elif dom.startswith("factored"):
+            bpp = gb                              # statistic passes read the gradient
+        elif dom == "apollo_project":
+            bpp = gb
+        else:
+            bpp = gb + 8
         achieved = units * bpp / (tot_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "traffic": None, "kernel": dom, "launches": launches, "avg_launch_ms": tot_ms / launches,
@@ -300,17 +389,17 @@ def run_gpu_arm(args):
     # ---- end to end: gradients in pinned host memory ----
     e2e = None
     if not args.no_e2e:
-        host_sets = [[g.cpu().pin_memory() for g in grad_sets[0]]]
+        host = [g.cpu().pin_memory() for g in grad_sets[0]]
         dev_grads = [torch.empty_like(g) for g in grad_sets[0]]
         h2d = sum(g.numel() * g.element_size() for g in dev_grads)
         e2e_steps = max(1, min(args.steps, 5))
 
         def e2e_step():
-            for dg, hg, p in zip(dev_grads, host_sets[0], params):
+            for i, dg, hg in zip(owned, dev_grads, host):
                 dg.copy_(hg, non_blocking=True)
-                p.grad = dg
+                params[i].grad = dg
             opt.step()
-            return opt.update_norms()     # device->host read of the step's result
+            return inner.update_norms() if inner is not None else np.zeros(0, np.float32)   # device->host read
 
         e2e_step()
         barrier()
@@ -320,12 +409,14 @@ def run_gpu_arm(args):
         ev1.record()
         barrier()
         ems = ev0.elapsed_time(ev1) / e2e_steps
+        tot = torch.tensor([float(h2d), float(norms.nbytes)], device=device, dtype=torch.float64)
         if world > 1:
             t = torch.tensor([ems], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ems = float(t.item())
-        e2e = {"value": n_params * world / (ems * 1e-3) / 1e9, "unit": "Gparams/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": int(norms.nbytes), "ms_per_step": ems, "steps": e2e_steps}
+            dist.all_reduce(tot)
+        e2e = {"value": n_params / (ems * 1e-3) / 1e9, "unit": "Gparams/s", "h2d_bytes_per_step": int(tot[0].item()),
+               "d2h_bytes_per_step": int(tot[1].item()), "ms_per_step": ems, "steps": e2e_steps}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -336,14 +427,18 @@ def run_gpu_arm(args):
         line = {
             "metric": "optimizer_step_throughput", "value": value, "unit": "Gparams/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak" if world > 1 else "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "params": n_params, "tensors": len(params),
-                       "grad_dtype": wl["grad"], "param_dtype": "f32", "states": "M uf8 block 256, V al8 block 2048",
+                       "grad_dtype": wl["grad"], "param_dtype": "f32",
                        "l2_policy": "inputs larger than L2 (whole parameter set streamed every step)",
-                       "parallelism": "replicas" if world > 1 else "single"},
+                       "parallelism": f"zero1 x{world} (tensor-granular shards, in-place fp32 parameter all-gather)"
+                       if world > 1 else "single"},
             "hbm_gbs": value * wl["bytes_per_param"], "clocks": clocks.summary(),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
         }
+        if world > 1:
+            line["allgather_ms_per_step"] = gather_ms
+            line["update_only_value"] = n_params / (max(ms - gather_ms, 1e-6) * 1e-3) / 1e9
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
