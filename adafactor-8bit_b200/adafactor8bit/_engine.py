@@ -184,6 +184,8 @@ class FullrankPlan:
         c = self.cfg
         fast = (c.v_fmt == N.V_AL8 and c.m_fmt == N.M_UF8 and c.block == 2048 and c.m_block == 256
                 and c.use_adam_denom and not c.momentum_only and mode != N.MODE_SUMSQ_M)
+        if fast and mode == N.MODE_SUMSQ:
+            return "fullrank_stat"
         return ("fullrank_fast_" if fast else "fullrank_generic_") + _MODE_NAMES[mode]
 
     def _step(self, mode, host_buf, stream):

@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "fullrank_fast.cuh"
 #include "fullrank_generic.cuh"
+#include "fullrank_stat.cuh"
 
 namespace af8 {
 
@@ -115,6 +116,22 @@ inline int launch_fast(const FullrankLaunch &L, cudaStream_t st)
     return AF8_OK;
 }
 
+template <typename GradT>
+inline int launch_stat(const FullrankLaunch &L, cudaStream_t st)
+{
+    auto kernel = fullrank_stat_kernel<GradT>;
+    int per_sm = 0;
+    AF8_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, STAT_THREADS, 0));
+    if (per_sm < 1) return fail(AF8_ERR_CUDA, "statistic kernel does not fit on an SM");
+    const int64_t warps_per_cta = STAT_THREADS / 32;
+    int64_t grid = (int64_t)per_sm * sm_count();
+    const int64_t need = (L.total_blocks + warps_per_cta - 1) / warps_per_cta;
+    if (grid > need) grid = need;
+    kernel<<<(int)grid, STAT_THREADS, 0, st>>>(L);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
 template <typename GradT, int MODE>
 inline int launch_generic(const FullrankLaunch &L, const GenericCfg &C, cudaStream_t st)
 {
@@ -137,7 +154,7 @@ inline int dispatch_mode(bool fast, int mode, const FullrankLaunch &L, const Gen
     case AF8_MODE_NOCLIP:
         return fast ? launch_fast<GradT, AF8_MODE_NOCLIP>(L, st) : launch_generic<GradT, AF8_MODE_NOCLIP>(L, C, st);
     case AF8_MODE_SUMSQ:
-        return fast ? launch_fast<GradT, AF8_MODE_SUMSQ>(L, st) : launch_generic<GradT, AF8_MODE_SUMSQ>(L, C, st);
+        return fast ? launch_stat<GradT>(L, st) : launch_generic<GradT, AF8_MODE_SUMSQ>(L, C, st);
     case AF8_MODE_APPLY:
         return fast ? launch_fast<GradT, AF8_MODE_APPLY>(L, st) : launch_generic<GradT, AF8_MODE_APPLY>(L, C, st);
     default:

@@ -371,7 +371,7 @@ def run_gpu_arm(args):
         if dom.startswith("fullrank") and dom.endswith(("apply", "noclip")):
             bpp = gb + 8 + 4                      # grad + param r/w + M and V codes r/w
         elif dom.startswith("fullrank"):
-            bpp = gb + 2                          # statistic pass: grad + both codes
+            bpp = gb + 2                          # statistic pass (fullrank_stat, *_sumsq): grad + both codes
         elif dom == "factored_apply":
             bpp = gb + 8 + (2 if inner.param_groups[0].get("beta1") is not None else 0)
         elif dom.startswith("factored"):
