@@ -356,6 +356,7 @@ class FactoredPlan:
         self.cols = np.array([p.shape[1] for p in self.params], dtype=np.int64)
         self.numel = self.rows * self.cols
         self.total_numel = int(self.numel.sum())
+        self.cfg.aligned8 = int(bool((self.cols % 8 == 0).all()))
         lib = N.lib()
         m_quant = m_fmt not in (None, "fp32")
         self.chunk = lib.af8_factored_chunk(self.cfg.m_block if m_quant else 0)
@@ -365,7 +366,9 @@ class FactoredPlan:
         self.first_chunk = np.concatenate([[0], np.cumsum(self.nchunks)[:-1]]).astype(np.int64)
         self.first_tile = np.concatenate([[0], np.cumsum(ntiles)[:-1]]).astype(np.int64)
         self.total_chunks = int(self.nchunks.sum())
-        rc = int((self.rows + self.cols).sum())
+        # rows then columns of every tensor, each vector starting on a 16-byte boundary
+        self._vec_len = ((self.rows + 3) // 4 * 4) + ((self.cols + 3) // 4 * 4)
+        rc = int(self._vec_len.sum())
         self.d_sums = torch.empty(rc, dtype=torch.float64, device=self.device)
         self.d_inv = torch.empty(rc * (2 if self.came else 1), dtype=torch.float32, device=self.device)
         self.d_table = torch.empty(n * N.FACTORED_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
@@ -383,27 +386,28 @@ class FactoredPlan:
         t = np.zeros(self.n, dtype=N.FACTORED_TENSOR)
         off = 0
         sums, inv = self.d_sums.data_ptr(), self.d_inv.data_ptr()
-        half = int((self.rows + self.cols).sum())
+        half = int(self._vec_len.sum())
         for i, (p, st) in enumerate(zip(self.params, self.states)):
             R, C = int(self.rows[i]), int(self.cols[i])
+            Rp = (R + 3) // 4 * 4
             t["param"][i] = p.data_ptr()
             t["m_q"][i] = _ptr(st.get("m_q"))
             t["m_scale"][i] = _ptr(st.get("m_scale"))
             t["m_f32"][i] = _ptr(st.get("m"))
             t["row_sum"][i] = sums + 8 * off
-            t["col_sum"][i] = sums + 8 * (off + R)
+            t["col_sum"][i] = sums + 8 * (off + Rp)
             t["inv_row"][i] = inv + 4 * off
-            t["inv_col"][i] = inv + 4 * (off + R)
+            t["inv_col"][i] = inv + 4 * (off + Rp)
             if self.came:
                 t["inv_row_conf"][i] = inv + 4 * (half + off)
-                t["inv_col_conf"][i] = inv + 4 * (half + off + R)
+                t["inv_col_conf"][i] = inv + 4 * (half + off + Rp)
             block = st.get("block_size", 2048)
             _small_state_fields(t["row_var"][i:i + 1], st, "row_var", self.v_fmts[i], block)
             _small_state_fields(t["col_var"][i:i + 1], st, "col_var", self.v_fmts[i], block)
             if self.came:
                 _small_state_fields(t["conf_row"][i:i + 1], st, "conf_row", self.c_fmts[i], block)
                 _small_state_fields(t["conf_col"][i:i + 1], st, "conf_col", self.c_fmts[i], block)
-            off += R + C
+            off += int(self._vec_len[i])
         t["rows"], t["cols"] = self.rows, self.cols
         t["first_chunk"], t["first_tile"] = self.first_chunk, self.first_tile
         return t

@@ -89,6 +89,7 @@ class FactoredCfg(ctypes.Structure):
         ("param_dtype", ctypes.c_int32), ("grad_dtype", ctypes.c_int32), ("m_fmt", ctypes.c_int32),
         ("m_block", ctypes.c_int32), ("came", ctypes.c_int32), ("negate_grad", ctypes.c_int32),
         ("mode", ctypes.c_int32), ("v_floor", ctypes.c_float),
+        ("aligned8", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 
@@ -113,6 +114,7 @@ _c_f = ctypes.c_float
 PROTOTYPES = {
     "af8_version": (_c_i, []),
     "af8_last_error": (ctypes.c_char_p, []),
+    "af8_struct_size": (ctypes.c_int32, [ctypes.c_int32]),
     "af8_device_status": (_c_i, [ctypes.POINTER(ctypes.c_int32), _c_p]),
     "af8_set_qmap": (_c_i, [_c_p, _c_p, _c_p]),
     "af8_fullrank_step": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
@@ -164,6 +166,15 @@ def lib():
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args
+        # the mirrors of this module against the structures the library was compiled with
+        mirrors = [FULLRANK_TENSOR.itemsize, DYN_SCALARS.itemsize, ctypes.sizeof(FullrankCfg), NORM_TENSOR.itemsize,
+                   SCALE_TENSOR.itemsize, SMALL_STATE.itemsize, FACTORED_TENSOR.itemsize, ctypes.sizeof(FactoredCfg),
+                   ctypes.sizeof(ApolloScalarsIn), 16]
+        for i, mine in enumerate(mirrors):
+            theirs = handle.af8_struct_size(i)
+            if theirs != mine:
+                raise RuntimeError(f"{path}: structure {i} is {theirs} bytes in the library, {mine} in this binding; "
+                                   f"rebuild the library")
         _lib = handle
     return _lib
 

@@ -14,3 +14,15 @@
 extern "C" int af8_version(void) { return AF8_VERSION; }
 
 extern "C" const char *af8_last_error(void) { return af8::error_buffer(); }
+
+extern "C" int32_t af8_struct_size(int32_t index)
+{
+    static const int32_t sizes[] = {
+        (int32_t)sizeof(af8_fullrank_tensor), (int32_t)sizeof(af8_dyn_scalars), (int32_t)sizeof(af8_fullrank_cfg),
+        (int32_t)sizeof(af8_norm_tensor), (int32_t)sizeof(af8_scale_tensor), (int32_t)sizeof(af8_small_state),
+        (int32_t)sizeof(af8_factored_tensor), (int32_t)sizeof(af8_factored_cfg),
+        (int32_t)sizeof(af8_apollo_scalars_in), (int32_t)sizeof(af8_apollo_scalars),
+    };
+    if (index < 0 || index >= (int32_t)(sizeof(sizes) / sizeof(sizes[0]))) return -1;
+    return sizes[index];
+}

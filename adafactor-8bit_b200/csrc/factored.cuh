@@ -21,13 +21,16 @@
 //                           the momentum requantisation.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "fullrank_fast.cuh"
 #include "fullrank_generic.cuh"
+#include "fullrank_stat.cuh"
 
 namespace af8 {
 
-constexpr int FSTAT_ROWS = 64;
+constexpr int FSTAT_ROWS = 512;
 constexpr int FSTAT_COLS = 256;
 constexpr int FUPD_THREADS = 256;
 
@@ -353,6 +356,312 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
     }
 }
 
+// ---------------------------------------------------------------------------
+// vectorised variants: every tensor has cols % 8 == 0 and 16-byte aligned arrays, the
+// momentum block (if quantised) is 256.  A thread owns 8 consecutive elements of one row:
+// 128-bit loads of the gradient, the parameter and the column vectors; a warp owns one
+// momentum block, so its absmax is a warp reduction.  Same arithmetic as the kernels above.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+template <typename GradT> __device__ __forceinline__ constexpr int sizeof_grad() { return std::is_same<GradT, float>::value ? 4 : 2; }
+
+template <typename GradT>
+__device__ __forceinline__ void load_g8(const void *grad, int64_t off, int negate, float (&g)[8])
+{
+    stat_load_g<GradT>(grad, off, g);
+    if (negate) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = -g[j];
+    }
+}
+
+__device__ __forceinline__ void load_f8(const float *p, float (&x)[8])
+{
+    const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+
+__device__ __forceinline__ void load_f8_ro(const float *p, float (&x)[8])     // read-only data, kept in L1
+{
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p + 4));
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+
+// old momentum of 8 consecutive elements (one momentum block)
+__device__ __forceinline__ void m_old8(const af8_factored_tensor &T, int m_fmt, int m_block, int64_t flat, float (&m)[8])
+{
+    if (m_fmt == AF8_M_FP32) { load_f8(T.m_f32 + flat, m); return; }
+    const float sc = __ldg(T.m_scale + flat / m_block);
+    if (m_fmt == AF8_M_UF8) {
+        const uint2 w = *reinterpret_cast<const uint2 *>(T.m_q + flat);
+        const float mc = __fdiv_rn(sc, 128.0f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m[j] = __fmul_rn((float)((int)(((j < 4 ? w.x : w.y) >> (8 * (j & 3))) & 0xffu) - 128), mc);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m[j] = m_decode(T.m_q, sc, flat + j, m_fmt);
+    }
+}
+
+// Rows r0 + warp + 8k of the tile, NB at a time so that NB independent 128-bit loads per lane
+// are in flight.  Column partials go to a per-warp shared array (no shared-memory atomics).
+template <typename GradT, int NB>
+__device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t c,
+                                           bool col_ok, float pre_div, const float (&ic)[8], double (&cacc)[8])
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t R = sT.rows, C = sT.cols;
+    for (int k0 = 0; k0 < FSTAT_ROWS / 8; k0 += NB) {
+        if (r0 + warp + 8 * k0 >= R) break;                       // uniform over the warp
+        float g[NB][8];
+#pragma unroll
+        for (int k = 0; k < NB; ++k) {
+            const int64_t r = r0 + warp + 8 * (k0 + k);
+            if (col_ok && r < R) load_g8<GradT>(sT.grad, r * C + c, L.negate_grad, g[k]);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) g[k][j] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < NB; ++k) {
+            const int64_t r = r0 + warp + 8 * (k0 + k);
+            const bool live = col_ok && r < R;
+            float x[8];
+            if (L.mode == AF8_FSTAT_GRADSQ) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(g[k][j], g[k][j]);
+            } else if (live) {
+                const int64_t flat = r * C + c;
+                const float ir = sT.inv_row[r];
+                float mo[8];
+                m_old8(sT, L.m_fmt, L.m_block, flat, mo);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float u = u_clipped(g[k][j], ir, ic[j], pre_div);
+                    const float m = lerp_t(mo[j], u, sT.m_w);
+                    const float df = __fsub_rn(u, m);
+                    x[j] = __fadd_rn(__fmul_rn(df, df), sT.eps_came);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] = 0.0f;
+            }
+            double racc = 0.0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const double xd = (double)x[j];
+                racc += xd;
+                cacc[j] += xd;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) racc += __shfl_xor_sync(0xffffffffu, racc, o);
+            if (lane == 0 && r < R) atomicAdd(sT.row_sum + r, racc);
+        }
+    }
+}
+
+template <typename GradT>
+__global__ void __launch_bounds__(256)
+factored_stats_vec_kernel(const FactoredLaunch L)
+{
+    __shared__ double s_col[8][FSTAT_COLS];      // [warp][j * 32 + lane]
+    __shared__ af8_factored_tensor sT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int cur_t = -1;
+
+    for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
+        int t = cur_t;
+        if (t < 0) t = find_factored_tile(L.tensors, L.n_tensors, id);
+        else while (t + 1 < L.n_tensors && __ldg(&L.tensors[t + 1].first_tile) <= id) ++t;
+        __syncthreads();                                           // s_col of the previous tile was read
+        if (t != cur_t) {
+            if (tid < (int)(sizeof(af8_factored_tensor) / 4))
+                reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
+            cur_t = t;
+            __syncthreads();
+        }
+        const int64_t C = sT.cols;
+        const int64_t ntc = (C + FSTAT_COLS - 1) / FSTAT_COLS;
+        const int64_t local = id - sT.first_tile;
+        const int64_t r0 = (local / ntc) * FSTAT_ROWS;
+        const int64_t c0 = (local % ntc) * FSTAT_COLS;
+        const int64_t c = c0 + lane * 8;                           // this lane's 8 columns
+        const bool col_ok = c < C;                                 // C % 8 == 0: all 8 or none
+        float pre_div = 1.0f;
+        float ic[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ic[j] = 0.0f;
+        if (L.mode == AF8_FSTAT_RESIDUAL) {
+            pre_div = L.dyn[t].pre_div;
+            if (col_ok) load_f8_ro(sT.inv_col + c, ic);
+        }
+        double cacc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cacc[j] = 0.0;
+        if (L.mode == AF8_FSTAT_GRADSQ) stats_rows<GradT, 4>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
+        else stats_rows<GradT, 2>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s_col[warp][j * 32 + lane] = cacc[j];
+        __syncthreads();
+        // thread tid owns column c0 + tid = c0 + 8 * (tid >> 3) + (tid & 7)
+        if (c0 + tid < C) {
+            double sum = 0.0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) sum += s_col[w][(tid & 7) * 32 + (tid >> 3)];
+            atomicAdd(sT.col_sum + c0 + tid, sum);
+        }
+    }
+}
+
+// chunk = 2048 elements = 8 warps x 256; requires m_block == 256 when the momentum is quantised
+template <typename GradT>
+__global__ void __launch_bounds__(FUPD_THREADS)
+factored_update_vec_kernel(const FactoredLaunch L)
+{
+    __shared__ af8_factored_tensor sT;
+    __shared__ double s_acc[FUPD_THREADS / 32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool has_m = L.m_fmt != AF8_M_NONE;
+    const bool m_quant = has_m && L.m_fmt != AF8_M_FP32;
+    const bool writes = L.mode == AF8_FUPD_APPLY;
+    int cur_t = -1;
+
+    for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
+        int t = cur_t;
+        if (t < 0) t = find_factored_chunk(L.tensors, L.n_tensors, id);
+        else while (t + 1 < L.n_tensors && __ldg(&L.tensors[t + 1].first_chunk) <= id) ++t;
+        if (t != cur_t) {
+            __syncthreads();
+            if (tid < (int)(sizeof(af8_factored_tensor) / 4))
+                reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
+            cur_t = t;
+            __syncthreads();
+        }
+        const int64_t C = sT.cols, numel = sT.rows * sT.cols;
+        const int64_t flat = (id - sT.first_chunk) * 2048 + tid * 8;
+        const bool ok = flat < numel;                                // numel % 8 == 0: all 8 or none
+        {   // pull the next chunk of this CTA toward L2 while this one is processed
+            const int64_t nf = flat + (int64_t)gridDim.x * 2048;
+            if (nf < numel && (tid & 1) == 0) {                      // one request per 32 bytes
+                prefetch_l2(static_cast<const char *>(sT.grad) + nf * (int64_t)sizeof_grad<GradT>());
+                if (writes) {
+                    prefetch_l2(static_cast<const float *>(sT.param) + nf);
+                    prefetch_l2(static_cast<const float *>(sT.param) + nf + 8);
+                }
+                if (std::is_same<GradT, float>::value) prefetch_l2(static_cast<const float *>(sT.grad) + nf + 8);
+            }
+        }
+        float pre_div = 1.0f, step_mul = -sT.alpha, fira = 1.0f;
+        bool zero_upd = false;
+        if (L.dyn != nullptr) {
+            const af8_dyn_scalars ds = L.dyn[t];
+            if (L.came) pre_div = ds.pre_div;
+            if (writes) { step_mul = ds.step; fira = ds.fira; zero_upd = ds.zero != 0.0f; }
+        }
+        if (L.mode == AF8_FUPD_SUMSQ_U) pre_div = 1.0f;
+        float mj[8];
+        double part = 0.0;
+        if (ok) {
+            const int64_t row = flat / C, col = flat - row * C;
+            float g[8], ic[8], u[8];
+            load_g8<GradT>(sT.grad, flat, L.negate_grad, g);
+            load_f8_ro(sT.inv_col + col, ic);
+            const float ir = sT.inv_row[row];
+            if (L.came) {
+                if (L.mode == AF8_FUPD_SUMSQ_U) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) u[j] = u_clipped(g[j], ir, ic[j], 1.0f);
+                } else {
+                    float mo[8], icc[8];
+                    m_old8(sT, L.m_fmt, L.m_block, flat, mo);
+                    load_f8_ro(sT.inv_col_conf + col, icc);
+                    const float irc = sT.inv_row_conf[row];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        mj[j] = lerp_t(mo[j], u_clipped(g[j], ir, ic[j], pre_div), sT.m_w);
+                        u[j] = __fmul_rn(__fmul_rn(mj[j], irc), icc[j]);
+                    }
+                }
+            } else if (has_m) {
+                float mo[8];
+                m_old8(sT, L.m_fmt, L.m_block, flat, mo);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    mj[j] = lerp_t(mo[j], g[j], sT.m_w);
+                    u[j] = __fmul_rn(__fmul_rn(mj[j], ir), ic[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) u[j] = __fmul_rn(__fmul_rn(g[j], ir), ic[j]);
+            }
+            if (!writes) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) part += (double)__fmul_rn(u[j], u[j]);
+            } else {
+                float *pp = static_cast<float *>(sT.param) + flat;
+                float p[8];
+                load_f8(pp, p);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float pj = __fmul_rn(p[j], sT.decay);
+                    if (!zero_upd) pj = __fmaf_rn(step_mul, __fmul_rn(u[j], fira), pj);
+                    p[j] = pj;
+                }
+                *reinterpret_cast<float4 *>(pp) = make_float4(p[0], p[1], p[2], p[3]);
+                *reinterpret_cast<float4 *>(pp + 4) = make_float4(p[4], p[5], p[6], p[7]);
+                if (has_m && !m_quant) {
+                    *reinterpret_cast<float4 *>(sT.m_f32 + flat) = make_float4(mj[0], mj[1], mj[2], mj[3]);
+                    *reinterpret_cast<float4 *>(sT.m_f32 + flat + 4) = make_float4(mj[4], mj[5], mj[6], mj[7]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mj[j] = 0.0f;
+        }
+        if (!writes) {
+            double acc = part;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            __syncthreads();
+            if (lane == 0) s_acc[warp] = acc;
+            __syncthreads();
+            if (tid == 0) {
+                double s = 0.0;
+                for (int w = 0; w < FUPD_THREADS / 32; ++w) s += s_acc[w];
+                L.block_sumsq[id] = s;
+            }
+            continue;
+        }
+        if (m_quant) {
+            // one warp = one momentum block of 256 (the block exists iff its first element does)
+            const int64_t w0 = (id - sT.first_chunk) * 2048 + warp * 256;
+            float am = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(mj[j]));
+            am = fmaxf(warp_max(am), 1e-12f);
+            if (w0 < numel) {
+                if (L.m_fmt == AF8_M_UF8 || L.m_fmt == AF8_M_D8) {
+                    uint32_t o0 = 0, o1 = 0;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        o0 |= m_encode(mj[j], am, L.m_fmt) << (8 * j);
+                        o1 |= m_encode(mj[j + 4], am, L.m_fmt) << (8 * j);
+                    }
+                    if (ok) *reinterpret_cast<uint2 *>(sT.m_q + flat) = make_uint2(o0, o1);
+                } else {
+                    uint32_t o = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2)
+                        o |= ((m_encode(mj[j], am, L.m_fmt) << 4) | m_encode(mj[j + 1], am, L.m_fmt)) << (4 * j);
+                    if (ok) *reinterpret_cast<uint32_t *>(sT.m_q + (flat >> 1)) = o;
+                }
+                if (lane == 0) sT.m_scale[w0 / 256] = am;
+            }
+        }
+    }
+}
+
 inline int factored_chunk_for(int m_block)
 {
     if (m_block <= 0) return 2048;
@@ -370,6 +679,12 @@ inline int validate_factored(const af8_factored_cfg &c, const af8_factored_tenso
     for (int i = 0; i < n; ++i) {
         const af8_factored_tensor &t = T[i];
         if (t.rows <= 0 || t.cols <= 0) return fail(AF8_ERR_INVALID, "factored tensor %d: empty shape", i);
+        if (c.aligned8) {
+            if (t.cols % 8 != 0) return fail(AF8_ERR_INVALID, "factored tensor %d: aligned8 needs cols %% 8 == 0", i);
+            const void *ptrs[] = {t.param, t.grad, t.m_q, t.m_f32, t.inv_col, t.inv_col_conf};
+            for (const void *q : ptrs)
+                if (q && (reinterpret_cast<uintptr_t>(q) & 15u)) return fail(AF8_ERR_INVALID, "factored tensor %d: aligned8 needs 16-byte aligned arrays", i);
+        }
         if (t.rows * t.cols >= ((int64_t)1 << 40)) return fail(AF8_ERR_UNSUPPORTED, "factored tensor %d: too large", i);
         if (!t.param || !t.grad || !t.row_sum || !t.col_sum || !t.inv_row || !t.inv_col)
             return fail(AF8_ERR_INVALID, "factored tensor %d: null pointer", i);
@@ -450,16 +765,27 @@ extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factore
     if (cfg->mode == AF8_FSTAT_RESIDUAL && (!cfg->came || !dyn)) return fail(AF8_ERR_INVALID, "af8_factored_stats: the residual needs CAME and dyn");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int64_t tiles = 0;
+    // clear the accumulators; ranges that follow one another in memory share one memset
+    char *run_begin = nullptr, *run_end = nullptr;
     for (int i = 0; i < n_tensors; ++i) {
         const af8_factored_tensor &t = host_tensors[i];
-        AF8_CUDA_TRY(cudaMemsetAsync(t.row_sum, 0, sizeof(double) * (size_t)t.rows, st));
-        AF8_CUDA_TRY(cudaMemsetAsync(t.col_sum, 0, sizeof(double) * (size_t)t.cols, st));
+        char *const ptr[2] = {reinterpret_cast<char *>(t.row_sum), reinterpret_cast<char *>(t.col_sum)};
+        const size_t len[2] = {sizeof(double) * (size_t)t.rows, sizeof(double) * (size_t)t.cols};
+        for (int k = 0; k < 2; ++k) {
+            if (ptr[k] == run_end) { run_end += len[k]; continue; }
+            if (run_end != run_begin) AF8_CUDA_TRY(cudaMemsetAsync(run_begin, 0, (size_t)(run_end - run_begin), st));
+            run_begin = ptr[k];
+            run_end = ptr[k] + len[k];
+        }
         tiles += ((t.rows + FSTAT_ROWS - 1) / FSTAT_ROWS) * ((t.cols + FSTAT_COLS - 1) / FSTAT_COLS);
     }
+    if (run_end != run_begin) AF8_CUDA_TRY(cudaMemsetAsync(run_begin, 0, (size_t)(run_end - run_begin), st));
     FactoredLaunch L = make_factored_launch(*cfg, dev_tensors, n_tensors, tiles, dyn, nullptr);
     int64_t grid = (int64_t)sm_count() * 6;
     if (grid > tiles) grid = tiles;
-    factored_stats_kernel<<<(int)grid, 256, 0, st>>>(L);
+    if (cfg->aligned8 && cfg->grad_dtype == AF8_BF16) factored_stats_vec_kernel<bf16_tag><<<(int)grid, 256, 0, st>>>(L);
+    else if (cfg->aligned8) factored_stats_vec_kernel<float><<<(int)grid, 256, 0, st>>>(L);
+    else factored_stats_kernel<<<(int)grid, 256, 0, st>>>(L);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }
@@ -496,7 +822,10 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     const size_t smem = sizeof(float) * (size_t)chunk;
     int64_t grid = (int64_t)sm_count() * 6;
     if (grid > total_chunks) grid = total_chunks;
-    factored_update_kernel<<<(int)grid, FUPD_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(L, chunk);
+    const bool vec = cfg->aligned8 && chunk == 2048 && (!m_quant || cfg->m_block == 256);
+    if (vec && cfg->grad_dtype == AF8_BF16) factored_update_vec_kernel<bf16_tag><<<(int)grid, FUPD_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(L);
+    else if (vec) factored_update_vec_kernel<float><<<(int)grid, FUPD_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(L);
+    else factored_update_kernel<<<(int)grid, FUPD_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(L, chunk);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }

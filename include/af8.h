@@ -69,6 +69,12 @@ enum {
 AF8_API int af8_version(void);
 AF8_API const char *af8_last_error(void);
 
+/* sizeof() of the i-th structure of this header as the library was compiled, in the order
+ * fullrank_tensor, dyn_scalars, fullrank_cfg, norm_tensor, scale_tensor, small_state,
+ * factored_tensor, factored_cfg, apollo_scalars_in, apollo_scalars; -1 for any other index.
+ * A binding checks its own mirrors against these when it loads the library. */
+AF8_API int32_t af8_struct_size(int32_t index);
+
 /* Device-side health: waits inside the kernels (on asynchronous copies) are
  * bounded; a wait that ran out sets a sticky flag on the device instead of
  * hanging.  This call synchronises `stream` and returns the flag of the current
@@ -271,6 +277,9 @@ typedef struct af8_factored_cfg {
     int32_t negate_grad;
     int32_t mode;           /* AF8_FSTAT_* for af8_factored_stats, AF8_FUPD_* for af8_factored_update */
     float v_floor;          /* min_log floor of the AL requantisation (-126) */
+    int32_t aligned8;       /* 1: every tensor has cols % 8 == 0 and 16-byte aligned arrays
+                               (checked by af8_factored_upload); selects the 128-bit kernels */
+    int32_t reserved;
 } af8_factored_cfg;
 
 /* Number of flattened elements per work unit of af8_factored_update for a

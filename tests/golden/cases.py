@@ -127,8 +127,8 @@ CASES = {
 
 
 def case_inputs(name):
-    """-> (params0, grads[step][i]) for a case, steps numbered from 1."""
-    c = CASES[name]
+    """-> (params0, grads[step][i]) for a case (its name, or a dict of the same form), steps numbered from 1."""
+    c = name if isinstance(name, dict) else CASES[name]
     params = [make_param(s, c["seed"] * 1000 + i) for i, s in enumerate(c["shapes"])]
     grads = {}
     for t in range(1, c["steps"] + 1):

@@ -15,11 +15,12 @@ def load_golden(name):
 
 
 class OracleRun:
-    def __init__(self, name):
+    def __init__(self, name, case=None):
+        """`case`: a dict of the same form as the entries of cases.CASES, for cases without fixtures."""
         self.name = name
-        self.case = cases.CASES[name]
+        self.case = case if case is not None else cases.CASES[name]
         self.hp = o.hyper(**self.case["hp"])
-        self.params0, self.grads = cases.case_inputs(name)
+        self.params0, self.grads = cases.case_inputs(self.case)
         self.params = [p.copy() for p in self.params0]
         self.states = [o.init_state(p.shape, self.hp) for p in self.params]
         seed = 1                                 # optimizer-level counter (optimizer.py:1460, 1727-1728)

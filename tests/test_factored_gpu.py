@@ -32,9 +32,31 @@ def compare(name, t, i, st_gpu, st_cpu, p_gpu, p_cpu, param_tol):
     parity.assert_params(p_gpu.detach().cpu().numpy(), p_cpu, f"{name} t{t} p{i} param", tol=param_tol)
 
 
-@pytest.mark.parametrize("name", FACTORED_CASES)
+# Cases without fixtures.  "odd": column counts that are not multiples of 8 take the
+# element-wise kernels; "tiles": several statistic tiles per tensor with ragged edges and
+# chunks that end inside a momentum block, through the 128-bit kernels.
+EXTRA_CASES = {
+    "adafactor_odd": dict(shapes=[(37, 131), (50, 100)], steps=3, seed=31, grad=cases.CASES["adafactor_factored"]["grad"],
+                          hp=cases.CASES["adafactor_factored"]["hp"]),
+    "adafactor_m_odd": dict(shapes=[(37, 131), (130, 273)], steps=3, seed=32, grad=cases.CASES["adafactor_factored_m"]["grad"],
+                            hp=cases.CASES["adafactor_factored_m"]["hp"]),
+    "came_odd": dict(shapes=[(33, 77), (129, 300)], steps=3, seed=33, grad=cases.CASES["came_al16"]["grad"],
+                     hp=cases.CASES["came_al16"]["hp"]),
+    "adafactor_tiles": dict(shapes=[(200, 520), (70, 264), (3, 8)], steps=3, seed=34,
+                            grad=cases.CASES["adafactor_factored"]["grad"], hp=cases.CASES["adafactor_factored"]["hp"]),
+    "adafactor_m_tiles": dict(shapes=[(200, 520), (70, 264), (3, 8)], steps=3, seed=35,
+                              grad=cases.CASES["adafactor_factored_m"]["grad"], hp=cases.CASES["adafactor_factored_m"]["hp"]),
+    "adafactor_m_uf4_tiles": dict(shapes=[(200, 520), (5, 24)], steps=3, seed=36,
+                                  grad=cases.CASES["adafactor_factored_m"]["grad"],
+                                  hp=dict(cases.CASES["adafactor_factored_m"]["hp"], m_quant_type="uf4")),
+    "came_tiles": dict(shapes=[(200, 520), (70, 264), (3, 8)], steps=3, seed=37, grad=cases.CASES["came_al16"]["grad"],
+                       hp=dict(cases.CASES["came_al16"]["hp"], block_size=256)),
+}
+
+
+@pytest.mark.parametrize("name", FACTORED_CASES + sorted(EXTRA_CASES))
 def test_factored_free_running_matches_oracle(name, oracle):
-    run = OracleRun(name)
+    run = OracleRun(name, EXTRA_CASES.get(name))
     params, opt = make_optimizer(run)
     steps = run.case["steps"]
     for t in range(1, steps + 1):
