@@ -375,6 +375,48 @@ __device__ __forceinline__ void load_g8(const void *grad, int64_t off, int negat
     }
 }
 
+// 8 consecutive gradient elements as loaded, so that the load of the next chunk can be
+// issued before the current one is processed
+template <typename GradT> struct GradRaw8;
+template <> struct GradRaw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ __forceinline__ void load(const void *grad, int64_t off)
+    {
+        const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(grad) + off);
+        a = __ldcs(p); b = __ldcs(p + 1);
+    }
+    __device__ __forceinline__ void unpack(int negate, float (&g)[8]) const
+    {
+        g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+        if (negate) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] = -g[j];
+        }
+    }
+};
+template <> struct GradRaw8<bf16_tag> {
+    uint4 a;
+    __device__ __forceinline__ void zero() { a = make_uint4(0u, 0u, 0u, 0u); }
+    __device__ __forceinline__ void load(const void *grad, int64_t off)
+    {
+        a = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(grad) + off));
+    }
+    __device__ __forceinline__ void unpack(int negate, float (&g)[8]) const
+    {
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            g[2 * k] = __uint_as_float(w[k] << 16);
+            g[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        }
+        if (negate) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[j] = -g[j];
+        }
+    }
+};
+
 __device__ __forceinline__ void load_f8(const float *p, float (&x)[8])
 {
     const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
@@ -388,12 +430,14 @@ __device__ __forceinline__ void load_f8_ro(const float *p, float (&x)[8])     //
 }
 
 // old momentum of 8 consecutive elements (one momentum block)
-__device__ __forceinline__ void m_old8(const af8_factored_tensor &T, int m_fmt, int m_block, int64_t flat, float (&m)[8])
+// `pre`: the 8 UF8 codes if the caller has loaded them already (have_pre)
+__device__ __forceinline__ void m_old8(const af8_factored_tensor &T, int m_fmt, int m_block, int64_t flat, float (&m)[8],
+                                       bool have_pre = false, uint2 pre = make_uint2(0u, 0u))
 {
     if (m_fmt == AF8_M_FP32) { load_f8(T.m_f32 + flat, m); return; }
     const float sc = __ldg(T.m_scale + flat / m_block);
     if (m_fmt == AF8_M_UF8) {
-        const uint2 w = *reinterpret_cast<const uint2 *>(T.m_q + flat);
+        const uint2 w = have_pre ? pre : *reinterpret_cast<const uint2 *>(T.m_q + flat);
         const float mc = __fdiv_rn(sc, 128.0f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) m[j] = __fmul_rn((float)((int)(((j < 4 ? w.x : w.y) >> (8 * (j & 3))) & 0xffu) - 128), mc);
@@ -515,17 +559,25 @@ factored_stats_vec_kernel(const FactoredLaunch L)
 }
 
 // chunk = 2048 elements = 8 warps x 256; requires m_block == 256 when the momentum is quantised
-template <typename GradT>
-__global__ void __launch_bounds__(FUPD_THREADS)
+// WRITES: the APPLY pass; the two sum-of-squares passes keep fewer values live and run
+// with more resident CTAs
+template <typename GradT, bool WRITES>
+__global__ void __launch_bounds__(FUPD_THREADS, WRITES ? 3 : 5)
 factored_update_vec_kernel(const FactoredLaunch L)
 {
     __shared__ af8_factored_tensor sT;
-    __shared__ double s_acc[FUPD_THREADS / 32];
+    __shared__ double s_acc2[2][FUPD_THREADS / 32];
+    int parity = 0;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool has_m = L.m_fmt != AF8_M_NONE;
     const bool m_quant = has_m && L.m_fmt != AF8_M_FP32;
-    const bool writes = L.mode == AF8_FUPD_APPLY;
+    constexpr bool writes = WRITES;
     int cur_t = -1;
+    GradRaw8<GradT> ng;
+    float4 np0 = make_float4(0.f, 0.f, 0.f, 0.f), np1 = np0;
+    uint2 nm = make_uint2(0u, 0u);
+    bool have = false;
+    ng.zero();
 
     for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
         int t = cur_t;
@@ -541,15 +593,25 @@ factored_update_vec_kernel(const FactoredLaunch L)
         const int64_t C = sT.cols, numel = sT.rows * sT.cols;
         const int64_t flat = (id - sT.first_chunk) * 2048 + tid * 8;
         const bool ok = flat < numel;                                // numel % 8 == 0: all 8 or none
-        {   // pull the next chunk of this CTA toward L2 while this one is processed
-            const int64_t nf = flat + (int64_t)gridDim.x * 2048;
-            if (nf < numel && (tid & 1) == 0) {                      // one request per 32 bytes
-                prefetch_l2(static_cast<const char *>(sT.grad) + nf * (int64_t)sizeof_grad<GradT>());
-                if (writes) {
-                    prefetch_l2(static_cast<const float *>(sT.param) + nf);
-                    prefetch_l2(static_cast<const float *>(sT.param) + nf + 8);
-                }
-                if (std::is_same<GradT, float>::value) prefetch_l2(static_cast<const float *>(sT.grad) + nf + 8);
+        // this chunk's streams, loaded one iteration ahead when the chunk is in the same tensor
+        GradRaw8<GradT> cg;
+        float4 cp0 = make_float4(0.f, 0.f, 0.f, 0.f), cp1 = cp0;
+        uint2 cm = make_uint2(0u, 0u);
+        const bool pre_m = has_m && L.m_fmt == AF8_M_UF8 && L.mode != AF8_FUPD_SUMSQ_U;
+        float *const pbase = static_cast<float *>(sT.param);
+        if (have) { cg = ng; cp0 = np0; cp1 = np1; cm = nm; }
+        else if (ok) {
+            cg.load(sT.grad, flat);
+            if (writes) { cp0 = *reinterpret_cast<const float4 *>(pbase + flat); cp1 = *reinterpret_cast<const float4 *>(pbase + flat + 4); }
+            if (pre_m) cm = *reinterpret_cast<const uint2 *>(sT.m_q + flat);
+        } else cg.zero();
+        {
+            const int64_t nf = flat + (int64_t)gridDim.x * 2048;     // inside this tensor => the same tensor next time
+            have = nf < numel;
+            if (have) {
+                ng.load(sT.grad, nf);
+                if (writes) { np0 = *reinterpret_cast<const float4 *>(pbase + nf); np1 = *reinterpret_cast<const float4 *>(pbase + nf + 4); }
+                if (pre_m) nm = *reinterpret_cast<const uint2 *>(sT.m_q + nf);
             }
         }
         float pre_div = 1.0f, step_mul = -sT.alpha, fira = 1.0f;
@@ -563,20 +625,23 @@ factored_update_vec_kernel(const FactoredLaunch L)
         float mj[8];
         double part = 0.0;
         if (ok) {
-            const int64_t row = flat / C, col = flat - row * C;
+            int64_t row;
+            if (flat < ((int64_t)1 << 32) && C < ((int64_t)1 << 32)) row = (int64_t)((uint32_t)flat / (uint32_t)C);
+            else row = flat / C;
+            const int64_t col = flat - row * C;
             float g[8], ic[8], u[8];
-            load_g8<GradT>(sT.grad, flat, L.negate_grad, g);
+            cg.unpack(L.negate_grad, g);
             load_f8_ro(sT.inv_col + col, ic);
-            const float ir = sT.inv_row[row];
+            const float ir = __ldg(sT.inv_row + row);
             if (L.came) {
                 if (L.mode == AF8_FUPD_SUMSQ_U) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) u[j] = u_clipped(g[j], ir, ic[j], 1.0f);
                 } else {
                     float mo[8], icc[8];
-                    m_old8(sT, L.m_fmt, L.m_block, flat, mo);
+                    m_old8(sT, L.m_fmt, L.m_block, flat, mo, pre_m, cm);
                     load_f8_ro(sT.inv_col_conf + col, icc);
-                    const float irc = sT.inv_row_conf[row];
+                    const float irc = __ldg(sT.inv_row_conf + row);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         mj[j] = lerp_t(mo[j], u_clipped(g[j], ir, ic[j], pre_div), sT.m_w);
@@ -585,7 +650,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
                 }
             } else if (has_m) {
                 float mo[8];
-                m_old8(sT, L.m_fmt, L.m_block, flat, mo);
+                m_old8(sT, L.m_fmt, L.m_block, flat, mo, pre_m, cm);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     mj[j] = lerp_t(mo[j], g[j], sT.m_w);
@@ -599,9 +664,8 @@ factored_update_vec_kernel(const FactoredLaunch L)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) part += (double)__fmul_rn(u[j], u[j]);
             } else {
-                float *pp = static_cast<float *>(sT.param) + flat;
-                float p[8];
-                load_f8(pp, p);
+                float *pp = pbase + flat;
+                float p[8] = {cp0.x, cp0.y, cp0.z, cp0.w, cp1.x, cp1.y, cp1.z, cp1.w};
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     float pj = __fmul_rn(p[j], sT.decay);
@@ -620,17 +684,20 @@ factored_update_vec_kernel(const FactoredLaunch L)
             for (int j = 0; j < 8; ++j) mj[j] = 0.0f;
         }
         if (!writes) {
+            // One barrier per chunk: the warp partials alternate between two shared rows, and a
+            // row is rewritten only two chunks later, after a barrier that warp 0 reaches once it
+            // has read the row.
             double acc = part;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            __syncthreads();
-            if (lane == 0) s_acc[warp] = acc;
+            if (lane == 0) s_acc2[parity][warp] = acc;
             __syncthreads();
             if (tid == 0) {
                 double s = 0.0;
-                for (int w = 0; w < FUPD_THREADS / 32; ++w) s += s_acc[w];
+                for (int w = 0; w < FUPD_THREADS / 32; ++w) s += s_acc2[parity][w];
                 L.block_sumsq[id] = s;
             }
+            parity ^= 1;
             continue;
         }
         if (m_quant) {
@@ -823,8 +890,17 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     int64_t grid = (int64_t)sm_count() * 6;
     if (grid > total_chunks) grid = total_chunks;
     const bool vec = cfg->aligned8 && chunk == 2048 && (!m_quant || cfg->m_block == 256);
-    if (vec && cfg->grad_dtype == AF8_BF16) factored_update_vec_kernel<bf16_tag><<<(int)grid, FUPD_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(L);
-    else if (vec) factored_update_vec_kernel<float><<<(int)grid, FUPD_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(L);
+    const bool apply = cfg->mode == AF8_FUPD_APPLY;
+    if (vec) {                                   // persistent: the CTAs that are resident together
+        grid = (int64_t)sm_count() * (apply ? 3 : 5);
+        if (grid > total_chunks) grid = total_chunks;
+    }
+    cudaStream_t cst = static_cast<cudaStream_t>(stream);
+    const bool bf = cfg->grad_dtype == AF8_BF16;
+    if (vec && bf && apply) factored_update_vec_kernel<bf16_tag, true><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    else if (vec && bf) factored_update_vec_kernel<bf16_tag, false><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    else if (vec && apply) factored_update_vec_kernel<float, true><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    else if (vec) factored_update_vec_kernel<float, false><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
     else factored_update_kernel<<<(int)grid, FUPD_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(L, chunk);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;

@@ -20,6 +20,14 @@
 namespace af8 {
 
 constexpr int STAT_THREADS = 256;
+#ifndef AF8_STAT_MIN_CTAS
+#define AF8_STAT_MIN_CTAS 3
+#endif
+#ifndef AF8_STAT_UNROLL
+#define AF8_STAT_UNROLL 2
+#endif
+#define AF8_PRAGMA_(x) _Pragma(#x)
+#define AF8_UNROLL_(n) AF8_PRAGMA_(unroll n)
 
 __device__ __forceinline__ float ex2_approx(float x)
 {
@@ -50,7 +58,7 @@ __device__ __forceinline__ void stat_load_g<bf16_tag>(const void *grad, int64_t 
 }
 
 template <typename GradT>
-__global__ void __launch_bounds__(STAT_THREADS)
+__global__ void __launch_bounds__(STAT_THREADS, AF8_STAT_MIN_CTAS)
 fullrank_stat_kernel(const FullrankLaunch L)
 {
     const int lane = threadIdx.x & 31;
@@ -93,7 +101,7 @@ fullrank_stat_kernel(const FullrankLaunch L)
         if (rem >= FAST_VBLOCK && small_w) {
             const float2 a2 = bc2(a), c2 = bc2(c), wv2 = bc2(v_w), wm2 = bc2(m_w), ed2 = bc2(eps_d);
             float2 acc2 = make_float2(0.0f, 0.0f);
-#pragma unroll 2
+AF8_UNROLL_(AF8_STAT_UNROLL)
             for (int s = 0; s < FAST_VBLOCK / FAST_MBLOCK; ++s) {
                 const int64_t off = base + s * FAST_MBLOCK + lane * 8;
                 float g[8];
