@@ -558,18 +558,27 @@ fullrank_fast_kernel(const FullrankLaunch L)
             continue;
         }
 
-        // ---- block extrema of v as integers: for v >= 0 the bit patterns order like the
-        //      values, and bits-1 sends the excluded zeros to the top (optimizer.py:312-313) ----
+        // ---- block extrema of v.  v >= 0, so the bit patterns order like the values.  The
+        //      minimum runs over the non-zero elements (optimizer.py:312-313) and travels as
+        //      bits-1, which sends "none" to the top; a warp that holds a zero (rare after the
+        //      first steps, except in all-zero regions) rescans its registers for it ----
         {
-            uint32_t umin = 0xffffffffu, umax = 0u;
+            float fmn = v[0], fmx = v[0];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t bits = __float_as_uint(v[j]);
-                umin = min(umin, bits - 1u);
-                umax = max(umax, bits);
+            for (int j = 1; j < 8; ++j) {
+                fmn = fminf(fmn, v[j]);
+                fmx = fmaxf(fmx, v[j]);
             }
-            umin = __reduce_min_sync(0xffffffffu, umin);
-            umax = __reduce_max_sync(0xffffffffu, umax);
+            uint32_t umin = __reduce_min_sync(0xffffffffu, __float_as_uint(fmn));
+            const uint32_t umax = __reduce_max_sync(0xffffffffu, __float_as_uint(fmx));
+            if (umin == 0u) {                                    // uniform over the warp
+                uint32_t um = 0xffffffffu;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) um = min(um, __float_as_uint(v[j]) - 1u);
+                umin = __reduce_min_sync(0xffffffffu, um);
+            } else {
+                umin -= 1u;
+            }
             if (lane == 0) { s_redmin[warp] = umin; s_redmax[warp] = umax; }
         }
         // ---- D: only warp 0 consumes the extrema; the other warps signal and move on ----
@@ -598,9 +607,10 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 const float lmax = fmaxf(fmaxf(fabsf(r.min_log), fabsf(mx)), 1.0f);
                 const float err = __fmaf_rn(__fmul_rn(lmax, LG2_REL_BOUND), r.k, 2.0e-4f);
                 r.thr = 0.5f - err;
-                // absurd range (NaN / inf) or a floor below the normal range, where the estimate's
-                // clamp of subnormal values would not match: exact path for all
-                if (!(r.k >= 1.0f) || L.v_floor < -126.0f) r.thr = -1.0f;
+                // Exact path for every element of the block when the range is absurd (NaN / inf)
+                // or when some non-zero element lies below the floor (subnormal values with the
+                // default floor): the estimate path has no lower clamp and flushes subnormals.
+                if (!(r.k >= 1.0f) || L.v_floor < -126.0f || mn < L.v_floor) r.thr = -1.0f;
                 s_vr = r;
                 sT.v_scale[b] = r.scale;
                 sT.v_min_log[b] = r.min_log;
@@ -668,19 +678,21 @@ fullrank_fast_kernel(const FullrankLaunch L)
             const float2 k2 = bc2(r.k), c2 = bc2(r.c), mg2 = bc2(AF8_MAGIC_F + 1.0f), nmg2 = bc2(-(AF8_MAGIC_F + 1.0f));
 #pragma unroll
             for (int j = 0; j < 8; j += 2) {
-                // zeros and subnormal values estimate as 2^-126: at or below every stored min_log
-                const float2 le = make_float2(lg2_approx(fmaxf(v[j], 1.17549435e-38f)),
-                                              lg2_approx(fmaxf(v[j + 1], 1.17549435e-38f)));
+                // An exact zero estimates as -inf: te and sm are -inf, whose low byte is 0, the
+                // reserved code, and d is NaN, which the tests below ignore.  Every other element
+                // of a block that takes this path is a normal number at or above min_log, so
+                // 0 <= t <= 254 up to the estimate's error and no clamp is needed.
+                const float2 le = make_float2(lg2_approx(v[j]), lg2_approx(v[j + 1]));
                 const float2 te = __ffma2_rn(le, k2, c2);
                 const float2 sm = __fadd2_rn(te, mg2);             // rint(te) + 1 in the low bits
                 const float2 rf = __fadd2_rn(sm, nmg2);
                 const float2 d = sub2(te, rf);                     // distance to the chosen integer
                 dd[j] = d.x; dd[j + 1] = d.y;
-                dmax = fmaxf(dmax, fmaxf(fabsf(d.x), fabsf(d.y)));
+                dmax = fmaxf(dmax, fmaxf(fabsf(d.x), fabsf(d.y)));   // fmaxf drops NaN
                 kk[j] = __float_as_int(sm.x); kk[j + 1] = __float_as_int(sm.y);
             }
-            if (__any_sync(0xffffffffu, !(dmax <= r.thr))) {
-                // rare: redo the codes in doubt with the exact sequence
+            if (__any_sync(0xffffffffu, dmax > r.thr)) {
+                // rare: redo the codes in doubt (and the zeros of this thread) with the exact sequence
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     if (!(fabsf(dd[j]) <= r.thr))
@@ -688,12 +700,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
             }
             uint32_t raw[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                // t <= 254 for every element of the block, so only the lower clamp can bind
-                // (values below the min_log floor); code 0 is reserved for exact zero
-                const int k = max(kk[j], AF8_MAGIC_I + 1);
-                raw[j] = (v[j] == 0.0f) ? (uint32_t)AF8_MAGIC_I : (uint32_t)k;
-            }
+            for (int j = 0; j < 8; ++j) raw[j] = (uint32_t)kk[j];
             const uint32_t o0 = __byte_perm(__byte_perm(raw[0], raw[1], 0x0040), __byte_perm(raw[2], raw[3], 0x0040), 0x5410);
             const uint32_t o1 = __byte_perm(__byte_perm(raw[4], raw[5], 0x0040), __byte_perm(raw[6], raw[7], 0x0040), 0x5410);
             uint8_t *vp = static_cast<uint8_t *>(sT.v_q) + base;

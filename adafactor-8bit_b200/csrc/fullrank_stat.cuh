@@ -10,8 +10,9 @@
 // elements, 8 per lane), keeps its sum in registers and writes one float: no shared
 // memory, no block-wide barrier, plain coalesced 64/128-bit loads.
 //
-// Per element: 3 MUFU operations (exp2, sqrt, reciprocal); at 16 MUFU lanes per SM
-// that pipe and the 4 bytes per parameter of HBM traffic bound the pass about equally.
+// Per element: 3 special-function operations (exp2, sqrt, reciprocal); at 16 such lanes
+// per SM that pipe and the 4 bytes per parameter of HBM traffic bound the pass about
+// equally.  (Replacing the reciprocal by rsqrt and a short series was measured slower.)
 #pragma once
 
 #include "common.cuh"
@@ -21,10 +22,10 @@ namespace af8 {
 
 constexpr int STAT_THREADS = 256;
 #ifndef AF8_STAT_MIN_CTAS
-#define AF8_STAT_MIN_CTAS 3
+#define AF8_STAT_MIN_CTAS 4
 #endif
 #ifndef AF8_STAT_UNROLL
-#define AF8_STAT_UNROLL 2
+#define AF8_STAT_UNROLL 4
 #endif
 #define AF8_PRAGMA_(x) _Pragma(#x)
 #define AF8_UNROLL_(n) AF8_PRAGMA_(unroll n)
