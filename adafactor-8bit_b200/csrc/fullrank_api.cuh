@@ -173,6 +173,7 @@ inline int validate_fullrank_table(const af8_fullrank_cfg &c, const af8_fullrank
     for (int i = 0; i < n; ++i) {
         const af8_fullrank_tensor &t = T[i];
         if (t.numel <= 0) return fail(AF8_ERR_INVALID, "tensor %d: numel must be positive", i);
+        if (t.numel >= ((int64_t)1 << 38)) return fail(AF8_ERR_UNSUPPORTED, "tensor %d: more than 2^38 elements", i);   // 32-bit block indices
         if (t.first_block != next) return fail(AF8_ERR_INVALID, "tensor %d: first_block %lld, expected %lld", i, (long long)t.first_block, (long long)next);
         next += (t.numel + c.block - 1) / c.block;
         if (!t.param || !t.grad) return fail(AF8_ERR_INVALID, "tensor %d: null param or grad", i);

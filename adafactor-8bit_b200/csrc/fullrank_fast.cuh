@@ -45,6 +45,8 @@
 //     approximations of sqrt and reciprocal (relative error below 3e-7).
 #pragma once
 
+#include <cstddef>
+
 #include "common.cuh"
 
 namespace af8 {
@@ -327,7 +329,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
 
     extern __shared__ __align__(128) unsigned char s_ring[];     // NST slots of STAGE_BYTES
     __shared__ __align__(8) uint64_t s_full[NST];
-    __shared__ af8_fullrank_tensor sT;
+    __shared__ __align__(16) af8_fullrank_tensor sT;
     __shared__ float s_tab[2][256];
     __shared__ uint32_t s_redmin[FAST_WARPS];
     __shared__ uint32_t s_redmax[FAST_WARPS];
@@ -350,6 +352,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
 
     int cur_t = -1;
     int64_t cur_first = 0, cur_end = 0;      // block range of the current tensor
+    int nfull = 0;                           // number of full blocks of the current tensor
+    const int G = (int)gridDim.x;
     uint32_t phase = 0;                      // bit k: parity to wait for on ring slot k
     int ahead = 0;                           // consecutive blocks from the current one whose copies are in flight
     bool staged = false;                     // this block's decode table and ranges were prepared last iteration
@@ -374,23 +378,21 @@ fullrank_fast_kernel(const FullrankLaunch L)
             cur_t = t;
             cur_first = sT.first_block;
             cur_end = cur_first + (sT.numel + FAST_VBLOCK - 1) / FAST_VBLOCK;
+            nfull = (int)(sT.numel / FAST_VBLOCK);   // a tensor has fewer than 2^31 blocks (checked on the host)
             staged = false;                          // (ahead is 0 here: copies never cross a tensor)
         }
-        const int64_t b = blk - cur_first;            // V block index inside the tensor
-        const int64_t base = b * FAST_VBLOCK;         // first element of the block
-        const int64_t rem = sT.numel - base;          // real elements from base on (> 0)
-        const bool full = rem >= FAST_VBLOCK;
+        const int b = (int)(blk - cur_first);         // V block index inside the tensor
+        const int64_t base = (int64_t)b * FAST_VBLOCK;   // first element of the block
+        const bool full = b < nfull;
+        const int64_t rem = full ? FAST_VBLOCK : sT.numel - base;   // real elements from base on (> 0), capped
         const int stage = n & 1;                      // decode-table / partial-sum buffer of this block
         const int slot = n % NST;                     // ring slot of this block
-        const int64_t blk_next = blk + gridDim.x;
-        const int64_t b_next = blk_next - cur_first;
+        const int b_next = b + G;
         // blocks blk, blk+G, ... that are full blocks of this tensor get their copies issued ahead
         int want = 0;
 #pragma unroll
-        for (int k = 0; k < NST; ++k) {
-            const int64_t bk = b + (int64_t)k * gridDim.x;
-            if (want == k && blk + (int64_t)k * gridDim.x < cur_end && sT.numel - bk * FAST_VBLOCK >= FAST_VBLOCK) want = k + 1;
-        }
+        for (int k = 0; k < NST; ++k)
+            if (want == k && b + k * G < nfull) want = k + 1;
         const bool next_staged = want >= 2;           // the next block gets its table and ranges prepared here
 
         // ---- issue the bulk copies (one thread) ----
@@ -400,7 +402,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
             const unsigned char *vp = static_cast<const unsigned char *>(sT.v_q);
             fence_proxy_async();
             for (int k = ahead; k < want; ++k) {
-                const int64_t nb = (b + (int64_t)k * gridDim.x) * FAST_VBLOCK;
+                const int64_t nb = (int64_t)(b + k * G) * FAST_VBLOCK;
                 const int sl = (n + k) % NST;
                 unsigned char *dst = s_ring + sl * STAGE_BYTES;
                 mbar_expect_tx(&s_full[sl], STAGE_BYTES);
@@ -418,7 +420,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
             const float sc = __ldg(sT.v_scale + b);
             const float ml = __ldg(sT.v_min_log + b);
             mscale_cur = m_exists ? __ldg(sT.m_scale + b * (FAST_VBLOCK / FAST_MBLOCK) + warp) : 0.0f;
-            s_tab[stage][tid] = al_decode((uint32_t)tid, sc, ml, 254.0f);   // optimizer.py:341-349
+            s_tab[stage][tid] = al8_decode_fast((uint32_t)tid, sc, ml);   // optimizer.py:341-349
             __syncthreads();
         }
         if (next_staged) {
@@ -493,15 +495,21 @@ fullrank_fast_kernel(const FullrankLaunch L)
 
         // ---- scalars of the step ----
         StepScalars S;
-        S.decay = sT.decay; S.v_w = sT.v_w; S.m_w = sT.m_w;
+        {   // three vector loads instead of six scalar ones (the descriptor is 16-byte aligned)
+            static_assert(offsetof(af8_fullrank_tensor, decay) % 8 == 0 && offsetof(af8_fullrank_tensor, v_w) % 16 == 0 &&
+                          offsetof(af8_fullrank_tensor, m_w) == offsetof(af8_fullrank_tensor, v_w) + 12 &&
+                          offsetof(af8_fullrank_tensor, eps_gradsq) % 8 == 0 &&
+                          offsetof(af8_fullrank_tensor, eps_denom) == offsetof(af8_fullrank_tensor, eps_gradsq) + 4, "descriptor layout");
+            const float2 da = *reinterpret_cast<const float2 *>(&sT.decay);
+            const float4 vw = *reinterpret_cast<const float4 *>(&sT.v_w);
+            const float2 ep = *reinterpret_cast<const float2 *>(&sT.eps_gradsq);
+            S.decay = da.x; S.step_mul = -da.y; S.v_w = vw.x; S.m_w = vw.w; S.eps_g = ep.x; S.eps_d = ep.y;
+        }
         S.v_wm1 = __fsub_rn(S.v_w, 1.0f); S.m_wm1 = __fsub_rn(S.m_w, 1.0f);
-        S.eps_g = sT.eps_gradsq; S.eps_d = sT.eps_denom;
         S.fira = 1.0f; S.zero_upd = false;
         if (MODE == AF8_MODE_APPLY) {
             const af8_dyn_scalars ds = L.dyn[cur_t];
             S.step_mul = ds.step; S.fira = ds.fira; S.zero_upd = ds.zero != 0.0f;
-        } else {
-            S.step_mul = -sT.alpha;
         }
 
         // ---- EMAs and update: everything that reaches a state is exact ----
@@ -541,7 +549,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
         if (MODE == AF8_MODE_SUMSQ) {
             acc = warp_sum(acc);
             if (lane == 0) s_redsum[stage][warp] = acc;
-            if (next_staged) s_tab[stage ^ 1][tid] = al_decode((uint32_t)tid, nsc, nml, 254.0f);
+            if (next_staged) s_tab[stage ^ 1][tid] = al8_decode_fast((uint32_t)tid, nsc, nml);
             __syncthreads();
             if (s_abort) {   // a copy never completed: give the ones still in flight a bounded chance, then stop
                 for (int k = 1; k < in_flight; ++k) mbar_wait_bounded(&s_full[(n + k) % NST], (phase >> ((n + k) % NST)) & 1u);
@@ -662,7 +670,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
         }
 
         // ---- decode table of the next block, while warp 0 finishes the range ----
-        if (next_staged) s_tab[stage ^ 1][tid] = al_decode((uint32_t)tid, nsc, nml, 254.0f);
+        if (next_staged) s_tab[stage ^ 1][tid] = al8_decode_fast((uint32_t)tid, nsc, nml);
         __syncthreads();                     // ---- E ----
         if (s_abort) {       // a copy never completed: give the ones still in flight a bounded chance, then stop
             for (int k = 1; k < in_flight; ++k) mbar_wait_bounded(&s_full[(n + k) % NST], (phase >> ((n + k) % NST)) & 1u);
