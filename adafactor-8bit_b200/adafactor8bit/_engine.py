@@ -547,6 +547,11 @@ class FactoredPlan:
         return dyn["norm"].copy()
 
 
+# True: APOLLO projections as correctly rounded dot products (binary64 accumulation, SIMT);
+# False: bf16 gradients go through the tensor cores with a three-plane split of the projection
+EXACT_PROJECTION = False
+
+
 class ApolloPlan:
     """APOLLO tensors of one parameter group (optimizer.py:2587-3084): per-tensor
     projection, one batched low-rank state update (the full-rank kernel run on the
@@ -572,6 +577,19 @@ class ApolloPlan:
         self.g_low = [torch.empty(n, dtype=torch.float32, device=dev) for n in self.nl]
         self.upd = [torch.zeros(n, dtype=torch.float32, device=dev) for n in self.nl]
         self.chan_g2 = [torch.empty(n, dtype=torch.float64, device=dev) for n in self.nch]
+        # tensor-core projection: per-tensor workspaces (flag + bf16 planes of the projection)
+        # cut from one buffer, and the task table of the multi-tensor launch
+        lib = N.lib()
+        need = [(int(lib.af8_apollo_project_workspace(r, c, self.rank)) + 255) // 256 * 256
+                for r, c in zip(self.rows, self.cols)]
+        self.ws_bytes = need
+        self.workspace = torch.empty(sum(need) + 256, dtype=torch.uint8, device=dev)
+        base = (self.workspace.data_ptr() + 255) // 256 * 256
+        self.ws_ptr = [base + sum(need[:i]) for i in range(self.n)]
+        task_bytes = int(lib.af8_apollo_project_task_bytes()) * self.n
+        self.h_tasks = _PinnedRing(task_bytes)
+        self.d_tasks = torch.empty(task_bytes, dtype=torch.uint8, device=dev)
+        self.descs = np.zeros(self.n, dtype=N.APOLLO_PROJ_DESC)
         self.sf = [torch.empty(n, dtype=torch.float32, device=dev) for n in self.nch]
         self.sums = torch.zeros(3 * self.n, dtype=torch.float64, device=dev)
         self.out = torch.zeros(4 * self.n, dtype=torch.float32, device=dev)
@@ -609,10 +627,17 @@ class ApolloPlan:
         if log is not None:
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
             ev[0].record(stream)
+        d = self.descs
         for i in range(self.n):
-            N.check(lib.af8_apollo_project(grads[i].data_ptr(), self.grad_dtype, self.negate, pts[i].data_ptr(),
-                                           self.rows[i], self.cols[i], self.rank, self.g_low[i].data_ptr(),
-                                           self.chan_g2[i].data_ptr(), s), "af8_apollo_project")
+            d["grad"][i], d["pt"][i] = grads[i].data_ptr(), pts[i].data_ptr()
+            d["g_low"][i], d["chan_g2"][i] = self.g_low[i].data_ptr(), self.chan_g2[i].data_ptr()
+            d["workspace"][i] = 0 if EXACT_PROJECTION else self.ws_ptr[i]
+            d["workspace_bytes"][i] = 0 if EXACT_PROJECTION else self.ws_bytes[i]
+            d["rows"][i], d["cols"][i], d["rank"][i], d["negate"][i] = self.rows[i], self.cols[i], self.rank, self.negate
+        h_tasks = self.h_tasks.next()
+        N.check(lib.af8_apollo_project_batch(d.ctypes.data, self.n, self.grad_dtype, h_tasks.data_ptr(),
+                                             self.d_tasks.data_ptr(), s), "af8_apollo_project_batch")
+        self.h_tasks.mark(stream)
         if log is not None:
             ev[1].record(stream)
         for first in (True, False):

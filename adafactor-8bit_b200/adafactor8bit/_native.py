@@ -48,6 +48,10 @@ NORM_TENSOR = np.dtype([
 ], align=True)
 assert NORM_TENSOR.itemsize == 64
 
+APOLLO_PROJ_DESC = np.dtype([(n, np.uint64) for n in ("grad", "pt", "g_low", "chan_g2", "workspace")] +
+                            [(n, np.int64) for n in ("workspace_bytes", "rows", "cols", "rank")] +
+                            [("negate", np.int32), ("reserved", np.int32)], align=True)     # af8_apollo_proj_desc, 80 B
+
 SMALL_STATE = np.dtype([
     ("q", _P), ("scale", _P), ("min_log", _P), ("f32", _P), ("fmt", np.int32), ("block", np.int32),
 ], align=True)
@@ -127,6 +131,10 @@ PROTOTYPES = {
     "af8_factored_small": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_i, _c_p]),
     "af8_factored_update": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
     "af8_apollo_project": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_l, _c_l, _c_l, _c_p, _c_p, _c_p]),
+    "af8_apollo_project_workspace": (ctypes.c_int64, [_c_l, _c_l, _c_l]),
+    "af8_apollo_project_ws": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_l, _c_l, _c_l, _c_p, _c_p, _c_p, _c_l, _c_p]),
+    "af8_apollo_project_task_bytes": (ctypes.c_int32, []),
+    "af8_apollo_project_batch": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p]),
     "af8_apollo_scales": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn), _c_p, _c_p, _c_p,
                                  _c_p, _c_p]),
     "af8_apollo_apply": (_c_i, [_c_p, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn),
@@ -169,7 +177,7 @@ def lib():
         # the mirrors of this module against the structures the library was compiled with
         mirrors = [FULLRANK_TENSOR.itemsize, DYN_SCALARS.itemsize, ctypes.sizeof(FullrankCfg), NORM_TENSOR.itemsize,
                    SCALE_TENSOR.itemsize, SMALL_STATE.itemsize, FACTORED_TENSOR.itemsize, ctypes.sizeof(FactoredCfg),
-                   ctypes.sizeof(ApolloScalarsIn), 16]
+                   ctypes.sizeof(ApolloScalarsIn), 16, APOLLO_PROJ_DESC.itemsize]
         for i, mine in enumerate(mirrors):
             theirs = handle.af8_struct_size(i)
             if theirs != mine:

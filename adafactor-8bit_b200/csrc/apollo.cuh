@@ -18,6 +18,7 @@
 
 #include "common.cuh"
 #include "fullrank_fast.cuh"
+#include "apollo_mma.cuh"
 
 namespace af8 {
 
@@ -28,6 +29,13 @@ __device__ __forceinline__ float apollo_grad(const void *g, int dtype, int64_t i
     float x = dtype == AF8_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t *>(g)[i]) : static_cast<const float *>(g)[i];
     if (!isfinite(x)) x = 0.0f;
     return negate ? -x : x;
+}
+
+__device__ __forceinline__ float apollo_grad_flag(const void *g, int dtype, int64_t i, bool &odd)
+{
+    float x = dtype == AF8_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t *>(g)[i]) : static_cast<const float *>(g)[i];
+    if (!isfinite(x)) { x = 0.0f; odd = true; }
+    return x;
 }
 
 // ---------------------------------------------------------------------------
@@ -105,14 +113,16 @@ apollo_project_kernel(const void *grad, int grad_dtype, int negate, const float 
 
 // squared channel norms of G in binary64: per row (right) or per column (left)
 __global__ void __launch_bounds__(256)
-apollo_channel_sumsq_kernel(const void *grad, int grad_dtype, int64_t rows, int64_t cols, int right, double *chan)
+apollo_channel_sumsq_kernel(const void *grad, int grad_dtype, int64_t rows, int64_t cols, int right, double *chan,
+                            int *nonfinite_flag)
 {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    bool odd = false;                                  // met a non-finite entry (which counts as zero)
     if (right) {
         for (int64_t r = (int64_t)blockIdx.x * 8 + warp; r < rows; r += (int64_t)gridDim.x * 8) {
             double a = 0.0;
             for (int64_t c = lane; c < cols; c += 32) {
-                const float x = apollo_grad(grad, grad_dtype, r * cols + c, 0);
+                const float x = apollo_grad_flag(grad, grad_dtype, r * cols + c, odd);
                 a += (double)__fmul_rn(x, x);
             }
 #pragma unroll
@@ -127,12 +137,13 @@ apollo_channel_sumsq_kernel(const void *grad, int grad_dtype, int64_t rows, int6
             double a = 0.0;
             const int64_t r1 = min(rows, r0 + 256);
             for (int64_t r = r0; r < r1; ++r) {
-                const float x = apollo_grad(grad, grad_dtype, r * cols + c, 0);
+                const float x = apollo_grad_flag(grad, grad_dtype, r * cols + c, odd);
                 a += (double)__fmul_rn(x, x);
             }
             atomicAdd(chan + c, a);
         }
     }
+    if (nonfinite_flag != nullptr && odd) atomicOr(nonfinite_flag, 1);
 }
 
 // ---------------------------------------------------------------------------
@@ -278,36 +289,165 @@ apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, 
 
 }  // namespace af8
 
+namespace af8 {
+
+inline int64_t apollo_workspace_bytes(int64_t rows, int64_t cols, int64_t rank)
+{
+    const int64_t k = rows >= cols ? cols : rows;              // the contracted dimension
+    return 256 + 6 * k * rank;                                 // flag (padded) + three bf16 planes of Pt
+}
+
+inline int apollo_channel_norms(const void *grad, int32_t grad_dtype, int64_t rows, int64_t cols, double *chan_g2,
+                                int *flag, cudaStream_t st)
+{
+    const int right = rows >= cols;
+    if (right) {
+        int64_t g = (rows + 7) / 8;
+        if (g > 148 * 16) g = 148 * 16;
+        apollo_channel_sumsq_kernel<<<(int)g, 256, 0, st>>>(grad, grad_dtype, rows, cols, 1, chan_g2, flag);
+    } else {
+        AF8_CUDA_TRY(cudaMemsetAsync(chan_g2, 0, sizeof(double) * (size_t)cols, st));
+        dim3 grid((unsigned)((cols + 255) / 256), (unsigned)((rows + 255) / 256));
+        apollo_channel_sumsq_kernel<<<grid, 256, 0, st>>>(grad, grad_dtype, rows, cols, 0, chan_g2, flag);
+    }
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+inline bool apollo_tc_eligible(const af8_apollo_proj_desc &d, int32_t grad_dtype)
+{
+    return d.workspace != nullptr && grad_dtype == AF8_BF16 && d.rows % 8 == 0 && d.cols % 8 == 0 && d.rank % 8 == 0 &&
+           d.workspace_bytes >= apollo_workspace_bytes(d.rows, d.cols, d.rank) &&
+           (reinterpret_cast<uintptr_t>(d.workspace) & 255u) == 0 && aligned16(d.grad);
+}
+
+inline int apollo_check_desc(const af8_apollo_proj_desc &d, int32_t grad_dtype)
+{
+    if (!d.grad || !d.pt || !d.g_low || !d.chan_g2) return fail(AF8_ERR_INVALID, "af8_apollo_project: null argument");
+    if (d.rows <= 0 || d.cols <= 0 || d.rank <= 0 || d.rows >= (1 << 30) || d.cols >= (1 << 30) || d.rank > 4096)
+        return fail(AF8_ERR_INVALID, "af8_apollo_project: bad shape %lld x %lld, rank %lld", (long long)d.rows, (long long)d.cols, (long long)d.rank);
+    if (grad_dtype != AF8_F32 && grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_project: gradients must be fp32 or bf16");
+    return AF8_OK;
+}
+
+// correctly rounded dot products (SIMT, binary64 accumulation) + channel norms
+inline int apollo_project_exact(const af8_apollo_proj_desc &d, int32_t grad_dtype, cudaStream_t st)
+{
+    if (d.rows >= d.cols) {
+        dim3 grid((unsigned)((d.rank + PJ_TN - 1) / PJ_TN), (unsigned)((d.rows + PJ_TM - 1) / PJ_TM));
+        apollo_project_kernel<true><<<grid, 256, 0, st>>>(d.grad, grad_dtype, d.negate, d.pt, d.g_low, (int)d.rows, (int)d.rank, (int)d.cols);
+    } else {
+        dim3 grid((unsigned)((d.cols + PJ_TN - 1) / PJ_TN), (unsigned)((d.rank + PJ_TM - 1) / PJ_TM));
+        apollo_project_kernel<false><<<grid, 256, 0, st>>>(d.grad, grad_dtype, d.negate, d.pt, d.g_low, (int)d.rank, (int)d.cols, (int)d.rows);
+    }
+    AF8_CUDA_TRY(cudaGetLastError());
+    return apollo_channel_norms(d.grad, grad_dtype, d.rows, d.cols, d.chan_g2, nullptr, st);
+}
+
+// tensor-core path, per tensor: non-finite flag + channel norms, bf16 planes of Pt; fills the task
+inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dtype, ProjTask &task, int &next_tile, cudaStream_t st)
+{
+    int *flag = static_cast<int *>(d.workspace);
+    __nv_bfloat16 *planes = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(d.workspace) + 256);
+    AF8_CUDA_TRY(cudaMemsetAsync(flag, 0, sizeof(int), st));
+    int rc = apollo_channel_norms(d.grad, grad_dtype, d.rows, d.cols, d.chan_g2, flag, st);
+    if (rc) return rc;
+    const bool right = d.rows >= d.cols;
+    const int64_t kdim = right ? d.cols : d.rows;
+    const int64_t pn = kdim * d.rank;
+    int64_t sg = (pn + 255) / 256;
+    if (sg > 148 * 8) sg = 148 * 8;
+    apollo_split_kernel<<<(int)sg, 256, 0, st>>>(d.pt, pn, planes);
+    AF8_CUDA_TRY(cudaGetLastError());
+    task.grad = static_cast<const __nv_bfloat16 *>(d.grad);
+    task.planes = planes;
+    task.out = d.g_low;
+    task.nonfinite_flag = flag;
+    task.M = (int)(right ? d.rows : d.cols);
+    task.N = (int)d.rank;
+    task.K = (int)kdim;
+    task.right = right ? 1 : 0;
+    task.negate = d.negate;
+    task.first_tile = next_tile;
+    task.tiles_n = (task.N + MM_BN - 1) / MM_BN;
+    task.reserved = 0;
+    const int64_t tiles = (int64_t)((task.M + MM_BM - 1) / MM_BM) * task.tiles_n;
+    if (tiles + next_tile >= (1ll << 31)) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_project: too many tiles in one launch");
+    next_tile += (int)tiles;
+    return AF8_OK;
+}
+
+inline int apollo_project_launch(const ProjTask *dev_tasks, int n, int total_tiles, cudaStream_t st)
+{
+    auto kernel = apollo_project_mma_kernel;
+    AF8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mm_smem_bytes()));
+    int grid = sm_count();                                   // one CTA per SM (shared memory and registers)
+    if (grid > total_tiles) grid = total_tiles;
+    kernel<<<grid, MM_THREADS, mm_smem_bytes(), st>>>(dev_tasks, n, total_tiles);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+}  // namespace af8
+
 extern "C" int af8_apollo_project(const void *grad, int32_t grad_dtype, int32_t negate, const float *pt,
                                   int64_t rows, int64_t cols, int64_t rank, float *g_low, double *chan_g2,
                                   void *stream)
 {
     using namespace af8;
-    if (!grad || !pt || !g_low || !chan_g2) return fail(AF8_ERR_INVALID, "af8_apollo_project: null argument");
-    if (rows <= 0 || cols <= 0 || rank <= 0 || rows >= (1 << 30) || cols >= (1 << 30) || rank > 4096)
-        return fail(AF8_ERR_INVALID, "af8_apollo_project: bad shape %lld x %lld, rank %lld", (long long)rows, (long long)cols, (long long)rank);
-    if (grad_dtype != AF8_F32 && grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_project: gradients must be fp32 or bf16");
+    af8_apollo_proj_desc d = {grad, pt, g_low, chan_g2, nullptr, 0, rows, cols, rank, negate, 0};
+    int rc = apollo_check_desc(d, grad_dtype);
+    if (rc) return rc;
+    return apollo_project_exact(d, grad_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t af8_apollo_project_workspace(int64_t rows, int64_t cols, int64_t rank)
+{
+    return af8::apollo_workspace_bytes(rows, cols, rank);
+}
+
+extern "C" int af8_apollo_project_ws(const void *grad, int32_t grad_dtype, int32_t negate, const float *pt,
+                                     int64_t rows, int64_t cols, int64_t rank, float *g_low, double *chan_g2,
+                                     void *workspace, int64_t workspace_bytes, void *stream)
+{
+    using namespace af8;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int right = rows >= cols;
-    if (right) {
-        dim3 grid((unsigned)((rank + PJ_TN - 1) / PJ_TN), (unsigned)((rows + PJ_TM - 1) / PJ_TM));
-        apollo_project_kernel<true><<<grid, 256, 0, st>>>(grad, grad_dtype, negate, pt, g_low, (int)rows, (int)rank, (int)cols);
-    } else {
-        dim3 grid((unsigned)((cols + PJ_TN - 1) / PJ_TN), (unsigned)((rank + PJ_TM - 1) / PJ_TM));
-        apollo_project_kernel<false><<<grid, 256, 0, st>>>(grad, grad_dtype, negate, pt, g_low, (int)rank, (int)cols, (int)rows);
+    af8_apollo_proj_desc d = {grad, pt, g_low, chan_g2, workspace, workspace_bytes, rows, cols, rank, negate, 0};
+    int rc = apollo_check_desc(d, grad_dtype);
+    if (rc) return rc;
+    if (!apollo_tc_eligible(d, grad_dtype)) return apollo_project_exact(d, grad_dtype, st);
+    ProjTask task;
+    int tiles = 0;
+    rc = apollo_project_prepare(d, grad_dtype, task, tiles, st);
+    if (rc) return rc;
+    // the task lives in the workspace between the flag and the planes; the copy from this
+    // stack variable is staged by the runtime before the call returns (pageable source)
+    ProjTask *dev_task = reinterpret_cast<ProjTask *>(static_cast<char *>(workspace) + 64);
+    AF8_CUDA_TRY(cudaMemcpyAsync(dev_task, &task, sizeof(ProjTask), cudaMemcpyHostToDevice, st));
+    return apollo_project_launch(dev_task, 1, tiles, st);
+}
+
+extern "C" int32_t af8_apollo_project_task_bytes(void) { return (int32_t)sizeof(af8::ProjTask); }
+
+extern "C" int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32_t n, int32_t grad_dtype,
+                                        void *host_scratch, void *dev_scratch, void *stream)
+{
+    using namespace af8;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!descs || n <= 0) return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: null or empty table");
+    if (!host_scratch || !dev_scratch) return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: scratch buffers are required");
+    ProjTask *host_tasks = static_cast<ProjTask *>(host_scratch);
+    int n_tc = 0, tiles = 0;
+    for (int i = 0; i < n; ++i) {
+        int rc = apollo_check_desc(descs[i], grad_dtype);
+        if (rc) return rc;
+        if (apollo_tc_eligible(descs[i], grad_dtype)) rc = apollo_project_prepare(descs[i], grad_dtype, host_tasks[n_tc++], tiles, st);
+        else rc = apollo_project_exact(descs[i], grad_dtype, st);
+        if (rc) return rc;
     }
-    AF8_CUDA_TRY(cudaGetLastError());
-    if (right) {
-        int64_t g = (rows + 7) / 8;
-        if (g > 148 * 16) g = 148 * 16;
-        apollo_channel_sumsq_kernel<<<(int)g, 256, 0, st>>>(grad, grad_dtype, rows, cols, 1, chan_g2);
-    } else {
-        AF8_CUDA_TRY(cudaMemsetAsync(chan_g2, 0, sizeof(double) * (size_t)cols, st));
-        dim3 grid((unsigned)((cols + 255) / 256), (unsigned)((rows + 255) / 256));
-        apollo_channel_sumsq_kernel<<<grid, 256, 0, st>>>(grad, grad_dtype, rows, cols, 0, chan_g2);
-    }
-    AF8_CUDA_TRY(cudaGetLastError());
-    return AF8_OK;
+    if (n_tc == 0) return AF8_OK;
+    AF8_CUDA_TRY(cudaMemcpyAsync(dev_scratch, host_tasks, sizeof(ProjTask) * (size_t)n_tc, cudaMemcpyHostToDevice, st));
+    return apollo_project_launch(static_cast<const ProjTask *>(dev_scratch), n_tc, tiles, st);
 }
 
 extern "C" int af8_apollo_scales(const float *upd, const float *g_low, const double *chan_g2, int64_t rows,

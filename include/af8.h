@@ -71,7 +71,8 @@ AF8_API const char *af8_last_error(void);
 
 /* sizeof() of the i-th structure of this header as the library was compiled, in the order
  * fullrank_tensor, dyn_scalars, fullrank_cfg, norm_tensor, scale_tensor, small_state,
- * factored_tensor, factored_cfg, apollo_scalars_in, apollo_scalars; -1 for any other index.
+ * factored_tensor, factored_cfg, apollo_scalars_in, apollo_scalars, apollo_proj_desc; -1 for any
+ * other index.
  * A binding checks its own mirrors against these when it loads the library. */
 AF8_API int32_t af8_struct_size(int32_t index);
 
@@ -356,6 +357,38 @@ typedef struct af8_apollo_scalars {
 AF8_API int af8_apollo_project(const void *grad, int32_t grad_dtype, int32_t negate, const float *pt,
                                int64_t rows, int64_t cols, int64_t rank, float *g_low, double *chan_g2,
                                void *stream);
+
+/* The same projection with a caller-provided workspace of at least
+ * af8_apollo_project_workspace(rows, cols, rank) bytes, 256-byte aligned.  With bf16
+ * gradients and rows, cols and rank multiples of 8 the contraction runs on the tensor
+ * cores: Pt is split into three bf16 planes (exact to 24 bits) and accumulated in
+ * binary32, i.e. the accuracy of an fp32 matmul instead of the correctly rounded dot
+ * products of af8_apollo_project.  Any other case takes the exact path and ignores the
+ * workspace.  Replaces torch.matmul (optimizer.py:2678-2681). */
+AF8_API int64_t af8_apollo_project_workspace(int64_t rows, int64_t cols, int64_t rank);
+AF8_API int af8_apollo_project_ws(const void *grad, int32_t grad_dtype, int32_t negate, const float *pt,
+                                  int64_t rows, int64_t cols, int64_t rank, float *g_low, double *chan_g2,
+                                  void *workspace, int64_t workspace_bytes, void *stream);
+
+/* Many projections in one call.  Every descriptor that qualifies for the tensor-core path
+ * (see af8_apollo_project_ws) joins ONE launch over the tiles of all tensors, which keeps
+ * the GPU full when a single matrix has fewer tiles than there are SMs; the others take
+ * the exact path one by one.  host_scratch (pinned, valid until the copy has run) and
+ * dev_scratch each hold n * af8_apollo_project_task_bytes() bytes. */
+typedef struct af8_apollo_proj_desc {
+    const void *grad;       /* rows x cols */
+    const float *pt;        /* cols x rank (rows >= cols) or rank x rows */
+    float *g_low;           /* rows x rank or rank x cols */
+    double *chan_g2;        /* max(rows, cols) */
+    void *workspace;        /* af8_apollo_project_workspace() bytes, 256-byte aligned; NULL: exact path */
+    int64_t workspace_bytes;
+    int64_t rows, cols, rank;
+    int32_t negate;
+    int32_t reserved;
+} af8_apollo_proj_desc;
+AF8_API int32_t af8_apollo_project_task_bytes(void);
+AF8_API int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32_t n, int32_t grad_dtype,
+                                     void *host_scratch, void *dev_scratch, void *stream);
 
 /* Scaling factors sf[channel] = ||update_low|| / (||g_low|| + 1e-8) (one entry
  * for the tensor-wide variant), the global norm, the Fira limiter, the clip
