@@ -96,14 +96,14 @@ __constant__ double2 c_log2_tab[97] = {
 #include "log2_table.inc"
 };
 
-__device__ __forceinline__ float log2_cr_fast(float x)
+__device__ __forceinline__ float log2_cr_fast(float x, const double2 *tab = c_log2_tab)
 {
     const double xd = (double)x;
     const int hi = __double2hiint(xd);
     const int e = (hi - 0x3fe80000) >> 20;                 // 0x3fe80000: high word of 0.75
     const double m = __hiloint2double(hi - (e << 20), __double2loint(xd));
     const int j = __double2int_rn((m - 0.75) * 128.0);
-    const double2 t = c_log2_tab[j];
+    const double2 t = tab[j];
     const double r = fma(m, t.x, -1.0);
     double p = 0x1.a61762a7adedap-3;        //  1/(7 ln 2)
     p = fma(p, r, -0x1.ec709dc3a03fep-3);   // -1/(6 ln 2)
@@ -127,7 +127,9 @@ __device__ __forceinline__ float exp2_cr(float x) { return __double2float_rn(exp
 #include "exp2_table.inc"
 __constant__ double c_exp2_tab[32] = AF8_EXP2_TAB;
 
-__device__ __forceinline__ float exp2_cr_fast(float x)
+// `tab`: the 32-entry table, in constant memory (c_exp2_tab) or a copy of it in shared memory
+// (indexed constant loads run on a slow path, which matters when every thread decodes)
+__device__ __forceinline__ float exp2_cr_fast(float x, const double *tab = c_exp2_tab)
 {
     const double xd = (double)x;
     const double z = fma(xd, 32.0, 0x1.8p52);               // n in the low word (round half to even)
@@ -140,7 +142,7 @@ __device__ __forceinline__ float exp2_cr_fast(float x)
     p = fma(p, r, AF8_EXP2_C2);
     p = fma(p, r, AF8_EXP2_C1);
     p = fma(p, r, 1.0);
-    const double y = c_exp2_tab[n & 31] * p;                // in [1, 2.03)
+    const double y = tab[n & 31] * p;                       // in [1, 2.03)
     return __double2float_rn(__hiloint2double(__double2hiint(y) + ((n >> 5) << 20), __double2loint(y)));
 }
 
@@ -150,7 +152,7 @@ __device__ __forceinline__ float rsqrt_t(float x) { return __frcp_rn(__fsqrt_rn(
 // log2 of a second-moment value as _log_quantize_nonneg sees it
 // (optimizer.py:308-310): values below 1e-38 (zero included) are lifted to 1e-38.
 __device__ __forceinline__ float al_log2(float v) { return (v > AF8_TINY) ? log2_cr(v) : AF8_LOG2_TINY; }
-__device__ __forceinline__ float al_log2_fast(float v) { return (v > AF8_TINY) ? log2_cr_fast(v) : AF8_LOG2_TINY; }
+__device__ __forceinline__ float al_log2_fast(float v, const double2 *tab = c_log2_tab) { return (v > AF8_TINY) ? log2_cr_fast(v, tab) : AF8_LOG2_TINY; }
 
 // AL dequantisation of one code (optimizer.py:341-349).  qm1 = levels - 2.
 __device__ __forceinline__ float al_decode(uint32_t code, float scale, float min_log, float qm1)
@@ -166,14 +168,14 @@ __device__ __forceinline__ float al_decode(uint32_t code, float scale, float min
 // reciprocal and one residual step (equal to the IEEE quotient for every x >= 1e-13,
 // checked exhaustively on the host; (code-1)*scale is 0 or at least 1e-12), then
 // exp2_cr_fast.  min_log >= -127.3 and the block maximum is below 128, so |t| <= 150.
-__device__ __forceinline__ float al8_decode_fast(uint32_t code, float scale, float min_log)
+__device__ __forceinline__ float al8_decode_fast(uint32_t code, float scale, float min_log, const double *tab = c_exp2_tab)
 {
     if (code == 0) return 0.0f;
     const float x = __fmul_rn((float)(code - 1), scale);
     const float rc = 0x1.020408p-8f;                        // fl(1 / 254)
     const float q0 = __fmul_rn(x, rc);
     const float q = __fmaf_rn(__fmaf_rn(-q0, 254.0f, x), rc, q0);
-    return exp2_cr_fast(__fadd_rn(q, min_log));
+    return exp2_cr_fast(__fadd_rn(q, min_log), tab);
 }
 
 // Block range of _log_quantize_nonneg from the reduced extrema

@@ -336,6 +336,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
     __shared__ float s_redsum[2][FAST_WARPS];
     __shared__ VRange s_vr;
     __shared__ int s_abort;
+    __shared__ double s_exp2[32];            // copy of the exp2 table of the decode
+    __shared__ double2 s_log2[97];           // copy of the log2 table of the range computation
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -343,6 +345,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
     const int oa = warp * FAST_MBLOCK + lane * 4;   // first 4-element group of this thread
     const int ob = oa + 128;                         // second group
 
+    if (tid < 32) s_exp2[tid] = c_exp2_tab[tid];
+    if (tid < 97) s_log2[tid] = c_log2_tab[tid];
     if (tid == 0) {
         for (int k = 0; k < NST; ++k) mbar_init(&s_full[k], 1);
         s_abort = 0;
@@ -420,7 +424,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
             const float sc = __ldg(sT.v_scale + b);
             const float ml = __ldg(sT.v_min_log + b);
             mscale_cur = m_exists ? __ldg(sT.m_scale + b * (FAST_VBLOCK / FAST_MBLOCK) + warp) : 0.0f;
-            s_tab[stage][tid] = al8_decode_fast((uint32_t)tid, sc, ml);   // optimizer.py:341-349
+            s_tab[stage][tid] = al8_decode_fast((uint32_t)tid, sc, ml, s_exp2);   // optimizer.py:341-349
             __syncthreads();
         }
         if (next_staged) {
@@ -549,7 +553,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
         if (MODE == AF8_MODE_SUMSQ) {
             acc = warp_sum(acc);
             if (lane == 0) s_redsum[stage][warp] = acc;
-            if (next_staged) s_tab[stage ^ 1][tid] = al8_decode_fast((uint32_t)tid, nsc, nml);
+            if (next_staged) s_tab[stage ^ 1][tid] = al8_decode_fast((uint32_t)tid, nsc, nml, s_exp2);
             __syncthreads();
             if (s_abort) {   // a copy never completed: give the ones still in flight a bounded chance, then stop
                 for (int k = 1; k < in_flight; ++k) mbar_wait_bounded(&s_full[(n + k) % NST], (phase >> ((n + k) % NST)) & 1u);
@@ -600,8 +604,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
             umin = __reduce_min_sync(0xffffffffu, umin);
             umax = __reduce_max_sync(0xffffffffu, umax);
             // lane 0 takes the log of the minimum, lane 1 of the maximum
-            float lg = (lane == 0) ? ((umin == 0xffffffffu) ? INFINITY : al_log2_fast(__uint_as_float(umin + 1u)))
-                                   : ((lane == 1) ? al_log2_fast(__uint_as_float(umax)) : 0.0f);
+            float lg = (lane == 0) ? ((umin == 0xffffffffu) ? INFINITY : al_log2_fast(__uint_as_float(umin + 1u), s_log2))
+                                   : ((lane == 1) ? al_log2_fast(__uint_as_float(umax), s_log2) : 0.0f);
             const float mx_l = __shfl_sync(0xffffffffu, lg, 1);
             if (lane == 0) {
                 const float mn = lg;
@@ -670,7 +674,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
         }
 
         // ---- decode table of the next block, while warp 0 finishes the range ----
-        if (next_staged) s_tab[stage ^ 1][tid] = al8_decode_fast((uint32_t)tid, nsc, nml);
+        if (next_staged) s_tab[stage ^ 1][tid] = al8_decode_fast((uint32_t)tid, nsc, nml, s_exp2);
         __syncthreads();                     // ---- E ----
         if (s_abort) {       // a copy never completed: give the ones still in flight a bounded chance, then stop
             for (int k = 1; k < in_flight; ++k) mbar_wait_bounded(&s_full[(n + k) % NST], (phase >> ((n + k) % NST)) & 1u);
@@ -704,7 +708,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
                     if (!(fabsf(dd[j]) <= r.thr))
-                        kk[j] = AF8_MAGIC_I + (int)al_encode(v[j], al_log2_fast(v[j]), r.min_log, r.scale, 254.0f, 255);
+                        kk[j] = AF8_MAGIC_I + (int)al_encode(v[j], al_log2_fast(v[j], s_log2), r.min_log, r.scale, 254.0f, 255);
             }
             uint32_t raw[8];
 #pragma unroll
