@@ -146,6 +146,64 @@ apollo_channel_sumsq_kernel(const void *grad, int grad_dtype, int64_t rows, int6
     if (nonfinite_flag != nullptr && odd) atomicOr(nonfinite_flag, 1);
 }
 
+// the same for bf16 gradients with cols % 8 == 0: 8 columns per thread, 128-bit loads
+__device__ __forceinline__ void bf16x8_squares(const uint4 a, double (&acc)[8], bool &odd)
+{
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float x = __uint_as_float(w[k] << 16), y = __uint_as_float(w[k] & 0xffff0000u);
+        if (!isfinite(x)) { x = 0.0f; odd = true; }
+        if (!isfinite(y)) { y = 0.0f; odd = true; }
+        acc[2 * k] += (double)__fmul_rn(x, x);
+        acc[2 * k + 1] += (double)__fmul_rn(y, y);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+apollo_channel_sumsq_bf16_kernel(const uint16_t *__restrict__ grad, int64_t rows, int64_t cols, int right, double *chan,
+                                 int *nonfinite_flag)
+{
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    bool odd = false;
+    if (right) {
+        for (int64_t r = (int64_t)blockIdx.x * 8 + warp; r < rows; r += (int64_t)gridDim.x * 8) {
+            double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const uint16_t *row = grad + r * cols;
+            for (int64_t c = (int64_t)lane * 8; c < cols; c += 256)
+                bf16x8_squares(__ldg(reinterpret_cast<const uint4 *>(row + c)), acc, odd);
+            double a = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            if (lane == 0) chan[r] = a;
+        }
+    } else {
+        // tile of 64 rows x 256 columns per CTA: a warp takes every 8th row, a lane 8 columns;
+        // the warps' partial sums meet in shared memory, then one atomic per column
+        __shared__ double s_col[8][256];
+        const int64_t c = (int64_t)blockIdx.x * 256 + lane * 8;
+        const int64_t r0 = (int64_t)blockIdx.y * 64;
+        double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (c < cols) {
+            const int64_t r1 = min(rows, r0 + 64);
+            for (int64_t r = r0 + warp; r < r1; r += 8)
+                bf16x8_squares(__ldg(reinterpret_cast<const uint4 *>(grad + r * cols + c)), acc, odd);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s_col[warp][k * 32 + lane] = acc[k];
+        __syncthreads();
+        // thread tid owns column 8 * (tid >> 3) + (tid & 7) of the tile
+        const int64_t cc = (int64_t)blockIdx.x * 256 + tid;
+        if (cc < cols) {
+            double a = 0.0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) a += s_col[w][(tid & 7) * 32 + (tid >> 3)];
+            atomicAdd(chan + cc, a);
+        }
+    }
+    if (nonfinite_flag != nullptr && odd) atomicOr(nonfinite_flag, 1);
+}
+
 // ---------------------------------------------------------------------------
 // 3. scaling factors and the global norm
 // ---------------------------------------------------------------------------
@@ -287,6 +345,65 @@ apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, 
     }
 }
 
+// the same with 8 consecutive elements per thread and 128-bit accesses (cols % 8 == 0,
+// 16-byte aligned arrays, fewer than 2^34 elements)
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+apollo_apply_vec_kernel(float *__restrict__ param, const void *__restrict__ grad, int negate, const float *__restrict__ sf,
+                        const af8_apollo_scalars *__restrict__ sc, int64_t rows, int64_t cols, int right, int scale_tensor,
+                        int fira, int front, float sqrt_scale, float decay, int has_decay)
+{
+    const float us = sc->update_scale, fs = sc->fira;
+    const uint32_t gpr = (uint32_t)(cols >> 3);                 // groups of 8 per row
+    const uint32_t ngroups = (uint32_t)((rows * cols) >> 3);
+    const float st = scale_tensor ? __ldg(sf) : 0.0f;
+    for (uint32_t grp = blockIdx.x * 256u + threadIdx.x; grp < ngroups; grp += gridDim.x * 256u) {
+        const uint32_t row = grp / gpr, c8 = (grp - row * gpr) << 3;
+        const int64_t idx = (int64_t)grp << 3;
+        float g[8], f[8], pv[8];
+        if (BF16) {
+            const uint4 a = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(grad) + idx));
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { g[2 * k] = __uint_as_float(w[k] << 16); g[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+        } else {
+            const float4 a = __ldcs(reinterpret_cast<const float4 *>(static_cast<const float *>(grad) + idx));
+            const float4 b = __ldcs(reinterpret_cast<const float4 *>(static_cast<const float *>(grad) + idx) + 1);
+            g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+        }
+        if (scale_tensor) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = st;
+        } else if (right) {
+            const float fr = __ldg(sf + row);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = fr;
+        } else {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(sf + c8)), b = __ldg(reinterpret_cast<const float4 *>(sf + c8) + 1);
+            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+        }
+        float4 *pp = reinterpret_cast<float4 *>(param + idx);
+        const float4 p0 = pp[0], p1 = pp[1];
+        pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float ge = g[e];
+            if (!isfinite(ge)) ge = 0.0f;                                    // optimizer.py:2606
+            if (negate) ge = -ge;
+            float fe = f[e];
+            if (fira) fe = __fmul_rn(fe, fs);                                // optimizer.py:2994
+            if (!front) fe = __fmul_rn(fe, sqrt_scale);                      // optimizer.py:3000
+            float x = pv[e];
+            if (has_decay) x = __fmul_rn(x, decay);                          // optimizer.py:3075
+            if (scale_tensor) x = __fmaf_rn(__fmul_rn(us, fe), ge, x);       // optimizer.py:3079
+            else x = __fmaf_rn(__fmul_rn(us, ge), fe, x);                    // optimizer.py:3077
+            pv[e] = x;
+        }
+        pp[0] = make_float4(pv[0], pv[1], pv[2], pv[3]);
+        pp[1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
+    }
+}
+
 }  // namespace af8
 
 namespace af8 {
@@ -301,14 +418,22 @@ inline int apollo_channel_norms(const void *grad, int32_t grad_dtype, int64_t ro
                                 int *flag, cudaStream_t st)
 {
     const int right = rows >= cols;
+    const bool vec = grad_dtype == AF8_BF16 && cols % 8 == 0 && aligned16(grad);
+    const uint16_t *gb = static_cast<const uint16_t *>(grad);
     if (right) {
         int64_t g = (rows + 7) / 8;
         if (g > 148 * 16) g = 148 * 16;
-        apollo_channel_sumsq_kernel<<<(int)g, 256, 0, st>>>(grad, grad_dtype, rows, cols, 1, chan_g2, flag);
+        if (vec) apollo_channel_sumsq_bf16_kernel<<<(int)g, 256, 0, st>>>(gb, rows, cols, 1, chan_g2, flag);
+        else apollo_channel_sumsq_kernel<<<(int)g, 256, 0, st>>>(grad, grad_dtype, rows, cols, 1, chan_g2, flag);
     } else {
         AF8_CUDA_TRY(cudaMemsetAsync(chan_g2, 0, sizeof(double) * (size_t)cols, st));
-        dim3 grid((unsigned)((cols + 255) / 256), (unsigned)((rows + 255) / 256));
-        apollo_channel_sumsq_kernel<<<grid, 256, 0, st>>>(grad, grad_dtype, rows, cols, 0, chan_g2, flag);
+        if (vec) {
+            dim3 grid((unsigned)((cols + 255) / 256), (unsigned)((rows + 63) / 64));
+            apollo_channel_sumsq_bf16_kernel<<<grid, 256, 0, st>>>(gb, rows, cols, 0, chan_g2, flag);
+        } else {
+            dim3 grid((unsigned)((cols + 255) / 256), (unsigned)((rows + 255) / 256));
+            apollo_channel_sumsq_kernel<<<grid, 256, 0, st>>>(grad, grad_dtype, rows, cols, 0, chan_g2, flag);
+        }
     }
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
@@ -485,6 +610,20 @@ extern "C" int af8_apollo_apply(void *param, const void *grad, int32_t grad_dtyp
     if (!param || !grad || !sf || !scalars || !in) return fail(AF8_ERR_INVALID, "af8_apollo_apply: null argument");
     if (grad_dtype != AF8_F32 && grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_apply: gradients must be fp32 or bf16");
     const int64_t n = rows * cols;
+    const int right = rows >= cols ? 1 : 0;
+    if (cols % 8 == 0 && n < ((int64_t)1 << 34) && aligned16(param) && aligned16(grad) && (right || in->scale_tensor || aligned16(sf))) {
+        int64_t gv = (n / 8 + 255) / 256;
+        if (gv > 148 * 8) gv = 148 * 8;
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (grad_dtype == AF8_BF16)
+            apollo_apply_vec_kernel<true><<<(int)gv, 256, 0, st>>>(static_cast<float *>(param), grad, negate, sf, scalars, rows, cols, right,
+                                                                 in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay);
+        else
+            apollo_apply_vec_kernel<false><<<(int)gv, 256, 0, st>>>(static_cast<float *>(param), grad, negate, sf, scalars, rows, cols, right,
+                                                                  in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay);
+        AF8_CUDA_TRY(cudaGetLastError());
+        return AF8_OK;
+    }
     int64_t g = (n + 1023) / 1024;
     if (g > 148 * 16) g = 148 * 16;
     apollo_apply_kernel<<<(int)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
