@@ -601,7 +601,7 @@ factored_stats_vec_kernel(const FactoredLaunch L)
 // WRITES: the APPLY pass; the two sum-of-squares passes keep fewer values live and run
 // with more resident CTAs
 template <typename GradT, bool WRITES>
-__global__ void __launch_bounds__(FUPD_THREADS, WRITES ? 3 : 5)
+__global__ void __launch_bounds__(FUPD_THREADS, WRITES ? 3 : 4)
 factored_update_vec_kernel(const FactoredLaunch L)
 {
     __shared__ af8_factored_tensor sT;
@@ -618,19 +618,53 @@ factored_update_vec_kernel(const FactoredLaunch L)
     bool have = false;
     ng.zero();
 
-    for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
-        int t = cur_t;
-        if (t < 0) t = find_factored_chunk(L.tensors, L.n_tensors, id);
-        else while (t + 1 < L.n_tensors && __ldg(&L.tensors[t + 1].first_chunk) <= id) ++t;
-        if (t != cur_t) {
+    // Every CTA takes a contiguous run of chunks, so a thread's position (flat index, row,
+    // column) and the tensor's scalars advance incrementally: the division by the column
+    // count and the table lookups happen once per tensor, not once per chunk.
+    const int64_t per_cta = (L.total_units + gridDim.x - 1) / gridDim.x;
+    const int64_t id_begin = (int64_t)blockIdx.x * per_cta;
+    const int64_t id_end = min(id_begin + per_cta, L.total_units);
+    int64_t next_first = 0, flat = 0, row = 0, col = 0;
+    float pre_div = 1.0f, step_mul = 0.0f, fira = 1.0f;
+    bool zero_upd = false;
+    DivBy D = make_div(1.0f);
+
+    for (int64_t id = id_begin; id < id_end; ++id) {
+        const int t = cur_t;
+        if (cur_t < 0 || id >= next_first) {
+            int tn = cur_t;
+            if (tn < 0) tn = find_factored_chunk(L.tensors, L.n_tensors, id);
+            else while (tn + 1 < L.n_tensors && __ldg(&L.tensors[tn + 1].first_chunk) <= id) ++tn;
             __syncthreads();
             if (tid < (int)(sizeof(af8_factored_tensor) / 4))
-                reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
-            cur_t = t;
+                reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + tn) + tid);
+            cur_t = tn;
             __syncthreads();
+            next_first = tn + 1 < L.n_tensors ? __ldg(&L.tensors[tn + 1].first_chunk) : L.total_units;
+            flat = (id - sT.first_chunk) * 2048 + tid * 8;
+            row = flat / sT.cols;
+            col = flat - row * sT.cols;
+            have = false;
+            pre_div = 1.0f; step_mul = -sT.alpha; fira = 1.0f; zero_upd = false;
+            if (L.dyn != nullptr) {
+                const af8_dyn_scalars ds = L.dyn[tn];
+                if (L.came && L.mode != AF8_FUPD_SUMSQ_U) pre_div = ds.pre_div;
+                if (writes) { step_mul = ds.step; fira = ds.fira; zero_upd = ds.zero != 0.0f; }
+            }
+            D = make_div(pre_div);
+        } else {
+            flat += 2048;
+            col += 2048;
+            if (sT.cols >= 2048) {
+                if (col >= sT.cols) { col -= sT.cols; ++row; }
+            } else {
+                const uint32_t q = (uint32_t)col / (uint32_t)sT.cols;
+                row += q;
+                col -= (int64_t)q * sT.cols;
+            }
         }
-        const int64_t C = sT.cols, numel = sT.rows * sT.cols;
-        const int64_t flat = (id - sT.first_chunk) * 2048 + tid * 8;
+        (void)t;
+        const int64_t numel = sT.rows * sT.cols;
         const bool ok = flat < numel;                                // numel % 8 == 0: all 8 or none
         // this chunk's streams, loaded one iteration ahead when the chunk is in the same tensor
         GradRaw8<GradT> cg;
@@ -645,29 +679,17 @@ factored_update_vec_kernel(const FactoredLaunch L)
             if (pre_m) cm = *reinterpret_cast<const uint2 *>(sT.m_q + flat);
         } else cg.zero();
         {
-            const int64_t nf = flat + (int64_t)gridDim.x * 2048;     // inside this tensor => the same tensor next time
-            have = nf < numel;
+            const int64_t nf = flat + 2048;                          // the next chunk of this CTA, if it is in this tensor
+            have = id + 1 < id_end && nf < numel;
             if (have) {
                 ng.load(sT.grad, nf);
                 if (writes) { np0 = *reinterpret_cast<const float4 *>(pbase + nf); np1 = *reinterpret_cast<const float4 *>(pbase + nf + 4); }
                 if (pre_m) nm = *reinterpret_cast<const uint2 *>(sT.m_q + nf);
             }
         }
-        float pre_div = 1.0f, step_mul = -sT.alpha, fira = 1.0f;
-        bool zero_upd = false;
-        if (L.dyn != nullptr) {
-            const af8_dyn_scalars ds = L.dyn[t];
-            if (L.came) pre_div = ds.pre_div;
-            if (writes) { step_mul = ds.step; fira = ds.fira; zero_upd = ds.zero != 0.0f; }
-        }
-        if (L.mode == AF8_FUPD_SUMSQ_U) pre_div = 1.0f;
         float mj[8];
         double part = 0.0;
         if (ok) {
-            int64_t row;
-            if (flat < ((int64_t)1 << 32) && C < ((int64_t)1 << 32)) row = (int64_t)((uint32_t)flat / (uint32_t)C);
-            else row = flat / C;
-            const int64_t col = flat - row * C;
             float g[8], ic[8], u[8];
             cg.unpack(L.negate_grad, g);
             load_f8_ro(sT.inv_col + col, ic);
@@ -678,7 +700,6 @@ factored_update_vec_kernel(const FactoredLaunch L)
                     for (int j = 0; j < 8; ++j) u[j] = u_clipped(g[j], ir, ic[j], 1.0f);
                 } else {
                     float mo[8], icc[8];
-                    const DivBy D = make_div(pre_div);
                     m_old8(sT, L.m_fmt, L.m_block, flat, mo, pre_m, cm);
                     load_f8_ro(sT.inv_col_conf + col, icc);
                     const float irc = __ldg(sT.inv_row_conf + row);
@@ -941,7 +962,7 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     const bool vec = cfg->aligned8 && chunk == 2048 && (!m_quant || cfg->m_block == 256);
     const bool apply = cfg->mode == AF8_FUPD_APPLY;
     if (vec) {                                   // persistent: the CTAs that are resident together
-        grid = (int64_t)sm_count() * (apply ? 3 : 5);
+        grid = (int64_t)sm_count() * (apply ? 3 : 4);
         if (grid > total_chunks) grid = total_chunks;
     }
     cudaStream_t cst = static_cast<cudaStream_t>(stream);

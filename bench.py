@@ -68,6 +68,12 @@ WORKLOADS = {
         hp=dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=0.9999, factored=True, relative_step=False,
                 scale_parameter=False, scale_weight_decay=False, d=1.0, eps_came=1e-16, lr=1e-4,
                 m_quant_type="uf8", v_quant_type="al16", c_quant_type="al16", block_size=2048)),
+    # one Llama-2-7B layer with CAME (202 M parameters): the small case for profiler captures
+    "llama2_layer_came": dict(
+        shapes=lambda: llama_shapes(1, 4096, 11008, 4096, 32000)[1:-2], grad="bf16", bytes_per_param=12,
+        hp=dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=0.9999, factored=True, relative_step=False,
+                scale_parameter=False, scale_weight_decay=False, d=1.0, eps_came=1e-16, lr=1e-4,
+                m_quant_type="uf8", v_quant_type="al16", c_quant_type="al16", block_size=2048)),
     # APOLLO rank 256 on the attention / MLP matrices, AdamW-style fallback elsewhere: Llama-3-8B shapes
     "llama3_8b_apollo": dict(
         shapes=lambda: llama_shapes(32, 4096, 14336, 1024, 128256), grad="bf16", bytes_per_param=10,
