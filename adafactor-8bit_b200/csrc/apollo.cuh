@@ -16,9 +16,12 @@
 // 0 and step 1, is update_low); this file holds steps 1, 3, 4 and 5.
 #pragma once
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "fullrank_fast.cuh"
 #include "apollo_mma.cuh"
+#include "apollo_umma.cuh"
 
 namespace af8 {
 
@@ -470,7 +473,14 @@ inline int apollo_project_exact(const af8_apollo_proj_desc &d, int32_t grad_dtyp
 }
 
 // tensor-core path, per tensor: non-finite flag + channel norms, bf16 planes of Pt; fills the task
-inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dtype, ProjTask &task, int &next_tile, cudaStream_t st)
+// true: this projection runs on tcgen05 (right case, rank a multiple of 16 up to 256)
+inline bool apollo_umma_eligible(const af8_apollo_proj_desc &d)
+{
+    static const bool disabled = getenv("AF8_NO_UMMA") != nullptr;
+    return !disabled && d.rows >= d.cols && d.rank % 16 == 0 && d.rank >= 16 && d.rank <= UM_MAXN;
+}
+
+inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dtype, ProjTask &task, int &next_tile, bool umma, cudaStream_t st)
 {
     int *flag = static_cast<int *>(d.workspace);
     __nv_bfloat16 *planes = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(d.workspace) + 256);
@@ -480,9 +490,14 @@ inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dt
     const bool right = d.rows >= d.cols;
     const int64_t kdim = right ? d.cols : d.rows;
     const int64_t pn = kdim * d.rank;
-    int64_t sg = (pn + 255) / 256;
-    if (sg > 148 * 8) sg = 148 * 8;
-    apollo_split_kernel<<<(int)sg, 256, 0, st>>>(d.pt, pn, planes);
+    if (umma) {                                              // planes transposed to [rank][cols]
+        dim3 grid((unsigned)((kdim + 31) / 32), (unsigned)((d.rank + 31) / 32));
+        apollo_split_transposed_kernel<<<grid, 256, 0, st>>>(d.pt, (int)kdim, (int)d.rank, planes);
+    } else {
+        int64_t sg = (pn + 255) / 256;
+        if (sg > 148 * 8) sg = 148 * 8;
+        apollo_split_kernel<<<(int)sg, 256, 0, st>>>(d.pt, pn, planes);
+    }
     AF8_CUDA_TRY(cudaGetLastError());
     task.grad = static_cast<const __nv_bfloat16 *>(d.grad);
     task.planes = planes;
@@ -494,11 +509,23 @@ inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dt
     task.right = right ? 1 : 0;
     task.negate = d.negate;
     task.first_tile = next_tile;
-    task.tiles_n = (task.N + MM_BN - 1) / MM_BN;
+    task.tiles_n = umma ? 1 : (task.N + MM_BN - 1) / MM_BN;
     task.reserved = 0;
-    const int64_t tiles = (int64_t)((task.M + MM_BM - 1) / MM_BM) * task.tiles_n;
+    const int64_t tiles = (int64_t)((task.M + MM_BM - 1) / MM_BM) * task.tiles_n;      // MM_BM == UM_BM
     if (tiles + next_tile >= (1ll << 31)) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_project: too many tiles in one launch");
     next_tile += (int)tiles;
+    return AF8_OK;
+}
+
+inline int apollo_project_launch_umma(const ProjTask *dev_tasks, int n, int total_tiles, cudaStream_t st)
+{
+    static_assert(MM_BM == UM_BM, "tile height");
+    auto kernel = apollo_project_umma_kernel;
+    AF8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)um_smem_bytes()));
+    int grid = sm_count();
+    if (grid > total_tiles) grid = total_tiles;
+    kernel<<<grid, UM_THREADS, um_smem_bytes(), st>>>(dev_tasks, n, total_tiles);
+    AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }
 
@@ -543,13 +570,14 @@ extern "C" int af8_apollo_project_ws(const void *grad, int32_t grad_dtype, int32
     if (!apollo_tc_eligible(d, grad_dtype)) return apollo_project_exact(d, grad_dtype, st);
     ProjTask task;
     int tiles = 0;
-    rc = apollo_project_prepare(d, grad_dtype, task, tiles, st);
+    const bool umma = apollo_umma_eligible(d);
+    rc = apollo_project_prepare(d, grad_dtype, task, tiles, umma, st);
     if (rc) return rc;
     // the task lives in the workspace between the flag and the planes; the copy from this
     // stack variable is staged by the runtime before the call returns (pageable source)
     ProjTask *dev_task = reinterpret_cast<ProjTask *>(static_cast<char *>(workspace) + 64);
     AF8_CUDA_TRY(cudaMemcpyAsync(dev_task, &task, sizeof(ProjTask), cudaMemcpyHostToDevice, st));
-    return apollo_project_launch(dev_task, 1, tiles, st);
+    return umma ? apollo_project_launch_umma(dev_task, 1, tiles, st) : apollo_project_launch(dev_task, 1, tiles, st);
 }
 
 extern "C" int32_t af8_apollo_project_task_bytes(void) { return (int32_t)sizeof(af8::ProjTask); }
@@ -562,17 +590,30 @@ extern "C" int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32
     if (!descs || n <= 0) return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: null or empty table");
     if (!host_scratch || !dev_scratch) return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: scratch buffers are required");
     ProjTask *host_tasks = static_cast<ProjTask *>(host_scratch);
-    int n_tc = 0, tiles = 0;
+    // tensor-core tasks: the tcgen05 ones first, then the mma.sync ones; each kind is one launch
+    int n_umma = 0, n_mma = 0;
     for (int i = 0; i < n; ++i) {
         int rc = apollo_check_desc(descs[i], grad_dtype);
         if (rc) return rc;
-        if (apollo_tc_eligible(descs[i], grad_dtype)) rc = apollo_project_prepare(descs[i], grad_dtype, host_tasks[n_tc++], tiles, st);
-        else rc = apollo_project_exact(descs[i], grad_dtype, st);
+        if (apollo_tc_eligible(descs[i], grad_dtype)) { if (apollo_umma_eligible(descs[i])) ++n_umma; else ++n_mma; }
+    }
+    int iu = 0, im = n_umma, tiles_u = 0, tiles_m = 0;
+    for (int i = 0; i < n; ++i) {
+        int rc;
+        if (!apollo_tc_eligible(descs[i], grad_dtype)) rc = apollo_project_exact(descs[i], grad_dtype, st);
+        else if (apollo_umma_eligible(descs[i])) rc = apollo_project_prepare(descs[i], grad_dtype, host_tasks[iu++], tiles_u, true, st);
+        else rc = apollo_project_prepare(descs[i], grad_dtype, host_tasks[im++], tiles_m, false, st);
         if (rc) return rc;
     }
-    if (n_tc == 0) return AF8_OK;
-    AF8_CUDA_TRY(cudaMemcpyAsync(dev_scratch, host_tasks, sizeof(ProjTask) * (size_t)n_tc, cudaMemcpyHostToDevice, st));
-    return apollo_project_launch(static_cast<const ProjTask *>(dev_scratch), n_tc, tiles, st);
+    if (n_umma + n_mma == 0) return AF8_OK;
+    AF8_CUDA_TRY(cudaMemcpyAsync(dev_scratch, host_tasks, sizeof(ProjTask) * (size_t)(n_umma + n_mma), cudaMemcpyHostToDevice, st));
+    const ProjTask *dev_tasks = static_cast<const ProjTask *>(dev_scratch);
+    if (n_umma) {
+        int rc = apollo_project_launch_umma(dev_tasks, n_umma, tiles_u, st);
+        if (rc) return rc;
+    }
+    if (n_mma) return apollo_project_launch(dev_tasks + n_umma, n_mma, tiles_m, st);
+    return AF8_OK;
 }
 
 extern "C" int af8_apollo_scales(const float *upd, const float *g_low, const double *chan_g2, int64_t rows,
