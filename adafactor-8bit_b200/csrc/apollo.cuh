@@ -17,6 +17,7 @@
 #pragma once
 
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "fullrank_fast.cuh"
@@ -411,10 +412,12 @@ apollo_apply_vec_kernel(float *__restrict__ param, const void *__restrict__ grad
 
 namespace af8 {
 
+constexpr int64_t APOLLO_WS_HEADER = 1024;    // flag at 0, the task of a single-tensor call at 128, planes after the header
+
 inline int64_t apollo_workspace_bytes(int64_t rows, int64_t cols, int64_t rank)
 {
     const int64_t k = rows >= cols ? cols : rows;              // the contracted dimension
-    return 256 + 6 * k * rank;                                 // flag (padded) + three bf16 planes of Pt
+    return APOLLO_WS_HEADER + 6 * k * rank;                    // header + three bf16 planes of Pt
 }
 
 inline int apollo_channel_norms(const void *grad, int32_t grad_dtype, int64_t rows, int64_t cols, double *chan_g2,
@@ -483,7 +486,7 @@ inline bool apollo_umma_eligible(const af8_apollo_proj_desc &d)
 inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dtype, ProjTask &task, int &next_tile, bool umma, cudaStream_t st)
 {
     int *flag = static_cast<int *>(d.workspace);
-    __nv_bfloat16 *planes = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(d.workspace) + 256);
+    __nv_bfloat16 *planes = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(d.workspace) + APOLLO_WS_HEADER);
     AF8_CUDA_TRY(cudaMemsetAsync(flag, 0, sizeof(int), st));
     int rc = apollo_channel_norms(d.grad, grad_dtype, d.rows, d.cols, d.chan_g2, flag, st);
     if (rc) return rc;
@@ -517,7 +520,51 @@ inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dt
     return AF8_OK;
 }
 
-inline int apollo_project_launch_umma(const ProjTask *dev_tasks, int n, int total_tiles, cudaStream_t st)
+// cuTensorMapEncodeTiled, fetched through the runtime so that the library needs no link-time
+// dependency on the driver library
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// the two tensor maps of a tcgen05 task: G as [M][K] with boxes of 128 x 32, the planes as
+// [3][N][K] with boxes of 3 x N x 32, both with the 64-byte swizzle and zero fill outside
+inline int apollo_umma_maps(UmmaTask &u)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(AF8_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    const ProjTask &t = u.t;
+    {
+        const cuuint64_t dim[2] = {(cuuint64_t)t.K, (cuuint64_t)t.M}, stride[1] = {(cuuint64_t)t.K * 2};
+        const cuuint32_t box[2] = {UM_BK, UM_BM}, es[2] = {1, 1};
+        const CUresult r = enc(&u.map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16 *>(t.grad), dim, stride, box, es,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(AF8_ERR_CUDA, "cuTensorMapEncodeTiled (gradient) failed with %d", (int)r);
+    }
+    {
+        const cuuint64_t dim[3] = {(cuuint64_t)t.K, (cuuint64_t)t.N, 3};
+        const cuuint64_t stride[2] = {(cuuint64_t)t.K * 2, (cuuint64_t)t.K * t.N * 2};
+        const cuuint32_t box[3] = {UM_BK, (cuuint32_t)t.N, 3}, es[3] = {1, 1, 1};
+        const CUresult r = enc(&u.map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16 *>(t.planes), dim, stride, box, es,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(AF8_ERR_CUDA, "cuTensorMapEncodeTiled (planes) failed with %d", (int)r);
+    }
+    return AF8_OK;
+}
+
+inline int apollo_project_launch_umma(const UmmaTask *dev_tasks, int n, int total_tiles, cudaStream_t st)
 {
     static_assert(MM_BM == UM_BM, "tile height");
     auto kernel = apollo_project_umma_kernel;
@@ -575,12 +622,21 @@ extern "C" int af8_apollo_project_ws(const void *grad, int32_t grad_dtype, int32
     if (rc) return rc;
     // the task lives in the workspace between the flag and the planes; the copy from this
     // stack variable is staged by the runtime before the call returns (pageable source)
-    ProjTask *dev_task = reinterpret_cast<ProjTask *>(static_cast<char *>(workspace) + 64);
-    AF8_CUDA_TRY(cudaMemcpyAsync(dev_task, &task, sizeof(ProjTask), cudaMemcpyHostToDevice, st));
-    return umma ? apollo_project_launch_umma(dev_task, 1, tiles, st) : apollo_project_launch(dev_task, 1, tiles, st);
+    char *slot = static_cast<char *>(workspace) + 128;
+    if (umma) {
+        UmmaTask u;
+        memset(&u, 0, sizeof(u));
+        u.t = task;
+        rc = apollo_umma_maps(u);
+        if (rc) return rc;
+        AF8_CUDA_TRY(cudaMemcpyAsync(slot, &u, sizeof(UmmaTask), cudaMemcpyHostToDevice, st));
+        return apollo_project_launch_umma(reinterpret_cast<const UmmaTask *>(slot), 1, tiles, st);
+    }
+    AF8_CUDA_TRY(cudaMemcpyAsync(slot, &task, sizeof(ProjTask), cudaMemcpyHostToDevice, st));
+    return apollo_project_launch(reinterpret_cast<const ProjTask *>(slot), 1, tiles, st);
 }
 
-extern "C" int32_t af8_apollo_project_task_bytes(void) { return (int32_t)sizeof(af8::ProjTask); }
+extern "C" int32_t af8_apollo_project_task_bytes(void) { return (int32_t)sizeof(af8::UmmaTask); }
 
 extern "C" int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32_t n, int32_t grad_dtype,
                                         void *host_scratch, void *dev_scratch, void *stream)
@@ -589,30 +645,42 @@ extern "C" int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!descs || n <= 0) return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: null or empty table");
     if (!host_scratch || !dev_scratch) return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: scratch buffers are required");
-    ProjTask *host_tasks = static_cast<ProjTask *>(host_scratch);
-    // tensor-core tasks: the tcgen05 ones first, then the mma.sync ones; each kind is one launch
+    // tensor-core tasks: the tcgen05 ones (with their tensor maps) first, then the mma.sync ones;
+    // each kind is one launch.  The scratch holds n slots of sizeof(UmmaTask), 64-byte aligned.
+    if ((reinterpret_cast<uintptr_t>(host_scratch) & 63u) || (reinterpret_cast<uintptr_t>(dev_scratch) & 63u))
+        return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: scratch buffers must be 64-byte aligned");
     int n_umma = 0, n_mma = 0;
     for (int i = 0; i < n; ++i) {
         int rc = apollo_check_desc(descs[i], grad_dtype);
         if (rc) return rc;
         if (apollo_tc_eligible(descs[i], grad_dtype)) { if (apollo_umma_eligible(descs[i])) ++n_umma; else ++n_mma; }
     }
-    int iu = 0, im = n_umma, tiles_u = 0, tiles_m = 0;
+    UmmaTask *host_u = static_cast<UmmaTask *>(host_scratch);
+    ProjTask *host_m = reinterpret_cast<ProjTask *>(host_u + n_umma);
+    int iu = 0, im = 0, tiles_u = 0, tiles_m = 0;
     for (int i = 0; i < n; ++i) {
         int rc;
-        if (!apollo_tc_eligible(descs[i], grad_dtype)) rc = apollo_project_exact(descs[i], grad_dtype, st);
-        else if (apollo_umma_eligible(descs[i])) rc = apollo_project_prepare(descs[i], grad_dtype, host_tasks[iu++], tiles_u, true, st);
-        else rc = apollo_project_prepare(descs[i], grad_dtype, host_tasks[im++], tiles_m, false, st);
+        if (!apollo_tc_eligible(descs[i], grad_dtype)) {
+            rc = apollo_project_exact(descs[i], grad_dtype, st);
+        } else if (apollo_umma_eligible(descs[i])) {
+            UmmaTask &u = host_u[iu++];
+            memset(&u, 0, sizeof(u));
+            rc = apollo_project_prepare(descs[i], grad_dtype, u.t, tiles_u, true, st);
+            if (!rc) rc = apollo_umma_maps(u);
+        } else {
+            rc = apollo_project_prepare(descs[i], grad_dtype, host_m[im++], tiles_m, false, st);
+        }
         if (rc) return rc;
     }
     if (n_umma + n_mma == 0) return AF8_OK;
-    AF8_CUDA_TRY(cudaMemcpyAsync(dev_scratch, host_tasks, sizeof(ProjTask) * (size_t)(n_umma + n_mma), cudaMemcpyHostToDevice, st));
-    const ProjTask *dev_tasks = static_cast<const ProjTask *>(dev_scratch);
+    const size_t bytes = sizeof(UmmaTask) * (size_t)n_umma + sizeof(ProjTask) * (size_t)n_mma;
+    AF8_CUDA_TRY(cudaMemcpyAsync(dev_scratch, host_scratch, bytes, cudaMemcpyHostToDevice, st));
+    const UmmaTask *dev_u = static_cast<const UmmaTask *>(dev_scratch);
     if (n_umma) {
-        int rc = apollo_project_launch_umma(dev_tasks, n_umma, tiles_u, st);
+        int rc = apollo_project_launch_umma(dev_u, n_umma, tiles_u, st);
         if (rc) return rc;
     }
-    if (n_mma) return apollo_project_launch(dev_tasks + n_umma, n_mma, tiles_m, st);
+    if (n_mma) return apollo_project_launch(reinterpret_cast<const ProjTask *>(dev_u + n_umma), n_mma, tiles_m, st);
     return AF8_OK;
 }
 

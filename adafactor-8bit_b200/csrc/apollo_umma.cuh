@@ -1,48 +1,70 @@
 // APOLLO projection, "right" case (rows >= cols), on the fifth-generation tensor cores:
 //   g_low[M x N] = G[M x K] @ Pt[K x N],   M = rows, K = cols, N = rank
 // with the same three-plane bf16 split of Pt as apollo_mma.cuh.  tcgen05.mma reads both
-// operands from shared memory and accumulates in tensor memory (TMEM); one thread issues
-// the instructions, four warps feed shared memory and later drain the accumulator.
+// operands from shared memory and accumulates in tensor memory (TMEM).
 //
-// Operands are K-major without swizzle: a tile is a grid of 8-row x 16-byte "core
-// matrices" (128 contiguous bytes each); core matrices that follow one another along K are
-// 128 bytes apart (leading byte offset), 8-row groups 512 bytes apart (stride byte offset)
-// for the 32-element K step of a stage.  The gradient already has K contiguous; the planes
-// of Pt are written transposed ([N][K]) by the split kernel.
+// Operands are K-major with the 64-byte swizzle: a stage holds 32 values of K, i.e. rows of
+// 64 bytes, written by tiled bulk tensor copies (TMA) whose tensor maps use
+// CU_TENSOR_MAP_SWIZZLE_64B; the matrix descriptors name the same swizzle, 512 bytes between
+// 8-row groups, and advance by 32 bytes per 16 values of K.  The gradient already has K
+// contiguous; the planes of Pt are written transposed ([3][N][K]) by the split kernel and
+// arrive with one three-dimensional copy per stage.
 //
-// CTA = 160 threads, one CTA per SM, persistent over (task, M tile) pairs:
-//   warps 0-3  cp.async loaders (128 threads), then epilogue: tcgen05.ld of the 128 x N
-//              accumulator (warp w owns TMEM lanes 32w..32w+31) and stores to g_low
-//   warp 4     allocates / frees TMEM; its lane 0 issues the MMAs and the commits
-// Four 56 KB stages; "full" barriers are arrived on by the loaders after their copies have
-// landed and been fenced for the asynchronous proxy, "empty" barriers by tcgen05.commit.
-// Every wait is bounded (two seconds of %globaltimer); on a time-out the CTA raises the
-// device error flag, skips its remaining work, frees its TMEM and returns.
+// CTA = 320 threads, one CTA per SM, persistent over (task, M tile) pairs:
+//   warps 0-7  drain the accumulator: warp w owns TMEM lanes 32 (w % 4) .. +31 and columns
+//              128 (w / 4) .. +127, 128 totals per thread; then store g_low.  When the
+//              gradient holds non-finite values they also clean each stage before its MMAs.
+//   warp 8     allocates / frees TMEM; its lane 0 issues the MMAs and the commits
+//   warp 9     lane 0 issues the copies
+// Four 56 KB stages; a "full" barrier completes on the copies' transaction bytes, an "empty"
+// barrier on tcgen05.commit.
+//
+// The tensor cores add into their binary32 accumulators with truncation, whose error grows
+// linearly with K (measured 1.4e-5 relative at K = 4096, as with mma.sync).  The accumulation
+// is therefore cut into chunks of 256 values of K that alternate between two TMEM accumulators;
+// while one is being filled the other is added, with rounding, into the workers' registers.
+//
+// Every wait is bounded (two seconds of %globaltimer); on a time-out the thread raises the
+// device error flag and leaves; the others follow at their next wait or tile, and the tensor
+// memory is freed after all have reported (or after a bounded wait).  After the start-up
+// barrier no block-wide barrier is used, so a lost role cannot hang the others.  No copy
+// uses cluster multicast.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include "common.cuh"
 #include "fullrank_fast.cuh"     // mbarrier helpers, g_device_error
-#include "apollo_mma.cuh"        // ProjTask, cp_async16, clean_chunk
+#include "apollo_mma.cuh"        // ProjTask, clean_chunk
 
 namespace af8 {
 
-constexpr int UM_BM = 128, UM_BK = 32, UM_STAGES = 4, UM_THREADS = 288, UM_WORKERS = 256, UM_MMA_WARP = 8;
+constexpr int UM_BM = 128, UM_BK = 32, UM_STAGES = 4, UM_THREADS = 320, UM_WORKERS = 256, UM_MMA_WARP = 8, UM_TMA_WARP = 9;
 constexpr int UM_FLUSH = 8;        // stages (256 values of K) per accumulator chunk
 constexpr int UM_MAXN = 256;
-constexpr int UM_A_BYTES = UM_BM * UM_BK * 2;                 // 8 KB
-constexpr int UM_B_BYTES = UM_MAXN * UM_BK * 2;               // 16 KB per plane
+constexpr int UM_ROW_BYTES = UM_BK * 2;                       // 64
+constexpr int UM_A_BYTES = UM_BM * UM_ROW_BYTES;              // 8 KB
+constexpr int UM_B_BYTES = UM_MAXN * UM_ROW_BYTES;            // 16 KB per plane at N = 256
 constexpr int UM_STAGE_BYTES = UM_A_BYTES + 3 * UM_B_BYTES;   // 56 KB
-constexpr int UM_LBO = 128, UM_SBO = (UM_BK / 8) * 128;       // bytes
+constexpr int UM_SBO = 8 * UM_ROW_BYTES;                      // 512 bytes between 8-row groups
 constexpr int DEVERR_UMMA_TIMEOUT = 2;
+
+// One projection of a tcgen05 launch: the mma.sync task plus the two tensor maps
+struct __align__(64) UmmaTask {
+    CUtensorMap map_a;       // G as [M][K], box 128 x 32
+    CUtensorMap map_b;       // planes as [3][N][K], box 3 x N x 32
+    ProjTask t;
+    unsigned char pad[384 - 2 * sizeof(CUtensorMap) - sizeof(ProjTask)];
+};
+static_assert(sizeof(CUtensorMap) == 128 && sizeof(UmmaTask) == 384, "task layout");
 
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr)
 {
-    // start address, leading and stride byte offsets in units of 16 bytes; descriptor version 1;
-    // no swizzle (layout type 0)
-    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(UM_LBO >> 4) << 16) | ((uint64_t)(UM_SBO >> 4) << 32) |
-           (1ull << 46);
+    // start address and stride byte offset in units of 16 bytes (the leading byte offset is not
+    // used by swizzled K-major layouts); descriptor version 1; layout type 4 = 64-byte swizzle
+    return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)(UM_SBO >> 4) << 32) |
+           (1ull << 46) | (4ull << 61);
 }
 // kind::f16 instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N = n
 __device__ __forceinline__ uint32_t umma_instr_desc(int n)
@@ -65,6 +87,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// tiled bulk tensor copies global -> shared, completion as transaction bytes on `bar`
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
 
 // Pt[K][N] (fp32) -> three bf16 planes stored [N][K]
 __global__ void __launch_bounds__(256)
@@ -98,16 +131,16 @@ apollo_split_transposed_kernel(const float *__restrict__ p, int K, int N, __nv_b
 __device__ __forceinline__ int volatile_load(const int *p) { return *reinterpret_cast<const volatile int *>(p); }
 
 __global__ void __launch_bounds__(UM_THREADS, 1)
-apollo_project_umma_kernel(const ProjTask *__restrict__ tasks, int n_tasks, int total_tiles)
+apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int total_tiles)
 {
     extern __shared__ __align__(1024) unsigned char um_smem[];
-    __shared__ __align__(8) uint64_t s_full[UM_STAGES], s_empty[UM_STAGES], s_acc_full[2], s_acc_empty[2], s_done;
+    __shared__ __align__(8) uint64_t s_full[UM_STAGES], s_clean[UM_STAGES], s_empty[UM_STAGES], s_acc_full[2], s_acc_empty[2], s_done;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&s_full[s], UM_WORKERS); mbar_init(&s_empty[s], 1); }
+        for (int s = 0; s < UM_STAGES; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_clean[s], UM_WORKERS); mbar_init(&s_empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&s_acc_full[b], 1); mbar_init(&s_acc_empty[b], UM_WORKERS); }
         mbar_init(&s_done, UM_THREADS);
         s_abort = 0;
@@ -126,66 +159,36 @@ apollo_project_umma_kernel(const ProjTask *__restrict__ tasks, int n_tasks, int 
     // Running counters, advanced identically by every thread: stage fills and accumulator
     // chunks since the kernel started.  Use number n of a barrier = counter / ring size; the
     // consumer of use n waits for phase parity n & 1, the producer of use n >= 1 for (n-1) & 1.
+    // s_clean is only used by tiles of a tensor with non-finite entries; bit s of clean_phase
+    // is the parity its next consumer waits for.
     int fills = 0, gchunk = 0;
+    uint32_t clean_phase = 0;
 
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         if (volatile_load(&s_abort)) break;
         int lo = 0, hi = n_tasks - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if (__ldg(&tasks[mid].first_tile) <= tile) lo = mid; else hi = mid - 1;
+            if (__ldg(&tasks[mid].t.first_tile) <= tile) lo = mid; else hi = mid - 1;
         }
-        const ProjTask *T = tasks + lo;
+        const UmmaTask *U = tasks + lo;
+        const ProjTask *T = &U->t;
         const int M = __ldg(&T->M), N = __ldg(&T->N), K = __ldg(&T->K);
         const int m0 = (tile - __ldg(&T->first_tile)) * UM_BM;
         const int ksteps = (K + UM_BK - 1) / UM_BK;
         const int nchunks = (ksteps + UM_FLUSH - 1) / UM_FLUSH;
+        const bool dirty = __ldg(T->nonfinite_flag) != 0;      // rare: non-finite gradient entries count as zero
+        const int plane_bytes = N * UM_ROW_BYTES;
         bool failed = false;
 
         if (warp < UM_MMA_WARP) {
-            // ---------------- loaders / flushers (256 threads) ----------------
-            const __nv_bfloat16 *__restrict__ grad = T->grad;
-            const __nv_bfloat16 *__restrict__ planes = T->planes;
-            const bool dirty = __ldg(T->nonfinite_flag) != 0;
-            const int64_t plane_elems = (int64_t)K * N;
-            const int kc = tid & 3, r_in = tid >> 2;            // 16-byte chunk along K; row inside a 64-row slab
-            const uint32_t dst0 = (uint32_t)((r_in >> 3) * UM_SBO + kc * UM_LBO + (r_in & 7) * 16);
-            const __nv_bfloat16 *a_src = grad + (int64_t)(m0 + r_in) * K + kc * 8;
-            const __nv_bfloat16 *b_src = planes + (int64_t)r_in * K + kc * 8;
-            const int64_t slab = (int64_t)64 * K;               // 64 rows further down
+            // ---------------- workers (256 threads) ----------------
             // this thread's part of the accumulator: TMEM lanes 32 (warp % 4) + lane, columns 128 (warp / 4) ...
             const int row = (warp & 3) * 32 + lane, col_half = warp >> 2;
             float total[128];
 #pragma unroll
             for (int i = 0; i < 128; ++i) total[i] = 0.0f;
 
-            auto issue = [&](int ks) {
-                unsigned char *st = um_smem + ((fills + ks) % UM_STAGES) * UM_STAGE_BYTES;
-                const int k0 = ks * UM_BK;
-                const bool kv = k0 + kc * 8 < K;
-#pragma unroll
-                for (int rr = 0; rr < 2; ++rr) {                // A: 128 rows
-                    const bool v = kv && (m0 + rr * 64 + r_in < M);
-                    cp_async16(st + dst0 + rr * 8 * UM_SBO, v ? a_src + rr * slab + k0 : grad, v);
-                }
-                for (int t = 0; t < 3; ++t) {
-                    unsigned char *sb = st + UM_A_BYTES + t * UM_B_BYTES + dst0;
-                    const __nv_bfloat16 *src = b_src + t * plane_elems + k0;
-                    for (int rr = 0; rr * 64 < N; ++rr) {       // B plane t: N rows
-                        const bool v = kv && (rr * 64 + r_in < N);
-                        cp_async16(sb + rr * 8 * UM_SBO, v ? src + rr * slab : planes, v);
-                    }
-                }
-            };
-            auto publish = [&](int ks) {                        // this thread's copies of step ks have landed
-                if (dirty) {
-                    unsigned char *st = um_smem + ((fills + ks) % UM_STAGES) * UM_STAGE_BYTES;
-#pragma unroll
-                    for (int rr = 0; rr < 2; ++rr) clean_chunk(st + dst0 + rr * 8 * UM_SBO);
-                }
-                fence_proxy_async();
-                mbar_arrive(&s_full[(fills + ks) % UM_STAGES]);
-            };
             // add accumulator chunk c of this tile into the totals, with rounding, and hand the buffer back
             auto flush = [&](int c) -> bool {
                 const int g = gchunk + c, buf = g & 1;
@@ -209,31 +212,26 @@ apollo_project_umma_kernel(const ProjTask *__restrict__ tasks, int n_tasks, int 
                 mbar_arrive(&s_acc_empty[buf]);
                 return true;
             };
-
-            constexpr int LAG = UM_STAGES - 1;
-            int flushed = 0;
-            for (int ks = 0; ks < ksteps && !failed; ++ks) {
-                if (ks >= LAG) {
-                    cp_async_wait<LAG - 1>();                   // groups 0 .. ks-LAG are complete
-                    publish(ks - LAG);
+            // dirty gradients: zero the non-finite entries of the stages of chunk c before their MMAs
+            auto clean = [&](int c) -> bool {
+                const int k_end = min(ksteps, (c + 1) * UM_FLUSH);
+                for (int ks = c * UM_FLUSH; ks < k_end; ++ks) {
+                    const int f = fills + ks, slot = f % UM_STAGES;
+                    if (!mbar_wait_bounded(&s_full[slot], (uint32_t)(f / UM_STAGES) & 1u)) return false;
+                    unsigned char *st = um_smem + slot * UM_STAGE_BYTES;
+                    clean_chunk(st + tid * 16);                  // the 8 KB gradient tile: two 16-byte chunks per thread
+                    clean_chunk(st + (tid + UM_WORKERS) * 16);
+                    fence_proxy_async();
+                    mbar_arrive(&s_clean[slot]);
                 }
-                const int f = fills + ks, slot = f % UM_STAGES, use = f / UM_STAGES;
-                if (use >= 1 && !mbar_wait_bounded(&s_empty[slot], (uint32_t)(use - 1) & 1u)) { failed = true; break; }
-                issue(ks);
-                cp_async_commit();
-                // a chunk boundary: the chunk before the one just issued finished long ago
-                if ((ks % UM_FLUSH) == UM_FLUSH - 1 && flushed < ks / UM_FLUSH) {
-                    if (!flush(flushed)) { failed = true; break; }
-                    ++flushed;
-                }
+                return true;
+            };
+            for (int c = 0; c < nchunks && !failed; ++c) {
+                if (dirty && !clean(c)) { failed = true; break; }
+                if (dirty) { if (c >= 1 && !flush(c - 1)) failed = true; }
+                else if (!flush(c)) failed = true;
             }
-            cp_async_wait<0>();
-            if (!failed)
-                for (int ks = max(0, ksteps - LAG); ks < ksteps; ++ks) publish(ks);
-            while (!failed && flushed < nchunks) {
-                if (!flush(flushed)) failed = true;
-                ++flushed;
-            }
+            if (dirty && !failed && !flush(nchunks - 1)) failed = true;
             // ---------------- epilogue: the totals to g_low ----------------
             if (!failed) {
                 const int m = m0 + row;
@@ -249,32 +247,47 @@ apollo_project_umma_kernel(const ProjTask *__restrict__ tasks, int n_tasks, int 
                     }
                 }
             }
-        } else if (lane == 0) {
+        } else if (warp == UM_MMA_WARP && lane == 0) {
             // ---------------- MMA issuer ----------------
             const uint32_t idesc = umma_instr_desc(N);
+            uint32_t cph = clean_phase;
             for (int ks = 0; ks < ksteps; ++ks) {
                 const int g = gchunk + ks / UM_FLUSH, buf = g & 1;
                 const bool chunk_start = (ks % UM_FLUSH) == 0;
-                if (chunk_start && g >= 2) {                    // the flushers have drained this buffer
+                if (chunk_start && g >= 2) {                    // the workers have drained this buffer
                     if (!mbar_wait_bounded(&s_acc_empty[buf], (uint32_t)((g >> 1) - 1) & 1u)) { failed = true; break; }
                     tc_fence_after();
                 }
                 const int f = fills + ks, slot = f % UM_STAGES, use = f / UM_STAGES;
-                if (!mbar_wait_bounded(&s_full[slot], (uint32_t)use & 1u)) { failed = true; break; }
+                bool ok;
+                if (dirty) { ok = mbar_wait_bounded(&s_clean[slot], (cph >> slot) & 1u); cph ^= 1u << slot; }
+                else ok = mbar_wait_bounded(&s_full[slot], (uint32_t)use & 1u);
+                if (!ok) { failed = true; break; }
                 tc_fence_after();
                 const uint32_t a0 = smem_base + slot * UM_STAGE_BYTES;
                 const uint32_t d = tmem + (uint32_t)(buf * UM_MAXN);
 #pragma unroll
                 for (int k16 = 0; k16 < UM_BK / 16; ++k16) {
-                    const uint64_t ad = umma_smem_desc(a0 + k16 * 2 * UM_LBO);
+                    const uint64_t ad = umma_smem_desc(a0 + k16 * 32);
 #pragma unroll
                     for (int t = 2; t >= 0; --t) {              // smallest plane first
-                        const uint64_t bd = umma_smem_desc(a0 + UM_A_BYTES + t * UM_B_BYTES + k16 * 2 * UM_LBO);
+                        const uint64_t bd = umma_smem_desc(a0 + UM_A_BYTES + t * plane_bytes + k16 * 32);
                         umma_bf16(d, ad, bd, idesc, (!chunk_start || k16 > 0 || t < 2) ? 1u : 0u);
                     }
                 }
                 umma_commit(&s_empty[slot]);                    // frees the slot when these MMAs are done
                 if ((ks % UM_FLUSH) == UM_FLUSH - 1 || ks == ksteps - 1) umma_commit(&s_acc_full[buf]);
+            }
+        } else if (warp == UM_TMA_WARP && lane == 0) {
+            // ---------------- copies ----------------
+            const uint32_t bytes = (uint32_t)(UM_A_BYTES + 3 * plane_bytes);
+            for (int ks = 0; ks < ksteps; ++ks) {
+                const int f = fills + ks, slot = f % UM_STAGES, use = f / UM_STAGES;
+                if (use >= 1 && !mbar_wait_bounded(&s_empty[slot], (uint32_t)(use - 1) & 1u)) { failed = true; break; }
+                unsigned char *st = um_smem + slot * UM_STAGE_BYTES;
+                mbar_expect_tx(&s_full[slot], bytes);
+                tma_load_2d(st, &U->map_a, ks * UM_BK, m0, &s_full[slot]);
+                tma_load_3d(st + UM_A_BYTES, &U->map_b, ks * UM_BK, 0, 0, &s_full[slot]);
             }
         }
         if (failed) {
@@ -282,6 +295,8 @@ apollo_project_umma_kernel(const ProjTask *__restrict__ tasks, int n_tasks, int 
             atomicExch(&g_device_error, DEVERR_UMMA_TIMEOUT);
             break;
         }
+        if (dirty)
+            for (int ks = 0; ks < ksteps; ++ks) clean_phase ^= 1u << ((fills + ks) % UM_STAGES);
         fills += ksteps;
         gchunk += nchunks;
     }
