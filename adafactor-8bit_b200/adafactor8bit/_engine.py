@@ -590,6 +590,12 @@ class ApolloPlan:
         self.h_tasks = _PinnedRing(task_bytes)
         self.d_tasks = torch.empty(task_bytes, dtype=torch.uint8, device=dev)
         self.descs = np.zeros(self.n, dtype=N.APOLLO_PROJ_DESC)
+        # room for transposed gradients of left-case tensors (rows < cols): the largest one, or
+        # 256 MB when several fit, so that they reach the tcgen05 kernel a few at a time
+        left = [r * c * 2 for r, c in zip(self.rows, self.cols) if r < c]
+        self.t_bytes = 0 if (not left or grad_dtype != torch.bfloat16) else (max(max(left), min(sum(left), 256 << 20)) + 255) // 256 * 256 + 256 * len(left)
+        self.t_scratch = torch.empty(self.t_bytes + 256, dtype=torch.uint8, device=dev) if self.t_bytes else None
+        self.t_ptr = (self.t_scratch.data_ptr() + 255) // 256 * 256 if self.t_bytes else 0
         self.sf = [torch.empty(n, dtype=torch.float32, device=dev) for n in self.nch]
         self.sums = torch.zeros(3 * self.n, dtype=torch.float64, device=dev)
         self.out = torch.zeros(4 * self.n, dtype=torch.float32, device=dev)
@@ -636,7 +642,7 @@ class ApolloPlan:
             d["rows"][i], d["cols"][i], d["rank"][i], d["negate"][i] = self.rows[i], self.cols[i], self.rank, self.negate
         h_tasks = self.h_tasks.next()
         N.check(lib.af8_apollo_project_batch(d.ctypes.data, self.n, self.grad_dtype, h_tasks.data_ptr(),
-                                             self.d_tasks.data_ptr(), s), "af8_apollo_project_batch")
+                                             self.d_tasks.data_ptr(), self.t_ptr, self.t_bytes, s), "af8_apollo_project_batch")
         self.h_tasks.mark(stream)
         if log is not None:
             ev[1].record(stream)

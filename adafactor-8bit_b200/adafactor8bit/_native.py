@@ -134,7 +134,7 @@ PROTOTYPES = {
     "af8_apollo_project_workspace": (ctypes.c_int64, [_c_l, _c_l, _c_l]),
     "af8_apollo_project_ws": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_l, _c_l, _c_l, _c_p, _c_p, _c_p, _c_l, _c_p]),
     "af8_apollo_project_task_bytes": (ctypes.c_int32, []),
-    "af8_apollo_project_batch": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p]),
+    "af8_apollo_project_batch": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p, _c_l, _c_p]),
     "af8_apollo_scales": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn), _c_p, _c_p, _c_p,
                                  _c_p, _c_p]),
     "af8_apollo_apply": (_c_i, [_c_p, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn),

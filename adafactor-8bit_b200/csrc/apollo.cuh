@@ -477,13 +477,23 @@ inline int apollo_project_exact(const af8_apollo_proj_desc &d, int32_t grad_dtyp
 
 // tensor-core path, per tensor: non-finite flag + channel norms, bf16 planes of Pt; fills the task
 // true: this projection runs on tcgen05 (right case, rank a multiple of 16 up to 256)
-inline bool apollo_umma_eligible(const af8_apollo_proj_desc &d)
+// bytes of the transposed gradient that a left-case tensor needs on the tcgen05 path
+inline int64_t apollo_transpose_need(const af8_apollo_proj_desc &d)
 {
-    static const bool disabled = getenv("AF8_NO_UMMA") != nullptr;
-    return !disabled && d.rows >= d.cols && d.rank % 16 == 0 && d.rank >= 16 && d.rank <= UM_MAXN;
+    return d.rows >= d.cols ? 0 : (d.rows * d.cols * 2 + 255) / 256 * 256;
 }
 
-inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dtype, ProjTask &task, int &next_tile, bool umma, cudaStream_t st)
+// true: this projection runs on tcgen05 (rank a multiple of 16 up to 256; the left case also
+// needs room for the transposed gradient, because the kernel takes both operands K-major)
+inline bool apollo_umma_eligible(const af8_apollo_proj_desc &d, int64_t transpose_bytes)
+{
+    static const bool disabled = getenv("AF8_NO_UMMA") != nullptr;
+    return !disabled && d.rank % 16 == 0 && d.rank >= 16 && d.rank <= UM_MAXN && apollo_transpose_need(d) <= transpose_bytes;
+}
+
+// gt: where the transposed gradient of a left-case tcgen05 task goes (nullptr otherwise)
+inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dtype, ProjTask &task, int &next_tile, bool umma,
+                                  cudaStream_t st, void *gt = nullptr)
 {
     int *flag = static_cast<int *>(d.workspace);
     __nv_bfloat16 *planes = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(d.workspace) + APOLLO_WS_HEADER);
@@ -493,16 +503,23 @@ inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dt
     const bool right = d.rows >= d.cols;
     const int64_t kdim = right ? d.cols : d.rows;
     const int64_t pn = kdim * d.rank;
-    if (umma) {                                              // planes transposed to [rank][cols]
+    if (umma && right) {                                     // planes transposed to [rank][cols]
         dim3 grid((unsigned)((kdim + 31) / 32), (unsigned)((d.rank + 31) / 32));
         apollo_split_transposed_kernel<<<grid, 256, 0, st>>>(d.pt, (int)kdim, (int)d.rank, planes);
-    } else {
+    } else {                                                 // Pt is [rank][rows] already in the left case
         int64_t sg = (pn + 255) / 256;
         if (sg > 148 * 8) sg = 148 * 8;
         apollo_split_kernel<<<(int)sg, 256, 0, st>>>(d.pt, pn, planes);
     }
     AF8_CUDA_TRY(cudaGetLastError());
     task.grad = static_cast<const __nv_bfloat16 *>(d.grad);
+    if (umma && !right) {                                    // the kernel reads G^T [cols][rows]
+        dim3 grid((unsigned)((d.cols + 63) / 64), (unsigned)((d.rows + 63) / 64));
+        apollo_transpose_bf16_kernel<<<grid, 256, 0, st>>>(static_cast<const uint16_t *>(d.grad), (int)d.rows, (int)d.cols,
+                                                            static_cast<uint16_t *>(gt));
+        AF8_CUDA_TRY(cudaGetLastError());
+        task.grad = static_cast<const __nv_bfloat16 *>(gt);
+    }
     task.planes = planes;
     task.out = d.g_low;
     task.nonfinite_flag = flag;
@@ -617,7 +634,7 @@ extern "C" int af8_apollo_project_ws(const void *grad, int32_t grad_dtype, int32
     if (!apollo_tc_eligible(d, grad_dtype)) return apollo_project_exact(d, grad_dtype, st);
     ProjTask task;
     int tiles = 0;
-    const bool umma = apollo_umma_eligible(d);
+    const bool umma = apollo_umma_eligible(d, 0);            // no room for a transposed gradient here: right case only
     rc = apollo_project_prepare(d, grad_dtype, task, tiles, umma, st);
     if (rc) return rc;
     // the task lives in the workspace between the flag and the planes; the copy from this
@@ -639,7 +656,8 @@ extern "C" int af8_apollo_project_ws(const void *grad, int32_t grad_dtype, int32
 extern "C" int32_t af8_apollo_project_task_bytes(void) { return (int32_t)sizeof(af8::UmmaTask); }
 
 extern "C" int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32_t n, int32_t grad_dtype,
-                                        void *host_scratch, void *dev_scratch, void *stream)
+                                        void *host_scratch, void *dev_scratch, void *transpose_scratch,
+                                        int64_t transpose_bytes, void *stream)
 {
     using namespace af8;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -649,38 +667,61 @@ extern "C" int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32
     // each kind is one launch.  The scratch holds n slots of sizeof(UmmaTask), 64-byte aligned.
     if ((reinterpret_cast<uintptr_t>(host_scratch) & 63u) || (reinterpret_cast<uintptr_t>(dev_scratch) & 63u))
         return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: scratch buffers must be 64-byte aligned");
+    if (transpose_bytes > 0 && (!transpose_scratch || (reinterpret_cast<uintptr_t>(transpose_scratch) & 255u)))
+        return fail(AF8_ERR_INVALID, "af8_apollo_project_batch: transpose_scratch must be 256-byte aligned");
     int n_umma = 0, n_mma = 0;
     for (int i = 0; i < n; ++i) {
         int rc = apollo_check_desc(descs[i], grad_dtype);
         if (rc) return rc;
-        if (apollo_tc_eligible(descs[i], grad_dtype)) { if (apollo_umma_eligible(descs[i])) ++n_umma; else ++n_mma; }
+        if (apollo_tc_eligible(descs[i], grad_dtype)) { if (apollo_umma_eligible(descs[i], transpose_bytes)) ++n_umma; else ++n_mma; }
     }
     UmmaTask *host_u = static_cast<UmmaTask *>(host_scratch);
+    const UmmaTask *dev_u = static_cast<const UmmaTask *>(dev_scratch);
     ProjTask *host_m = reinterpret_cast<ProjTask *>(host_u + n_umma);
     int iu = 0, im = 0, tiles_u = 0, tiles_m = 0;
+    // The tcgen05 tasks go out in sub-batches: a new one starts when the transposed gradients
+    // of the left-case tensors would no longer fit the scratch (stream order makes its reuse safe).
+    int sub_start = 0;
+    int64_t t_off = 0;
+    auto launch_sub = [&](int end) -> int {
+        if (end > sub_start) {
+            AF8_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(dev_scratch) + sizeof(UmmaTask) * (size_t)sub_start, host_u + sub_start,
+                                         sizeof(UmmaTask) * (size_t)(end - sub_start), cudaMemcpyHostToDevice, st));
+            int rc = apollo_project_launch_umma(dev_u + sub_start, end - sub_start, tiles_u, st);
+            if (rc) return rc;
+        }
+        sub_start = end;
+        tiles_u = 0;
+        t_off = 0;
+        return AF8_OK;
+    };
     for (int i = 0; i < n; ++i) {
         int rc;
         if (!apollo_tc_eligible(descs[i], grad_dtype)) {
             rc = apollo_project_exact(descs[i], grad_dtype, st);
-        } else if (apollo_umma_eligible(descs[i])) {
+        } else if (apollo_umma_eligible(descs[i], transpose_bytes)) {
+            const int64_t need = apollo_transpose_need(descs[i]);
+            if (need > 0 && t_off + need > transpose_bytes) {
+                rc = launch_sub(iu);
+                if (rc) return rc;
+            }
             UmmaTask &u = host_u[iu++];
             memset(&u, 0, sizeof(u));
-            rc = apollo_project_prepare(descs[i], grad_dtype, u.t, tiles_u, true, st);
+            rc = apollo_project_prepare(descs[i], grad_dtype, u.t, tiles_u, true, st, need > 0 ? static_cast<char *>(transpose_scratch) + t_off : nullptr);
+            t_off += need;
             if (!rc) rc = apollo_umma_maps(u);
         } else {
             rc = apollo_project_prepare(descs[i], grad_dtype, host_m[im++], tiles_m, false, st);
         }
         if (rc) return rc;
     }
-    if (n_umma + n_mma == 0) return AF8_OK;
-    const size_t bytes = sizeof(UmmaTask) * (size_t)n_umma + sizeof(ProjTask) * (size_t)n_mma;
-    AF8_CUDA_TRY(cudaMemcpyAsync(dev_scratch, host_scratch, bytes, cudaMemcpyHostToDevice, st));
-    const UmmaTask *dev_u = static_cast<const UmmaTask *>(dev_scratch);
-    if (n_umma) {
-        int rc = apollo_project_launch_umma(dev_u, n_umma, tiles_u, st);
-        if (rc) return rc;
+    int rc = launch_sub(iu);
+    if (rc) return rc;
+    if (n_mma) {
+        ProjTask *dev_m = reinterpret_cast<ProjTask *>(static_cast<char *>(dev_scratch) + sizeof(UmmaTask) * (size_t)n_umma);
+        AF8_CUDA_TRY(cudaMemcpyAsync(dev_m, host_m, sizeof(ProjTask) * (size_t)n_mma, cudaMemcpyHostToDevice, st));
+        return apollo_project_launch(dev_m, n_mma, tiles_m, st);
     }
-    if (n_mma) return apollo_project_launch(reinterpret_cast<const ProjTask *>(dev_u + n_umma), n_mma, tiles_m, st);
     return AF8_OK;
 }
 

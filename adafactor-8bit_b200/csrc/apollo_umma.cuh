@@ -99,6 +99,31 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
                  ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
 }
 
+// G[R][C] (bf16) -> G^T[C][R], non-finite entries replaced by zero (optimizer.py:2606).
+// 64 x 64 tiles through shared memory, two elements per thread and access.  R and C even.
+__global__ void __launch_bounds__(256)
+apollo_transpose_bf16_kernel(const uint16_t *__restrict__ in, int R, int C, uint16_t *__restrict__ out)
+{
+    __shared__ uint16_t tile[64][66];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 pairs x 8 rows
+    for (int i = ty; i < 64; i += 8) {
+        const int r = r0 + i, c = c0 + 2 * tx;
+        uint32_t w = 0;
+        if (r < R && c < C) w = __ldg(reinterpret_cast<const uint32_t *>(in + (int64_t)r * C + c));
+        if ((w & 0x7f80u) == 0x7f80u) w &= 0xffff0000u;
+        if ((w & 0x7f800000u) == 0x7f800000u) w &= 0x0000ffffu;
+        tile[i][2 * tx] = (uint16_t)w;
+        tile[i][2 * tx + 1] = (uint16_t)(w >> 16);
+    }
+    __syncthreads();
+    for (int i = ty; i < 64; i += 8) {
+        const int c = c0 + i, r = r0 + 2 * tx;
+        if (c < C && r < R)
+            *reinterpret_cast<uint32_t *>(out + (int64_t)c * R + r) = (uint32_t)tile[2 * tx][i] | ((uint32_t)tile[2 * tx + 1][i] << 16);
+    }
+}
+
 // Pt[K][N] (fp32) -> three bf16 planes stored [N][K]
 __global__ void __launch_bounds__(256)
 apollo_split_transposed_kernel(const float *__restrict__ p, int K, int N, __nv_bfloat16 *__restrict__ planes)
@@ -237,13 +262,21 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
                 const int m = m0 + row;
                 const float sgn = __ldg(&T->negate) ? -1.0f : 1.0f;
                 float *__restrict__ out = T->out;
-                if (m < M) {
+                if (m < M && __ldg(&T->right)) {
 #pragma unroll
                     for (int q = 0; q < 32; ++q) {
                         const int n = col_half * 128 + q * 4;
                         if (n < N)
                             *reinterpret_cast<float4 *>(out + (int64_t)m * N + n) =
                                 make_float4(sgn * total[4 * q], sgn * total[4 * q + 1], sgn * total[4 * q + 2], sgn * total[4 * q + 3]);
+                    }
+                } else if (m < M) {
+                    // left case computed as the transposed problem: g_low is [N][M]; a warp's 32
+                    // rows are consecutive addresses of one output row
+#pragma unroll
+                    for (int e = 0; e < 128; ++e) {
+                        const int n = col_half * 128 + e;
+                        if (n < N) out[(int64_t)n * M + m] = sgn * total[e];
                     }
                 }
             }

@@ -373,8 +373,12 @@ AF8_API int af8_apollo_project_ws(const void *grad, int32_t grad_dtype, int32_t 
 /* Many projections in one call.  Every descriptor that qualifies for the tensor-core path
  * (see af8_apollo_project_ws) joins ONE launch over the tiles of all tensors, which keeps
  * the GPU full when a single matrix has fewer tiles than there are SMs; the others take
- * the exact path one by one.  host_scratch (pinned, valid until the copy has run) and
- * dev_scratch each hold n * af8_apollo_project_task_bytes() bytes. */
+ * the exact path one by one.  host_scratch (pinned, valid until the copies have run) and
+ * dev_scratch each hold n * af8_apollo_project_task_bytes() bytes, 64-byte aligned.
+ * transpose_scratch (device, 256-byte aligned, may be NULL with transpose_bytes 0) lets
+ * left-case tensors (rows < cols) use the tcgen05 kernel, which wants both operands with the
+ * contracted dimension contiguous: their gradients are transposed into it, as many tensors at
+ * a time as fit; a tensor whose transposed gradient does not fit stays on the mma.sync kernel. */
 typedef struct af8_apollo_proj_desc {
     const void *grad;       /* rows x cols */
     const float *pt;        /* cols x rank (rows >= cols) or rank x rows */
@@ -388,7 +392,8 @@ typedef struct af8_apollo_proj_desc {
 } af8_apollo_proj_desc;
 AF8_API int32_t af8_apollo_project_task_bytes(void);
 AF8_API int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32_t n, int32_t grad_dtype,
-                                     void *host_scratch, void *dev_scratch, void *stream);
+                                     void *host_scratch, void *dev_scratch, void *transpose_scratch,
+                                     int64_t transpose_bytes, void *stream);
 
 /* Scaling factors sf[channel] = ||update_low|| / (||g_low|| + 1e-8) (one entry
  * for the tensor-wide variant), the global norm, the Fira limiter, the clip

@@ -116,6 +116,50 @@ def test_tensor_core_projection(rows, cols, rank, negate):
     assert np.allclose(chan.cpu().numpy(), want_ch, rtol=1e-12)
 
 
+def test_tensor_core_projection_batch():
+    """af8_apollo_project_batch over mixed shapes: right-case tensors and, through the transposed
+    gradient, left-case ones on the tcgen05 kernel; a rank that is no multiple of 16 on mma.sync;
+    a scratch too small for the last tensor, which then stays on mma.sync as well."""
+    from adafactor8bit import _native as N
+    lib = N.lib()
+    rng = np.random.default_rng(5)
+    shapes = [(512, 256, 64), (128, 640, 64), (64, 1032, 32), (264, 136, 24), (96, 2048, 256)]
+    stream = torch.cuda.current_stream().cuda_stream
+    descs = np.zeros(len(shapes), dtype=N.APOLLO_PROJ_DESC)
+    keep, wants, outs = [], [], []
+    for i, (rows, cols, rank) in enumerate(shapes):
+        g = torch.from_numpy((rng.standard_normal((rows, cols)) * 1e-3).astype(np.float32)).to(torch.bfloat16)
+        g[1, 2] = float("nan")
+        right = rows >= cols
+        pt = (rng.standard_normal((cols, rank) if right else (rank, rows)) / np.sqrt(rank)).astype(np.float32)
+        gc = g.to(torch.float32).numpy().astype(np.float64)
+        gc = np.where(np.isfinite(gc), gc, 0.0)
+        wants.append(gc @ pt.astype(np.float64) if right else pt.astype(np.float64) @ gc)
+        d_g, d_pt = g.cuda(), torch.from_numpy(pt).cuda()
+        out = torch.full((wants[-1].size,), float("nan"), dtype=torch.float32, device="cuda")
+        chan = torch.empty(max(rows, cols), dtype=torch.float64, device="cuda")
+        nbytes = int(lib.af8_apollo_project_workspace(rows, cols, rank))
+        ws = torch.empty(nbytes + 256, dtype=torch.uint8, device="cuda")
+        keep += [d_g, d_pt, chan, ws]
+        outs.append(out)
+        descs["grad"][i], descs["pt"][i], descs["g_low"][i], descs["chan_g2"][i] = d_g.data_ptr(), d_pt.data_ptr(), out.data_ptr(), chan.data_ptr()
+        descs["workspace"][i], descs["workspace_bytes"][i] = (ws.data_ptr() + 255) // 256 * 256, nbytes
+        descs["rows"][i], descs["cols"][i], descs["rank"][i] = rows, cols, rank
+    tb = int(lib.af8_apollo_project_task_bytes()) * len(shapes)
+    h = torch.empty(tb, dtype=torch.uint8).pin_memory()
+    d = torch.empty(tb, dtype=torch.uint8, device="cuda")
+    t_bytes = 200 * 1024                      # fits tensors 1 and 2 one at a time (160 KB, 129 KB), not tensor 4 (384 KB)
+    t = torch.empty(t_bytes + 256, dtype=torch.uint8, device="cuda")
+    N.check(lib.af8_apollo_project_batch(descs.ctypes.data, len(shapes), N.BF16, h.data_ptr(), d.data_ptr(),
+                                         (t.data_ptr() + 255) // 256 * 256, t_bytes, stream), "project_batch")
+    torch.cuda.synchronize()
+    assert N.device_status(stream) == 0
+    for (rows, cols, rank), want, out in zip(shapes, wants, outs):
+        got = out.cpu().numpy().reshape(want.shape).astype(np.float64)
+        assert np.isfinite(got).all(), (rows, cols, rank)
+        assert np.abs(got - want).max() <= 4e-6 * np.abs(want).max(), (rows, cols, rank, float(np.abs(got - want).max() / np.abs(want).max()))
+
+
 def test_projection_is_correctly_rounded():
     """af8_apollo_project against a binary64 matmul, both sides."""
     from adafactor8bit import _native as N
