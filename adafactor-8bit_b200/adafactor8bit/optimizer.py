@@ -223,6 +223,10 @@ class Adafactor8Bit(Optimizer):
                  for idx, st in state_dict["state"].items()}
         saved_vals = {idx: {k: v for k, v in st.items() if isinstance(v, Tensor)}
                       for idx, st in state_dict["state"].items()}
+        # ... and it rebuilds every iterable value element by element, which turns the format
+        # names (strings) and shapes into garbage: keep the saved non-tensor values as they are
+        saved_plain = {idx: {k: v for k, v in st.items() if not isinstance(v, Tensor)}
+                       for idx, st in state_dict["state"].items()}
         super().load_state_dict(state_dict)
         idx_of = {}
         i = 0
@@ -240,6 +244,9 @@ class Adafactor8Bit(Optimizer):
             for k, dt in src.items():
                 if k in st and isinstance(st[k], Tensor) and st[k].dtype != dt:
                     st[k] = vals[k].to(device=p.device, dtype=dt).clone()
+            plain = saved_plain.get(idx, saved_plain.get(str(idx))) or {}
+            for k, v in plain.items():
+                st[k] = v
             if "step" in st and isinstance(st["step"], Tensor):
                 st["step"] = int(st["step"].item())
         del keys
