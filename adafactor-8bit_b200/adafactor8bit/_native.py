@@ -19,7 +19,8 @@ V_FP32, V_AL8, V_AL16 = 0, 8, 16
 M_NONE, M_UF8, M_UF4, M_D8, M_D4, M_FP32 = 0, 1, 2, 3, 4, 5
 MODE_NOCLIP, MODE_SUMSQ, MODE_APPLY, MODE_SUMSQ_M = 0, 1, 2, 3
 
-V_FMT = {"fp32": V_FP32, "al8": V_AL8, "al16": V_AL16}
+V_NONE = 1
+V_FMT = {"fp32": V_FP32, "al8": V_AL8, "al16": V_AL16, "none": V_NONE}
 M_FMT = {None: M_NONE, "uf8": M_UF8, "uf4": M_UF4, "d8": M_D8, "d4": M_D4, "fp32": M_FP32}
 
 _P = np.uint64   # device / host pointers inside tables

@@ -403,8 +403,15 @@ class Adafactor8Bit(Optimizer):
         sgd = group["beta2"] is None and group["beta2_decay"] is None
         fullrank, factored_items, apollo_items = {}, {}, []
         for p, g, st in entries:
-            if sgd:
-                raise NotImplementedError("the SGD preset is not available in this build")
+            if sgd:                 # optimizer.py:2045-2071: no second moment, every shape takes the flat path
+                if group.get("beta1") is not None:
+                    m_fmt = "fp32" if "m" in st else st.get("m_quant_type", "uf8")
+                    m_block = st.get("m_block_size", group.get("m_block_size", 256))
+                else:
+                    m_fmt, m_block = None, 0
+                key = (p.device, g.dtype, "none", m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block)
+                fullrank.setdefault(key, []).append((p, g, st))
+                continue
             if apollo_rank > 0 and "apollo_seed" in st:
                 if g.dim() != 2:
                     raise NotImplementedError("APOLLO tensors with more than two dimensions are not available in this build")
@@ -617,6 +624,9 @@ class Adafactor8Bit(Optimizer):
         momentum_only = group.get("momentum_only_1d")
         if momentum_only is None:
             momentum_only = not sc0["adam"]
+        sgd = v_fmt == "none"
+        if sgd:
+            momentum_only = False
         ids = tuple(id(p) for p, _, _ in items)
         pkey = (gi, "fullrank", key, bool(momentum_only), bool(group["maximize"]))
         plan = self._plans.get(pkey)
@@ -643,7 +653,8 @@ class Adafactor8Bit(Optimizer):
                 sc = self._step_scalars(group, step)
                 alpha, decay = self._alpha_decay(group, sc)
                 bv = sc["beta_val"]
-                vals = (decay, alpha, f32(bv), f32(1.0 - bv), f32(bv * sc["eps_gradsq"]),
+                keep = f32(1.0 - group["beta1"]) if (sgd and group.get("beta1") is not None) else f32(1.0 - bv)
+                vals = (decay, alpha, f32(bv), keep, f32(bv * sc["eps_gradsq"]),
                         f32(1.0 - group["beta1"]) if group.get("beta1") is not None else f32(0.0),
                         f32(sc["eps_gradsq"]), f32(sc["eps_denom"]), f32(sc["eps_sq"]))
                 cache[step] = vals

@@ -167,7 +167,8 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline int validate_fullrank_table(const af8_fullrank_cfg &c, const af8_fullrank_tensor *T, int n, int64_t total_blocks)
 {
     int64_t next = 0;
-    const bool v_quant = c.v_fmt != AF8_V_FP32;
+    const bool no_v = c.v_fmt == AF8_V_NONE;
+    const bool v_quant = c.v_fmt != AF8_V_FP32 && !no_v;
     const bool has_m = c.m_fmt != AF8_M_NONE;
     const bool m_quant = has_m && c.m_fmt != AF8_M_FP32;
     for (int i = 0; i < n; ++i) {
@@ -181,9 +182,10 @@ inline int validate_fullrank_table(const af8_fullrank_cfg &c, const af8_fullrank
         if (v_quant) {
             if (!t.v_q || !t.v_scale || !t.v_min_log) return fail(AF8_ERR_INVALID, "tensor %d: null quantised V state", i);
             if (!aligned16(t.v_q)) return fail(AF8_ERR_INVALID, "tensor %d: v_q must be 16-byte aligned", i);
-        } else if (!t.v_f32) {
+        } else if (!no_v && !t.v_f32) {
             return fail(AF8_ERR_INVALID, "tensor %d: null fp32 V state", i);
         }
+        if (no_v && has_m && !(t.v_keep > 0.0f)) return fail(AF8_ERR_INVALID, "tensor %d: the SGD mode needs v_keep = 1 - beta1 > 0", i);
         if (m_quant) {
             if (!t.m_q || !t.m_scale) return fail(AF8_ERR_INVALID, "tensor %d: null quantised M state", i);
             if (!aligned16(t.m_q)) return fail(AF8_ERR_INVALID, "tensor %d: m_q must be 16-byte aligned", i);
@@ -207,7 +209,7 @@ extern "C" int af8_fullrank_step(const af8_fullrank_cfg *cfg, const af8_fullrank
     const af8_fullrank_cfg &c = *cfg;
     if (c.param_dtype != AF8_F32) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: only fp32 parameters are supported");
     if (c.grad_dtype != AF8_F32 && c.grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: gradients must be fp32 or bf16");
-    if (c.v_fmt != AF8_V_FP32 && c.v_fmt != AF8_V_AL8 && c.v_fmt != AF8_V_AL16) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad v_fmt %d", c.v_fmt);
+    if (c.v_fmt != AF8_V_FP32 && c.v_fmt != AF8_V_AL8 && c.v_fmt != AF8_V_AL16 && c.v_fmt != AF8_V_NONE) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad v_fmt %d", c.v_fmt);
     if (c.m_fmt < AF8_M_NONE || c.m_fmt > AF8_M_FP32) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad m_fmt %d", c.m_fmt);
     if (c.block < 128 || c.block % 128 != 0) return fail(AF8_ERR_INVALID, "af8_fullrank_step: block must be a multiple of 128, >= 128 (got %d)", c.block);
     if (c.block > GEN_MAX_BLOCK) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: block %d exceeds the supported maximum %d", c.block, GEN_MAX_BLOCK);

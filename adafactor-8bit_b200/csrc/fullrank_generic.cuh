@@ -96,7 +96,8 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const bool v_quant = C.v_fmt != AF8_V_FP32;
+    const bool no_v = C.v_fmt == AF8_V_NONE;     // SGD mode: no second moment (optimizer.py:2045-2071)
+    const bool v_quant = C.v_fmt != AF8_V_FP32 && !no_v;
     const bool has_m = C.m_fmt != AF8_M_NONE;
     const bool m_quant = has_m && C.m_fmt != AF8_M_FP32;
     const bool writes = (MODE == AF8_MODE_NOCLIP || MODE == AF8_MODE_APPLY);
@@ -147,7 +148,8 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                 float gj = GradLoad<GradT>::load1(sT.grad, base + i);
                 if (L.negate_grad) gj = -gj;
                 // ---- second moment ----
-                if (v_quant) {   // optimizer.py:2117-2119
+                if (no_v) {
+                } else if (v_quant) {   // optimizer.py:2117-2119
                     uint32_t code = (C.v_fmt == AF8_V_AL16)
                                         ? static_cast<const uint16_t *>(sT.v_q)[base + i]
                                         : static_cast<const uint8_t *>(sT.v_q)[base + i];
@@ -162,7 +164,8 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                 }
                 // ---- normaliser ----
                 float inv = 0.0f, den = 1.0f;
-                if (C.use_adam_denom) {
+                if (no_v) {
+                } else if (C.use_adam_denom) {
                     den = __fadd_rn(__fsqrt_rn(vj), sT.eps_denom);   // optimizer.py:905, 913
                     inv = __frcp_rn(den);
                 } else {
@@ -170,7 +173,10 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                 }
                 // ---- momentum and update ----
                 float u;
-                if (has_m) {
+                if (no_v && !has_m) {
+                    u = gj;                     // optimizer.py:2065-2066
+                    if (MODE == AF8_MODE_SUMSQ) acc = __fmaf_rn(u, u, acc);
+                } else if (has_m) {
                     float m_old;
                     if (m_quant) {
                         const int64_t sb = (base + i) / C.m_block;
@@ -178,7 +184,11 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                     } else {
                         m_old = sT.m_f32[base + i];
                     }
-                    if (C.momentum_only) {      // optimizer.py:894-901
+                    if (no_v) {                 // optimizer.py:2047-2064: momentum / float(1 - beta1), kept in v_keep
+                        mj = lerp_t(m_old, gj, sT.m_w);
+                        u = __fdiv_rn(mj, sT.v_keep);
+                        if (MODE == AF8_MODE_SUMSQ) acc = __fmaf_rn(u, u, acc);
+                    } else if (C.momentum_only) {      // optimizer.py:894-901
                         float ut = __fmul_rn(gj, inv);
                         if (MODE == AF8_MODE_SUMSQ) {
                             acc = __fmaf_rn(ut, ut, acc);

@@ -50,7 +50,8 @@ enum { AF8_F32 = 0, AF8_BF16 = 1, AF8_F16 = 2 };
 
 /* second-moment / confidence state formats (v_quant_type, c_quant_type;
  * optimizer.py:25) */
-enum { AF8_V_FP32 = 0, AF8_V_AL8 = 8, AF8_V_AL16 = 16 };
+enum { AF8_V_FP32 = 0, AF8_V_AL8 = 8, AF8_V_AL16 = 16,
+       AF8_V_NONE = 1 };  /* no second moment: the SGD mode (beta2 and beta2_decay both None) */
 
 /* momentum state formats (m_quant_type; optimizer.py:24); NONE = beta1 is None */
 enum { AF8_M_NONE = 0, AF8_M_UF8 = 1, AF8_M_UF4 = 2, AF8_M_D8 = 3, AF8_M_D4 = 4, AF8_M_FP32 = 5 };
@@ -123,7 +124,8 @@ typedef struct af8_fullrank_tensor {
     float decay;            /* 1 - wd_mult*wd; 1.0 when weight_decay == 0 */
     float alpha;            /* step size with bias correction folded in */
     float v_w;              /* second-moment EMA weight beta_val */
-    float v_keep;           /* float(1 - beta_val), used by the fp32 V state */
+    float v_keep;           /* float(1 - beta_val), used by the fp32 V state; with AF8_V_NONE:
+                               float(1 - beta1), the divisor of the momentum */
     float v_eps_add;        /* float(beta_val * eps_for_grad_sq), fp32 V state */
     float m_w;              /* float(1 - beta1) */
     float eps_gradsq;       /* added to g*g (0 in Adam mode) */

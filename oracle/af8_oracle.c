@@ -48,7 +48,7 @@
 #define LOG_QUANT_FLOOR 1.17549435e-38f
 
 /* state formats */
-enum { AF8O_V_FP32 = 0, AF8O_V_AL8 = 8, AF8O_V_AL16 = 16 };
+enum { AF8O_V_FP32 = 0, AF8O_V_AL8 = 8, AF8O_V_AL16 = 16, AF8O_V_NONE = 1 };   /* NONE: the SGD mode, no second moment */
 enum { AF8O_M_NONE = 0, AF8O_M_UF8 = 1, AF8O_M_UF4 = 2, AF8O_M_D8 = 3, AF8O_M_D4 = 4, AF8O_M_FP32 = 5 };
 enum { AF8O_G_F32 = 0, AF8O_G_BF16 = 1 };
 
@@ -387,7 +387,8 @@ typedef struct {
     float decay;          /* 1 - wd_mult*wd (optimizer.py:2034-2039) */
     float alpha;          /* optimizer.py:2018-2030 */
     float v_w;            /* beta_val as the lerp weight (optimizer.py:2012-2017) */
-    float v_keep;         /* float(1.0 - beta_val), fp32-state path (optimizer.py:2187) */
+    float v_keep;         /* float(1.0 - beta_val), fp32-state path (optimizer.py:2187);
+                             with AF8O_V_NONE: float(1.0 - beta1), the divisor of the momentum (optimizer.py:2064) */
     float v_eps_add;      /* float(beta_val*eps_for_grad_sq) (optimizer.py:2189) */
     float m_w;            /* float(1.0 - beta1) (optimizer.py:698) */
     float eps_gradsq;     /* optimizer.py:1967 */
@@ -453,6 +454,35 @@ AF8O_API int af8o_fullrank_step(const af8o_fullrank_cfg *c, float *p,
     const int64_t n = c->numel;
     const int has_m = c->m_fmt != AF8O_M_NONE;
     const int m_quant = has_m && c->m_fmt != AF8O_M_FP32;
+    if (c->v_fmt == AF8O_V_NONE) {
+        /* SGD mode (optimizer.py:2045-2071): no second moment; the update is the gradient, or
+         * the momentum divided by float(1 - beta1); then the common _apply_update_pytorch */
+        float *gs = (float *)malloc((size_t)(n ? n : 1) * sizeof(float));
+        float *us = (float *)malloc((size_t)(n ? n : 1) * sizeof(float));
+        if (!gs || !us) { free(gs); free(us); return 2; }
+        int rcs = 0;
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            gs[i] = load_grad(grad, c->grad_dtype, i, c->negate_grad);
+            if (c->has_decay) p[i] = p[i] * c->decay;
+        }
+        if (has_m) {
+            float *m = m_quant ? us : m_f32;
+            if (m_quant) af8o_m_dequantize(m_q, m_scale, n, c->m_block, c->m_fmt, map, m);
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < n; ++i) m[i] = lerp_t(m[i], gs[i], c->m_w);
+            if (m_quant) rcs = af8o_m_quantize(m, n, c->m_block, c->m_fmt, map, m_q, m_scale);
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < n; ++i) us[i] = m[i] / c->v_keep;
+        } else {
+            memcpy(us, gs, (size_t)n * sizeof(float));
+        }
+        float norms = apply_update(p, us, n, c->alpha, c->d, c->clip_div, c->fira, c->fira_margin1, fira_has_prev, fira_prev);
+        if (norm_out) *norm_out = norms;
+        free(gs);
+        free(us);
+        return rcs;
+    }
     const int v_quant = c->v_fmt != AF8O_V_FP32;
     float *g = (float *)malloc((size_t)(n ? n : 1) * sizeof(float));
     float *v = v_quant ? (float *)malloc((size_t)(n ? n : 1) * sizeof(float)) : v_f32;

@@ -25,7 +25,7 @@ _SRC = os.path.join(_HERE, "af8_oracle.c")
 
 LOG_QUANT_FLOOR = 1.17549435e-38  # optimizer.py:23
 
-V_FMT = {"fp32": 0, "al8": 8, "al16": 16}
+V_FMT = {"fp32": 0, "al8": 8, "al16": 16, "none": 1}
 M_FMT = {None: 0, "uf8": 1, "uf4": 2, "d8": 3, "d4": 4, "fp32": 5}
 G_F32, G_BF16 = 0, 1
 
@@ -273,6 +273,11 @@ def init_state(shape, hp):
           "v_quant_type": vqt, "c_quant_type": cqt, "shape": shape}
     use_apollo = hp["apollo_rank"] > 0 and len(shape) >= 2
     factored = len(shape) >= 2 and hp["factored"]
+    if is_sgd(hp):
+        # optimizer.py:1719-1725: only the momentum, quantised or fp32
+        if hp["beta1"] is not None:
+            _init_m(st, numel, hp["m_block_size"], hp["m_quant_type"] if use_quant else "fp32")
+        return st
     v_fmt = vqt if use_quant else "fp32"
     c_fmt = cqt if use_quant else "fp32"
     m_fmt = hp["m_quant_type"] if use_quant else "fp32"
@@ -298,6 +303,11 @@ def init_state(shape, hp):
         if hp["beta1"] is not None:
             _init_m(st, numel, hp["m_block_size"], m_fmt)
     return st
+
+
+def is_sgd(hp):
+    """SGD mode: neither beta2 nor beta2_decay (optimizer.py:1957)."""
+    return hp["beta2"] is None and hp["beta2_decay"] is None
 
 
 def _grad_args(g):
@@ -326,7 +336,11 @@ def prologue(p, state, hp):
         momentum_only = not use_adam_denom
     step = state["step"] + 1
     state["step"] = step
-    beta_val = 1.0 - beta2 if beta2 is not None else math.pow(step, hp["beta2_decay"])
+    sgd = is_sgd(hp)
+    if sgd:
+        beta_val = 0.0
+    else:
+        beta_val = 1.0 - beta2 if beta2 is not None else math.pow(step, hp["beta2_decay"])
     lr = hp["lr"]
     rho = f32(min(lr, 1.0 / math.sqrt(step)) if hp["relative_step"] else lr)
     if hp["scale_parameter"]:
@@ -335,7 +349,7 @@ def prologue(p, state, hp):
         alpha = f32(max(rms, f32(eps2))) * rho
     else:
         alpha = rho
-    if beta1 is not None and not hp["relative_step"]:
+    if beta1 is not None and not hp["relative_step"] and not sgd:
         apply_bc = use_adam_denom if hp["bias_correction"] is None else hp["bias_correction"]
         if apply_bc:
             bc1 = 1.0 - beta1 ** step
@@ -366,6 +380,9 @@ def fullrank_step(p, g, state, hp, sc=None):
     g, gdt = _grad_args(g)
     quant = state["is_quantized"]
     vqt = state["v_quant_type"] if quant else "fp32"
+    sgd = is_sgd(hp)
+    if sgd:
+        vqt = "none"
     has_m = hp["beta1"] is not None
     mqt = (state.get("m_quant_type", "uf8") if has_m else None)
     cfg = FullrankCfg()
@@ -383,7 +400,7 @@ def fullrank_step(p, g, state, hp, sc=None):
     cfg.decay = float(sc["decay"]) if sc["decay"] is not None else 1.0
     cfg.alpha = float(sc["alpha"])
     cfg.v_w = float(f32(sc["beta_val"]))
-    cfg.v_keep = float(f32(1.0 - sc["beta_val"]))
+    cfg.v_keep = float(f32(1.0 - hp["beta1"])) if (sgd and has_m) else float(f32(1.0 - sc["beta_val"]))
     cfg.v_eps_add = float(f32(sc["beta_val"] * sc["eps_for_grad_sq"]))
     cfg.m_w = float(f32(1.0 - hp["beta1"])) if has_m else 0.0
     cfg.eps_gradsq = float(f32(sc["eps_for_grad_sq"]))

@@ -63,6 +63,8 @@ _ADAMW = dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=None, factored=Fal
 _CAME = dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=0.9999, factored=True,
              relative_step=False, scale_parameter=False, scale_weight_decay=False,
              d=1.0, eps_came=1e-16)
+_SGD = dict(beta1=None, beta2=None, beta2_decay=None, beta3=None, factored=False, relative_step=False,
+            scale_parameter=False, scale_weight_decay=False, d=0.0)
 _RMSPROP = dict(beta1=None, beta2=0.99, beta2_decay=None, beta3=None, factored=False,
                 relative_step=False, scale_parameter=False, scale_weight_decay=False,
                 d=0.0, eps=(1e-8, 1e-3))
@@ -103,6 +105,12 @@ CASES = {
                                     m_quant_type="fp32", v_quant_type="al8")),
     "rmsprop_al8": dict(shapes=[(40, 130)], steps=4, seed=17, grad=_G_CFG0,
                         hp=dict(_RMSPROP, lr=1e-3, block_size=256)),
+    # SGD mode (neither beta2 nor beta2_decay): quantised momentum, clipping and the limiter
+    "sgd_momentum_uf8": dict(shapes=[(40, 130), (4096,)], steps=4, seed=23, grad=_G_CFG0,
+                             hp=dict(_SGD, beta1=0.9, lr=1e-2, weight_decay=0.01, d=1.0, block_size=256,
+                                     enable_fira_for_adafactor=True, min_8bit_size=1024)),
+    # plain SGD, bf16 gradients, no momentum, no clipping
+    "sgd_plain_bf16": dict(shapes=[(40, 130)], steps=3, seed=24, grad=_G_BF16, hp=dict(_SGD, lr=1e-2, block_size=256)),
     # unfactored Adafactor (relative step, parameter scaling, clip d=1).
     "adafactor_unfactored": dict(shapes=[(40, 130), (300,)], steps=4, seed=18, grad=_G_HEAVY,
                                  hp=dict(factored=False, block_size=256)),

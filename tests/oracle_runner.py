@@ -5,7 +5,7 @@ import af8_oracle as o
 import cases
 
 FULLRANK_CASES = ["adamw_uf8_al8", "adamw_fira_bf16", "adamw_uf4_al16", "adamw_d8_al8", "adamw_d4_al8",
-                  "adamw_fp32m_al8", "rmsprop_al8", "adafactor_unfactored"]
+                  "adamw_fp32m_al8", "rmsprop_al8", "adafactor_unfactored", "sgd_momentum_uf8", "sgd_plain_bf16"]
 
 
 def load_golden(name):
@@ -34,7 +34,7 @@ class OracleRun:
         shape = p.shape
         if self.hp["apollo_rank"] > 0 and len(shape) >= 2:
             return o.apollo_step(p, g, st, self.hp)
-        if len(shape) >= 2 and self.hp["factored"]:
+        if len(shape) >= 2 and self.hp["factored"] and not o.is_sgd(self.hp):
             return o.factored_step(p, g, st, self.hp)
         return o.fullrank_step(p.reshape(-1), g.reshape(-1), st, self.hp)
 
