@@ -235,12 +235,10 @@ struct StepScalars {
 template <int MODE, bool HAS_EPSG, bool TAIL>
 __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], const uint32_t (&mq)[2],
                                            const uint32_t (&vq)[2], const float *tab, float mc,
-                                           const StepScalars &S, int nva, int nvb, float (&v)[8], float (&m)[8],
-                                           float &acc)
+                                           const StepScalars &S, int nva, int nvb, float (&v)[8], float (&m)[8])
 {
     const float2 w_v = bc2(S.v_w), w_m = bc2(S.m_w), mc2 = bc2(mc), eps_d2 = bc2(S.eps_d);
     const float2 decay2 = bc2(S.decay), step2 = bc2(S.step_mul), fira2 = bc2(S.fira);
-    float2 acc2 = make_float2(0.0f, 0.0f);
 #pragma unroll
     for (int j = 0; j < 8; j += 2) {
         const uint32_t c0 = __byte_perm(vq[j >> 2], 0u, 0x4440u | (uint32_t)(j & 3));
@@ -271,17 +269,12 @@ __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], c
             if (!real0) u.x = 0.0f;
             if (!real1) u.y = 0.0f;
         }
-        if (MODE == AF8_MODE_SUMSQ) {
-            acc2 = __ffma2_rn(u, u, acc2);                        // padding contributes m = 0
-        } else {
-            float2 pj = __fmul2_rn(make_float2(p[j], p[j + 1]), decay2);     // optimizer.py:2039
-            if (MODE == AF8_MODE_APPLY) u = __fmul2_rn(u, fira2);             // optimizer.py:803
-            if (!(MODE == AF8_MODE_APPLY && S.zero_upd))          // non-finite norm: zero update (optimizer.py:798-800)
-                pj = __ffma2_rn(step2, u, pj);                    // optimizer.py:874
-            p[j] = pj.x; p[j + 1] = pj.y;
-        }
+        float2 pj = __fmul2_rn(make_float2(p[j], p[j + 1]), decay2);     // optimizer.py:2039
+        if (MODE == AF8_MODE_APPLY) u = __fmul2_rn(u, fira2);             // optimizer.py:803
+        if (!(MODE == AF8_MODE_APPLY && S.zero_upd))              // non-finite norm: zero update (optimizer.py:798-800)
+            pj = __ffma2_rn(step2, u, pj);                        // optimizer.py:874
+        p[j] = pj.x; p[j + 1] = pj.y;
     }
-    if (MODE == AF8_MODE_SUMSQ) acc = __fadd_rn(acc2.x, acc2.y);
 }
 
 // ---------------------------------------------------------------------------
@@ -296,22 +289,19 @@ __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], c
 #ifndef AF8_FAST_STAGES_UPDATE_F32
 #define AF8_FAST_STAGES_UPDATE_F32 2  /* the same with fp32 gradients (20 KB per slot) */
 #endif
-#ifndef AF8_FAST_STAGES_STAT
-#define AF8_FAST_STAGES_STAT 2        /* ring depth of the SUMSQ pass (8-12 KB per slot) */
-#endif
 
 // Measured on B200 (TinyLlama set): depths 2 / 3 / 4 / 6 change the pass times by a few
 // per cent in the wrong direction (fewer resident CTAs), so the default stays at 2.
 // Ring geometry of one kernel variant: byte offsets inside a slot and the slot count.
 template <typename GradT, int MODE> struct FastRing {
     static constexpr int GB = GradBytes<GradT>::value;
-    static constexpr bool NEED_P = MODE != AF8_MODE_SUMSQ;
+    static_assert(MODE == AF8_MODE_NOCLIP || MODE == AF8_MODE_APPLY, "the statistic pass has its own kernel (fullrank_stat.cuh)");
     static constexpr int P_OFF = 0;
-    static constexpr int G_OFF = NEED_P ? FAST_VBLOCK * 4 : 0;
+    static constexpr int G_OFF = FAST_VBLOCK * 4;
     static constexpr int MQ_OFF = G_OFF + FAST_VBLOCK * GB;
     static constexpr int VQ_OFF = MQ_OFF + FAST_VBLOCK;
     static constexpr int STAGE_BYTES = VQ_OFF + FAST_VBLOCK;
-    static constexpr int NST = NEED_P ? (GB == 2 ? AF8_FAST_STAGES_UPDATE : AF8_FAST_STAGES_UPDATE_F32) : AF8_FAST_STAGES_STAT;
+    static constexpr int NST = GB == 2 ? AF8_FAST_STAGES_UPDATE : AF8_FAST_STAGES_UPDATE_F32;
     static constexpr int SMEM_BYTES = NST * STAGE_BYTES;
     static_assert(NST >= 2 && NST <= 8, "ring depth");
 };
@@ -322,7 +312,6 @@ fullrank_fast_kernel(const FullrankLaunch L)
 {
     using Ring = FastRing<GradT, MODE>;
     constexpr int GB = Ring::GB;
-    constexpr bool NEED_P = Ring::NEED_P;
     constexpr int P_OFF = Ring::P_OFF, G_OFF = Ring::G_OFF, MQ_OFF = Ring::MQ_OFF, VQ_OFF = Ring::VQ_OFF;
     constexpr int STAGE_BYTES = Ring::STAGE_BYTES;
     constexpr int NST = Ring::NST;
@@ -333,7 +322,6 @@ fullrank_fast_kernel(const FullrankLaunch L)
     __shared__ float s_tab[2][256];
     __shared__ uint32_t s_redmin[FAST_WARPS];
     __shared__ uint32_t s_redmax[FAST_WARPS];
-    __shared__ float s_redsum[2][FAST_WARPS];
     __shared__ VRange s_vr;
     __shared__ int s_abort;
     __shared__ double s_exp2[32];            // copy of the exp2 table of the decode
@@ -410,7 +398,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 const int sl = (n + k) % NST;
                 unsigned char *dst = s_ring + sl * STAGE_BYTES;
                 mbar_expect_tx(&s_full[sl], STAGE_BYTES);
-                if (NEED_P) bulk_g2s(dst + P_OFF, pp + nb * 4, FAST_VBLOCK * 4, &s_full[sl]);
+                bulk_g2s(dst + P_OFF, pp + nb * 4, FAST_VBLOCK * 4, &s_full[sl]);
                 bulk_g2s(dst + G_OFF, gp + nb * GB, FAST_VBLOCK * GB, &s_full[sl]);
                 bulk_g2s(dst + MQ_OFF, sT.m_q + nb, FAST_VBLOCK, &s_full[sl]);
                 bulk_g2s(dst + VQ_OFF, vp + nb, FAST_VBLOCK, &s_full[sl]);
@@ -451,7 +439,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
             }
             phase ^= 1u << slot;
             const unsigned char *st = s_ring + slot * STAGE_BYTES;
-            if (NEED_P) {
+            {
                 const float4 a = *reinterpret_cast<const float4 *>(st + P_OFF + oa * 4);
                 const float4 c = *reinterpret_cast<const float4 *>(st + P_OFF + ob * 4);
                 p[0] = a.x; p[1] = a.y; p[2] = a.z; p[3] = a.w;
@@ -488,7 +476,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
             for (int j = 0; j < 8; ++j) {
                 const int e = (j < 4) ? oa + j : ob + j - 4;
                 const bool ok = (j < 4) ? (j < nva) : (j - 4 < nvb);
-                p[j] = (ok && NEED_P) ? static_cast<const float *>(sT.param)[base + e] : 0.0f;
+                p[j] = ok ? static_cast<const float *>(sT.param)[base + e] : 0.0f;
                 g[j] = ok ? GradLoad<GradT>::load1(sT.grad, base + e) : 0.0f;
             }
         }
@@ -518,14 +506,13 @@ fullrank_fast_kernel(const FullrankLaunch L)
 
         // ---- EMAs and update: everything that reaches a state is exact ----
         float v[8], m[8];
-        float acc = 0.0f;
         const bool small_w = fabsf(S.v_w) < 0.5f && fabsf(S.m_w) < 0.5f;   // ATen's lerp has two forms
         if (small_w) {
             if (full) {
-                if (S.eps_g == 0.0f) ema_update<MODE, false, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
-                else ema_update<MODE, true, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
+                if (S.eps_g == 0.0f) ema_update<MODE, false, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m);
+                else ema_update<MODE, true, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m);
             } else {
-                ema_update<MODE, true, true>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, acc);
+                ema_update<MODE, true, true>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m);
             }
         } else {
 #pragma unroll
@@ -539,35 +526,11 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 v[j] = vj; m[j] = mj;
                 float u = __fmul_rn(mj, rcp_approx(__fadd_rn(sqrt_approx(vj), S.eps_d)));
                 if (!real) u = 0.0f;
-                if (MODE == AF8_MODE_SUMSQ) {
-                    acc = __fmaf_rn(u, u, acc);
-                } else {
-                    float pj = __fmul_rn(p[j], S.decay);
-                    const float us = (MODE == AF8_MODE_APPLY) ? __fmul_rn(u, S.fira) : u;
-                    if (!(MODE == AF8_MODE_APPLY && S.zero_upd)) pj = __fmaf_rn(S.step_mul, us, pj);
-                    p[j] = pj;
-                }
+                float pj = __fmul_rn(p[j], S.decay);
+                const float us = (MODE == AF8_MODE_APPLY) ? __fmul_rn(u, S.fira) : u;
+                if (!(MODE == AF8_MODE_APPLY && S.zero_upd)) pj = __fmaf_rn(S.step_mul, us, pj);
+                p[j] = pj;
             }
-        }
-
-        if (MODE == AF8_MODE_SUMSQ) {
-            acc = warp_sum(acc);
-            if (lane == 0) s_redsum[stage][warp] = acc;
-            if (next_staged) s_tab[stage ^ 1][tid] = al8_decode_fast((uint32_t)tid, nsc, nml, s_exp2);
-            __syncthreads();
-            if (s_abort) {   // a copy never completed: give the ones still in flight a bounded chance, then stop
-                for (int k = 1; k < in_flight; ++k) mbar_wait_bounded(&s_full[(n + k) % NST], (phase >> ((n + k) % NST)) & 1u);
-                break;
-            }
-            if (tid == 0) {
-                float s = 0.0f;
-#pragma unroll
-                for (int w = 0; w < FAST_WARPS; ++w) s = __fadd_rn(s, s_redsum[stage][w]);
-                L.block_sumsq[blk] = s;
-            }
-            staged = next_staged;
-            mscale_cur = nms;
-            continue;
         }
 
         // ---- block extrema of v.  v >= 0, so the bit patterns order like the values.  The

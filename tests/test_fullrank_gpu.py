@@ -205,6 +205,40 @@ def test_large_tensor_codes_are_exact(kind, oracle):
         parity.assert_params(param.detach().cpu().numpy(), op, f"{kind} step {t} param", tol=1e-6)
 
 
+@pytest.mark.parametrize("fira", [False, True], ids=["noclip", "limiter"])
+def test_config0_full_size_is_exact(fira, oracle):
+    """The reference's own CPU-runnable configuration at its full size: one 4096 x 4096 fp32
+    parameter (16.8 M elements, 8192 V blocks), fp32 gradients N(0, 1e-2) with 1 % exact zeros,
+    AdamW UF8/AL8 with weight decay; with and without the limiter.  Every code and every block
+    range must equal the oracle's; parameters within 1e-6."""
+    from adafactor8bit import Adafactor8Bit
+    hp = dict(cases.CASES["adamw_uf8_al8"]["hp"])
+    if fira:
+        hp.update(enable_fira_for_adafactor=True, fira_margin=0.01)
+    shape = (4096, 4096)
+    rng = np.random.default_rng(4096)
+    p0 = (rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    param = torch.nn.Parameter(torch.from_numpy(p0.copy()).cuda())
+    opt = Adafactor8Bit([param], **hp)
+    ohp = oracle.hyper(**hp)
+    ost = oracle.init_state(shape, ohp)
+    op = p0.copy()
+    for t in range(1, 4):
+        g = (rng.standard_normal(shape, dtype=np.float32) * np.float32(1e-2 * (100.0 if (fira and t == 3) else 1.0))).astype(np.float32)
+        g[rng.random(shape) < 0.01] = 0.0
+        param.grad = torch.from_numpy(g).cuda()
+        opt.step()
+        oracle.fullrank_step(op.reshape(-1), g.reshape(-1), ost, ohp)
+        torch.cuda.synchronize()
+        st = opt.state[param]
+        for key in ("variance_q", "m_q"):
+            s = parity.code_stats(state_np(st, key), ost[key])
+            assert s["neq"] == 0, f"step {t} {key}: {s}"
+        for key in RANGE_KEYS:
+            assert int(parity.ulp_diff(state_np(st, key), ost[key]).max()) == 0, f"step {t} {key}"
+        parity.assert_params(param.detach().cpu().numpy(), op, f"step {t} param", tol=1e-6)
+
+
 def test_device_status_is_clean_after_the_runs_above():
     from adafactor8bit import _native
     assert _native.device_status(torch.cuda.current_stream().cuda_stream) == 0
