@@ -202,6 +202,7 @@ class Adafactor8Bit(Optimizer):
         self._apollo_seed_counter = 1          # optimizer.py:1460-1461
         self._sr_seed_counter = 1
         self._plans = {}
+        self._after_group = None               # optional hook(gi, group), called when a group's launches are enqueued
 
     # ------------------------------------------------------------------
     # checkpointing (optimizer.py:1463-1553)
@@ -395,6 +396,8 @@ class Adafactor8Bit(Optimizer):
                 entries.append((p, p.grad, state))
             if entries:
                 self._run_group(gi, group, entries)
+            if self._after_group is not None:
+                self._after_group(gi, group)
         return loss
 
     def _run_group(self, gi, group, entries):

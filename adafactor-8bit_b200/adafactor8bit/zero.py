@@ -10,11 +10,11 @@ parameters.
 Partition.  Whole tensors are assigned to ranks (longest-processing-time greedy
 on the element count), so every statistic of a step (update norms, row / column
 sums, projections) is local to one rank and the only data exchange of the step
-is the parameter all-gather.  All parameters live in ONE flat buffer laid out
-[rank 0's tensors | rank 1's tensors | ...] with equal-sized rank regions, and
-`param.data` of every parameter is a view into it: the kernels write updated
-values straight into the all-gather buffer and `all_gather_into_tensor` runs in
-place, without a staging copy.
+is the parameter all-gather.  All parameters live in ONE flat buffer made of a few
+gather units, each laid out [rank 0's part | rank 1's part | ...] with equal slots,
+and `param.data` of every parameter is a view into it: the kernels write updated
+values straight into the all-gather buffer, `all_gather_into_tensor` runs in place,
+without a staging copy, and the gather of one unit overlaps the update of the next.
 """
 import torch
 import torch.distributed as dist
@@ -35,15 +35,30 @@ def partition_tensors(numels, world):
     return owner
 
 
+def split_parts(sizes, k):
+    """Cut a sequence of sizes into k consecutive parts of roughly equal total -> part index per item."""
+    total = sum(sizes)
+    part, acc, out = 0, 0, []
+    for n in sizes:
+        # move on when the running total has passed this part's share (never beyond the last part)
+        while part < k - 1 and acc >= total * (part + 1) / k:
+            part += 1
+        out.append(part)
+        acc += n
+    return out
+
+
 class ShardedAdafactor8Bit:
     """Adafactor8Bit whose states and step are partitioned over a process group.
 
     params: an iterable of tensors or of param-group dicts, as for Adafactor8Bit.
+    gather_chunks: the tensors of every rank are cut into this many consecutive parts; the
+    all-gather of part k runs on a second stream while part k + 1 is being updated.
     inner_factory: class of the per-rank optimizer (the default is Adafactor8Bit; the
     CPU tests of the sharding logic plug in a stock torch optimizer).
     """
 
-    def __init__(self, params, process_group=None, inner_factory=Adafactor8Bit, **kwargs):
+    def __init__(self, params, process_group=None, inner_factory=Adafactor8Bit, gather_chunks=4, **kwargs):
         self.group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
@@ -61,28 +76,46 @@ class ShardedAdafactor8Bit:
         numels = [p.numel() for p in all_params]
         self.owner = partition_tensors(numels, self.world)
         padded = [(n + _ALIGN - 1) // _ALIGN * _ALIGN for n in numels]
-        fill = [0] * self.world
+        # every rank's tensors, in order, cut into parts; part k of all ranks forms gather unit k:
+        # [rank 0's part k | rank 1's part k | ...] with equal slots, the units one after another
+        k_parts = max(1, int(gather_chunks)) if self.world > 1 else 1
+        part = [0] * len(all_params)
+        for r in range(self.world):
+            mine = [i for i in range(len(all_params)) if self.owner[i] == r]
+            for i, pk in zip(mine, split_parts([padded[i] for i in mine], k_parts)):
+                part[i] = pk
+        fill = [[0] * k_parts for _ in range(self.world)]
         offset = [0] * len(all_params)
         for i, r in enumerate(self.owner):
-            offset[i] = fill[r]
-            fill[r] += padded[i]
-        self.region = max(max(fill), _ALIGN)
-        self.flat = torch.zeros(self.world * self.region, dtype=dt, device=dev)
+            offset[i] = fill[r][part[i]]
+            fill[r][part[i]] += padded[i]
+        self.unit_slot = [max(max(fill[r][k] for r in range(self.world)), 0) for k in range(k_parts)]
+        if sum(self.unit_slot) == 0:
+            self.unit_slot[0] = _ALIGN
+        self.unit_start = [0] * k_parts
+        for k in range(1, k_parts):
+            self.unit_start[k] = self.unit_start[k - 1] + self.world * self.unit_slot[k - 1]
+        self.flat = torch.zeros(self.unit_start[-1] + self.world * self.unit_slot[-1], dtype=dt, device=dev)
         with torch.no_grad():
             for i, p in enumerate(all_params):
-                start = self.owner[i] * self.region + offset[i]
+                start = self.unit_start[part[i]] + self.owner[i] * self.unit_slot[part[i]] + offset[i]
                 view = self.flat[start:start + numels[i]].view(p.shape)
                 view.copy_(p.data)
                 p.data = view
         self.all_params = all_params
+        self.part = part
         owned = {id(p) for i, p in enumerate(all_params) if self.owner[i] == self.rank}
+        part_of = {id(p): part[i] for i, p in enumerate(all_params)}
         self.owned_numel = sum(n for i, n in enumerate(numels) if self.owner[i] == self.rank)
         self.total_numel = sum(numels)
-        inner_groups = []
-        for g in groups:
-            mine = [p for p in g["params"] if id(p) in owned]
-            if mine:
-                inner_groups.append(dict(g, params=mine))
+        # inner groups: part-major, so that a part's launches are complete before the next part starts
+        inner_groups, self._last_group_of_part = [], {}
+        for k in range(k_parts):
+            for g in groups:
+                mine = [p for p in g["params"] if id(p) in owned and part_of[id(p)] == k]
+                if mine:
+                    inner_groups.append(dict(g, params=mine))
+                    self._last_group_of_part[k] = len(inner_groups) - 1
         self.inner = inner_factory(inner_groups, **kwargs) if inner_groups else None
         self.gather_stream = None
 
@@ -105,15 +138,52 @@ class ShardedAdafactor8Bit:
         """Update the tensors this rank owns (no communication)."""
         return self.inner.step(closure) if self.inner is not None else None
 
+    def _gather_unit(self, k):
+        slot = self.unit_slot[k]
+        if slot == 0:
+            return
+        unit = self.flat[self.unit_start[k]:self.unit_start[k] + self.world * slot]
+        dist.all_gather_into_tensor(unit, unit[self.rank * slot:(self.rank + 1) * slot], group=self.group)
+
     def gather(self):
-        """In-place all-gather of the rank regions of the flat parameter buffer."""
+        """In-place all-gather of every unit of the flat parameter buffer."""
         if self.world > 1:
-            mine = self.flat[self.rank * self.region:(self.rank + 1) * self.region]
-            dist.all_gather_into_tensor(self.flat, mine, group=self.group)
+            for k in range(len(self.unit_slot)):
+                self._gather_unit(k)
 
     def step(self, closure=None):
-        loss = self.local_step(closure)
-        self.gather()
+        """Local update and parameter all-gather.  On CUDA with the native optimizer the gather of a
+        part starts, on a second stream, as soon as the launches of that part have been enqueued."""
+        pipelined = (self.world > 1 and self.flat.is_cuda and self.inner is not None and hasattr(self.inner, "_after_group"))
+        if not pipelined:
+            loss = self.local_step(closure)
+            self.gather()
+            return loss
+        if self.gather_stream is None:
+            self.gather_stream = torch.cuda.Stream(device=self.flat.device)
+        main = torch.cuda.current_stream(self.flat.device)
+        done = set()
+
+        def after_group(gi, group):
+            for k, last in self._last_group_of_part.items():
+                if last == gi and k not in done:
+                    done.add(k)
+                    ev = torch.cuda.Event()
+                    ev.record(main)
+                    with torch.cuda.stream(self.gather_stream):
+                        self.gather_stream.wait_event(ev)
+                        self._gather_unit(k)
+
+        self.inner._after_group = after_group
+        try:
+            loss = self.inner.step(closure)
+        finally:
+            self.inner._after_group = None
+        with torch.cuda.stream(self.gather_stream):          # parts this rank owns nothing of
+            for k in range(len(self.unit_slot)):
+                if k not in done:
+                    self._gather_unit(k)
+        main.wait_stream(self.gather_stream)
         return loss
 
     def state_dict(self):

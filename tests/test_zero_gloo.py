@@ -86,3 +86,17 @@ def test_partition_is_balanced_and_deterministic():
         loads = [sum(n for n, o in zip(numels, owner) if o == r) for r in range(world)]
         assert owner == partition_tensors(numels, world)
         assert max(loads) <= 1.02 * sum(numels) / world + 1
+
+
+def test_split_parts_and_partition():
+    sys.path.insert(0, os.path.join(ROOT, "adafactor-8bit_b200"))
+    from adafactor8bit.zero import partition_tensors, split_parts
+    assert split_parts([], 4) == []
+    assert split_parts([10], 4) == [0]
+    parts = split_parts([5, 5, 5, 5, 5, 5, 5, 5], 4)
+    assert parts == [0, 0, 1, 1, 2, 2, 3, 3]
+    parts = split_parts([100, 1, 1, 1], 2)
+    assert parts[0] == 0 and parts[-1] == 1 and parts == sorted(parts)
+    owner = partition_tensors([8, 7, 6, 5, 4, 3, 2, 1], 2)
+    loads = [sum(n for n, o in zip([8, 7, 6, 5, 4, 3, 2, 1], owner) if o == r) for r in range(2)]
+    assert loads == [18, 18]
