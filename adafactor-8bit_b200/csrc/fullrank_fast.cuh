@@ -26,7 +26,7 @@
 // af8_device_status() reports, the threads skip the stores of that block and
 // the CTA stops at its next block-wide barrier.
 //
-// Instruction budget.  At 14-16 bytes per parameter the HBM roofline leaves
+// Instruction count.  At 14-16 bytes per parameter the HBM roofline leaves
 // roughly 60 issue slots per parameter, so exact IEEE arithmetic is spent only
 // where it decides a stored bit:
 //   * the EMAs, the dequantisation and both requantisations are bit-exact

@@ -189,9 +189,9 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # CPU implementation of the reference step (the oracle), bounded sample
 # ---------------------------------------------------------------------------
-def cpu_reference_run(workload, steps, warmup, budget_params=24_000_000):
+def cpu_reference_run(workload, steps, warmup, sample_limit=24_000_000):
     """Time the CPU restatement of the reference's step on a bounded sample of
-    the workload: its largest tensors are cut to at most `budget_params`
+    the workload: its largest tensors are cut to at most `sample_limit`
     parameters in total (whole rows), all host threads."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
@@ -200,20 +200,20 @@ def cpu_reference_run(workload, steps, warmup, budget_params=24_000_000):
     wl = WORKLOADS[workload]
     hp = o.hyper(**wl["hp"])
     shapes = wl["shapes"]()
-    # sample: one of each distinct shape, in order, until the budget is spent
+    # sample: one of each distinct shape, in order, until the limit is reached
     seen, sample, sample_names, total = set(), [], [], 0
     if wl.get("apollo_targets"):
-        budget_params = min(budget_params, 6_000_000)      # the CPU projection costs 2*rank flops per parameter
+        sample_limit = min(sample_limit, 6_000_000)      # the CPU projection costs 2*rank flops per parameter
     for name, shp in shapes:
         if shp in seen:
             continue
         seen.add(shp)
         n = int(np.prod(shp))
-        if total + n > budget_params and len(shp) == 2:
-            rows = max(1, (budget_params - total) // shp[1])
+        if total + n > sample_limit and len(shp) == 2:
+            rows = max(1, (sample_limit - total) // shp[1])
             shp = (min(rows, shp[0]), shp[1])
             n = int(np.prod(shp))
-        if n == 0 or total + n > budget_params * 1.05:
+        if n == 0 or total + n > sample_limit * 1.05:
             continue
         sample.append(shp)
         sample_names.append(name)

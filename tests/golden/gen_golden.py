@@ -99,7 +99,7 @@ def run_case(name, out_dir, suffix=""):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference",
+    ap.add_argument("--reference", required=True,
                     help="directory that contains the reference's adafactor8bit package")
     ap.add_argument("--accurate-norm", action="store_true")
     ap.add_argument("cases", nargs="*")
