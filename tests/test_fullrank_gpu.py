@@ -242,3 +242,51 @@ def test_config0_full_size_is_exact(fira, oracle):
 def test_device_status_is_clean_after_the_runs_above():
     from adafactor8bit import _native
     assert _native.device_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+def test_maximize_equals_negated_gradients(oracle):
+    """maximize=True (optimizer.py:1973-1974) is a sign flip of the gradient and nothing else."""
+    from adafactor8bit import Adafactor8Bit
+    hp = dict(cases.CASES["adamw_fira_bf16"]["hp"])
+    shape = (96, 200)
+    rng = np.random.default_rng(9)
+    p0 = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    a = torch.nn.Parameter(torch.from_numpy(p0.copy()).cuda())
+    b = torch.nn.Parameter(torch.from_numpy(p0.copy()).cuda())
+    a.grad_dtype = b.grad_dtype = None
+    oa, ob = Adafactor8Bit([a], **hp), Adafactor8Bit([b], **dict(hp, maximize=True))
+    for t in range(1, 4):
+        g = cases.make_grad(shape, 555, t, cases.CASES["adamw_fira_bf16"]["grad"])
+        a.grad = to_cuda_grad(g, shape)
+        b.grad = -to_cuda_grad(g, shape)
+        oa.step()
+        ob.step()
+    torch.cuda.synchronize()
+    assert torch.equal(a.detach(), b.detach())
+    for key in CODE_KEYS + RANGE_KEYS:
+        assert torch.equal(oa.state[a][key], ob.state[b][key]), key
+
+
+def test_param_groups_and_closure(oracle):
+    """Two groups with different learning rates step like two optimizers; the closure's loss is returned."""
+    from adafactor8bit import Adafactor8Bit
+    hp = dict(cases.CASES["adamw_uf8_al8"]["hp"])
+    rng = np.random.default_rng(10)
+    shapes = [(64, 200), (4096,)]
+    p0 = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
+    pa = [torch.nn.Parameter(torch.from_numpy(x.copy()).cuda()) for x in p0]
+    pb = [torch.nn.Parameter(torch.from_numpy(x.copy()).cuda()) for x in p0]
+    both = Adafactor8Bit([dict(params=[pa[0]], lr=1e-3), dict(params=[pa[1]], lr=5e-4)], **{k: v for k, v in hp.items() if k != "lr"})
+    one = Adafactor8Bit([pb[0]], **dict(hp, lr=1e-3))
+    two = Adafactor8Bit([pb[1]], **dict(hp, lr=5e-4))
+    for t in range(1, 4):
+        gs = [(rng.standard_normal(s) * 1e-2).astype(np.float32) for s in shapes]
+        for p, q, g in zip(pa, pb, gs):
+            p.grad = torch.from_numpy(g).cuda()
+            q.grad = torch.from_numpy(g).cuda()
+        assert both.step(lambda: torch.tensor(1.25)) == 1.25
+        one.step()
+        two.step()
+    torch.cuda.synchronize()
+    for p, q in zip(pa, pb):
+        assert torch.equal(p.detach(), q.detach())
