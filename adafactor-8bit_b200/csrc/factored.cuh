@@ -487,30 +487,39 @@ __device__ __forceinline__ void m_old8(const af8_factored_tensor &T, int m_fmt, 
 
 // Rows r0 + warp + 8k of the tile, NB at a time so that NB independent 128-bit loads per lane
 // are in flight.  Column partials go to a per-warp shared array (no shared-memory atomics).
-template <typename GradT, int NB>
+template <typename GradT, int NB, bool PREFETCH, bool RESIDUAL>
 __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t c,
                                            bool col_ok, float pre_div, const float (&ic)[8], double (&cacc)[8])
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t R = sT.rows, C = sT.cols;
-    for (int k0 = 0; k0 < FSTAT_ROWS / 8; k0 += NB) {
-        if (r0 + warp + 8 * k0 >= R) break;                       // uniform over the warp
-        float g[NB][8];
+    // PREFETCH: the loads of the next NB rows are issued before the current ones are processed
+    GradRaw8<GradT> cur[NB], nxt[NB];
+    auto fetch = [&](GradRaw8<GradT> (&dst)[NB], int k0) {
 #pragma unroll
         for (int k = 0; k < NB; ++k) {
             const int64_t r = r0 + warp + 8 * (k0 + k);
-            if (col_ok && r < R) load_g8<GradT>(sT.grad, r * C + c, L.negate_grad, g[k]);
-            else {
+            if (col_ok && r < R && k0 + k < FSTAT_ROWS / 8) dst[k].load(sT.grad, r * C + c);
+            else dst[k].zero();
+        }
+    };
+    if (PREFETCH) fetch(cur, 0);
+    for (int k0 = 0; k0 < FSTAT_ROWS / 8; k0 += NB) {
+        if (r0 + warp + 8 * k0 >= R) break;                       // uniform over the warp
+        if (PREFETCH) fetch(nxt, k0 + NB);
+        else fetch(cur, k0);
+        float g[NB][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) g[k][j] = 0.0f;
-            }
+        for (int k = 0; k < NB; ++k) {
+            cur[k].unpack(L.negate_grad, g[k]);
+            if (PREFETCH) cur[k] = nxt[k];
         }
 #pragma unroll
         for (int k = 0; k < NB; ++k) {
             const int64_t r = r0 + warp + 8 * (k0 + k);
             const bool live = col_ok && r < R;
             float x[8];
-            if (L.mode == AF8_FSTAT_GRADSQ) {
+            if (!RESIDUAL) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(g[k][j], g[k][j]);
             } else if (live) {
@@ -544,7 +553,9 @@ __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_fa
     }
 }
 
-template <typename GradT>
+// RESIDUAL: CAME's (U - M)^2 + eps statistic; otherwise g^2 (separate instantiations, so that
+// the lighter one keeps its lower register count)
+template <typename GradT, bool RESIDUAL>
 __global__ void __launch_bounds__(256)
 factored_stats_vec_kernel(const FactoredLaunch L)
 {
@@ -575,15 +586,15 @@ factored_stats_vec_kernel(const FactoredLaunch L)
         float ic[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) ic[j] = 0.0f;
-        if (L.mode == AF8_FSTAT_RESIDUAL) {
+        if (RESIDUAL) {
             pre_div = L.dyn[t].pre_div;
             if (col_ok) load_f8_ro(sT.inv_col + c, ic);
         }
         double cacc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) cacc[j] = 0.0;
-        if (L.mode == AF8_FSTAT_GRADSQ) stats_rows<GradT, 4>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
-        else stats_rows<GradT, 2>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
+        if (!RESIDUAL) stats_rows<GradT, 4, true, false>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
+        else stats_rows<GradT, 2, false, true>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
 #pragma unroll
         for (int j = 0; j < 8; ++j) s_col[warp][j * 32 + lane] = cacc[j];
         __syncthreads();
@@ -920,8 +931,11 @@ extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factore
     FactoredLaunch L = make_factored_launch(*cfg, dev_tensors, n_tensors, tiles, dyn, nullptr);
     int64_t grid = (int64_t)sm_count() * 6;
     if (grid > tiles) grid = tiles;
-    if (cfg->aligned8 && cfg->grad_dtype == AF8_BF16) factored_stats_vec_kernel<bf16_tag><<<(int)grid, 256, 0, st>>>(L);
-    else if (cfg->aligned8) factored_stats_vec_kernel<float><<<(int)grid, 256, 0, st>>>(L);
+    const bool bf = cfg->grad_dtype == AF8_BF16, res = cfg->mode == AF8_FSTAT_RESIDUAL;
+    if (cfg->aligned8 && bf && res) factored_stats_vec_kernel<bf16_tag, true><<<(int)grid, 256, 0, st>>>(L);
+    else if (cfg->aligned8 && bf) factored_stats_vec_kernel<bf16_tag, false><<<(int)grid, 256, 0, st>>>(L);
+    else if (cfg->aligned8 && res) factored_stats_vec_kernel<float, true><<<(int)grid, 256, 0, st>>>(L);
+    else if (cfg->aligned8) factored_stats_vec_kernel<float, false><<<(int)grid, 256, 0, st>>>(L);
     else factored_stats_kernel<<<(int)grid, 256, 0, st>>>(L);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
