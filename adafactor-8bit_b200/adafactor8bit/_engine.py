@@ -575,7 +575,10 @@ class ApolloPlan:
         self.total_numel = int(sum(r * c for r, c in zip(self.rows, self.cols)))
         dev = self.device
         self.g_low = [torch.empty(n, dtype=torch.float32, device=dev) for n in self.nl]
-        self.upd = [torch.zeros(n, dtype=torch.float32, device=dev) for n in self.nl]
+        # update_low of every tensor in one buffer (cleared with one memset per step), 512-byte aligned slices
+        offs = np.concatenate([[0], np.cumsum([(n + 127) // 128 * 128 for n in self.nl])]).astype(np.int64)
+        self.upd_all = torch.zeros(int(offs[-1]), dtype=torch.float32, device=dev)
+        self.upd = [self.upd_all[int(offs[i]):int(offs[i]) + self.nl[i]] for i in range(self.n)]
         self.chan_g2 = [torch.empty(n, dtype=torch.float64, device=dev) for n in self.nch]
         # tensor-core projection: per-tensor workspaces (flag + bf16 planes of the projection)
         # cut from one buffer, and the task table of the multi-tensor launch
@@ -600,6 +603,18 @@ class ApolloPlan:
         self.sums = torch.zeros(3 * self.n, dtype=torch.float64, device=dev)
         self.out = torch.zeros(4 * self.n, dtype=torch.float32, device=dev)
         self._low_plans = {}
+        # table of the batched scaling-factor / scalar-chain launches (static part)
+        fs = np.zeros(self.n, dtype=N.APOLLO_FINISH_TENSOR)
+        units = [(n + 7) // 8 for n in self.nch]
+        for i in range(self.n):
+            fs["upd"][i], fs["g_low"][i], fs["chan_g2"][i] = self.upd[i].data_ptr(), self.g_low[i].data_ptr(), self.chan_g2[i].data_ptr()
+            fs["sf"][i], fs["sums"][i], fs["out"][i] = self.sf[i].data_ptr(), self.sums.data_ptr() + 24 * i, self.out.data_ptr() + 16 * i
+            fs["rows"][i], fs["cols"][i], fs["rank"][i] = self.rows[i], self.cols[i], self.rank
+            fs["first_unit"][i] = sum(units[:i])
+        self._finish_static = fs
+        self.finish_units = int(sum(units))
+        self.h_finish = _PinnedRing(self.n * N.APOLLO_FINISH_TENSOR.itemsize)
+        self.d_finish = torch.empty(self.n * N.APOLLO_FINISH_TENSOR.itemsize, dtype=torch.uint8, device=dev)
 
     def _low_plan(self, idx):
         """Full-rank plan over the projected space for the tensors `idx` (they share the
@@ -646,6 +661,7 @@ class ApolloPlan:
         self.h_tasks.mark(stream)
         if log is not None:
             ev[1].record(stream)
+        self.upd_all.zero_()        # the low-rank step writes p*0 + u into it; stale NaNs must not survive
         for first in (True, False):
             idx = [i for i in range(self.n) if bool(first_flags[i]) == first]
             if not idx:
@@ -659,11 +675,10 @@ class ApolloPlan:
                         m_w=np.full(k, lowrank_scalars["m_w"], np.float32), eps_gradsq=np.zeros(k, np.float32),
                         eps_denom=np.full(k, lowrank_scalars["apollo_eps"], np.float32),
                         eps_sq=np.full(k, 1.17549435e-38, np.float32))
-            for i in idx:
-                self.upd[i].zero_()
             plan.run([self.g_low[i] for i in idx], cols, d=0.0, fira=False)
         if log is not None:
             ev[2].record(stream)
+        sins = []
         for i in range(self.n):
             t = per_tensor[i]
             sin = N.ApolloScalarsIn()
@@ -671,11 +686,29 @@ class ApolloPlan:
                 setattr(sin, k, float(t[k]))
             for k in ("bc_mode", "fira", "fira_has_prev", "scale_tensor", "scale_front"):
                 setattr(sin, k, int(t[k]))
-            prev = t.get("fira_prev")
-            N.check(lib.af8_apollo_scales(self.upd[i].data_ptr(), self.g_low[i].data_ptr(), self.chan_g2[i].data_ptr(),
-                                          self.rows[i], self.cols[i], self.rank, ctypes.byref(sin), self.sf[i].data_ptr(),
-                                          self.sums.data_ptr() + 24 * i, prev.data_ptr() if prev is not None else None,
-                                          self.out.data_ptr() + 16 * i, s), "af8_apollo_scales")
+            sins.append(sin)
+        if any(sin.scale_tensor for sin in sins):
+            for i, sin in enumerate(sins):          # tensor-wise scaling: one tensor at a time
+                prev = per_tensor[i].get("fira_prev")
+                N.check(lib.af8_apollo_scales(self.upd[i].data_ptr(), self.g_low[i].data_ptr(), self.chan_g2[i].data_ptr(),
+                                              self.rows[i], self.cols[i], self.rank, ctypes.byref(sin), self.sf[i].data_ptr(),
+                                              self.sums.data_ptr() + 24 * i, prev.data_ptr() if prev is not None else None,
+                                              self.out.data_ptr() + 16 * i, s), "af8_apollo_scales")
+        else:                                       # channel-wise scaling: all tensors in two launches
+            h = self.h_finish.next()
+            ft = np.frombuffer(h.numpy(), dtype=N.APOLLO_FINISH_TENSOR, count=self.n)
+            ft[:] = self._finish_static
+            for i, sin in enumerate(sins):
+                prev = per_tensor[i].get("fira_prev")
+                ft["fira_prev"][i] = prev.data_ptr() if prev is not None else 0
+                for k in ("alpha", "bc", "d", "clip_div", "fira_margin1", "sqrt_scale", "bc_mode", "fira", "fira_has_prev",
+                          "scale_tensor", "scale_front"):
+                    ft[k][i] = getattr(sin, k)
+            N.check(lib.af8_apollo_scales_batch(h.data_ptr(), self.d_finish.data_ptr(), self.n, self.finish_units, s),
+                    "af8_apollo_scales_batch")
+            self.h_finish.mark(stream)
+        for i, sin in enumerate(sins):
+            t = per_tensor[i]
             N.check(lib.af8_apollo_apply(self.params[i].data_ptr(), grads[i].data_ptr(), self.grad_dtype, self.negate,
                                          self.sf[i].data_ptr(), self.out.data_ptr() + 16 * i, self.rows[i], self.cols[i],
                                          ctypes.byref(sin), float(t["decay"]), int(t["has_decay"]), s), "af8_apollo_apply")

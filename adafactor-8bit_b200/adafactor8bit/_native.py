@@ -53,6 +53,13 @@ APOLLO_PROJ_DESC = np.dtype([(n, np.uint64) for n in ("grad", "pt", "g_low", "ch
                             [(n, np.int64) for n in ("workspace_bytes", "rows", "cols", "rank")] +
                             [("negate", np.int32), ("reserved", np.int32)], align=True)     # af8_apollo_proj_desc, 80 B
 
+APOLLO_FINISH_TENSOR = np.dtype(
+    [(n, np.uint64) for n in ("upd", "g_low", "chan_g2", "sf", "sums", "fira_prev", "out")] +
+    [(n, np.int64) for n in ("rows", "cols", "rank", "first_unit")] +
+    [(n, np.float32) for n in ("alpha", "bc", "d", "clip_div", "fira_margin1", "sqrt_scale")] +
+    [(n, np.int32) for n in ("bc_mode", "fira", "fira_has_prev", "scale_tensor", "scale_front", "in_reserved")] +
+    [("reserved", np.int64)], align=True)     # af8_apollo_finish_tensor, 144 B
+
 SMALL_STATE = np.dtype([
     ("q", _P), ("scale", _P), ("min_log", _P), ("f32", _P), ("fmt", np.int32), ("block", np.int32),
 ], align=True)
@@ -136,6 +143,7 @@ PROTOTYPES = {
     "af8_apollo_project_ws": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_l, _c_l, _c_l, _c_p, _c_p, _c_p, _c_l, _c_p]),
     "af8_apollo_project_task_bytes": (ctypes.c_int32, []),
     "af8_apollo_project_batch": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p, _c_l, _c_p]),
+    "af8_apollo_scales_batch": (_c_i, [_c_p, _c_p, _c_i, _c_l, _c_p]),
     "af8_apollo_scales": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn), _c_p, _c_p, _c_p,
                                  _c_p, _c_p]),
     "af8_apollo_apply": (_c_i, [_c_p, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn),
@@ -178,7 +186,7 @@ def lib():
         # the mirrors of this module against the structures the library was compiled with
         mirrors = [FULLRANK_TENSOR.itemsize, DYN_SCALARS.itemsize, ctypes.sizeof(FullrankCfg), NORM_TENSOR.itemsize,
                    SCALE_TENSOR.itemsize, SMALL_STATE.itemsize, FACTORED_TENSOR.itemsize, ctypes.sizeof(FactoredCfg),
-                   ctypes.sizeof(ApolloScalarsIn), 16, APOLLO_PROJ_DESC.itemsize]
+                   ctypes.sizeof(ApolloScalarsIn), 16, APOLLO_PROJ_DESC.itemsize, APOLLO_FINISH_TENSOR.itemsize]
         for i, mine in enumerate(mirrors):
             theirs = handle.af8_struct_size(i)
             if theirs != mine:

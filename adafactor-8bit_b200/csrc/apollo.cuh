@@ -281,8 +281,8 @@ apollo_tensor_sums_kernel(const float *upd, const float *g_low, int64_t nl, cons
 // ---------------------------------------------------------------------------
 // 4. scalar chain of one tensor (one thread)
 // ---------------------------------------------------------------------------
-__global__ void apollo_finalize_kernel(const af8_apollo_scalars_in in, const double *sums, float *sf_tensor,
-                                       float *fira_prev, af8_apollo_scalars *out)
+__device__ __forceinline__ void apollo_finalize_one(const af8_apollo_scalars_in &in, const double *sums, float *sf_tensor,
+                                                    float *fira_prev, af8_apollo_scalars *out)
 {
     float norm, s_tensor = 0.0f;
     if (in.scale_tensor) {
@@ -319,6 +319,80 @@ __global__ void apollo_finalize_kernel(const af8_apollo_scalars_in in, const dou
     out->fira = fs;
     out->norm = norm;
     out->reserved = 0.0f;
+}
+
+__global__ void apollo_finalize_kernel(const af8_apollo_scalars_in in, const double *sums, float *sf_tensor,
+                                       float *fira_prev, af8_apollo_scalars *out)
+{
+    apollo_finalize_one(in, sums, sf_tensor, fira_prev, out);
+}
+
+// ---------------------------------------------------------------------------
+// steps 3 and 4 for all tensors of a group in two launches (channel-wise scaling)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int find_finish_tensor(const af8_apollo_finish_tensor *t, int n, int64_t unit)
+{
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(&t[mid].first_unit) <= unit) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+// unit = 8 channels of one tensor, one warp per channel (as apollo_scales_kernel)
+__global__ void __launch_bounds__(256)
+apollo_scales_multi_kernel(const af8_apollo_finish_tensor *__restrict__ T, int n, int64_t total_units)
+{
+    __shared__ double s_part[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int64_t unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+        const af8_apollo_finish_tensor *t = T + find_finish_tensor(T, n, unit);
+        const int64_t rows = __ldg(&t->rows), cols = __ldg(&t->cols), rank = __ldg(&t->rank);
+        const bool right = rows >= cols;
+        const int64_t nch = right ? rows : cols;
+        const int64_t ch = (unit - __ldg(&t->first_unit)) * 8 + warp;
+        const float *upd = t->upd, *g_low = t->g_low;
+        double local = 0.0;
+        if (ch < nch) {
+            double nu = 0.0, ng = 0.0;
+            for (int64_t k = lane; k < rank; k += 32) {
+                const int64_t idx = right ? ch * rank + k : k * nch + ch;
+                const float u = upd[idx], g = g_low[idx];
+                nu += (double)__fmul_rn(u, u);
+                ng += (double)__fmul_rn(g, g);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                nu += __shfl_xor_sync(0xffffffffu, nu, o);
+                ng += __shfl_xor_sync(0xffffffffu, ng, o);
+            }
+            if (lane == 0) {
+                float s = __fdiv_rn(__double2float_rn(sqrt(nu)), __fadd_rn(__double2float_rn(sqrt(ng)), 1e-8f));   // optimizer.py:2964
+                if (__ldg(&t->in.scale_front)) s = __fmul_rn(s, __ldg(&t->in.sqrt_scale));                       // optimizer.py:2969-2971
+                t->sf[ch] = s;
+                const float nG = __double2float_rn(sqrt(t->chan_g2[ch]));
+                local = (double)__fmul_rn(__fmul_rn(nG, nG), __fmul_rn(s, s));                                   // optimizer.py:2975-2982
+            }
+        }
+        __syncthreads();
+        if (lane == 0) s_part[warp] = local;
+        __syncthreads();
+        if (tid == 0) {
+            double s = 0.0;
+            for (int w = 0; w < 8; ++w) s += s_part[w];
+            atomicAdd(t->sums, s);
+        }
+    }
+}
+
+__global__ void apollo_finalize_multi_kernel(const af8_apollo_finish_tensor *T, int n)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const af8_apollo_scalars_in in = T[i].in;
+        apollo_finalize_one(in, T[i].sums, T[i].sf, T[i].fira_prev, T[i].out);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -748,6 +822,41 @@ extern "C" int af8_apollo_scales(const float *upd, const float *g_low, const dou
     }
     AF8_CUDA_TRY(cudaGetLastError());
     apollo_finalize_kernel<<<1, 1, 0, st>>>(*in, sums, sf, fira_prev, out);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+extern "C" int af8_apollo_scales_batch(const af8_apollo_finish_tensor *host_tensors, af8_apollo_finish_tensor *dev_tensors,
+                                       int32_t n, int64_t total_units, void *stream)
+{
+    using namespace af8;
+    if (!host_tensors || !dev_tensors || n <= 0) return fail(AF8_ERR_INVALID, "af8_apollo_scales_batch: null or empty table");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int64_t next = 0;
+    char *run_begin = nullptr, *run_end = nullptr;
+    for (int i = 0; i < n; ++i) {
+        const af8_apollo_finish_tensor &t = host_tensors[i];
+        if (!t.upd || !t.g_low || !t.chan_g2 || !t.sf || !t.sums || !t.out) return fail(AF8_ERR_INVALID, "af8_apollo_scales_batch: tensor %d: null pointer", i);
+        if (t.in.scale_tensor) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_scales_batch: tensor-wise scaling takes af8_apollo_scales");
+        if (t.in.fira && !t.fira_prev) return fail(AF8_ERR_INVALID, "af8_apollo_scales_batch: tensor %d: the limiter needs fira_prev", i);
+        if (t.rows <= 0 || t.cols <= 0 || t.rank <= 0) return fail(AF8_ERR_INVALID, "af8_apollo_scales_batch: tensor %d: bad shape", i);
+        if (t.first_unit != next) return fail(AF8_ERR_INVALID, "af8_apollo_scales_batch: tensor %d: first_unit %lld, expected %lld", i, (long long)t.first_unit, (long long)next);
+        next += ((t.rows >= t.cols ? t.rows : t.cols) + 7) / 8;
+        // clear the three accumulators of every tensor; neighbours in memory share one memset
+        char *p = reinterpret_cast<char *>(t.sums);
+        if (p == run_end) { run_end += 24; continue; }
+        if (run_end != run_begin) AF8_CUDA_TRY(cudaMemsetAsync(run_begin, 0, (size_t)(run_end - run_begin), st));
+        run_begin = p;
+        run_end = p + 24;
+    }
+    if (run_end != run_begin) AF8_CUDA_TRY(cudaMemsetAsync(run_begin, 0, (size_t)(run_end - run_begin), st));
+    if (next != total_units) return fail(AF8_ERR_INVALID, "af8_apollo_scales_batch: total_units is %lld but the table holds %lld", (long long)total_units, (long long)next);
+    AF8_CUDA_TRY(cudaMemcpyAsync(dev_tensors, host_tensors, sizeof(af8_apollo_finish_tensor) * (size_t)n, cudaMemcpyHostToDevice, st));
+    int64_t grid = (int64_t)sm_count() * 8;
+    if (grid > total_units) grid = total_units;
+    apollo_scales_multi_kernel<<<(int)grid, 256, 0, st>>>(dev_tensors, n, total_units);
+    AF8_CUDA_TRY(cudaGetLastError());
+    apollo_finalize_multi_kernel<<<(n + 127) / 128, 128, 0, st>>>(dev_tensors, n);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }

@@ -72,8 +72,8 @@ AF8_API const char *af8_last_error(void);
 
 /* sizeof() of the i-th structure of this header as the library was compiled, in the order
  * fullrank_tensor, dyn_scalars, fullrank_cfg, norm_tensor, scale_tensor, small_state,
- * factored_tensor, factored_cfg, apollo_scalars_in, apollo_scalars, apollo_proj_desc; -1 for any
- * other index.
+ * factored_tensor, factored_cfg, apollo_scalars_in, apollo_scalars, apollo_proj_desc,
+ * apollo_finish_tensor; -1 for any other index.
  * A binding checks its own mirrors against these when it loads the library. */
 AF8_API int32_t af8_struct_size(int32_t index);
 
@@ -410,6 +410,25 @@ AF8_API int af8_apollo_scales(const float *upd, const float *g_low, const double
 /* p = p*decay + (update_scale * G) * (sf[channel] * fira * sqrt_scale) for fp32
  * parameters.  Replaces the apollo_apply_* kernels (kernels.cu:2834-3000) and the
  * torch mul_/addcmul_ write-back (optimizer.py:3073-3079). */
+/* af8_apollo_scales for all tensors of a group in two launches (channel-wise scaling only).
+ * host_tensors is pinned and stays valid until the copy has run; dev_tensors holds n entries.
+ * first_unit numbers 8-channel units across the table, total_units is their count. */
+typedef struct af8_apollo_finish_tensor {
+    const float *upd;       /* update_low, shaped like g_low */
+    const float *g_low;
+    const double *chan_g2;  /* from af8_apollo_project* */
+    float *sf;              /* out: max(rows, cols) scaling factors */
+    double *sums;           /* 3 accumulators */
+    float *fira_prev;       /* limiter state (NULL without the limiter) */
+    af8_apollo_scalars *out;
+    int64_t rows, cols, rank;
+    int64_t first_unit;
+    af8_apollo_scalars_in in;
+    int64_t reserved;
+} af8_apollo_finish_tensor;
+AF8_API int af8_apollo_scales_batch(const af8_apollo_finish_tensor *host_tensors, af8_apollo_finish_tensor *dev_tensors,
+                                    int32_t n, int64_t total_units, void *stream);
+
 AF8_API int af8_apollo_apply(void *param, const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
                              const af8_apollo_scalars *scalars, int64_t rows, int64_t cols,
                              const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *stream);
