@@ -13,7 +13,9 @@
 //   4. Fira limiter on that norm, clip, bias correction   optimizer.py:2990-3023
 //   5. p = p*decay + (update_scale * G) * final_scale      optimizer.py:3073-3079
 // Step 2 is the full-rank kernel run on g_low (its "parameter" output, with decay
-// 0 and step 1, is update_low); this file holds steps 1, 3, 4 and 5.
+// 0 and step 1, is update_low); this file holds steps 3, 4 and 5, the helpers of step 1
+// (channel norms, bf16 planes of Pt) and its exact SIMT form.  The tensor-core forms of
+// step 1 are in apollo_umma.cuh (tcgen05 + TMA) and apollo_mma.cuh (mma.sync).
 #pragma once
 
 #include <cstdlib>
@@ -48,8 +50,8 @@ __device__ __forceinline__ float apollo_grad_flag(const void *g, int dtype, int6
 //    Products of two binary32 numbers are exact in binary64 and the accumulation runs in
 //    binary64, so every output is the correctly rounded dot product whatever the order of
 //    summation: the low-rank states that are quantised from it do not depend on tiling.
-//    (A tensor-core version with a three-term bf16 split of Pt is the faster route for
-//    bf16 gradients; its binary32 accumulation moves codes next to a block minimum.)
+//    This is the path of fp32 gradients and odd shapes, and the bit-exact reference of the
+//    tensor-core kernels, whose binary32 accumulation moves codes next to a block minimum.
 // ---------------------------------------------------------------------------
 constexpr int PJ_TM = 64, PJ_TN = 64, PJ_TK = 16;
 
