@@ -187,6 +187,7 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
     // s_clean is only used by tiles of a tensor with non-finite entries; bit s of clean_phase
     // is the parity its next consumer waits for.
     int fills = 0, gchunk = 0;
+    int issued = 0;                 // producer only: stage fills issued so far
     uint32_t clean_phase = 0;
 
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -321,11 +322,21 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
                 mbar_expect_tx(&s_full[slot], bytes);
                 tma_load_2d(st, &U->map_a, ks * UM_BK, m0, &s_full[slot]);
                 tma_load_3d(st + UM_A_BYTES, &U->map_b, ks * UM_BK, 0, 0, &s_full[slot]);
+                issued = f + 1;
             }
         }
         if (failed) {
             s_abort = 1;
             atomicExch(&g_device_error, DEVERR_UMMA_TIMEOUT);
+        }
+        if (failed || volatile_load(&s_abort)) {
+            // a role gave up: the producer gives its copies still in flight a bounded chance to land
+            // before the block may end
+            if (warp == UM_TMA_WARP && lane == 0)
+                for (int back = 0; back < UM_STAGES && back < issued; ++back) {
+                    const int f = issued - 1 - back;
+                    mbar_wait_bounded(&s_full[f % UM_STAGES], (uint32_t)(f / UM_STAGES) & 1u);
+                }
             break;
         }
         if (dirty)
