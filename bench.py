@@ -256,8 +256,8 @@ def run_reference_arm(args):
     if rank != 0:
         return
     wl = WORKLOADS[args.workload]
-    steps = max(1, min(args.steps, 5))
-    warm = max(1, min(args.warmup, 2))
+    steps = max(1, min(args.steps, 50))     # about 0.1 s per step on the sample
+    warm = max(1, min(args.warmup, 5))
     r = cpu_reference_run(args.workload, steps, warm)
     line = {
         "impl": "reference", "metric": "optimizer_step_throughput", "value": r["value"], "unit": "Gparams/s",
