@@ -50,7 +50,7 @@
 /* state formats */
 enum { AF8O_V_FP32 = 0, AF8O_V_AL8 = 8, AF8O_V_AL16 = 16, AF8O_V_NONE = 1 };   /* NONE: the SGD mode, no second moment */
 enum { AF8O_M_NONE = 0, AF8O_M_UF8 = 1, AF8O_M_UF4 = 2, AF8O_M_D8 = 3, AF8O_M_D4 = 4, AF8O_M_FP32 = 5 };
-enum { AF8O_G_F32 = 0, AF8O_G_BF16 = 1 };
+enum { AF8O_G_F32 = 0, AF8O_G_BF16 = 1, AF8O_G_F16 = 2 };  /* gradient and parameter formats */
 
 AF8O_API int af8o_num_threads(void)
 {
@@ -92,11 +92,150 @@ static inline float lerp_t(float s, float e, float w)
     return (fabsf(w) < 0.5f) ? fmaf(w, d, s) : fmaf(w - 1.0f, d, e);
 }
 
+static inline float f16_to_f32(uint16_t h)
+{
+    _Float16 x;
+    memcpy(&x, &h, 2);
+    return (float)x;
+}
+
 static inline float load_grad(const void *g, int dtype, int64_t i, int negate)
 {
     float x = (dtype == AF8O_G_BF16) ? bf16_to_f32(((const uint16_t *)g)[i])
+            : (dtype == AF8O_G_F16)  ? f16_to_f32(((const uint16_t *)g)[i])
                                      : ((const float *)g)[i];
     return negate ? -x : x;
+}
+
+/* ------------------------------------------------------------------ */
+/* low-precision parameters and stochastic rounding                    */
+/* ------------------------------------------------------------------ */
+
+/* Tensor.to(torch.bfloat16) of a binary32 value: round to nearest even, NaN -> quiet NaN */
+static inline uint16_t f32_to_bf16_rn(float x)
+{
+    uint32_t b;
+    memcpy(&b, &x, 4);
+    if ((b & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((b >> 16) | 0x0040u);
+    b += 0x7fffu + ((b >> 16) & 1u);
+    return (uint16_t)(b >> 16);
+}
+static inline uint16_t f32_to_f16_rn(float x)
+{
+    _Float16 h = (_Float16)x;
+    uint16_t b;
+    memcpy(&b, &h, 2);
+    return b;
+}
+
+/* _stochastic_round_bf16_pytorch (optimizer.py:162-219): x lies between the bf16 numbers lo
+ * (truncation) and hi = lo + one unit; hi is taken when rand < (x - lo) / (hi - lo).  No
+ * step up out of an infinity or into one (finite overflow saturates); NaN keeps its sign. */
+AF8O_API uint16_t af8o_sr_bf16(float x, float rnd)
+{
+    uint32_t b;
+    memcpy(&b, &x, 4);
+    const uint32_t lo = b & 0xffff0000u;
+    const int is_nan = (b & 0x7f800000u) == 0x7f800000u && (b & 0x007fffffu) != 0;
+    if (is_nan) return (uint16_t)(((b & 0x80000000u) | 0x7fc00000u) >> 16);
+    const uint32_t hi = lo + 0x00010000u;
+    const int lo_inf = (lo & 0x7f800000u) == 0x7f800000u;
+    const int hi_inf = (hi & 0x7f800000u) == 0x7f800000u && (hi & 0x007fffffu) == 0;
+    const int can_up = (b & 0xffffu) != 0 && !lo_inf && !hi_inf;
+    if (!can_up) return (uint16_t)(lo >> 16);
+    float flo, fhi;
+    memcpy(&flo, &lo, 4);
+    memcpy(&fhi, &hi, 4);
+    const float prob = (x - flo) / (fhi - flo);
+    return (uint16_t)(((rnd < prob) ? hi : lo) >> 16);
+}
+
+/* _stochastic_round_fp16_pytorch (optimizer.py:222-283): the two fp16 neighbours of x are found
+ * from the nearest one; overflow saturates at the largest finite value, infinities and NaNs keep
+ * their sign. */
+AF8O_API uint16_t af8o_sr_f16(float x, float rnd)
+{
+    uint32_t xb;
+    memcpy(&xb, &x, 4);
+    const uint16_t sign = (xb & 0x80000000u) ? 0x8000u : 0u;
+    if (x != x) return (uint16_t)(sign | 0x7e00u);
+    if (isinf(x)) return (uint16_t)(sign | 0x7c00u);
+    if (fabsf(x) > 65504.0f) return (uint16_t)(sign | 0x7bffu);
+    const uint16_t q = f32_to_f16_rn(x);
+    const float qf = f16_to_f32(q);
+    if (qf == x) return q;
+    uint16_t up, down;
+    if (q == 0x8000u) up = 0x0001u; else up = (q & 0x8000u) ? (uint16_t)(q - 1) : (uint16_t)(q + 1);
+    if (q == 0x0000u) down = 0x8001u; else down = (q & 0x8000u) ? (uint16_t)(q + 1) : (uint16_t)(q - 1);
+    const uint16_t lo_b = (qf < x) ? q : down;
+    const uint16_t hi_b = (qf < x) ? up : q;
+    const float lo = f16_to_f32(lo_b), hi = f16_to_f32(hi_b);
+    const float span = hi - lo;
+    if (span == 0.0f) return lo_b;
+    const float prob = (x - lo) / span;
+    return (rnd < prob) ? hi_b : lo_b;
+}
+
+/* The uniform number of element idx: a counter-based generator, so that every element draws
+ * independently of the launch geometry.  The counter mixes the per-parameter seed and the step
+ * with the two odd constants of the reference's seeded stream (optimizer.py:205); the SplitMix64
+ * finaliser (Steele, Lea, Flood 2014) of counter + golden-gamma gives 64 bits, of which the top
+ * 24 become a number in [0, 1) (kernels.cu:48-65). */
+AF8O_API float af8o_sr_uniform(uint64_t seed, uint64_t step, uint64_t idx)
+{
+    uint64_t z = seed * 0x9E3779B97F4A7C15ull + step * 0xD1B54A32D192ED03ull + idx;
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (float)((uint32_t)(z >> 32) >> 8) * (1.0f / 16777216.0f);
+}
+
+/* Format of the parameter tensor that the next step call updates.  The parameter array of every
+ * step function holds binary32 numbers; for a bf16 / fp16 parameter they are the exactly
+ * representable values, and every write rounds to that format.  (A process-wide setting: the
+ * oracle steps one tensor at a time.) */
+static struct {
+    int32_t dtype;        /* AF8O_G_F32 / AF8O_G_BF16 / AF8O_G_F16 */
+    int32_t sr;           /* stochastic_round_writeback and a low-precision parameter (optimizer.py:2032) */
+    uint64_t seed, step;  /* state["sr_seed"], state["step"] (optimizer.py:2040) */
+    float decay;          /* decay_factor of the step under way (optimizer.py:2036) */
+} g_pf = {AF8O_G_F32, 0, 0, 0, 1.0f};
+
+AF8O_API void af8o_set_param_format(int32_t dtype, int32_t sr, uint64_t seed, uint64_t step)
+{
+    g_pf.dtype = dtype;
+    g_pf.sr = sr && dtype != AF8O_G_F32;
+    g_pf.seed = seed;
+    g_pf.step = step;
+    g_pf.decay = 1.0f;
+}
+
+static inline float round_param(float x)
+{
+    if (g_pf.dtype == AF8O_G_BF16) return bf16_to_f32(f32_to_bf16_rn(x));
+    if (g_pf.dtype == AF8O_G_F16) return f16_to_f32(f32_to_f16_rn(x));
+    return x;
+}
+
+/* weight decay (optimizer.py:2033-2039): param.mul_(1 - wd_mult*wd) in the parameter's own
+ * format, or, under stochastic rounding, a factor kept for the write (optimizer.py:2036) */
+static inline float decay_param(float p, int has_decay, float decay)
+{
+    if (!has_decay || g_pf.sr) return p;
+    return round_param(p * decay);
+}
+static void note_decay(int has_decay, float decay) { g_pf.decay = has_decay ? decay : 1.0f; }
+
+/* the write of _apply_update_pytorch (optimizer.py:873-881): p + s*u in binary32, then the
+ * parameter's format (nearest, or stochastic after the folded decay) */
+static inline float write_param(float p, float s, float u, int64_t i)
+{
+    if (!g_pf.sr) return round_param(fmaf(s, u, p));
+    float pf = p * g_pf.decay;                           /* optimizer.py:878 */
+    pf = fmaf(s, u, pf);                                 /* optimizer.py:879 */
+    const float rnd = af8o_sr_uniform(g_pf.seed, g_pf.step, (uint64_t)i);
+    return (g_pf.dtype == AF8O_G_BF16) ? bf16_to_f32(af8o_sr_bf16(pf, rnd)) : f16_to_f32(af8o_sr_f16(pf, rnd));
 }
 
 /* ------------------------------------------------------------------ */
@@ -431,7 +570,7 @@ static float apply_update(float *p, float *u, int64_t n, float alpha, float d,
     }
     float s = -alpha / denom;                            /* optimizer.py:874 */
 #pragma omp parallel for schedule(static)
-    for (int64_t i = 0; i < n; ++i) p[i] = fmaf(s, u[i], p[i]);
+    for (int64_t i = 0; i < n; ++i) p[i] = write_param(p[i], s, u[i], i);
     return norm;
 }
 
@@ -461,10 +600,11 @@ AF8O_API int af8o_fullrank_step(const af8o_fullrank_cfg *c, float *p,
         float *us = (float *)malloc((size_t)(n ? n : 1) * sizeof(float));
         if (!gs || !us) { free(gs); free(us); return 2; }
         int rcs = 0;
+    note_decay(c->has_decay, c->decay);
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < n; ++i) {
             gs[i] = load_grad(grad, c->grad_dtype, i, c->negate_grad);
-            if (c->has_decay) p[i] = p[i] * c->decay;
+            p[i] = decay_param(p[i], c->has_decay, c->decay);
         }
         if (has_m) {
             float *m = m_quant ? us : m_f32;
@@ -491,10 +631,11 @@ AF8O_API int af8o_fullrank_step(const af8o_fullrank_cfg *c, float *p,
 
     /* grad upcast (optimizer.py:1997), weight decay as its own pass
      * (optimizer.py:2039) */
+    note_decay(c->has_decay, c->decay);
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) {
         g[i] = load_grad(grad, c->grad_dtype, i, c->negate_grad);
-        if (c->has_decay) p[i] = p[i] * c->decay;
+        p[i] = decay_param(p[i], c->has_decay, c->decay);
     }
 
     if (v_quant) {
@@ -700,10 +841,11 @@ AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void
     float *inv_c = (float *)malloc((size_t)C * sizeof(float));
     if (!g || !u || !rmean || !cmean || !row || !col || !inv_r || !inv_c) return 2;
 
+    note_decay(c->has_decay, c->decay);
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) {
         g[i] = load_grad(grad, c->grad_dtype, i, c->negate_grad);
-        if (c->has_decay) p[i] = p[i] * c->decay;          /* optimizer.py:2039 */
+        p[i] = decay_param(p[i], c->has_decay, c->decay);          /* optimizer.py:2039 */
         u[i] = g[i] * g[i];                                /* optimizer.py:2221 */
     }
     row_col_means(u, R, C, rmean, cmean);                  /* optimizer.py:2222-2223 */

@@ -27,7 +27,8 @@ LOG_QUANT_FLOOR = 1.17549435e-38  # optimizer.py:23
 
 V_FMT = {"fp32": 0, "al8": 8, "al16": 16, "none": 1}
 M_FMT = {None: 0, "uf8": 1, "uf4": 2, "d8": 3, "d4": 4, "fp32": 5}
-G_F32, G_BF16 = 0, 1
+G_F32, G_BF16, G_F16 = 0, 1, 2
+P_FMT = {"f32": G_F32, "bf16": G_BF16, "f16": G_F16}
 
 f32 = np.float32
 c_f = ctypes.c_float
@@ -78,6 +79,12 @@ def lib():
         _lib.af8o_m_dequantize.argtypes = [c_p, c_p, c_l, c_l, c_i, c_p, c_p]
         _lib.af8o_fullrank_step.argtypes = [ctypes.POINTER(FullrankCfg)] + [c_p] * 10 + [
             ctypes.POINTER(c_i), ctypes.POINTER(c_f), ctypes.POINTER(c_f)]
+        _lib.af8o_set_param_format.argtypes = [c_i, c_i, ctypes.c_uint64, ctypes.c_uint64]
+        _lib.af8o_sr_uniform.restype = c_f
+        _lib.af8o_sr_uniform.argtypes = [ctypes.c_uint64] * 3
+        for fn in (_lib.af8o_sr_bf16, _lib.af8o_sr_f16):
+            fn.restype = ctypes.c_uint16
+            fn.argtypes = [c_f, c_f]
     return _lib
 
 
@@ -224,6 +231,8 @@ DEFAULTS = dict(
     apollo_factorize=False, apollo_cache_proj=False, enable_fira_for_apollo=True,
     scale_weight_decay=True, enable_fira_for_adafactor=False, fira_margin=0.01,
     lag_norm=False, momentum_only_1d=None, bias_correction=None,
+    stochastic_round_writeback=False,
+    param_dtype="f32",      # not a constructor option: the dtype of the parameter tensors of the run
 )
 
 
@@ -310,10 +319,39 @@ def is_sgd(hp):
     return hp["beta2"] is None and hp["beta2_decay"] is None
 
 
+class param_format:
+    """Context: the parameter array of the step calls inside holds the exact values of a bf16 /
+    fp16 parameter; writes round to that format, to nearest or stochastically with the
+    per-parameter seed (state["sr_seed"], optimizer.py:1889-1892) and the step number."""
+
+    def __init__(self, hp, state, step):
+        self.args = (P_FMT[hp.get("param_dtype", "f32")], int(bool(hp.get("stochastic_round_writeback", False))),
+                     int(state.get("sr_seed", 0)), int(step))
+
+    def __enter__(self):
+        lib().af8o_set_param_format(*self.args)
+
+    def __exit__(self, *exc):
+        lib().af8o_set_param_format(G_F32, 0, 0, 0)
+
+
+def sr_round(x, rnd, fmt):
+    """Stochastic rounding of binary32 values with given uniform numbers -> uint16 bit patterns."""
+    fn = lib().af8o_sr_bf16 if fmt == "bf16" else lib().af8o_sr_f16
+    return np.array([fn(float(a), float(b)) for a, b in zip(np.asarray(x, f32).reshape(-1), np.asarray(rnd, f32).reshape(-1))],
+                    dtype=np.uint16)
+
+
+def sr_uniform(seed, step, idx):
+    return f32(lib().af8o_sr_uniform(int(seed), int(step), int(idx)))
+
+
 def _grad_args(g):
     g = np.ascontiguousarray(g)
     if g.dtype == np.uint16:
         return g, G_BF16
+    if g.dtype == np.float16:
+        return g, G_F16
     assert g.dtype == f32
     return g, G_F32
 
@@ -414,12 +452,13 @@ def fullrank_step(p, g, state, hp, sc=None):
     has_prev = c_i(1 if "fira_prev_norm" in state else 0)
     prev = c_f(float(state.get("fira_prev_norm", 0.0)))
     norm = c_f(-1.0)
-    rc = lib().af8o_fullrank_step(
-        ctypes.byref(cfg), _ptr(p.reshape(-1)), _ptr(g.reshape(-1)),
-        _ptr(state.get("variance_q")), _ptr(state.get("variance_scale")),
-        _ptr(state.get("variance_min_log")), _ptr(state.get("variance")),
-        _ptr(state.get("m_q")), _ptr(state.get("m_scale")), _ptr(state.get("m")),
-        _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev), ctypes.byref(norm))
+    with param_format(hp, state, sc["step"]):
+        rc = lib().af8o_fullrank_step(
+            ctypes.byref(cfg), _ptr(p.reshape(-1)), _ptr(g.reshape(-1)),
+            _ptr(state.get("variance_q")), _ptr(state.get("variance_scale")),
+            _ptr(state.get("variance_min_log")), _ptr(state.get("variance")),
+            _ptr(state.get("m_q")), _ptr(state.get("m_scale")), _ptr(state.get("m")),
+            _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev), ctypes.byref(norm))
     if rc != 0:
         raise RuntimeError(f"af8o_fullrank_step failed with {rc}")
     if has_prev.value:
@@ -508,11 +547,12 @@ def factored_step(p, g, state, hp, sc=None):
     has_prev = c_i(1 if "fira_prev_norm" in state else 0)
     prev = c_f(float(state.get("fira_prev_norm", 0.0)))
     norm = c_f(-1.0)
-    rc = lib_.af8o_factored_step(
-        ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), ctypes.byref(row), ctypes.byref(col),
-        ctypes.byref(crow), ctypes.byref(ccol), _ptr(state.get("m_q")), _ptr(state.get("m_scale")),
-        _ptr(state.get("m")), _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev),
-        ctypes.byref(norm))
+    with param_format(hp, state, sc["step"]):
+        rc = lib_.af8o_factored_step(
+            ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), ctypes.byref(row), ctypes.byref(col),
+            ctypes.byref(crow), ctypes.byref(ccol), _ptr(state.get("m_q")), _ptr(state.get("m_scale")),
+            _ptr(state.get("m")), _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev),
+            ctypes.byref(norm))
     if rc != 0:
         raise RuntimeError(f"af8o_factored_step failed with {rc}")
     if has_prev.value:

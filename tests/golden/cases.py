@@ -24,9 +24,30 @@ def bf16_bits_to_f32(h):
     return (h.astype(np.uint32) << 16).view(f32)
 
 
-def make_param(shape, seed, std=0.02):
+def make_param(shape, seed, std=0.02, dtype="f32"):
+    """Initial parameter values as float32; for a bf16 / f16 parameter they are rounded to that
+    format first, so the float32 array holds the parameter exactly."""
     rng = np.random.Generator(np.random.PCG64(seed))
-    return (rng.standard_normal(shape, dtype=np.float64) * std).astype(f32)
+    p = (rng.standard_normal(shape, dtype=np.float64) * std).astype(f32)
+    if dtype == "bf16":
+        p = bf16_bits_to_f32(f32_to_bf16_bits(p)).reshape(shape)
+    elif dtype == "f16":
+        p = p.astype(np.float16).astype(f32)
+    return p
+
+
+def sr_uniform(seed, step, n):
+    """The n uniform numbers that stochastic rounding draws for the elements of one parameter at
+    one step: SplitMix64 finaliser of a counter made of the parameter's seed, the step and the
+    element index; the top 24 of its upper 32 bits scaled to [0, 1)."""
+    m64 = (1 << 64) - 1
+    base = (int(seed) * 0x9E3779B97F4A7C15 + int(step) * 0xD1B54A32D192ED03 + 0x9E3779B97F4A7C15) & m64
+    with np.errstate(over="ignore"):
+        z = np.arange(n, dtype=np.uint64) + np.uint64(base)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z = z ^ (z >> np.uint64(31))
+    return ((z >> np.uint64(40)).astype(f32) * f32(1.0 / 16777216.0)).astype(f32)
 
 
 def make_grad(shape, seed, step, spec):
@@ -47,7 +68,19 @@ def make_grad(shape, seed, step, spec):
     g = g.astype(f32)
     if spec.get("dtype", "f32") == "bf16":
         return f32_to_bf16_bits(g)
+    if spec.get("dtype") == "f16":
+        return g.astype(np.float16)
     return g
+
+
+def sr_edge_inputs():
+    """-> (x, rnd): every edge value paired with every uniform number."""
+    vals = np.array([0.0, -0.0, 1.0, 1.0 + 2.0 ** -9, -1.0 - 2.0 ** -9, 1.0 + 2.0 ** -8, 1.0 + 2.0 ** -11, 1.0 + 3 * 2.0 ** -12,
+                     3.3895313892515355e38, 3.39e38, 3.4028234663852886e38, -3.4e38, np.inf, -np.inf, np.nan, -np.nan,
+                     65504.0, 65505.0, 65519.0, 65520.0, 1e5, -1e5, 6e-8, -6e-8, 2.0 ** -25, 1e-10, -1e-10, 1e-45, 0.1, -0.3,
+                     6.1e-5, 6.097e-5], dtype=f32)
+    u = np.array([0.0, 0.1, 0.25, 0.5, 0.75, 0.9, 0.99999994], dtype=f32)
+    return np.repeat(vals, u.size).copy(), np.tile(u, vals.size).copy()
 
 
 def digest(arrays):
@@ -131,13 +164,38 @@ CASES = {
                        hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=32,
                                apollo_update_proj_gap=3, m_quant_type="uf8",
                                v_quant_type="al8", block_size=2048)),
+    # ---- bf16 / fp16 parameters (case key param_dtype): nearest rounding on every write, or
+    #      stochastic rounding fed by the counter generator of sr_uniform ----
+    "adamw_bf16p": dict(shapes=[(64, 200), (4096,)], steps=6, seed=31, param_dtype="bf16",
+                        grad=dict(_G_HEAVY, spike_step=4, spike_mult=100.0),
+                        hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
+                                enable_fira_for_adafactor=True, fira_margin=0.01)),
+    "adamw_f16p": dict(shapes=[(40, 130)], steps=4, seed=32, param_dtype="f16",
+                       grad=dict(dist="normal", std=1e-2, zero_frac=0.01, dtype="f16"),
+                       hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256)),
+    "adamw_sr_bf16p": dict(shapes=[(64, 200), (4096,)], steps=6, seed=33, param_dtype="bf16",
+                           grad=dict(_G_HEAVY, spike_step=4, spike_mult=100.0),
+                           hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
+                                   enable_fira_for_adafactor=True, fira_margin=0.01, stochastic_round_writeback=True)),
+    "adamw_sr_f16p": dict(shapes=[(40, 130)], steps=4, seed=34, param_dtype="f16",
+                          grad=dict(dist="normal", std=1e-2, zero_frac=0.01, dtype="f16"),
+                          hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
+                                  stochastic_round_writeback=True)),
+    "adafactor_bf16p": dict(shapes=[(320, 192), (2048,)], steps=4, seed=35, param_dtype="bf16", grad=_G_HEAVY,
+                            hp=dict(block_size=256, weight_decay=0.01)),
+    "came_sr_bf16p": dict(shapes=[(64, 384)], steps=4, seed=36, param_dtype="bf16", grad=_G_BF16,
+                          hp=dict(_CAME, lr=1e-4, weight_decay=0.01, m_quant_type="uf8", v_quant_type="al16", c_quant_type="al16",
+                                  block_size=2048, stochastic_round_writeback=True)),
 }
+
+LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]
+LOWP_FACTORED_CASES = ["adafactor_bf16p", "came_sr_bf16p"]
 
 
 def case_inputs(name):
     """-> (params0, grads[step][i]) for a case (its name, or a dict of the same form), steps numbered from 1."""
     c = name if isinstance(name, dict) else CASES[name]
-    params = [make_param(s, c["seed"] * 1000 + i) for i, s in enumerate(c["shapes"])]
+    params = [make_param(s, c["seed"] * 1000 + i, dtype=c.get("param_dtype", "f32")) for i, s in enumerate(c["shapes"])]
     grads = {}
     for t in range(1, c["steps"] + 1):
         grads[t] = [make_grad(s, c["seed"] * 1000 + 500 + i, t, c["grad"])

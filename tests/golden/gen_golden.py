@@ -18,6 +18,16 @@ It writes one ``<case>.npz`` per case.  Keys: ``digest`` (sha256 of the inputs),
 ``t<step>_p<i>_param`` and ``t<step>_p<i>_<state key>`` for every tensor-valued
 state entry after that step.  Arrays of 50 000 elements or more are stored only
 after steps 1, 2 and the last one; smaller ones after every step.
+
+Cases with ``param_dtype`` "bf16" / "f16" run the reference on parameters of that
+dtype (stored in the fixture converted to float32, which is exact).  With
+``stochastic_round_writeback`` the reference draws its uniform numbers from a
+seeded torch generator, whose stream nothing else can reproduce; for those cases
+``torch.rand`` is swapped, during the reference's rounding routine only, for the
+counter generator of cases.sr_uniform (the stream of the reference's own CUDA
+kernels, kernels.cu:48-65), fed with the seed and step that the reference
+passes.  The reference's rounding logic itself (neighbours, probability,
+saturation) runs unchanged.
 """
 import argparse
 import os
@@ -50,6 +60,26 @@ def install_accurate_norm():
     torch.Tensor.norm = tensor_norm
 
 
+def install_counter_uniforms():
+    """Make the reference's stochastic rounding draw from cases.sr_uniform(seed, step, n)."""
+    import torch
+    import adafactor8bit.optimizer as ro
+    inner = ro._stochastic_round_lowp_pytorch
+    real_rand = torch.rand
+
+    def lowp(fp32_tensor, dtype, seed=None, step=None):
+        u = torch.from_numpy(cases.sr_uniform(seed, step, fp32_tensor.numel()))
+        fn = ro._stochastic_round_bf16_pytorch if dtype == torch.bfloat16 else ro._stochastic_round_fp16_pytorch
+        torch.rand = lambda *a, **k: u
+        try:
+            return fn(fp32_tensor, generator=True)
+        finally:
+            torch.rand = real_rand
+
+    ro._stochastic_round_lowp_pytorch = lowp
+    return inner
+
+
 def run_case(name, out_dir, suffix=""):
     import torch
     from adafactor8bit import Adafactor8Bit
@@ -57,7 +87,10 @@ def run_case(name, out_dir, suffix=""):
     c = cases.CASES[name]
     params0, grads = cases.case_inputs(name)
     out = {"digest": np.array(cases.inputs_digest(params0, grads))}
-    params = [torch.nn.Parameter(torch.from_numpy(p.copy())) for p in params0]
+    tdt = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[c.get("param_dtype", "f32")]
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(tdt)) for p in params0]
+    if c["hp"].get("stochastic_round_writeback"):
+        install_counter_uniforms()
     for p in params:
         p.grad_dtype = None  # allow bf16 grads on fp32 parameters
     opt = Adafactor8Bit(params, use_cuda_kernel=False, **c["hp"])
@@ -71,7 +104,7 @@ def run_case(name, out_dir, suffix=""):
         opt.step()
         keep_big = t in (1, 2, steps)
         for i, p in enumerate(params):
-            entries = {"param": p.detach()}
+            entries = {"param": p.detach().float()}
             for k, v in opt.state[p].items():
                 if isinstance(v, torch.Tensor):
                     entries[k] = v
@@ -97,6 +130,25 @@ def run_case(name, out_dir, suffix=""):
     print(f"{name}: {len(out)} arrays, {os.path.getsize(path) / 1e6:.2f} MB")
 
 
+def run_sr_edges(out_dir):
+    """Known answers of the reference's two stochastic rounding routines on the values of
+    cases.sr_edge_inputs() (zeros, ties, the largest finite numbers, infinities, NaNs, subnormals),
+    each with every uniform number of the list."""
+    import torch
+    import adafactor8bit.optimizer as ro
+    x, rnd = cases.sr_edge_inputs()
+    real_rand = torch.rand
+    out = {"digest": np.array(cases.digest([x, rnd]))}
+    torch.rand = lambda *a, **k: torch.from_numpy(rnd.copy())
+    try:
+        out["bf16"] = ro._stochastic_round_bf16_pytorch(torch.from_numpy(x.copy()), generator=True).view(torch.int16).numpy().view(np.uint16)
+        out["f16"] = ro._stochastic_round_fp16_pytorch(torch.from_numpy(x.copy()), generator=True).view(torch.int16).numpy().view(np.uint16)
+    finally:
+        torch.rand = real_rand
+    np.savez_compressed(os.path.join(out_dir, "sr_edges.npz"), **out)
+    print("sr_edges:", x.size, "values")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True,
@@ -107,10 +159,13 @@ def main():
     sys.path.insert(0, args.reference)
     import torch
     torch.manual_seed(0)
-    names = args.cases or list(cases.CASES)
+    names = args.cases or (list(cases.CASES) + ["sr_edges"])
     if args.accurate_norm:
         install_accurate_norm()
     for name in names:
+        if name == "sr_edges":
+            run_sr_edges(HERE)
+            continue
         run_case(name, HERE, "__accnorm" if args.accurate_norm else "")
 
 

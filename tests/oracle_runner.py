@@ -19,7 +19,7 @@ class OracleRun:
         """`case`: a dict of the same form as the entries of cases.CASES, for cases without fixtures."""
         self.name = name
         self.case = case if case is not None else cases.CASES[name]
-        self.hp = o.hyper(**self.case["hp"])
+        self.hp = o.hyper(**self.case["hp"], param_dtype=self.case.get("param_dtype", "f32"))
         self.params0, self.grads = cases.case_inputs(self.case)
         self.params = [p.copy() for p in self.params0]
         self.states = [o.init_state(p.shape, self.hp) for p in self.params]
@@ -28,6 +28,9 @@ class OracleRun:
             if "apollo_seed" in st:
                 st["apollo_seed"] = seed
                 seed += 1
+        if self.hp["stochastic_round_writeback"] and self.hp["param_dtype"] != "f32":
+            for k, st in enumerate(self.states):     # optimizer-level counter from 1, in parameter order (optimizer.py:1461, 1889-1892)
+                st["sr_seed"] = k + 1
         self.t = 0
 
     def step_param(self, i, p, g, st):

@@ -75,3 +75,27 @@ def assert_params(a, b, what, tol=PARAM_REL):
     r = rel_l2(a, b)
     assert r <= tol, f"{what}: parameter relative L2 error {r:.3e} > {tol}"
     return r
+
+
+def lowp_ordinal(x, fmt):
+    """Position of each value (exactly representable in bf16 / f16) on that format's number line."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    if fmt == "bf16":
+        bits = (x.view(np.uint32) >> 16).astype(np.int64)
+    else:
+        bits = x.astype(np.float16).view(np.uint16).astype(np.int64)
+    return np.where(bits & 0x8000, -(bits & 0x7FFF), bits)
+
+
+def lowp_stats(a, b, fmt):
+    d = np.abs(lowp_ordinal(a, fmt) - lowp_ordinal(b, fmt))
+    return dict(n=d.size, neq=int((d > 0).sum()), max=int(d.max()) if d.size else 0)
+
+
+def assert_lowp_params(a, b, fmt, what, frac, max_units=1):
+    """bf16 / f16 parameters: equal except on a fraction `frac` of the elements, which may sit
+    on the neighbouring number of the format."""
+    s = lowp_stats(a, b, fmt)
+    assert s["max"] <= max_units, f"{what}: a parameter is {s['max']} units of the format away; {s}"
+    assert s["neq"] <= max(1, math.ceil(frac * s["n"])), f"{what}: {s['neq']} of {s['n']} parameters differ (allowed fraction {frac})"
+    return s

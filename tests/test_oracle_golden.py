@@ -207,3 +207,54 @@ def test_apollo_oracle_against_reference(oracle):
             elif "variance_q" in ref:
                 parity.assert_codes(st["variance_q"], ref["variance_q"], what + " variance_q")
                 parity.assert_codes(st["m_q"], ref["m_q"], what + " m_q", zero_reserved=False)
+
+
+# ---------------------------------------------------------------------------
+# bf16 / fp16 parameters, nearest and stochastic rounding (optimizer.py:162-292, 866-881)
+# ---------------------------------------------------------------------------
+def test_stochastic_rounding_known_answers(oracle):
+    """The two rounding routines on edge values (zeros, exact values, the largest finite numbers,
+    overflow, infinities, NaNs, subnormals), bit for bit against the reference's routines."""
+    gold = load_golden("sr_edges")
+    x, rnd = cases.sr_edge_inputs()
+    assert str(gold["digest"]) == cases.digest([x, rnd])
+    for fmt in ("bf16", "f16"):
+        assert np.array_equal(oracle.sr_round(x, rnd, fmt), gold[fmt]), fmt
+    # the counter generator: the C routine and the numpy restatement that fed the reference
+    u = cases.sr_uniform(3, 7, 1000)
+    assert u.min() >= 0.0 and u.max() < 1.0 and abs(float(u.mean()) - 0.5) < 0.03
+    for idx in (0, 1, 17, 999):
+        assert oracle.sr_uniform(3, 7, idx) == u[idx]
+
+
+@pytest.mark.parametrize("name", cases.LOWP_FULLRANK_CASES + cases.LOWP_FACTORED_CASES)
+def test_low_precision_parameters_free_running(name, oracle):
+    """Free-running steps on bf16 / fp16 parameters.  The full-rank cases agree with the reference
+    in every parameter bit and every code, stochastic rounding included (same uniform numbers);
+    in the factored cases torch's float32 means move a parameter in ten thousand to the
+    neighbouring number of its format and an occasional small-state code by one."""
+    run = OracleRun(name)
+    gold = load_golden(name)
+    assert str(gold["digest"]) == cases.inputs_digest(run.params0, run.grads)
+    fmt = run.case["param_dtype"]
+    exact = name in cases.LOWP_FULLRANK_CASES
+    for t in range(1, run.case["steps"] + 1):
+        run.step()
+        for i, (p, st) in enumerate(zip(run.params, run.states)):
+            ref = golden_entries(gold, t, i)
+            for key, want in ref.items():
+                what = f"{name} step {t} param {i} {key}"
+                if key == "param":
+                    parity.assert_lowp_params(p, want, fmt, what, frac=0.0 if exact else 2e-4)
+                    if exact:
+                        assert np.array_equal(p.reshape(-1), want), what
+                elif key in CODE_KEYS:
+                    if exact:
+                        assert np.array_equal(st[key], want), what
+                    else:
+                        s = parity.code_stats(st[key], want)
+                        al16 = want.dtype == np.uint16
+                        assert s["zero_mismatch"] == 0 and s["max"] <= (parity.CODE_SLACK_AL16 if al16 else 1), (what, s)
+                        assert s["neq"] <= max(2, (3e-2 if al16 else 1e-4) * s["n"]), (what, s)
+                elif key.endswith(RANGE_SUFFIXES):
+                    parity.assert_ranges(st[key], want, what, max_ulp=0 if exact else 128)
