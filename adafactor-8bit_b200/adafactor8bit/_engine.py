@@ -14,7 +14,16 @@ import torch
 
 from . import _native as N
 
-_GRAD_DT = {torch.float32: N.F32, torch.bfloat16: N.BF16}
+_GRAD_DT = {torch.float32: N.F32, torch.bfloat16: N.BF16, torch.float16: N.F16}
+_SR_K1, _SR_K2, _M64 = 0x9E3779B97F4A7C15, 0xD1B54A32D192ED03, (1 << 64) - 1
+
+
+def sr_base(seed, step):
+    """Counter origin of a parameter's stochastic rounding at one step: the seed / step mix of
+    the reference's seeded stream (optimizer.py:205; kernels.cu:56-61); element i draws from
+    counter sr_base + i."""
+    return (int(seed) * _SR_K1 + int(step) * _SR_K2) & _M64
+
 
 
 def _ptr(t):
@@ -101,14 +110,18 @@ class FullrankPlan:
     the kernel configuration `key`; per-tensor scalars live in the table."""
 
     def __init__(self, device, grad_dtype, v_fmt, m_fmt, block, m_block, use_adam_denom,
-                 momentum_only, negate, params, states):
+                 momentum_only, negate, params, states, stochastic_round=False):
         self.device = torch.device(device)
         self.params = list(params)
         self.states = list(states)
         n = len(self.params)
         self.n = n
         self.cfg = N.FullrankCfg()
-        self.cfg.param_dtype = N.F32
+        pdt = self.params[0].dtype
+        if pdt not in _GRAD_DT or any(p.dtype != pdt for p in self.params):
+            raise RuntimeError("the full-rank kernels update fp32, bf16 or fp16 parameters, one dtype per launch group")
+        self.cfg.param_dtype = _GRAD_DT[pdt]
+        self.cfg.stochastic_round = int(bool(stochastic_round) and pdt != torch.float32)   # optimizer.py:2032
         self.cfg.grad_dtype = _GRAD_DT[grad_dtype]
         self.cfg.v_fmt = N.V_FMT[v_fmt]
         self.cfg.m_fmt = N.M_FMT[m_fmt]
@@ -141,8 +154,6 @@ class FullrankPlan:
         self._static = None
         self._alpha_on_device = False
         for p in self.params:
-            if p.dtype != torch.float32:
-                raise RuntimeError("the full-rank kernels update fp32 parameters only")
             if not p.is_contiguous():
                 raise RuntimeError("parameters must be contiguous")
 
@@ -177,13 +188,16 @@ class FullrankPlan:
         table["grad"] = [g.data_ptr() for g in grads]
         for k in ("decay", "alpha", "v_w", "v_keep", "v_eps_add", "m_w", "eps_gradsq", "eps_denom", "eps_sq"):
             table[k] = scalars[k]
+        table["sr_base"] = scalars.get("sr_base", 0)
         return buf, table
 
     # -- launches ------------------------------------------------------------
     def kernel_name(self, mode):
         c = self.cfg
         fast = (c.v_fmt == N.V_AL8 and c.m_fmt == N.M_UF8 and c.block == 2048 and c.m_block == 256
-                and c.use_adam_denom and not c.momentum_only and mode != N.MODE_SUMSQ_M)
+                and c.use_adam_denom and not c.momentum_only and mode != N.MODE_SUMSQ_M
+                and ((c.param_dtype == N.F32 and c.grad_dtype in (N.F32, N.BF16))
+                     or (c.param_dtype == N.BF16 and c.grad_dtype == N.BF16)))
         if fast and mode == N.MODE_SUMSQ:
             return "fullrank_stat"
         return ("fullrank_fast_" if fast else "fullrank_generic_") + _MODE_NAMES[mode]
@@ -263,6 +277,7 @@ class FullrankPlan:
         t["numel"] = self.numel
         t["first_chunk"] = np.concatenate([[0], np.cumsum(nchunks)[:-1]])
         t["sqrt_n"] = np.sqrt(self.numel.astype(np.float64)).astype(np.float32)
+        t["param_dtype"] = self.cfg.param_dtype
         for k in ("rho", "eps2", "bc", "weight_decay", "bc_mode", "scale_weight_decay"):
             t[k] = scale[k]
         rc = N.lib().af8_param_scale(hb.data_ptr(), self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(),

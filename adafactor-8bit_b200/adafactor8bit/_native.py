@@ -32,8 +32,9 @@ FULLRANK_TENSOR = np.dtype([
     ("decay", np.float32), ("alpha", np.float32), ("v_w", np.float32), ("v_keep", np.float32),
     ("v_eps_add", np.float32), ("m_w", np.float32), ("eps_gradsq", np.float32),
     ("eps_denom", np.float32), ("eps_sq", np.float32), ("reserved", np.float32),
+    ("sr_base", np.uint64), ("reserved2", np.uint64),
 ], align=True)
-assert FULLRANK_TENSOR.itemsize == 128
+assert FULLRANK_TENSOR.itemsize == 144
 
 DYN_SCALARS = np.dtype([
     ("step", np.float32), ("fira", np.float32), ("pre_div", np.float32), ("zero", np.float32),
@@ -80,7 +81,7 @@ SCALE_TENSOR = np.dtype([
     ("param", _P), ("numel", np.int64), ("first_chunk", np.int64),
     ("sqrt_n", np.float32), ("rho", np.float32), ("eps2", np.float32), ("bc", np.float32),
     ("weight_decay", np.float32), ("bc_mode", np.int32), ("scale_weight_decay", np.int32),
-    ("reserved", np.int32),
+    ("param_dtype", np.int32),
 ], align=True)
 assert SCALE_TENSOR.itemsize == 56
 
@@ -92,7 +93,7 @@ class FullrankCfg(ctypes.Structure):
         ("block", ctypes.c_int32), ("m_block", ctypes.c_int32),
         ("use_adam_denom", ctypes.c_int32), ("momentum_only", ctypes.c_int32),
         ("negate_grad", ctypes.c_int32), ("mode", ctypes.c_int32),
-        ("v_floor", ctypes.c_float), ("reserved", ctypes.c_int32),
+        ("v_floor", ctypes.c_float), ("stochastic_round", ctypes.c_int32),
     ]
 
 

@@ -22,7 +22,9 @@ from torch import Tensor
 from torch.optim import Optimizer
 
 from . import _native as N
-from ._engine import ApolloPlan, FactoredPlan, FullrankPlan
+from ._engine import ApolloPlan, FactoredPlan, FullrankPlan, sr_base
+
+_FULLRANK_COLS = ("decay", "alpha", "v_w", "v_keep", "v_eps_add", "m_w", "eps_gradsq", "eps_denom", "eps_sq")
 
 __all__ = ["Adafactor8Bit"]
 
@@ -400,6 +402,14 @@ class Adafactor8Bit(Optimizer):
                 self._after_group(gi, group)
         return loss
 
+    def _sr_seed(self, state):
+        """The parameter's stochastic-rounding seed, taken from the optimizer-level counter the
+        first time the parameter is rounded (optimizer.py:1889-1892)."""
+        if "sr_seed" not in state:
+            state["sr_seed"] = self._sr_seed_counter
+            self._sr_seed_counter += 1
+        return state["sr_seed"]
+
     def _run_group(self, gi, group, entries):
         apollo_rank = group.get("apollo_rank", 0)
         factored = group.get("factored", True)
@@ -412,7 +422,7 @@ class Adafactor8Bit(Optimizer):
                     m_block = st.get("m_block_size", group.get("m_block_size", 256))
                 else:
                     m_fmt, m_block = None, 0
-                key = (p.device, g.dtype, "none", m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block)
+                key = (p.device, g.dtype, "none", m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block, p.dtype)
                 fullrank.setdefault(key, []).append((p, g, st))
                 continue
             if apollo_rank > 0 and "apollo_seed" in st:
@@ -434,7 +444,7 @@ class Adafactor8Bit(Optimizer):
                 factored_items.setdefault(key, []).append((p, g, st))
                 continue
             v_fmt = st.get("v_quant_type", "al8") if quant else "fp32"
-            key = (p.device, g.dtype, v_fmt, m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block)
+            key = (p.device, g.dtype, v_fmt, m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block, p.dtype)
             fullrank.setdefault(key, []).append((p, g, st))
         for key, items in fullrank.items():
             self._run_fullrank(gi, group, key, items)
@@ -622,7 +632,8 @@ class Adafactor8Bit(Optimizer):
                      fira_margin=float(group.get("fira_margin", 0.01)), scale=scale)
 
     def _run_fullrank(self, gi, group, key, items):
-        device, gdtype, v_fmt, m_fmt, block, m_block = key
+        device, gdtype, v_fmt, m_fmt, block, m_block, pdtype = key
+        sr = bool(group.get("stochastic_round_writeback", False)) and pdtype in (torch.bfloat16, torch.float16)
         sc0 = self._step_scalars(group, 1)
         momentum_only = group.get("momentum_only_1d")
         if momentum_only is None:
@@ -631,11 +642,12 @@ class Adafactor8Bit(Optimizer):
         if sgd:
             momentum_only = False
         ids = tuple(id(p) for p, _, _ in items)
-        pkey = (gi, "fullrank", key, bool(momentum_only), bool(group["maximize"]))
+        pkey = (gi, "fullrank", key, bool(momentum_only), bool(group["maximize"]), sr)
         plan = self._plans.get(pkey)
         if plan is None or plan.ids != ids:
             plan = FullrankPlan(device, gdtype, v_fmt, m_fmt, block, m_block, sc0["adam"], momentum_only,
-                                group["maximize"], [p for p, _, _ in items], [s for _, _, s in items])
+                                group["maximize"], [p for p, _, _ in items], [s for _, _, s in items],
+                                stochastic_round=sr)
             plan.ids = ids
             self._plans[pkey] = plan
         n = len(items)
@@ -644,13 +656,16 @@ class Adafactor8Bit(Optimizer):
             scale = {k: np.zeros(n, dtype=f32) for k in ("rho", "eps2", "bc", "weight_decay")}
             scale["bc_mode"] = np.zeros(n, dtype=np.int32)
             scale["scale_weight_decay"] = np.full(n, int(bool(group.get("scale_weight_decay", True))), dtype=np.int32)
-        cols = {k: np.empty(n, dtype=f32) for k in
-                ("decay", "alpha", "v_w", "v_keep", "v_eps_add", "m_w", "eps_gradsq", "eps_denom", "eps_sq")}
+        cols = {k: np.empty(n, dtype=f32) for k in _FULLRANK_COLS}
+        if sr:
+            cols["sr_base"] = np.zeros(n, dtype=np.uint64)
         cache = {}
         grads = []
         for i, (p, g, st) in enumerate(items):
             step = st["step"] + 1
             st["step"] = step
+            if sr:
+                cols["sr_base"][i] = sr_base(self._sr_seed(st), step)
             vals = cache.get(step)
             if vals is None:
                 sc = self._step_scalars(group, step)
@@ -661,7 +676,7 @@ class Adafactor8Bit(Optimizer):
                         f32(1.0 - group["beta1"]) if group.get("beta1") is not None else f32(0.0),
                         f32(sc["eps_gradsq"]), f32(sc["eps_denom"]), f32(sc["eps_sq"]))
                 cache[step] = vals
-            for k, v in zip(cols, vals):
+            for k, v in zip(_FULLRANK_COLS, vals):
                 cols[k][i] = v
             if scale is not None:
                 sc = self._step_scalars(group, step)

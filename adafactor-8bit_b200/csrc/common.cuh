@@ -11,6 +11,8 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
@@ -71,6 +73,104 @@ inline int sm_count()
 #define AF8_TINY 1e-38f
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+
+// ---------------------------------------------------------------------------
+// bf16 / fp16 parameters: nearest and stochastic rounding
+// (optimizer.py:162-292, 866-881; kernels.cu:48-161)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+
+// Tensor.to(bfloat16) / Tensor.to(float16) of a binary32 value: nearest even
+__device__ __forceinline__ uint32_t f32_to_bf16_rn_bits(float x) { return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ uint32_t f32_to_f16_rn_bits(float x) { return (uint32_t)__half_as_ushort(__float2half_rn(x)); }
+
+__device__ __forceinline__ float param_load(const void *p, int64_t i, int dtype)
+{
+    if (dtype == AF8_F32) return static_cast<const float *>(p)[i];
+    const uint32_t h = static_cast<const uint16_t *>(p)[i];
+    return dtype == AF8_BF16 ? bf16_bits_to_f32(h) : f16_bits_to_f32(h);
+}
+// x rounded to the nearest number of the parameter's format, as a binary32 value
+__device__ __forceinline__ float param_round(float x, int dtype)
+{
+    if (dtype == AF8_BF16) return bf16_bits_to_f32(f32_to_bf16_rn_bits(x));
+    if (dtype == AF8_F16) return f16_bits_to_f32(f32_to_f16_rn_bits(x));
+    return x;
+}
+
+// The 24 random bits of element idx: SplitMix64 finaliser of counter + golden gamma, upper
+// 32 bits, top 24 of those.  `base` = seed * 0x9E3779B97F4A7C15 + step * 0xD1B54A32D192ED03
+// (mod 2^64) is computed on the host per parameter and step.
+__device__ __forceinline__ uint32_t sr_bits24(uint64_t base, uint64_t idx)
+{
+    uint64_t z = base + idx + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (uint32_t)(z >> 40);
+}
+
+// Stochastic rounding to bf16: the truncation lo, or lo + one unit with probability
+// (x - lo) / unit = low16 / 65536.  The uniform number is r24 / 2^24, so "uniform < probability"
+// is the integer comparison r24 < low16 * 256.  No step out of or into an infinity; NaN keeps
+// its sign (optimizer.py:162-219).
+__device__ __forceinline__ uint32_t sr_bf16_bits(float x, uint32_t r24)
+{
+    const uint32_t b = __float_as_uint(x);
+    const uint32_t low = b & 0xffffu;
+    const uint32_t lo = b >> 16;
+    if ((b & 0x7fffffffu) > 0x7f800000u) return ((b >> 16) & 0x8000u) | 0x7fc0u;
+    const bool can_up = low != 0u && (lo & 0x7f80u) != 0x7f80u && ((lo + 1u) & 0x7fffu) != 0x7f80u;
+    return (can_up && r24 < (low << 8)) ? lo + 1u : lo;
+}
+
+// Stochastic rounding to fp16 between the two neighbours of x found from the nearest one;
+// overflow saturates, infinities and NaNs keep their sign (optimizer.py:222-283).
+__device__ __forceinline__ uint32_t sr_f16_bits(float x, uint32_t r24)
+{
+    const uint32_t sign = (__float_as_uint(x) >> 16) & 0x8000u;
+    if (isnan(x)) return sign | 0x7e00u;
+    if (isinf(x)) return sign | 0x7c00u;
+    if (fabsf(x) > 65504.0f) return sign | 0x7bffu;
+    const uint32_t q = f32_to_f16_rn_bits(x);
+    const float qf = f16_bits_to_f32(q);
+    if (qf == x) return q;
+    const uint32_t up = (q == 0x8000u) ? 0x0001u : ((q & 0x8000u) ? q - 1u : q + 1u);
+    const uint32_t down = (q == 0x0000u) ? 0x8001u : ((q & 0x8000u) ? q + 1u : q - 1u);
+    const uint32_t lo_b = (qf < x) ? q : down, hi_b = (qf < x) ? up : q;
+    const float lo = f16_bits_to_f32(lo_b), hi = f16_bits_to_f32(hi_b);
+    const float span = __fsub_rn(hi, lo);
+    if (span == 0.0f) return lo_b;
+    const float prob = __fdiv_rn(__fsub_rn(x, lo), span);
+    const float u = __fmul_rn((float)r24, 1.0f / 16777216.0f);
+    return (u < prob) ? hi_b : lo_b;
+}
+
+// One parameter write of _apply_update_pytorch (optimizer.py:866-881) plus the weight decay
+// of the prologue (optimizer.py:2033-2039):
+//   fp32:            p*decay, then fma(step, u, .)
+//   bf16/fp16:       the same two operations, each rounded to the parameter's format
+//   stochastic:      fma(step, u, p*decay) in binary32, one stochastic rounding
+// p is the loaded parameter as binary32; the result is the value to store (binary32 for fp32
+// parameters, else the 16-bit pattern).
+__device__ __forceinline__ uint32_t param_step_bits(float p, float decay, float step, float u, int dtype, int sr,
+                                                    uint64_t sr_base, int64_t idx)
+{
+    if (dtype == AF8_F32) return __float_as_uint(__fmaf_rn(step, u, __fmul_rn(p, decay)));
+    if (!sr) {
+        const float p1 = param_round(__fmul_rn(p, decay), dtype);
+        const float p2 = __fmaf_rn(step, u, p1);
+        return dtype == AF8_BF16 ? f32_to_bf16_rn_bits(p2) : f32_to_f16_rn_bits(p2);
+    }
+    const float pf = __fmaf_rn(step, u, __fmul_rn(p, decay));
+    const uint32_t r = sr_bits24(sr_base, (uint64_t)idx);
+    return dtype == AF8_BF16 ? sr_bf16_bits(pf, r) : sr_f16_bits(pf, r);
+}
+__device__ __forceinline__ void param_store_bits(void *p, int64_t i, uint32_t bits, int dtype)
+{
+    if (dtype == AF8_F32) static_cast<uint32_t *>(p)[i] = bits;
+    else static_cast<uint16_t *>(p)[i] = (uint16_t)bits;
+}
 
 // Tensor.lerp_(end, w) as ATen computes it (optimizer.py:698, 2119).
 __device__ __forceinline__ float lerp_t(float s, float e, float w)

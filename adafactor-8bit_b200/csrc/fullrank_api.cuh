@@ -98,11 +98,11 @@ inline int persistent_grid(K kernel, int threads, size_t smem, int64_t total_blo
     return AF8_OK;
 }
 
-template <typename GradT, int MODE>
+template <typename GradT, typename ParamT, int MODE>
 inline int launch_fast(const FullrankLaunch &L, cudaStream_t st)
 {
-    using Ring = FastRing<GradT, MODE>;
-    auto kernel = fullrank_fast_kernel<GradT, MODE>;
+    using Ring = FastRing<GradT, ParamT, MODE>;
+    auto kernel = fullrank_fast_kernel<GradT, ParamT, MODE>;
     // the ring lives in dynamic shared memory (up to 48-60 KB per CTA): opt in and ask for
     // the large shared-memory carve-out
     AF8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring::SMEM_BYTES));
@@ -147,18 +147,26 @@ inline int launch_generic(const FullrankLaunch &L, const GenericCfg &C, cudaStre
     return AF8_OK;
 }
 
+// the general kernel in any mode
 template <typename GradT>
-inline int dispatch_mode(bool fast, int mode, const FullrankLaunch &L, const GenericCfg &C, cudaStream_t st)
+inline int dispatch_generic(int mode, const FullrankLaunch &L, const GenericCfg &C, cudaStream_t st)
 {
     switch (mode) {
-    case AF8_MODE_NOCLIP:
-        return fast ? launch_fast<GradT, AF8_MODE_NOCLIP>(L, st) : launch_generic<GradT, AF8_MODE_NOCLIP>(L, C, st);
-    case AF8_MODE_SUMSQ:
-        return fast ? launch_stat<GradT>(L, st) : launch_generic<GradT, AF8_MODE_SUMSQ>(L, C, st);
-    case AF8_MODE_APPLY:
-        return fast ? launch_fast<GradT, AF8_MODE_APPLY>(L, st) : launch_generic<GradT, AF8_MODE_APPLY>(L, C, st);
-    default:
-        return launch_generic<GradT, AF8_MODE_SUMSQ_M>(L, C, st);
+    case AF8_MODE_NOCLIP: return launch_generic<GradT, AF8_MODE_NOCLIP>(L, C, st);
+    case AF8_MODE_SUMSQ: return launch_generic<GradT, AF8_MODE_SUMSQ>(L, C, st);
+    case AF8_MODE_APPLY: return launch_generic<GradT, AF8_MODE_APPLY>(L, C, st);
+    default: return launch_generic<GradT, AF8_MODE_SUMSQ_M>(L, C, st);
+    }
+}
+
+// the specialised kernels (AdamW UF8/AL8 layout): statistic pass, or the update pass for ParamT
+template <typename GradT, typename ParamT>
+inline int dispatch_fast(int mode, const FullrankLaunch &L, cudaStream_t st)
+{
+    switch (mode) {
+    case AF8_MODE_NOCLIP: return launch_fast<GradT, ParamT, AF8_MODE_NOCLIP>(L, st);
+    case AF8_MODE_SUMSQ: return launch_stat<GradT>(L, st);
+    default: return launch_fast<GradT, ParamT, AF8_MODE_APPLY>(L, st);
     }
 }
 
@@ -207,8 +215,9 @@ extern "C" int af8_fullrank_step(const af8_fullrank_cfg *cfg, const af8_fullrank
     if (!cfg || !dev_tensors) return fail(AF8_ERR_INVALID, "af8_fullrank_step: null cfg or table");
     if (n_tensors <= 0 || total_blocks <= 0) return fail(AF8_ERR_INVALID, "af8_fullrank_step: empty launch (n_tensors=%d, total_blocks=%lld)", n_tensors, (long long)total_blocks);
     const af8_fullrank_cfg &c = *cfg;
-    if (c.param_dtype != AF8_F32) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: only fp32 parameters are supported");
-    if (c.grad_dtype != AF8_F32 && c.grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: gradients must be fp32 or bf16");
+    if (c.param_dtype != AF8_F32 && c.param_dtype != AF8_BF16 && c.param_dtype != AF8_F16) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad param_dtype %d", c.param_dtype);
+    if (c.grad_dtype != AF8_F32 && c.grad_dtype != AF8_BF16 && c.grad_dtype != AF8_F16) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad grad_dtype %d", c.grad_dtype);
+    if (c.stochastic_round && c.param_dtype == AF8_F32) return fail(AF8_ERR_INVALID, "af8_fullrank_step: stochastic rounding applies to bf16 / fp16 parameters only");
     if (c.v_fmt != AF8_V_FP32 && c.v_fmt != AF8_V_AL8 && c.v_fmt != AF8_V_AL16 && c.v_fmt != AF8_V_NONE) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad v_fmt %d", c.v_fmt);
     if (c.m_fmt < AF8_M_NONE || c.m_fmt > AF8_M_FP32) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad m_fmt %d", c.m_fmt);
     if (c.block < 128 || c.block % 128 != 0) return fail(AF8_ERR_INVALID, "af8_fullrank_step: block must be a multiple of 128, >= 128 (got %d)", c.block);
@@ -237,13 +246,20 @@ extern "C" int af8_fullrank_step(const af8_fullrank_cfg *cfg, const af8_fullrank
     L.n_tensors = n_tensors;
     L.negate_grad = c.negate_grad ? 1 : 0;
     L.v_floor = c.v_floor;
+    L.param_dtype = c.param_dtype;
+    L.sr = c.stochastic_round ? 1 : 0;
     GenericCfg C{c.v_fmt, c.m_fmt, c.block, c.m_block, c.use_adam_denom ? 1 : 0, c.momentum_only ? 1 : 0};
 
     const bool fast = c.v_fmt == AF8_V_AL8 && c.m_fmt == AF8_M_UF8 && c.block == FAST_VBLOCK &&
                       c.m_block == FAST_MBLOCK && c.use_adam_denom && !c.momentum_only &&
                       c.mode != AF8_MODE_SUMSQ_M;
-    if (c.grad_dtype == AF8_BF16) return dispatch_mode<bf16_tag>(fast, c.mode, L, C, st);
-    return dispatch_mode<float>(fast, c.mode, L, C, st);
+    // specialised kernels: fp32 parameters with fp32 / bf16 gradients, bf16 parameters with bf16 gradients
+    if (fast && c.param_dtype == AF8_F32 && c.grad_dtype == AF8_BF16) return dispatch_fast<bf16_tag, float>(c.mode, L, st);
+    if (fast && c.param_dtype == AF8_F32 && c.grad_dtype == AF8_F32) return dispatch_fast<float, float>(c.mode, L, st);
+    if (fast && c.param_dtype == AF8_BF16 && c.grad_dtype == AF8_BF16) return dispatch_fast<bf16_tag, bf16_tag>(c.mode, L, st);
+    if (c.grad_dtype == AF8_BF16) return dispatch_generic<bf16_tag>(c.mode, L, C, st);
+    if (c.grad_dtype == AF8_F16) return dispatch_generic<f16_tag>(c.mode, L, C, st);
+    return dispatch_generic<float>(c.mode, L, C, st);
 }
 
 extern "C" int af8_fullrank_upload(const af8_fullrank_cfg *cfg, const af8_fullrank_tensor *host_tensors,

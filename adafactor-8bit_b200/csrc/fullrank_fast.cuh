@@ -1,6 +1,7 @@
 // Full-rank fused step, specialised kernel: AdamW-style update with UF8
 // momentum (M block 256) and AL8 second moment (V block 2048), fp32
-// parameters, fp32 or bf16 gradients.
+// parameters with fp32 or bf16 gradients, or bf16 parameters (rounded to
+// nearest or stochastically) with bf16 gradients.
 //
 // Reference semantics: _update_param_8bit full-rank branch with the Adam
 // denominator (optimizer.py:2115-2123), _fallback_1d_update
@@ -65,6 +66,8 @@ struct FullrankLaunch {
     int32_t n_tensors;
     int32_t negate_grad;
     float v_floor;
+    int32_t param_dtype;    // AF8_F32 / AF8_BF16 / AF8_F16
+    int32_t sr;             // stochastic rounding of 16-bit parameters
 };
 
 // Index of the tensor that owns flat block `blk` (first_block is ascending).
@@ -95,6 +98,13 @@ template <> struct GradLoad<float> {
 };
 
 struct bf16_tag {};
+struct f16_tag {};
+template <> struct GradLoad<f16_tag> {      // (general kernel only)
+    static __device__ __forceinline__ float load1(const void *base, int64_t off)
+    {
+        return f16_bits_to_f32(static_cast<const uint16_t *>(base)[off]);
+    }
+};
 template <> struct GradLoad<bf16_tag> {
     static __device__ __forceinline__ void load8(const void *base, int64_t off, float (&g)[8])
     {
@@ -159,6 +169,14 @@ struct __align__(16) VRange {
 // a 64-bit register; each component rounds exactly like the scalar *_rn operation.
 __device__ __forceinline__ float2 bc2(float x) { return make_float2(x, x); }
 __device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(bc2(-1.0f), b, a); }   // a - b, one rounding
+
+// two binary32 numbers rounded to nearest bf16, packed (first one in the low half)
+__device__ __forceinline__ uint32_t bf16x2_rn(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 
 template <bool SMALL_W>
 __device__ __forceinline__ float lerp_sel(float s, float e, float w, float wm1)
@@ -230,6 +248,7 @@ template <> struct GradBytes<bf16_tag> { static constexpr int value = 2; };
 struct StepScalars {
     float decay, v_w, v_wm1, m_w, m_wm1, eps_g, eps_d, step_mul, fira;
     bool zero_upd;
+    bool round_decay;   // bf16 parameter, nearest rounding: p*decay is rounded to bf16 before the update is added
 };
 
 template <int MODE, bool HAS_EPSG, bool TAIL>
@@ -270,6 +289,10 @@ __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], c
             if (!real1) u.y = 0.0f;
         }
         float2 pj = __fmul2_rn(make_float2(p[j], p[j + 1]), decay2);     // optimizer.py:2039
+        if (S.round_decay) {                                      // Tensor.mul_ on a bf16 tensor rounds to bf16
+            const uint32_t pk = bf16x2_rn(pj.x, pj.y);
+            pj = make_float2(__uint_as_float(pk << 16), __uint_as_float(pk & 0xffff0000u));
+        }
         if (MODE == AF8_MODE_APPLY) u = __fmul2_rn(u, fira2);             // optimizer.py:803
         if (!(MODE == AF8_MODE_APPLY && S.zero_upd))              // non-finite norm: zero update (optimizer.py:798-800)
             pj = __ffma2_rn(step2, u, pj);                        // optimizer.py:874
@@ -293,11 +316,12 @@ __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], c
 // Measured on B200 (TinyLlama set): depths 2 / 3 / 4 / 6 change the pass times by a few
 // per cent in the wrong direction (fewer resident CTAs), so the default stays at 2.
 // Ring geometry of one kernel variant: byte offsets inside a slot and the slot count.
-template <typename GradT, int MODE> struct FastRing {
+template <typename GradT, typename ParamT, int MODE> struct FastRing {
     static constexpr int GB = GradBytes<GradT>::value;
+    static constexpr int PB = GradBytes<ParamT>::value;     // bytes per parameter: 4 (float) or 2 (bf16_tag)
     static_assert(MODE == AF8_MODE_NOCLIP || MODE == AF8_MODE_APPLY, "the statistic pass has its own kernel (fullrank_stat.cuh)");
     static constexpr int P_OFF = 0;
-    static constexpr int G_OFF = FAST_VBLOCK * 4;
+    static constexpr int G_OFF = FAST_VBLOCK * PB;
     static constexpr int MQ_OFF = G_OFF + FAST_VBLOCK * GB;
     static constexpr int VQ_OFF = MQ_OFF + FAST_VBLOCK;
     static constexpr int STAGE_BYTES = VQ_OFF + FAST_VBLOCK;
@@ -306,12 +330,13 @@ template <typename GradT, int MODE> struct FastRing {
     static_assert(NST >= 2 && NST <= 8, "ring depth");
 };
 
-template <typename GradT, int MODE>
+template <typename GradT, typename ParamT, int MODE>
 __global__ void __launch_bounds__(FAST_THREADS, AF8_FAST_MIN_CTAS)
 fullrank_fast_kernel(const FullrankLaunch L)
 {
-    using Ring = FastRing<GradT, MODE>;
+    using Ring = FastRing<GradT, ParamT, MODE>;
     constexpr int GB = Ring::GB;
+    constexpr int PB = Ring::PB;
     constexpr int P_OFF = Ring::P_OFF, G_OFF = Ring::G_OFF, MQ_OFF = Ring::MQ_OFF, VQ_OFF = Ring::VQ_OFF;
     constexpr int STAGE_BYTES = Ring::STAGE_BYTES;
     constexpr int NST = Ring::NST;
@@ -398,7 +423,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 const int sl = (n + k) % NST;
                 unsigned char *dst = s_ring + sl * STAGE_BYTES;
                 mbar_expect_tx(&s_full[sl], STAGE_BYTES);
-                bulk_g2s(dst + P_OFF, pp + nb * 4, FAST_VBLOCK * 4, &s_full[sl]);
+                bulk_g2s(dst + P_OFF, pp + nb * PB, FAST_VBLOCK * PB, &s_full[sl]);
                 bulk_g2s(dst + G_OFF, gp + nb * GB, FAST_VBLOCK * GB, &s_full[sl]);
                 bulk_g2s(dst + MQ_OFF, sT.m_q + nb, FAST_VBLOCK, &s_full[sl]);
                 bulk_g2s(dst + VQ_OFF, vp + nb, FAST_VBLOCK, &s_full[sl]);
@@ -429,8 +454,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
         uint32_t mq[2], vq[2];
         int nva = 4, nvb = 4;
         bool bad = false;
-        float *pa = static_cast<float *>(sT.param) + base + oa;
-        float *pb = static_cast<float *>(sT.param) + base + ob;
+        unsigned char *pa = static_cast<unsigned char *>(sT.param) + (base + oa) * PB;
+        unsigned char *pb = static_cast<unsigned char *>(sT.param) + (base + ob) * PB;
         if (full) {
             if (!mbar_wait_bounded(&s_full[slot], (phase >> slot) & 1u)) {
                 bad = true;      // this thread stores nothing for the block
@@ -439,11 +464,18 @@ fullrank_fast_kernel(const FullrankLaunch L)
             }
             phase ^= 1u << slot;
             const unsigned char *st = s_ring + slot * STAGE_BYTES;
-            {
+            if (PB == 4) {
                 const float4 a = *reinterpret_cast<const float4 *>(st + P_OFF + oa * 4);
                 const float4 c = *reinterpret_cast<const float4 *>(st + P_OFF + ob * 4);
                 p[0] = a.x; p[1] = a.y; p[2] = a.z; p[3] = a.w;
                 p[4] = c.x; p[5] = c.y; p[6] = c.z; p[7] = c.w;
+            } else {
+                const uint2 a = *reinterpret_cast<const uint2 *>(st + P_OFF + oa * 2);
+                const uint2 c = *reinterpret_cast<const uint2 *>(st + P_OFF + ob * 2);
+                p[0] = __uint_as_float(a.x << 16); p[1] = __uint_as_float(a.x & 0xffff0000u);
+                p[2] = __uint_as_float(a.y << 16); p[3] = __uint_as_float(a.y & 0xffff0000u);
+                p[4] = __uint_as_float(c.x << 16); p[5] = __uint_as_float(c.x & 0xffff0000u);
+                p[6] = __uint_as_float(c.y << 16); p[7] = __uint_as_float(c.y & 0xffff0000u);
             }
             if (GB == 4) {
                 const float4 a = *reinterpret_cast<const float4 *>(st + G_OFF + oa * 4);
@@ -476,7 +508,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
             for (int j = 0; j < 8; ++j) {
                 const int e = (j < 4) ? oa + j : ob + j - 4;
                 const bool ok = (j < 4) ? (j < nva) : (j - 4 < nvb);
-                p[j] = ok ? static_cast<const float *>(sT.param)[base + e] : 0.0f;
+                p[j] = ok ? param_load(sT.param, base + e, PB == 4 ? AF8_F32 : AF8_BF16) : 0.0f;
                 g[j] = ok ? GradLoad<GradT>::load1(sT.grad, base + e) : 0.0f;
             }
         }
@@ -499,6 +531,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
         }
         S.v_wm1 = __fsub_rn(S.v_w, 1.0f); S.m_wm1 = __fsub_rn(S.m_w, 1.0f);
         S.fira = 1.0f; S.zero_upd = false;
+        S.round_decay = PB == 2 && !L.sr;
         if (MODE == AF8_MODE_APPLY) {
             const af8_dyn_scalars ds = L.dyn[cur_t];
             S.step_mul = ds.step; S.fira = ds.fira; S.zero_upd = ds.zero != 0.0f;
@@ -527,6 +560,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 float u = __fmul_rn(mj, rcp_approx(__fadd_rn(sqrt_approx(vj), S.eps_d)));
                 if (!real) u = 0.0f;
                 float pj = __fmul_rn(p[j], S.decay);
+                if (S.round_decay) pj = param_round(pj, AF8_BF16);
                 const float us = (MODE == AF8_MODE_APPLY) ? __fmul_rn(u, S.fira) : u;
                 if (!(MODE == AF8_MODE_APPLY && S.zero_upd)) pj = __fmaf_rn(S.step_mul, us, pj);
                 p[j] = pj;
@@ -594,14 +628,42 @@ fullrank_fast_kernel(const FullrankLaunch L)
 
         // ---- parameter store ----
         if (bad) {
-        } else if (full) {
-            *reinterpret_cast<float4 *>(pa) = make_float4(p[0], p[1], p[2], p[3]);
-            *reinterpret_cast<float4 *>(pb) = make_float4(p[4], p[5], p[6], p[7]);
-        } else {
+        } else if (PB == 4) {
+            if (full) {
+                *reinterpret_cast<float4 *>(pa) = make_float4(p[0], p[1], p[2], p[3]);
+                *reinterpret_cast<float4 *>(pb) = make_float4(p[4], p[5], p[6], p[7]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (j < nva) pa[j] = p[j];
-                if (j < nvb) pb[j] = p[j + 4];
+                for (int j = 0; j < 4; ++j) {
+                    if (j < nva) reinterpret_cast<float *>(pa)[j] = p[j];
+                    if (j < nvb) reinterpret_cast<float *>(pb)[j] = p[j + 4];
+                }
+            }
+        } else {
+            // bf16 parameters: the last rounding, to nearest or stochastic (optimizer.py:873-881)
+            uint32_t w[4];
+            if (L.sr) {
+                uint32_t h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    h[j] = sr_bf16_bits(p[j], sr_bits24(sT.sr_base, (uint64_t)(base + ((j < 4) ? oa + j : ob + j - 4))));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = h[2 * j] | (h[2 * j + 1] << 16);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = bf16x2_rn(p[2 * j], p[2 * j + 1]);
+            }
+            if (full) {
+                *reinterpret_cast<uint2 *>(pa) = make_uint2(w[0], w[1]);
+                *reinterpret_cast<uint2 *>(pb) = make_uint2(w[2], w[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t ha = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
+                    const uint32_t hb = (j & 1) ? (w[2 + (j >> 1)] >> 16) : (w[2 + (j >> 1)] & 0xffffu);
+                    if (j < nva) reinterpret_cast<uint16_t *>(pa)[j] = (uint16_t)ha;
+                    if (j < nvb) reinterpret_cast<uint16_t *>(pb)[j] = (uint16_t)hb;
+                }
             }
         }
 

@@ -139,7 +139,6 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
         }
 
         float acc = 0.0f, mn = INFINITY, mx = -INFINITY;
-        float *param = static_cast<float *>(sT.param) + base;
 
         for (int i = tid; i < C.block; i += GEN_THREADS) {
             const bool real = i < valid;
@@ -209,8 +208,10 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                 }
                 if (writes) {
                     if (MODE == AF8_MODE_APPLY) u = zero_upd ? 0.0f : __fmul_rn(u, fira);
-                    const float p1 = __fmul_rn(param[i], sT.decay);
-                    param[i] = __fmaf_rn(step_mul, u, p1);
+                    const float pv = param_load(sT.param, base + i, L.param_dtype);
+                    param_store_bits(sT.param, base + i,
+                                     param_step_bits(pv, sT.decay, step_mul, u, L.param_dtype, L.sr, sT.sr_base, base + i),
+                                     L.param_dtype);
                 }
             }
             if (writes) {

@@ -26,13 +26,13 @@
 namespace af8 {
 
 constexpr size_t NOALLOC_BYTES = 1u << 20;          // 1 MiB per GPU that loads the library
-constexpr size_t NOALLOC_TABLE_OFF = 0;             // one af8_fullrank_tensor (128 B)
-constexpr size_t NOALLOC_NORM_OFF = 128;            // one af8_norm_tensor (64 B)
-constexpr size_t NOALLOC_DYN_OFF = 192;             // one af8_dyn_scalars (32 B)
+constexpr size_t NOALLOC_TABLE_OFF = 0;             // one af8_fullrank_tensor (144 B)
+constexpr size_t NOALLOC_DYN_OFF = 160;             // one af8_dyn_scalars (32 B)
+constexpr size_t NOALLOC_NORM_OFF = 192;            // one af8_norm_tensor (64 B)
 constexpr size_t NOALLOC_SUMSQ_OFF = 256;           // float partial sums, one per V block
 constexpr int64_t NOALLOC_MAX_BLOCKS = (int64_t)((NOALLOC_BYTES - NOALLOC_SUMSQ_OFF) / sizeof(float));
 
-static_assert(sizeof(af8_fullrank_tensor) == 128, "table row layout");
+static_assert(sizeof(af8_fullrank_tensor) == 144, "table row layout");
 static_assert(sizeof(af8_norm_tensor) == 64, "norm row layout");
 static_assert(sizeof(af8_dyn_scalars) == 32, "dyn layout");
 
@@ -155,16 +155,22 @@ extern "C" int af8_fullrank_limited_step_noalloc(const af8_fullrank_cfg *cfg, co
     L.n_tensors = 1;
     L.negate_grad = c.negate_grad ? 1 : 0;
     L.v_floor = c.v_floor;
+    L.param_dtype = AF8_F32;
+    L.sr = 0;
     GenericCfg C{c.v_fmt, c.m_fmt, c.block, c.m_block, c.use_adam_denom ? 1 : 0, 0};
     const bool fast = c.v_fmt == AF8_V_AL8 && c.m_fmt == AF8_M_UF8 && c.block == FAST_VBLOCK &&
                       c.m_block == FAST_MBLOCK && c.use_adam_denom;
     const bool bf16 = c.grad_dtype == AF8_BF16;
 
-    rc = bf16 ? dispatch_mode<bf16_tag>(fast, AF8_MODE_SUMSQ, L, C, st) : dispatch_mode<float>(fast, AF8_MODE_SUMSQ, L, C, st);
+    auto pass = [&](int mode) {
+        if (fast) return bf16 ? dispatch_fast<bf16_tag, float>(mode, L, st) : dispatch_fast<float, float>(mode, L, st);
+        return bf16 ? dispatch_generic<bf16_tag>(mode, L, C, st) : dispatch_generic<float>(mode, L, C, st);
+    };
+    rc = pass(AF8_MODE_SUMSQ);
     if (rc) return rc;
     norm_finalize_kernel<<<1, 256, 0, st>>>(d_norm, d_sumsq, d_dyn);
     AF8_CUDA_TRY(cudaGetLastError());
-    rc = bf16 ? dispatch_mode<bf16_tag>(fast, AF8_MODE_APPLY, L, C, st) : dispatch_mode<float>(fast, AF8_MODE_APPLY, L, C, st);
+    rc = pass(AF8_MODE_APPLY);
     if (rc) return rc;
     if (norm_out)   // device-to-device: lets the caller read the measured norm later
         AF8_CUDA_TRY(cudaMemcpyAsync(norm_out, &d_dyn->norm, sizeof(float), cudaMemcpyDeviceToDevice, st));

@@ -38,20 +38,38 @@ param_sumsq_kernel(const ScaleLaunch L)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int64_t chunk = blockIdx.x; chunk < L.total_chunks; chunk += gridDim.x) {
         const int t = find_scale_tensor(L.tensors, L.n_tensors, chunk);
-        const float *p = L.tensors[t].param;
+        const void *p = L.tensors[t].param;
+        const int pdt = L.tensors[t].param_dtype;
         const int64_t base = (chunk - L.tensors[t].first_chunk) * SCALE_CHUNK;
         const int64_t rem = L.tensors[t].numel - base;
         float acc = 0.0f;
-        if (rem >= SCALE_CHUNK) {
-            const float4 *p4 = reinterpret_cast<const float4 *>(p + base);
+        if (rem >= SCALE_CHUNK && pdt == AF8_F32) {
+            const float4 *p4 = reinterpret_cast<const float4 *>(static_cast<const float *>(p) + base);
 #pragma unroll
             for (int k = 0; k < SCALE_CHUNK / 4 / 256; ++k) {
                 const float4 v = p4[tid + k * 256];
                 acc = __fmaf_rn(v.x, v.x, acc); acc = __fmaf_rn(v.y, v.y, acc);
                 acc = __fmaf_rn(v.z, v.z, acc); acc = __fmaf_rn(v.w, v.w, acc);
             }
+        } else if (rem >= SCALE_CHUNK) {
+            // bf16 / fp16 parameters enter the norm as binary32 (vector_norm(..., dtype=float32), optimizer.py:850-851)
+            const uint2 *p2 = reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(p) + base);
+#pragma unroll
+            for (int k = 0; k < SCALE_CHUNK / 4 / 256; ++k) {
+                const uint2 w = p2[tid + k * 256];
+                float v[4];
+                if (pdt == AF8_BF16) {
+                    v[0] = __uint_as_float(w.x << 16); v[1] = __uint_as_float(w.x & 0xffff0000u);
+                    v[2] = __uint_as_float(w.y << 16); v[3] = __uint_as_float(w.y & 0xffff0000u);
+                } else {
+                    v[0] = f16_bits_to_f32(w.x & 0xffffu); v[1] = f16_bits_to_f32(w.x >> 16);
+                    v[2] = f16_bits_to_f32(w.y & 0xffffu); v[3] = f16_bits_to_f32(w.y >> 16);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc = __fmaf_rn(v[j], v[j], acc);
+            }
         } else {
-            for (int i = tid; i < rem; i += 256) { const float v = p[base + i]; acc = __fmaf_rn(v, v, acc); }
+            for (int i = tid; i < rem; i += 256) { const float v = param_load(p, base + i, pdt); acc = __fmaf_rn(v, v, acc); }
         }
         acc = warp_sum(acc);
         __syncthreads();

@@ -132,12 +132,18 @@ typedef struct af8_fullrank_tensor {
     float eps_denom;        /* added to sqrt(v) in Adam mode */
     float eps_sq;           /* floor of v outside Adam mode */
     float reserved;
+    uint64_t sr_base;       /* stochastic rounding: seed * 0x9E3779B97F4A7C15 + step * 0xD1B54A32D192ED03
+                               (mod 2^64) with the parameter's state["sr_seed"] and step number
+                               (optimizer.py:1889-1892, 2040); element i draws from counter sr_base + i */
+    uint64_t reserved2;
 } af8_fullrank_tensor;
 
 /* Launch-wide configuration: everything that selects a kernel variant. */
 typedef struct af8_fullrank_cfg {
-    int32_t param_dtype;    /* AF8_F32 */
-    int32_t grad_dtype;     /* AF8_F32 or AF8_BF16 */
+    int32_t param_dtype;    /* AF8_F32, AF8_BF16 or AF8_F16.  A 16-bit parameter is rounded to nearest
+                               after the weight decay and again after the update, as the reference's
+                               in-place ops on such a tensor do, or once, stochastically (below) */
+    int32_t grad_dtype;     /* AF8_F32, AF8_BF16 or AF8_F16 */
     int32_t v_fmt;          /* AF8_V_* */
     int32_t m_fmt;          /* AF8_M_* */
     int32_t block;          /* V block size: multiple of 128, >= 128 */
@@ -147,7 +153,9 @@ typedef struct af8_fullrank_cfg {
     int32_t negate_grad;    /* maximize */
     int32_t mode;           /* AF8_MODE_* */
     float v_floor;          /* lower clamp of a block's min_log (-126 on this path) */
-    int32_t reserved;
+    int32_t stochastic_round; /* 16-bit parameters only: p*decay + step*u is formed in binary32 and rounded
+                               stochastically with the counter generator of af8_fullrank_tensor.sr_base
+                               (stochastic_round_writeback, optimizer.py:873-881; kernels.cu:48-161) */
 } af8_fullrank_cfg;
 
 /* One fused pass over every tensor of the table.
@@ -487,7 +495,7 @@ AF8_API int64_t af8_noalloc_max_numel(int32_t block);
 
 /* One tensor of af8_param_scale. */
 typedef struct af8_scale_tensor {
-    const float *param;
+    const void *param;          /* numel elements of param_dtype */
     int64_t numel;
     int64_t first_chunk;        /* running sum of ceil(numel / af8_scale_chunk()) */
     float sqrt_n;               /* float(sqrt(numel)) */
@@ -497,13 +505,13 @@ typedef struct af8_scale_tensor {
     float weight_decay;         /* 0 disables */
     int32_t bc_mode;            /* 0: none, 1: alpha *= bc, 2: alpha /= bc */
     int32_t scale_weight_decay; /* 1: decay uses alpha, 0: decay uses rho */
-    int32_t reserved;
+    int32_t param_dtype;        /* AF8_F32, AF8_BF16 or AF8_F16 */
 } af8_scale_tensor;
 
 /* alpha = max(||p|| / sqrt(n), eps2) * rho (then bias correction) and
  * decay = 1 - mult * weight_decay for every tensor, written into the float
  * fields at alpha_offset / decay_offset of row i of a device table whose rows
- * are table_stride bytes apart (for af8_fullrank_tensor: stride 128, offsets of
+ * are table_stride bytes apart (for af8_fullrank_tensor: its size, and the offsets of
  * `alpha` and `decay`).  chunk_sumsq is scratch: one float per chunk of
  * af8_scale_chunk() parameters, summed over the tensors.
  * Replaces the torch.linalg.vector_norm pass of _compute_alpha with
