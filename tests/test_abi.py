@@ -44,7 +44,7 @@ def test_version_and_error_string():
 
 def test_struct_sizes_match_header():
     from adafactor8bit import _native
-    assert _native.FULLRANK_TENSOR.itemsize == 128
+    assert _native.FULLRANK_TENSOR.itemsize == 144
     assert _native.DYN_SCALARS.itemsize == 32
     assert _native.NORM_TENSOR.itemsize == 64
     assert _native.SCALE_TENSOR.itemsize == 56
