@@ -349,13 +349,18 @@ class FactoredPlan:
     """One multi-tensor launch group of the factored path (2-D tensors with row /
     column second moments; optionally momentum; optionally CAME confidence)."""
 
-    def __init__(self, device, grad_dtype, m_fmt, m_block, came, negate, params, states, v_fmts, c_fmts):
+    def __init__(self, device, grad_dtype, m_fmt, m_block, came, negate, params, states, v_fmts, c_fmts,
+                 stochastic_round=False):
         self.device = torch.device(device)
         self.params, self.states = list(params), list(states)
         self.n = n = len(self.params)
         self.came = bool(came)
         self.cfg = N.FactoredCfg()
-        self.cfg.param_dtype = N.F32
+        pdt = self.params[0].dtype
+        if pdt not in _GRAD_DT or any(p.dtype != pdt for p in self.params):
+            raise RuntimeError("the factored kernels update fp32, bf16 or fp16 parameters, one dtype per launch group")
+        self.cfg.param_dtype = _GRAD_DT[pdt]
+        self.cfg.stochastic_round = int(bool(stochastic_round) and pdt != torch.float32)   # optimizer.py:2032
         self.cfg.grad_dtype = _GRAD_DT[grad_dtype]
         self.cfg.m_fmt = N.M_FMT[m_fmt]
         self.cfg.m_block = int(m_block) if m_block else 0
@@ -365,8 +370,8 @@ class FactoredPlan:
         if m_fmt in ("d8", "d4"):
             ensure_qmap(self.device)
         for p in self.params:
-            if p.dtype != torch.float32 or not p.is_contiguous() or p.dim() != 2:
-                raise RuntimeError("the factored kernels update contiguous 2-D fp32 parameters")
+            if not p.is_contiguous() or p.dim() != 2:
+                raise RuntimeError("the factored kernels update contiguous 2-D parameters")
         self.rows = np.array([p.shape[0] for p in self.params], dtype=np.int64)
         self.cols = np.array([p.shape[1] for p in self.params], dtype=np.int64)
         self.numel = self.rows * self.cols
@@ -510,6 +515,7 @@ class FactoredPlan:
         table["grad"] = [g.data_ptr() for g in grads]
         for k in ("decay", "alpha", "v_w", "m_w", "c_w", "eps1", "eps_came"):
             table[k] = scalars[k]
+        table["sr_base"] = scalars.get("sr_base", 0)
         lib = N.lib()
         N.check(lib.af8_factored_upload(ctypes.byref(self.cfg), buf.data_ptr(), self.d_table.data_ptr(), self.n,
                                         stream.cuda_stream), "af8_factored_upload")
@@ -549,6 +555,7 @@ class FactoredPlan:
         t["numel"] = self.numel
         t["first_chunk"] = np.concatenate([[0], np.cumsum(nchunks)[:-1]])
         t["sqrt_n"] = np.sqrt(self.numel.astype(np.float64)).astype(np.float32)
+        t["param_dtype"] = self.cfg.param_dtype
         for k in ("rho", "eps2", "bc", "weight_decay", "bc_mode", "scale_weight_decay"):
             t[k] = scale[k]
         self._log("param_scale", lambda: N.check(N.lib().af8_param_scale(

@@ -74,8 +74,9 @@ FACTORED_TENSOR = np.dtype([
     ("rows", np.int64), ("cols", np.int64), ("first_chunk", np.int64), ("first_tile", np.int64),
     ("decay", np.float32), ("alpha", np.float32), ("v_w", np.float32), ("m_w", np.float32),
     ("c_w", np.float32), ("eps1", np.float32), ("eps_came", np.float32), ("reserved", np.float32),
+    ("sr_base", np.uint64),
 ], align=True)
-assert FACTORED_TENSOR.itemsize == 312
+assert FACTORED_TENSOR.itemsize == 320
 
 SCALE_TENSOR = np.dtype([
     ("param", _P), ("numel", np.int64), ("first_chunk", np.int64),
@@ -102,7 +103,7 @@ class FactoredCfg(ctypes.Structure):
         ("param_dtype", ctypes.c_int32), ("grad_dtype", ctypes.c_int32), ("m_fmt", ctypes.c_int32),
         ("m_block", ctypes.c_int32), ("came", ctypes.c_int32), ("negate_grad", ctypes.c_int32),
         ("mode", ctypes.c_int32), ("v_floor", ctypes.c_float),
-        ("aligned8", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("aligned8", ctypes.c_int32), ("stochastic_round", ctypes.c_int32),
     ]
 
 

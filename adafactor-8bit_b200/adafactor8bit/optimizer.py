@@ -395,6 +395,8 @@ class Adafactor8Bit(Optimizer):
                 state = self.state[p]
                 if len(state) == 0 or "is_quantized" not in state:
                     state = self._create_state(p, p.grad, group)
+                if group.get("stochastic_round_writeback", False) and p.dtype in (torch.bfloat16, torch.float16):
+                    self._sr_seed(state)        # seeds follow the parameter order of the step (optimizer.py:1889-1892)
                 entries.append((p, p.grad, state))
             if entries:
                 self._run_group(gi, group, entries)
@@ -440,7 +442,7 @@ class Adafactor8Bit(Optimizer):
                 if g.dim() != 2:
                     raise NotImplementedError("factored tensors with more than two dimensions are not available in this build")
                 came = group.get("beta3") is not None and group.get("beta1") is not None
-                key = (p.device, g.dtype, m_fmt, m_block, came)
+                key = (p.device, g.dtype, m_fmt, m_block, came, p.dtype)
                 factored_items.setdefault(key, []).append((p, g, st))
                 continue
             v_fmt = st.get("v_quant_type", "al8") if quant else "fp32"
@@ -597,25 +599,30 @@ class Adafactor8Bit(Optimizer):
             scale["bc"][i], scale["bc_mode"][i] = sc["bc_div"], 2
 
     def _run_factored(self, gi, group, key, items):
-        device, gdtype, m_fmt, m_block, came = key
+        device, gdtype, m_fmt, m_block, came, pdtype = key
+        sr = bool(group.get("stochastic_round_writeback", False)) and pdtype in (torch.bfloat16, torch.float16)
         ids = tuple(id(p) for p, _, _ in items)
-        pkey = (gi, "factored", key, bool(group["maximize"]))
+        pkey = (gi, "factored", key, bool(group["maximize"]), sr)
         plan = self._plans.get(pkey)
         if plan is None or plan.ids != ids:
             v_fmts = [(st.get("v_quant_type", "al8") if st.get("is_quantized", False) else "fp32") for _, _, st in items]
             c_fmts = [(st.get("c_quant_type", st.get("v_quant_type", "al8")) if st.get("is_quantized", False) else "fp32")
                       for _, _, st in items]
             plan = FactoredPlan(device, gdtype, m_fmt, m_block, came, group["maximize"],
-                                [p for p, _, _ in items], [s for _, _, s in items], v_fmts, c_fmts)
+                                [p for p, _, _ in items], [s for _, _, s in items], v_fmts, c_fmts, stochastic_round=sr)
             plan.ids = ids
             self._plans[pkey] = plan
         n = len(items)
         scale = self._scale_inputs(group, n) if group["scale_parameter"] else None
         cols = {k: np.empty(n, dtype=f32) for k in ("decay", "alpha", "v_w", "m_w", "c_w", "eps1", "eps_came")}
+        if sr:
+            cols["sr_base"] = np.zeros(n, dtype=np.uint64)
         grads = []
         for i, (p, g, st) in enumerate(items):
             step = st["step"] + 1
             st["step"] = step
+            if sr:
+                cols["sr_base"][i] = sr_base(self._sr_seed(st), step)
             sc = self._step_scalars(group, step)
             alpha, decay = self._alpha_decay(group, sc)
             cols["decay"][i], cols["alpha"][i] = decay, alpha

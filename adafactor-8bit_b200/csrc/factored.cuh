@@ -42,6 +42,7 @@ struct FactoredLaunch {
     int32_t n_tensors;
     int32_t grad_dtype, m_fmt, m_block, came, negate_grad, mode;
     float v_floor;
+    int32_t param_dtype, sr;
 };
 
 __device__ __forceinline__ int find_factored_tile(const af8_factored_tensor *t, int n, int64_t id)
@@ -65,8 +66,9 @@ __device__ __forceinline__ int find_factored_chunk(const af8_factored_tensor *t,
 
 __device__ __forceinline__ float load_grad_any(const void *g, int dtype, int64_t i)
 {
-    return dtype == AF8_BF16 ? bf16_bits_to_f32(static_cast<const uint16_t *>(g)[i])
-                             : static_cast<const float *>(g)[i];
+    if (dtype == AF8_F32) return static_cast<const float *>(g)[i];
+    const uint32_t h = static_cast<const uint16_t *>(g)[i];
+    return dtype == AF8_BF16 ? bf16_bits_to_f32(h) : f16_bits_to_f32(h);
 }
 
 // momentum before the EMA (optimizer.py:694-697): dequantised codes or the fp32 state
@@ -323,7 +325,6 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
         int64_t row = (base + tid) / C;
         int64_t col = (base + tid) - row * C;
         double acc = 0.0;
-        float *param = static_cast<float *>(sT.param);
         for (int i = tid; i < chunk; i += FUPD_THREADS) {
             float mj = 0.0f;
             if (i < valid) {
@@ -350,9 +351,11 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
                     acc += (double)__fmul_rn(u, u);
                 } else {
                     if (!m_quant && has_m) sT.m_f32[flat] = mj;
-                    float pj = __fmul_rn(param[flat], sT.decay);                           // optimizer.py:2039
-                    if (!zero_upd) pj = __fmaf_rn(step_mul, __fmul_rn(u, fira), pj);       // optimizer.py:803, 874
-                    param[flat] = pj;
+                    // optimizer.py:2039, 803, 874 (a zero update still applies the decay and the rounding)
+                    const float uu = zero_upd ? 0.0f : __fmul_rn(u, fira);
+                    const float pv = param_load(sT.param, flat, L.param_dtype);
+                    param_store_bits(sT.param, flat, param_step_bits(pv, sT.decay, step_mul, uu, L.param_dtype, L.sr, sT.sr_base, flat),
+                                     L.param_dtype);
                 }
             }
             if (writes && m_quant) s_m[i] = mj;
@@ -683,10 +686,15 @@ factored_update_vec_kernel(const FactoredLaunch L)
         uint2 cm = make_uint2(0u, 0u);
         const bool pre_m = has_m && L.m_fmt == AF8_M_UF8 && L.mode != AF8_FUPD_SUMSQ_U;
         float *const pbase = static_cast<float *>(sT.param);
+        const bool lowp = L.param_dtype != AF8_F32;                  // 16-bit parameters: 8 of them in cp0
+        const uint16_t *const hbase = static_cast<const uint16_t *>(sT.param);
         if (have) { cg = ng; cp0 = np0; cp1 = np1; cm = nm; }
         else if (ok) {
             cg.load(sT.grad, flat);
-            if (writes) { cp0 = *reinterpret_cast<const float4 *>(pbase + flat); cp1 = *reinterpret_cast<const float4 *>(pbase + flat + 4); }
+            if (writes) {
+                if (lowp) cp0 = *reinterpret_cast<const float4 *>(hbase + flat);
+                else { cp0 = *reinterpret_cast<const float4 *>(pbase + flat); cp1 = *reinterpret_cast<const float4 *>(pbase + flat + 4); }
+            }
             if (pre_m) cm = *reinterpret_cast<const uint2 *>(sT.m_q + flat);
         } else cg.zero();
         {
@@ -694,7 +702,10 @@ factored_update_vec_kernel(const FactoredLaunch L)
             have = id + 1 < id_end && nf < numel;
             if (have) {
                 ng.load(sT.grad, nf);
-                if (writes) { np0 = *reinterpret_cast<const float4 *>(pbase + nf); np1 = *reinterpret_cast<const float4 *>(pbase + nf + 4); }
+                if (writes) {
+                    if (lowp) np0 = *reinterpret_cast<const float4 *>(hbase + nf);
+                    else { np0 = *reinterpret_cast<const float4 *>(pbase + nf); np1 = *reinterpret_cast<const float4 *>(pbase + nf + 4); }
+                }
                 if (pre_m) nm = *reinterpret_cast<const uint2 *>(sT.m_q + nf);
             }
         }
@@ -736,16 +747,32 @@ factored_update_vec_kernel(const FactoredLaunch L)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) part += (double)__fmul_rn(u[j], u[j]);
             } else {
-                float *pp = pbase + flat;
-                float p[8] = {cp0.x, cp0.y, cp0.z, cp0.w, cp1.x, cp1.y, cp1.z, cp1.w};
+                if (lowp) {
+                    // bf16 / fp16 parameters: rounded after the decay and after the update, or once,
+                    // stochastically (optimizer.py:873-881, 2033-2039)
+                    const uint32_t w[4] = {__float_as_uint(cp0.x), __float_as_uint(cp0.y), __float_as_uint(cp0.z), __float_as_uint(cp0.w)};
+                    uint32_t o[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float pj = __fmul_rn(p[j], sT.decay);
-                    if (!zero_upd) pj = __fmaf_rn(step_mul, __fmul_rn(u[j], fira), pj);
-                    p[j] = pj;
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t h = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
+                        const float pv = L.param_dtype == AF8_BF16 ? bf16_bits_to_f32(h) : f16_bits_to_f32(h);
+                        const float uu = zero_upd ? 0.0f : __fmul_rn(u[j], fira);
+                        const uint32_t r = param_step_bits(pv, sT.decay, step_mul, uu, L.param_dtype, L.sr, sT.sr_base, flat + j);
+                        if (j & 1) o[j >> 1] |= r << 16; else o[j >> 1] = r;
+                    }
+                    *reinterpret_cast<uint4 *>(const_cast<uint16_t *>(hbase) + flat) = make_uint4(o[0], o[1], o[2], o[3]);
+                } else {
+                    float *pp = pbase + flat;
+                    float p[8] = {cp0.x, cp0.y, cp0.z, cp0.w, cp1.x, cp1.y, cp1.z, cp1.w};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float pj = __fmul_rn(p[j], sT.decay);
+                        if (!zero_upd) pj = __fmaf_rn(step_mul, __fmul_rn(u[j], fira), pj);
+                        p[j] = pj;
+                    }
+                    *reinterpret_cast<float4 *>(pp) = make_float4(p[0], p[1], p[2], p[3]);
+                    *reinterpret_cast<float4 *>(pp + 4) = make_float4(p[4], p[5], p[6], p[7]);
                 }
-                *reinterpret_cast<float4 *>(pp) = make_float4(p[0], p[1], p[2], p[3]);
-                *reinterpret_cast<float4 *>(pp + 4) = make_float4(p[4], p[5], p[6], p[7]);
                 if (has_m && !m_quant) {
                     *reinterpret_cast<float4 *>(sT.m_f32 + flat) = make_float4(mj[0], mj[1], mj[2], mj[3]);
                     *reinterpret_cast<float4 *>(sT.m_f32 + flat + 4) = make_float4(mj[4], mj[5], mj[6], mj[7]);
@@ -862,8 +889,9 @@ inline int validate_factored(const af8_factored_cfg &c, const af8_factored_tenso
 inline int check_factored_cfg(const af8_factored_cfg *cfg, const char *who)
 {
     if (!cfg) return fail(AF8_ERR_INVALID, "%s: null cfg", who);
-    if (cfg->param_dtype != AF8_F32) return fail(AF8_ERR_UNSUPPORTED, "%s: only fp32 parameters are supported", who);
-    if (cfg->grad_dtype != AF8_F32 && cfg->grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "%s: gradients must be fp32 or bf16", who);
+    if (cfg->param_dtype != AF8_F32 && cfg->param_dtype != AF8_BF16 && cfg->param_dtype != AF8_F16) return fail(AF8_ERR_INVALID, "%s: bad param_dtype %d", who, cfg->param_dtype);
+    if (cfg->grad_dtype != AF8_F32 && cfg->grad_dtype != AF8_BF16 && cfg->grad_dtype != AF8_F16) return fail(AF8_ERR_INVALID, "%s: bad grad_dtype %d", who, cfg->grad_dtype);
+    if (cfg->stochastic_round && cfg->param_dtype == AF8_F32) return fail(AF8_ERR_INVALID, "%s: stochastic rounding applies to bf16 / fp16 parameters only", who);
     if (cfg->m_fmt < AF8_M_NONE || cfg->m_fmt > AF8_M_FP32) return fail(AF8_ERR_INVALID, "%s: bad m_fmt %d", who, cfg->m_fmt);
     const bool m_quant = cfg->m_fmt != AF8_M_NONE && cfg->m_fmt != AF8_M_FP32;
     if (m_quant && (cfg->m_block < 32 || cfg->m_block % 4 != 0 || cfg->m_block > 2048)) return fail(AF8_ERR_INVALID, "%s: bad m_block %d", who, cfg->m_block);
@@ -878,6 +906,7 @@ inline FactoredLaunch make_factored_launch(const af8_factored_cfg &c, const af8_
     L.tensors = dev; L.dyn = dyn; L.block_sumsq = sumsq; L.total_units = units; L.n_tensors = n;
     L.grad_dtype = c.grad_dtype; L.m_fmt = c.m_fmt; L.m_block = c.m_block > 0 ? c.m_block : 256;
     L.came = c.came ? 1 : 0; L.negate_grad = c.negate_grad ? 1 : 0; L.mode = c.mode; L.v_floor = c.v_floor;
+    L.param_dtype = c.param_dtype; L.sr = c.stochastic_round ? 1 : 0;
     return L;
 }
 
@@ -932,10 +961,11 @@ extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factore
     int64_t grid = (int64_t)sm_count() * 6;
     if (grid > tiles) grid = tiles;
     const bool bf = cfg->grad_dtype == AF8_BF16, res = cfg->mode == AF8_FSTAT_RESIDUAL;
-    if (cfg->aligned8 && bf && res) factored_stats_vec_kernel<bf16_tag, true><<<(int)grid, 256, 0, st>>>(L);
-    else if (cfg->aligned8 && bf) factored_stats_vec_kernel<bf16_tag, false><<<(int)grid, 256, 0, st>>>(L);
-    else if (cfg->aligned8 && res) factored_stats_vec_kernel<float, true><<<(int)grid, 256, 0, st>>>(L);
-    else if (cfg->aligned8) factored_stats_vec_kernel<float, false><<<(int)grid, 256, 0, st>>>(L);
+    const bool vec = cfg->aligned8 && cfg->grad_dtype != AF8_F16;      // fp16 gradients take the general kernels
+    if (vec && bf && res) factored_stats_vec_kernel<bf16_tag, true><<<(int)grid, 256, 0, st>>>(L);
+    else if (vec && bf) factored_stats_vec_kernel<bf16_tag, false><<<(int)grid, 256, 0, st>>>(L);
+    else if (vec && res) factored_stats_vec_kernel<float, true><<<(int)grid, 256, 0, st>>>(L);
+    else if (vec) factored_stats_vec_kernel<float, false><<<(int)grid, 256, 0, st>>>(L);
     else factored_stats_kernel<<<(int)grid, 256, 0, st>>>(L);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
@@ -973,7 +1003,7 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     const size_t smem = sizeof(float) * (size_t)chunk;
     int64_t grid = (int64_t)sm_count() * 6;
     if (grid > total_chunks) grid = total_chunks;
-    const bool vec = cfg->aligned8 && chunk == 2048 && (!m_quant || cfg->m_block == 256);
+    const bool vec = cfg->aligned8 && chunk == 2048 && (!m_quant || cfg->m_block == 256) && cfg->grad_dtype != AF8_F16;
     const bool apply = cfg->mode == AF8_FUPD_APPLY;
     if (vec) {                                   // persistent: the CTAs that are resident together
         grid = (int64_t)sm_count() * (apply ? 3 : 4);

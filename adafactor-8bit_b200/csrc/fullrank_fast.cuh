@@ -239,6 +239,8 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+template <typename T> struct ParamElem { typedef float type; };
+template <> struct ParamElem<bf16_tag> { typedef uint16_t type; };
 template <typename T> struct GradBytes { static constexpr int value = 4; };
 template <> struct GradBytes<bf16_tag> { static constexpr int value = 2; };
 
@@ -337,6 +339,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
     using Ring = FastRing<GradT, ParamT, MODE>;
     constexpr int GB = Ring::GB;
     constexpr int PB = Ring::PB;
+    using PElem = typename ParamElem<ParamT>::type;
     constexpr int P_OFF = Ring::P_OFF, G_OFF = Ring::G_OFF, MQ_OFF = Ring::MQ_OFF, VQ_OFF = Ring::VQ_OFF;
     constexpr int STAGE_BYTES = Ring::STAGE_BYTES;
     constexpr int NST = Ring::NST;
@@ -454,8 +457,9 @@ fullrank_fast_kernel(const FullrankLaunch L)
         uint32_t mq[2], vq[2];
         int nva = 4, nvb = 4;
         bool bad = false;
-        unsigned char *pa = static_cast<unsigned char *>(sT.param) + (base + oa) * PB;
-        unsigned char *pb = static_cast<unsigned char *>(sT.param) + (base + ob) * PB;
+        // (typed pointers: with byte pointers and a scaled offset the update pass ran 2.5 % slower)
+        PElem *pa = static_cast<PElem *>(sT.param) + base + oa;
+        PElem *pb = static_cast<PElem *>(sT.param) + base + ob;
         if (full) {
             if (!mbar_wait_bounded(&s_full[slot], (phase >> slot) & 1u)) {
                 bad = true;      // this thread stores nothing for the block
@@ -628,16 +632,14 @@ fullrank_fast_kernel(const FullrankLaunch L)
 
         // ---- parameter store ----
         if (bad) {
+        } else if (PB == 4 && full) {
+            *reinterpret_cast<float4 *>(pa) = make_float4(p[0], p[1], p[2], p[3]);
+            *reinterpret_cast<float4 *>(pb) = make_float4(p[4], p[5], p[6], p[7]);
         } else if (PB == 4) {
-            if (full) {
-                *reinterpret_cast<float4 *>(pa) = make_float4(p[0], p[1], p[2], p[3]);
-                *reinterpret_cast<float4 *>(pb) = make_float4(p[4], p[5], p[6], p[7]);
-            } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (j < nva) reinterpret_cast<float *>(pa)[j] = p[j];
-                    if (j < nvb) reinterpret_cast<float *>(pb)[j] = p[j + 4];
-                }
+            for (int j = 0; j < 4; ++j) {
+                if (j < nva) pa[j] = p[j];
+                if (j < nvb) pb[j] = p[j + 4];
             }
         } else {
             // bf16 parameters: the last rounding, to nearest or stochastic (optimizer.py:873-881)
@@ -661,8 +663,8 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t ha = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
                     const uint32_t hb = (j & 1) ? (w[2 + (j >> 1)] >> 16) : (w[2 + (j >> 1)] & 0xffffu);
-                    if (j < nva) reinterpret_cast<uint16_t *>(pa)[j] = (uint16_t)ha;
-                    if (j < nvb) reinterpret_cast<uint16_t *>(pb)[j] = (uint16_t)hb;
+                    if (j < nva) pa[j] = (PElem)ha;
+                    if (j < nvb) pb[j] = (PElem)hb;
                 }
             }
         }

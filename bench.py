@@ -99,6 +99,16 @@ WORKLOADS = {
         shapes=lambda: llama_shapes(4, 2048, 5632, 256, 32000)[1:-2], grad="bf16", bytes_per_param=14,
         hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
                 m_quant_type="uf8", v_quant_type="al8", enable_fira_for_adafactor=True, fira_margin=0.01)),
+    # the headline optimizer on bf16 parameters (10 B/param), rounded to nearest or stochastically
+    "tinyllama_adamw_fira_bf16p": dict(
+        shapes=lambda: llama_shapes(22, 2048, 5632, 256, 32000), grad="bf16", param="bf16", bytes_per_param=10,
+        hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
+                m_quant_type="uf8", v_quant_type="al8", enable_fira_for_adafactor=True, fira_margin=0.01)),
+    "tinyllama_adamw_fira_bf16p_sr": dict(
+        shapes=lambda: llama_shapes(22, 2048, 5632, 256, 32000), grad="bf16", param="bf16", bytes_per_param=10,
+        hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
+                m_quant_type="uf8", v_quant_type="al8", enable_fira_for_adafactor=True, fira_margin=0.01,
+                stochastic_round_writeback=True)),
     # one 4096x4096 fp32 parameter with fp32 gradients
     "single_4096_adamw": dict(
         shapes=lambda: [("w", (4096, 4096))], grad="f32", bytes_per_param=16,
@@ -198,7 +208,7 @@ def cpu_reference_run(workload, steps, warmup, sample_limit=24_000_000):
     import af8_oracle as o
     import cases
     wl = WORKLOADS[workload]
-    hp = o.hyper(**wl["hp"])
+    hp = o.hyper(**wl["hp"], param_dtype=wl.get("param", "f32"))
     shapes = wl["shapes"]()
     # sample: one of each distinct shape, in order, until the limit is reached
     seen, sample, sample_names, total = set(), [], [], 0
@@ -219,13 +229,15 @@ def cpu_reference_run(workload, steps, warmup, sample_limit=24_000_000):
         sample_names.append(name)
         total += n
     spec = dict(dist="rowscale", std=1e-3, zero_frac=0.005, dtype="bf16" if wl["grad"] == "bf16" else "f32")
-    params = [cases.make_param(s, 100 + i) for i, s in enumerate(sample)]
+    params = [cases.make_param(s, 100 + i, dtype=wl.get("param", "f32")) for i, s in enumerate(sample)]
     targets = wl.get("apollo_targets")
     hps = [hp if (not targets or nm in targets) else dict(hp, apollo_rank=0) for nm in sample_names]
     states = [o.init_state(s, h) for s, h in zip(sample, hps)]
     for k, st in enumerate(states):
         if "apollo_seed" in st:
             st["apollo_seed"] = k + 1
+        if hp["stochastic_round_writeback"] and hp["param_dtype"] != "f32":
+            st["sr_seed"] = k + 1
     grads = [cases.make_grad(s, 200 + i, 1, spec) for i, s in enumerate(sample)]
 
     def one(p, g, st, h):
@@ -302,10 +314,11 @@ def run_gpu_arm(args):
     wl = WORKLOADS[args.workload]
     shapes = wl["shapes"]()
     gdtype = torch.bfloat16 if wl["grad"] == "bf16" else torch.float32
+    pdtype = torch.bfloat16 if wl.get("param") == "bf16" else torch.float32
     gen = torch.Generator(device=device).manual_seed(1234)
     named = []
     for name, shp in shapes:
-        p = torch.nn.Parameter(torch.randn(shp, generator=gen, device=device) * 0.02)
+        p = torch.nn.Parameter((torch.randn(shp, generator=gen, device=device) * 0.02).to(pdtype))
         p.grad_dtype = None
         named.append((name, p))
     params = [p for _, p in named]
@@ -391,12 +404,13 @@ def run_gpu_arm(args):
         dom = max(per_kernel, key=lambda k: per_kernel[k][0])
         tot_ms, launches, units = per_kernel[dom]
         gb = {"bf16": 2, "f32": 4}[wl["grad"]]
+        pb2 = 2 * {"bf16": 2, "f32": 4}[wl.get("param", "f32")]     # parameter read + write
         if dom.startswith("fullrank") and dom.endswith(("apply", "noclip")):
-            bpp = gb + 8 + 4                      # grad + param r/w + M and V codes r/w
+            bpp = gb + pb2 + 4                    # grad + param r/w + M and V codes r/w
         elif dom.startswith("fullrank"):
             bpp = gb + 2                          # statistic pass (fullrank_stat, *_sumsq): grad + both codes
         elif dom == "factored_apply":
-            bpp = gb + 8 + (2 if inner.param_groups[0].get("beta1") is not None else 0)
+            bpp = gb + pb2 + (2 if inner.param_groups[0].get("beta1") is not None else 0)
         elif dom.startswith("factored"):
             bpp = gb                              # statistic passes read the gradient
         elif dom == "apollo_project":
@@ -407,7 +421,7 @@ def run_gpu_arm(args):
         # DRAM bytes per parameter (read + write) from the profiler capture of this kernel on the
         # four-layer case (profiles/); every block is independent, so traffic scales with the
         # parameter count
-        measured_bpp = NCU_TRAFFIC_BPP.get((dom, wl["grad"]))
+        measured_bpp = NCU_TRAFFIC_BPP.get((dom, wl["grad"])) if wl.get("param", "f32") == "f32" else None
         traffic = None if measured_bpp is None else measured_bpp * units / launches
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "traffic": traffic, "traffic_unit": "bytes per launch (ncu small case, scaled by parameters)",
@@ -458,7 +472,7 @@ def run_gpu_arm(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "params": n_params, "tensors": len(params),
-                       "grad_dtype": wl["grad"], "param_dtype": "f32",
+                       "grad_dtype": wl["grad"], "param_dtype": wl.get("param", "f32"),
                        "l2_policy": "inputs larger than L2 (whole parameter set streamed every step)",
                        "parallelism": f"zero1 x{world} (tensor-granular shards, in-place fp32 parameter all-gather pipelined in 4 units)"
                        if world > 1 else "single"},

@@ -241,7 +241,7 @@ typedef struct af8_small_state {
 
 /* One 2-D tensor (rows x cols, row-major) of a factored launch. */
 typedef struct af8_factored_tensor {
-    void *param;                /* fp32 */
+    void *param;                /* rows*cols elements of cfg.param_dtype */
     const void *grad;           /* fp32 or bf16 */
     uint8_t *m_q;               /* momentum codes over the flattened tensor, or NULL */
     float *m_scale;
@@ -265,6 +265,8 @@ typedef struct af8_factored_tensor {
     float eps1;
     float eps_came;
     float reserved;
+    uint64_t sr_base;           /* stochastic rounding counter origin, as af8_fullrank_tensor.sr_base;
+                                   element r*cols + c draws from counter sr_base + r*cols + c */
 } af8_factored_tensor;
 
 enum {
@@ -280,8 +282,8 @@ enum {
 };
 
 typedef struct af8_factored_cfg {
-    int32_t param_dtype;    /* AF8_F32 */
-    int32_t grad_dtype;     /* AF8_F32 or AF8_BF16 */
+    int32_t param_dtype;    /* AF8_F32, AF8_BF16 or AF8_F16 (rounding rules as in af8_fullrank_cfg) */
+    int32_t grad_dtype;     /* AF8_F32, AF8_BF16 or AF8_F16 */
     int32_t m_fmt;          /* AF8_M_*; AF8_M_NONE when beta1 is None */
     int32_t m_block;
     int32_t came;           /* 1: CAME (needs momentum) */
@@ -290,7 +292,7 @@ typedef struct af8_factored_cfg {
     float v_floor;          /* min_log floor of the AL requantisation (-126) */
     int32_t aligned8;       /* 1: every tensor has cols % 8 == 0 and 16-byte aligned arrays
                                (checked by af8_factored_upload); selects the 128-bit kernels */
-    int32_t reserved;
+    int32_t stochastic_round; /* as af8_fullrank_cfg.stochastic_round */
 } af8_factored_cfg;
 
 /* Number of flattened elements per work unit of af8_factored_update for a

@@ -109,3 +109,40 @@ def test_stochastic_rounding_is_unbiased_and_seeded():
     assert abs(dev.mean()) < 5.0 / np.sqrt(12.0 * n) + 1e-3
     nearest = exact.to(torch.bfloat16)
     assert (outs[0][0] != nearest).float().mean().item() > 0.1      # it is not round-to-nearest
+
+
+@pytest.mark.parametrize("name", cases.LOWP_FACTORED_CASES)
+def test_factored_low_precision_params(name, oracle):
+    """Factored Adafactor (bf16 parameters, parameter-scaled relative step) and CAME with stochastic
+    rounding, step by step from the oracle's state (AL16 small states move by a code when a mean
+    differs in its last bit, so the comparison restarts from identical state every step)."""
+    run = OracleRun(name)
+    fmt = run.case["param_dtype"]
+    params, opt = make(run)
+    dt = TORCH_DT[fmt]
+    for t in range(1, run.case["steps"] + 1):
+        for p, g in zip(params, run.grads[t]):
+            p.grad = cuda_grad(g, p.shape)
+        if t > 1:
+            for i, p in enumerate(params):
+                st = opt.state[p]
+                p.data.copy_(torch.from_numpy(run.params[i]).reshape(p.shape).to(dt))
+                for key, val in run.states[i].items():
+                    if isinstance(val, np.ndarray) and key in st and isinstance(st[key], torch.Tensor):
+                        src = torch.from_numpy(val.view(np.int16) if val.dtype == np.uint16 else val)
+                        st[key].copy_(src.reshape(st[key].shape))
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            got = p.detach().float().cpu().numpy()
+            parity.assert_lowp_params(got, run.params[i], fmt, f"{name} t{t} p{i} param", frac=2e-4)
+            check_codes(name, t, i, opt.state[p], run.states[i], al16_frac=3e-2)
+            if run.hp["stochastic_round_writeback"]:
+                assert opt.state[p]["sr_seed"] == i + 1
+    gold = load_golden(name)
+    steps = run.case["steps"]
+    for i, p in enumerate(params):
+        ref = golden_entries(gold, steps, i)
+        if "param" in ref:
+            parity.assert_lowp_params(p.detach().float().cpu().numpy(), ref["param"], fmt, f"{name} final p{i} vs reference", frac=1e-3)
