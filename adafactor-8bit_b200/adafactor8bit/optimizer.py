@@ -203,6 +203,7 @@ class Adafactor8Bit(Optimizer):
         super().__init__(params, defaults)
         self._apollo_seed_counter = 1          # optimizer.py:1460-1461
         self._sr_seed_counter = 1
+        self._sr_seed_map = None
         self._plans = {}
         self._after_group = None               # optional hook(gi, group), called when a group's launches are enqueued
 
@@ -396,7 +397,7 @@ class Adafactor8Bit(Optimizer):
                 if len(state) == 0 or "is_quantized" not in state:
                     state = self._create_state(p, p.grad, group)
                 if group.get("stochastic_round_writeback", False) and p.dtype in (torch.bfloat16, torch.float16):
-                    self._sr_seed(state)        # seeds follow the parameter order of the step (optimizer.py:1889-1892)
+                    self._sr_seed(state, p)     # seeds follow the parameter order of the step (optimizer.py:1889-1892)
                 entries.append((p, p.grad, state))
             if entries:
                 self._run_group(gi, group, entries)
@@ -404,12 +405,18 @@ class Adafactor8Bit(Optimizer):
                 self._after_group(gi, group)
         return loss
 
-    def _sr_seed(self, state):
+    def _sr_seed(self, state, p=None):
         """The parameter's stochastic-rounding seed, taken from the optimizer-level counter the
-        first time the parameter is rounded (optimizer.py:1889-1892)."""
+        first time the parameter is rounded (optimizer.py:1889-1892).  A wrapper that steps only a
+        subset of the parameters (the sharded optimizer) presets `_sr_seed_map` (id(param) -> seed)
+        so that the seeds are those of the unsharded run."""
         if "sr_seed" not in state:
-            state["sr_seed"] = self._sr_seed_counter
-            self._sr_seed_counter += 1
+            preset = self._sr_seed_map.get(id(p)) if (self._sr_seed_map is not None and p is not None) else None
+            if preset is not None:
+                state["sr_seed"] = preset
+            else:
+                state["sr_seed"] = self._sr_seed_counter
+                self._sr_seed_counter += 1
         return state["sr_seed"]
 
     def _run_group(self, gi, group, entries):

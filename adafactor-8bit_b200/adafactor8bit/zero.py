@@ -117,6 +117,18 @@ class ShardedAdafactor8Bit:
                     inner_groups.append(dict(g, params=mine))
                     self._last_group_of_part[k] = len(inner_groups) - 1
         self.inner = inner_factory(inner_groups, **kwargs) if inner_groups else None
+        if self.inner is not None and hasattr(self.inner, "_sr_seed_map"):
+            # stochastic-rounding seeds as the unsharded optimizer would hand them out: one per
+            # 16-bit parameter of a group that rounds stochastically, in parameter order
+            seeds, nxt = {}, 1
+            for g in groups:
+                sr = g.get("stochastic_round_writeback", kwargs.get("stochastic_round_writeback", False))
+                for p in g["params"]:
+                    if sr and p.dtype in (torch.bfloat16, torch.float16):
+                        seeds[id(p)] = nxt
+                        nxt += 1
+            self.inner._sr_seed_map = seeds
+            self.inner._sr_seed_counter = nxt
         self.gather_stream = None
 
     @property

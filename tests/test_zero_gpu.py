@@ -15,11 +15,15 @@ pytestmark = pytest.mark.gpu
 SHAPES = [(300, 200), (4096,), (2048,), (128, 256), (64, 2048)]
 
 
-def _inputs():
+def _inputs(variant="f32"):
+    """variant "f32": fp32 parameters; "bf16_sr": bf16 parameters written with stochastic rounding
+    (the seeds must be those of the unsharded run)."""
     sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
     import cases
     hp = dict(cases.CASES["adamw_fira_bf16"]["hp"])
-    p0 = [cases.make_param(s, 7000 + i) for i, s in enumerate(SHAPES)]
+    if variant == "bf16_sr":
+        hp["stochastic_round_writeback"] = True
+    p0 = [cases.make_param(s, 7000 + i, dtype="bf16" if variant == "bf16_sr" else "f32") for i, s in enumerate(SHAPES)]
     grads = {t: [cases.make_grad(s, 7100 + i, t, cases.CASES["adamw_fira_bf16"]["grad"]) for i, s in enumerate(SHAPES)]
              for t in (1, 2, 3)}
     return hp, p0, grads
@@ -29,7 +33,11 @@ def _bf16(g, shape, dev):
     return torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(shape).to(dev)
 
 
-def _worker(rank, world, port, out):
+def _pdt(variant):
+    return torch.bfloat16 if variant == "bf16_sr" else torch.float32
+
+
+def _worker(rank, world, port, out, variant):
     sys.path.insert(0, os.path.join(ROOT, "adafactor-8bit_b200"))
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -39,8 +47,8 @@ def _worker(rank, world, port, out):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         from adafactor8bit import ShardedAdafactor8Bit
-        hp, p0, grads = _inputs()
-        params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(dev)) for p in p0]
+        hp, p0, grads = _inputs(variant)
+        params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(dev).to(_pdt(variant))) for p in p0]
         for p in params:
             p.grad_dtype = None
         opt = ShardedAdafactor8Bit(params, **hp)
@@ -49,22 +57,23 @@ def _worker(rank, world, port, out):
                 p.grad = _bf16(g, p.shape, dev)
             opt.step()
         torch.cuda.synchronize()
-        out[rank] = [p.detach().cpu().numpy().copy() for p in params]
+        out[rank] = [p.detach().float().cpu().numpy().copy() for p in params]
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu():
+@pytest.mark.parametrize("variant", ["f32", "bf16_sr"])
+def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
     import torch.multiprocessing as mp
     sys.path.insert(0, os.path.join(ROOT, "adafactor-8bit_b200"))
     from adafactor8bit import Adafactor8Bit
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
-    hp, p0, grads = _inputs()
-    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).cuda()) for p in p0]
+    mp.spawn(_worker, args=(2, port, out, variant), nprocs=2, join=True)
+    hp, p0, grads = _inputs(variant)
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).cuda().to(_pdt(variant))) for p in p0]
     for p in params:
         p.grad_dtype = None
     opt = Adafactor8Bit(params, **hp)
@@ -75,4 +84,4 @@ def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu():
     torch.cuda.synchronize()
     for rank in (0, 1):
         for a, p in zip(out[rank], params):
-            assert np.array_equal(a, p.detach().cpu().numpy())
+            assert np.array_equal(a, p.detach().float().cpu().numpy())
