@@ -60,7 +60,46 @@ _QMAP_DEVICES = set()
 # start event, end event), recorded on the launch stream.  Used by bench.py to
 # time individual kernels inside its timed region; None disables it.
 LAUNCH_LOG = None
-_MODE_NAMES = {N.MODE_NOCLIP: "noclip", N.MODE_SUMSQ: "sumsq", N.MODE_APPLY: "apply", N.MODE_SUMSQ_M: "sumsq_m"}
+_MODE_NAMES = {N.MODE_NOCLIP: "noclip", N.MODE_SUMSQ: "sumsq", N.MODE_APPLY: "apply", N.MODE_SUMSQ_M: "sumsq_m",
+               N.MODE_LAG: "lag"}
+
+
+def lag_table(h_ring, d_table, states, device, first_block, n_blocks, numel, table_alpha, alpha_dev, d, fira,
+              fira_margin, partials_f64, stream):
+    """Fill and upload the af8_lag_tensor rows of a plan.  The three scalars are the reference's
+    state entries (optimizer.py:1056-1071); entries that do not exist yet are created here."""
+    n = len(states)
+    buf = h_ring.next()
+    lt = buf.numpy()[: n * N.LAG_TENSOR.itemsize].view(N.LAG_TENSOR)
+    lt[:] = np.zeros(n, dtype=N.LAG_TENSOR)
+    lt["first_block"], lt["n_blocks"] = first_block, n_blocks
+    lt["alpha"] = table_alpha
+    lt["alpha_dev"] = alpha_dev
+    sqrt_n = np.sqrt(numel.astype(np.float64))
+    lt["clip_div"] = (sqrt_n * d).astype(np.float32) if d > 0 else np.float32(0.0)
+    lt["fira_margin1"] = np.float32(1.0 + fira_margin)
+    lt["partials_f64"] = int(partials_f64)
+    for i, st in enumerate(states):
+        pun = st.get("prev_update_norm")
+        if pun is None:
+            pun = torch.zeros(1, dtype=torch.float32, device=device)
+            st["prev_update_norm"] = pun
+        lt["prev_update_norm"][i] = pun.data_ptr()
+        if fira:
+            fs = st.get("lag_fira_scale")
+            lt["has_lag_fira"][i] = int(fs is not None)
+            if fs is None:
+                fs = torch.ones((), dtype=torch.float32, device=device)
+                st["lag_fira_scale"] = fs
+            prev = st.get("fira_prev_norm")
+            lt["fira_has_prev"][i] = int(prev is not None)
+            if prev is None:
+                prev = torch.zeros((), dtype=torch.float32, device=device)
+                st["fira_prev_norm"] = prev
+            lt["lag_fira_scale"][i] = fs.data_ptr()
+            lt["fira_prev"][i] = prev.data_ptr()
+    d_table.copy_(buf[: d_table.numel()], non_blocking=True)
+    h_ring.mark(stream)
 
 
 def ensure_qmap(device):
@@ -151,6 +190,7 @@ class FullrankPlan:
         self.h_scale = None
         self.d_scale = None
         self.d_chunks = None
+        self.h_lag = self.d_lag = None
         self._static = None
         self._alpha_on_device = False
         for p in self.params:
@@ -289,11 +329,37 @@ class FullrankPlan:
         if LAUNCH_LOG is not None:
             pass
 
-    def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None):
+    def _alpha_dev_ptrs(self):
+        if not self._alpha_on_device:
+            return 0
+        return (self.d_table.data_ptr() + np.arange(self.n, dtype=np.uint64) * np.uint64(N.FULLRANK_TENSOR.itemsize)
+                + np.uint64(N.FULLRANK_TENSOR.fields["alpha"][1]))
+
+    def _run_lag(self, buf, table, d, fira, fira_margin, stream):
+        """lag_norm=True: one pass that clips and limits with the previous step's norm and leaves
+        this step's norm for the next one (optimizer.py:1056-1071)."""
+        if self.h_lag is None:
+            self.h_lag = _PinnedRing(self.n * N.LAG_TENSOR.itemsize)
+            self.d_lag = torch.empty(self.n * N.LAG_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+        lag_table(self.h_lag, self.d_lag, self.states, self.device, self.first_block, self.nblocks, self.numel,
+                  table["alpha"], self._alpha_dev_ptrs(), d, fira, fira_margin, False, stream)
+        lib = N.lib()
+        if buf is not None:
+            N.check(lib.af8_fullrank_upload(ctypes.byref(self.cfg), buf.data_ptr(), self.d_table.data_ptr(), self.n,
+                                            self.total_blocks, stream.cuda_stream), "af8_fullrank_upload")
+            self.h_table.mark(stream)
+        N.check(lib.af8_lag_scalars(self.d_lag.data_ptr(), self.n, 0, None, self.d_dyn.data_ptr(), stream.cuda_stream),
+                "af8_lag_scalars")
+        self._step(N.MODE_LAG, None, stream)
+        N.check(lib.af8_lag_scalars(self.d_lag.data_ptr(), self.n, 1, self.d_sumsq.data_ptr(), self.d_dyn.data_ptr(),
+                                    stream.cuda_stream), "af8_lag_scalars")
+
+    def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None, lag=False):
         """One optimizer step for every tensor of the plan
         (_dispatch_cuda_clip's pass structure, optimizer.py:1048-1077).
         scale: per-tensor inputs of af8_param_scale when alpha depends on the
-        parameter RMS; the table's alpha / decay are then produced on the device."""
+        parameter RMS; the table's alpha / decay are then produced on the device.
+        lag: lag_norm=True; the momentum-only rule keeps its exact passes."""
         stream = stream or torch.cuda.current_stream(self.device)
         buf, table = self.fill_table(grads, scalars)
         self._alpha_on_device = scale is not None
@@ -307,6 +373,9 @@ class FullrankPlan:
             return
         if self.d_sumsq is None:
             self.d_sumsq = torch.empty(self.total_blocks, dtype=torch.float32, device=self.device)
+        if lag and not mom_only:
+            self._run_lag(buf, table, d, fira, fira_margin, stream)
+            return
         if not mom_only:
             self._step(N.MODE_SUMSQ, buf, stream)
             self._finalize(table, 0, d, fira, fira_margin, stream)

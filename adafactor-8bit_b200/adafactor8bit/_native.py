@@ -17,7 +17,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA = 0, 1, 2, 3
 F32, BF16, F16 = 0, 1, 2
 V_FP32, V_AL8, V_AL16 = 0, 8, 16
 M_NONE, M_UF8, M_UF4, M_D8, M_D4, M_FP32 = 0, 1, 2, 3, 4, 5
-MODE_NOCLIP, MODE_SUMSQ, MODE_APPLY, MODE_SUMSQ_M = 0, 1, 2, 3
+MODE_NOCLIP, MODE_SUMSQ, MODE_APPLY, MODE_SUMSQ_M, MODE_LAG = 0, 1, 2, 3, 4
 
 V_NONE = 1
 V_FMT = {"fp32": V_FP32, "al8": V_AL8, "al16": V_AL16, "none": V_NONE}
@@ -49,6 +49,13 @@ NORM_TENSOR = np.dtype([
     ("fira_margin1", np.float32), ("partials_f64", np.int32), ("alpha_dev", _P),
 ], align=True)
 assert NORM_TENSOR.itemsize == 64
+
+LAG_TENSOR = np.dtype([
+    ("first_block", np.int64), ("n_blocks", np.int64), ("prev_update_norm", _P), ("lag_fira_scale", _P),
+    ("fira_prev", _P), ("alpha_dev", _P), ("alpha", np.float32), ("clip_div", np.float32), ("fira_margin1", np.float32),
+    ("has_lag_fira", np.int32), ("fira_has_prev", np.int32), ("partials_f64", np.int32), ("reserved", np.int32, (2,)),
+], align=True)      # af8_lag_tensor
+assert LAG_TENSOR.itemsize == 80
 
 APOLLO_PROJ_DESC = np.dtype([(n, np.uint64) for n in ("grad", "pt", "g_low", "chan_g2", "workspace")] +
                             [(n, np.int64) for n in ("workspace_bytes", "rows", "cols", "rank")] +
@@ -151,6 +158,7 @@ PROTOTYPES = {
     "af8_apollo_apply": (_c_i, [_c_p, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn),
                                 _c_f, _c_i, _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
+    "af8_lag_scalars": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p]),
     "af8_fullrank_limited_step_noalloc": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_f, _c_i, _c_f, _c_p, _c_i, _c_p, _c_p]),
     "af8_noalloc_max_numel": (_c_l, [_c_i]),
     "af8_param_scale": (_c_i, [_c_p, _c_p, _c_i, _c_p, _c_p, _c_l, _c_l, _c_l, _c_p]),
@@ -188,7 +196,8 @@ def lib():
         # the mirrors of this module against the structures the library was compiled with
         mirrors = [FULLRANK_TENSOR.itemsize, DYN_SCALARS.itemsize, ctypes.sizeof(FullrankCfg), NORM_TENSOR.itemsize,
                    SCALE_TENSOR.itemsize, SMALL_STATE.itemsize, FACTORED_TENSOR.itemsize, ctypes.sizeof(FactoredCfg),
-                   ctypes.sizeof(ApolloScalarsIn), 16, APOLLO_PROJ_DESC.itemsize, APOLLO_FINISH_TENSOR.itemsize]
+                   ctypes.sizeof(ApolloScalarsIn), 16, APOLLO_PROJ_DESC.itemsize, APOLLO_FINISH_TENSOR.itemsize,
+                   LAG_TENSOR.itemsize]
         for i, mine in enumerate(mirrors):
             theirs = handle.af8_struct_size(i)
             if theirs != mine:

@@ -83,6 +83,62 @@ norm_finalize_kernel(const af8_norm_tensor *tensors, const void *block_sumsq, af
     dyn[blockIdx.x] = out;
 }
 
+// One CTA per tensor: the scalars of the one-step-lag variant (af8_lag_scalars).
+__global__ void __launch_bounds__(256)
+lag_scalars_kernel(const af8_lag_tensor *tensors, int phase, const void *block_sumsq, af8_dyn_scalars *dyn)
+{
+    __shared__ double s_acc[256];
+    const af8_lag_tensor T = tensors[blockIdx.x];
+    const int tid = threadIdx.x;
+    if (phase == 0) {
+        if (tid != 0) return;
+        const float alpha = T.alpha_dev ? *T.alpha_dev : T.alpha;
+        const float fs = (T.lag_fira_scale != nullptr && T.has_lag_fira) ? *T.lag_fira_scale : 1.0f;
+        const float alpha_eff = __fmul_rn(alpha, fs);                                      // optimizer.py:1062
+        const float pn = *T.prev_update_norm;
+        const float denom = T.clip_div > 0.0f ? fmaxf(1.0f, __fdiv_rn(pn, T.clip_div)) : 1.0f;   // kernels.cu:652-653
+        af8_dyn_scalars out = dyn[blockIdx.x];
+        out.fira = 1.0f;
+        out.zero = 0.0f;
+        out.step = -__fdiv_rn(alpha_eff, denom);
+        out.pre_div = 1.0f;
+        dyn[blockIdx.x] = out;
+        return;
+    }
+    double acc = 0.0;
+    if (T.partials_f64) {
+        const double *ps = static_cast<const double *>(block_sumsq);
+        for (int64_t i = tid; i < T.n_blocks; i += 256) acc += ps[T.first_block + i];
+    } else {
+        const float *ps = static_cast<const float *>(block_sumsq);
+        for (int64_t i = tid; i < T.n_blocks; i += 256) acc += (double)ps[T.first_block + i];
+    }
+    s_acc[tid] = acc;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (tid < o) s_acc[tid] += s_acc[tid + o];
+        __syncthreads();
+    }
+    if (tid != 0) return;
+    const float raw = __double2float_rn(sqrt(s_acc[0]));
+    *T.prev_update_norm = raw;                                                              // optimizer.py:1066-1067
+    dyn[blockIdx.x].norm = raw;
+    if (T.lag_fira_scale == nullptr || T.fira_prev == nullptr) return;
+    const float norm = isfinite(raw) ? raw : 0.0f;                                           // optimizer.py:767-768
+    float fs = 1.0f;
+    if (T.fira_has_prev) {
+        const float fp = *T.fira_prev;
+        const bool reset = fp < 1e-6f;
+        const float ratio = __fdiv_rn(norm, __fadd_rn(fp, 1e-8f));
+        const float lim = __fdiv_rn(fmaxf(ratio, T.fira_margin1), T.fira_margin1);
+        fs = reset ? 1.0f : __frcp_rn(lim);
+        *T.fira_prev = reset ? norm : __fmul_rn(norm, fs);
+    } else {
+        *T.fira_prev = norm;
+    }
+    *T.lag_fira_scale = fs;                                                                 // optimizer.py:1069-1070
+}
+
 // ---------------------------------------------------------------------------
 // launch helpers
 // ---------------------------------------------------------------------------
@@ -155,6 +211,7 @@ inline int dispatch_generic(int mode, const FullrankLaunch &L, const GenericCfg 
     case AF8_MODE_NOCLIP: return launch_generic<GradT, AF8_MODE_NOCLIP>(L, C, st);
     case AF8_MODE_SUMSQ: return launch_generic<GradT, AF8_MODE_SUMSQ>(L, C, st);
     case AF8_MODE_APPLY: return launch_generic<GradT, AF8_MODE_APPLY>(L, C, st);
+    case AF8_MODE_LAG: return launch_generic<GradT, AF8_MODE_LAG>(L, C, st);
     default: return launch_generic<GradT, AF8_MODE_SUMSQ_M>(L, C, st);
     }
 }
@@ -166,6 +223,7 @@ inline int dispatch_fast(int mode, const FullrankLaunch &L, cudaStream_t st)
     switch (mode) {
     case AF8_MODE_NOCLIP: return launch_fast<GradT, ParamT, AF8_MODE_NOCLIP>(L, st);
     case AF8_MODE_SUMSQ: return launch_stat<GradT>(L, st);
+    case AF8_MODE_LAG: return launch_fast<GradT, ParamT, AF8_MODE_LAG>(L, st);
     default: return launch_fast<GradT, ParamT, AF8_MODE_APPLY>(L, st);
     }
 }
@@ -225,9 +283,10 @@ extern "C" int af8_fullrank_step(const af8_fullrank_cfg *cfg, const af8_fullrank
     const bool m_quant = c.m_fmt != AF8_M_NONE && c.m_fmt != AF8_M_FP32;
     if (m_quant && (c.m_block < 32 || c.m_block % 4 != 0 || c.block % c.m_block != 0))
         return fail(AF8_ERR_INVALID, "af8_fullrank_step: m_block must be a multiple of 4, >= 32 and divide block (got %d, block %d)", c.m_block, c.block);
-    if (c.mode < AF8_MODE_NOCLIP || c.mode > AF8_MODE_SUMSQ_M) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad mode %d", c.mode);
-    if ((c.mode == AF8_MODE_APPLY || c.mode == AF8_MODE_SUMSQ_M) && !dyn) return fail(AF8_ERR_INVALID, "af8_fullrank_step: this mode needs dyn");
-    if ((c.mode == AF8_MODE_SUMSQ || c.mode == AF8_MODE_SUMSQ_M) && !block_sumsq) return fail(AF8_ERR_INVALID, "af8_fullrank_step: this mode needs block_sumsq");
+    if (c.mode < AF8_MODE_NOCLIP || c.mode > AF8_MODE_LAG) return fail(AF8_ERR_INVALID, "af8_fullrank_step: bad mode %d", c.mode);
+    if ((c.mode == AF8_MODE_APPLY || c.mode == AF8_MODE_SUMSQ_M || c.mode == AF8_MODE_LAG) && !dyn) return fail(AF8_ERR_INVALID, "af8_fullrank_step: this mode needs dyn");
+    if ((c.mode == AF8_MODE_SUMSQ || c.mode == AF8_MODE_SUMSQ_M || c.mode == AF8_MODE_LAG) && !block_sumsq) return fail(AF8_ERR_INVALID, "af8_fullrank_step: this mode needs block_sumsq");
+    if (c.mode == AF8_MODE_LAG && c.momentum_only) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_step: the lag mode does not cover the momentum-only rule");
     if (c.mode == AF8_MODE_SUMSQ_M && !(c.momentum_only && c.m_fmt != AF8_M_NONE)) return fail(AF8_ERR_INVALID, "af8_fullrank_step: SUMSQ_M needs the momentum-only rule");
     if (c.momentum_only && c.use_adam_denom) return fail(AF8_ERR_INVALID, "af8_fullrank_step: momentum_only excludes the Adam denominator");
 
@@ -285,6 +344,19 @@ extern "C" int af8_device_status(int32_t *status_out, void *stream)
     AF8_CUDA_TRY(cudaMemcpyFromSymbolAsync(&v, g_device_error, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
     AF8_CUDA_TRY(cudaStreamSynchronize(st));
     *status_out = v;
+    return AF8_OK;
+}
+
+extern "C" int af8_lag_scalars(const af8_lag_tensor *tensors, int32_t n_tensors, int32_t phase, const void *block_sumsq,
+                               af8_dyn_scalars *dyn, void *stream)
+{
+    using namespace af8;
+    if (!tensors || !dyn) return fail(AF8_ERR_INVALID, "af8_lag_scalars: null argument");
+    if (n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_lag_scalars: n_tensors must be positive");
+    if (phase != 0 && phase != 1) return fail(AF8_ERR_INVALID, "af8_lag_scalars: phase must be 0 or 1");
+    if (phase == 1 && !block_sumsq) return fail(AF8_ERR_INVALID, "af8_lag_scalars: phase 1 needs block_sumsq");
+    lag_scalars_kernel<<<n_tensors, 256, 0, static_cast<cudaStream_t>(stream)>>>(tensors, phase, block_sumsq, dyn);
+    AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }
 

@@ -253,11 +253,15 @@ struct StepScalars {
     bool round_decay;   // bf16 parameter, nearest rounding: p*decay is rounded to bf16 before the update is added
 };
 
+// MODE: NOCLIP, APPLY (scalars of the statistic pass) or LAG (scalars of the previous step; the sum
+// of squares of this step's raw update is added to usq)
 template <int MODE, bool HAS_EPSG, bool TAIL>
 __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], const uint32_t (&mq)[2],
                                            const uint32_t (&vq)[2], const float *tab, float mc,
-                                           const StepScalars &S, int nva, int nvb, float (&v)[8], float (&m)[8])
+                                           const StepScalars &S, int nva, int nvb, float (&v)[8], float (&m)[8],
+                                           float &usq)
 {
+    constexpr bool DYN = MODE == AF8_MODE_APPLY || MODE == AF8_MODE_LAG;
     const float2 w_v = bc2(S.v_w), w_m = bc2(S.m_w), mc2 = bc2(mc), eps_d2 = bc2(S.eps_d);
     const float2 decay2 = bc2(S.decay), step2 = bc2(S.step_mul), fira2 = bc2(S.fira);
 #pragma unroll
@@ -295,8 +299,9 @@ __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], c
             const uint32_t pk = bf16x2_rn(pj.x, pj.y);
             pj = make_float2(__uint_as_float(pk << 16), __uint_as_float(pk & 0xffff0000u));
         }
-        if (MODE == AF8_MODE_APPLY) u = __fmul2_rn(u, fira2);             // optimizer.py:803
-        if (!(MODE == AF8_MODE_APPLY && S.zero_upd))              // non-finite norm: zero update (optimizer.py:798-800)
+        if (MODE == AF8_MODE_LAG) usq = __fmaf_rn(u.y, u.y, __fmaf_rn(u.x, u.x, usq));
+        if (DYN) u = __fmul2_rn(u, fira2);                        // optimizer.py:803
+        if (!(DYN && S.zero_upd))                                 // non-finite norm: zero update (optimizer.py:798-800)
             pj = __ffma2_rn(step2, u, pj);                        // optimizer.py:874
         p[j] = pj.x; p[j + 1] = pj.y;
     }
@@ -321,7 +326,7 @@ __device__ __forceinline__ void ema_update(const float (&g)[8], float (&p)[8], c
 template <typename GradT, typename ParamT, int MODE> struct FastRing {
     static constexpr int GB = GradBytes<GradT>::value;
     static constexpr int PB = GradBytes<ParamT>::value;     // bytes per parameter: 4 (float) or 2 (bf16_tag)
-    static_assert(MODE == AF8_MODE_NOCLIP || MODE == AF8_MODE_APPLY, "the statistic pass has its own kernel (fullrank_stat.cuh)");
+    static_assert(MODE == AF8_MODE_NOCLIP || MODE == AF8_MODE_APPLY || MODE == AF8_MODE_LAG, "the statistic pass has its own kernel (fullrank_stat.cuh)");
     static constexpr int P_OFF = 0;
     static constexpr int G_OFF = FAST_VBLOCK * PB;
     static constexpr int MQ_OFF = G_OFF + FAST_VBLOCK * GB;
@@ -350,6 +355,7 @@ fullrank_fast_kernel(const FullrankLaunch L)
     __shared__ float s_tab[2][256];
     __shared__ uint32_t s_redmin[FAST_WARPS];
     __shared__ uint32_t s_redmax[FAST_WARPS];
+    __shared__ float s_usq[FAST_WARPS];
     __shared__ VRange s_vr;
     __shared__ int s_abort;
     __shared__ double s_exp2[32];            // copy of the exp2 table of the decode
@@ -536,7 +542,9 @@ fullrank_fast_kernel(const FullrankLaunch L)
         S.v_wm1 = __fsub_rn(S.v_w, 1.0f); S.m_wm1 = __fsub_rn(S.m_w, 1.0f);
         S.fira = 1.0f; S.zero_upd = false;
         S.round_decay = PB == 2 && !L.sr;
-        if (MODE == AF8_MODE_APPLY) {
+        constexpr bool DYN = MODE == AF8_MODE_APPLY || MODE == AF8_MODE_LAG;
+        float usq = 0.0f;                    // LAG: this thread's sum of squares of the raw update
+        if (DYN) {
             const af8_dyn_scalars ds = L.dyn[cur_t];
             S.step_mul = ds.step; S.fira = ds.fira; S.zero_upd = ds.zero != 0.0f;
         }
@@ -546,10 +554,10 @@ fullrank_fast_kernel(const FullrankLaunch L)
         const bool small_w = fabsf(S.v_w) < 0.5f && fabsf(S.m_w) < 0.5f;   // ATen's lerp has two forms
         if (small_w) {
             if (full) {
-                if (S.eps_g == 0.0f) ema_update<MODE, false, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m);
-                else ema_update<MODE, true, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m);
+                if (S.eps_g == 0.0f) ema_update<MODE, false, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, usq);
+                else ema_update<MODE, true, false>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, usq);
             } else {
-                ema_update<MODE, true, true>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m);
+                ema_update<MODE, true, true>(g, p, mq, vq, s_tab[stage], mc, S, nva, nvb, v, m, usq);
             }
         } else {
 #pragma unroll
@@ -565,8 +573,9 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 if (!real) u = 0.0f;
                 float pj = __fmul_rn(p[j], S.decay);
                 if (S.round_decay) pj = param_round(pj, AF8_BF16);
-                const float us = (MODE == AF8_MODE_APPLY) ? __fmul_rn(u, S.fira) : u;
-                if (!(MODE == AF8_MODE_APPLY && S.zero_upd)) pj = __fmaf_rn(S.step_mul, us, pj);
+                if (MODE == AF8_MODE_LAG) usq = __fmaf_rn(u, u, usq);
+                const float us = DYN ? __fmul_rn(u, S.fira) : u;
+                if (!(DYN && S.zero_upd)) pj = __fmaf_rn(S.step_mul, us, pj);
                 p[j] = pj;
             }
         }
@@ -593,6 +602,10 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 umin -= 1u;
             }
             if (lane == 0) { s_redmin[warp] = umin; s_redmax[warp] = umax; }
+            if (MODE == AF8_MODE_LAG) {      // the block's sum of squares travels with the extrema
+                const float ws = warp_sum(usq);
+                if (lane == 0) s_usq[warp] = ws;
+            }
         }
         // ---- D: only warp 0 consumes the extrema; the other warps signal and move on ----
         if (warp == 0) asm volatile("bar.sync 1, %0;" ::"n"(FAST_THREADS) : "memory");
@@ -627,6 +640,12 @@ fullrank_fast_kernel(const FullrankLaunch L)
                 s_vr = r;
                 sT.v_scale[b] = r.scale;
                 sT.v_min_log[b] = r.min_log;
+                if (MODE == AF8_MODE_LAG) {
+                    float s = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < FAST_WARPS; ++w) s = __fadd_rn(s, s_usq[w]);
+                    L.block_sumsq[blk] = s;
+                }
             }
         }
 

@@ -100,7 +100,9 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
     const bool v_quant = C.v_fmt != AF8_V_FP32 && !no_v;
     const bool has_m = C.m_fmt != AF8_M_NONE;
     const bool m_quant = has_m && C.m_fmt != AF8_M_FP32;
-    const bool writes = (MODE == AF8_MODE_NOCLIP || MODE == AF8_MODE_APPLY);
+    const bool writes = (MODE == AF8_MODE_NOCLIP || MODE == AF8_MODE_APPLY || MODE == AF8_MODE_LAG);
+    constexpr bool DYN = MODE == AF8_MODE_APPLY || MODE == AF8_MODE_LAG;   // scalars of a statistic pass or of the previous step
+    constexpr bool SUMS = MODE == AF8_MODE_SUMSQ || MODE == AF8_MODE_LAG;  // partial sums of squares of the raw update
     const float qm1 = (C.v_fmt == AF8_V_AL16) ? 65534.0f : 254.0f;
     const int qmax = (C.v_fmt == AF8_V_AL16) ? 65535 : 255;
     int cur_t = -1;
@@ -132,10 +134,10 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
 
         float step_mul = -sT.alpha, fira = 1.0f, pre_div = 1.0f;
         bool zero_upd = false;
-        if (MODE == AF8_MODE_APPLY || MODE == 3) {
+        if (DYN || MODE == 3) {
             const af8_dyn_scalars ds = L.dyn[cur_t];
             pre_div = ds.pre_div;
-            if (MODE == AF8_MODE_APPLY) { step_mul = ds.step; fira = ds.fira; zero_upd = ds.zero != 0.0f; }
+            if (DYN) { step_mul = ds.step; fira = ds.fira; zero_upd = ds.zero != 0.0f; }
         }
 
         float acc = 0.0f, mn = INFINITY, mx = -INFINITY;
@@ -174,7 +176,7 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                 float u;
                 if (no_v && !has_m) {
                     u = gj;                     // optimizer.py:2065-2066
-                    if (MODE == AF8_MODE_SUMSQ) acc = __fmaf_rn(u, u, acc);
+                    if (SUMS) acc = __fmaf_rn(u, u, acc);
                 } else if (has_m) {
                     float m_old;
                     if (m_quant) {
@@ -186,10 +188,10 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                     if (no_v) {                 // optimizer.py:2047-2064: momentum / float(1 - beta1), kept in v_keep
                         mj = lerp_t(m_old, gj, sT.m_w);
                         u = __fdiv_rn(mj, sT.v_keep);
-                        if (MODE == AF8_MODE_SUMSQ) acc = __fmaf_rn(u, u, acc);
+                        if (SUMS) acc = __fmaf_rn(u, u, acc);
                     } else if (C.momentum_only) {      // optimizer.py:894-901
                         float ut = __fmul_rn(gj, inv);
-                        if (MODE == AF8_MODE_SUMSQ) {
+                        if (SUMS) {
                             acc = __fmaf_rn(ut, ut, acc);
                         }
                         ut = __fdiv_rn(ut, pre_div);
@@ -199,15 +201,15 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                     } else {                    // optimizer.py:903-910
                         mj = lerp_t(m_old, gj, sT.m_w);
                         u = __fmul_rn(mj, inv);
-                        if (MODE == AF8_MODE_SUMSQ) acc = __fmaf_rn(u, u, acc);
+                        if (SUMS) acc = __fmaf_rn(u, u, acc);
                     }
                     if (!m_quant && writes) sT.m_f32[base + i] = mj;
                 } else {                        // optimizer.py:911-917
                     u = C.use_adam_denom ? __fdiv_rn(gj, den) : __fmul_rn(gj, inv);
-                    if (MODE == AF8_MODE_SUMSQ) acc = __fmaf_rn(u, u, acc);
+                    if (SUMS) acc = __fmaf_rn(u, u, acc);
                 }
                 if (writes) {
-                    if (MODE == AF8_MODE_APPLY) u = zero_upd ? 0.0f : __fmul_rn(u, fira);
+                    if (DYN) u = zero_upd ? 0.0f : __fmul_rn(u, fira);
                     const float pv = param_load(sT.param, base + i, L.param_dtype);
                     param_store_bits(sT.param, base + i,
                                      param_step_bits(pv, sT.decay, step_mul, u, L.param_dtype, L.sr, sT.sr_base, base + i),
@@ -225,7 +227,7 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
             }
         }
 
-        if (!writes) {
+        if (!writes || MODE == AF8_MODE_LAG) {
             acc = warp_sum(acc);
             if (lane == 0) s_red[2][warp] = acc;
             __syncthreads();
@@ -234,7 +236,7 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                 for (int w = 0; w < GEN_THREADS / 32; ++w) s = __fadd_rn(s, s_red[2][w]);
                 L.block_sumsq[blk] = s;
             }
-            continue;
+            if (!writes) continue;
         }
 
         if (v_quant) {

