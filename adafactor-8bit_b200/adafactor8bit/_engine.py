@@ -467,6 +467,7 @@ class FactoredPlan:
         self.h_table = _PinnedRing(n * N.FACTORED_TENSOR.itemsize)
         self.h_norm = _PinnedRing(n * N.NORM_TENSOR.itemsize)
         self.h_scale = self.d_scale = self.d_chunks = None
+        self.h_lag = self.d_lag = None
         self.v_fmts, self.c_fmts = list(v_fmts), list(c_fmts)
         self._static = None
         self._alpha_on_device = False
@@ -531,7 +532,7 @@ class FactoredPlan:
     def _update(self, mode, use_dyn, stream):
         self.cfg.mode = mode
         lib = N.lib()
-        name = {N.FUPD_SUMSQ_U: "sumsq_u", N.FUPD_SUMSQ: "sumsq", N.FUPD_APPLY: "apply"}[mode]
+        name = {N.FUPD_SUMSQ_U: "sumsq_u", N.FUPD_SUMSQ: "sumsq", N.FUPD_APPLY: "apply", N.FUPD_LAG: "lag"}[mode]
         self._log(name, lambda: N.check(
             lib.af8_factored_update(ctypes.byref(self.cfg), self.d_table.data_ptr(), self.n, self.total_chunks,
                                     self.d_dyn.data_ptr() if use_dyn else None, self.d_sumsq.data_ptr(),
@@ -573,7 +574,7 @@ class FactoredPlan:
         N.check(N.lib().af8_norm_finalize(self.d_norm.data_ptr(), self.n, self.d_sumsq.data_ptr(),
                                           self.d_dyn.data_ptr(), stream.cuda_stream), "af8_norm_finalize")
 
-    def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None):
+    def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None, lag=False):
         """One optimizer step for every tensor of the plan (optimizer.py:2202-2552)."""
         stream = stream or torch.cuda.current_stream(self.device)
         if self._static is None:
@@ -604,6 +605,22 @@ class FactoredPlan:
                 self._update(N.FUPD_SUMSQ, True, stream)
                 self._finalize(table, 2, 0.0, True, fira_margin, stream)
             self._update(N.FUPD_APPLY, True, stream)
+        elif (fira or d > 0) and lag:
+            # lag_norm=True: one pass with the previous step's norm (optimizer.py:1056-1071)
+            if self.h_lag is None:
+                self.h_lag = _PinnedRing(self.n * N.LAG_TENSOR.itemsize)
+                self.d_lag = torch.empty(self.n * N.LAG_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+            alpha_dev = 0
+            if self._alpha_on_device:
+                alpha_dev = (self.d_table.data_ptr() + np.arange(self.n, dtype=np.uint64) * np.uint64(N.FACTORED_TENSOR.itemsize)
+                             + np.uint64(N.FACTORED_TENSOR.fields["alpha"][1]))
+            lag_table(self.h_lag, self.d_lag, self.states, self.device, self.first_chunk, self.nchunks, self.numel,
+                      table["alpha"], alpha_dev, d, fira, fira_margin, True, stream)
+            N.check(lib.af8_lag_scalars(self.d_lag.data_ptr(), self.n, 0, None, self.d_dyn.data_ptr(), stream.cuda_stream),
+                    "af8_lag_scalars")
+            self._update(N.FUPD_LAG, True, stream)
+            N.check(lib.af8_lag_scalars(self.d_lag.data_ptr(), self.n, 1, self.d_sumsq.data_ptr(), self.d_dyn.data_ptr(),
+                                        stream.cuda_stream), "af8_lag_scalars")
         elif fira or d > 0:
             self._update(N.FUPD_SUMSQ, False, stream)
             self._finalize(table, 0, d, fira, fira_margin, stream)

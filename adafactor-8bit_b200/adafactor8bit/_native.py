@@ -124,7 +124,7 @@ class ApolloScalarsIn(ctypes.Structure):
 
 
 FSTAT_GRADSQ, FSTAT_RESIDUAL = 0, 1
-FUPD_SUMSQ_U, FUPD_SUMSQ, FUPD_APPLY = 0, 1, 2
+FUPD_SUMSQ_U, FUPD_SUMSQ, FUPD_APPLY, FUPD_LAG = 0, 1, 2, 3
 
 _c_p = ctypes.c_void_p
 _c_i = ctypes.c_int32

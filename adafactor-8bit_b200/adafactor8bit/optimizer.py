@@ -643,7 +643,7 @@ class Adafactor8Bit(Optimizer):
             grads.append(g if g.is_contiguous() else g.contiguous())
         with torch.cuda.device(device):
             plan.run(grads, cols, d=float(group["d"]), fira=bool(group.get("enable_fira_for_adafactor", False)),
-                     fira_margin=float(group.get("fira_margin", 0.01)), scale=scale)
+                     fira_margin=float(group.get("fira_margin", 0.01)), scale=scale, lag=bool(group.get("lag_norm", False)))
 
     def _run_fullrank(self, gi, group, key, items):
         device, gdtype, v_fmt, m_fmt, block, m_block, pdtype = key

@@ -302,7 +302,8 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool has_m = L.m_fmt != AF8_M_NONE;
     const bool m_quant = has_m && L.m_fmt != AF8_M_FP32;
-    const bool writes = L.mode == AF8_FUPD_APPLY;
+    const bool writes = L.mode == AF8_FUPD_APPLY || L.mode == AF8_FUPD_LAG;
+    const bool sums = !writes || L.mode == AF8_FUPD_LAG;
 
     for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
         const int t = find_factored_chunk(L.tensors, L.n_tensors, id);
@@ -347,9 +348,8 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
                 } else {
                     u = __fmul_rn(__fmul_rn(g, ir), ic);                                   // optimizer.py:968-969
                 }
-                if (!writes) {
-                    acc += (double)__fmul_rn(u, u);
-                } else {
+                if (sums) acc += (double)__fmul_rn(u, u);
+                if (writes) {
                     if (!m_quant && has_m) sT.m_f32[flat] = mj;
                     // optimizer.py:2039, 803, 874 (a zero update still applies the decay and the rounding)
                     const float uu = zero_upd ? 0.0f : __fmul_rn(u, fira);
@@ -362,7 +362,7 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
             col += FUPD_THREADS;
             while (col >= C) { col -= C; ++row; }
         }
-        if (!writes) {
+        if (sums) {
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (lane == 0) s_acc[warp] = acc;
@@ -372,7 +372,7 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
                 for (int w = 0; w < FUPD_THREADS / 32; ++w) s += s_acc[w];
                 L.block_sumsq[id] = s;
             }
-            continue;
+            if (!writes) continue;
         }
         if (m_quant) {
             __syncthreads();
@@ -612,12 +612,14 @@ factored_stats_vec_kernel(const FactoredLaunch L)
 }
 
 // chunk = 2048 elements = 8 warps x 256; requires m_block == 256 when the momentum is quantised
-// WRITES: the APPLY pass; the two sum-of-squares passes keep fewer values live and run
-// with more resident CTAs
-template <typename GradT, bool WRITES>
-__global__ void __launch_bounds__(FUPD_THREADS, WRITES ? 3 : 4)
+// PASS 0: a sum-of-squares pass (fewer values live, more resident CTAs); 1: the APPLY pass;
+// 2: the LAG pass (APPLY plus the sums of this step's raw update)
+template <typename GradT, int PASS>
+__global__ void __launch_bounds__(FUPD_THREADS, PASS != 0 ? 3 : 4)
 factored_update_vec_kernel(const FactoredLaunch L)
 {
+    constexpr bool WRITES = PASS != 0;
+    constexpr bool SUMS = PASS != 1;
     __shared__ af8_factored_tensor sT;
     __shared__ double s_acc2[2][FUPD_THREADS / 32];
     int parity = 0;
@@ -743,10 +745,11 @@ factored_update_vec_kernel(const FactoredLaunch L)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) u[j] = __fmul_rn(__fmul_rn(g[j], ir), ic[j]);
             }
-            if (!writes) {
+            if (SUMS) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) part += (double)__fmul_rn(u[j], u[j]);
-            } else {
+            }
+            if (writes) {
                 if (lowp) {
                     // bf16 / fp16 parameters: rounded after the decay and after the update, or once,
                     // stochastically (optimizer.py:873-881, 2033-2039)
@@ -782,7 +785,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
 #pragma unroll
             for (int j = 0; j < 8; ++j) mj[j] = 0.0f;
         }
-        if (!writes) {
+        if (SUMS) {
             // One barrier per chunk: the warp partials alternate between two shared rows, and a
             // row is rewritten only two chunks later, after a barrier that warp 0 reaches once it
             // has read the row.
@@ -797,7 +800,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
                 L.block_sumsq[id] = s;
             }
             parity ^= 1;
-            continue;
+            if (!writes) continue;
         }
         if (m_quant) {
             // one warp = one momentum block of 256 (the block exists iff its first element does)
@@ -993,7 +996,8 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     int rc = check_factored_cfg(cfg, "af8_factored_update");
     if (rc) return rc;
     if (!dev_tensors || n_tensors <= 0 || total_chunks <= 0) return fail(AF8_ERR_INVALID, "af8_factored_update: null or empty table");
-    if (cfg->mode < AF8_FUPD_SUMSQ_U || cfg->mode > AF8_FUPD_APPLY) return fail(AF8_ERR_INVALID, "af8_factored_update: bad mode %d", cfg->mode);
+    if (cfg->mode < AF8_FUPD_SUMSQ_U || cfg->mode > AF8_FUPD_LAG) return fail(AF8_ERR_INVALID, "af8_factored_update: bad mode %d", cfg->mode);
+    if (cfg->mode == AF8_FUPD_LAG && (cfg->came || !dyn)) return fail(AF8_ERR_INVALID, "af8_factored_update: the lag pass needs dyn and excludes CAME");
     if (cfg->mode != AF8_FUPD_APPLY && !block_sumsq) return fail(AF8_ERR_INVALID, "af8_factored_update: this mode needs block_sumsq");
     if (cfg->mode == AF8_FUPD_SUMSQ_U && !cfg->came) return fail(AF8_ERR_INVALID, "af8_factored_update: SUMSQ_U is a CAME pass");
     if (cfg->came && cfg->mode != AF8_FUPD_SUMSQ_U && !dyn) return fail(AF8_ERR_INVALID, "af8_factored_update: CAME passes need dyn");
@@ -1004,17 +1008,20 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     int64_t grid = (int64_t)sm_count() * 6;
     if (grid > total_chunks) grid = total_chunks;
     const bool vec = cfg->aligned8 && chunk == 2048 && (!m_quant || cfg->m_block == 256) && cfg->grad_dtype != AF8_F16;
-    const bool apply = cfg->mode == AF8_FUPD_APPLY;
+    const bool apply = cfg->mode == AF8_FUPD_APPLY || cfg->mode == AF8_FUPD_LAG;
+    const bool lag = cfg->mode == AF8_FUPD_LAG;
     if (vec) {                                   // persistent: the CTAs that are resident together
         grid = (int64_t)sm_count() * (apply ? 3 : 4);
         if (grid > total_chunks) grid = total_chunks;
     }
     cudaStream_t cst = static_cast<cudaStream_t>(stream);
     const bool bf = cfg->grad_dtype == AF8_BF16;
-    if (vec && bf && apply) factored_update_vec_kernel<bf16_tag, true><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
-    else if (vec && bf) factored_update_vec_kernel<bf16_tag, false><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
-    else if (vec && apply) factored_update_vec_kernel<float, true><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
-    else if (vec) factored_update_vec_kernel<float, false><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    if (vec && bf && lag) factored_update_vec_kernel<bf16_tag, 2><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    else if (vec && lag) factored_update_vec_kernel<float, 2><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    else if (vec && bf && apply) factored_update_vec_kernel<bf16_tag, 1><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    else if (vec && bf) factored_update_vec_kernel<bf16_tag, 0><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    else if (vec && apply) factored_update_vec_kernel<float, 1><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    else if (vec) factored_update_vec_kernel<float, 0><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
     else factored_update_kernel<<<(int)grid, FUPD_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(L, chunk);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;

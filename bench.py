@@ -109,6 +109,11 @@ WORKLOADS = {
         hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
                 m_quant_type="uf8", v_quant_type="al8", enable_fira_for_adafactor=True, fira_margin=0.01,
                 stochastic_round_writeback=True)),
+    # the headline optimizer with lag_norm=True: the limiter uses the previous step's norm, one pass
+    "tinyllama_adamw_fira_lag": dict(
+        shapes=lambda: llama_shapes(22, 2048, 5632, 256, 32000), grad="bf16", bytes_per_param=14,
+        hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
+                m_quant_type="uf8", v_quant_type="al8", enable_fira_for_adafactor=True, fira_margin=0.01, lag_norm=True)),
     # one 4096x4096 fp32 parameter with fp32 gradients
     "single_4096_adamw": dict(
         shapes=lambda: [("w", (4096, 4096))], grad="f32", bytes_per_param=16,
@@ -405,7 +410,7 @@ def run_gpu_arm(args):
         tot_ms, launches, units = per_kernel[dom]
         gb = {"bf16": 2, "f32": 4}[wl["grad"]]
         pb2 = 2 * {"bf16": 2, "f32": 4}[wl.get("param", "f32")]     # parameter read + write
-        if dom.startswith("fullrank") and dom.endswith(("apply", "noclip")):
+        if dom.startswith("fullrank") and dom.endswith(("apply", "noclip", "lag")):
             bpp = gb + pb2 + 4                    # grad + param r/w + M and V codes r/w
         elif dom.startswith("fullrank"):
             bpp = gb + 2                          # statistic pass (fullrank_stat, *_sumsq): grad + both codes

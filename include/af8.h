@@ -311,7 +311,9 @@ enum {
     AF8_FUPD_SUMSQ_U = 0,     /* per-chunk sum of squares of U = g*inv_row*inv_col (CAME clip,
                                  optimizer.py:826-828) or of the final update (d-clip / Fira) */
     AF8_FUPD_SUMSQ = 1,       /* per-chunk sum of squares of the final update */
-    AF8_FUPD_APPLY = 2        /* write parameters (and momentum codes), scaled by af8_dyn_scalars */
+    AF8_FUPD_APPLY = 2,       /* write parameters (and momentum codes), scaled by af8_dyn_scalars */
+    AF8_FUPD_LAG = 3          /* APPLY with the scalars af8_lag_scalars(phase 0) prepared, plus this step's
+                                 partial sums of squares of the raw update (lag_norm=True; not with CAME) */
 };
 
 typedef struct af8_factored_cfg {

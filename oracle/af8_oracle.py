@@ -580,7 +580,8 @@ def factored_step(p, g, state, hp, sc=None):
     has_prev = c_i(1 if "fira_prev_norm" in state else 0)
     prev = c_f(float(state.get("fira_prev_norm", 0.0)))
     norm = c_f(-1.0)
-    with param_format(hp, state, sc["step"]):
+    lag = lag_mode(state, hp, bool(hp["lag_norm"]) and (cfg.fira or hp["d"] > 0) and not came)
+    with param_format(hp, state, sc["step"]), lag:
         rc = lib_.af8o_factored_step(
             ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), ctypes.byref(row), ctypes.byref(col),
             ctypes.byref(crow), ctypes.byref(ccol), _ptr(state.get("m_q")), _ptr(state.get("m_scale")),
@@ -588,7 +589,9 @@ def factored_step(p, g, state, hp, sc=None):
             ctypes.byref(norm))
     if rc != 0:
         raise RuntimeError(f"af8o_factored_step failed with {rc}")
-    if has_prev.value:
+    if lag.active:
+        lag.finish(norm.value, bool(cfg.fira))
+    elif has_prev.value:
         state["fira_prev_norm"] = f32(prev.value)
     return float(norm.value)
 

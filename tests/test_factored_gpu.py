@@ -54,6 +54,18 @@ EXTRA_CASES = {
 }
 
 
+# lag_norm=True (one pass with the previous step's norm; optimizer.py:1056-1071): the vector kernels, the
+# element-wise kernels (odd column counts) and the limiter on top of the clip
+EXTRA_CASES.update({
+    "adafactor_lag": dict(cases.CASES["adafactor_factored"], steps=5,
+                          hp=dict(cases.CASES["adafactor_factored"]["hp"], lag_norm=True)),
+    "adafactor_m_lag_fira": dict(shapes=[(200, 520), (37, 131)], steps=5, seed=38,
+                                 grad=dict(cases.CASES["adafactor_factored_m"]["grad"], spike_step=3, spike_mult=50.0),
+                                 hp=dict(cases.CASES["adafactor_factored_m"]["hp"], lag_norm=True,
+                                         enable_fira_for_adafactor=True)),
+})
+
+
 @pytest.mark.parametrize("name", FACTORED_CASES + sorted(EXTRA_CASES))
 def test_factored_free_running_matches_oracle(name, oracle):
     run = OracleRun(name, EXTRA_CASES.get(name))
@@ -67,6 +79,12 @@ def test_factored_free_running_matches_oracle(name, oracle):
         torch.cuda.synchronize()
         for i, p in enumerate(params):
             compare(name, t, i, opt.state[p], run.states[i], p, run.params[i], param_tol=2e-6)
+            for key in ("prev_update_norm", "lag_fira_scale"):
+                if key in run.states[i]:
+                    a, b = float(opt.state[p][key].item()), float(run.states[i][key])
+                    assert abs(a - b) <= 2e-6 * max(abs(b), 1.0), f"{name} t{t} p{i} {key}: {a} vs {b}"
+    if run.hp["lag_norm"]:
+        assert all("prev_update_norm" in opt.state[p] for p in params if p.dim() == 2)
     from adafactor8bit import _native
     assert _native.device_status(torch.cuda.current_stream().cuda_stream) == 0
 
