@@ -204,6 +204,7 @@ class Adafactor8Bit(Optimizer):
         self._apollo_seed_counter = 1          # optimizer.py:1460-1461
         self._sr_seed_counter = 1
         self._sr_seed_map = None
+        self._cfg_seen = {}       # id(param) -> option signature its state was last checked against
         self._plans = {}
         self._after_group = None               # optional hook(gi, group), called when a group's launches are enqueued
 
@@ -218,6 +219,8 @@ class Adafactor8Bit(Optimizer):
 
     def load_state_dict(self, state_dict):
         state_dict = dict(state_dict)
+        self._cfg_seen.clear()       # loaded states are checked against the group options at the next step
+        self._plans.clear()
         self._apollo_seed_counter = state_dict.pop("_apollo_seed_counter", self._apollo_seed_counter)
         self._sr_seed_counter = state_dict.pop("_sr_seed_counter", self._sr_seed_counter)
         # torch's loader casts floating-point state to the parameter's dtype and
@@ -318,6 +321,212 @@ class Adafactor8Bit(Optimizer):
         return state
 
     # ------------------------------------------------------------------
+    # state migration when a group option changed between steps (optimizer.py:1650-1860, 976-1045)
+    # ------------------------------------------------------------------
+    @staticmethod
+    def _config_signature(group, grad):
+        return (bool(group.get("quantize", True)), group.get("block_size", 2048), group.get("m_block_size", 256),
+                group.get("m_quant_type", "uf8"), group.get("v_quant_type", "al8"), group.get("c_quant_type"),
+                group.get("min_8bit_size", 4096), group.get("apollo_rank", 0), bool(group.get("apollo_factorize", False)),
+                bool(group.get("factored", True)), group.get("beta1") is None, group.get("beta2") is None,
+                group.get("beta2_decay") is None, group.get("beta3") is None, grad.dim())
+
+    @staticmethod
+    def _reset_keep_step(state):
+        """optimizer.py:380-386"""
+        step, seed = state.get("step", 0), state.get("sr_seed")
+        state.clear()
+        state["step"] = step
+        if seed is not None:
+            state["sr_seed"] = seed
+
+    @staticmethod
+    def _al_to_fp32(state, prefix):
+        """_deq_v(..., pop=True) (optimizer.py:358-365) through af8_al_dequant."""
+        q = state.pop(prefix + "_q")
+        scale, min_log = state.pop(prefix + "_scale"), state.pop(prefix + "_min_log")
+        shape, pad = state.pop(prefix + "_shape"), state.pop(prefix + "_pad")
+        numel = q.numel() - pad
+        out = torch.empty(numel, dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            N.check(N.lib().af8_al_dequant(q.data_ptr(), scale.data_ptr(), min_log.data_ptr(), numel, q.numel() // scale.numel(),
+                                           8 if q.dtype == torch.uint8 else 16, out.data_ptr(),
+                                           torch.cuda.current_stream(q.device).cuda_stream), "af8_al_dequant")
+        return out.view(list(shape))
+
+    @staticmethod
+    def _fp32_to_al(state, prefix, tensor, block, fmt):
+        """_quant_v (optimizer.py:373-377) through af8_al_quant."""
+        x = tensor.contiguous().float()
+        numel = x.numel()
+        pad = _pad_to(numel, block)
+        q = torch.empty(numel + pad, dtype=torch.uint8 if fmt == "al8" else torch.int16, device=x.device)
+        scale = torch.empty((numel + pad) // block, dtype=torch.float32, device=x.device)
+        min_log = torch.empty_like(scale)
+        with torch.cuda.device(x.device):
+            N.check(N.lib().af8_al_quant(x.data_ptr(), numel, block, 8 if fmt == "al8" else 16, -126.0, q.data_ptr(),
+                                         scale.data_ptr(), min_log.data_ptr(),
+                                         torch.cuda.current_stream(x.device).cuda_stream), "af8_al_quant")
+        state[prefix + "_q"], state[prefix + "_scale"], state[prefix + "_min_log"] = q, scale, min_log
+        state[prefix + "_shape"], state[prefix + "_pad"] = tensor.shape, pad
+
+    @staticmethod
+    def _m_to_fp32(state, p, m_block):
+        """_m_dequantize of the stored momentum (optimizer.py:1029-1039)."""
+        fmt = state.get("m_quant_type", "uf8")
+        if fmt in ("d8", "d4"):
+            from ._engine import ensure_qmap
+            ensure_qmap(p.device)
+        q, scale = state["m_q"], state["m_scale"]
+        out = torch.empty(p.numel(), dtype=torch.float32, device=p.device)
+        with torch.cuda.device(p.device):
+            N.check(N.lib().af8_m_dequant(q.data_ptr(), scale.data_ptr(), p.numel(), m_block, N.M_FMT[fmt], out.data_ptr(),
+                                          torch.cuda.current_stream(p.device).cuda_stream), "af8_m_dequant")
+        return out.view(p.shape)
+
+    @staticmethod
+    def _fp32_to_m(state, m, fmt, m_block):
+        """_m_quantize (optimizer.py:547-552) through af8_m_quant."""
+        if fmt in ("d8", "d4"):
+            from ._engine import ensure_qmap
+            ensure_qmap(m.device)
+        x = m.contiguous().float()
+        numel = x.numel()
+        padded = ((numel + m_block - 1) // m_block) * m_block
+        q = torch.empty(padded // 2 if fmt in ("uf4", "d4") else padded, dtype=torch.uint8, device=x.device)
+        scale = torch.empty(padded // m_block, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            N.check(N.lib().af8_m_quant(x.data_ptr(), numel, m_block, N.M_FMT[fmt], q.data_ptr(), scale.data_ptr(),
+                                        torch.cuda.current_stream(x.device).cuda_stream), "af8_m_quant")
+        state["m_q"], state["m_scale"] = q, scale
+
+    def _sync_state(self, p, grad, group, state):
+        """Bring an existing state in line with the group's current options, as _init_group does at
+        every step (optimizer.py:1650-1860): a changed momentum format resets the momentum, a changed
+        V / C format or block size and a changed mode (APOLLO, factored) re-initialise the state and
+        keep the step count, the quantize flag converts the states in place, CAME's confidence states
+        come and go with beta3.  Returns the state to step with."""
+        numel = p.numel()
+        use_quant = group.get("quantize", True) and not (numel < group.get("min_8bit_size", 4096))
+        block, m_block = group.get("block_size", 2048), group.get("m_block_size", 256)
+        mqt, vqt = group.get("m_quant_type", "uf8"), group.get("v_quant_type", "al8")
+        cqt = group.get("c_quant_type") or vqt
+        beta1, beta3 = group.get("beta1"), group.get("beta3")
+        sgd = group.get("beta2") is None and group.get("beta2_decay") is None
+        use_apollo = group.get("apollo_rank", 0) > 0 and grad.dim() >= 2
+        expect_factored = grad.dim() >= 2 and group.get("factored", True)
+        shape = tuple(p.shape)
+        needs_init = False
+
+        old_mqt = state.get("m_quant_type", "uf8")
+        if old_mqt not in _M_TYPES:
+            state["m_quant_type"] = old_mqt = "uf8"
+        old_mbs = state.get("m_block_size", m_block)
+        if not isinstance(old_mbs, int):
+            state["m_block_size"] = old_mbs = m_block
+        if (old_mqt != mqt or old_mbs != m_block) and use_quant:
+            logger.warning(f"Adafactor8Bit: M config changed (type: '{old_mqt}'->'{mqt}', block: {old_mbs}->{m_block}) "
+                           f"for param shape {p.shape}. Momentum history will be reset to zero.")
+            for k in ("m_q", "m_scale", "m_block_size", "m", "m_low_q", "m_low_scale", "m_low"):
+                state.pop(k, None)
+            state["m_quant_type"] = mqt
+        old_vqt = state.get("v_quant_type", "al8")
+        old_cqt = state.get("c_quant_type", old_vqt)
+        old_bs = state.get("block_size", block)
+        if (old_vqt != vqt or old_cqt != cqt or old_bs != block) and use_quant:
+            logger.warning(f"Adafactor8Bit: V/C/Block config changed (V: '{old_vqt}'->'{vqt}', C: '{old_cqt}'->'{cqt}', "
+                           f"BS: {old_bs}->{block}) for param shape {p.shape}. Re-initializing state.")
+            self._reset_keep_step(state)
+            needs_init = True
+        is_apollo_state = "apollo_seed" in state
+        if use_apollo != is_apollo_state:
+            logger.warning(f"Adafactor8Bit: Apollo/Adafactor mode changed for param shape {p.shape}. Re-initializing state.")
+            self._reset_keep_step(state)
+            needs_init = True
+        elif use_apollo:
+            came_toggled = (state.get("beta3") is None) != (beta3 is None)
+            if (state.get("apollo_rank") != group.get("apollo_rank", 0)
+                    or state.get("apollo_factorize", False) != group.get("apollo_factorize", False) or came_toggled):
+                logger.warning(f"Adafactor8Bit: Apollo/CAME config changed for param shape {p.shape}. Re-initializing state.")
+                self._reset_keep_step(state)
+                needs_init = True
+            else:
+                state["beta3"] = beta3
+        elif not sgd:
+            if ("row_var" in state or "row_var_q" in state) != expect_factored:
+                logger.warning(f"Adafactor8Bit: factored mode mismatch for param shape {p.shape}. Re-initializing state.")
+                self._reset_keep_step(state)
+                needs_init = True
+        if needs_init:
+            return self._create_state(p, grad, group)
+
+        cur_block = state.get("block_size", block)
+        cur_m_block = state.get("m_block_size", m_block) if beta1 is not None else 0
+        was_quant = state.get("is_quantized", False)
+        if use_apollo and use_quant != was_quant:
+            raise NotImplementedError("changing `quantize` on APOLLO states is not available in this build")
+        if use_quant and not was_quant:                      # optimizer.py:978-1019
+            if vqt != "fp32":
+                for k in ("row_var", "col_var", "variance"):
+                    if k in state and k + "_q" not in state:
+                        self._fp32_to_al(state, k, state.pop(k), cur_block, vqt)
+            if cqt != "fp32" and beta3 is not None:
+                for k in ("conf_row", "conf_col"):
+                    if k in state and k + "_q" not in state:
+                        self._fp32_to_al(state, k, state.pop(k), cur_block, cqt)
+            if beta1 is not None and "m_q" not in state and mqt != "fp32":
+                mb = state.get("m_block_size", cur_m_block)
+                if "m" in state:
+                    self._fp32_to_m(state, state.pop("m"), mqt, mb)
+                    state["m_quant_type"] = mqt
+                else:
+                    _new_m_state(state, numel, mb, mqt, p.device, p.shape)
+                state["m_block_size"] = mb
+            state["is_quantized"] = True
+        elif not use_quant and was_quant:                    # optimizer.py:1021-1045
+            for k in ("row_var", "col_var", "conf_row", "conf_col", "variance"):
+                if k + "_q" in state:
+                    state[k] = self._al_to_fp32(state, k)
+            if "m_q" in state:
+                state["m"] = self._m_to_fp32(state, p, state.get("m_block_size", cur_m_block))
+                for k in ("m_q", "m_scale", "m_block_size", "m_quant_type"):
+                    state.pop(k, None)
+            state["is_quantized"] = False
+
+        if not use_apollo:
+            if beta3 is None:                                # optimizer.py:1799-1806
+                for prefix in ("conf_row", "conf_col"):
+                    state.pop(prefix, None)
+                    for suffix in ("q", "scale", "min_log", "shape", "pad"):
+                        state.pop(f"{prefix}_{suffix}", None)
+            elif expect_factored:                            # optimizer.py:1808-1836
+                r_shape = list(shape[:-2]) + [shape[-2], 1]
+                c_shape = list(shape[:-2]) + [1, shape[-1]]
+                c_fmt = cqt if use_quant else "fp32"
+                if "conf_row" not in state and "conf_row_q" not in state:
+                    _new_al_state(state, "conf_row", r_shape, cur_block, p.device, c_fmt)
+                if "conf_col" not in state and "conf_col_q" not in state:
+                    _new_al_state(state, "conf_col", c_shape, cur_block, p.device, c_fmt)
+        if beta1 is not None and "m_q" not in state and not use_apollo:     # optimizer.py:1838-1849
+            mb = state.get("m_block_size", m_block)
+            if use_quant and mqt != "fp32":
+                if "m" in state:
+                    self._fp32_to_m(state, state.pop("m"), mqt, mb)
+                    state["m_quant_type"] = mqt
+                else:
+                    _new_m_state(state, numel, mb, mqt, p.device, p.shape)
+                state["m_block_size"] = mb
+            elif "m" not in state and mqt == "fp32":
+                state["m"] = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
+                state["m_quant_type"] = "fp32"
+        if "block_size" not in state:
+            state["block_size"] = block
+        if beta1 is None:
+            for k in ("m_q", "m_scale", "m_block_size", "m_quant_type", "m"):
+                state.pop(k, None)
+        return state
+
+    # ------------------------------------------------------------------
     # per-step host scalars (optimizer.py:1957-2040, 832-856)
     # ------------------------------------------------------------------
     @staticmethod
@@ -396,6 +605,13 @@ class Adafactor8Bit(Optimizer):
                 state = self.state[p]
                 if len(state) == 0 or "is_quantized" not in state:
                     state = self._create_state(p, p.grad, group)
+                    self._cfg_seen[id(p)] = self._config_signature(group, p.grad)
+                else:
+                    sig = self._config_signature(group, p.grad)
+                    if self._cfg_seen.get(id(p)) != sig:     # first step after a load, or an option was edited
+                        state = self._sync_state(p, p.grad, group, state)
+                        self._cfg_seen[id(p)] = sig
+                        self._plans.clear()                  # launch plans cache state pointers and formats
                 if group.get("stochastic_round_writeback", False) and p.dtype in (torch.bfloat16, torch.float16):
                     self._sr_seed(state, p)     # seeds follow the parameter order of the step (optimizer.py:1889-1892)
                 entries.append((p, p.grad, state))

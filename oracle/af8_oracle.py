@@ -452,7 +452,7 @@ def fullrank_step(p, g, state, hp, sc=None):
     if sgd:
         vqt = "none"
     has_m = hp["beta1"] is not None
-    mqt = (state.get("m_quant_type", "uf8") if has_m else None)
+    mqt = (("fp32" if "m" in state else state.get("m_quant_type", "uf8")) if has_m else None)
     cfg = FullrankCfg()
     cfg.numel = n
     cfg.block = state["block_size"]
@@ -549,7 +549,7 @@ def factored_step(p, g, state, hp, sc=None):
     vqt = state["v_quant_type"] if quant else "fp32"
     cqt = state["c_quant_type"] if quant else "fp32"
     has_m = hp["beta1"] is not None
-    mqt = state.get("m_quant_type", "uf8") if has_m else None
+    mqt = ("fp32" if "m" in state else state.get("m_quant_type", "uf8")) if has_m else None
     came = hp["beta3"] is not None and has_m
     cfg = FactoredCfg()
     cfg.rows, cfg.cols = R, C
@@ -727,3 +727,117 @@ def apollo_step(p, g, state, hp):
     if has_prev.value:
         state["scaled_grad_norm_prev"] = f32(prev.value)
     return float(norm.value)
+
+
+# ---------------------------------------------------------------------------
+# state migration when a group option changes between steps
+# ---------------------------------------------------------------------------
+def _al_keys(prefix):
+    return [prefix + s for s in ("_q", "_scale", "_min_log", "_pad")]
+
+
+def _to_al(state, prefix, x, block, fmt):
+    """_quant_v (optimizer.py:373-377)."""
+    q, s, ml, pad = al_quantize(np.ascontiguousarray(x, dtype=f32).reshape(-1), block, bits=8 if fmt == "al8" else 16)
+    state[prefix + "_q"], state[prefix + "_scale"], state[prefix + "_min_log"], state[prefix + "_pad"] = q, s, ml, pad
+
+
+def _from_al(state, prefix):
+    """_deq_v(..., pop=True) (optimizer.py:358-365)."""
+    q = state.pop(prefix + "_q")
+    s, ml, pad = state.pop(prefix + "_scale"), state.pop(prefix + "_min_log"), state.pop(prefix + "_pad")
+    return al_dequantize(q, s, ml, q.size - pad, bits=8 if q.dtype == np.uint8 else 16)
+
+
+def migrate_state(state, hp, shape):
+    """What _init_group does to an existing state at the start of a step (optimizer.py:1650-1860,
+    976-1045) for the full-rank and factored paths: momentum reset on a momentum-format change,
+    re-initialisation (step kept) on a V / C / block change or a factored-mode change, in-place
+    conversion on a `quantize` change, CAME's confidence states dropped or created with beta3.
+    Returns the state to use (a new dict after a re-initialisation)."""
+    shape = tuple(shape)
+    numel = int(np.prod(shape)) if shape else 1
+    use_quant = hp["quantize"] and not (numel < hp["min_8bit_size"])
+    block, m_block = hp["block_size"], hp["m_block_size"]
+    mqt, vqt = hp["m_quant_type"], hp["v_quant_type"]
+    cqt = hp["c_quant_type"] or vqt
+    beta1, beta3 = hp["beta1"], hp["beta3"]
+    expect_factored = len(shape) >= 2 and hp["factored"]
+
+    def reinit():
+        new = init_state(shape, hp)
+        new["step"] = state.get("step", 0)
+        if "sr_seed" in state:
+            new["sr_seed"] = state["sr_seed"]
+        return new
+
+    old_mqt = state.get("m_quant_type", "uf8")
+    old_mbs = state.get("m_block_size", m_block)
+    if (old_mqt != mqt or old_mbs != m_block) and use_quant:
+        for k in ("m_q", "m_scale", "m_block_size", "m"):
+            state.pop(k, None)
+        state["m_quant_type"] = mqt
+    old_vqt = state.get("v_quant_type", "al8")
+    old_cqt = state.get("c_quant_type", old_vqt)
+    if (old_vqt != vqt or old_cqt != cqt or state.get("block_size", block) != block) and use_quant:
+        return reinit()
+    if not is_sgd(hp) and (("row_var" in state or "row_var_q" in state) != expect_factored):
+        return reinit()
+
+    cur_block = state.get("block_size", block)
+    was_quant = state.get("is_quantized", False)
+    if use_quant and not was_quant:
+        if vqt != "fp32":
+            for k in ("row_var", "col_var", "variance"):
+                if k in state and k + "_q" not in state:
+                    _to_al(state, k, state.pop(k), cur_block, vqt)
+        if cqt != "fp32" and beta3 is not None:
+            for k in ("conf_row", "conf_col"):
+                if k in state and k + "_q" not in state:
+                    _to_al(state, k, state.pop(k), cur_block, cqt)
+        if beta1 is not None and "m_q" not in state and mqt != "fp32":
+            mb = state.get("m_block_size", m_block)
+            if "m" in state:
+                state["m_q"], state["m_scale"] = m_quantize(state.pop("m"), mb, mqt)
+                state["m_quant_type"] = mqt
+            else:
+                _init_m(state, numel, mb, mqt)
+            state["m_block_size"] = mb
+        state["is_quantized"] = True
+    elif not use_quant and was_quant:
+        for k in ("row_var", "col_var", "conf_row", "conf_col", "variance"):
+            if k + "_q" in state:
+                state[k] = _from_al(state, k)
+        if "m_q" in state:
+            mb = state.get("m_block_size", m_block)
+            state["m"] = m_dequantize(state["m_q"], state["m_scale"], numel, mb, state.get("m_quant_type", "uf8"))
+            for k in ("m_q", "m_scale", "m_block_size", "m_quant_type"):
+                state.pop(k, None)
+        state["is_quantized"] = False
+
+    if beta3 is None:
+        for prefix in ("conf_row", "conf_col"):
+            state.pop(prefix, None)
+            for k in _al_keys(prefix):
+                state.pop(k, None)
+    elif expect_factored:
+        c_fmt = cqt if use_quant else "fp32"
+        if "conf_row" not in state and "conf_row_q" not in state:
+            _init_al(state, "conf_row", shape[-2], cur_block, c_fmt)
+        if "conf_col" not in state and "conf_col_q" not in state:
+            _init_al(state, "conf_col", shape[-1], cur_block, c_fmt)
+    if beta1 is not None and "m_q" not in state:
+        mb = state.get("m_block_size", m_block)
+        if use_quant and mqt != "fp32":
+            if "m" in state:
+                state["m_q"], state["m_scale"] = m_quantize(state.pop("m"), mb, mqt)
+                state["m_quant_type"] = mqt
+            else:
+                _init_m(state, numel, mb, mqt)
+            state["m_block_size"] = mb
+        elif "m" not in state and mqt == "fp32":
+            _init_m(state, numel, mb, "fp32")
+    if beta1 is None:
+        for k in ("m_q", "m_scale", "m_block_size", "m_quant_type", "m"):
+            state.pop(k, None)
+    return state

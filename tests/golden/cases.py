@@ -188,6 +188,24 @@ CASES = {
                                   block_size=2048, stochastic_round_writeback=True)),
 }
 
+# ---- group options edited between steps (case key `changes`: {step: {option: value}}, applied to the
+#      parameter group before that step): the state migrations of _init_group (optimizer.py:1650-1860) ----
+CASES.update({
+    "migrate_quantize_off_on": dict(shapes=[(40, 130), (4096,)], steps=6, seed=41, grad=_G_CFG0,
+                                    changes={3: {"quantize": False}, 5: {"quantize": True}},
+                                    hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256)),
+    "migrate_formats": dict(shapes=[(40, 130)], steps=6, seed=42, grad=_G_CFG0,
+                            changes={3: {"m_quant_type": "uf4"}, 5: {"v_quant_type": "al16"}},
+                            hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256)),
+    "migrate_came_toggle": dict(shapes=[(64, 384)], steps=6, seed=43, grad=_G_BF16,
+                                changes={3: {"beta3": None}, 5: {"beta3": 0.9999}},
+                                hp=dict(_CAME, lr=1e-4, m_quant_type="uf8", v_quant_type="al8", block_size=256)),
+    "migrate_factored_off": dict(shapes=[(128, 256)], steps=5, seed=44, grad=_G_HEAVY,
+                                 changes={3: {"factored": False}, 5: {"quantize": False}},
+                                 hp=dict(block_size=256, beta1=0.9, relative_step=False, lr=1e-3)),
+})
+MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
+
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]
 LOWP_FACTORED_CASES = ["adafactor_bf16p", "came_sr_bf16p"]
 

@@ -96,6 +96,9 @@ def run_case(name, out_dir, suffix=""):
     opt = Adafactor8Bit(params, use_cuda_kernel=False, **c["hp"])
     steps = c["steps"]
     for t in range(1, steps + 1):
+        for k, v in c.get("changes", {}).get(t, {}).items():     # an option edited between steps
+            for group in opt.param_groups:
+                group[k] = v
         for p, g in zip(params, grads[t]):
             if g.dtype == np.uint16:
                 p.grad = torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(p.shape)

@@ -43,6 +43,10 @@ class OracleRun:
 
     def step(self):
         self.t += 1
+        edits = self.case.get("changes", {}).get(self.t)
+        if edits:                                # a group option edited before this step
+            self.hp.update(edits)
+            self.states = [o.migrate_state(st, self.hp, p.shape) for st, p in zip(self.states, self.params)]
         norms = []
         for i, (p, st) in enumerate(zip(self.params, self.states)):
             norms.append(self.step_param(i, p, self.grads[self.t][i], st))

@@ -258,3 +258,38 @@ def test_low_precision_parameters_free_running(name, oracle):
                         assert s["neq"] <= max(2, (3e-2 if al16 else 1e-4) * s["n"]), (what, s)
                 elif key.endswith(RANGE_SUFFIXES):
                     parity.assert_ranges(st[key], want, what, max_ulp=0 if exact else 128)
+
+
+# ---------------------------------------------------------------------------
+# group options edited between steps: the state migrations of _init_group (optimizer.py:1650-1860)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name", cases.MIGRATION_CASES)
+def test_state_migration_against_reference(name, oracle):
+    """`quantize` off and on again, a new momentum format (momentum reset), a new V format
+    (re-initialisation, step kept), CAME switched off and on (confidence states dropped and
+    recreated), factored mode switched off: after every step the oracle holds the same state
+    entries as the reference, with codes, ranges and parameters inside the usual bounds."""
+    run = OracleRun(name)
+    gold = load_golden(name)
+    assert str(gold["digest"]) == cases.inputs_digest(run.params0, run.grads)
+    for t in range(1, run.case["steps"] + 1):
+        run.step()
+        for i, (p, st) in enumerate(zip(run.params, run.states)):
+            ref = golden_entries(gold, t, i)
+            mine = {k for k, v in st.items() if isinstance(v, np.ndarray)}
+            theirs = {k for k in ref if k not in ("param", "fira_prev_norm")}
+            assert mine == theirs, f"{name} step {t} param {i}: state entries {sorted(mine ^ theirs)} differ"
+            for key, want in ref.items():
+                what = f"{name} step {t} param {i} {key}"
+                if key == "param":
+                    parity.assert_params(p, want, what)
+                elif key in CODE_KEYS:
+                    fmt = st.get("m_quant_type") if key.startswith("m") else None
+                    got = st[key]
+                    if fmt in ("uf4", "d4"):
+                        got, want = parity.unpack_nibbles(got), parity.unpack_nibbles(want)
+                    parity.assert_codes(got, want, what, al16=want.dtype == np.uint16, zero_reserved=not key.startswith("m"))
+                elif key.endswith(RANGE_SUFFIXES):
+                    parity.assert_ranges(st[key], want, what, max_ulp=128)
+                elif key in st:
+                    assert parity.rel_l2(st[key], want) <= 2e-4, what
