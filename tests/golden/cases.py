@@ -204,6 +204,12 @@ CASES.update({
                                  changes={3: {"factored": False}, 5: {"quantize": False}},
                                  hp=dict(block_size=256, beta1=0.9, relative_step=False, lr=1e-3)),
 })
+# APOLLO with one scaling factor per tensor (apollo_scale_type="tensor") and a larger apollo_scale, rank 8
+CASES["apollo_r8_tensor"] = dict(shapes=[(256, 128), (64, 384)], steps=5, seed=45,
+                                 grad=dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="bf16"),
+                                 hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=8, apollo_update_proj_gap=3,
+                                         apollo_scale_type="tensor", apollo_scale=128.0, m_quant_type="uf8",
+                                         v_quant_type="al8", block_size=2048))
 MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
 
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]

@@ -12,13 +12,13 @@ from test_fullrank_gpu import make_optimizer, state_np, to_cuda_grad
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("name", ["apollo_r32", "apollo_r8_tensor"])
 @pytest.mark.parametrize("exact", [True, False], ids=["exact_projection", "tensor_core_projection"])
-def test_apollo_free_running_matches_oracle(oracle, exact):
+def test_apollo_free_running_matches_oracle(oracle, exact, name):
     """exact: correctly rounded projections, states bit-comparable with the oracle.  Tensor
     cores: the projected gradient carries the rounding of a binary32 accumulation (as the
     reference's own matmul does), so ranges and the limiter state move by a few ulp."""
     from adafactor8bit import _engine, optimizer as opt_mod
-    name = "apollo_r32"
     run = OracleRun(name)
     opt_mod.APOLLO_RNG_DEVICE = "cpu"
     saved = _engine.EXACT_PROJECTION

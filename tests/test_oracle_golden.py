@@ -178,13 +178,14 @@ def test_came_free_running_states(oracle):
         _check_step(name, t, i, p, st, golden_entries(gold, t, i), param_tol=5e-5, al16_frac=3e-2, range_ulp=4096)
 
 
-def test_apollo_oracle_against_reference(oracle):
+@pytest.mark.parametrize("name", ["apollo_r32", "apollo_r8_tensor"])
+def test_apollo_oracle_against_reference(oracle, name):
     """APOLLO, 8 free-running steps with a refresh of the projection every 3.  The projected
     gradient comes out of a float32 GEMM in the reference and out of exactly rounded dot products
     in the oracle; outputs that nearly cancel differ in many ulps, they sit at the minimum of
     their AL block and move that block's range.  Hence: momentum codes and seeds exact, V codes
-    only bounded statistically, the limiter state to 1e-4, parameters to 5e-5."""
-    name = "apollo_r32"
+    only bounded statistically, the limiter state to 1e-4, parameters to 5e-5.  The second case
+    scales per tensor (apollo_scale_type="tensor") with apollo_scale=128."""
     run = OracleRun(name)
     gold = load_golden(name)
     assert str(gold["digest"]) == cases.inputs_digest(run.params0, run.grads)
