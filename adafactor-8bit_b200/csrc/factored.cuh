@@ -512,6 +512,7 @@ __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_fa
         if (PREFETCH) fetch(nxt, k0 + NB);
         else fetch(cur, k0);
         float g[NB][8];
+        double rsum[NB];
 #pragma unroll
         for (int k = 0; k < NB; ++k) {
             cur[k].unpack(L.negate_grad, g[k]);
@@ -549,17 +550,52 @@ __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_fa
                 racc += xd;
                 cacc[j] += xd;
             }
+            rsum[k] = racc;
+        }
+        // The NB row sums of the warp are reduced together: each exchange halves the number of
+        // values a lane carries, so NB rows cost NB - 1 + (5 - log2 NB) shuffles instead of 5 NB.
+        // The sum of row k0 + i ends up in lane 32 i / NB.
+        static_assert(NB == 2 || NB == 4, "row-sum reduction is written for 2 or 4 rows");
+        double v;
+        if (NB == 4) {
+            const bool hi = lane & 16;
+            const double r0x = __shfl_xor_sync(0xffffffffu, hi ? rsum[0] : rsum[2], 16);
+            const double r1x = __shfl_xor_sync(0xffffffffu, hi ? rsum[1] : rsum[NB - 1], 16);
+            const double k0v = (hi ? rsum[2] : rsum[0]) + r0x;
+            const double k1v = (hi ? rsum[NB - 1] : rsum[1]) + r1x;
+            const bool h2 = lane & 8;
+            v = (h2 ? k1v : k0v) + __shfl_xor_sync(0xffffffffu, h2 ? k0v : k1v, 8);
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) racc += __shfl_xor_sync(0xffffffffu, racc, o);
-            if (lane == 0 && r < R) atomicAdd(sT.row_sum + r, racc);
+            for (int o = 4; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if ((lane & 7) == 0) {
+                const int64_t r = r0 + warp + 8 * (k0 + (lane >> 3));
+                if (r < R && k0 + (lane >> 3) < FSTAT_ROWS / 8) atomicAdd(sT.row_sum + r, v);
+            }
+        } else {
+            const bool hi = lane & 16;
+            v = (hi ? rsum[1] : rsum[0]) + __shfl_xor_sync(0xffffffffu, hi ? rsum[0] : rsum[1], 16);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if ((lane & 15) == 0) {
+                const int64_t r = r0 + warp + 8 * (k0 + (lane >> 4));
+                if (r < R && k0 + (lane >> 4) < FSTAT_ROWS / 8) atomicAdd(sT.row_sum + r, v);
+            }
         }
     }
 }
 
 // RESIDUAL: CAME's (U - M)^2 + eps statistic; otherwise g^2 (separate instantiations, so that
 // the lighter one keeps its lower register count)
+// resident CTAs asked of the compiler (measured on B200: 3 for the g*g pass, 1.02 -> 0.76 ms on the
+// TinyLlama set; 5 for the residual pass)
+#ifndef AF8_FSTAT_MIN_CTAS
+#define AF8_FSTAT_MIN_CTAS 3
+#endif
+#ifndef AF8_FSTAT_MIN_CTAS_RES
+#define AF8_FSTAT_MIN_CTAS_RES 5
+#endif
 template <typename GradT, bool RESIDUAL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, RESIDUAL ? AF8_FSTAT_MIN_CTAS_RES : AF8_FSTAT_MIN_CTAS)
 factored_stats_vec_kernel(const FactoredLaunch L)
 {
     __shared__ double s_col[8][FSTAT_COLS];      // [warp][j * 32 + lane]
@@ -621,8 +657,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
     constexpr bool WRITES = PASS != 0;
     constexpr bool SUMS = PASS != 1;
     __shared__ af8_factored_tensor sT;
-    __shared__ double s_acc2[2][FUPD_THREADS / 32];
-    int parity = 0;
+    __shared__ double s_acc2[1][FUPD_THREADS / 32];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool has_m = L.m_fmt != AF8_M_NONE;
     const bool m_quant = has_m && L.m_fmt != AF8_M_FP32;
@@ -645,9 +680,32 @@ factored_update_vec_kernel(const FactoredLaunch L)
     bool zero_upd = false;
     DivBy D = make_div(1.0f);
 
+    // Sum-of-squares passes: a thread keeps one binary64 partial over all the chunks of a tensor
+    // that its CTA processes; at the end of that run the CTA reduces it once and stores the total in
+    // the slot of the run's first chunk and zero in the others (the finaliser adds a tensor's slots).
+    double run_acc = 0.0;
+    int64_t run_first = -1;
+    auto flush_sums = [&](int64_t end) {
+        double acc = run_acc;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) s_acc2[0][warp] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double sum = 0.0;
+            for (int w = 0; w < FUPD_THREADS / 32; ++w) sum += s_acc2[0][w];
+            L.block_sumsq[run_first] = sum;
+        }
+        for (int64_t i = run_first + 1 + tid; i < end; i += FUPD_THREADS) L.block_sumsq[i] = 0.0;
+        __syncthreads();
+        run_acc = 0.0;
+    };
+
     for (int64_t id = id_begin; id < id_end; ++id) {
         const int t = cur_t;
         if (cur_t < 0 || id >= next_first) {
+            if (SUMS && run_first >= 0) flush_sums(id);
+            run_first = id;
             int tn = cur_t;
             if (tn < 0) tn = find_factored_chunk(L.tensors, L.n_tensors, id);
             else while (tn + 1 < L.n_tensors && __ldg(&L.tensors[tn + 1].first_chunk) <= id) ++tn;
@@ -786,20 +844,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
             for (int j = 0; j < 8; ++j) mj[j] = 0.0f;
         }
         if (SUMS) {
-            // One barrier per chunk: the warp partials alternate between two shared rows, and a
-            // row is rewritten only two chunks later, after a barrier that warp 0 reaches once it
-            // has read the row.
-            double acc = part;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (lane == 0) s_acc2[parity][warp] = acc;
-            __syncthreads();
-            if (tid == 0) {
-                double s = 0.0;
-                for (int w = 0; w < FUPD_THREADS / 32; ++w) s += s_acc2[parity][w];
-                L.block_sumsq[id] = s;
-            }
-            parity ^= 1;
+            run_acc += part;                 // reduced over the CTA once per tensor (flush_sums)
             if (!writes) continue;
         }
         if (m_quant) {
@@ -838,6 +883,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
             }
         }
     }
+    if (SUMS && run_first >= 0) flush_sums(id_end);
 }
 
 inline int factored_chunk_for(int m_block)
