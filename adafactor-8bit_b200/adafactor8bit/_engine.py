@@ -500,6 +500,11 @@ class FactoredPlan:
             off += int(self._vec_len[i])
         t["rows"], t["cols"] = self.rows, self.cols
         t["first_chunk"], t["first_tile"] = self.first_chunk, self.first_tile
+        # units of the small-state launch: the quantisation blocks of the row state, then of the column state
+        sb = t["row_var"]["block"].astype(np.int64)
+        units = (self.rows + sb - 1) // sb + (self.cols + sb - 1) // sb
+        t["first_small"] = np.concatenate([[0], np.cumsum(units)[:-1]])
+        self.small_units = int(units.sum())
         return t
 
     def kernel_name(self, what):
@@ -526,7 +531,7 @@ class FactoredPlan:
     def _small(self, conf, stream):
         lib = N.lib()
         self._log("small_conf" if conf else "small_var", lambda: N.check(
-            lib.af8_factored_small(ctypes.byref(self.cfg), self.d_table.data_ptr(), self.n, int(conf),
+            lib.af8_factored_small(ctypes.byref(self.cfg), self.d_table.data_ptr(), self.n, int(conf), self.small_units,
                                    stream.cuda_stream), "af8_factored_small"), stream)
 
     def _update(self, mode, use_dyn, stream):

@@ -80,7 +80,7 @@ FACTORED_TENSOR = np.dtype([
     ("row_var", SMALL_STATE), ("col_var", SMALL_STATE), ("conf_row", SMALL_STATE), ("conf_col", SMALL_STATE),
     ("rows", np.int64), ("cols", np.int64), ("first_chunk", np.int64), ("first_tile", np.int64),
     ("decay", np.float32), ("alpha", np.float32), ("v_w", np.float32), ("m_w", np.float32),
-    ("c_w", np.float32), ("eps1", np.float32), ("eps_came", np.float32), ("reserved", np.float32),
+    ("c_w", np.float32), ("eps1", np.float32), ("eps_came", np.float32), ("first_small", np.int32),
     ("sr_base", np.uint64),
 ], align=True)
 assert FACTORED_TENSOR.itemsize == 320
@@ -145,7 +145,7 @@ PROTOTYPES = {
     "af8_factored_tile_cols": (_c_i, []),
     "af8_factored_upload": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_p, _c_i, _c_p]),
     "af8_factored_stats": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_p, _c_i, _c_p, _c_p]),
-    "af8_factored_small": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_i, _c_p]),
+    "af8_factored_small": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_i, _c_i, _c_p]),
     "af8_factored_update": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
     "af8_apollo_project": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_l, _c_l, _c_l, _c_p, _c_p, _c_p]),
     "af8_apollo_project_workspace": (ctypes.c_int64, [_c_l, _c_l, _c_l]),

@@ -197,16 +197,18 @@ factored_stats_kernel(const FactoredLaunch L)
 // ---------------------------------------------------------------------------
 // small states
 // ---------------------------------------------------------------------------
-// EMA + requantisation of one small state of n elements (optimizer.py:2232-2238,
-// 937-946, 2248-2251).  `out` receives the un-requantised values.  Returns this
-// thread's partial sum of the values (binary64) for the mean of the row state.
-__device__ double small_state_ema(const af8_small_state &S, const double *sums, double count, int64_t n,
-                                  float eps_add, float w, float floor_log, float *out, float *s_l, float (*s_red)[8])
+// EMA + requantisation of block b of one small state of n elements (optimizer.py:2232-2238,
+// 937-946, 2248-2251).  `out` receives the un-requantised values.  Returns this thread's partial
+// sum of the block's values (binary64) for the mean of the row state.
+__device__ double small_state_block(const af8_small_state &S, const double *sums, double count, int64_t n, int64_t b,
+                                    float eps_add, float w, float floor_log, float *out, float *s_l, float (*s_red)[8])
 {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int block = S.block;
     double acc = 0.0;
     if (S.fmt == AF8_V_FP32) {
-        for (int64_t i = tid; i < n; i += blockDim.x) {
+        const int64_t end = min(n, (b + 1) * (int64_t)block);
+        for (int64_t i = b * block + tid; i < end; i += blockDim.x) {
             const float nv = __fadd_rn(__double2float_rn(sums[i] / count), eps_add);
             const float v = lerp_t(S.f32[i], nv, w);
             S.f32[i] = v;
@@ -218,76 +220,113 @@ __device__ double small_state_ema(const af8_small_state &S, const double *sums, 
     const int bits = S.fmt;
     const float qm1 = bits == 16 ? 65534.0f : 254.0f;
     const int qmax = bits == 16 ? 65535 : 255;
-    const int block = S.block;
-    const int64_t nblocks = (n + block - 1) / block;
-    for (int64_t b = 0; b < nblocks; ++b) {
-        const float sc = S.scale[b], ml = S.min_log[b];
-        float mn = INFINITY, mx = -INFINITY;
-        __syncthreads();
-        for (int i = tid; i < block; i += blockDim.x) {
-            const int64_t e = b * block + i;
-            float v = 0.0f;                                       // padding re-enters as zeros (optimizer.py:303-305)
-            if (e < n) {
-                const uint32_t code = bits == 16 ? static_cast<const uint16_t *>(S.q)[e] : static_cast<const uint8_t *>(S.q)[e];
-                const float nv = __fadd_rn(__double2float_rn(sums[e] / count), eps_add);
-                v = lerp_t(al_decode(code, sc, ml, qm1), nv, w);
-                out[e] = v;
-                acc += (double)v;
-            }
-            const float l = al_log2(v);
-            if (v != 0.0f) mn = fminf(mn, l);
-            mx = fmaxf(mx, l);
-            s_l[i] = (v != 0.0f) ? l : -INFINITY;
+    const float sc = S.scale[b], ml = S.min_log[b];
+    float mn = INFINITY, mx = -INFINITY;
+    for (int i = tid; i < block; i += blockDim.x) {
+        const int64_t e = b * block + i;
+        float v = 0.0f;                                       // padding re-enters as zeros (optimizer.py:303-305)
+        if (e < n) {
+            const uint32_t code = bits == 16 ? static_cast<const uint16_t *>(S.q)[e] : static_cast<const uint8_t *>(S.q)[e];
+            const float nv = __fadd_rn(__double2float_rn(sums[e] / count), eps_add);
+            v = lerp_t(al_decode(code, sc, ml, qm1), nv, w);
+            out[e] = v;
+            acc += (double)v;
         }
-        mn = warp_min(mn);
-        mx = warp_max(mx);
-        if (lane == 0) { s_red[0][warp] = mn; s_red[1][warp] = mx; }
-        __syncthreads();
-        for (int w8 = 0; w8 < 8; ++w8) { mn = fminf(mn, s_red[0][w8]); mx = fmaxf(mx, s_red[1][w8]); }
-        float min_log, scale;
-        al_range(mn, mx, floor_log, min_log, scale);
-        for (int i = tid; i < block; i += blockDim.x) {
-            const float l = s_l[i];
-            const uint32_t code = (l == -INFINITY) ? 0u : al_encode(1.0f, l, min_log, scale, qm1, qmax);
-            const int64_t e = b * block + i;
-            if (bits == 16) static_cast<uint16_t *>(S.q)[e] = (uint16_t)code;
-            else static_cast<uint8_t *>(S.q)[e] = (uint8_t)code;
-        }
-        if (tid == 0) { S.scale[b] = scale; S.min_log[b] = min_log; }
+        const float l = al_log2(v);
+        if (v != 0.0f) mn = fminf(mn, l);
+        mx = fmaxf(mx, l);
+        s_l[i] = (v != 0.0f) ? l : -INFINITY;
     }
+    mn = warp_min(mn);
+    mx = warp_max(mx);
+    if (lane == 0) { s_red[0][warp] = mn; s_red[1][warp] = mx; }
+    __syncthreads();
+    for (int w8 = 0; w8 < 8; ++w8) { mn = fminf(mn, s_red[0][w8]); mx = fmaxf(mx, s_red[1][w8]); }
+    float min_log, scale;
+    al_range(mn, mx, floor_log, min_log, scale);
+    for (int i = tid; i < block; i += blockDim.x) {
+        const float l = s_l[i];
+        const uint32_t code = (l == -INFINITY) ? 0u : al_encode(1.0f, l, min_log, scale, qm1, qmax);
+        const int64_t e = b * block + i;
+        if (bits == 16) static_cast<uint16_t *>(S.q)[e] = (uint16_t)code;
+        else static_cast<uint8_t *>(S.q)[e] = (uint8_t)code;
+    }
+    if (tid == 0) { S.scale[b] = scale; S.min_log[b] = min_log; }
     return acc;
 }
 
+__device__ __forceinline__ int find_factored_small(const af8_factored_tensor *t, int n, int id)
+{
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (__ldg(&t[mid].first_small) <= id) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+// One CTA per quantisation block of a row or column state: every block of every tensor in
+// parallel (a 32000-row state has 125 blocks of 256; one CTA per tensor walked them in turn).
 __global__ void __launch_bounds__(256)
-factored_small_kernel(const af8_factored_tensor *tensors, int conf, float floor_log)
+factored_small_kernel(const af8_factored_tensor *tensors, int n_tensors, int conf, float floor_log)
 {
     extern __shared__ float s_l[];
     __shared__ float s_red[2][8];
-    __shared__ double s_acc[256];
-    const af8_factored_tensor T = tensors[blockIdx.x];
-    const int tid = threadIdx.x;
-    const af8_small_state &SR = conf ? T.conf_row : T.row_var;
-    const af8_small_state &SC = conf ? T.conf_col : T.col_var;
-    float *inv_r = conf ? T.inv_row_conf : T.inv_row;
-    float *inv_c = conf ? T.inv_col_conf : T.inv_col;
+    __shared__ double s_acc[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t = find_factored_small(tensors, n_tensors, (int)blockIdx.x);
+    const af8_factored_tensor T = tensors[t];
+    const int block = (conf ? T.conf_row : T.row_var).block;
+    const int64_t nbr = (T.rows + block - 1) / block;
+    const int64_t local = (int64_t)blockIdx.x - T.first_small;
+    const bool is_row = local < nbr;
+    const int64_t b = is_row ? local : local - nbr;
     const float w = conf ? T.c_w : T.v_w;
     const float eps_add = conf ? 0.0f : T.eps1;                 // optimizer.py:2222-2223 vs 933-934
-
-    const double part = small_state_ema(SR, T.row_sum, (double)T.cols, T.rows, eps_add, w, floor_log, inv_r, s_l, s_red);
-    small_state_ema(SC, T.col_sum, (double)T.rows, T.cols, eps_add, w, floor_log, inv_c, s_l, s_red);
-
-    // mean of the row state, clamped (optimizer.py:2236, 948)
-    s_acc[tid] = part;
-    __syncthreads();
-    for (int o = 128; o > 0; o >>= 1) {
-        if (tid < o) s_acc[tid] += s_acc[tid + o];
-        __syncthreads();
+    double part;
+    if (is_row)
+        part = small_state_block(conf ? T.conf_row : T.row_var, T.row_sum, (double)T.cols, T.rows, b, eps_add, w, floor_log,
+                                 conf ? T.inv_row_conf : T.inv_row, s_l, s_red);
+    else
+        part = small_state_block(conf ? T.conf_col : T.col_var, T.col_sum, (double)T.rows, T.cols, b, eps_add, w, floor_log,
+                                 conf ? T.inv_col_conf : T.inv_col, s_l, s_red);
+    if (!is_row) return;
+    // the block's share of the mean of the row state goes where its first row sum was
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) s_acc[warp] = part;
+    __syncthreads();                                            // (also: every thread has read its row sums)
+    if (tid == 0) {
+        double s = 0.0;
+        for (int k = 0; k < 8; ++k) s += s_acc[k];
+        T.row_sum[b * block] = s;
     }
-    float rm = __double2float_rn(s_acc[0] / (double)T.rows);
-    if (rm < T.eps1) rm = T.eps1;
-    // inverse std vectors (optimizer.py:818-821)
-    for (int64_t i = tid; i < T.rows; i += blockDim.x) inv_r[i] = rsqrt_t(__fdiv_rn(inv_r[i], rm));
-    for (int64_t j = tid; j < T.cols; j += blockDim.x) inv_c[j] = rsqrt_t(inv_c[j]);
+}
+
+// grid (n_tensors, slices): mean of the row state, clamped (optimizer.py:2236, 948), then the
+// inverse-std vectors (optimizer.py:818-821); the CTAs of a tensor share its elements
+__global__ void __launch_bounds__(256)
+factored_inv_kernel(const af8_factored_tensor *tensors, int conf)
+{
+    __shared__ float s_rm;
+    const af8_factored_tensor T = tensors[blockIdx.x];
+    const int tid = threadIdx.x;
+    float *inv_r = conf ? T.inv_row_conf : T.inv_row;
+    float *inv_c = conf ? T.inv_col_conf : T.inv_col;
+    const int block = (conf ? T.conf_row : T.row_var).block;
+    if (tid == 0) {
+        double s = 0.0;
+        for (int64_t e = 0; e < T.rows; e += block) s += T.row_sum[e];      // fixed order
+        float rm = __double2float_rn(s / (double)T.rows);
+        if (rm < T.eps1) rm = T.eps1;
+        s_rm = rm;
+    }
+    __syncthreads();
+    const float rm = s_rm;
+    const int64_t stride = (int64_t)blockDim.x * gridDim.y;
+    const int64_t first = (int64_t)blockIdx.y * blockDim.x + tid;
+    for (int64_t i = first; i < T.rows; i += stride) inv_r[i] = rsqrt_t(__fdiv_rn(inv_r[i], rm));
+    for (int64_t j = first; j < T.cols; j += stride) inv_c[j] = rsqrt_t(inv_c[j]);
 }
 
 // ---------------------------------------------------------------------------
@@ -899,7 +938,7 @@ inline int validate_factored(const af8_factored_cfg &c, const af8_factored_tenso
     const bool has_m = c.m_fmt != AF8_M_NONE;
     const bool m_quant = has_m && c.m_fmt != AF8_M_FP32;
     const int chunk = factored_chunk_for(m_quant ? c.m_block : 0);
-    int64_t next_chunk = 0, next_tile = 0;
+    int64_t next_chunk = 0, next_tile = 0, next_small = 0;
     for (int i = 0; i < n; ++i) {
         const af8_factored_tensor &t = T[i];
         if (t.rows <= 0 || t.cols <= 0) return fail(AF8_ERR_INVALID, "factored tensor %d: empty shape", i);
@@ -920,8 +959,14 @@ inline int validate_factored(const af8_factored_cfg &c, const af8_factored_tenso
         next_chunk += (t.rows * t.cols + chunk - 1) / chunk;
         next_tile += ((t.rows + FSTAT_ROWS - 1) / FSTAT_ROWS) * ((t.cols + FSTAT_COLS - 1) / FSTAT_COLS);
         const af8_small_state *ss[4] = {&t.row_var, &t.col_var, &t.conf_row, &t.conf_col};
+        const int sb = t.row_var.block;
+        if (sb <= 0) return fail(AF8_ERR_INVALID, "factored tensor %d: small-state block must be positive", i);
+        if (t.first_small != next_small) return fail(AF8_ERR_INVALID, "factored tensor %d: first_small %d, expected %lld", i, t.first_small, (long long)next_small);
+        next_small += (t.rows + sb - 1) / sb + (t.cols + sb - 1) / sb;
+        if (next_small > 0x7fffffff) return fail(AF8_ERR_UNSUPPORTED, "factored table: too many small-state blocks");
         for (int k = 0; k < (c.came ? 4 : 2); ++k) {
             const af8_small_state &s = *ss[k];
+            if (s.block != sb) return fail(AF8_ERR_INVALID, "factored tensor %d: the small states of a tensor must share one block size", i);
             if (s.fmt == AF8_V_FP32) {
                 if (!s.f32) return fail(AF8_ERR_INVALID, "factored tensor %d: null fp32 small state %d", i, k);
             } else if (s.fmt == AF8_V_AL8 || s.fmt == AF8_V_AL16) {
@@ -1021,15 +1066,18 @@ extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factore
 }
 
 extern "C" int af8_factored_small(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
-                                  int32_t n_tensors, int32_t conf, void *stream)
+                                  int32_t n_tensors, int32_t conf, int32_t total_units, void *stream)
 {
     using namespace af8;
     int rc = check_factored_cfg(cfg, "af8_factored_small");
     if (rc) return rc;
-    if (!dev_tensors || n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_factored_small: null or empty table");
+    if (!dev_tensors || n_tensors <= 0 || total_units <= 0) return fail(AF8_ERR_INVALID, "af8_factored_small: null or empty table");
     if (conf && !cfg->came) return fail(AF8_ERR_INVALID, "af8_factored_small: confidence states exist only with CAME");
     const size_t smem = sizeof(float) * GEN_MAX_BLOCK;
-    factored_small_kernel<<<n_tensors, 256, smem, static_cast<cudaStream_t>(stream)>>>(dev_tensors, conf, cfg->v_floor);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    factored_small_kernel<<<total_units, 256, smem, st>>>(dev_tensors, n_tensors, conf, cfg->v_floor);
+    AF8_CUDA_TRY(cudaGetLastError());
+    factored_inv_kernel<<<dim3((unsigned)n_tensors, 8), 256, 0, st>>>(dev_tensors, conf);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }

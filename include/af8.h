@@ -297,7 +297,8 @@ typedef struct af8_factored_tensor {
     float c_w;                  /* float(1 - beta3) */
     float eps1;
     float eps_came;
-    float reserved;
+    int32_t first_small;        /* running sum of ceil(rows / B) + ceil(cols / B), B = row_var.block: this tensor's
+                                   first unit in af8_factored_small (its row blocks, then its column blocks) */
     uint64_t sr_base;           /* stochastic rounding counter origin, as af8_fullrank_tensor.sr_base;
                                    element r*cols + c draws from counter sr_base + r*cols + c */
 } af8_factored_tensor;
@@ -351,11 +352,14 @@ AF8_API int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factored_t
 
 /* Per tensor: means from the sums, EMA into the row / column states (second
  * moment when conf == 0, CAME confidence when conf != 0), requantisation, and
- * the inverse-std vectors inv_row / inv_col (or inv_*_conf).
+ * the inverse-std vectors inv_row / inv_col (or inv_*_conf).  Two launches: one CTA per
+ * quantisation block of a state (total_units of them, see af8_factored_tensor.first_small), then
+ * the mean of the row state and the inverse-std vectors.  The row sums are consumed: the first
+ * entry of each block of row_sum is overwritten with the block's partial sum of the new state.
  * Replaces fused_log_quantize_lerp on the small states and the torch glue
  * around it (optimizer.py:2226-2252, 2289-2294, 818-821). */
 AF8_API int af8_factored_small(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
-                               int32_t n_tensors, int32_t conf, void *stream);
+                               int32_t n_tensors, int32_t conf, int32_t total_units, void *stream);
 
 /* One pass over all elements in chunks.  block_sumsq: one DOUBLE per chunk
  * (SUMSQ modes; set af8_norm_tensor.partials_f64 when finalising them).  dyn: per-tensor scalars (pre_div always read when cfg->came,
