@@ -78,6 +78,21 @@ __device__ __forceinline__ float m_old_at(const af8_factored_tensor &T, int m_fm
     return m_decode(T.m_q, __ldg(T.m_scale + flat / m_block), flat, m_fmt);
 }
 
+// Tensor.lerp_ with a weight that is the same for many elements: the choice between ATen's two
+// forms is made once (LerpW), an element costs a subtraction, a select and one fma.
+struct LerpW { float ww; bool small; };
+__device__ __forceinline__ LerpW make_lerp(float w)
+{
+    LerpW l;
+    l.small = fabsf(w) < 0.5f;
+    l.ww = l.small ? w : __fsub_rn(w, 1.0f);
+    return l;
+}
+__device__ __forceinline__ float lerp_w(float s, float e, const LerpW &l)
+{
+    return __fmaf_rn(l.ww, __fsub_rn(e, s), l.small ? s : e);
+}
+
 // U = g * inv_row * inv_col, then the RMS clip divisor (optimizer.py:825-828)
 __device__ __forceinline__ float u_clipped(float g, float ir, float ic, float pre_div)
 {
@@ -518,9 +533,9 @@ __device__ __forceinline__ void m_old8(const af8_factored_tensor &T, int m_fmt, 
     const float sc = __ldg(T.m_scale + flat / m_block);
     if (m_fmt == AF8_M_UF8) {
         const uint2 w = have_pre ? pre : *reinterpret_cast<const uint2 *>(T.m_q + flat);
-        const float mc = __fdiv_rn(sc, 128.0f);
+        const float mc = __fmul_rn(sc, 0.0078125f);      // fl(scale / 128): a power-of-two divisor, scale >= 1e-12
 #pragma unroll
-        for (int j = 0; j < 8; ++j) m[j] = __fmul_rn((float)((int)(((j < 4 ? w.x : w.y) >> (8 * (j & 3))) & 0xffu) - 128), mc);
+        for (int j = 0; j < 8; ++j) m[j] = __fmul_rn(byte_minus_128(j < 4 ? w.x : w.y, j & 3), mc);   // no integer conversion
     } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) m[j] = m_decode(T.m_q, sc, flat + j, m_fmt);
@@ -569,12 +584,13 @@ __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_fa
                 const int64_t flat = r * C + c;
                 const float ir = sT.inv_row[r];
                 const DivBy D = make_div(pre_div);
+                const LerpW LW = make_lerp(sT.m_w);
                 float mo[8];
                 m_old8(sT, L.m_fmt, L.m_block, flat, mo);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float u = u_clipped_fast(g[k][j], ir, ic[j], D);
-                    const float m = lerp_t(mo[j], u, sT.m_w);
+                    const float m = lerp_w(mo[j], u, LW);
                     const float df = __fsub_rn(u, m);
                     x[j] = __fadd_rn(__fmul_rn(df, df), sT.eps_came);
                 }
@@ -625,13 +641,19 @@ __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_fa
 
 // RESIDUAL: CAME's (U - M)^2 + eps statistic; otherwise g^2 (separate instantiations, so that
 // the lighter one keeps its lower register count)
-// resident CTAs asked of the compiler (measured on B200: 3 for the g*g pass, 1.02 -> 0.76 ms on the
-// TinyLlama set; 5 for the residual pass)
+// resident CTAs asked of the compiler (measured on B200: 3 for both passes; the g*g pass went
+// from 1.02 to 0.76 ms on the TinyLlama set with it)
 #ifndef AF8_FSTAT_MIN_CTAS
 #define AF8_FSTAT_MIN_CTAS 3
 #endif
+#ifndef AF8_FSTAT_RES_NB
+#define AF8_FSTAT_RES_NB 2
+#endif
+#ifndef AF8_FSTAT_RES_PREFETCH
+#define AF8_FSTAT_RES_PREFETCH true
+#endif
 #ifndef AF8_FSTAT_MIN_CTAS_RES
-#define AF8_FSTAT_MIN_CTAS_RES 5
+#define AF8_FSTAT_MIN_CTAS_RES 3
 #endif
 template <typename GradT, bool RESIDUAL>
 __global__ void __launch_bounds__(256, RESIDUAL ? AF8_FSTAT_MIN_CTAS_RES : AF8_FSTAT_MIN_CTAS)
@@ -672,7 +694,7 @@ factored_stats_vec_kernel(const FactoredLaunch L)
 #pragma unroll
         for (int j = 0; j < 8; ++j) cacc[j] = 0.0;
         if (!RESIDUAL) stats_rows<GradT, 4, true, false>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
-        else stats_rows<GradT, 2, false, true>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
+        else stats_rows<GradT, AF8_FSTAT_RES_NB, AF8_FSTAT_RES_PREFETCH, true>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
 #pragma unroll
         for (int j = 0; j < 8; ++j) s_col[warp][j * 32 + lane] = cacc[j];
         __syncthreads();
@@ -689,8 +711,11 @@ factored_stats_vec_kernel(const FactoredLaunch L)
 // chunk = 2048 elements = 8 warps x 256; requires m_block == 256 when the momentum is quantised
 // PASS 0: a sum-of-squares pass (fewer values live, more resident CTAs); 1: the APPLY pass;
 // 2: the LAG pass (APPLY plus the sums of this step's raw update)
-template <typename GradT, int PASS>
-__global__ void __launch_bounds__(FUPD_THREADS, PASS != 0 ? 3 : 4)
+// CTAS: resident CTAs per SM asked of the compiler.  Measured on B200: 4 for the sum passes; for the
+// writing passes 3 with momentum (CAME, 0.78 ms per Llama-2-7B layer) and 2 without (Adafactor on the
+// TinyLlama set: 2.51 -> 2.21 ms, no register spills).
+template <typename GradT, int PASS, int CTAS>
+__global__ void __launch_bounds__(FUPD_THREADS, CTAS)
 factored_update_vec_kernel(const FactoredLaunch L)
 {
     constexpr bool WRITES = PASS != 0;
@@ -812,6 +837,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
         double part = 0.0;
         if (ok) {
             float g[8], ic[8], u[8];
+            const LerpW LW = make_lerp(sT.m_w);
             cg.unpack(L.negate_grad, g);
             load_f8_ro(sT.inv_col + col, ic);
             const float ir = __ldg(sT.inv_row + row);
@@ -826,7 +852,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
                     const float irc = __ldg(sT.inv_row_conf + row);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        mj[j] = lerp_t(mo[j], u_clipped_fast(g[j], ir, ic[j], D), sT.m_w);
+                        mj[j] = lerp_w(mo[j], u_clipped_fast(g[j], ir, ic[j], D), LW);
                         u[j] = __fmul_rn(__fmul_rn(mj[j], irc), icc[j]);
                     }
                 }
@@ -835,7 +861,7 @@ factored_update_vec_kernel(const FactoredLaunch L)
                 m_old8(sT, L.m_fmt, L.m_block, flat, mo, pre_m, cm);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    mj[j] = lerp_t(mo[j], g[j], sT.m_w);
+                    mj[j] = lerp_w(mo[j], g[j], LW);
                     u[j] = __fmul_rn(__fmul_rn(mj[j], ir), ic[j]);
                 }
             } else {
@@ -1105,17 +1131,20 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     const bool apply = cfg->mode == AF8_FUPD_APPLY || cfg->mode == AF8_FUPD_LAG;
     const bool lag = cfg->mode == AF8_FUPD_LAG;
     if (vec) {                                   // persistent: the CTAs that are resident together
-        grid = (int64_t)sm_count() * (apply ? 3 : 4);
+        grid = (int64_t)sm_count() * (apply ? (cfg->m_fmt == AF8_M_NONE ? 2 : 3) : 4);
         if (grid > total_chunks) grid = total_chunks;
     }
     cudaStream_t cst = static_cast<cudaStream_t>(stream);
     const bool bf = cfg->grad_dtype == AF8_BF16;
-    if (vec && bf && lag) factored_update_vec_kernel<bf16_tag, 2><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
-    else if (vec && lag) factored_update_vec_kernel<float, 2><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
-    else if (vec && bf && apply) factored_update_vec_kernel<bf16_tag, 1><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
-    else if (vec && bf) factored_update_vec_kernel<bf16_tag, 0><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
-    else if (vec && apply) factored_update_vec_kernel<float, 1><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
-    else if (vec) factored_update_vec_kernel<float, 0><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+    const bool no_m = cfg->m_fmt == AF8_M_NONE;
+#define AF8_LAUNCH_FUPD(G, P, C) factored_update_vec_kernel<G, P, C><<<(int)grid, FUPD_THREADS, 0, cst>>>(L)
+    if (vec && bf && lag) { if (no_m) AF8_LAUNCH_FUPD(bf16_tag, 2, 2); else AF8_LAUNCH_FUPD(bf16_tag, 2, 3); }
+    else if (vec && lag) { if (no_m) AF8_LAUNCH_FUPD(float, 2, 2); else AF8_LAUNCH_FUPD(float, 2, 3); }
+    else if (vec && bf && apply) { if (no_m) AF8_LAUNCH_FUPD(bf16_tag, 1, 2); else AF8_LAUNCH_FUPD(bf16_tag, 1, 3); }
+    else if (vec && bf) AF8_LAUNCH_FUPD(bf16_tag, 0, 4);
+    else if (vec && apply) { if (no_m) AF8_LAUNCH_FUPD(float, 1, 2); else AF8_LAUNCH_FUPD(float, 1, 3); }
+    else if (vec) AF8_LAUNCH_FUPD(float, 0, 4);
+#undef AF8_LAUNCH_FUPD
     else factored_update_kernel<<<(int)grid, FUPD_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(L, chunk);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
