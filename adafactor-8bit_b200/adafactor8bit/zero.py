@@ -110,12 +110,16 @@ class ShardedAdafactor8Bit:
         self.total_numel = sum(numels)
         # inner groups: part-major, so that a part's launches are complete before the next part starts
         inner_groups, self._last_group_of_part = [], {}
+        self._origin = []                  # inner group -> index of the group it was cut from
         for k in range(k_parts):
-            for g in groups:
+            for gi, g in enumerate(groups):
                 mine = [p for p in g["params"] if id(p) in owned and part_of[id(p)] == k]
                 if mine:
                     inner_groups.append(dict(g, params=mine))
+                    self._origin.append(gi)
                     self._last_group_of_part[k] = len(inner_groups) - 1
+        self._groups = groups
+        self._global_index = {id(p): i for i, p in enumerate(all_params)}
         self.inner = inner_factory(inner_groups, **kwargs) if inner_groups else None
         if self.inner is not None and hasattr(self.inner, "_sr_seed_map"):
             # stochastic-rounding seeds as the unsharded optimizer would hand them out: one per
@@ -198,8 +202,66 @@ class ShardedAdafactor8Bit:
         main.wait_stream(self.gather_stream)
         return loss
 
+    # -- checkpoints in the unsharded optimizer's layout ------------------------------------------
+    def full_state_dict(self, dst=0):
+        """The state of all ranks merged into the layout an unsharded optimizer saves (and the
+        reference's class loads): {"state": {parameter index: state}, "param_groups": [...]} plus
+        the optimizer-level counters.  Tensors are moved to the CPU.  Collective: every rank calls
+        it; rank `dst` gets the dictionary, the others None."""
+        inner_sd = self.inner.state_dict() if self.inner is not None else {"state": {}, "param_groups": []}
+        inner_params = [p for g in self.inner.param_groups for p in g["params"]] if self.inner is not None else []
+        mine = {}
+        for idx, st in inner_sd["state"].items():
+            mine[self._global_index[id(inner_params[idx])]] = {
+                k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in st.items()}
+        extras = {k: v for k, v in inner_sd.items() if k not in ("state", "param_groups")}
+        options = {self._origin[j]: {k: v for k, v in g.items() if k != "params"}
+                   for j, g in enumerate(inner_sd["param_groups"])}
+        payload = (mine, extras, options)
+        if self.world > 1:
+            gathered = [None] * self.world if self.rank == dst else None
+            dist.gather_object(payload, gathered, dst=dst, group=self.group)
+            if self.rank != dst:
+                return None
+        else:
+            gathered = [payload]
+        state, extras, options = {}, {}, {}
+        for m, e, o in gathered:
+            state.update(m)
+            for k, v in e.items():
+                extras[k] = max(extras[k], v) if (k in extras and isinstance(v, (int, float))) else v
+            for gi, opts in o.items():
+                options.setdefault(gi, opts)
+        groups, first = [], 0
+        for gi, g in enumerate(self._groups):
+            opts = options.get(gi, {k: v for k, v in g.items() if k != "params"})
+            groups.append(dict(opts, params=list(range(first, first + len(g["params"])))))
+            first += len(g["params"])
+        return dict(extras, state=dict(sorted(state.items())), param_groups=groups)
+
+    def load_full_state_dict(self, sd):
+        """Load a state dictionary in the unsharded layout (from full_state_dict, from an unsharded
+        optimizer of this package or from the reference): every rank keeps the states of the
+        tensors it owns."""
+        if self.inner is None:
+            return
+        inner_sd = self.inner.state_dict()
+        inner_params = [p for g in self.inner.param_groups for p in g["params"]]
+        state = {}
+        for idx, p in enumerate(inner_params):
+            st = sd["state"].get(self._global_index[id(p)])
+            if st is not None:
+                state[idx] = st
+        groups = []
+        for j, g in enumerate(inner_sd["param_groups"]):
+            saved = sd["param_groups"][self._origin[j]]
+            groups.append(dict({k: v for k, v in saved.items() if k != "params"}, params=g["params"]))
+        extras = {k: v for k, v in sd.items() if k not in ("state", "param_groups")}
+        self.inner.load_state_dict(dict(extras, state=state, param_groups=groups))
+
     def state_dict(self):
-        """State of the tensors this rank owns (a per-rank shard, not the reference's full layout)."""
+        """State of the tensors this rank owns (a per-rank shard; full_state_dict gives the
+        unsharded layout)."""
         return {"rank": self.rank, "world": self.world, "owner": list(self.owner),
                 "inner": self.inner.state_dict() if self.inner is not None else None}
 

@@ -58,6 +58,9 @@ def _worker(rank, world, port, out, variant):
             opt.step()
         torch.cuda.synchronize()
         out[rank] = [p.detach().float().cpu().numpy().copy() for p in params]
+        full = opt.full_state_dict(dst=0)          # the merged checkpoint, in the unsharded layout
+        if rank == 0:
+            out["full"] = full
     finally:
         dist.destroy_process_group()
 
@@ -85,3 +88,16 @@ def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
     for rank in (0, 1):
         for a, p in zip(out[rank], params):
             assert np.array_equal(a, p.detach().float().cpu().numpy())
+    # the merged checkpoint equals the one-GPU optimizer's, entry by entry
+    full, want = out["full"], opt.state_dict()
+    assert sorted(full["state"]) == sorted(want["state"])
+    assert full["_sr_seed_counter"] == want["_sr_seed_counter"]
+    assert [g["params"] for g in full["param_groups"]] == [g["params"] for g in want["param_groups"]]
+    for idx, st in want["state"].items():
+        got = full["state"][idx]
+        assert sorted(got) == sorted(st), (idx, sorted(got), sorted(st))
+        for k, v in st.items():
+            if isinstance(v, torch.Tensor):
+                assert torch.equal(got[k], v.cpu()), (idx, k)
+            else:
+                assert got[k] == v, (idx, k, got[k], v)
