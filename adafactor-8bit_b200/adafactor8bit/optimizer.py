@@ -614,6 +614,9 @@ class Adafactor8Bit(Optimizer):
                         self._plans.clear()                  # launch plans cache state pointers and formats
                 if group.get("stochastic_round_writeback", False) and p.dtype in (torch.bfloat16, torch.float16):
                     self._sr_seed(state, p)     # seeds follow the parameter order of the step (optimizer.py:1889-1892)
+                if p.numel() == 0:              # an empty parameter has a state and a step count, nothing to launch
+                    state["step"] = state.get("step", 0) + 1
+                    continue
                 entries.append((p, p.grad, state))
             if entries:
                 self._run_group(gi, group, entries)

@@ -210,6 +210,12 @@ CASES["apollo_r8_tensor"] = dict(shapes=[(256, 128), (64, 384)], steps=5, seed=4
                                  hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=8, apollo_update_proj_gap=3,
                                          apollo_scale_type="tensor", apollo_scale=128.0, m_quant_type="uf8",
                                          v_quant_type="al8", block_size=2048))
+# ragged sizes with quantised states from one element up (min_8bit_size=1): single elements, sizes one below
+# and one above the M block (256) and the V block (2048), a matrix whose rows straddle blocks
+CASES["adamw_ragged"] = dict(shapes=[(1,), (255,), (257,), (2047,), (2049,), (3, 700), (4097,)], steps=4, seed=46,
+                             grad=dict(_G_HEAVY, spike_step=3, spike_mult=100.0),
+                             hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256, min_8bit_size=1,
+                                     enable_fira_for_adafactor=True, fira_margin=0.01))
 MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
 
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]

@@ -5,7 +5,7 @@ import af8_oracle as o
 import cases
 
 FULLRANK_CASES = ["adamw_uf8_al8", "adamw_fira_bf16", "adamw_uf4_al16", "adamw_d8_al8", "adamw_d4_al8",
-                  "adamw_fp32m_al8", "rmsprop_al8", "adafactor_unfactored", "sgd_momentum_uf8", "sgd_plain_bf16"]
+                  "adamw_fp32m_al8", "rmsprop_al8", "adafactor_unfactored", "sgd_momentum_uf8", "sgd_plain_bf16", "adamw_ragged"]
 
 
 def load_golden(name):

@@ -338,3 +338,22 @@ def test_lag_norm_single_pass(name, oracle):
                 assert abs(float(st["fira_prev_norm"].item()) - float(so["fira_prev_norm"])) <= 2e-6 * abs(float(so["fira_prev_norm"])), what
     # the lagged run is a different algorithm: after the spike it must differ from the exact one
     assert any("prev_update_norm" in opt.state[p] for p in params)
+
+
+def test_empty_parameter_is_stepped_without_a_launch():
+    """A parameter without elements gets a state and a step count, like in the reference, and
+    does not disturb the other tensors of its group."""
+    from adafactor8bit import Adafactor8Bit
+    hp = dict(cases.CASES["adamw_uf8_al8"]["hp"])
+    empty = torch.nn.Parameter(torch.zeros(0, 4, device="cuda"))
+    full = torch.nn.Parameter(torch.ones(64, 128, device="cuda"))
+    alone = torch.nn.Parameter(torch.ones(64, 128, device="cuda"))
+    opt, ref = Adafactor8Bit([empty, full], **hp), Adafactor8Bit([alone], **hp)
+    for t in range(2):
+        g = torch.full((64, 128), 0.01 * (t + 1), device="cuda")
+        empty.grad, full.grad, alone.grad = torch.zeros(0, 4, device="cuda"), g.clone(), g.clone()
+        opt.step()
+        ref.step()
+    torch.cuda.synchronize()
+    assert opt.state[empty]["step"] == 2 and opt.state[empty]["variance"].shape == (0, 4)
+    assert torch.equal(full.detach(), alone.detach())
