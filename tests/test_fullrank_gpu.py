@@ -357,3 +357,45 @@ def test_empty_parameter_is_stepped_without_a_launch():
     torch.cuda.synchronize()
     assert opt.state[empty]["step"] == 2 and opt.state[empty]["variance"].shape == (0, 4)
     assert torch.equal(full.detach(), alone.detach())
+
+
+def test_tensor_beyond_2_31_elements():
+    """64-bit indexing: a tensor of 2^31 + 6149 elements (17 GB with its states).  V blocks are
+    independent without the limiter, so the first and the last blocks must come out exactly like
+    the same values stepped as small tensors."""
+    from adafactor8bit import Adafactor8Bit
+    if torch.cuda.get_device_properties(0).total_memory < 60 * 2 ** 30:
+        pytest.skip("needs 60 GB of device memory")
+    hp = dict(cases.CASES["adamw_uf8_al8"]["hp"], min_8bit_size=1)
+    n = 2 ** 31 + 6149
+    tail0 = (n // 2048 - 1) * 2048                         # the last full block and the ragged one after it
+
+    def fill(t, scale, lo, hi):                            # a value pattern that depends on the global index
+        for a in range(lo, hi, 2 ** 27):
+            b = min(a + 2 ** 27, hi)
+            idx = torch.arange(a, b, device="cuda", dtype=torch.int64)
+            t[a - lo:b - lo] = (((idx * 2654435761) % 2001) - 1000).to(torch.float32).mul_(scale).to(t.dtype)
+    big = torch.nn.Parameter(torch.empty(n, device="cuda"))
+    fill(big.data, 2e-5, 0, n)
+    gbig = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    fill(gbig, 1e-6, 0, n)
+    head = torch.nn.Parameter(big.detach()[:4096].clone())
+    tail = torch.nn.Parameter(big.detach()[tail0:].clone())
+    for p in (big, head, tail):
+        p.grad_dtype = None
+    opt, ref = Adafactor8Bit([big], **hp), Adafactor8Bit([head, tail], **hp)
+    for t in range(2):
+        big.grad, head.grad, tail.grad = gbig, gbig[:4096].clone(), gbig[tail0:].clone()
+        opt.step()
+        ref.step()
+    torch.cuda.synchronize()
+    assert torch.equal(big.detach()[:4096], head.detach())
+    assert torch.equal(big.detach()[tail0:], tail.detach())
+    sb, st = opt.state[big], ref.state[tail]
+    assert torch.equal(sb["variance_q"][tail0:tail0 + st["variance_q"].numel()], st["variance_q"])
+    assert torch.equal(sb["m_q"][tail0:tail0 + st["m_q"].numel()], st["m_q"])
+    assert torch.equal(sb["variance_scale"][tail0 // 2048:], st["variance_scale"])
+    mid = big.detach()[2 ** 31 - 4096:2 ** 31 + 4096]
+    assert torch.isfinite(mid).all() and (mid != 0).any()
+    from adafactor8bit import _native
+    assert _native.device_status(torch.cuda.current_stream().cuda_stream) == 0
