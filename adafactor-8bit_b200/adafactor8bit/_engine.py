@@ -679,8 +679,9 @@ class ApolloPlan:
         self.negate = int(bool(negate))
         self.rank = int(rank)
         for p in self.params:
-            if p.dtype != torch.float32 or not p.is_contiguous() or p.dim() != 2:
-                raise RuntimeError("the APOLLO kernels update contiguous 2-D fp32 parameters")
+            if p.dtype not in _GRAD_DT or p.dtype != self.params[0].dtype or not p.is_contiguous() or p.dim() != 2:
+                raise RuntimeError("the APOLLO kernels update contiguous 2-D fp32, bf16 or fp16 parameters, one dtype per group")
+        self.param_dtype = _GRAD_DT[self.params[0].dtype]
         self.rows = [int(p.shape[0]) for p in self.params]
         self.cols = [int(p.shape[1]) for p in self.params]
         self.nch = [max(r, c) for r, c in zip(self.rows, self.cols)]
@@ -822,7 +823,8 @@ class ApolloPlan:
             self.h_finish.mark(stream)
         for i, sin in enumerate(sins):
             t = per_tensor[i]
-            N.check(lib.af8_apollo_apply(self.params[i].data_ptr(), grads[i].data_ptr(), self.grad_dtype, self.negate,
+            N.check(lib.af8_apollo_apply(self.params[i].data_ptr(), self.param_dtype, int(t.get("sr", False)), int(t.get("sr_base", 0)),
+                                         grads[i].data_ptr(), self.grad_dtype, self.negate,
                                          self.sf[i].data_ptr(), self.out.data_ptr() + 16 * i, self.rows[i], self.cols[i],
                                          ctypes.byref(sin), float(t["decay"]), int(t["has_decay"]), s), "af8_apollo_apply")
         if log is not None:

@@ -155,8 +155,8 @@ PROTOTYPES = {
     "af8_apollo_scales_batch": (_c_i, [_c_p, _c_p, _c_i, _c_l, _c_p]),
     "af8_apollo_scales": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn), _c_p, _c_p, _c_p,
                                  _c_p, _c_p]),
-    "af8_apollo_apply": (_c_i, [_c_p, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn),
-                                _c_f, _c_i, _c_p]),
+    "af8_apollo_apply": (_c_i, [_c_p, _c_i, _c_i, ctypes.c_uint64, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l,
+                                ctypes.POINTER(ApolloScalarsIn), _c_f, _c_i, _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
     "af8_lag_scalars": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p]),
     "af8_fullrank_limited_step_noalloc": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_f, _c_i, _c_f, _c_p, _c_i, _c_p, _c_p]),

@@ -734,7 +734,8 @@ class Adafactor8Bit(Optimizer):
         if v_fmt == "fp32" or m_fmt == "fp32":
             raise NotImplementedError("APOLLO with fp32 low-rank states is not available in this build")
         ids = tuple(id(p) for p, _, _ in items)
-        pkey = (gi, "apollo", items[0][1].dtype, v_fmt, m_fmt, rank, bool(group["maximize"]))
+        pkey = (gi, "apollo", items[0][1].dtype, items[0][0].dtype, v_fmt, m_fmt, rank, bool(group["maximize"]))
+        sr = bool(group.get("stochastic_round_writeback", False)) and items[0][0].dtype in (torch.bfloat16, torch.float16)
         plan = self._plans.get(pkey)
         first_flags, pts, per_tensor, grads = [], [], [], []
         apollo_eps = group.get("apollo_eps", 1e-6)
@@ -781,7 +782,8 @@ class Adafactor8Bit(Optimizer):
                      sqrt_scale=f32(math.sqrt(group.get("apollo_scale", 1.0))),
                      fira=bool(group.get("enable_fira_for_apollo", True)),
                      scale_tensor=group.get("apollo_scale_type", "channel") == "tensor",
-                     scale_front=bool(group.get("apollo_scale_front", False)), decay=decay, has_decay=wd != 0)
+                     scale_front=bool(group.get("apollo_scale_front", False)), decay=decay, has_decay=wd != 0,
+                     sr=sr, sr_base=sr_base(self._sr_seed(st, p), step) if sr else 0)      # optimizer.py:3050-3051
             if beta1 is not None and not group["relative_step"]:                       # optimizer.py:3015-3023
                 apply_bc = True if group.get("bias_correction") is None else group["bias_correction"]
                 if apply_bc:

@@ -400,6 +400,42 @@ __global__ void apollo_finalize_multi_kernel(const af8_apollo_finish_tensor *T, 
 // ---------------------------------------------------------------------------
 // 5. apply: p = p*decay + (us*G) * final_scale[channel]
 // ---------------------------------------------------------------------------
+// bf16 / fp16 parameters (optimizer.py:3043-3079).  Nearest rounding: the in-place ops of the fp32 rule,
+// each rounded to the parameter's format (mul_ by the decay, then addcmul_ / add_).  Stochastic rounding:
+// p*decay + (g * final_scale) * update_scale with every product and the sum rounded to binary32
+// (optimizer.py:3061-3065), then one stochastic rounding with the counter generator.
+struct ApolloLowp { int dtype, sr; uint64_t sr_base; };
+__device__ __forceinline__ uint32_t apollo_lowp_bits(float p, float g, float f, float us, float decay, int has_decay,
+                                                     int scale_tensor, const ApolloLowp &P, int64_t idx)
+{
+    if (!P.sr) {
+        float x = has_decay ? param_round(__fmul_rn(p, decay), P.dtype) : p;
+        x = scale_tensor ? __fmaf_rn(__fmul_rn(us, f), g, x) : __fmaf_rn(__fmul_rn(us, g), f, x);
+        return P.dtype == AF8_BF16 ? f32_to_bf16_rn_bits(x) : f32_to_f16_rn_bits(x);
+    }
+    float x = has_decay ? __fmul_rn(p, decay) : p;
+    x = __fadd_rn(x, __fmul_rn(__fmul_rn(g, f), us));
+    const uint32_t r = sr_bits24(P.sr_base, (uint64_t)idx);
+    return P.dtype == AF8_BF16 ? sr_bf16_bits(x, r) : sr_f16_bits(x, r);
+}
+
+__global__ void __launch_bounds__(256)
+apollo_apply_lowp_kernel(void *param, const void *grad, int grad_dtype, int negate, const float *sf,
+                         const af8_apollo_scalars *sc, int64_t rows, int64_t cols, int right, int scale_tensor,
+                         int fira, int front, float sqrt_scale, float decay, int has_decay, const ApolloLowp P)
+{
+    const float us = sc->update_scale, fs = sc->fira;
+    const int64_t n = rows * cols;
+    for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * 256) {
+        const float g = apollo_grad(grad, grad_dtype, idx, negate);
+        float f = scale_tensor ? sf[0] : (right ? sf[idx / cols] : sf[idx % cols]);
+        if (fira) f = __fmul_rn(f, fs);                                  // optimizer.py:2994
+        if (!front) f = __fmul_rn(f, sqrt_scale);                        // optimizer.py:3000
+        const float pv = param_load(param, idx, P.dtype);
+        static_cast<uint16_t *>(param)[idx] = (uint16_t)apollo_lowp_bits(pv, g, f, us, decay, has_decay, scale_tensor, P, idx);
+    }
+}
+
 __global__ void __launch_bounds__(256)
 apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, const float *sf,
                     const af8_apollo_scalars *sc, int64_t rows, int64_t cols, int right, int scale_tensor,
@@ -427,12 +463,14 @@ apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, 
 
 // the same with 8 consecutive elements per thread and 128-bit accesses (cols % 8 == 0,
 // 16-byte aligned arrays, fewer than 2^34 elements)
-template <bool BF16>
+// LOWP: the parameter is bf16 / fp16 (8 of them in one 128-bit word); P is ignored otherwise
+template <bool BF16, bool LOWP>
 __global__ void __launch_bounds__(256)
-apollo_apply_vec_kernel(float *__restrict__ param, const void *__restrict__ grad, int negate, const float *__restrict__ sf,
+apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ grad, int negate, const float *__restrict__ sf,
                         const af8_apollo_scalars *__restrict__ sc, int64_t rows, int64_t cols, int right, int scale_tensor,
-                        int fira, int front, float sqrt_scale, float decay, int has_decay)
+                        int fira, int front, float sqrt_scale, float decay, int has_decay, const ApolloLowp P)
 {
+    float *const param = static_cast<float *>(param_v);
     const float us = sc->update_scale, fs = sc->fira;
     const uint32_t gpr = (uint32_t)(cols >> 3);                 // groups of 8 per row
     const uint32_t ngroups = (uint32_t)((rows * cols) >> 3);
@@ -461,6 +499,27 @@ apollo_apply_vec_kernel(float *__restrict__ param, const void *__restrict__ grad
         } else {
             const float4 a = __ldg(reinterpret_cast<const float4 *>(sf + c8)), b = __ldg(reinterpret_cast<const float4 *>(sf + c8) + 1);
             f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+        }
+        if (LOWP) {
+            uint4 *ph = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(param_v) + idx);
+            const uint4 pw = *ph;
+            const uint32_t w[4] = {pw.x, pw.y, pw.z, pw.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t h = (e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffffu);
+                const float p = P.dtype == AF8_BF16 ? bf16_bits_to_f32(h) : f16_bits_to_f32(h);
+                float ge = g[e];
+                if (!isfinite(ge)) ge = 0.0f;
+                if (negate) ge = -ge;
+                float fe = f[e];
+                if (fira) fe = __fmul_rn(fe, fs);
+                if (!front) fe = __fmul_rn(fe, sqrt_scale);
+                const uint32_t r = apollo_lowp_bits(p, ge, fe, us, decay, has_decay, scale_tensor, P, idx + e);
+                if (e & 1) o[e >> 1] |= r << 16; else o[e >> 1] = r;
+            }
+            *ph = make_uint4(o[0], o[1], o[2], o[3]);
+            continue;
         }
         float4 *pp = reinterpret_cast<float4 *>(param + idx);
         const float4 p0 = pp[0], p1 = pp[1];
@@ -863,25 +922,38 @@ extern "C" int af8_apollo_scales_batch(const af8_apollo_finish_tensor *host_tens
     return AF8_OK;
 }
 
-extern "C" int af8_apollo_apply(void *param, const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
+extern "C" int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stochastic_round, uint64_t sr_base,
+                                const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
                                 const af8_apollo_scalars *scalars, int64_t rows, int64_t cols,
                                 const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *stream)
 {
     using namespace af8;
     if (!param || !grad || !sf || !scalars || !in) return fail(AF8_ERR_INVALID, "af8_apollo_apply: null argument");
     if (grad_dtype != AF8_F32 && grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_apply: gradients must be fp32 or bf16");
+    if (param_dtype != AF8_F32 && param_dtype != AF8_BF16 && param_dtype != AF8_F16) return fail(AF8_ERR_INVALID, "af8_apollo_apply: bad param_dtype %d", param_dtype);
+    if (stochastic_round && param_dtype == AF8_F32) return fail(AF8_ERR_INVALID, "af8_apollo_apply: stochastic rounding applies to bf16 / fp16 parameters only");
+    const bool lowp = param_dtype != AF8_F32;
+    const ApolloLowp P{param_dtype, stochastic_round ? 1 : 0, sr_base};
     const int64_t n = rows * cols;
     const int right = rows >= cols ? 1 : 0;
     if (cols % 8 == 0 && n < ((int64_t)1 << 34) && aligned16(param) && aligned16(grad) && (right || in->scale_tensor || aligned16(sf))) {
         int64_t gv = (n / 8 + 255) / 256;
         if (gv > 148 * 8) gv = 148 * 8;
         cudaStream_t st = static_cast<cudaStream_t>(stream);
-        if (grad_dtype == AF8_BF16)
-            apollo_apply_vec_kernel<true><<<(int)gv, 256, 0, st>>>(static_cast<float *>(param), grad, negate, sf, scalars, rows, cols, right,
-                                                                 in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay);
-        else
-            apollo_apply_vec_kernel<false><<<(int)gv, 256, 0, st>>>(static_cast<float *>(param), grad, negate, sf, scalars, rows, cols, right,
-                                                                  in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay);
+#define AF8_APOLLO_APPLY(B, L) apollo_apply_vec_kernel<B, L><<<(int)gv, 256, 0, st>>>(param, grad, negate, sf, scalars, rows, cols, right, \
+        in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay, P)
+        if (grad_dtype == AF8_BF16) { if (lowp) AF8_APOLLO_APPLY(true, true); else AF8_APOLLO_APPLY(true, false); }
+        else { if (lowp) AF8_APOLLO_APPLY(false, true); else AF8_APOLLO_APPLY(false, false); }
+#undef AF8_APOLLO_APPLY
+        AF8_CUDA_TRY(cudaGetLastError());
+        return AF8_OK;
+    }
+    if (lowp) {
+        int64_t gl = (n + 255) / 256;
+        if (gl > 148 * 16) gl = 148 * 16;
+        apollo_apply_lowp_kernel<<<(int)gl, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            param, grad, grad_dtype, negate, sf, scalars, rows, cols, right, in->scale_tensor, in->fira, in->scale_front,
+            in->sqrt_scale, decay, has_decay, P);
         AF8_CUDA_TRY(cudaGetLastError());
         return AF8_OK;
     }

@@ -478,7 +478,12 @@ typedef struct af8_apollo_finish_tensor {
 AF8_API int af8_apollo_scales_batch(const af8_apollo_finish_tensor *host_tensors, af8_apollo_finish_tensor *dev_tensors,
                                     int32_t n, int64_t total_units, void *stream);
 
-AF8_API int af8_apollo_apply(void *param, const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
+/* param_dtype AF8_F32, AF8_BF16 or AF8_F16.  A 16-bit parameter is rounded to nearest after the decay and
+ * after the update, or, with stochastic_round, p*decay + (g*final_scale)*update_scale is formed in binary32
+ * and rounded stochastically with the counter generator at sr_base (see af8_fullrank_tensor.sr_base;
+ * optimizer.py:3043-3079, apollo_apply_{bf16,fp16}_{sr,det}). */
+AF8_API int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stochastic_round, uint64_t sr_base,
+                             const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
                              const af8_apollo_scalars *scalars, int64_t rows, int64_t cols,
                              const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *stream);
 

@@ -1099,20 +1099,33 @@ AF8O_API int af8o_apollo_step(const af8o_apollo_cfg *c, float *p, const void *gr
     if (c->d > 0.0f) { denom = norm_unscaled / c->clip_div; if (denom < 1.0f) denom = 1.0f; }   /* optimizer.py:3003-3005 */
     float us = -c->alpha / denom;                             /* optimizer.py:3013 */
     if (c->bc_mode == 1) us = us * c->bc; else if (c->bc_mode == 2) us = us / c->bc;
-    /* fp32 parameters (optimizer.py:3074-3079) */
-    if (!c->scale_tensor) {
+    if (g_pf.sr) {
+        /* bf16 / fp16 parameters with stochastic rounding (optimizer.py:3061-3067): separate tensor ops,
+         * param*decay, grad*final_scale, *update_scale, +, each rounded to binary32 */
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < n; ++i) {
-            float pv = c->has_decay ? p[i] * c->decay : p[i];
+            float pf = c->has_decay ? p[i] * c->decay : p[i];
+            const float f = c->scale_tensor ? sf[0] : (right ? sf[i / C] : sf[i % C]);
+            float t = G[i] * f;
+            t = t * us;
+            pf = pf + t;
+            const float rnd = af8o_sr_uniform(g_pf.seed, g_pf.step, (uint64_t)i);
+            p[i] = (g_pf.dtype == AF8O_G_BF16) ? bf16_to_f32(af8o_sr_bf16(pf, rnd)) : f16_to_f32(af8o_sr_f16(pf, rnd));
+        }
+    } else if (!c->scale_tensor) {
+        /* optimizer.py:3074-3077: mul_ then addcmul_ in place, each rounded to the parameter's format */
+#pragma omp parallel for schedule(static)
+        for (int64_t i = 0; i < n; ++i) {
+            float pv = c->has_decay ? round_param(p[i] * c->decay) : p[i];
             float f = right ? sf[i / C] : sf[i % C];
-            p[i] = fmaf(us * G[i], f, pv);
+            p[i] = round_param(fmaf(us * G[i], f, pv));
         }
     } else {
-        float a = us * sf[0];
+        float a = us * sf[0];                                 /* optimizer.py:3079 */
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < n; ++i) {
-            float pv = c->has_decay ? p[i] * c->decay : p[i];
-            p[i] = fmaf(a, G[i], pv);
+            float pv = c->has_decay ? round_param(p[i] * c->decay) : p[i];
+            p[i] = round_param(fmaf(a, G[i], pv));
         }
     }
     if (norm_out) *norm_out = norm_unscaled;

@@ -717,11 +717,12 @@ def apollo_step(p, g, state, hp):
     has_prev = c_i(1 if "scaled_grad_norm_prev" in state else 0)
     prev = c_f(float(state.get("scaled_grad_norm_prev", 0.0)))
     norm = c_f(-1.0)
-    rc = lib_.af8o_apollo_step(
-        ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), _ptr(pt),
-        _ptr(state.get("v_low_q")), _ptr(state.get("v_low_scale")), _ptr(state.get("v_low_min_log")),
-        _ptr(state.get("v_low")), _ptr(state.get("m_low_q")), _ptr(state.get("m_low_scale")), _ptr(state.get("m_low")),
-        _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev), ctypes.byref(norm))
+    with param_format(hp, state, state["step"]):
+        rc = lib_.af8o_apollo_step(
+            ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), _ptr(pt),
+            _ptr(state.get("v_low_q")), _ptr(state.get("v_low_scale")), _ptr(state.get("v_low_min_log")),
+            _ptr(state.get("v_low")), _ptr(state.get("m_low_q")), _ptr(state.get("m_low_scale")), _ptr(state.get("m_low")),
+            _ptr(_map_for(mqt)), ctypes.byref(has_prev), ctypes.byref(prev), ctypes.byref(norm))
     if rc != 0:
         raise RuntimeError(f"af8o_apollo_step failed with {rc}")
     if has_prev.value:

@@ -216,6 +216,12 @@ CASES["adamw_ragged"] = dict(shapes=[(1,), (255,), (257,), (2047,), (2049,), (3,
                              grad=dict(_G_HEAVY, spike_step=3, spike_mult=100.0),
                              hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256, min_8bit_size=1,
                                      enable_fira_for_adafactor=True, fira_margin=0.01))
+# APOLLO on bf16 parameters: nearest rounding (mul_ / addcmul_ in place) and stochastic rounding
+CASES["apollo_bf16p"] = dict(shapes=[(256, 128), (64, 384), (4096,)], steps=5, seed=47, param_dtype="bf16",
+                             grad=dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="bf16"),
+                             hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=16, apollo_update_proj_gap=3,
+                                     m_quant_type="uf8", v_quant_type="al8", block_size=2048))
+CASES["apollo_sr_bf16p"] = dict(CASES["apollo_bf16p"], seed=48, hp=dict(CASES["apollo_bf16p"]["hp"], stochastic_round_writeback=True))
 MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
 
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]

@@ -146,3 +146,38 @@ def test_factored_low_precision_params(name, oracle):
         ref = golden_entries(gold, steps, i)
         if "param" in ref:
             parity.assert_lowp_params(p.detach().float().cpu().numpy(), ref["param"], fmt, f"{name} final p{i} vs reference", frac=1e-3)
+
+
+@pytest.mark.parametrize("name", ["apollo_bf16p", "apollo_sr_bf16p"])
+def test_apollo_low_precision_params(name, oracle):
+    """APOLLO on bf16 parameters with exact projections (the states then agree with the oracle, see
+    test_apollo_gpu.py): parameters equal except for the usual share on a neighbouring bf16 number."""
+    from adafactor8bit import _engine, optimizer as opt_mod
+    run = OracleRun(name)
+    opt_mod.APOLLO_RNG_DEVICE = "cpu"
+    saved = _engine.EXACT_PROJECTION
+    _engine.EXACT_PROJECTION = True
+    try:
+        params, opt = make(run)
+        for t in range(1, run.case["steps"] + 1):
+            for p, g in zip(params, run.grads[t]):
+                p.grad = cuda_grad(g, p.shape)
+            opt.step()
+            run.step()
+            torch.cuda.synchronize()
+            for i, p in enumerate(params):
+                assert p.dtype == torch.bfloat16
+                parity.assert_lowp_params(p.detach().float().cpu().numpy(), run.params[i], "bf16", f"{name} t{t} p{i} param", frac=2e-4)
+                if "m_low_q" in run.states[i]:
+                    parity.assert_codes(state_np(opt.state[p], "m_low_q"), run.states[i]["m_low_q"], f"{name} t{t} p{i} m_low_q", zero_reserved=False)
+                    parity.assert_codes(state_np(opt.state[p], "v_low_q"), run.states[i]["v_low_q"], f"{name} t{t} p{i} v_low_q")
+        gold = load_golden(name)
+        steps = run.case["steps"]
+        for i, p in enumerate(params):
+            ref = golden_entries(gold, steps, i)
+            got = p.detach().float().cpu().numpy()
+            s = parity.lowp_stats(got, ref["param"], "bf16")
+            assert s["neq"] <= 2e-3 * s["n"] and parity.rel_l2(got, ref["param"]) <= 5e-4, (name, i, s)
+    finally:
+        opt_mod.APOLLO_RNG_DEVICE = None
+        _engine.EXACT_PROJECTION = saved
