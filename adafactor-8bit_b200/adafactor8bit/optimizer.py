@@ -588,13 +588,23 @@ class Adafactor8Bit(Optimizer):
     # step
     # ------------------------------------------------------------------
     @torch.no_grad()
-    def step(self, closure=None):
+    def step(self, closure=None, *, grad_ready=None):
+        """One optimization step (optimizer.py:1866-1938).
+
+        grad_ready (not in the reference): an optional sequence with one CUDA event (or None) per
+        parameter group.  The launches of a group wait for its event on the current stream, so a
+        caller that brings gradients in on another stream (host-to-device copies, a reduce-scatter)
+        group by group overlaps that transfer with the update of the groups already there."""
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
         N.lib()   # fail loudly when the CUDA library is missing
+        if grad_ready is not None and len(grad_ready) != len(self.param_groups):
+            raise ValueError("grad_ready needs one entry per parameter group")
         for gi, group in enumerate(self.param_groups):
+            if grad_ready is not None and grad_ready[gi] is not None:
+                torch.cuda.current_stream().wait_event(grad_ready[gi])
             entries = []
             for p in group["params"]:
                 if p.grad is None:

@@ -399,3 +399,39 @@ def test_tensor_beyond_2_31_elements():
     assert torch.isfinite(mid).all() and (mid != 0).any()
     from adafactor8bit import _native
     assert _native.device_status(torch.cuda.current_stream().cuda_stream) == 0
+
+
+def test_step_waits_for_gradients_arriving_on_another_stream():
+    """step(grad_ready=[event per group]): gradients copied from pinned host memory on a second stream,
+    one event per parameter group; the result equals a plain step on resident gradients."""
+    from adafactor8bit import Adafactor8Bit
+    hp = dict(cases.CASES["adamw_fira_bf16"]["hp"])
+    rng = np.random.default_rng(5)
+    shapes = [(300, 200), (4096,), (128, 256), (2048,)]
+    p0 = [(rng.standard_normal(s) * 0.02).astype(np.float32) for s in shapes]
+    a = [torch.nn.Parameter(torch.from_numpy(x.copy()).cuda()) for x in p0]
+    b = [torch.nn.Parameter(torch.from_numpy(x.copy()).cuda()) for x in p0]
+    oa = Adafactor8Bit([{"params": a[:2]}, {"params": a[2:]}], **hp)
+    ob = Adafactor8Bit([{"params": b[:2]}, {"params": b[2:]}], **hp)
+    side = torch.cuda.Stream()
+    for t in range(3):
+        host = [torch.from_numpy((rng.standard_normal(s) * 1e-3).astype(np.float32)).pin_memory() for s in shapes]
+        events = []
+        with torch.cuda.stream(side):
+            for grp in (a[:2], a[2:]):
+                for p in grp:
+                    i = next(k for k, q in enumerate(a) if q is p)
+                    p.grad = torch.empty_like(p)
+                    p.grad.copy_(host[i], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                events.append(ev)
+        oa.step(grad_ready=events)
+        for p, h in zip(b, host):
+            p.grad = h.cuda()
+        ob.step()
+        torch.cuda.synchronize()
+    for p, q in zip(a, b):
+        assert torch.equal(p.detach(), q.detach())
+    with pytest.raises(ValueError):
+        oa.step(grad_ready=[None])
