@@ -54,6 +54,16 @@ EXTRA_CASES = {
 }
 
 
+# column counts that are multiples of 2048: the apply pass walks such tensors strip by strip
+EXTRA_CASES.update({
+    "adafactor_strips": dict(shapes=[(5, 2048), (70, 4096), (1, 2048), (33, 6144)], steps=3, seed=39,
+                             grad=cases.CASES["adafactor_factored"]["grad"], hp=cases.CASES["adafactor_factored"]["hp"]),
+    "adafactor_m_strips": dict(shapes=[(5, 2048), (70, 4096), (33, 6144)], steps=3, seed=40,
+                               grad=cases.CASES["adafactor_factored_m"]["grad"], hp=cases.CASES["adafactor_factored_m"]["hp"]),
+    "came_strips": dict(shapes=[(5, 2048), (70, 4096), (33, 6144)], steps=3, seed=41, grad=cases.CASES["came_al16"]["grad"],
+                        hp=cases.CASES["came_al16"]["hp"]),
+})
+
 # lag_norm=True (one pass with the previous step's norm; optimizer.py:1056-1071): the vector kernels, the
 # element-wise kernels (odd column counts) and the limiter on top of the clip
 EXTRA_CASES.update({
