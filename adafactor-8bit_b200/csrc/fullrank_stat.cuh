@@ -5,14 +5,16 @@
 // Nothing computed here reaches a stored state: the sums only produce the norm that
 // feeds the Fira limiter and the RMS clip, i.e. fp32 parameters with a 1e-5 tolerance.
 // So, unlike the update kernel, this pass decodes the second moment with the hardware
-// exp2 (relative error 2^-22) instead of the exact per-block table, which removes the
-// only data shared between warps.  One WARP owns one V block (8 sub-steps of 256
-// elements, 8 per lane), keeps its sum in registers and writes one float: no shared
-// memory, no block-wide barrier, plain coalesced 64/128-bit loads.
+// exp2 (relative error 2^-22) instead of the exact sequence.  One WARP owns one V block
+// (8 sub-steps of 256 elements, 8 per lane), keeps its sum in registers and writes one
+// float: no block-wide barrier, plain coalesced 64/128-bit loads.  The 256 possible values
+// of the block's codes go into a per-warp shared-memory table first (8 exp2 per lane and
+// block instead of 64; entry 0 is the exact zero), guarded by warp-level syncs only.
 //
-// Per element: 3 special-function operations (exp2, sqrt, reciprocal); at 16 such lanes
-// per SM that pipe and the 4 bytes per parameter of HBM traffic bound the pass about
-// equally.  (Replacing the reciprocal by rsqrt and a short series was measured slower.)
+// Per element: 2 special-function operations (sqrt, reciprocal) plus 1/8 for the table; the
+// special-function pipe was the busiest unit with the decode per element (3 operations,
+// 70 % busy): the table took the pass from 1.04 to 0.93 ms on the TinyLlama set.
+// (Replacing the reciprocal by rsqrt and a short series was measured slower.)
 #pragma once
 
 #include "common.cuh"
@@ -22,7 +24,7 @@ namespace af8 {
 
 constexpr int STAT_THREADS = 256;
 #ifndef AF8_STAT_MIN_CTAS
-#define AF8_STAT_MIN_CTAS 4
+#define AF8_STAT_MIN_CTAS 5
 #endif
 #ifndef AF8_STAT_UNROLL
 #define AF8_STAT_UNROLL 4
@@ -62,7 +64,11 @@ template <typename GradT>
 __global__ void __launch_bounds__(STAT_THREADS, AF8_STAT_MIN_CTAS)
 fullrank_stat_kernel(const FullrankLaunch L)
 {
+    // per-warp decode table of the block's 256 second-moment codes: 8 exponentials per lane and block
+    // instead of 64 (the special-function pipe is the busiest unit of this pass); entry 0 is exact zero
+    __shared__ float s_dec[STAT_THREADS / 32][256];
     const int lane = threadIdx.x & 31;
+    float *const dec = s_dec[threadIdx.x >> 5];
     const int64_t warps = (int64_t)gridDim.x * (STAT_THREADS / 32);
     const int64_t w0 = (int64_t)blockIdx.x * (STAT_THREADS / 32) + (threadIdx.x >> 5);
 
@@ -100,7 +106,14 @@ fullrank_stat_kernel(const FullrankLaunch L)
         float acc = 0.0f;
 
         if (rem >= FAST_VBLOCK && small_w) {
-            const float2 a2 = bc2(a), c2 = bc2(c), wv2 = bc2(v_w), wm2 = bc2(m_w), ed2 = bc2(eps_d);
+            __syncwarp();                                   // the previous block's look-ups are done
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int code = lane + 32 * k;
+                dec[code] = code ? ex2_approx(__fmaf_rn((float)code, a, c)) : 0.0f;
+            }
+            __syncwarp();
+            const float2 wv2 = bc2(v_w), wm2 = bc2(m_w), ed2 = bc2(eps_d);
             float2 acc2 = make_float2(0.0f, 0.0f);
 AF8_UNROLL_(AF8_STAT_UNROLL)
             for (int s = 0; s < FAST_VBLOCK / FAST_MBLOCK; ++s) {
@@ -116,13 +129,8 @@ AF8_UNROLL_(AF8_STAT_UNROLL)
                     const float2 gj = make_float2(g[j], g[j + 1]);
                     float2 g2 = __fmul2_rn(gj, gj);
                     if (eps_g != 0.0f) g2 = __fadd2_rn(g2, bc2(eps_g));
-                    // byte -> float without a conversion instruction: 2^23 + byte, minus 2^23
-                    const float2 vb = make_float2(__uint_as_float(__byte_perm(vword, 0x4b000000u, 0x7540u | (uint32_t)(j & 3))),
-                                                  __uint_as_float(__byte_perm(vword, 0x4b000000u, 0x7540u | (uint32_t)((j + 1) & 3))));
-                    const float2 te = __ffma2_rn(__fadd2_rn(vb, bc2(-8388608.0f)), a2, c2);
-                    float2 v_old = make_float2(ex2_approx(te.x), ex2_approx(te.y));
-                    if (vb.x == 8388608.0f) v_old.x = 0.0f;              // code 0 is exact zero
-                    if (vb.y == 8388608.0f) v_old.y = 0.0f;
+                    const float2 v_old = make_float2(dec[__byte_perm(vword, 0u, 0x4440u | (uint32_t)(j & 3))],
+                                                     dec[__byte_perm(vword, 0u, 0x4440u | (uint32_t)((j + 1) & 3))]);
                     const float2 vj = __ffma2_rn(wv2, sub2(g2, v_old), v_old);
                     const float2 mb = make_float2(__uint_as_float(__byte_perm(mword, 0x4b000000u, 0x7540u | (uint32_t)(j & 3))),
                                                   __uint_as_float(__byte_perm(mword, 0x4b000000u, 0x7540u | (uint32_t)((j + 1) & 3))));
