@@ -137,7 +137,7 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "tinyllama_adamw_fira"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per parameter, (kernel, gradient dtype) -> bytes
-NCU_TRAFFIC_BPP = {("fullrank_fast_apply", "bf16"): 13.72, ("fullrank_stat", "bf16"): 4.04}
+NCU_TRAFFIC_BPP = {("fullrank_fast_apply", "bf16"): 13.72, ("fullrank_stat", "bf16"): 4.12}
 
 
 def make_groups(wl, named_params):
