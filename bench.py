@@ -226,6 +226,11 @@ def cpu_reference_run(workload, steps, warmup, sample_limit=24_000_000):
     sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
     import af8_oracle as o
     import cases
+    # all host threads this process may use (a multi-process launcher sets OMP_NUM_THREADS=1 for its ranks)
+    try:
+        o.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        o.set_num_threads(os.cpu_count() or 1)
     wl = WORKLOADS[workload]
     hp = o.hyper(**wl["hp"], param_dtype=wl.get("param", "f32"))
     shapes = wl["shapes"]()
