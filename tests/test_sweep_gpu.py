@@ -1,0 +1,180 @@
+"""A seeded sweep over the option space of the full-rank path (state formats, block sizes, update rules,
+parameter and gradient dtypes, limiter and clip) against the CPU oracle: combinations that no fixture names."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import parity
+from oracle_runner import OracleRun
+from test_fullrank_gpu import state_np
+
+pytestmark = pytest.mark.gpu
+
+TORCH_DT = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
+
+
+def _configs(n, seed=2024):
+    rng = np.random.default_rng(seed)
+    out = []
+    for k in range(n):
+        block = int(rng.choice([128, 256, 512, 1024, 2048]))
+        m_block = int(rng.choice([b for b in (32, 64, 128, 256) if block % b == 0]))
+        rule = str(rng.choice(["adam", "rmsprop", "momentum_only", "adafactor_unfactored"]))
+        hp = dict(block_size=block, m_block_size=m_block, min_8bit_size=int(rng.choice([1, 4096])),
+                  v_quant_type=str(rng.choice(["al8", "al16", "fp32"])), lr=float(rng.choice([1e-3, 1e-2])),
+                  weight_decay=float(rng.choice([0.0, 0.01])), factored=False,
+                  enable_fira_for_adafactor=bool(rng.integers(0, 2)), maximize=bool(rng.integers(0, 4) == 0))
+        if rule == "adam":
+            hp.update(beta1=0.9, beta2=0.999, beta2_decay=None, relative_step=False, scale_parameter=False,
+                      scale_weight_decay=False, d=float(rng.choice([0.0, 1.0])), eps=(1e-8, 1e-3),
+                      m_quant_type=str(rng.choice(["uf8", "uf4", "d8", "d4", "fp32"])))
+        elif rule == "rmsprop":
+            hp.update(beta1=None, beta2=0.99, beta2_decay=None, relative_step=False, scale_parameter=False,
+                      scale_weight_decay=False, d=float(rng.choice([0.0, 1.0])), eps=(1e-8, 1e-3))
+        elif rule == "momentum_only":       # Adafactor-style second moment with momentum: the momentum-only rule
+            hp.update(beta1=0.9, relative_step=False, scale_parameter=bool(rng.integers(0, 2)), d=1.0,
+                      m_quant_type=str(rng.choice(["uf8", "uf4", "d8"])))
+        pd = str(rng.choice(["f32", "f32", "bf16", "f16"]))
+        gd = {"f32": str(rng.choice(["f32", "bf16"])), "bf16": "bf16", "f16": "f16"}[pd]
+        if pd != "f32":
+            hp["stochastic_round_writeback"] = bool(rng.integers(0, 2))
+        shapes = [tuple(int(x) for x in rng.integers(1, 90, size=int(rng.integers(1, 3)))) for _ in range(3)] + [(int(rng.integers(4096, 9000)),)]
+        grad = dict(dist="rowscale", std=1e-3, zero_frac=float(rng.choice([0.0, 0.01])), dtype=gd)
+        out.append(dict(shapes=shapes, steps=3, seed=500 + k, grad=grad, hp=hp, param_dtype=pd))
+    return out
+
+
+CONFIGS = _configs(24)
+
+
+@pytest.mark.parametrize("k", range(len(CONFIGS)))
+def test_fullrank_option_sweep(k, oracle):
+    from adafactor8bit import Adafactor8Bit, _engine
+    case = CONFIGS[k]
+    if case["hp"].get("m_quant_type") in ("d8", "d4"):
+        for bits in (8, 4):
+            oracle.set_dynamic_map(bits, _engine.dynamic_map(bits))
+    run = OracleRun(f"sweep{k}", case=case)
+    fmt = case["param_dtype"]
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(TORCH_DT[fmt]).cuda()) for p in run.params0]
+    for p in params:
+        p.grad_dtype = None
+    opt = Adafactor8Bit(params, **case["hp"])
+    for t in range(1, case["steps"] + 1):
+        for p, g in zip(params, run.grads[t]):
+            if g.dtype == np.uint16:
+                p.grad = torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(p.shape).cuda()
+            else:
+                p.grad = torch.from_numpy(g.copy()).reshape(p.shape).cuda()
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            what = f"sweep {k} {case['hp']} t{t} p{i}"
+            st, so = opt.state[p], run.states[i]
+            got = p.detach().float().cpu().numpy()
+            if fmt == "f32":
+                parity.assert_params(got, run.params[i], what, tol=2e-6)
+            else:
+                parity.assert_lowp_params(got, run.params[i], fmt, what, frac=2e-4)
+            for key in ("variance_q", "m_q"):
+                if key in so:
+                    a, b = state_np(st, key), np.asarray(so[key]).reshape(-1)
+                    if key == "m_q" and so.get("m_quant_type") in ("uf4", "d4"):
+                        a, b = parity.unpack_nibbles(a), parity.unpack_nibbles(b)
+                    parity.assert_codes(a, b, what + " " + key, al16=(b.dtype == np.uint16), zero_reserved=(key != "m_q"))
+            for key in ("variance", "m"):
+                if key in so:
+                    assert parity.rel_l2(state_np(st, key), so[key]) <= 1e-6, what + " " + key
+
+
+def _factored_configs(n, seed=4048):
+    rng = np.random.default_rng(seed)
+    out = []
+    for k in range(n):
+        rule = str(rng.choice(["adafactor", "adafactor_m", "came"]))
+        block = int(rng.choice([128, 256, 1024, 2048]))
+        hp = dict(block_size=block, m_block_size=int(rng.choice([64, 128, 256])), min_8bit_size=int(rng.choice([1, 4096])),
+                  v_quant_type=str(rng.choice(["al8", "al16", "fp32"])), weight_decay=float(rng.choice([0.0, 0.01])),
+                  enable_fira_for_adafactor=bool(rng.integers(0, 2)), maximize=bool(rng.integers(0, 4) == 0))
+        if rule == "adafactor":
+            hp.update(lag_norm=bool(rng.integers(0, 2)), d=float(rng.choice([0.0, 1.0])))
+        elif rule == "adafactor_m":
+            hp.update(beta1=0.9, relative_step=False, lr=1e-3, m_quant_type=str(rng.choice(["uf8", "uf4", "d8", "fp32"])),
+                      lag_norm=bool(rng.integers(0, 2)))
+        else:
+            hp.update(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=0.9999, relative_step=False, scale_parameter=False,
+                      scale_weight_decay=False, d=float(rng.choice([0.0, 1.0])), eps_came=1e-16, lr=1e-4,
+                      m_quant_type=str(rng.choice(["uf8", "uf4", "fp32"])), c_quant_type=str(rng.choice(["al8", "al16"])))
+        pd = str(rng.choice(["f32", "f32", "bf16"]))
+        gd = "bf16" if pd == "bf16" else str(rng.choice(["f32", "bf16"]))
+        if pd != "f32":
+            hp["stochastic_round_writeback"] = bool(rng.integers(0, 2))
+        shapes = []
+        for _ in range(3):
+            cols = int(rng.integers(1, 40)) * 8 if rng.integers(0, 3) else int(rng.integers(3, 300))
+            shapes.append((int(rng.integers(1, 200)), cols))
+        shapes.append((int(rng.integers(2, 40)), int(rng.choice([256, 512, 2048, 2304]))))
+        grad = dict(dist="rowscale", std=1e-3, zero_frac=float(rng.choice([0.0, 0.01])), dtype=gd)
+        out.append(dict(shapes=shapes, steps=3, seed=700 + k, grad=grad, hp=hp, param_dtype=pd))
+    return out
+
+
+FACTORED_CONFIGS = _factored_configs(16)
+SMALL_CODE_KEYS = ("row_var_q", "col_var_q", "conf_row_q", "conf_col_q", "m_q")
+
+
+@pytest.mark.parametrize("k", range(len(FACTORED_CONFIGS)))
+def test_factored_option_sweep(k, oracle):
+    """The same for the factored path; every step starts from the oracle's state (AL16 small states move by a
+    code when a mean differs in its last bit, which would otherwise accumulate over the steps)."""
+    from adafactor8bit import Adafactor8Bit, _engine
+    case = FACTORED_CONFIGS[k]
+    if case["hp"].get("m_quant_type") in ("d8", "d4"):
+        for bits in (8, 4):
+            oracle.set_dynamic_map(bits, _engine.dynamic_map(bits))
+    run = OracleRun(f"fsweep{k}", case=case)
+    fmt = case["param_dtype"]
+    dt = TORCH_DT[fmt]
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(dt).cuda()) for p in run.params0]
+    for p in params:
+        p.grad_dtype = None
+    opt = Adafactor8Bit(params, **case["hp"])
+    for t in range(1, case["steps"] + 1):
+        for p, g in zip(params, run.grads[t]):
+            if g.dtype == np.uint16:
+                p.grad = torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(p.shape).cuda()
+            else:
+                p.grad = torch.from_numpy(g.copy()).reshape(p.shape).cuda()
+        if t > 1:
+            for i, p in enumerate(params):
+                st = opt.state[p]
+                p.data.copy_(torch.from_numpy(run.params[i]).reshape(p.shape).to(dt))
+                for key, val in run.states[i].items():
+                    if isinstance(val, np.ndarray) and key in st and isinstance(st[key], torch.Tensor):
+                        src = torch.from_numpy(val.view(np.int16) if val.dtype == np.uint16 else val)
+                        st[key].copy_(src.reshape(st[key].shape))
+                for key in ("fira_prev_norm", "prev_update_norm", "lag_fira_scale"):
+                    if key in run.states[i] and key in st:
+                        st[key].fill_(float(run.states[i][key]))
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            what = f"factored sweep {k} {case['hp']} {tuple(p.shape)} t{t}"
+            st, so = opt.state[p], run.states[i]
+            got = p.detach().float().cpu().numpy()
+            if fmt == "f32":
+                parity.assert_params(got, run.params[i], what, tol=2e-6)
+            else:
+                parity.assert_lowp_params(got, run.params[i], fmt, what, frac=3e-4)
+            for key in SMALL_CODE_KEYS:
+                if key in so:
+                    a, b = state_np(st, key), np.asarray(so[key]).reshape(-1)
+                    if key == "m_q" and so.get("m_quant_type") in ("uf4", "d4"):
+                        a, b = parity.unpack_nibbles(a), parity.unpack_nibbles(b)
+                    s = parity.code_stats(a, b)
+                    al16 = b.dtype == np.uint16
+                    assert (key == "m_q" or s["zero_mismatch"] == 0) and s["max"] <= (parity.CODE_SLACK_AL16 if al16 else 1), (what, key, s)
+                    assert s["neq"] <= max(2, (3e-2 if al16 else 1e-4) * s["n"]), (what, key, s)
