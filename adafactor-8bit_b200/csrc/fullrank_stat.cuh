@@ -120,6 +120,10 @@ AF8_UNROLL_(AF8_STAT_UNROLL)
                 const int64_t off = base + s * FAST_MBLOCK + lane * 8;
                 float g[8];
                 stat_load_g<GradT>(grad, off, g);
+                if (L.negate_grad) {                       // maximize (optimizer.py:1973-1974)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) g[j] = -g[j];
+                }
                 const uint2 mw = __ldcs(reinterpret_cast<const uint2 *>(mq + off));
                 const uint2 vw = __ldcs(reinterpret_cast<const uint2 *>(vq + off));
                 const float2 mc2 = bc2(__ldg(m_scale + b * (FAST_VBLOCK / FAST_MBLOCK) + s) * 0.0078125f);
@@ -147,7 +151,8 @@ AF8_UNROLL_(AF8_STAT_UNROLL)
             for (int64_t i = lane; i < FAST_VBLOCK; i += 32) {
                 if (i >= rem) break;
                 const int64_t e = base + i;
-                const float gj = GradLoad<GradT>::load1(grad, e);
+                float gj = GradLoad<GradT>::load1(grad, e);
+                if (L.negate_grad) gj = -gj;
                 const float g2 = __fadd_rn(__fmul_rn(gj, gj), eps_g);
                 const uint32_t code = vq[e];
                 const float v_old = code ? ex2_approx(__fmaf_rn((float)code, a, c)) : 0.0f;

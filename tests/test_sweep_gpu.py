@@ -178,3 +178,72 @@ def test_factored_option_sweep(k, oracle):
                     al16 = b.dtype == np.uint16
                     assert (key == "m_q" or s["zero_mismatch"] == 0) and s["max"] <= (parity.CODE_SLACK_AL16 if al16 else 1), (what, key, s)
                     assert s["neq"] <= max(2, (3e-2 if al16 else 1e-4) * s["n"]), (what, key, s)
+
+
+def _apollo_configs(n, seed=777):
+    rng = np.random.default_rng(seed)
+    out = []
+    for k in range(n):
+        rank = int(rng.choice([4, 8, 16, 24, 32]))
+        hp = dict(cases._APOLLO, lr=1e-3, weight_decay=float(rng.choice([0.0, 0.01])), apollo_rank=rank,
+                  apollo_update_proj_gap=int(rng.choice([1, 2, 5])), m_quant_type=str(rng.choice(["uf8", "uf4", "d8"])),
+                  v_quant_type=str(rng.choice(["al8", "al16"])), block_size=int(rng.choice([256, 2048])),
+                  apollo_scale_type=str(rng.choice(["channel", "tensor"])), apollo_scale=float(rng.choice([1.0, 128.0])),
+                  apollo_scale_front=bool(rng.integers(0, 2)), enable_fira_for_apollo=bool(rng.integers(0, 2)),
+                  d=float(rng.choice([0.0, 1.0])), maximize=bool(rng.integers(0, 4) == 0), min_8bit_size=1)
+        pd = str(rng.choice(["f32", "f32", "bf16"]))
+        if pd != "f32":
+            hp["stochastic_round_writeback"] = bool(rng.integers(0, 2))
+        shapes = [(int(rng.integers(rank, 160)), int(rng.integers(rank // 8 + 1, 30)) * 8),      # rows or cols may be the larger one
+                  (int(rng.integers(rank, 80)), int(rng.integers(rank, 200))),
+                  (int(rng.integers(100, 3000)),)]
+        grad = dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="bf16")
+        out.append(dict(shapes=shapes, steps=4, seed=900 + k, grad=grad, hp=hp, param_dtype=pd))
+    return out
+
+
+APOLLO_CONFIGS = _apollo_configs(10)
+
+
+@pytest.mark.parametrize("k", range(len(APOLLO_CONFIGS)))
+def test_apollo_option_sweep(k, oracle):
+    """APOLLO with exact projections (so that the low-rank states are comparable code by code)."""
+    from adafactor8bit import Adafactor8Bit, _engine, optimizer as opt_mod
+    case = APOLLO_CONFIGS[k]
+    if case["hp"].get("m_quant_type") in ("d8", "d4"):
+        for bits in (8, 4):
+            oracle.set_dynamic_map(bits, _engine.dynamic_map(bits))
+    run = OracleRun(f"asweep{k}", case=case)
+    fmt = case["param_dtype"]
+    opt_mod.APOLLO_RNG_DEVICE = "cpu"
+    saved = _engine.EXACT_PROJECTION
+    _engine.EXACT_PROJECTION = True
+    try:
+        params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(TORCH_DT[fmt]).cuda()) for p in run.params0]
+        for p in params:
+            p.grad_dtype = None
+        opt = Adafactor8Bit(params, **case["hp"])
+        for t in range(1, case["steps"] + 1):
+            for p, g in zip(params, run.grads[t]):
+                p.grad = torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(p.shape).cuda()
+            opt.step()
+            run.step()
+            torch.cuda.synchronize()
+            for i, p in enumerate(params):
+                what = f"apollo sweep {k} {case['hp']} {tuple(p.shape)} t{t}"
+                got = p.detach().float().cpu().numpy()
+                if fmt == "f32":
+                    parity.assert_params(got, run.params[i], what, tol=2e-6)
+                else:
+                    parity.assert_lowp_params(got, run.params[i], fmt, what, frac=3e-4)
+                st, so = opt.state[p], run.states[i]
+                if "m_low_q" in so:
+                    a, b = state_np(st, "m_low_q"), np.asarray(so["m_low_q"]).reshape(-1)
+                    if so.get("m_quant_type") in ("uf4", "d4"):
+                        a, b = parity.unpack_nibbles(a), parity.unpack_nibbles(b)
+                    parity.assert_codes(a, b, what + " m_low_q", zero_reserved=False)
+                    b = np.asarray(so["v_low_q"]).reshape(-1)
+                    parity.assert_codes(state_np(st, "v_low_q"), b, what + " v_low_q", al16=(b.dtype == np.uint16))
+    finally:
+        opt_mod.APOLLO_RNG_DEVICE = None
+        _engine.EXACT_PROJECTION = saved
