@@ -247,3 +247,73 @@ def test_apollo_option_sweep(k, oracle):
     finally:
         opt_mod.APOLLO_RNG_DEVICE = None
         _engine.EXACT_PROJECTION = saved
+
+
+def _fast_configs(n, seed=31337):
+    """The AdamW UF8/AL8 layout of the specialised kernels (V block 2048, M block 256), everything else varied."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for k in range(n):
+        beta1 = float(rng.choice([0.9, 0.9, 0.3, 0.95]))             # 0.3: EMA weight 0.7, the second lerp form
+        beta2 = float(rng.choice([0.999, 0.99, 0.4]))
+        hp = dict(cases._ADAMW, beta1=beta1, beta2=beta2, lr=float(rng.choice([1e-3, 3e-4])),
+                  weight_decay=float(rng.choice([0.0, 0.01, 0.1])), block_size=2048, m_block_size=256,
+                  m_quant_type="uf8", v_quant_type="al8", min_8bit_size=int(rng.choice([1, 4096])),
+                  d=float(rng.choice([0.0, 0.0, 1.0])), enable_fira_for_adafactor=bool(rng.integers(0, 2)),
+                  lag_norm=bool(rng.integers(0, 3) == 0), maximize=bool(rng.integers(0, 2)),
+                  eps=(float(rng.choice([1e-8, 1e-6, 1e-12])), 1e-3),
+                  bias_correction=None if rng.integers(0, 3) else False,
+                  scale_weight_decay=bool(rng.integers(0, 2)))
+        pd = str(rng.choice(["f32", "f32", "bf16"]))
+        gd = "bf16" if pd == "bf16" else str(rng.choice(["f32", "bf16"]))
+        if pd != "f32":
+            hp["stochastic_round_writeback"] = bool(rng.integers(0, 2))
+        shapes = [(int(rng.integers(1, 40)), int(rng.integers(1, 700))), (int(rng.integers(4096, 20000)),),
+                  (2048 * int(rng.integers(1, 4)),), (int(rng.integers(1, 300)),)]
+        grad = dict(dist="rowscale", std=float(rng.choice([1e-3, 1e-5, 1.0])), zero_frac=float(rng.choice([0.0, 0.01, 0.3])), dtype=gd)
+        if rng.integers(0, 2):
+            grad.update(spike_step=2, spike_mult=100.0)
+        out.append(dict(shapes=shapes, steps=4, seed=1300 + k, grad=grad, hp=hp, param_dtype=pd))
+    return out
+
+
+FAST_CONFIGS = _fast_configs(32)
+
+
+@pytest.mark.parametrize("k", range(len(FAST_CONFIGS)))
+def test_fast_kernel_option_sweep(k, oracle):
+    from adafactor8bit import Adafactor8Bit
+    case = FAST_CONFIGS[k]
+    run = OracleRun(f"fast{k}", case=case)
+    fmt = case["param_dtype"]
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(TORCH_DT[fmt]).cuda()) for p in run.params0]
+    for p in params:
+        p.grad_dtype = None
+    opt = Adafactor8Bit(params, **case["hp"])
+    for t in range(1, case["steps"] + 1):
+        for p, g in zip(params, run.grads[t]):
+            if g.dtype == np.uint16:
+                p.grad = torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(p.shape).cuda()
+            else:
+                p.grad = torch.from_numpy(g.copy()).reshape(p.shape).cuda()
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            what = f"fast sweep {k} {case['hp']} {case['grad']} {tuple(p.shape)} t{t}"
+            st, so = opt.state[p], run.states[i]
+            got = p.detach().float().cpu().numpy()
+            if fmt == "f32":
+                parity.assert_params(got, run.params[i], what, tol=2e-6)
+            else:
+                parity.assert_lowp_params(got, run.params[i], fmt, what, frac=2e-4)
+            for key in ("variance_q", "m_q"):
+                if key in so:
+                    parity.assert_codes(state_np(st, key), np.asarray(so[key]).reshape(-1), what + " " + key, zero_reserved=(key != "m_q"))
+            for key in ("variance_scale", "variance_min_log", "m_scale"):
+                if key in so:
+                    parity.assert_ranges(state_np(st, key), so[key], what + " " + key, max_ulp=4)
+            for key in ("fira_prev_norm", "prev_update_norm"):
+                if key in so:
+                    a, b = float(st[key].item()), float(so[key])
+                    assert abs(a - b) <= 3e-6 * max(abs(b), 1e-30), (what, key, a, b)
