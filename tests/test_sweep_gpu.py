@@ -317,3 +317,76 @@ def test_fast_kernel_option_sweep(k, oracle):
                 if key in so:
                     a, b = float(st[key].item()), float(so[key])
                     assert abs(a - b) <= 3e-6 * max(abs(b), 1e-30), (what, key, a, b)
+
+
+def _migration_configs(n, seed=99):
+    """Random sequences of option edits between steps on a group with a matrix and a vector."""
+    rng = np.random.default_rng(seed)
+    edits = [("quantize", [True, False]), ("m_quant_type", ["uf8", "uf4", "d8", "fp32"]), ("v_quant_type", ["al8", "al16"]),
+             ("block_size", [256, 2048]), ("factored", [True, False]), ("beta3", [None, 0.9999]), ("beta1", [None, 0.9]),
+             ("min_8bit_size", [1, 4096]), ("weight_decay", [0.0, 0.01])]
+    out = []
+    for k in range(n):
+        hp = dict(beta1=0.9, beta2=0.999, beta2_decay=None, beta3=None if rng.integers(0, 2) else 0.9999,
+                  factored=bool(rng.integers(0, 2)), relative_step=False, scale_parameter=False, scale_weight_decay=False,
+                  d=1.0, eps=(1e-8, 1e-3), eps_came=1e-16, lr=1e-3, weight_decay=0.01, block_size=256, m_block_size=256,
+                  m_quant_type="uf8", v_quant_type="al8", min_8bit_size=4096)
+        if hp["beta3"] is not None:
+            hp["factored"] = True                          # the constructor refuses CAME without factoring
+        changes, now = {}, dict(hp)
+        for t in (2, 3, 4, 5):
+            if rng.integers(0, 4):
+                name, vals = edits[int(rng.integers(0, len(edits)))]
+                val = vals[int(rng.integers(0, len(vals)))]
+                trial = dict(now, **{name: val})
+                if trial["beta3"] is not None and (not trial["factored"] or trial["beta1"] is None):
+                    continue                               # keep the edited options a combination the reference accepts
+                now = trial
+                changes.setdefault(t, {})[name] = val
+        shapes = [(int(rng.integers(20, 90)), int(rng.integers(8, 40)) * 8), (int(rng.integers(4096, 6000)),), (300,)]
+        out.append(dict(shapes=shapes, steps=5, seed=1700 + k, grad=dict(dist="rowscale", std=1e-3, zero_frac=0.01, dtype="bf16"),
+                        hp=hp, changes=changes))
+    return out
+
+
+MIGRATION_CONFIGS = _migration_configs(12)
+
+
+@pytest.mark.parametrize("k", range(len(MIGRATION_CONFIGS)))
+def test_migration_sweep(k, oracle):
+    from adafactor8bit import Adafactor8Bit, _engine
+    case = MIGRATION_CONFIGS[k]
+    for bits in (8, 4):
+        oracle.set_dynamic_map(bits, _engine.dynamic_map(bits))
+    run = OracleRun(f"mig{k}", case=case)
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).cuda()) for p in run.params0]
+    for p in params:
+        p.grad_dtype = None
+    opt = Adafactor8Bit(params, **case["hp"])
+    for t in range(1, case["steps"] + 1):
+        for name, v in case["changes"].get(t, {}).items():
+            for group in opt.param_groups:
+                group[name] = v
+        for p, g in zip(params, run.grads[t]):
+            p.grad = torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(p.shape).cuda()
+        opt.step()
+        run.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            what = f"migration sweep {k} changes {case['changes']} {tuple(p.shape)} t{t}"
+            st, so = opt.state[p], run.states[i]
+            skip = ("fira_prev_norm", "prev_update_norm", "lag_fira_scale")
+            mine = {key for key, v in st.items() if isinstance(v, torch.Tensor) and key not in skip}
+            theirs = {key for key, v in so.items() if isinstance(v, np.ndarray)}
+            assert mine == theirs, (what, sorted(mine ^ theirs))
+            assert st["step"] == so["step"], what
+            parity.assert_params(p.detach().cpu().numpy(), run.params[i], what, tol=5e-6)
+            for key in theirs:
+                a, b = state_np(st, key), np.asarray(so[key]).reshape(-1)
+                if key.endswith("_q"):
+                    if key == "m_q" and so.get("m_quant_type") in ("uf4", "d4"):
+                        a, b = parity.unpack_nibbles(a), parity.unpack_nibbles(b)
+                    s = parity.code_stats(a, b)
+                    al16 = b.dtype == np.uint16
+                    assert (key == "m_q" or s["zero_mismatch"] == 0) and s["max"] <= (parity.CODE_SLACK_AL16 if al16 else 1), (what, key, s)
+                    assert s["neq"] <= max(2, (3e-2 if al16 else 1e-4) * s["n"]), (what, key, s)
