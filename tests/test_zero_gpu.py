@@ -17,12 +17,16 @@ SHAPES = [(300, 200), (4096,), (2048,), (128, 256), (64, 2048)]
 
 def _inputs(variant="f32"):
     """variant "f32": fp32 parameters; "bf16_sr": bf16 parameters written with stochastic rounding
-    (the seeds must be those of the unsharded run)."""
+    (the seeds must be those of the unsharded run); "adafactor" / "came": the factored paths."""
     sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
     import cases
     hp = dict(cases.CASES["adamw_fira_bf16"]["hp"])
     if variant == "bf16_sr":
         hp["stochastic_round_writeback"] = True
+    if variant == "adafactor":          # factored second moments, relative step, parameter scaling, clip
+        hp = dict(cases.CASES["adafactor_factored"]["hp"])
+    if variant == "came":
+        hp = dict(cases.CASES["came_al16"]["hp"])
     p0 = [cases.make_param(s, 7000 + i, dtype="bf16" if variant == "bf16_sr" else "f32") for i, s in enumerate(SHAPES)]
     grads = {t: [cases.make_grad(s, 7100 + i, t, cases.CASES["adamw_fira_bf16"]["grad"]) for i, s in enumerate(SHAPES)]
              for t in (1, 2, 3)}
@@ -66,7 +70,7 @@ def _worker(rank, world, port, out, variant):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("variant", ["f32", "bf16_sr"])
+@pytest.mark.parametrize("variant", ["f32", "bf16_sr", "adafactor", "came"])
 def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
     import torch.multiprocessing as mp
     sys.path.insert(0, os.path.join(ROOT, "adafactor-8bit_b200"))
