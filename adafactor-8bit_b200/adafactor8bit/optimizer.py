@@ -204,6 +204,7 @@ class Adafactor8Bit(Optimizer):
         self._apollo_seed_counter = 1          # optimizer.py:1460-1461
         self._sr_seed_counter = 1
         self._sr_seed_map = None
+        self._apollo_seed_map = None
         self._cfg_seen = {}       # id(param) -> option signature its state was last checked against
         self._plans = {}
         self._after_group = None               # optional hook(gi, group), called when a group's launches are enqueued
@@ -294,8 +295,10 @@ class Adafactor8Bit(Optimizer):
             if beta1 is not None:
                 _new_m_state(state, numel, m_block, m_fmt, dev, p.shape)
         elif group.get("apollo_rank", 0) > 0 and grad.dim() >= 2:
-            seed = self._apollo_seed_counter
-            self._apollo_seed_counter += 1
+            seed = self._apollo_seed_map.get(id(p)) if self._apollo_seed_map is not None else None
+            if seed is None:                                  # (a sharding wrapper presets the seeds of the unsharded run)
+                seed = self._apollo_seed_counter
+                self._apollo_seed_counter += 1
             gap = group.get("apollo_update_proj_gap", 200)
             state.update(apollo_seed=seed, apollo_rank=group["apollo_rank"],
                          apollo_factorize=group.get("apollo_factorize", False), beta3=beta3,

@@ -133,6 +133,18 @@ class ShardedAdafactor8Bit:
                         nxt += 1
             self.inner._sr_seed_map = seeds
             self.inner._sr_seed_counter = nxt
+        if self.inner is not None and hasattr(self.inner, "_apollo_seed_map"):
+            # the same for the projection seeds of APOLLO (one per tensor of two or more dimensions in a group
+            # with a rank, in parameter order: optimizer.py:1726-1728)
+            seeds, nxt = {}, 1
+            for g in groups:
+                rank = g.get("apollo_rank", kwargs.get("apollo_rank", 0))
+                for p in g["params"]:
+                    if rank and rank > 0 and p.dim() >= 2:
+                        seeds[id(p)] = nxt
+                        nxt += 1
+            self.inner._apollo_seed_map = seeds
+            self.inner._apollo_seed_counter = nxt
         self.gather_stream = None
 
     @property

@@ -27,6 +27,8 @@ def _inputs(variant="f32"):
         hp = dict(cases.CASES["adafactor_factored"]["hp"])
     if variant == "came":
         hp = dict(cases.CASES["came_al16"]["hp"])
+    if variant == "apollo":             # projection seeds must be those of the unsharded run
+        hp = dict(cases.CASES["apollo_r32"]["hp"], apollo_rank=16)
     p0 = [cases.make_param(s, 7000 + i, dtype="bf16" if variant == "bf16_sr" else "f32") for i, s in enumerate(SHAPES)]
     grads = {t: [cases.make_grad(s, 7100 + i, t, cases.CASES["adamw_fira_bf16"]["grad"]) for i, s in enumerate(SHAPES)]
              for t in (1, 2, 3)}
@@ -70,7 +72,7 @@ def _worker(rank, world, port, out, variant):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("variant", ["f32", "bf16_sr", "adafactor", "came"])
+@pytest.mark.parametrize("variant", ["f32", "bf16_sr", "adafactor", "came", "apollo"])
 def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
     import torch.multiprocessing as mp
     sys.path.insert(0, os.path.join(ROOT, "adafactor-8bit_b200"))
