@@ -390,3 +390,53 @@ def test_migration_sweep(k, oracle):
                     al16 = b.dtype == np.uint16
                     assert (key == "m_q" or s["zero_mismatch"] == 0) and s["max"] <= (parity.CODE_SLACK_AL16 if al16 else 1), (what, key, s)
                     assert s["neq"] <= max(2, (3e-2 if al16 else 1e-4) * s["n"]), (what, key, s)
+
+
+CHECKPOINT_CASES = ([("fast", k) for k in range(0, 32, 4)] + [("factored", k) for k in range(0, 16, 3)]
+                    + [("apollo", k) for k in range(0, 10, 3)] + [("fullrank", k) for k in range(0, 24, 5)])
+
+
+@pytest.mark.parametrize("family,k", CHECKPOINT_CASES)
+def test_checkpoint_continuity_sweep(family, k):
+    """Two steps, state_dict, a fresh optimizer on copies of the parameters, load_state_dict, one more step on
+    both: the continued run equals the uninterrupted one bit for bit (every state entry a step needs - limiter and
+    lag scalars, rounding seeds, projection seeds and matrices, step counts - travels through the checkpoint)."""
+    import copy
+    from adafactor8bit import Adafactor8Bit
+    case = {"fast": FAST_CONFIGS, "factored": FACTORED_CONFIGS, "apollo": APOLLO_CONFIGS, "fullrank": CONFIGS}[family][k]
+    params0, grads = cases.case_inputs(case)
+    dt = TORCH_DT[case.get("param_dtype", "f32")]
+
+    def grad_of(g, p):
+        if g.dtype == np.uint16:
+            return torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(p.shape).cuda()
+        return torch.from_numpy(g.copy()).reshape(p.shape).cuda()
+
+    a = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(dt).cuda()) for p in params0]
+    for p in a:
+        p.grad_dtype = None
+    oa = Adafactor8Bit(a, **case["hp"])
+    for t in (1, 2):
+        for p, g in zip(a, grads[t]):
+            p.grad = grad_of(g, p)
+        oa.step()
+    sd = copy.deepcopy(oa.state_dict())
+    b = [torch.nn.Parameter(p.detach().clone()) for p in a]
+    for p in b:
+        p.grad_dtype = None
+    ob = Adafactor8Bit(b, **case["hp"])
+    ob.load_state_dict(sd)
+    for opt, ps in ((oa, a), (ob, b)):
+        for p, g in zip(ps, grads[3]):
+            p.grad = grad_of(g, p)
+        opt.step()
+    torch.cuda.synchronize()
+    for i, (p, q) in enumerate(zip(a, b)):
+        assert torch.equal(p.detach(), q.detach()), f"{family} {k} {case['hp']} param {i} {tuple(p.shape)}"
+        sa, sb = oa.state[p], ob.state[q]
+        assert sorted(sa) == sorted(sb), (family, k, i, sorted(set(sa) ^ set(sb)))
+        for key, v in sa.items():
+            if isinstance(v, torch.Tensor):
+                assert torch.equal(v, sb[key]), (family, k, i, key)
+            elif key not in ("variance_shape", "row_var_shape", "col_var_shape", "conf_row_shape", "conf_col_shape", "v_low_shape"):
+                assert v == sb[key], (family, k, i, key, v, sb[key])
