@@ -53,12 +53,16 @@ class Tiny(nn.Module):
 @pytest.mark.parametrize("preset,extra", [
     ("adamw", {}), ("rmsprop", {}), ("sgd", dict(lr=5e-2)), ("adafactor", {}), ("came", {}),
     ("apollo", dict(apollo_rank=16)), ("adamw", dict(grouping="G0", m_quant_type="uf4", v_quant_type="al16")),
+    ("adamw", dict(bf16=True, stochastic_round_writeback=True)), ("apollo", dict(bf16=True, apollo_rank=16, stochastic_round_writeback=True)),
+    ("came", dict(bf16=True)), ("adamw", dict(enable_fira_for_adafactor=True, lag_norm=True)),
 ])
 def test_preset_trains_on_gpu(preset, extra):
     from adafactor8bit import Adafactor8Bit, build_param_groups
     torch.manual_seed(0)
     model = Tiny().cuda()
     extra = dict(extra)
+    if extra.pop("bf16", False):
+        model = model.bfloat16()
     kw = {k: extra.pop(k) for k in list(extra) if k in ("grouping", "apollo_rank")}
     lr = extra.pop("lr", 2e-3)
     groups = build_param_groups(model, preset, **kw)
