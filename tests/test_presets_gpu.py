@@ -55,6 +55,7 @@ class Tiny(nn.Module):
     ("apollo", dict(apollo_rank=16)), ("adamw", dict(grouping="G0", m_quant_type="uf4", v_quant_type="al16")),
     ("adamw", dict(bf16=True, stochastic_round_writeback=True)), ("apollo", dict(bf16=True, apollo_rank=16, stochastic_round_writeback=True)),
     ("came", dict(bf16=True)), ("adamw", dict(enable_fira_for_adafactor=True, lag_norm=True)),
+    ("adamw", dict(f16=True, stochastic_round_writeback=True)), ("adafactor", dict(f16=True)), ("came", dict(f16=True)),
 ])
 def test_preset_trains_on_gpu(preset, extra):
     from adafactor8bit import Adafactor8Bit, build_param_groups
@@ -63,6 +64,8 @@ def test_preset_trains_on_gpu(preset, extra):
     extra = dict(extra)
     if extra.pop("bf16", False):
         model = model.bfloat16()
+    if extra.pop("f16", False):
+        model = model.half()
     kw = {k: extra.pop(k) for k in list(extra) if k in ("grouping", "apollo_rank")}
     lr = extra.pop("lr", 2e-3)
     groups = build_param_groups(model, preset, **kw)
