@@ -440,3 +440,41 @@ def test_checkpoint_continuity_sweep(family, k):
                 assert torch.equal(v, sb[key]), (family, k, i, key)
             elif key not in ("variance_shape", "row_var_shape", "col_var_shape", "conf_row_shape", "conf_col_shape", "v_low_shape"):
                 assert v == sb[key], (family, k, i, key, v, sb[key])
+
+
+@pytest.mark.parametrize("family", ["fast", "factored"])
+def test_parameters_without_gradient_are_skipped(family, oracle):
+    """Parameters whose .grad is None at a step keep their state and step count (optimizer.py:1637): the launch
+    plan is rebuilt for the tensors that do have gradients, and their per-tensor step numbers drift apart."""
+    from adafactor8bit import Adafactor8Bit
+    plain = next(c for c in FACTORED_CONFIGS if not c["hp"].get("stochastic_round_writeback") and not c["hp"].get("lag_norm"))
+    case = dict(FAST_CONFIGS[0] if family == "fast" else plain, steps=5)
+    case = dict(case, grad=dict(case["grad"]), hp=dict(case["hp"]))
+    run = OracleRun(f"skip_{family}", case=case)
+    dt = TORCH_DT[case.get("param_dtype", "f32")]
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(dt).cuda()) for p in run.params0]
+    for p in params:
+        p.grad_dtype = None
+    opt = Adafactor8Bit(params, **case["hp"])
+    n = len(params)
+    active = {1: range(n), 2: [0, 2], 3: [1], 4: range(n), 5: [n - 1]}
+    for t in range(1, 6):
+        for i, p in enumerate(params):
+            p.grad = None
+        for i in active[t]:
+            g = run.grads[t][i]
+            p = params[i]
+            p.grad = (torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16) if g.dtype == np.uint16
+                      else torch.from_numpy(g.copy())).reshape(p.shape).cuda()
+            run.step_param(i, run.params[i], g, run.states[i])
+        opt.step()
+        torch.cuda.synchronize()
+        for i, p in enumerate(params):
+            what = f"{family} t{t} p{i}"
+            if i in active[t] or t > 1:
+                assert opt.state[p]["step"] == run.states[i]["step"], what
+            got = p.detach().float().cpu().numpy()
+            if dt == torch.float32:
+                parity.assert_params(got, run.params[i], what, tol=2e-6)
+            else:
+                parity.assert_lowp_params(got, run.params[i], case["param_dtype"], what, frac=3e-4)
