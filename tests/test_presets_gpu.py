@@ -89,3 +89,30 @@ def test_preset_trains_on_gpu(preset, extra):
         assert any("row_var_q" in st or "row_var" in st for st in states)
     if preset == "came":
         assert any("conf_row_q" in st or "conf_row" in st for st in states)
+
+
+def test_lr_scheduler_and_tensor_lr():
+    """The learning rate is read from the group at every step: a torch scheduler, a manual edit and a 0-d tensor
+    give the same run."""
+    from adafactor8bit import Adafactor8Bit
+    torch.manual_seed(1)
+    w0 = torch.randn(96, 160, device="cuda") * 0.02
+    grads = [torch.randn(96, 160, device="cuda") * 1e-3 for _ in range(4)]
+    hp = dict(beta1=0.9, beta2=0.999, beta2_decay=None, factored=False, relative_step=False, scale_parameter=False,
+              scale_weight_decay=False, d=0.0, eps=(1e-8, 1e-3), weight_decay=0.01, min_8bit_size=1)
+    outs = []
+    for mode in ("scheduler", "manual", "tensor"):
+        p = torch.nn.Parameter(w0.clone())
+        opt = Adafactor8Bit([p], lr=1e-3, **hp)
+        sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda e: 0.5 ** e) if mode == "scheduler" else None
+        for t, g in enumerate(grads):
+            if mode == "manual":
+                opt.param_groups[0]["lr"] = 1e-3 * 0.5 ** t
+            if mode == "tensor":
+                opt.param_groups[0]["lr"] = torch.tensor(1e-3 * 0.5 ** t, device="cuda", dtype=torch.float64)
+            p.grad = g.clone()
+            opt.step()
+            if sched is not None:
+                sched.step()
+        outs.append(p.detach().clone())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
