@@ -608,7 +608,7 @@ class Adafactor8Bit(Optimizer):
         for gi, group in enumerate(self.param_groups):
             if grad_ready is not None and grad_ready[gi] is not None:
                 torch.cuda.current_stream().wait_event(grad_ready[gi])
-            entries = []
+            entries, copy_back = [], []
             for p in group["params"]:
                 if p.grad is None:
                     continue
@@ -630,9 +630,15 @@ class Adafactor8Bit(Optimizer):
                 if p.numel() == 0:              # an empty parameter has a state and a step count, nothing to launch
                     state["step"] = state.get("step", 0) + 1
                     continue
-                entries.append((p, p.grad, state))
+                work = p
+                if not p.is_contiguous():       # stepped on a contiguous copy, copied back (optimizer.py:2000-2005, 3081-3084)
+                    work = p.detach().contiguous()
+                    copy_back.append((p, work))
+                entries.append((work, p.grad, state))
             if entries:
                 self._run_group(gi, group, entries)
+                for p, work in copy_back:
+                    p.copy_(work)
             if self._after_group is not None:
                 self._after_group(gi, group)
         return loss

@@ -116,3 +116,24 @@ def test_lr_scheduler_and_tensor_lr():
                 sched.step()
         outs.append(p.detach().clone())
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+@pytest.mark.parametrize("hp", [dict(beta1=0.9, beta2=0.999, beta2_decay=None, factored=False, relative_step=False,
+                                     scale_parameter=False, d=0.0, eps=(1e-8, 1e-3), lr=1e-3),
+                                dict()], ids=["adamw", "adafactor"])
+def test_non_contiguous_parameter(hp):
+    """A transposed (non-contiguous) parameter is stepped like its contiguous twin."""
+    from adafactor8bit import Adafactor8Bit
+    torch.manual_seed(2)
+    base = torch.randn(160, 96, device="cuda") * 0.02
+    a = torch.nn.Parameter(base.t())                      # shape (96, 160), strides (1, 96)
+    b = torch.nn.Parameter(base.t().contiguous())
+    assert not a.is_contiguous() and b.is_contiguous()
+    oa, ob = Adafactor8Bit([a], min_8bit_size=1, **hp), Adafactor8Bit([b], min_8bit_size=1, **hp)
+    for t in range(3):
+        g = torch.randn(160, 96, device="cuda") * 1e-3
+        a.grad, b.grad = g.t(), g.t().contiguous()
+        oa.step()
+        ob.step()
+    torch.cuda.synchronize()
+    assert not a.is_contiguous() and torch.equal(a.detach(), b.detach())
