@@ -156,6 +156,15 @@ SCENARIOS += [
     ("err-policy-route", "llama", dict(preset="adamw", policy={"mapping": {"attention": {"lr": 1.0}}})),
     ("err-policy-unknown-preset", "llama", dict(preset="adamw", policy={"mapping": {"other": {"preset": "nope"}}})),
     ("err-policy-rank", "llama", dict(preset="adamw", policy={"mapping": {"one_d": {"apollo_rank": 4}}})),
+    ("err-policy-cycle3", "llama", dict(preset="adamw", policy={"presets": {"a": {"preset": "b"}, "b": {"preset": "c"}, "c": {"preset": "a"}}})),
+    ("err-policy-parent-type", "llama", dict(preset="adamw", policy={"presets": {"a": {"preset": 5}}})),
+    ("err-policy-parent-list", "llama", dict(preset="adamw", policy={"presets": {"a": {"preset": ["x"]}}})),
+    ("err-policy-empty-name", "llama", dict(preset="adamw", policy={"presets": {"": {"preset": "adamw"}}})),
+    ("err-policy-entry-type", "llama", dict(preset="adamw", policy={"mapping": {"other": 3}})),
+    ("err-policy-definition-type", "llama", dict(preset="adamw", policy={"presets": {"a": 3}})),
+    ("err-policy-unknown-parent", "llama", dict(preset="adamw", policy={"presets": {"a": {"preset": "zzz"}}})),
+    ("policy-chain", "llama", dict(preset="adamw", policy={"presets": {"a": {"preset": "adamw", "lr": 1e-4}, "b": {"preset": "a", "beta1": 0.8}},
+                                                            "mapping": {"other": {"preset": "b", "weight_decay": 0.1}}})),
     ("err-model", None, dict(preset="adamw")),
 ]
 
