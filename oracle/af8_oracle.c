@@ -991,6 +991,12 @@ typedef struct {
  * (2906-2953) states, update_low (2959), scaling factor (2961-2966), global norm
  * (2973-2988), Fira (2990-2996), write-back for fp32 parameters (3073-3079).
  * pt is proj_matrix_T: (cols, rank) when rows >= cols ("right"), else (rank, rows). */
+/* Test hook: the next af8o_apollo_step takes this projected gradient (rows x rank or rank x cols
+ * floats) instead of computing G*Pt, so that everything after the contraction can be compared
+ * with a device run that started from the same projected values.  Cleared by that call. */
+static const float *g_low_override = NULL;
+AF8O_API void af8o_apollo_override_g_low(const float *g_low) { g_low_override = g_low; }
+
 AF8O_API int af8o_apollo_step(const af8o_apollo_cfg *c, float *p, const void *grad, const float *pt,
                               void *v_q, float *v_scale, float *v_min_log, float *v_f32,
                               uint8_t *m_q, float *m_scale, float *m_f32, const float *map,
@@ -1015,23 +1021,44 @@ AF8O_API int af8o_apollo_step(const af8o_apollo_cfg *c, float *p, const void *gr
         float x = load_grad(grad, c->grad_dtype, i, c->negate_grad);
         G[i] = isfinite(x) ? x : 0.0f;
     }
-    /* optimizer.py:2678-2681, binary64 accumulation */
-    if (right) {
-#pragma omp parallel for schedule(static)
-        for (int64_t i = 0; i < R; ++i)
-            for (int64_t k = 0; k < r; ++k) {
-                double a = 0.0;
-                for (int64_t j = 0; j < C; ++j) a += (double)G[i * C + j] * (double)pt[j * r + k];
-                gl[i * r + k] = (float)a;
+    /* optimizer.py:2678-2681, binary64 accumulation.  Each output element sums its products in
+     * ascending order of the contracted index; the loops are arranged so that the innermost one
+     * walks memory contiguously. */
+    if (g_low_override) {
+        memcpy(gl, g_low_override, (size_t)nl * sizeof(float));
+        g_low_override = NULL;
+    } else if (right) {
+#pragma omp parallel
+        {
+            double *acc = (double *)malloc((size_t)r * sizeof(double));
+#pragma omp for schedule(static)
+            for (int64_t i = 0; i < R; ++i) {
+                for (int64_t k = 0; k < r; ++k) acc[k] = 0.0;
+                for (int64_t j = 0; j < C; ++j) {
+                    const double gij = (double)G[i * C + j];
+                    const float *prow = pt + j * r;
+                    for (int64_t k = 0; k < r; ++k) acc[k] += gij * (double)prow[k];
+                }
+                for (int64_t k = 0; k < r; ++k) gl[i * r + k] = (float)acc[k];
             }
+            free(acc);
+        }
     } else {
-#pragma omp parallel for schedule(static)
-        for (int64_t k = 0; k < r; ++k)
-            for (int64_t j = 0; j < C; ++j) {
-                double a = 0.0;
-                for (int64_t i = 0; i < R; ++i) a += (double)pt[k * R + i] * (double)G[i * C + j];
-                gl[k * C + j] = (float)a;
+#pragma omp parallel
+        {
+            double *acc = (double *)malloc((size_t)C * sizeof(double));
+#pragma omp for schedule(static)
+            for (int64_t k = 0; k < r; ++k) {
+                for (int64_t j = 0; j < C; ++j) acc[j] = 0.0;
+                for (int64_t i = 0; i < R; ++i) {
+                    const double pki = (double)pt[k * R + i];
+                    const float *grow = G + i * C;
+                    for (int64_t j = 0; j < C; ++j) acc[j] += pki * (double)grow[j];
+                }
+                for (int64_t j = 0; j < C; ++j) gl[k * C + j] = (float)acc[j];
             }
+            free(acc);
+        }
     }
     /* low-rank second moment */
     if (c->first_step) {                                     /* optimizer.py:2770-2779 */
@@ -1064,23 +1091,43 @@ AF8O_API int af8o_apollo_step(const af8o_apollo_cfg *c, float *p, const void *gr
     double total = 0.0;
     float norm_unscaled = 0.0f;
     if (!c->scale_tensor) {
-        for (int64_t ch = 0; ch < nch; ++ch) {
-            double nu = 0.0, ng = 0.0, nG = 0.0;
-            if (right) {
-                for (int64_t k = 0; k < r; ++k) { nu += (double)m[ch * r + k] * m[ch * r + k]; ng += (double)gl[ch * r + k] * gl[ch * r + k]; }
-                for (int64_t j = 0; j < C; ++j) nG += (double)G[ch * C + j] * G[ch * C + j];
-            } else {
-                for (int64_t k = 0; k < r; ++k) { nu += (double)m[k * C + ch] * m[k * C + ch]; ng += (double)gl[k * C + ch] * gl[k * C + ch]; }
-                for (int64_t i = 0; i < R; ++i) nG += (double)G[i * C + ch] * G[i * C + ch];
+        /* per-channel sums in binary64, each in ascending index order; channels are independent,
+         * the final sum over channels runs in channel order */
+        double *nu = (double *)calloc((size_t)nch * 3, sizeof(double));
+        if (!nu) return 2;
+        double *ng = nu + nch, *nG = ng + nch;
+        if (right) {
+#pragma omp parallel for schedule(static)
+            for (int64_t ch = 0; ch < nch; ++ch) {
+                double a = 0.0, b = 0.0, cc = 0.0;
+                for (int64_t k = 0; k < r; ++k) { a += (double)m[ch * r + k] * m[ch * r + k]; b += (double)gl[ch * r + k] * gl[ch * r + k]; }
+                for (int64_t j = 0; j < C; ++j) cc += (double)G[ch * C + j] * G[ch * C + j];
+                nu[ch] = a; ng[ch] = b; nG[ch] = cc;
             }
-            float s = (float)sqrt(nu) / ((float)sqrt(ng) + 1e-8f);
+        } else {
+            const int64_t strip = 512;                        /* columns per task: rows are walked contiguously */
+#pragma omp parallel for schedule(static)
+            for (int64_t c0 = 0; c0 < nch; c0 += strip) {
+                const int64_t c1 = c0 + strip < nch ? c0 + strip : nch;
+                for (int64_t k = 0; k < r; ++k)
+                    for (int64_t ch = c0; ch < c1; ++ch) {
+                        nu[ch] += (double)m[k * C + ch] * m[k * C + ch];
+                        ng[ch] += (double)gl[k * C + ch] * gl[k * C + ch];
+                    }
+                for (int64_t i = 0; i < R; ++i)
+                    for (int64_t ch = c0; ch < c1; ++ch) nG[ch] += (double)G[i * C + ch] * G[i * C + ch];
+            }
+        }
+        for (int64_t ch = 0; ch < nch; ++ch) {
+            float s = (float)sqrt(nu[ch]) / ((float)sqrt(ng[ch]) + 1e-8f);
             if (c->scale_front) s = s * c->sqrt_scale;        /* optimizer.py:2969-2971 */
             sf[ch] = s;
-            float nGf = (float)sqrt(nG);
+            float nGf = (float)sqrt(nG[ch]);
             float nG2 = nGf * nGf;                            /* vector_norm(...).square() */
             float s2 = s * s;
             total += (double)(nG2 * s2);
         }
+        free(nu);
         norm_unscaled = sqrtf((float)total);                  /* optimizer.py:2982 */
     } else {
         float s = norm2_f64(m, nl) / (norm2_f64(gl, nl) + 1e-8f);

@@ -643,9 +643,11 @@ def apollo_projection(state, shape, step, rank, gap):
     return pt
 
 
-def apollo_step(p, g, state, hp):
+def apollo_step(p, g, state, hp, g_low=None):
     """_update_param_apollo (optimizer.py:2587-3084) for 2-D fp32 parameters, without
-    factorisation and without CAME."""
+    factorisation and without CAME.  g_low: a projected gradient (float32, rows x rank or
+    rank x cols) to use instead of computing G @ Pt: everything after the contraction then
+    starts from the same values as a device run whose projection was copied here."""
     assert p.dtype == f32 and p.ndim == 2 and p.flags.c_contiguous
     lib_ = lib()
     if not hasattr(lib_, "_apollo_ready"):
@@ -717,6 +719,11 @@ def apollo_step(p, g, state, hp):
     has_prev = c_i(1 if "scaled_grad_norm_prev" in state else 0)
     prev = c_f(float(state.get("scaled_grad_norm_prev", 0.0)))
     norm = c_f(-1.0)
+    if g_low is not None:
+        g_low = np.ascontiguousarray(g_low, dtype=f32).reshape(-1)
+        assert g_low.size == nl
+        lib_.af8o_apollo_override_g_low.argtypes = [c_p]
+        lib_.af8o_apollo_override_g_low(_ptr(g_low))
     with param_format(hp, state, state["step"]):
         rc = lib_.af8o_apollo_step(
             ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), _ptr(pt),
