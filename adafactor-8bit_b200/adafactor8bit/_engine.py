@@ -30,6 +30,52 @@ def _ptr(t):
     return 0 if t is None else t.data_ptr()
 
 
+class Piece:
+    """Describes a launch-table entry that holds only part of a tensor: a run of flat elements
+    (full-rank path) or a run of rows (factored path) of a tensor whose other parts sit in other
+    launch tables, possibly on other GPUs (the sharded optimizer).  Everything that the
+    reference derives from the whole tensor -- its element count in the clip and RMS divisors, its
+    norms, its row and column statistics -- then comes from `full_*` and, for the sums, from the
+    exchange slots.
+
+    full_numel, full_rows: size of the whole tensor.
+    elem0: flat index, in the whole tensor, of the entry's first element (origin of the stochastic
+           rounding counters); row0: its first row (factored path).
+    slots: None when the entry holds the whole tensor.  Otherwise one float64 tensor per exchange
+           point of the plan's pass sequence: layout [8 scalars | full_rows row sums (padded to a
+           multiple of 4) | column sums].  The plan ADDS its local sums there; between two passes
+           the caller all-reduces the slots, after which they hold the whole tensor's sums.
+    copy:  optional bf16 tensor of the entry's size that receives the updated parameter rounded to
+           nearest (the compute copy of a mixed-precision run)."""
+    __slots__ = ("full_numel", "full_rows", "elem0", "row0", "slots", "copy")
+
+    def __init__(self, full_numel, full_rows=0, elem0=0, row0=0, slots=None, copy=None):
+        self.full_numel, self.full_rows, self.elem0, self.row0 = int(full_numel), int(full_rows), int(elem0), int(row0)
+        self.slots, self.copy = slots, copy
+
+
+def fullrank_exchanges(scale, d, fira, momentum_only, lag):
+    """Number of exchange points of FullrankPlan.stages for these options."""
+    need_stat = bool(fira) or d > 0
+    if not momentum_only:
+        if lag and need_stat:
+            return 0
+        return 1 if (scale or need_stat) else 0
+    return (1 if (scale or d > 0) else 0) + (1 if fira else 0)
+
+
+def factored_exchanges(came, d, fira, lag):
+    """Number of exchange points of FactoredPlan.stages for these options."""
+    if came:
+        return 3 + (1 if fira else 0)
+    return 1 + (1 if ((fira or d > 0) and not lag) else 0)
+
+
+def _add_to_slot(slot, k, values):
+    """slot[k] += sum(values) in binary64."""
+    slot[k].add_(values.sum(dtype=torch.float64))
+
+
 def dynamic_map(total_bits):
     """The signed dynamic-map codebook of the d8 / d4 momentum formats, built
     with the same torch float32 operations as the reference so that both produce
@@ -146,15 +192,20 @@ class FullrankKey(tuple):
 
 class FullrankPlan:
     """One multi-tensor launch group of the full-rank path: all tensors share
-    the kernel configuration `key`; per-tensor scalars live in the table."""
+    the kernel configuration `key`; per-tensor scalars live in the table.
+
+    pieces: optional list with a Piece (or None) per entry, for entries that are parts of larger
+    tensors."""
 
     def __init__(self, device, grad_dtype, v_fmt, m_fmt, block, m_block, use_adam_denom,
-                 momentum_only, negate, params, states, stochastic_round=False):
+                 momentum_only, negate, params, states, stochastic_round=False, pieces=None):
         self.device = torch.device(device)
         self.params = list(params)
         self.states = list(states)
         n = len(self.params)
         self.n = n
+        self.pieces = list(pieces) if pieces is not None else [None] * n
+        self.cut = [i for i, pc in enumerate(self.pieces) if pc is not None and pc.slots is not None]
         self.cfg = N.FullrankCfg()
         pdt = self.params[0].dtype
         if pdt not in _GRAD_DT or any(p.dtype != pdt for p in self.params):
@@ -176,6 +227,9 @@ class FullrankPlan:
         if m_fmt in ("d8", "d4"):
             ensure_qmap(self.device)
         self.numel = np.array([p.numel() for p in self.params], dtype=np.int64)
+        # element count of the tensor an entry belongs to: what the clip and RMS divisors use
+        self.full_numel = np.array([pc.full_numel if pc is not None else p.numel()
+                                    for p, pc in zip(self.params, self.pieces)], dtype=np.int64)
         self.nblocks = (self.numel + block - 1) // block
         self.first_block = np.concatenate([[0], np.cumsum(self.nblocks)[:-1]]).astype(np.int64)
         self.total_blocks = int(self.nblocks.sum())
@@ -192,14 +246,26 @@ class FullrankPlan:
         self.d_chunks = None
         self.h_lag = self.d_lag = None
         self._static = None
+        self._ptr_sig = None
         self._alpha_on_device = False
         for p in self.params:
             if not p.is_contiguous():
                 raise RuntimeError("parameters must be contiguous")
 
     # -- table ---------------------------------------------------------------
+    _STATE_KEYS = ("variance_q", "variance_scale", "variance_min_log", "variance", "m_q", "m_scale", "m")
+
+    def _pointer_signature(self):
+        """Addresses of everything the static part of the table points at.  A parameter whose
+        storage was replaced (p.data = ..., module.to(...)) or a state tensor that user code
+        swapped keeps its Python identity, so the cached table is checked against the addresses."""
+        sig = [p.data_ptr() for p in self.params]
+        for st in self.states:
+            sig += [id(st.get(k)) for k in self._STATE_KEYS]      # a state entry changes by being replaced
+        return sig
+
     def _static_fields(self):
-        """Pointers and sizes that only change when a state tensor is replaced."""
+        """Pointers and sizes that only change when a parameter's or a state's storage is replaced."""
         t = np.zeros(self.n, dtype=N.FULLRANK_TENSOR)
         for i, (p, st) in enumerate(zip(self.params, self.states)):
             t["param"][i] = p.data_ptr()
@@ -210,6 +276,11 @@ class FullrankPlan:
             t["m_q"][i] = _ptr(st.get("m_q"))
             t["m_scale"][i] = _ptr(st.get("m_scale"))
             t["m_f32"][i] = _ptr(st.get("m"))
+            pc = self.pieces[i]
+            if pc is not None and pc.copy is not None:
+                if pc.copy.numel() != p.numel() or pc.copy.dtype != torch.bfloat16:
+                    raise RuntimeError("the compute copy of a parameter must be a bf16 tensor of its size")
+                t["param_copy"][i] = pc.copy.data_ptr()
         t["numel"] = self.numel
         t["first_block"] = self.first_block
         return t
@@ -220,8 +291,10 @@ class FullrankPlan:
     def fill_table(self, grads, scalars):
         """scalars: dict of per-tensor float32 arrays (or python floats) named as
         the table fields."""
-        if self._static is None:
+        sig = self._pointer_signature()
+        if self._static is None or sig != self._ptr_sig:
             self._static = self._static_fields()
+            self._ptr_sig = sig
         buf = self.h_table.next()
         table = buf.numpy()[: self.n * N.FULLRANK_TENSOR.itemsize].view(N.FULLRANK_TENSOR)
         table[:] = self._static
@@ -260,11 +333,22 @@ class FullrankPlan:
         if host_buf is not None:
             self.h_table.mark(stream)
 
-    def _finalize(self, table, pre_div_mode, d, fira, fira_margin, stream):
+    def _sums_to_slots(self, x, k, partials, first, count):
+        """Add the local sum of every cut entry's partial sums into scalar k of its slot of exchange x."""
+        for i in self.cut:
+            a = int(first[i])
+            _add_to_slot(self.pieces[i].slots[x], k, partials[a:a + int(count[i])])
+
+    def _finalize(self, table, pre_div_mode, d, fira, fira_margin, stream, x=None, k=1):
+        """x, k: exchange index and scalar index where the whole sums of the cut entries are."""
         buf = self.h_norm.next()
         nt = buf.numpy()[: self.n * N.NORM_TENSOR.itemsize].view(N.NORM_TENSOR)
         nt["first_block"] = self.first_block
         nt["n_blocks"] = self.nblocks
+        if x is not None:
+            for i in self.cut:
+                nt["n_blocks"][i] = -1
+                nt["first_block"][i] = self.pieces[i].slots[x].data_ptr() + 8 * k
         nt["pre_div_mode"] = pre_div_mode
         nt["partials_f64"] = 0
         nt["alpha"] = table["alpha"]
@@ -273,7 +357,7 @@ class FullrankPlan:
                                + np.uint64(N.FULLRANK_TENSOR.fields["alpha"][1]))
         else:
             nt["alpha_dev"] = 0
-        sqrt_n = np.sqrt(self.numel.astype(np.float64))
+        sqrt_n = np.sqrt(self.full_numel.astype(np.float64))
         nt["sqrt_n"] = sqrt_n.astype(np.float32)
         nt["d"] = np.float32(d)
         use_clip = d > 0 and pre_div_mode == 0
@@ -298,9 +382,9 @@ class FullrankPlan:
                                        self.d_dyn.data_ptr(), stream.cuda_stream)
         N.check(rc, "af8_norm_finalize")
 
-    def _param_scale(self, buf, scale, stream):
-        """Upload the table, then let the device fill alpha / decay from the
-        parameters' RMS (scale_parameter=True, optimizer.py:850-853)."""
+    def _scale_table(self, buf, scale, stream):
+        """Upload the launch table and fill the host table of the parameter-RMS passes
+        (scale_parameter=True, optimizer.py:850-853)."""
         chunk = N.lib().af8_scale_chunk()
         nchunks = (self.numel + chunk - 1) // chunk
         if self.h_scale is None:
@@ -313,21 +397,28 @@ class FullrankPlan:
         self.h_table.mark(stream)
         hb = self.h_scale.next()
         t = hb.numpy()[: self.n * N.SCALE_TENSOR.itemsize].view(N.SCALE_TENSOR)
-        t["param"] = [p.data_ptr() for p in self.params]
-        t["numel"] = self.numel
-        t["first_chunk"] = np.concatenate([[0], np.cumsum(nchunks)[:-1]])
-        t["sqrt_n"] = np.sqrt(self.numel.astype(np.float64)).astype(np.float32)
-        t["param_dtype"] = self.cfg.param_dtype
-        for k in ("rho", "eps2", "bc", "weight_decay", "bc_mode", "scale_weight_decay"):
-            t[k] = scale[k]
-        rc = N.lib().af8_param_scale(hb.data_ptr(), self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(),
-                                     self.d_table.data_ptr(), N.FULLRANK_TENSOR.itemsize,
-                                     N.FULLRANK_TENSOR.fields["alpha"][1], N.FULLRANK_TENSOR.fields["decay"][1],
-                                     stream.cuda_stream)
-        N.check(rc, "af8_param_scale")
+        fill_scale_table(t, self.params, self.numel, self.full_numel, nchunks, self.cfg.param_dtype, scale)
+        self._scale_first, self._scale_count = t["first_chunk"].copy(), nchunks
+        return hb, t
+
+    def _param_scale(self, buf, scale, stream, x=None):
+        """First half of alpha / decay from the parameters' RMS: partial sums of squares; the cut
+        entries' local sums go to scalar 0 of their slots of exchange x.  _param_finish evaluates."""
+        hb, t = self._scale_table(buf, scale, stream)
+        if self.cut and x is not None:
+            for i in self.cut:
+                t["total"][i] = self.pieces[i].slots[x].data_ptr()         # scalar 0 of the slot
+        N.check(N.lib().af8_param_sumsq(hb.data_ptr(), self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(),
+                                        stream.cuda_stream), "af8_param_sumsq")
         self.h_scale.mark(stream)
-        if LAUNCH_LOG is not None:
-            pass
+        if x is not None:
+            self._sums_to_slots(x, 0, self.d_chunks, self._scale_first, self._scale_count)
+
+    def _param_finish(self, stream):
+        N.check(N.lib().af8_param_scale_finish(self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(),
+                                               self.d_table.data_ptr(), N.FULLRANK_TENSOR.itemsize,
+                                               N.FULLRANK_TENSOR.fields["alpha"][1], N.FULLRANK_TENSOR.fields["decay"][1],
+                                               stream.cuda_stream), "af8_param_scale_finish")
 
     def _alpha_dev_ptrs(self):
         if not self._alpha_on_device:
@@ -338,10 +429,12 @@ class FullrankPlan:
     def _run_lag(self, buf, table, d, fira, fira_margin, stream):
         """lag_norm=True: one pass that clips and limits with the previous step's norm and leaves
         this step's norm for the next one (optimizer.py:1056-1071)."""
+        if self.cut:
+            raise RuntimeError("lag_norm needs whole tensors: a tensor that is split over launch tables cannot lag")
         if self.h_lag is None:
             self.h_lag = _PinnedRing(self.n * N.LAG_TENSOR.itemsize)
             self.d_lag = torch.empty(self.n * N.LAG_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
-        lag_table(self.h_lag, self.d_lag, self.states, self.device, self.first_block, self.nblocks, self.numel,
+        lag_table(self.h_lag, self.d_lag, self.states, self.device, self.first_block, self.nblocks, self.full_numel,
                   table["alpha"], self._alpha_dev_ptrs(), d, fira, fira_margin, False, stream)
         lib = N.lib()
         if buf is not None:
@@ -355,51 +448,96 @@ class FullrankPlan:
                                     stream.cuda_stream), "af8_lag_scalars")
 
     def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None, lag=False):
-        """One optimizer step for every tensor of the plan
-        (_dispatch_cuda_clip's pass structure, optimizer.py:1048-1077).
+        """One optimizer step for every tensor of the plan, start to end."""
+        for _ in self.stages(grads, scalars, d=d, fira=fira, fira_margin=fira_margin, scale=scale, stream=stream, lag=lag):
+            pass
+
+    def stages(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None, lag=False):
+        """The step as a generator (_dispatch_cuda_clip's pass structure, optimizer.py:1048-1077).
+        It yields at every exchange point (fullrank_exchanges of them): the passes before a yield
+        have added the local sums of the cut entries to their slots, the passes after it expect
+        the slots to hold the whole tensors' sums.  Without cut entries the yields mean nothing.
+        The last segment is the pass that writes the parameters.
         scale: per-tensor inputs of af8_param_scale when alpha depends on the
         parameter RMS; the table's alpha / decay are then produced on the device.
         lag: lag_norm=True; the momentum-only rule keeps its exact passes."""
         stream = stream or torch.cuda.current_stream(self.device)
         buf, table = self.fill_table(grads, scalars)
         self._alpha_on_device = scale is not None
-        if scale is not None:
-            self._param_scale(buf, scale, stream)
-            buf = None
         mom_only = bool(self.cfg.momentum_only)
         clip_first = d > 0                      # a statistic of the raw update is needed
-        if not (fira or clip_first):
-            self._step(N.MODE_NOCLIP, buf, stream)
-            return
-        if self.d_sumsq is None:
+        need_stat = fira or clip_first
+        if need_stat and self.d_sumsq is None:
             self.d_sumsq = torch.empty(self.total_blocks, dtype=torch.float32, device=self.device)
-        if lag and not mom_only:
+        if need_stat and lag and not mom_only:
+            if scale is not None:
+                self._param_scale(buf, scale, stream)
+                self._param_finish(stream)
+                buf = None
             self._run_lag(buf, table, d, fira, fira_margin, stream)
             return
+        x = 0
         if not mom_only:
-            self._step(N.MODE_SUMSQ, buf, stream)
-            self._finalize(table, 0, d, fira, fira_margin, stream)
-            self._step(N.MODE_APPLY, None, stream)
+            if scale is not None:
+                self._param_scale(buf, scale, stream, x)
+                buf = None
+            if need_stat:
+                self._step(N.MODE_SUMSQ, buf, stream)
+                buf = None
+                self._sums_to_slots(x, 1, self.d_sumsq, self.first_block, self.nblocks)
+            if scale is not None or need_stat:
+                yield
+            if scale is not None:
+                self._param_finish(stream)
+            if need_stat:
+                self._finalize(table, 0, d, fira, fira_margin, stream, x, 1)
+                self._step(N.MODE_APPLY, None, stream)
+            else:
+                self._step(N.MODE_NOCLIP, buf, stream)
             return
         # momentum-only rule (optimizer.py:894-901): clip the normalised gradient
         # first, then limit the norm of the momentum that is applied with d = 0
         pending = buf
+        if scale is not None:
+            self._param_scale(pending, scale, stream, x)
+            pending = None
         if clip_first:
             self._step(N.MODE_SUMSQ, pending, stream)
             pending = None
-            self._finalize(table, 1, d, False, fira_margin, stream)
-        else:
+            self._sums_to_slots(x, 1, self.d_sumsq, self.first_block, self.nblocks)
+        if scale is not None or clip_first:
+            yield
+            if scale is not None:
+                self._param_finish(stream)
+            if clip_first:
+                self._finalize(table, 1, d, False, fira_margin, stream, x, 1)
+            x += 1
+        if not clip_first:
             self.d_dyn.view(torch.float32).view(self.n, 8)[:, 2] = 1.0   # pre_div
         if fira:
             self._step(N.MODE_SUMSQ_M, pending, stream)
             pending = None
-            self._finalize(table, 2, 0.0, True, fira_margin, stream)
+            self._sums_to_slots(x, 1, self.d_sumsq, self.first_block, self.nblocks)
+            yield
+            self._finalize(table, 2, 0.0, True, fira_margin, stream, x, 1)
         self._step(N.MODE_APPLY, pending, stream)
 
     def norms(self):
         """Update norms measured by the last two-pass step (one per tensor)."""
         dyn = self.d_dyn.cpu().numpy().view(N.DYN_SCALARS)
         return dyn["norm"].copy()
+
+
+def fill_scale_table(t, params, numel, full_numel, nchunks, param_dtype, scale):
+    """Fill an af8_scale_tensor table (host view `t`)."""
+    t["param"] = [p.data_ptr() for p in params]
+    t["numel"] = numel
+    t["first_chunk"] = np.concatenate([[0], np.cumsum(nchunks)[:-1]])
+    t["sqrt_n"] = np.sqrt(full_numel.astype(np.float64)).astype(np.float32)
+    t["param_dtype"] = param_dtype
+    t["total"] = 0
+    for k in ("rho", "eps2", "bc", "weight_decay", "bc_mode", "scale_weight_decay"):
+        t[k] = scale[k]
 
 
 def _small_state_fields(row, st, prefix, fmt, block):
@@ -416,13 +554,19 @@ def _small_state_fields(row, st, prefix, fmt, block):
 
 class FactoredPlan:
     """One multi-tensor launch group of the factored path (2-D tensors with row /
-    column second moments; optionally momentum; optionally CAME confidence)."""
+    column second moments; optionally momentum; optionally CAME confidence).
+
+    pieces: optional list with a Piece (or None) per entry.  An entry with a Piece holds the rows
+    row0 .. row0 + p.shape[0] of a tensor of full_rows rows; its row / column states describe the
+    whole tensor."""
 
     def __init__(self, device, grad_dtype, m_fmt, m_block, came, negate, params, states, v_fmts, c_fmts,
-                 stochastic_round=False):
+                 stochastic_round=False, pieces=None):
         self.device = torch.device(device)
         self.params, self.states = list(params), list(states)
         self.n = n = len(self.params)
+        self.pieces = list(pieces) if pieces is not None else [None] * n
+        self.cut = [i for i, pc in enumerate(self.pieces) if pc is not None and pc.slots is not None]
         self.came = bool(came)
         self.cfg = N.FactoredCfg()
         pdt = self.params[0].dtype
@@ -443,68 +587,121 @@ class FactoredPlan:
                 raise RuntimeError("the factored kernels update contiguous 2-D parameters")
         self.rows = np.array([p.shape[0] for p in self.params], dtype=np.int64)
         self.cols = np.array([p.shape[1] for p in self.params], dtype=np.int64)
+        self.full_rows = np.array([pc.full_rows if pc is not None else p.shape[0]
+                                   for p, pc in zip(self.params, self.pieces)], dtype=np.int64)
+        self.row0 = np.array([pc.row0 if pc is not None else 0 for pc in self.pieces], dtype=np.int64)
         self.numel = self.rows * self.cols
+        self.full_numel = self.full_rows * self.cols
         self.total_numel = int(self.numel.sum())
         self.cfg.aligned8 = int(bool((self.cols % 8 == 0).all()))
         lib = N.lib()
         m_quant = m_fmt not in (None, "fp32")
         self.chunk = lib.af8_factored_chunk(self.cfg.m_block if m_quant else 0)
-        tr, tc = lib.af8_factored_tile_rows(), lib.af8_factored_tile_cols()
+        self.tile = (lib.af8_factored_tile_rows(), lib.af8_factored_tile_cols())
         self.nchunks = (self.numel + self.chunk - 1) // self.chunk
-        ntiles = ((self.rows + tr - 1) // tr) * ((self.cols + tc - 1) // tc)
         self.first_chunk = np.concatenate([[0], np.cumsum(self.nchunks)[:-1]]).astype(np.int64)
-        self.first_tile = np.concatenate([[0], np.cumsum(ntiles)[:-1]]).astype(np.int64)
         self.total_chunks = int(self.nchunks.sum())
-        # rows then columns of every tensor, each vector starting on a 16-byte boundary
-        self._vec_len = ((self.rows + 3) // 4 * 4) + ((self.cols + 3) // 4 * 4)
+        # row sums (of the whole tensor's rows) then column sums of every tensor, each vector on a 16-byte boundary
+        self._vec_len = ((self.full_rows + 3) // 4 * 4) + ((self.cols + 3) // 4 * 4)
         rc = int(self._vec_len.sum())
-        self.d_sums = torch.empty(rc, dtype=torch.float64, device=self.device)
+        self.d_sums = torch.zeros(rc, dtype=torch.float64, device=self.device)
         self.d_inv = torch.empty(rc * (2 if self.came else 1), dtype=torch.float32, device=self.device)
-        self.d_table = torch.empty(n * N.FACTORED_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+        # one table for the passes over the elements (the entries as they are) and, when an entry holds
+        # only some rows of its tensor, two for the row / column states (whole tensors; sums from the slots)
+        self.n_tables = 3 if self.cut else 1
+        tb = n * N.FACTORED_TENSOR.itemsize
+        self.d_tables = torch.empty(self.n_tables * tb, dtype=torch.uint8, device=self.device)
+        self.d_table = self.d_tables[:tb]
         self.d_dyn = torch.zeros(n * N.DYN_SCALARS.itemsize, dtype=torch.uint8, device=self.device)
         self.d_norm = torch.empty(n * N.NORM_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
         self.d_sumsq = torch.empty(self.total_chunks, dtype=torch.float64, device=self.device)
-        self.h_table = _PinnedRing(n * N.FACTORED_TENSOR.itemsize)
+        self.h_table = _PinnedRing(self.n_tables * tb)
         self.h_norm = _PinnedRing(n * N.NORM_TENSOR.itemsize)
         self.h_scale = self.d_scale = self.d_chunks = None
         self.h_lag = self.d_lag = None
         self.v_fmts, self.c_fmts = list(v_fmts), list(c_fmts)
         self._static = None
+        self._ptr_sig = None
         self._alpha_on_device = False
 
+    _STATE_KEYS = ("m_q", "m_scale", "m", "row_var_q", "row_var", "col_var_q", "col_var", "conf_row_q", "conf_row",
+                   "conf_col_q", "conf_col")
+
+    def _pointer_signature(self):
+        sig = [p.data_ptr() for p in self.params]
+        for st in self.states:
+            sig += [id(st.get(k)) for k in self._STATE_KEYS]
+        return sig
+
+    @staticmethod
+    def _running(counts):
+        return np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.int64)
+
     def _static_fields(self):
-        t = np.zeros(self.n, dtype=N.FACTORED_TENSOR)
+        """-> the static part of the tables, shape (n_tables, n): [0] the entries as they are; with cut
+        entries [1] / [2] describe the whole tensors for the second-moment / confidence state passes."""
+        n = self.n
+        t = np.zeros((self.n_tables, n), dtype=N.FACTORED_TENSOR)
         off = 0
         sums, inv = self.d_sums.data_ptr(), self.d_inv.data_ptr()
         half = int(self._vec_len.sum())
+        tr, tc = self.tile
         for i, (p, st) in enumerate(zip(self.params, self.states)):
-            R, C = int(self.rows[i]), int(self.cols[i])
-            Rp = (R + 3) // 4 * 4
-            t["param"][i] = p.data_ptr()
-            t["m_q"][i] = _ptr(st.get("m_q"))
-            t["m_scale"][i] = _ptr(st.get("m_scale"))
-            t["m_f32"][i] = _ptr(st.get("m"))
-            t["row_sum"][i] = sums + 8 * off
-            t["col_sum"][i] = sums + 8 * (off + Rp)
-            t["inv_row"][i] = inv + 4 * off
-            t["inv_col"][i] = inv + 4 * (off + Rp)
-            if self.came:
-                t["inv_row_conf"][i] = inv + 4 * (half + off)
-                t["inv_col_conf"][i] = inv + 4 * (half + off + Rp)
+            C = int(self.cols[i])
+            Rp = (int(self.full_rows[i]) + 3) // 4 * 4
+            r0 = int(self.row0[i])
+            e = t[0]
+            e["param"][i] = p.data_ptr()
+            e["m_q"][i] = _ptr(st.get("m_q"))
+            e["m_scale"][i] = _ptr(st.get("m_scale"))
+            e["m_f32"][i] = _ptr(st.get("m"))
+            pc = self.pieces[i]
+            if pc is not None and pc.copy is not None:
+                if pc.copy.numel() != p.numel() or pc.copy.dtype != torch.bfloat16:
+                    raise RuntimeError("the compute copy of a parameter must be a bf16 tensor of its size")
+                e["param_copy"][i] = pc.copy.data_ptr()
             block = st.get("block_size", 2048)
-            _small_state_fields(t["row_var"][i:i + 1], st, "row_var", self.v_fmts[i], block)
-            _small_state_fields(t["col_var"][i:i + 1], st, "col_var", self.v_fmts[i], block)
+            _small_state_fields(e["row_var"][i:i + 1], st, "row_var", self.v_fmts[i], block)
+            _small_state_fields(e["col_var"][i:i + 1], st, "col_var", self.v_fmts[i], block)
             if self.came:
-                _small_state_fields(t["conf_row"][i:i + 1], st, "conf_row", self.c_fmts[i], block)
-                _small_state_fields(t["conf_col"][i:i + 1], st, "conf_col", self.c_fmts[i], block)
+                _small_state_fields(e["conf_row"][i:i + 1], st, "conf_row", self.c_fmts[i], block)
+                _small_state_fields(e["conf_col"][i:i + 1], st, "conf_col", self.c_fmts[i], block)
+            for k in range(1, self.n_tables):
+                t[k][i] = e[i]
+            # the entry's own rows inside the whole tensor's vectors
+            e["row_sum"][i] = sums + 8 * (off + r0)
+            e["col_sum"][i] = sums + 8 * (off + Rp)
+            e["inv_row"][i] = inv + 4 * (off + r0)
+            e["inv_col"][i] = inv + 4 * (off + Rp)
+            if self.came:
+                e["inv_row_conf"][i] = inv + 4 * (half + off + r0)
+                e["inv_col_conf"][i] = inv + 4 * (half + off + Rp)
+            for k in range(1, self.n_tables):
+                f = t[k]
+                for name in ("inv_col", "inv_col_conf", "col_sum"):
+                    f[name][i] = e[name][i]
+                f["row_sum"][i] = sums + 8 * off
+                f["inv_row"][i] = inv + 4 * off
+                if self.came:
+                    f["inv_row_conf"][i] = inv + 4 * (half + off)
+                if i in self.cut:               # whole sums: exchange 0 (second moment), exchange 2 (confidence)
+                    base = pc.slots[0 if k == 1 else 2].data_ptr() if (k == 1 or self.came) else 0
+                    if base:
+                        f["row_sum"][i] = base + 8 * 8
+                        f["col_sum"][i] = base + 8 * (8 + Rp)
             off += int(self._vec_len[i])
-        t["rows"], t["cols"] = self.rows, self.cols
-        t["first_chunk"], t["first_tile"] = self.first_chunk, self.first_tile
-        # units of the small-state launch: the quantisation blocks of the row state, then of the column state
-        sb = t["row_var"]["block"].astype(np.int64)
-        units = (self.rows + sb - 1) // sb + (self.cols + sb - 1) // sb
-        t["first_small"] = np.concatenate([[0], np.cumsum(units)[:-1]])
-        self.small_units = int(units.sum())
+        sb = t[0]["row_var"]["block"].astype(np.int64)
+        for k in range(self.n_tables):
+            rows = self.rows if k == 0 else self.full_rows
+            t[k]["rows"], t[k]["cols"] = rows, self.cols
+            t[k]["first_chunk"] = self._running((rows * self.cols + self.chunk - 1) // self.chunk)
+            t[k]["first_tile"] = self._running(((rows + tr - 1) // tr) * ((self.cols + tc - 1) // tc))
+            # units of the small-state launch: the quantisation blocks of the row state, then of the column state
+            units = (rows + sb - 1) // sb + (self.cols + sb - 1) // sb
+            t[k]["first_small"] = self._running(units)
+            if k == self.n_tables - 1:
+                self.small_units = int(units.sum())
+        self._sums_off = self._running(self._vec_len)
         return t
 
     def kernel_name(self, what):
@@ -521,20 +718,28 @@ class FactoredPlan:
         e1.record(stream)
         log.append((self.kernel_name(name), self.total_numel, e0, e1))
 
-    def _stats(self, mode, host_buf, stream):
+    def _table_ptr(self, k):
+        return self.d_tables.data_ptr() + k * self.n * N.FACTORED_TENSOR.itemsize
+
+    def _stats(self, mode, host_buf, stream, x=None):
         self.cfg.mode = mode
         lib = N.lib()
         self._log("stats_gradsq" if mode == N.FSTAT_GRADSQ else "stats_residual", lambda: N.check(
             lib.af8_factored_stats(ctypes.byref(self.cfg), self.d_table.data_ptr(), host_buf.data_ptr(), self.n,
                                    self.d_dyn.data_ptr(), stream.cuda_stream), "af8_factored_stats"), stream)
+        if x is not None:
+            for i in self.cut:                  # the entry's rows and its column partial sums join the whole tensor's
+                a, ln = int(self._sums_off[i]), int(self._vec_len[i])
+                self.pieces[i].slots[x][8:8 + ln].add_(self.d_sums[a:a + ln])
 
     def _small(self, conf, stream):
         lib = N.lib()
+        table = self._table_ptr((2 if conf else 1) if self.cut else 0)
         self._log("small_conf" if conf else "small_var", lambda: N.check(
-            lib.af8_factored_small(ctypes.byref(self.cfg), self.d_table.data_ptr(), self.n, int(conf), self.small_units,
+            lib.af8_factored_small(ctypes.byref(self.cfg), table, self.n, int(conf), self.small_units,
                                    stream.cuda_stream), "af8_factored_small"), stream)
 
-    def _update(self, mode, use_dyn, stream):
+    def _update(self, mode, use_dyn, stream, x=None):
         self.cfg.mode = mode
         lib = N.lib()
         name = {N.FUPD_SUMSQ_U: "sumsq_u", N.FUPD_SUMSQ: "sumsq", N.FUPD_APPLY: "apply", N.FUPD_LAG: "lag"}[mode]
@@ -542,12 +747,20 @@ class FactoredPlan:
             lib.af8_factored_update(ctypes.byref(self.cfg), self.d_table.data_ptr(), self.n, self.total_chunks,
                                     self.d_dyn.data_ptr() if use_dyn else None, self.d_sumsq.data_ptr(),
                                     stream.cuda_stream), "af8_factored_update"), stream)
+        if x is not None:
+            for i in self.cut:
+                a = int(self.first_chunk[i])
+                _add_to_slot(self.pieces[i].slots[x], 1, self.d_sumsq[a:a + int(self.nchunks[i])])
 
-    def _finalize(self, table, pre_div_mode, d, fira, fira_margin, stream):
+    def _finalize(self, table, pre_div_mode, d, fira, fira_margin, stream, x=None):
         buf = self.h_norm.next()
         nt = buf.numpy()[: self.n * N.NORM_TENSOR.itemsize].view(N.NORM_TENSOR)
         nt["first_block"] = self.first_chunk
         nt["n_blocks"] = self.nchunks
+        if x is not None:
+            for i in self.cut:
+                nt["n_blocks"][i] = -1
+                nt["first_block"][i] = self.pieces[i].slots[x].data_ptr() + 8
         nt["pre_div_mode"] = pre_div_mode
         nt["partials_f64"] = 1
         nt["alpha"] = table["alpha"]
@@ -556,7 +769,7 @@ class FactoredPlan:
                                + np.uint64(N.FACTORED_TENSOR.fields["alpha"][1]))
         else:
             nt["alpha_dev"] = 0
-        sqrt_n = np.sqrt(self.numel.astype(np.float64))
+        sqrt_n = np.sqrt(self.full_numel.astype(np.float64))
         nt["sqrt_n"] = sqrt_n.astype(np.float32)
         nt["d"] = np.float32(d)
         nt["clip_div"] = (sqrt_n * d).astype(np.float32) if (d > 0 and pre_div_mode == 0) else np.float32(0.0)
@@ -580,37 +793,59 @@ class FactoredPlan:
                                           self.d_dyn.data_ptr(), stream.cuda_stream), "af8_norm_finalize")
 
     def run(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None, lag=False):
-        """One optimizer step for every tensor of the plan (optimizer.py:2202-2552)."""
+        """One optimizer step for every tensor of the plan, start to end."""
+        for _ in self.stages(grads, scalars, d=d, fira=fira, fira_margin=fira_margin, scale=scale, stream=stream, lag=lag):
+            pass
+
+    def stages(self, grads, scalars, d=0.0, fira=False, fira_margin=0.01, scale=None, stream=None, lag=False):
+        """The step as a generator (optimizer.py:2202-2552) that yields at its factored_exchanges(...)
+        exchange points, like FullrankPlan.stages; the last segment writes the parameters."""
         stream = stream or torch.cuda.current_stream(self.device)
-        if self._static is None:
+        sig = self._pointer_signature()
+        if self._static is None or sig != self._ptr_sig:
             self._static = self._static_fields()
+            self._ptr_sig = sig
         buf = self.h_table.next()
-        table = buf.numpy()[: self.n * N.FACTORED_TENSOR.itemsize].view(N.FACTORED_TENSOR)
-        table[:] = self._static
+        tables = buf.numpy()[: self.n_tables * self.n * N.FACTORED_TENSOR.itemsize].view(N.FACTORED_TENSOR).reshape(self.n_tables, self.n)
+        tables[:] = self._static
+        table = tables[0]
         table["grad"] = [g.data_ptr() for g in grads]
         for k in ("decay", "alpha", "v_w", "m_w", "c_w", "eps1", "eps_came"):
             table[k] = scalars[k]
         table["sr_base"] = scalars.get("sr_base", 0)
+        for k in range(1, self.n_tables):
+            for name in ("grad", "decay", "alpha", "v_w", "m_w", "c_w", "eps1", "eps_came"):
+                tables[k][name] = table[name]
         lib = N.lib()
-        N.check(lib.af8_factored_upload(ctypes.byref(self.cfg), buf.data_ptr(), self.d_table.data_ptr(), self.n,
-                                        stream.cuda_stream), "af8_factored_upload")
+        for k in range(self.n_tables):
+            N.check(lib.af8_factored_upload(ctypes.byref(self.cfg), buf.data_ptr() + k * self.n * N.FACTORED_TENSOR.itemsize,
+                                            self._table_ptr(k), self.n, stream.cuda_stream), "af8_factored_upload")
         self.h_table.mark(stream)
         self._alpha_on_device = scale is not None
+        need_stat = fira or d > 0
+        if self.cut and not self.came and need_stat and lag:
+            raise RuntimeError("lag_norm needs whole tensors: a tensor that is split over launch tables cannot lag")
         if scale is not None:
-            self._param_scale(scale, stream)
-        self._stats(N.FSTAT_GRADSQ, buf, stream)
+            self._param_scale(scale, stream, 0)
+        self._stats(N.FSTAT_GRADSQ, buf, stream, 0)
+        yield
+        if scale is not None:
+            self._param_finish(stream)
         self._small(False, stream)
         if self.came:
             # clip of U (optimizer.py:826-828); d == 0 means no clip: an infinite threshold gives divisor 1
-            self._update(N.FUPD_SUMSQ_U, False, stream)
-            self._finalize(table, 1, d if d > 0 else float("inf"), False, fira_margin, stream)
-            self._stats(N.FSTAT_RESIDUAL, buf, stream)
+            self._update(N.FUPD_SUMSQ_U, False, stream, 1)
+            yield
+            self._finalize(table, 1, d if d > 0 else float("inf"), False, fira_margin, stream, 1)
+            self._stats(N.FSTAT_RESIDUAL, buf, stream, 2)
+            yield
             self._small(True, stream)
             if fira:                                    # the final update is applied with d = 0 (optimizer.py:953)
-                self._update(N.FUPD_SUMSQ, True, stream)
-                self._finalize(table, 2, 0.0, True, fira_margin, stream)
+                self._update(N.FUPD_SUMSQ, True, stream, 3)
+                yield
+                self._finalize(table, 2, 0.0, True, fira_margin, stream, 3)
             self._update(N.FUPD_APPLY, True, stream)
-        elif (fira or d > 0) and lag:
+        elif need_stat and lag:
             # lag_norm=True: one pass with the previous step's norm (optimizer.py:1056-1071)
             if self.h_lag is None:
                 self.h_lag = _PinnedRing(self.n * N.LAG_TENSOR.itemsize)
@@ -619,21 +854,22 @@ class FactoredPlan:
             if self._alpha_on_device:
                 alpha_dev = (self.d_table.data_ptr() + np.arange(self.n, dtype=np.uint64) * np.uint64(N.FACTORED_TENSOR.itemsize)
                              + np.uint64(N.FACTORED_TENSOR.fields["alpha"][1]))
-            lag_table(self.h_lag, self.d_lag, self.states, self.device, self.first_chunk, self.nchunks, self.numel,
+            lag_table(self.h_lag, self.d_lag, self.states, self.device, self.first_chunk, self.nchunks, self.full_numel,
                       table["alpha"], alpha_dev, d, fira, fira_margin, True, stream)
             N.check(lib.af8_lag_scalars(self.d_lag.data_ptr(), self.n, 0, None, self.d_dyn.data_ptr(), stream.cuda_stream),
                     "af8_lag_scalars")
             self._update(N.FUPD_LAG, True, stream)
             N.check(lib.af8_lag_scalars(self.d_lag.data_ptr(), self.n, 1, self.d_sumsq.data_ptr(), self.d_dyn.data_ptr(),
                                         stream.cuda_stream), "af8_lag_scalars")
-        elif fira or d > 0:
-            self._update(N.FUPD_SUMSQ, False, stream)
-            self._finalize(table, 0, d, fira, fira_margin, stream)
+        elif need_stat:
+            self._update(N.FUPD_SUMSQ, False, stream, 1)
+            yield
+            self._finalize(table, 0, d, fira, fira_margin, stream, 1)
             self._update(N.FUPD_APPLY, True, stream)
         else:
             self._update(N.FUPD_APPLY, False, stream)
 
-    def _param_scale(self, scale, stream):
+    def _param_scale(self, scale, stream, x=None):
         chunk = N.lib().af8_scale_chunk()
         nchunks = (self.numel + chunk - 1) // chunk
         if self.h_scale is None:
@@ -642,18 +878,24 @@ class FactoredPlan:
             self.d_chunks = torch.empty(int(nchunks.sum()), dtype=torch.float32, device=self.device)
         hb = self.h_scale.next()
         t = hb.numpy()[: self.n * N.SCALE_TENSOR.itemsize].view(N.SCALE_TENSOR)
-        t["param"] = [p.data_ptr() for p in self.params]
-        t["numel"] = self.numel
-        t["first_chunk"] = np.concatenate([[0], np.cumsum(nchunks)[:-1]])
-        t["sqrt_n"] = np.sqrt(self.numel.astype(np.float64)).astype(np.float32)
-        t["param_dtype"] = self.cfg.param_dtype
-        for k in ("rho", "eps2", "bc", "weight_decay", "bc_mode", "scale_weight_decay"):
-            t[k] = scale[k]
-        self._log("param_scale", lambda: N.check(N.lib().af8_param_scale(
-            hb.data_ptr(), self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(), self.d_table.data_ptr(),
-            N.FACTORED_TENSOR.itemsize, N.FACTORED_TENSOR.fields["alpha"][1], N.FACTORED_TENSOR.fields["decay"][1],
-            stream.cuda_stream), "af8_param_scale"), stream)
+        fill_scale_table(t, self.params, self.numel, self.full_numel, nchunks, self.cfg.param_dtype, scale)
+        if x is not None:
+            for i in self.cut:
+                t["total"][i] = self.pieces[i].slots[x].data_ptr()
+        self._log("param_scale", lambda: N.check(N.lib().af8_param_sumsq(
+            hb.data_ptr(), self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(), stream.cuda_stream), "af8_param_sumsq"),
+            stream)
         self.h_scale.mark(stream)
+        if x is not None:
+            first = t["first_chunk"]
+            for i in self.cut:
+                _add_to_slot(self.pieces[i].slots[x], 0, self.d_chunks[int(first[i]):int(first[i]) + int(nchunks[i])])
+
+    def _param_finish(self, stream):
+        N.check(N.lib().af8_param_scale_finish(
+            self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(), self.d_table.data_ptr(),
+            N.FACTORED_TENSOR.itemsize, N.FACTORED_TENSOR.fields["alpha"][1], N.FACTORED_TENSOR.fields["decay"][1],
+            stream.cuda_stream), "af8_param_scale_finish")
 
     def norms(self):
         dyn = self.d_dyn.cpu().numpy().view(N.DYN_SCALARS)
@@ -670,10 +912,13 @@ class ApolloPlan:
     projection, one batched low-rank state update (the full-rank kernel run on the
     projected gradients), per-tensor scaling and write-back."""
 
-    def __init__(self, device, grad_dtype, v_fmt, m_fmt, block, m_block, negate, params, states, rank):
+    def __init__(self, device, grad_dtype, v_fmt, m_fmt, block, m_block, negate, params, states, rank, copies=None):
+        """copies: optional list with a bf16 tensor (or None) per parameter that receives the updated
+        parameter rounded to nearest (the compute copy of a mixed-precision run)."""
         self.device = torch.device(device)
         self.params, self.states = list(params), list(states)
         self.n = len(self.params)
+        self.copies = list(copies) if copies is not None else [None] * self.n
         self.grad_dtype = _GRAD_DT[grad_dtype]
         self.v_fmt, self.m_fmt, self.block, self.m_block = v_fmt, m_fmt, int(block), int(m_block) if m_block else 0
         self.negate = int(bool(negate))
@@ -826,7 +1071,8 @@ class ApolloPlan:
             N.check(lib.af8_apollo_apply(self.params[i].data_ptr(), self.param_dtype, int(t.get("sr", False)), int(t.get("sr_base", 0)),
                                          grads[i].data_ptr(), self.grad_dtype, self.negate,
                                          self.sf[i].data_ptr(), self.out.data_ptr() + 16 * i, self.rows[i], self.cols[i],
-                                         ctypes.byref(sin), float(t["decay"]), int(t["has_decay"]), s), "af8_apollo_apply")
+                                         ctypes.byref(sin), float(t["decay"]), int(t["has_decay"]),
+                                         self.copies[i].data_ptr() if self.copies[i] is not None else None, s), "af8_apollo_apply")
         if log is not None:
             ev[3].record(stream)
             log.append(("apollo_project", self.total_numel, ev[0], ev[1]))

@@ -32,7 +32,7 @@ FULLRANK_TENSOR = np.dtype([
     ("decay", np.float32), ("alpha", np.float32), ("v_w", np.float32), ("v_keep", np.float32),
     ("v_eps_add", np.float32), ("m_w", np.float32), ("eps_gradsq", np.float32),
     ("eps_denom", np.float32), ("eps_sq", np.float32), ("reserved", np.float32),
-    ("sr_base", np.uint64), ("reserved2", np.uint64),
+    ("sr_base", np.uint64), ("param_copy", _P),
 ], align=True)
 assert FULLRANK_TENSOR.itemsize == 144
 
@@ -81,17 +81,17 @@ FACTORED_TENSOR = np.dtype([
     ("rows", np.int64), ("cols", np.int64), ("first_chunk", np.int64), ("first_tile", np.int64),
     ("decay", np.float32), ("alpha", np.float32), ("v_w", np.float32), ("m_w", np.float32),
     ("c_w", np.float32), ("eps1", np.float32), ("eps_came", np.float32), ("first_small", np.int32),
-    ("sr_base", np.uint64),
+    ("sr_base", np.uint64), ("param_copy", _P),
 ], align=True)
-assert FACTORED_TENSOR.itemsize == 320
+assert FACTORED_TENSOR.itemsize == 328
 
 SCALE_TENSOR = np.dtype([
     ("param", _P), ("numel", np.int64), ("first_chunk", np.int64),
     ("sqrt_n", np.float32), ("rho", np.float32), ("eps2", np.float32), ("bc", np.float32),
     ("weight_decay", np.float32), ("bc_mode", np.int32), ("scale_weight_decay", np.int32),
-    ("param_dtype", np.int32),
+    ("param_dtype", np.int32), ("total", _P),
 ], align=True)
-assert SCALE_TENSOR.itemsize == 56
+assert SCALE_TENSOR.itemsize == 64
 
 
 class FullrankCfg(ctypes.Structure):
@@ -156,12 +156,14 @@ PROTOTYPES = {
     "af8_apollo_scales": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn), _c_p, _c_p, _c_p,
                                  _c_p, _c_p]),
     "af8_apollo_apply": (_c_i, [_c_p, _c_i, _c_i, ctypes.c_uint64, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l,
-                                ctypes.POINTER(ApolloScalarsIn), _c_f, _c_i, _c_p]),
+                                ctypes.POINTER(ApolloScalarsIn), _c_f, _c_i, _c_p, _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
     "af8_lag_scalars": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p]),
     "af8_fullrank_limited_step_noalloc": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_f, _c_i, _c_f, _c_p, _c_i, _c_p, _c_p]),
     "af8_noalloc_max_numel": (_c_l, [_c_i]),
     "af8_param_scale": (_c_i, [_c_p, _c_p, _c_i, _c_p, _c_p, _c_l, _c_l, _c_l, _c_p]),
+    "af8_param_sumsq": (_c_i, [_c_p, _c_p, _c_i, _c_p, _c_p]),
+    "af8_param_scale_finish": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_l, _c_l, _c_l, _c_p]),
     "af8_scale_chunk": (_c_i, []),
     "af8_al_dequant": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_i, _c_i, _c_p, _c_p]),
     "af8_al_quant": (_c_i, [_c_p, _c_l, _c_i, _c_i, _c_f, _c_p, _c_p, _c_p, _c_p]),

@@ -22,7 +22,7 @@ from torch import Tensor
 from torch.optim import Optimizer
 
 from . import _native as N
-from ._engine import ApolloPlan, FactoredPlan, FullrankPlan, sr_base
+from ._engine import ApolloPlan, FactoredPlan, FullrankPlan, factored_exchanges, fullrank_exchanges, sr_base
 
 _FULLRANK_COLS = ("decay", "alpha", "v_w", "v_keep", "v_eps_add", "m_w", "eps_gradsq", "eps_denom", "eps_sq")
 
@@ -208,6 +208,11 @@ class Adafactor8Bit(Optimizer):
         self._cfg_seen = {}       # id(param) -> option signature its state was last checked against
         self._plans = {}
         self._after_group = None               # optional hook(gi, group), called when a group's launches are enqueued
+        # Set by a sharding wrapper (zero.py): `_pieces` maps id(parameter) to the _engine.Piece that says which
+        # part of which tensor the parameter is; `_shard` schedules the passes of all launch plans in
+        # rounds with an exchange of partial sums between them (see _step_sharded).
+        self._pieces = {}
+        self._shard = None
 
     # ------------------------------------------------------------------
     # checkpointing (optimizer.py:1463-1553)
@@ -273,7 +278,9 @@ class Adafactor8Bit(Optimizer):
     def _create_state(self, p, grad, group):
         state = self.state[p]
         numel = p.numel()
-        use_quant = group.get("quantize", True) and not (numel < group.get("min_8bit_size", 4096))
+        piece = self._pieces.get(id(p))
+        full_numel = piece.full_numel if piece is not None else numel      # the whole tensor decides the formats
+        use_quant = group.get("quantize", True) and not (full_numel < group.get("min_8bit_size", 4096))
         block = group.get("block_size", 2048)
         m_block = group.get("m_block_size", 256)
         vqt = group.get("v_quant_type", "al8")
@@ -308,6 +315,8 @@ class Adafactor8Bit(Optimizer):
                 state[k] = None
         elif grad.dim() >= 2 and group.get("factored", True):
             shape = grad.shape
+            if piece is not None and piece.full_rows:          # some rows of a tensor: its row state covers all rows
+                shape = (piece.full_rows, shape[-1])
             r_shape = list(shape[:-2]) + [shape[-2], 1]
             c_shape = list(shape[:-2]) + [1, shape[-1]]
             _new_al_state(state, "row_var", r_shape, block, dev, v_fmt)
@@ -410,7 +419,9 @@ class Adafactor8Bit(Optimizer):
         keep the step count, the quantize flag converts the states in place, CAME's confidence states
         come and go with beta3.  Returns the state to step with."""
         numel = p.numel()
-        use_quant = group.get("quantize", True) and not (numel < group.get("min_8bit_size", 4096))
+        piece = self._pieces.get(id(p))
+        full_numel = piece.full_numel if piece is not None else numel
+        use_quant = group.get("quantize", True) and not (full_numel < group.get("min_8bit_size", 4096))
         block, m_block = group.get("block_size", 2048), group.get("m_block_size", 256)
         mqt, vqt = group.get("m_quant_type", "uf8"), group.get("v_quant_type", "al8")
         cqt = group.get("c_quant_type") or vqt
@@ -419,6 +430,8 @@ class Adafactor8Bit(Optimizer):
         use_apollo = group.get("apollo_rank", 0) > 0 and grad.dim() >= 2
         expect_factored = grad.dim() >= 2 and group.get("factored", True)
         shape = tuple(p.shape)
+        if piece is not None and piece.full_rows and expect_factored:
+            shape = (piece.full_rows, shape[-1])
         needs_init = False
 
         old_mqt = state.get("m_quant_type", "uf8")
@@ -605,6 +618,7 @@ class Adafactor8Bit(Optimizer):
         N.lib()   # fail loudly when the CUDA library is missing
         if grad_ready is not None and len(grad_ready) != len(self.param_groups):
             raise ValueError("grad_ready needs one entry per parameter group")
+        pending = []                  # sharded step: (group index, exchange count, device, generator) of every launch plan
         for gi, group in enumerate(self.param_groups):
             if grad_ready is not None and grad_ready[gi] is not None:
                 torch.cuda.current_stream().wait_event(grad_ready[gi])
@@ -636,12 +650,60 @@ class Adafactor8Bit(Optimizer):
                     copy_back.append((p, work))
                 entries.append((work, p.grad, state))
             if entries:
-                self._run_group(gi, group, entries)
+                for e, dev, gen in self._run_group(gi, group, entries):
+                    if self._shard is not None:
+                        pending.append((gi, e, dev, gen))
+                        continue
+                    with torch.cuda.device(dev):             # the whole pass sequence of the plan, now
+                        for _ in gen:
+                            pass
                 for p, work in copy_back:
                     p.copy_(work)
             if self._after_group is not None:
                 self._after_group(gi, group)
+        if self._shard is not None:
+            self._step_sharded(pending)
         return loss
+
+    def _step_sharded(self, pending):
+        """The passes of all launch plans, scheduled for a sharding wrapper.  `self._shard` provides
+          rounds            the largest exchange count of any plan on any rank;
+          exchange(r)       sums the exchange slots of round r over the ranks (r = 0 .. rounds - 1);
+          part_of_group[gi] the part of the parameter space a parameter group lies in; parts are numbered
+                            in the order their parameters may be published;
+          parts             their number;
+          after_part(k)     called when every parameter-writing pass of part k has been enqueued.
+        A plan with e exchange points consists of e + 1 segments; they run in rounds
+        rounds - e .. rounds, so that the last segment of every plan, the one that writes parameters,
+        falls into the last round, where the plans run part by part.  Every rank calls exchange and
+        after_part in the same order, whatever it owns."""
+        sh = self._shard
+        S = int(sh.rounds)
+
+        def advance(item, last):
+            gi, e, dev, gen = item
+            with torch.cuda.device(dev):
+                try:
+                    next(gen)
+                    if last:
+                        raise RuntimeError("a launch plan has more exchange points than it announced")
+                except StopIteration:
+                    if not last:
+                        raise RuntimeError("a launch plan has fewer exchange points than it announced") from None
+
+        for gi, e, dev, gen in pending:
+            if e > S:
+                raise RuntimeError("a launch plan needs more exchange rounds than the sharding wrapper provides")
+        for r in range(S):
+            for item in pending:
+                if r >= S - item[1]:
+                    advance(item, False)
+            sh.exchange(r)
+        for k in range(int(sh.parts)):
+            for item in pending:
+                if sh.part_of_group[item[0]] == k:
+                    advance(item, True)
+            sh.after_part(k)
 
     def _sr_seed(self, state, p=None):
         """The parameter's stochastic-rounding seed, taken from the optimizer-level counter the
@@ -693,12 +755,14 @@ class Adafactor8Bit(Optimizer):
             v_fmt = st.get("v_quant_type", "al8") if quant else "fp32"
             key = (p.device, g.dtype, v_fmt, m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block, p.dtype)
             fullrank.setdefault(key, []).append((p, g, st))
+        out = []        # (exchange count, device, generator over the plan's pass sequence)
         for key, items in fullrank.items():
-            self._run_fullrank(gi, group, key, items)
+            out.append(self._run_fullrank(gi, group, key, items))
         for key, items in factored_items.items():
-            self._run_factored(gi, group, key, items)
+            out.append(self._run_factored(gi, group, key, items))
         if apollo_items:
-            self._run_apollo(gi, group, apollo_items)
+            out.append(self._run_apollo(gi, group, apollo_items))
+        return out
 
     # ------------------------------------------------------------------
     # APOLLO (optimizer.py:2557-3084)
@@ -781,8 +845,10 @@ class Adafactor8Bit(Optimizer):
                 tmp.pop("m_quant_type", None)
                 st.update(tmp)
         if plan is None or plan.ids != ids:
+            pcs = [self._pieces.get(id(p)) for p, _, _ in items]
             plan = ApolloPlan(device, items[0][1].dtype, v_fmt, m_fmt, block, m_block, group["maximize"],
-                              [p for p, _, _ in items], [s for _, _, s in items], rank)
+                              [p for p, _, _ in items], [s for _, _, s in items], rank,
+                              copies=[pc.copy if pc is not None else None for pc in pcs])
             plan.ids = ids
             self._plans[pkey] = plan
         step_any = None
@@ -827,8 +893,11 @@ class Adafactor8Bit(Optimizer):
         low = dict(v_w=f32(bv), v_keep=f32(1.0 - bv), m_w=f32(1.0 - beta1) if beta1 is not None else f32(0.0),
                    apollo_eps=f32(apollo_eps))
         floor_later = math.log2(max(apollo_eps * apollo_eps, _FLOOR))                  # optimizer.py:2766-2767
-        with torch.cuda.device(device):
+        def passes():
             plan.run(grads, pts, per_tensor, low, first_flags, floor_later)
+            return
+            yield                                                                       # (no exchange points)
+        return 0, device, passes()
 
     def _scale_inputs(self, group, n):
         scale = {k: np.zeros(n, dtype=f32) for k in ("rho", "eps2", "bc", "weight_decay")}
@@ -851,12 +920,14 @@ class Adafactor8Bit(Optimizer):
         ids = tuple(id(p) for p, _, _ in items)
         pkey = (gi, "factored", key, bool(group["maximize"]), sr)
         plan = self._plans.get(pkey)
+        pcs = [self._pieces.get(id(p)) for p, _, _ in items]
         if plan is None or plan.ids != ids:
             v_fmts = [(st.get("v_quant_type", "al8") if st.get("is_quantized", False) else "fp32") for _, _, st in items]
             c_fmts = [(st.get("c_quant_type", st.get("v_quant_type", "al8")) if st.get("is_quantized", False) else "fp32")
                       for _, _, st in items]
             plan = FactoredPlan(device, gdtype, m_fmt, m_block, came, group["maximize"],
-                                [p for p, _, _ in items], [s for _, _, s in items], v_fmts, c_fmts, stochastic_round=sr)
+                                [p for p, _, _ in items], [s for _, _, s in items], v_fmts, c_fmts, stochastic_round=sr,
+                                pieces=pcs)
             plan.ids = ids
             self._plans[pkey] = plan
         n = len(items)
@@ -868,8 +939,9 @@ class Adafactor8Bit(Optimizer):
         for i, (p, g, st) in enumerate(items):
             step = st["step"] + 1
             st["step"] = step
-            if sr:
-                cols["sr_base"][i] = sr_base(self._sr_seed(st), step)
+            if sr:                  # a part of a tensor draws the counters of its elements in the whole tensor
+                first = pcs[i].elem0 if pcs[i] is not None else 0
+                cols["sr_base"][i] = (sr_base(self._sr_seed(st), step) + first) & 0xFFFFFFFFFFFFFFFF
             sc = self._step_scalars(group, step)
             alpha, decay = self._alpha_decay(group, sc)
             cols["decay"][i], cols["alpha"][i] = decay, alpha
@@ -881,9 +953,9 @@ class Adafactor8Bit(Optimizer):
             if scale is not None:
                 self._fill_scale(scale, i, group, sc)
             grads.append(g if g.is_contiguous() else g.contiguous())
-        with torch.cuda.device(device):
-            plan.run(grads, cols, d=float(group["d"]), fira=bool(group.get("enable_fira_for_adafactor", False)),
-                     fira_margin=float(group.get("fira_margin", 0.01)), scale=scale, lag=bool(group.get("lag_norm", False)))
+        d, fira, lag = float(group["d"]), bool(group.get("enable_fira_for_adafactor", False)), bool(group.get("lag_norm", False))
+        return (factored_exchanges(came, d, fira, lag), device,
+                plan.stages(grads, cols, d=d, fira=fira, fira_margin=float(group.get("fira_margin", 0.01)), scale=scale, lag=lag))
 
     def _run_fullrank(self, gi, group, key, items):
         device, gdtype, v_fmt, m_fmt, block, m_block, pdtype = key
@@ -898,10 +970,11 @@ class Adafactor8Bit(Optimizer):
         ids = tuple(id(p) for p, _, _ in items)
         pkey = (gi, "fullrank", key, bool(momentum_only), bool(group["maximize"]), sr)
         plan = self._plans.get(pkey)
+        pcs = [self._pieces.get(id(p)) for p, _, _ in items]
         if plan is None or plan.ids != ids:
             plan = FullrankPlan(device, gdtype, v_fmt, m_fmt, block, m_block, sc0["adam"], momentum_only,
                                 group["maximize"], [p for p, _, _ in items], [s for _, _, s in items],
-                                stochastic_round=sr)
+                                stochastic_round=sr, pieces=pcs)
             plan.ids = ids
             self._plans[pkey] = plan
         n = len(items)
@@ -918,8 +991,9 @@ class Adafactor8Bit(Optimizer):
         for i, (p, g, st) in enumerate(items):
             step = st["step"] + 1
             st["step"] = step
-            if sr:
-                cols["sr_base"][i] = sr_base(self._sr_seed(st), step)
+            if sr:                  # a part of a tensor draws the counters of its elements in the whole tensor
+                first = pcs[i].elem0 if pcs[i] is not None else 0
+                cols["sr_base"][i] = (sr_base(self._sr_seed(st), step) + first) & 0xFFFFFFFFFFFFFFFF
             vals = cache.get(step)
             if vals is None:
                 sc = self._step_scalars(group, step)
@@ -942,6 +1016,6 @@ class Adafactor8Bit(Optimizer):
                 elif sc["bc_div"] is not None:
                     scale["bc"][i], scale["bc_mode"][i] = sc["bc_div"], 2
             grads.append(g if g.is_contiguous() else g.contiguous())
-        with torch.cuda.device(device):
-            plan.run(grads, cols, d=float(group["d"]), fira=bool(group.get("enable_fira_for_adafactor", False)),
-                     fira_margin=float(group.get("fira_margin", 0.01)), scale=scale, lag=bool(group.get("lag_norm", False)))
+        d, fira, lag = float(group["d"]), bool(group.get("enable_fira_for_adafactor", False)), bool(group.get("lag_norm", False))
+        return (fullrank_exchanges(scale is not None, d, fira, bool(plan.cfg.momentum_only), lag), device,
+                plan.stages(grads, cols, d=d, fira=fira, fira_margin=float(group.get("fira_margin", 0.01)), scale=scale, lag=lag))

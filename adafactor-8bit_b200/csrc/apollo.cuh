@@ -439,7 +439,7 @@ apollo_apply_lowp_kernel(void *param, const void *grad, int grad_dtype, int nega
 __global__ void __launch_bounds__(256)
 apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, const float *sf,
                     const af8_apollo_scalars *sc, int64_t rows, int64_t cols, int right, int scale_tensor,
-                    int fira, int front, float sqrt_scale, float decay, int has_decay)
+                    int fira, int front, float sqrt_scale, float decay, int has_decay, uint16_t *param_copy)
 {
     const float us = sc->update_scale, fs = sc->fira;
     const int64_t n = rows * cols;
@@ -457,6 +457,7 @@ apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, 
             if (scale_tensor) pv = __fmaf_rn(__fmul_rn(us, f), g, pv);       // optimizer.py:3079
             else pv = __fmaf_rn(__fmul_rn(us, g), f, pv);                    // optimizer.py:3077
             param[idx] = pv;
+            if (param_copy) param_copy[idx] = (uint16_t)f32_to_bf16_rn_bits(pv);   // bf16 compute copy
         }
     }
 }
@@ -468,7 +469,8 @@ template <bool BF16, bool LOWP>
 __global__ void __launch_bounds__(256)
 apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ grad, int negate, const float *__restrict__ sf,
                         const af8_apollo_scalars *__restrict__ sc, int64_t rows, int64_t cols, int right, int scale_tensor,
-                        int fira, int front, float sqrt_scale, float decay, int has_decay, const ApolloLowp P)
+                        int fira, int front, float sqrt_scale, float decay, int has_decay, const ApolloLowp P,
+                        uint16_t *__restrict__ param_copy)
 {
     float *const param = static_cast<float *>(param_v);
     const float us = sc->update_scale, fs = sc->fira;
@@ -540,6 +542,12 @@ apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ gra
         }
         pp[0] = make_float4(pv[0], pv[1], pv[2], pv[3]);
         pp[1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
+        if (param_copy) {                                                    // bf16 compute copy, round to nearest
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) o[k] = f32_to_bf16_rn_bits(pv[2 * k]) | (f32_to_bf16_rn_bits(pv[2 * k + 1]) << 16);
+            *reinterpret_cast<uint4 *>(param_copy + idx) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
     }
 }
 
@@ -925,10 +933,14 @@ extern "C" int af8_apollo_scales_batch(const af8_apollo_finish_tensor *host_tens
 extern "C" int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stochastic_round, uint64_t sr_base,
                                 const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
                                 const af8_apollo_scalars *scalars, int64_t rows, int64_t cols,
-                                const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *stream)
+                                const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *param_copy,
+                                void *stream)
 {
     using namespace af8;
     if (!param || !grad || !sf || !scalars || !in) return fail(AF8_ERR_INVALID, "af8_apollo_apply: null argument");
+    if (param_copy && (param_dtype != AF8_F32 || !aligned16(param_copy)))
+        return fail(AF8_ERR_INVALID, "af8_apollo_apply: param_copy needs fp32 parameters and a 16-byte aligned address");
+    uint16_t *const pc = static_cast<uint16_t *>(param_copy);
     if (grad_dtype != AF8_F32 && grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_apply: gradients must be fp32 or bf16");
     if (param_dtype != AF8_F32 && param_dtype != AF8_BF16 && param_dtype != AF8_F16) return fail(AF8_ERR_INVALID, "af8_apollo_apply: bad param_dtype %d", param_dtype);
     if (stochastic_round && param_dtype == AF8_F32) return fail(AF8_ERR_INVALID, "af8_apollo_apply: stochastic rounding applies to bf16 / fp16 parameters only");
@@ -941,7 +953,7 @@ extern "C" int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stocha
         if (gv > 148 * 8) gv = 148 * 8;
         cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define AF8_APOLLO_APPLY(B, L) apollo_apply_vec_kernel<B, L><<<(int)gv, 256, 0, st>>>(param, grad, negate, sf, scalars, rows, cols, right, \
-        in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay, P)
+        in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay, P, pc)
         if (grad_dtype == AF8_BF16) { if (lowp) AF8_APOLLO_APPLY(true, true); else AF8_APOLLO_APPLY(true, false); }
         else { if (lowp) AF8_APOLLO_APPLY(false, true); else AF8_APOLLO_APPLY(false, false); }
 #undef AF8_APOLLO_APPLY
@@ -961,7 +973,7 @@ extern "C" int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stocha
     if (g > 148 * 16) g = 148 * 16;
     apollo_apply_kernel<<<(int)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<float *>(param), grad, grad_dtype, negate, sf, scalars, rows, cols, rows >= cols ? 1 : 0,
-        in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay);
+        in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay, pc);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }

@@ -408,8 +408,10 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
                     // optimizer.py:2039, 803, 874 (a zero update still applies the decay and the rounding)
                     const float uu = zero_upd ? 0.0f : __fmul_rn(u, fira);
                     const float pv = param_load(sT.param, flat, L.param_dtype);
-                    param_store_bits(sT.param, flat, param_step_bits(pv, sT.decay, step_mul, uu, L.param_dtype, L.sr, sT.sr_base, flat),
-                                     L.param_dtype);
+                    const uint32_t pbits = param_step_bits(pv, sT.decay, step_mul, uu, L.param_dtype, L.sr, sT.sr_base, flat);
+                    param_store_bits(sT.param, flat, pbits, L.param_dtype);
+                    if (sT.param_copy != nullptr && L.param_dtype == AF8_F32)       // bf16 compute copy
+                        static_cast<uint16_t *>(sT.param_copy)[flat] = (uint16_t)f32_to_bf16_rn_bits(__uint_as_float(pbits));
                 }
             }
             if (writes && m_quant) s_m[i] = mj;
@@ -898,6 +900,9 @@ factored_update_vec_kernel(const FactoredLaunch L)
                     }
                     *reinterpret_cast<float4 *>(pp) = make_float4(p[0], p[1], p[2], p[3]);
                     *reinterpret_cast<float4 *>(pp + 4) = make_float4(p[4], p[5], p[6], p[7]);
+                    if (sT.param_copy != nullptr)                                    // bf16 compute copy
+                        *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(sT.param_copy) + flat) =
+                            make_uint4(bf16x2_rn(p[0], p[1]), bf16x2_rn(p[2], p[3]), bf16x2_rn(p[4], p[5]), bf16x2_rn(p[6], p[7]));
                 }
                 if (has_m && !m_quant) {
                     *reinterpret_cast<float4 *>(sT.m_f32 + flat) = make_float4(mj[0], mj[1], mj[2], mj[3]);
@@ -970,11 +975,12 @@ inline int validate_factored(const af8_factored_cfg &c, const af8_factored_tenso
         if (t.rows <= 0 || t.cols <= 0) return fail(AF8_ERR_INVALID, "factored tensor %d: empty shape", i);
         if (c.aligned8) {
             if (t.cols % 8 != 0) return fail(AF8_ERR_INVALID, "factored tensor %d: aligned8 needs cols %% 8 == 0", i);
-            const void *ptrs[] = {t.param, t.grad, t.m_q, t.m_f32, t.inv_col, t.inv_col_conf};
+            const void *ptrs[] = {t.param, t.grad, t.m_q, t.m_f32, t.inv_col, t.inv_col_conf, t.param_copy};
             for (const void *q : ptrs)
                 if (q && (reinterpret_cast<uintptr_t>(q) & 15u)) return fail(AF8_ERR_INVALID, "factored tensor %d: aligned8 needs 16-byte aligned arrays", i);
         }
         if (t.rows * t.cols >= ((int64_t)1 << 40)) return fail(AF8_ERR_UNSUPPORTED, "factored tensor %d: too large", i);
+        if (t.param_copy && c.param_dtype != AF8_F32) return fail(AF8_ERR_INVALID, "factored tensor %d: a bf16 copy exists only of fp32 parameters", i);
         if (!t.param || !t.grad || !t.row_sum || !t.col_sum || !t.inv_row || !t.inv_col)
             return fail(AF8_ERR_INVALID, "factored tensor %d: null pointer", i);
         if (c.came && (!t.inv_row_conf || !t.inv_col_conf)) return fail(AF8_ERR_INVALID, "factored tensor %d: CAME needs the confidence vectors", i);

@@ -41,7 +41,8 @@ norm_finalize_kernel(const af8_norm_tensor *tensors, const void *block_sumsq, af
     }
     if (tid != 0) return;
 
-    float norm = __double2float_rn(sqrt(s_acc[0]));
+    const double total = T.n_blocks < 0 ? *reinterpret_cast<const double *>(static_cast<uintptr_t>(T.first_block)) : s_acc[0];
+    float norm = __double2float_rn(sqrt(total));
     const float alpha = T.alpha_dev ? *T.alpha_dev : T.alpha;
     af8_dyn_scalars out = dyn[blockIdx.x];
     out.norm = norm;
@@ -245,6 +246,8 @@ inline int validate_fullrank_table(const af8_fullrank_cfg &c, const af8_fullrank
         next += (t.numel + c.block - 1) / c.block;
         if (!t.param || !t.grad) return fail(AF8_ERR_INVALID, "tensor %d: null param or grad", i);
         if (!aligned16(t.param) || !aligned16(t.grad)) return fail(AF8_ERR_INVALID, "tensor %d: param and grad must be 16-byte aligned", i);
+        if (t.param_copy && (c.param_dtype != AF8_F32 || !aligned16(t.param_copy)))
+            return fail(AF8_ERR_INVALID, "tensor %d: param_copy needs fp32 parameters and a 16-byte aligned address", i);
         if (v_quant) {
             if (!t.v_q || !t.v_scale || !t.v_min_log) return fail(AF8_ERR_INVALID, "tensor %d: null quantised V state", i);
             if (!aligned16(t.v_q)) return fail(AF8_ERR_INVALID, "tensor %d: v_q must be 16-byte aligned", i);

@@ -688,6 +688,22 @@ fullrank_fast_kernel(const FullrankLaunch L)
             }
         }
 
+        // ---- optional bf16 compute copy of the fp32 parameter (round to nearest) ----
+        if (PB == 4 && !bad && sT.param_copy != nullptr) {
+            uint16_t *ca = static_cast<uint16_t *>(sT.param_copy) + base + oa;
+            uint16_t *cb = static_cast<uint16_t *>(sT.param_copy) + base + ob;
+            if (full) {
+                *reinterpret_cast<uint2 *>(ca) = make_uint2(bf16x2_rn(p[0], p[1]), bf16x2_rn(p[2], p[3]));
+                *reinterpret_cast<uint2 *>(cb) = make_uint2(bf16x2_rn(p[4], p[5]), bf16x2_rn(p[6], p[7]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (j < nva) ca[j] = (uint16_t)f32_to_bf16_rn_bits(p[j]);
+                    if (j < nvb) cb[j] = (uint16_t)f32_to_bf16_rn_bits(p[j + 4]);
+                }
+            }
+        }
+
         // ---- momentum requantisation: one warp = one M block (optimizer.py:510, 518) ----
         {
             float amx = 0.0f;

@@ -211,9 +211,10 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                 if (writes) {
                     if (DYN) u = zero_upd ? 0.0f : __fmul_rn(u, fira);
                     const float pv = param_load(sT.param, base + i, L.param_dtype);
-                    param_store_bits(sT.param, base + i,
-                                     param_step_bits(pv, sT.decay, step_mul, u, L.param_dtype, L.sr, sT.sr_base, base + i),
-                                     L.param_dtype);
+                    const uint32_t pbits = param_step_bits(pv, sT.decay, step_mul, u, L.param_dtype, L.sr, sT.sr_base, base + i);
+                    param_store_bits(sT.param, base + i, pbits, L.param_dtype);
+                    if (sT.param_copy != nullptr && L.param_dtype == AF8_F32)       // bf16 compute copy
+                        static_cast<uint16_t *>(sT.param_copy)[base + i] = (uint16_t)f32_to_bf16_rn_bits(__uint_as_float(pbits));
                 }
             }
             if (writes) {

@@ -101,7 +101,7 @@ param_scale_finalize_kernel(const af8_scale_tensor *tensors, const float *block_
         __syncthreads();
     }
     if (tid != 0) return;
-    const float norm = __double2float_rn(sqrt(s_acc[0]));
+    const float norm = __double2float_rn(sqrt(T.total ? *T.total : s_acc[0]));
     const float rms = __fdiv_rn(norm, T.sqrt_n);                    // optimizer.py:851-852
     float alpha = __fmul_rn(fmaxf(rms, T.eps2), T.rho);             // optimizer.py:853
     if (T.bc_mode == 1) alpha = __fmul_rn(alpha, T.bc);             // optimizer.py:2026
@@ -118,22 +118,26 @@ param_scale_finalize_kernel(const af8_scale_tensor *tensors, const float *block_
 
 }  // namespace af8
 
-extern "C" int af8_param_scale(const af8_scale_tensor *host_tensors, af8_scale_tensor *dev_tensors,
-                               int32_t n_tensors, float *chunk_sumsq, void *dev_table, int64_t table_stride,
-                               int64_t alpha_offset, int64_t decay_offset, void *stream)
+namespace af8 {
+inline int param_scale_layout_ok(int64_t table_stride, int64_t alpha_offset, int64_t decay_offset)
+{
+    return !(table_stride <= 0 || alpha_offset < 0 || decay_offset < 0 || alpha_offset + 4 > table_stride ||
+             decay_offset + 4 > table_stride || (alpha_offset & 3) || (decay_offset & 3) || (table_stride & 3));
+}
+}  // namespace af8
+
+extern "C" int af8_param_sumsq(const af8_scale_tensor *host_tensors, af8_scale_tensor *dev_tensors,
+                               int32_t n_tensors, float *chunk_sumsq, void *stream)
 {
     using namespace af8;
-    if (!host_tensors || !dev_tensors || !chunk_sumsq || !dev_table) return fail(AF8_ERR_INVALID, "af8_param_scale: null argument");
-    if (n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_param_scale: n_tensors must be positive");
-    if (table_stride <= 0 || alpha_offset < 0 || decay_offset < 0 || alpha_offset + 4 > table_stride ||
-        decay_offset + 4 > table_stride || (alpha_offset & 3) || (decay_offset & 3) || (table_stride & 3))
-        return fail(AF8_ERR_INVALID, "af8_param_scale: bad table layout");
+    if (!host_tensors || !dev_tensors || !chunk_sumsq) return fail(AF8_ERR_INVALID, "af8_param_sumsq: null argument");
+    if (n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_param_sumsq: n_tensors must be positive");
     int64_t next = 0;
     for (int i = 0; i < n_tensors; ++i) {
         const af8_scale_tensor &t = host_tensors[i];
-        if (!t.param || t.numel <= 0) return fail(AF8_ERR_INVALID, "af8_param_scale: tensor %d is empty", i);
-        if (reinterpret_cast<uintptr_t>(t.param) & 15u) return fail(AF8_ERR_INVALID, "af8_param_scale: tensor %d: param must be 16-byte aligned", i);
-        if (t.first_chunk != next) return fail(AF8_ERR_INVALID, "af8_param_scale: tensor %d: first_chunk %lld, expected %lld", i, (long long)t.first_chunk, (long long)next);
+        if (!t.param || t.numel <= 0) return fail(AF8_ERR_INVALID, "af8_param_sumsq: tensor %d is empty", i);
+        if (reinterpret_cast<uintptr_t>(t.param) & 15u) return fail(AF8_ERR_INVALID, "af8_param_sumsq: tensor %d: param must be 16-byte aligned", i);
+        if (t.first_chunk != next) return fail(AF8_ERR_INVALID, "af8_param_sumsq: tensor %d: first_chunk %lld, expected %lld", i, (long long)t.first_chunk, (long long)next);
         next += (t.numel + SCALE_CHUNK - 1) / SCALE_CHUNK;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -143,10 +147,33 @@ extern "C" int af8_param_scale(const af8_scale_tensor *host_tensors, af8_scale_t
     if (grid > next) grid = next;
     param_sumsq_kernel<<<(int)grid, 256, 0, st>>>(L);
     AF8_CUDA_TRY(cudaGetLastError());
-    param_scale_finalize_kernel<<<n_tensors, 256, 0, st>>>(dev_tensors, chunk_sumsq, static_cast<uint8_t *>(dev_table),
-                                                         table_stride, alpha_offset, decay_offset);
+    return AF8_OK;
+}
+
+extern "C" int af8_param_scale_finish(const af8_scale_tensor *dev_tensors, int32_t n_tensors, const float *chunk_sumsq,
+                                      void *dev_table, int64_t table_stride, int64_t alpha_offset, int64_t decay_offset,
+                                      void *stream)
+{
+    using namespace af8;
+    if (!dev_tensors || !chunk_sumsq || !dev_table) return fail(AF8_ERR_INVALID, "af8_param_scale_finish: null argument");
+    if (n_tensors <= 0) return fail(AF8_ERR_INVALID, "af8_param_scale_finish: n_tensors must be positive");
+    if (!param_scale_layout_ok(table_stride, alpha_offset, decay_offset)) return fail(AF8_ERR_INVALID, "af8_param_scale_finish: bad table layout");
+    param_scale_finalize_kernel<<<n_tensors, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        dev_tensors, chunk_sumsq, static_cast<uint8_t *>(dev_table), table_stride, alpha_offset, decay_offset);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
+}
+
+extern "C" int af8_param_scale(const af8_scale_tensor *host_tensors, af8_scale_tensor *dev_tensors,
+                               int32_t n_tensors, float *chunk_sumsq, void *dev_table, int64_t table_stride,
+                               int64_t alpha_offset, int64_t decay_offset, void *stream)
+{
+    using namespace af8;
+    if (!dev_table) return fail(AF8_ERR_INVALID, "af8_param_scale: null argument");
+    if (!param_scale_layout_ok(table_stride, alpha_offset, decay_offset)) return fail(AF8_ERR_INVALID, "af8_param_scale: bad table layout");
+    int rc = af8_param_sumsq(host_tensors, dev_tensors, n_tensors, chunk_sumsq, stream);
+    if (rc) return rc;
+    return af8_param_scale_finish(dev_tensors, n_tensors, chunk_sumsq, dev_table, table_stride, alpha_offset, decay_offset, stream);
 }
 
 extern "C" int af8_scale_chunk(void) { return af8::SCALE_CHUNK; }

@@ -139,7 +139,10 @@ typedef struct af8_fullrank_tensor {
     uint64_t sr_base;       /* stochastic rounding: seed * 0x9E3779B97F4A7C15 + step * 0xD1B54A32D192ED03
                                (mod 2^64) with the parameter's state["sr_seed"] and step number
                                (optimizer.py:1889-1892, 2040); element i draws from counter sr_base + i */
-    uint64_t reserved2;
+    void *param_copy;       /* optional bf16 copy of the updated parameter (numel 16-bit words, 16-byte aligned),
+                               written next to the fp32 parameter with round-to-nearest: the compute copy of a
+                               mixed-precision run, e.g. this rank's slice of an all-gather buffer.  NULL: none.
+                               Only with cfg.param_dtype == AF8_F32.  No counterpart in the reference. */
 } af8_fullrank_tensor;
 
 /* Launch-wide configuration: everything that selects a kernel variant. */
@@ -198,7 +201,11 @@ AF8_API int af8_fullrank_upload(const af8_fullrank_cfg *cfg,
 /* Per-tensor description for af8_norm_finalize. */
 typedef struct af8_norm_tensor {
     int64_t first_block;    /* first entry of block_sumsq that belongs to the tensor */
-    int64_t n_blocks;
+    int64_t n_blocks;       /* number of entries; or -1: first_block then holds the device ADDRESS of one double,
+                               the tensor's whole sum of squares, and block_sumsq is not read for this tensor.
+                               That form serves a tensor whose elements are spread over several launch tables or
+                               several GPUs: the caller adds up the pieces' partial sums (and all-reduces them)
+                               before this call; sqrt_n and clip_div then describe the whole tensor. */
     float *fira_prev;       /* device scalar: previous limited norm (state key
                                "fira_prev_norm"); NULL when the limiter is off */
     int32_t fira_has_prev;  /* 0 on the first limited step of this tensor */
@@ -301,6 +308,7 @@ typedef struct af8_factored_tensor {
                                    first unit in af8_factored_small (its row blocks, then its column blocks) */
     uint64_t sr_base;           /* stochastic rounding counter origin, as af8_fullrank_tensor.sr_base;
                                    element r*cols + c draws from counter sr_base + r*cols + c */
+    void *param_copy;           /* optional bf16 copy of the updated fp32 parameter, as af8_fullrank_tensor.param_copy */
 } af8_factored_tensor;
 
 enum {
@@ -481,11 +489,14 @@ AF8_API int af8_apollo_scales_batch(const af8_apollo_finish_tensor *host_tensors
 /* param_dtype AF8_F32, AF8_BF16 or AF8_F16.  A 16-bit parameter is rounded to nearest after the decay and
  * after the update, or, with stochastic_round, p*decay + (g*final_scale)*update_scale is formed in binary32
  * and rounded stochastically with the counter generator at sr_base (see af8_fullrank_tensor.sr_base;
- * optimizer.py:3043-3079, apollo_apply_{bf16,fp16}_{sr,det}). */
+ * optimizer.py:3043-3079, apollo_apply_{bf16,fp16}_{sr,det}).
+ * param_copy: optional bf16 copy of the updated fp32 parameter (rows*cols 16-bit words, 16-byte aligned),
+ * as af8_fullrank_tensor.param_copy; NULL for none. */
 AF8_API int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stochastic_round, uint64_t sr_base,
                              const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
                              const af8_apollo_scalars *scalars, int64_t rows, int64_t cols,
-                             const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *stream);
+                             const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *param_copy,
+                             void *stream);
 
 /* ------------------------------------------------------------------------ */
 /* Step without caller-provided working memory                               */
@@ -552,6 +563,9 @@ typedef struct af8_scale_tensor {
     int32_t bc_mode;            /* 0: none, 1: alpha *= bc, 2: alpha /= bc */
     int32_t scale_weight_decay; /* 1: decay uses alpha, 0: decay uses rho */
     int32_t param_dtype;        /* AF8_F32, AF8_BF16 or AF8_F16 */
+    const double *total;        /* when not NULL: device location of the whole tensor's sum of squares, used by
+                                   af8_param_scale_finish instead of this table entry's partial sums (a tensor
+                                   spread over several tables or GPUs; sqrt_n then describes the whole tensor) */
 } af8_scale_tensor;
 
 /* alpha = max(||p|| / sqrt(n), eps2) * rho (then bias correction) and
@@ -567,6 +581,17 @@ AF8_API int af8_param_scale(const af8_scale_tensor *host_tensors,
                             af8_scale_tensor *dev_tensors, int32_t n_tensors,
                             float *chunk_sumsq, void *dev_table, int64_t table_stride,
                             int64_t alpha_offset, int64_t decay_offset, void *stream);
+
+/* The two halves of af8_param_scale, for callers that must combine partial sums between them (a tensor
+ * spread over several GPUs: sum the tensor's entries of chunk_sumsq, all-reduce, point
+ * af8_scale_tensor.total at the result).  af8_param_sumsq validates and uploads the table and fills
+ * chunk_sumsq; af8_param_scale_finish evaluates alpha / decay from the device table left by it.
+ * No counterpart in the reference (single-GPU). */
+AF8_API int af8_param_sumsq(const af8_scale_tensor *host_tensors, af8_scale_tensor *dev_tensors,
+                            int32_t n_tensors, float *chunk_sumsq, void *stream);
+AF8_API int af8_param_scale_finish(const af8_scale_tensor *dev_tensors, int32_t n_tensors,
+                                   const float *chunk_sumsq, void *dev_table, int64_t table_stride,
+                                   int64_t alpha_offset, int64_t decay_offset, void *stream);
 
 /* Number of parameters per partial sum of af8_param_scale. */
 AF8_API int af8_scale_chunk(void);

@@ -47,7 +47,7 @@ def test_struct_sizes_match_header():
     assert _native.FULLRANK_TENSOR.itemsize == 144
     assert _native.DYN_SCALARS.itemsize == 32
     assert _native.NORM_TENSOR.itemsize == 64
-    assert _native.SCALE_TENSOR.itemsize == 56
+    assert _native.SCALE_TENSOR.itemsize == 64
     assert ctypes.sizeof(_native.FullrankCfg) == 48
 
 
