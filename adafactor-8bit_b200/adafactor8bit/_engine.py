@@ -587,7 +587,7 @@ class FactoredPlan:
                 raise RuntimeError("the factored kernels update contiguous 2-D parameters")
         self.rows = np.array([p.shape[0] for p in self.params], dtype=np.int64)
         self.cols = np.array([p.shape[1] for p in self.params], dtype=np.int64)
-        self.full_rows = np.array([pc.full_rows if pc is not None else p.shape[0]
+        self.full_rows = np.array([(pc.full_rows or p.shape[0]) if pc is not None else p.shape[0]
                                    for p, pc in zip(self.params, self.pieces)], dtype=np.int64)
         self.row0 = np.array([pc.row0 if pc is not None else 0 for pc in self.pieces], dtype=np.int64)
         self.numel = self.rows * self.cols

@@ -1,5 +1,8 @@
-"""ShardedAdafactor8Bit on two GPUs over NCCL: the sharded step must equal the single-GPU
-step bit for bit (every tensor is updated by exactly one rank from identical inputs).
+"""ShardedAdafactor8Bit on two GPUs over NCCL: the sharded step must equal the single-GPU step.
+Tensors are cut across the two ranks and across two parts per rank; block-local arithmetic is
+identical by construction, and the statistics of cut tensors (update norms, RMS(p), row / column
+sums) are all-reduced in binary64, which reproduces the single-GPU values (a different rounding of
+a binary64 sum would have to fall on a binary32 rounding boundary to show).
 Skipped on machines with fewer than two GPUs."""
 import os
 import socket
@@ -12,7 +15,7 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(300, 200), (4096,), (2048,), (128, 256), (64, 2048)]
+SHAPES = [(300, 200), (4096,), (2048,), (128, 256), (64, 2048), (512, 384), (20000,)]
 
 
 def _inputs(variant="f32"):
@@ -23,6 +26,8 @@ def _inputs(variant="f32"):
     hp = dict(cases.CASES["adamw_fira_bf16"]["hp"])
     if variant == "bf16_sr":
         hp["stochastic_round_writeback"] = True
+    if variant == "adamw_noclip":       # no whole-tensor statistic at all
+        hp = dict(cases.CASES["adamw_uf8_al8"]["hp"])
     if variant == "adafactor":          # factored second moments, relative step, parameter scaling, clip
         hp = dict(cases.CASES["adafactor_factored"]["hp"])
     if variant == "came":
@@ -57,13 +62,21 @@ def _worker(rank, world, port, out, variant):
         params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(dev).to(_pdt(variant))) for p in p0]
         for p in params:
             p.grad_dtype = None
-        opt = ShardedAdafactor8Bit(params, **hp)
+        copy = variant == "bf16_copy"
+        opt = ShardedAdafactor8Bit(params, parts=2, min_piece=1, compute_dtype=torch.bfloat16 if copy else None, **hp)
+        assert any(len(lst) > 1 for lst in opt.pieces_of) or variant == "apollo", "the case must cut a tensor"
         for t in (1, 2, 3):
             for p, g in zip(params, grads[t]):
                 p.grad = _bf16(g, p.shape, dev)
             opt.step()
         torch.cuda.synchronize()
+        assert opt.gather_log == [0, 1]
         out[rank] = [p.detach().float().cpu().numpy().copy() for p in params]
+        if copy:                                    # the model's view is bf16; the fp32 masters stay sharded
+            assert all(p.dtype == torch.bfloat16 for p in params)
+            masters = opt.master_params(dst=0)
+            if rank == 0:
+                out["masters"] = [m.numpy().copy() for m in masters]
         full = opt.full_state_dict(dst=0)          # the merged checkpoint, in the unsharded layout
         if rank == 0:
             out["full"] = full
@@ -72,7 +85,7 @@ def _worker(rank, world, port, out, variant):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("variant", ["f32", "bf16_sr", "adafactor", "came", "apollo"])
+@pytest.mark.parametrize("variant", ["f32", "adamw_noclip", "bf16_sr", "adafactor", "came", "apollo", "bf16_copy"])
 def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
     import torch.multiprocessing as mp
     sys.path.insert(0, os.path.join(ROOT, "adafactor-8bit_b200"))
@@ -93,7 +106,13 @@ def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
     torch.cuda.synchronize()
     for rank in (0, 1):
         for a, p in zip(out[rank], params):
-            assert np.array_equal(a, p.detach().float().cpu().numpy())
+            want = p.detach()
+            if variant == "bf16_copy":               # every rank reads the rounded copy of the masters
+                want = want.to(torch.bfloat16)
+            assert np.array_equal(a, want.float().cpu().numpy())
+    if variant == "bf16_copy":
+        for a, p in zip(out["masters"], params):
+            assert np.array_equal(a, p.detach().cpu().numpy())
     # the merged checkpoint equals the one-GPU optimizer's, entry by entry
     full, want = out["full"], opt.state_dict()
     assert sorted(full["state"]) == sorted(want["state"])
