@@ -28,6 +28,15 @@ paths and of CAME's residual -- is summed locally, all-reduced in one small floa
 round (at most four rounds per step, only tensors that are cut take part) and finished identically
 on every owner.  Tensors that are not cut need no exchange.
 
+Exchange of the parameters.  On CUDA the flat space is allocated as symmetric memory
+(torch.distributed._symmetric_memory: every rank maps the other ranks' buffers), and a rank
+publishes a finished cell by copying it into the same place of every peer's buffer with plain
+asynchronous device copies, one stream per peer.  Those run on the copy engines: they take no SM
+away from the update kernels of the next part, which the kernels of an NCCL all-gather do (the
+update kernels are persistent grids sized to fill the GPU).  One small NCCL all-reduce per step,
+enqueued behind the copies, tells every rank that all cells have arrived.  Where symmetric memory
+is not available (or with `exchange="nccl"`) the cells travel by in-place `all_gather_into_tensor`.
+
 Mixed precision.  With `compute_dtype=torch.bfloat16` the flat space holds the bf16 compute copy of
 the parameters (what the model reads); the fp32 master values exist only for a rank's own cells, and
 the update kernels write the rounded copy straight into the gather buffer next to the master.  The
@@ -179,12 +188,13 @@ class ShardedAdafactor8Bit:
         module text).  The parameters passed in supply the initial master values; afterwards they are
         bf16 views of the gather buffer.
     min_piece: tensors with fewer elements are never cut.
+    exchange: "auto" (peer copies over symmetric memory when it can be set up, else NCCL), "push" or "nccl".
     inner_factory: class of the per-rank optimizer (the default is Adafactor8Bit; the CPU tests of the
         sharding logic plug in a stock torch optimizer, which sees the pieces as ordinary parameters).
     """
 
     def __init__(self, params, process_group=None, inner_factory=Adafactor8Bit, parts=None, compute_dtype=None,
-                 min_piece=1 << 20, **kwargs):
+                 min_piece=1 << 20, exchange="auto", **kwargs):
         self.group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
@@ -228,8 +238,8 @@ class ShardedAdafactor8Bit:
                  for i in range(len(all_params))]
         total = sum(_pad(n, UNIT) for n in numels)
         if parts is None:
-            parts = max(1, min(4, total // max(1, self.world) // (32 << 20)))
-        self.parts = parts = max(1, int(parts)) if self.world > 1 else 1
+            parts = max(1, min(4, total // max(1, self.world) // (32 << 20))) if self.world > 1 else 1
+        self.parts = parts = max(1, int(parts))
         n_cells = self.parts * self.world
         self.cell, offsets = plan_layout([(numels[i], rules[i][0], rules[i][1]) for i in range(len(numels))], n_cells)
         self.offsets = offsets
@@ -265,7 +275,14 @@ class ShardedAdafactor8Bit:
         self.xbuf = torch.zeros(max(1, sum(sizes)), dtype=torch.float64, device=dev) if native else None
         # the flat space = the gather buffer
         gather_dtype = compute_dtype if compute_dtype is not None else dt
-        self.flat = torch.zeros(n_cells * cell, dtype=gather_dtype, device=dev)
+        if exchange not in ("auto", "push", "nccl"):
+            raise ValueError("exchange must be 'auto', 'push' or 'nccl'")
+        self.flat, self.peer_flat = None, None
+        if exchange != "nccl" and self.world > 1 and dev.type == "cuda":
+            self.flat, self.peer_flat = self._symmetric_buffer(n_cells * cell, gather_dtype, dev, exchange == "push")
+        if self.flat is None:
+            self.flat = torch.zeros(n_cells * cell, dtype=gather_dtype, device=dev)
+        self.exchange = "push" if self.peer_flat is not None else "nccl"
         self.master = (torch.zeros(self.parts * cell, dtype=torch.float32, device=dev) if compute_dtype is not None else None)
         owned_numel = 0
         local = []                       # (tensor, lo, hi, part, piece parameter)
@@ -356,6 +373,9 @@ class ShardedAdafactor8Bit:
                                            if id(all_params[i]) in seeds}
             self.inner._apollo_seed_counter = nxt
         self.gather_stream = None
+        self._push_streams, self._pushed = None, False
+        self._fence = torch.zeros(1, dtype=torch.float32, device=dev) if self.peer_flat is not None else None
+        self._pipelined = self._in_step = False
         self.gather_log = []          # units in the order this rank gathered them during the last step
 
     # -- views of the inner optimizer ---------------------------------------------------------------
@@ -394,6 +414,8 @@ class ShardedAdafactor8Bit:
     def local_step(self, closure=None):
         """Update the pieces this rank owns.  With the native optimizer and cut tensors this includes
         the exchange of their statistics, so every rank must call it."""
+        if not self._in_step:
+            self._pipelined = False           # called on its own: no gather
         self._bind_grads()
         if self.xbuf is not None and self.rounds:
             self.xbuf.zero_()
@@ -412,20 +434,74 @@ class ShardedAdafactor8Bit:
             a = self._round_start[r]
             dist.all_reduce(self.xbuf[a:a + n], group=self.group)
 
+    def _symmetric_buffer(self, numel, dtype, dev, required):
+        """-> (buffer, [every rank's buffer as a tensor of this process]) in symmetric memory, or
+        (None, None) when it cannot be set up on every rank."""
+        ok, buf, peers = 1, None, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            buf = symm.empty(numel, dtype=dtype, device=dev)
+            group = self.group if self.group is not None else dist.group.WORLD
+            handle = symm.rendezvous(buf, group)
+            peers = [handle.get_buffer(r, (numel,), dtype) for r in range(self.world)]
+            buf.zero_()
+            self._symm_handle = handle
+        except Exception as e:          # no fabric / file-descriptor passing, old driver, ...
+            ok, self._symm_error = 0, repr(e)
+        flag = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 1:
+            return buf, peers
+        if required:
+            raise RuntimeError("symmetric memory could not be set up on every rank: " + getattr(self, "_symm_error", "another rank failed"))
+        return None, None
+
     def _unit(self, k):
         n = self.world * self.cell
         return self.flat[k * n:(k + 1) * n]
 
     def _gather_unit(self, k):
-        unit = self._unit(k)
+        """Publish this rank's cell of unit k (on the current stream's order)."""
         self.gather_log.append(k)
-        if self.world > 1:
+        if self.world == 1:
+            return
+        a = (k * self.world + self.rank) * self.cell
+        if self.peer_flat is None:
+            unit = self._unit(k)
             dist.all_gather_into_tensor(unit, unit[self.rank * self.cell:(self.rank + 1) * self.cell], group=self.group)
+            return
+        cur = torch.cuda.current_stream(self.flat.device)
+        if self._push_streams is None:
+            self._push_streams = [torch.cuda.Stream(device=self.flat.device) for _ in range(self.world)]
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        mine = self.flat[a:a + self.cell]
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            st = self._push_streams[r]
+            with torch.cuda.stream(st):
+                st.wait_event(ev)
+                self.peer_flat[r][a:a + self.cell].copy_(mine, non_blocking=True)     # a copy-engine transfer over NVLink
+        self._pushed = True
+
+    def _gather_fence(self):
+        """After the last unit: when this returns (in stream order), every rank's cells have arrived here."""
+        if self.peer_flat is None or self.world == 1 or not self._pushed:
+            return
+        cur = torch.cuda.current_stream(self.flat.device)
+        for r in range(self.world):
+            if r != self.rank:
+                cur.wait_stream(self._push_streams[r])
+        dist.all_reduce(self._fence, group=self.group)       # behind this rank's copies; complete only when all ranks got there
+        self._pushed = False
 
     def gather(self):
-        """In-place all-gather of every unit of the flat parameter buffer, in unit order."""
+        """Publish every unit of the flat parameter buffer, in unit order, and wait (in stream order)
+        for the other ranks' cells."""
         for k in range(self.parts):
             self._gather_unit(k)
+        self._gather_fence()
 
     def _after_part(self, k):
         if not self._pipelined:
@@ -450,7 +526,13 @@ class ShardedAdafactor8Bit:
         if self.gather_stream is None:
             self.gather_stream = torch.cuda.Stream(device=self.flat.device)
         self._main = torch.cuda.current_stream(self.flat.device)
-        loss = self.local_step(closure)
+        self._in_step = True
+        try:
+            loss = self.local_step(closure)
+        finally:
+            self._in_step = False
+        with torch.cuda.stream(self.gather_stream):
+            self._gather_fence()
         self._main.wait_stream(self.gather_stream)
         return loss
 

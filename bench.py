@@ -11,7 +11,12 @@ timed region.  `roofline` describes the dominant kernel against the measured HBM
 copy bandwidth; `cpu_baseline` is the CPU restatement of the reference's step
 timed on this machine's host cores on a bounded sample.
 
-`--impl reference` times that CPU implementation alone, with all host threads.
+`--impl reference` times the reference's own CPU path alone, with all host threads: the unmodified
+reference package (its pure-PyTorch step, use_cuda_kernel=False) when an offline install of it is
+present under baseline/_ref, else the C restatement under oracle/.
+
+With N > 1 ranks the step is sharded ZeRO-1 style over the flat parameter space; the parameters
+that travel are a bf16 compute copy written by the update kernels, the fp32 masters stay sharded.
 """
 import argparse
 import json
@@ -136,8 +141,13 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "tinyllama_adamw_fira"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per parameter, (kernel, gradient dtype) -> bytes
-NCU_TRAFFIC_BPP = {("fullrank_fast_apply", "bf16"): 13.72, ("fullrank_stat", "bf16"): 4.12}
+# dram__bytes_read.sum + dram__bytes_write.sum per parameter from the committed profiler summaries,
+# (kernel, gradient dtype) -> (bytes per parameter, summary file).  A constant taken from a capture of
+# the same kernel on a small case, not a measurement of this run.
+NCU_TRAFFIC_BPP = {
+    ("fullrank_fast_apply", "bf16"): (13.72, "profiles/fullrank_fast_apply_tinyllama_4layers.txt"),
+    ("fullrank_stat", "bf16"): (4.12, "profiles/fullrank_stat_tinyllama_4layers.txt"),
+}
 
 
 def make_groups(wl, named_params):
@@ -233,25 +243,7 @@ def cpu_reference_run(workload, steps, warmup, sample_limit=24_000_000):
         o.set_num_threads(os.cpu_count() or 1)
     wl = WORKLOADS[workload]
     hp = o.hyper(**wl["hp"], param_dtype=wl.get("param", "f32"))
-    shapes = wl["shapes"]()
-    # sample: one of each distinct shape, in order, until the limit is reached
-    seen, sample, sample_names, total = set(), [], [], 0
-    if wl.get("apollo_targets"):
-        sample_limit = min(sample_limit, 6_000_000)      # the CPU projection costs 2*rank flops per parameter
-    for name, shp in shapes:
-        if shp in seen:
-            continue
-        seen.add(shp)
-        n = int(np.prod(shp))
-        if total + n > sample_limit and len(shp) == 2:
-            rows = max(1, (sample_limit - total) // shp[1])
-            shp = (min(rows, shp[0]), shp[1])
-            n = int(np.prod(shp))
-        if n == 0 or total + n > sample_limit * 1.05:
-            continue
-        sample.append(shp)
-        sample_names.append(name)
-        total += n
+    sample, sample_names, total = sample_of(workload, sample_limit)
     spec = dict(dist="rowscale", std=1e-3, zero_frac=0.005, dtype="bf16" if wl["grad"] == "bf16" else "f32")
     params = [cases.make_param(s, 100 + i, dtype=wl.get("param", "f32")) for i, s in enumerate(sample)]
     targets = wl.get("apollo_targets")
@@ -287,20 +279,112 @@ def cpu_reference_run(workload, steps, warmup, sample_limit=24_000_000):
                 ms_per_step=sec * 1e3, sample_params=total)
 
 
+def reference_package_dir():
+    path = os.path.join(ROOT, "baseline", "_ref")
+    return path if os.path.exists(os.path.join(path, "adafactor8bit", "optimizer.py")) else None
+
+
+def sample_of(workload, sample_limit=24_000_000):
+    """The bounded sample both CPU legs step: one tensor of each distinct shape of the workload, in
+    order, the one that would pass the limit cut to whole rows."""
+    wl = WORKLOADS[workload]
+    if wl.get("apollo_targets"):
+        sample_limit = min(sample_limit, 6_000_000)      # the CPU projection costs 2*rank flops per parameter
+    seen, sample, names, total = set(), [], [], 0
+    for name, shp in wl["shapes"]():
+        if shp in seen:
+            continue
+        seen.add(shp)
+        n = int(np.prod(shp))
+        if total + n > sample_limit and len(shp) == 2:
+            rows = max(1, (sample_limit - total) // shp[1])
+            shp = (min(rows, shp[0]), shp[1])
+            n = int(np.prod(shp))
+        if n == 0 or total + n > sample_limit * 1.05:
+            continue
+        sample.append(shp)
+        names.append(name)
+        total += n
+    return sample, names, total
+
+
+def reference_package_run(workload, steps, warmup):
+    """Time the UNMODIFIED reference package (baseline/_ref, its pure-PyTorch CPU path through its own
+    optimizer class) on the bounded sample, all host threads.  Must run in a process that has not
+    imported this repository's package of the same name."""
+    import torch
+    sys.path[:] = [p for p in sys.path if not p.endswith("adafactor-8bit_b200")]
+    sys.path.insert(0, reference_package_dir())
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import adafactor8bit as ref
+    assert os.path.realpath(ref.__file__).startswith(os.path.realpath(reference_package_dir()))
+    import cases
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        torch.set_num_threads(os.cpu_count() or 1)
+    wl = WORKLOADS[workload]
+    sample, names, total = sample_of(workload)
+    spec = dict(dist="rowscale", std=1e-3, zero_frac=0.005, dtype="bf16" if wl["grad"] == "bf16" else "f32")
+    pdt = torch.bfloat16 if wl.get("param") == "bf16" else torch.float32
+    params = []
+    for i, s in enumerate(sample):
+        p = torch.nn.Parameter(torch.from_numpy(cases.make_param(s, 100 + i, dtype=wl.get("param", "f32"))).to(pdt))
+        p.grad_dtype = None                               # a bf16 gradient on an fp32 parameter
+        params.append(p)
+    grads = []
+    for i, s in enumerate(sample):
+        g = cases.make_grad(s, 200 + i, 1, spec)
+        grads.append(torch.from_numpy(g.view(np.int16).copy()).view(torch.bfloat16).reshape(s) if g.dtype == np.uint16
+                     else torch.from_numpy(g))
+    targets = wl.get("apollo_targets")
+    if targets:
+        groups = [dict(params=[p for p, n in zip(params, names) if n in targets])]
+        rest = [p for p, n in zip(params, names) if n not in targets]
+        if rest:
+            groups.append(dict(params=rest, apollo_rank=0))
+        groups = [g for g in groups if g["params"]]
+    else:
+        groups = [dict(params=params)]
+    opt = ref.Adafactor8Bit(groups, use_cuda_kernel=False, **wl["hp"])
+    times = []
+    for it in range(warmup + steps):
+        for p, g in zip(params, grads):
+            p.grad = g
+        t0 = time.perf_counter()
+        opt.step()
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    sec = float(np.mean(times))
+    return dict(value=total / sec / 1e9, unit="Gparams/s", cores=torch.get_num_threads(), kind="reference",
+                sample=f"the unmodified reference package, pure-PyTorch CPU path (use_cuda_kernel=False), on {len(sample)} tensors "
+                       f"of the workload ({total} parameters: one per distinct shape, largest cut to fit), {steps} timed steps "
+                       f"after {warmup} warm-up, {torch.get_num_threads()} torch threads",
+                ms_per_step=sec * 1e3, sample_params=total)
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     wl = WORKLOADS[args.workload]
-    steps = max(1, min(args.steps, 50))     # about 0.1 s per step on the sample
-    warm = max(1, min(args.warmup, 5))
-    r = cpu_reference_run(args.workload, steps, warm)
+    port = cpu_reference_run(args.workload, max(1, min(args.steps, 50)), max(1, min(args.warmup, 5)))
+    if reference_package_dir() is not None:
+        steps = max(1, min(args.steps, 8))       # about 1 s per step on the sample
+        warm = max(1, min(args.warmup, 2))
+        r = reference_package_run(args.workload, steps, warm)
+    else:
+        steps, warm, r = max(1, min(args.steps, 50)), max(1, min(args.warmup, 5)), port
+    cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    cpu["port_value"] = port["value"]              # the C + OpenMP restatement (oracle/) on the same sample
+    cpu["port_cores"] = port["cores"]
     line = {
         "impl": "reference", "metric": "optimizer_step_throughput", "value": r["value"], "unit": "Gparams/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": r["ms_per_step"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "grad_dtype": wl["grad"], "sample_params": r["sample_params"]},
-        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "cpu_baseline": cpu,
         "e2e": {"value": r["value"], "unit": "Gparams/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -348,11 +432,14 @@ def run_gpu_arm(args):
     params = [p for _, p in named]
     n_params = sum(p.numel() for p in params)
     groups = make_groups(wl, named)
+    copy_dtype = None
     if world > 1:
-        # ZeRO-1: whole tensors are owned by ranks; each rank updates its tensors, then one
-        # in-place all-gather of the flat parameter buffer (strong scaling: the job is fixed)
-        opt = ShardedAdafactor8Bit(groups, **wl["hp"])
-        owned = [i for i, o in enumerate(opt.owner) if o == opt.rank]
+        # ZeRO-1 over the flat parameter space: each rank updates its cells, then the in-place
+        # all-gather of the parameters (strong scaling: the job is fixed).  fp32 parameters travel as
+        # a bf16 compute copy written by the update kernels; the fp32 masters stay with their owner.
+        copy_dtype = torch.bfloat16 if (pdtype == torch.float32 and not args.fp32_gather) else None
+        opt = ShardedAdafactor8Bit(groups, compute_dtype=copy_dtype, **wl["hp"])
+        owned = sorted({i for (i, lo, hi, k, pc) in opt._local})      # tensors of which this rank updates a piece
     else:
         opt = Adafactor8Bit(groups, **wl["hp"])
         owned = list(range(len(params)))
@@ -365,6 +452,10 @@ def run_gpu_arm(args):
     def set_grads(k):
         for i, g in zip(owned, grad_sets[k % n_sets]):
             params[i].grad = g
+
+    gathered_bytes = 0
+    if world > 1:
+        gathered_bytes = opt.flat.numel() * opt.flat.element_size() * (world - 1) // world    # received per rank and step
 
     def barrier():
         if world > 1:
@@ -411,9 +502,28 @@ def run_gpu_arm(args):
                 update_ms = a.elapsed_time(b) / 3
             else:
                 gather_ms = a.elapsed_time(b) / 3
-        t = torch.tensor([ms, gather_ms, update_ms], device=device)
+        # the all-gather of the same layout in fp32 (what a run without the compute copy moves), for comparison
+        gather32_ms = 0.0
+        if copy_dtype is not None:
+            free_b, _ = torch.cuda.mem_get_info()
+            if opt.flat.numel() * 4 < free_b // 2:
+                tmp = torch.empty(opt.flat.numel(), dtype=torch.float32, device=device)
+                unit = world * opt.cell
+                barrier()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                for rep in range(4):
+                    if rep == 1:
+                        a.record()
+                    for k in range(opt.parts):
+                        u = tmp[k * unit:(k + 1) * unit]
+                        dist.all_gather_into_tensor(u, u[opt.rank * opt.cell:(opt.rank + 1) * opt.cell])
+                b.record()
+                barrier()
+                gather32_ms = a.elapsed_time(b) / 3
+                del tmp
+        t = torch.tensor([ms, gather_ms, update_ms, gather32_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, gather_ms, update_ms = float(t[0].item()), float(t[1].item()), float(t[2].item())
+        ms, gather_ms, update_ms, gather32_ms = (float(x) for x in t.tolist())
     value = n_params / (ms * 1e-3) / 1e9
 
     # ---- per-kernel durations inside the timed region (events on the launch stream) ----
@@ -441,17 +551,41 @@ def run_gpu_arm(args):
             bpp = gb
         else:
             bpp = gb + 8
+        if copy_dtype is not None and dom.endswith(("apply", "noclip", "lag", "scales_apply")):
+            bpp += 2                              # the bf16 compute copy written next to the fp32 master
         achieved = units * bpp / (tot_ms * 1e-3) / 1e9
-        # DRAM bytes per parameter (read + write) from the profiler capture of this kernel on the
-        # four-layer case (profiles/); every block is independent, so traffic scales with the
-        # parameter count
-        measured_bpp = NCU_TRAFFIC_BPP.get((dom, wl["grad"])) if wl.get("param", "f32") == "f32" else None
-        traffic = None if measured_bpp is None else measured_bpp * units / launches
+        # DRAM bytes per parameter (read + write) of this kernel: a constant from the committed profiler
+        # capture on the four-layer case; every block is independent, so traffic scales with the
+        # parameter count.  No entry for the kernel: traffic is null and the note says so.
+        entry = NCU_TRAFFIC_BPP.get((dom, wl["grad"])) if (wl.get("param", "f32") == "f32" and copy_dtype is None) else None
+        traffic = None if entry is None else entry[0] * units / launches
+        traffic_note = ("no profiler capture of this kernel and configuration is committed" if entry is None else
+                        f"bytes per launch = {entry[0]} B/param from {entry[1]} x parameters of the launch "
+                        f"(a constant from that capture, not measured in this run)")
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": traffic, "traffic_unit": "bytes per launch (ncu small case, scaled by parameters)",
+                    "frac_of_8tbs": achieved / 8000.0,
+                    "traffic": traffic, "traffic_unit": traffic_note,
                     "kernel": dom, "launches": launches, "avg_launch_ms": tot_ms / launches,
                     "algorithmic_bytes_per_param": bpp, "peak_source": peak_kind,
                     "all_kernels": {k: {"ms_total": v[0], "launches": v[1]} for k, v in per_kernel.items()}}
+        if dom == "apollo_project":
+            # the projection is a contraction: 2 * rank flops per parameter as specified, three times that
+            # issued (the projection matrix enters as three bf16 planes), against the measured bf16 GEMM rate
+            rank_ = int(wl["hp"].get("apollo_rank", 0))
+            peak_tf = 1648.3
+            try:
+                with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                    peak_tf = float(json.load(f)["bf16_tflops"])
+            except Exception:
+                peak_kind = "fallback"
+                peak_tf = 1590.0
+            tf = units * 2.0 * rank_ / (tot_ms * 1e-3) / 1e12
+            roofline.update({"bound": "tensor", "unit": "TFLOP/s", "peak": peak_tf, "achieved": 3.0 * tf,
+                             "frac": 3.0 * tf / peak_tf, "frac_of_8tbs": None, "achieved_as_specified": tf,
+                             "flops_note": "achieved = issued bf16 MMA flops (3 planes x 2*rank per parameter); "
+                                           "achieved_as_specified = 2*rank per parameter; the launch also transposes "
+                                           "left-case gradients and sums channel norms",
+                             "traffic": None, "peak_source": peak_kind})
 
     # ---- end to end: gradients in pinned host memory ----
     e2e = None
@@ -487,8 +621,15 @@ def run_gpu_arm(args):
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        r = cpu_reference_run(args.workload, 3, 1)
-        cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        # the reference arm in a process of its own (the reference package has the name of this repository's)
+        res = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--workload", args.workload,
+                              "--steps", "3", "--warmup", "1"], capture_output=True, text=True, timeout=900)
+        for ln in reversed(res.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                cpu = json.loads(ln)["cpu_baseline"]
+                break
+        if cpu is None:
+            raise RuntimeError("the CPU baseline run printed no result:\n" + res.stderr[-2000:])
 
     if rank == 0:
         line = {
@@ -498,8 +639,10 @@ def run_gpu_arm(args):
             "config": {"workload": args.workload, "params": n_params, "tensors": len(params),
                        "grad_dtype": wl["grad"], "param_dtype": wl.get("param", "f32"),
                        "l2_policy": "inputs larger than L2 (whole parameter set streamed every step)",
-                       "parallelism": f"zero1 x{world} (tensor-granular shards, in-place fp32 parameter all-gather pipelined in 4 units)"
-                       if world > 1 else "single"},
+                       "parallelism": (f"zero1 x{world}: flat block-aligned parameter space in {opt.parts} x {world} cells, "
+                                       + ("bf16 compute-copy all-gather, fp32 masters sharded" if copy_dtype is not None
+                                          else f"in-place {str(pdtype).replace('torch.', '')} parameter all-gather")
+                                       + f", gather of a part overlaps the update of the next") if world > 1 else "single"},
             "hbm_gbs": value * wl["bytes_per_param"], "clocks": clocks.summary(),
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches,
         }
@@ -507,6 +650,12 @@ def run_gpu_arm(args):
             line["allgather_ms_per_step"] = gather_ms          # measured alone; in `value` it overlaps the update
             line["update_ms_per_step"] = update_ms
             line["update_only_value"] = n_params / (max(update_ms, 1e-6) * 1e-3) / 1e9
+            line["allgather_bytes_received_per_rank"] = gathered_bytes
+            line["allgather_gbs_per_rank"] = gathered_bytes / (max(gather_ms, 1e-6) * 1e-3) / 1e9
+            line["allgather_fp32_ms_per_step"] = gather32_ms or None   # the same layout in fp32, measured alone
+            line["limiter"] = "parameter all-gather" if gather_ms > update_ms else "update kernels"
+            line["cut_tensors"] = sum(len(x) > 1 for x in opt.pieces_of)
+            line["exchange_rounds"] = opt.rounds
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -521,6 +670,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--fp32-gather", action="store_true", help="N > 1: gather the fp32 parameters themselves (no bf16 compute copy)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

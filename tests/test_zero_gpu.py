@@ -58,12 +58,16 @@ def _worker(rank, world, port, out, variant):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         from adafactor8bit import ShardedAdafactor8Bit
+        nccl = variant.endswith("_nccl")          # parameters by NCCL all-gather instead of peer copies
+        variant = variant.replace("_nccl", "")
         hp, p0, grads = _inputs(variant)
         params = [torch.nn.Parameter(torch.from_numpy(p.copy()).to(dev).to(_pdt(variant))) for p in p0]
         for p in params:
             p.grad_dtype = None
         copy = variant == "bf16_copy"
-        opt = ShardedAdafactor8Bit(params, parts=2, min_piece=1, compute_dtype=torch.bfloat16 if copy else None, **hp)
+        opt = ShardedAdafactor8Bit(params, parts=2, min_piece=1, compute_dtype=torch.bfloat16 if copy else None,
+                                   exchange="nccl" if nccl else "auto", **hp)
+        assert opt.exchange == ("nccl" if nccl else "push"), getattr(opt, "_symm_error", None)
         assert any(len(lst) > 1 for lst in opt.pieces_of) or variant == "apollo", "the case must cut a tensor"
         for t in (1, 2, 3):
             for p, g in zip(params, grads[t]):
@@ -85,7 +89,8 @@ def _worker(rank, world, port, out, variant):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("variant", ["f32", "adamw_noclip", "bf16_sr", "adafactor", "came", "apollo", "bf16_copy"])
+@pytest.mark.parametrize("variant", ["f32", "f32_nccl", "adamw_noclip", "bf16_sr", "adafactor", "came", "apollo", "bf16_copy",
+                                     "bf16_copy_nccl"])
 def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
     import torch.multiprocessing as mp
     sys.path.insert(0, os.path.join(ROOT, "adafactor-8bit_b200"))
@@ -94,6 +99,7 @@ def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
     mgr = mp.Manager()
     out = mgr.dict()
     mp.spawn(_worker, args=(2, port, out, variant), nprocs=2, join=True)
+    variant = variant.replace("_nccl", "")
     hp, p0, grads = _inputs(variant)
     params = [torch.nn.Parameter(torch.from_numpy(p.copy()).cuda().to(_pdt(variant))) for p in p0]
     for p in params:
