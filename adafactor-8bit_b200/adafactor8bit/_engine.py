@@ -253,16 +253,12 @@ class FullrankPlan:
                 raise RuntimeError("parameters must be contiguous")
 
     # -- table ---------------------------------------------------------------
-    _STATE_KEYS = ("variance_q", "variance_scale", "variance_min_log", "variance", "m_q", "m_scale", "m")
-
     def _pointer_signature(self):
-        """Addresses of everything the static part of the table points at.  A parameter whose
-        storage was replaced (p.data = ..., module.to(...)) or a state tensor that user code
-        swapped keeps its Python identity, so the cached table is checked against the addresses."""
-        sig = [p.data_ptr() for p in self.params]
-        for st in self.states:
-            sig += [id(st.get(k)) for k in self._STATE_KEYS]      # a state entry changes by being replaced
-        return sig
+        """Addresses of the parameters.  A parameter whose storage was replaced (p.data = ...,
+        module.to(...)) keeps its Python identity, so the cached table is checked against the
+        addresses at every step.  (State tensors are replaced only by the optimizer itself, which
+        then drops its launch plans.)"""
+        return [p.data_ptr() for p in self.params]
 
     def _static_fields(self):
         """Pointers and sizes that only change when a parameter's or a state's storage is replaced."""
@@ -364,15 +360,7 @@ class FullrankPlan:
         nt["clip_div"] = (sqrt_n * d).astype(np.float32) if use_clip else np.float32(0.0)
         nt["fira_margin1"] = np.float32(1.0 + fira_margin)
         if fira and pre_div_mode != 1:
-            for i, st in enumerate(self.states):
-                prev = st.get("fira_prev_norm")
-                if prev is None:
-                    prev = torch.zeros((), dtype=torch.float32, device=self.device)
-                    st["fira_prev_norm"] = prev
-                    nt["fira_has_prev"][i] = 0
-                else:
-                    nt["fira_has_prev"][i] = 1
-                nt["fira_prev"][i] = prev.data_ptr()
+            nt["fira_prev"], nt["fira_has_prev"] = fira_state_pointers(self)
         else:
             nt["fira_prev"] = 0
             nt["fira_has_prev"] = 0
@@ -528,6 +516,29 @@ class FullrankPlan:
         return dyn["norm"].copy()
 
 
+def fira_state_pointers(plan):
+    """-> (addresses of the tensors' "fira_prev_norm" scalars, flags: the scalar holds a value).  The
+    state entry is created on a tensor's first limited step (optimizer.py:780-781); once every tensor
+    of the plan has one, the addresses are reused while the entries stay the same objects."""
+    cached = getattr(plan, "_fira_cache", None)
+    if cached is not None and all(st.get("fira_prev_norm") is t for st, t in zip(plan.states, cached[0])):
+        return cached[1], 1
+    ptrs = np.zeros(plan.n, dtype=np.uint64)
+    has = np.zeros(plan.n, dtype=np.int32)
+    tensors = []
+    for i, st in enumerate(plan.states):
+        prev = st.get("fira_prev_norm")
+        if prev is None:
+            prev = torch.zeros((), dtype=torch.float32, device=plan.device)
+            st["fira_prev_norm"] = prev
+        else:
+            has[i] = 1
+        tensors.append(prev)
+        ptrs[i] = prev.data_ptr()
+    plan._fira_cache = (tensors, ptrs) if bool(has.all()) else None
+    return ptrs, has
+
+
 def fill_scale_table(t, params, numel, full_numel, nchunks, param_dtype, scale):
     """Fill an af8_scale_tensor table (host view `t`)."""
     t["param"] = [p.data_ptr() for p in params]
@@ -624,14 +635,8 @@ class FactoredPlan:
         self._ptr_sig = None
         self._alpha_on_device = False
 
-    _STATE_KEYS = ("m_q", "m_scale", "m", "row_var_q", "row_var", "col_var_q", "col_var", "conf_row_q", "conf_row",
-                   "conf_col_q", "conf_col")
-
     def _pointer_signature(self):
-        sig = [p.data_ptr() for p in self.params]
-        for st in self.states:
-            sig += [id(st.get(k)) for k in self._STATE_KEYS]
-        return sig
+        return [p.data_ptr() for p in self.params]
 
     @staticmethod
     def _running(counts):
@@ -775,15 +780,7 @@ class FactoredPlan:
         nt["clip_div"] = (sqrt_n * d).astype(np.float32) if (d > 0 and pre_div_mode == 0) else np.float32(0.0)
         nt["fira_margin1"] = np.float32(1.0 + fira_margin)
         if fira and pre_div_mode != 1:
-            for i, st in enumerate(self.states):
-                prev = st.get("fira_prev_norm")
-                if prev is None:
-                    prev = torch.zeros((), dtype=torch.float32, device=self.device)
-                    st["fira_prev_norm"] = prev
-                    nt["fira_has_prev"][i] = 0
-                else:
-                    nt["fira_has_prev"][i] = 1
-                nt["fira_prev"][i] = prev.data_ptr()
+            nt["fira_prev"], nt["fira_has_prev"] = fira_state_pointers(self)
         else:
             nt["fira_prev"] = 0
             nt["fira_has_prev"] = 0

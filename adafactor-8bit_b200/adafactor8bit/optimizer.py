@@ -207,6 +207,7 @@ class Adafactor8Bit(Optimizer):
         self._apollo_seed_map = None
         self._cfg_seen = {}       # id(param) -> option signature its state was last checked against
         self._plans = {}
+        self._group_cache = {}    # group index -> how its parameters were sorted into launch groups at the last step
         self._after_group = None               # optional hook(gi, group), called when a group's launches are enqueued
         # Set by a sharding wrapper (zero.py): `_pieces` maps id(parameter) to the _engine.Piece that says which
         # part of which tensor the parameter is; `_shard` schedules the passes of all launch plans in
@@ -227,6 +228,7 @@ class Adafactor8Bit(Optimizer):
         state_dict = dict(state_dict)
         self._cfg_seen.clear()       # loaded states are checked against the group options at the next step
         self._plans.clear()
+        self._group_cache.clear()
         self._apollo_seed_counter = state_dict.pop("_apollo_seed_counter", self._apollo_seed_counter)
         self._sr_seed_counter = state_dict.pop("_sr_seed_counter", self._sr_seed_counter)
         # torch's loader casts floating-point state to the parameter's dtype and
@@ -336,12 +338,17 @@ class Adafactor8Bit(Optimizer):
     # state migration when a group option changed between steps (optimizer.py:1650-1860, 976-1045)
     # ------------------------------------------------------------------
     @staticmethod
-    def _config_signature(group, grad):
+    def _group_signature(group):
+        """The group options that decide which states a parameter has and which kernels step it."""
         return (bool(group.get("quantize", True)), group.get("block_size", 2048), group.get("m_block_size", 256),
                 group.get("m_quant_type", "uf8"), group.get("v_quant_type", "al8"), group.get("c_quant_type"),
                 group.get("min_8bit_size", 4096), group.get("apollo_rank", 0), bool(group.get("apollo_factorize", False)),
                 bool(group.get("factored", True)), group.get("beta1") is None, group.get("beta2") is None,
-                group.get("beta2_decay") is None, group.get("beta3") is None, grad.dim())
+                group.get("beta2_decay") is None, group.get("beta3") is None)
+
+    @classmethod
+    def _config_signature(cls, group, grad):
+        return cls._group_signature(group) + (grad.dim(),)
 
     @staticmethod
     def _reset_keep_step(state):
@@ -622,43 +629,16 @@ class Adafactor8Bit(Optimizer):
         for gi, group in enumerate(self.param_groups):
             if grad_ready is not None and grad_ready[gi] is not None:
                 torch.cuda.current_stream().wait_event(grad_ready[gi])
-            entries, copy_back = [], []
-            for p in group["params"]:
-                if p.grad is None:
+            runs, copy_back = self._group_runs(gi, group)
+            for e, dev, gen in runs:
+                if self._shard is not None:
+                    pending.append((gi, e, dev, gen))
                     continue
-                if not p.is_cuda:
-                    raise RuntimeError("Adafactor8Bit (B200 build) only updates CUDA parameters; "
-                                       "there is no CPU path")
-                state = self.state[p]
-                if len(state) == 0 or "is_quantized" not in state:
-                    state = self._create_state(p, p.grad, group)
-                    self._cfg_seen[id(p)] = self._config_signature(group, p.grad)
-                else:
-                    sig = self._config_signature(group, p.grad)
-                    if self._cfg_seen.get(id(p)) != sig:     # first step after a load, or an option was edited
-                        state = self._sync_state(p, p.grad, group, state)
-                        self._cfg_seen[id(p)] = sig
-                        self._plans.clear()                  # launch plans cache state pointers and formats
-                if group.get("stochastic_round_writeback", False) and p.dtype in (torch.bfloat16, torch.float16):
-                    self._sr_seed(state, p)     # seeds follow the parameter order of the step (optimizer.py:1889-1892)
-                if p.numel() == 0:              # an empty parameter has a state and a step count, nothing to launch
-                    state["step"] = state.get("step", 0) + 1
-                    continue
-                work = p
-                if not p.is_contiguous():       # stepped on a contiguous copy, copied back (optimizer.py:2000-2005, 3081-3084)
-                    work = p.detach().contiguous()
-                    copy_back.append((p, work))
-                entries.append((work, p.grad, state))
-            if entries:
-                for e, dev, gen in self._run_group(gi, group, entries):
-                    if self._shard is not None:
-                        pending.append((gi, e, dev, gen))
-                        continue
-                    with torch.cuda.device(dev):             # the whole pass sequence of the plan, now
-                        for _ in gen:
-                            pass
-                for p, work in copy_back:
-                    p.copy_(work)
+                with torch.cuda.device(dev):             # the whole pass sequence of the plan, now
+                    for _ in gen:
+                        pass
+            for p, work in copy_back:
+                p.copy_(work)
             if self._after_group is not None:
                 self._after_group(gi, group)
         if self._shard is not None:
@@ -719,12 +699,79 @@ class Adafactor8Bit(Optimizer):
                 self._sr_seed_counter += 1
         return state["sr_seed"]
 
-    def _run_group(self, gi, group, entries):
+    def _group_runs(self, gi, group):
+        """-> ([(exchange count, device, generator)] for the launch plans of the group's parameters that
+        have gradients, [(parameter, contiguous copy)] to copy back).
+
+        The slow path looks at every parameter: creates its state on its first step, re-checks the
+        state against the group's options when they changed (or after a load), hands out
+        stochastic-rounding seeds, sorts the tensors into launch groups.  Its result is remembered;
+        while the same parameters carry gradients of the same kind and the options that matter are
+        unchanged, the next steps reuse the sorting and only collect the gradients."""
+        params = group["params"]
+        gsig = self._group_signature(group) + (bool(group.get("stochastic_round_writeback", False)),)
+        c = self._group_cache.get(gi)
+        if c is not None and c["gsig"] == gsig and len(c["params"]) == len(params):
+            grads = []
+            for p, q, kind in zip(params, c["params"], c["kinds"]):
+                g = p.grad
+                if p is not q or ((None if g is None else (g.dim(), g.dtype)) != kind):
+                    grads = None
+                    break
+                grads.append(g)
+            if grads is not None:
+                states = c["states"]
+                return [fn(gi, group, key, [(params[j], grads[j], states[j]) for j in idx])
+                        for fn, key, idx in c["launches"]], ()
+        entries, copy_back, kinds, states, cacheable = [], [], [], [], True
+        for j, p in enumerate(params):
+            g = p.grad
+            kinds.append(None if g is None else (g.dim(), g.dtype))
+            states.append(None)
+            if g is None:
+                continue
+            if not p.is_cuda:
+                raise RuntimeError("Adafactor8Bit (B200 build) only updates CUDA parameters; "
+                                   "there is no CPU path")
+            state = self.state[p]
+            if len(state) == 0 or "is_quantized" not in state:
+                state = self._create_state(p, g, group)
+                self._cfg_seen[id(p)] = self._config_signature(group, g)
+            else:
+                sig = self._config_signature(group, g)
+                if self._cfg_seen.get(id(p)) != sig:     # first step after a load, or an option was edited
+                    state = self._sync_state(p, g, group, state)
+                    self._cfg_seen[id(p)] = sig
+                    self._plans.clear()                  # launch plans cache state pointers and formats
+            states[j] = state
+            if group.get("stochastic_round_writeback", False) and p.dtype in (torch.bfloat16, torch.float16):
+                self._sr_seed(state, p)     # seeds follow the parameter order of the step (optimizer.py:1889-1892)
+            if p.numel() == 0:              # an empty parameter has a state and a step count, nothing to launch
+                state["step"] = state.get("step", 0) + 1
+                cacheable = False
+                continue
+            work = p
+            if not p.is_contiguous():       # stepped on a contiguous copy, copied back (optimizer.py:2000-2005, 3081-3084)
+                work = p.detach().contiguous()
+                copy_back.append((p, work))
+                cacheable = False
+            entries.append((j, work, g, state))
+        launches = self._sort_group(group, entries)
+        self._group_cache.pop(gi, None)
+        if cacheable:
+            self._group_cache[gi] = dict(gsig=gsig, params=list(params), kinds=kinds, states=states,
+                                         launches=[(fn, key, [e[0] for e in items]) for fn, key, items in launches])
+        return [fn(gi, group, key, [(p, g, st) for _, p, g, st in items]) for fn, key, items in launches], copy_back
+
+    def _sort_group(self, group, entries):
+        """Sort (index, parameter, gradient, state) entries into launch groups ->
+        [(method that runs one, its key, entries)]."""
         apollo_rank = group.get("apollo_rank", 0)
         factored = group.get("factored", True)
         sgd = group["beta2"] is None and group["beta2_decay"] is None
         fullrank, factored_items, apollo_items = {}, {}, []
-        for p, g, st in entries:
+        for ent in entries:
+            _, p, g, st = ent
             if sgd:                 # optimizer.py:2045-2071: no second moment, every shape takes the flat path
                 if group.get("beta1") is not None:
                     m_fmt = "fp32" if "m" in st else st.get("m_quant_type", "uf8")
@@ -732,12 +779,12 @@ class Adafactor8Bit(Optimizer):
                 else:
                     m_fmt, m_block = None, 0
                 key = (p.device, g.dtype, "none", m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block, p.dtype)
-                fullrank.setdefault(key, []).append((p, g, st))
+                fullrank.setdefault(key, []).append(ent)
                 continue
             if apollo_rank > 0 and "apollo_seed" in st:
                 if g.dim() != 2:
                     raise NotImplementedError("APOLLO tensors with more than two dimensions are not available in this build")
-                apollo_items.append((p, g, st))
+                apollo_items.append(ent)
                 continue
             quant = st.get("is_quantized", False)
             if group.get("beta1") is not None:
@@ -750,18 +797,15 @@ class Adafactor8Bit(Optimizer):
                     raise NotImplementedError("factored tensors with more than two dimensions are not available in this build")
                 came = group.get("beta3") is not None and group.get("beta1") is not None
                 key = (p.device, g.dtype, m_fmt, m_block, came, p.dtype)
-                factored_items.setdefault(key, []).append((p, g, st))
+                factored_items.setdefault(key, []).append(ent)
                 continue
             v_fmt = st.get("v_quant_type", "al8") if quant else "fp32"
             key = (p.device, g.dtype, v_fmt, m_fmt, st.get("block_size", group.get("block_size", 2048)), m_block, p.dtype)
-            fullrank.setdefault(key, []).append((p, g, st))
-        out = []        # (exchange count, device, generator over the plan's pass sequence)
-        for key, items in fullrank.items():
-            out.append(self._run_fullrank(gi, group, key, items))
-        for key, items in factored_items.items():
-            out.append(self._run_factored(gi, group, key, items))
+            fullrank.setdefault(key, []).append(ent)
+        out = [(self._run_fullrank, key, items) for key, items in fullrank.items()]
+        out += [(self._run_factored, key, items) for key, items in factored_items.items()]
         if apollo_items:
-            out.append(self._run_apollo(gi, group, apollo_items))
+            out.append((self._run_apollo, None, apollo_items))
         return out
 
     # ------------------------------------------------------------------
@@ -801,7 +845,7 @@ class Adafactor8Bit(Optimizer):
             state["_proj_T"] = proj_t      # same values the reference would regenerate each step
         return proj_t
 
-    def _run_apollo(self, gi, group, items):
+    def _run_apollo(self, gi, group, key, items):
         if group["scale_parameter"]:
             raise NotImplementedError("APOLLO with scale_parameter=True is not available in this build")
         if group.get("apollo_factorize", False) or group.get("beta3") is not None:
@@ -935,24 +979,29 @@ class Adafactor8Bit(Optimizer):
         cols = {k: np.empty(n, dtype=f32) for k in ("decay", "alpha", "v_w", "m_w", "c_w", "eps1", "eps_came")}
         if sr:
             cols["sr_base"] = np.zeros(n, dtype=np.uint64)
-        grads = []
-        for i, (p, g, st) in enumerate(items):
+        steps = []
+        for _, _, st in items:
             step = st["step"] + 1
             st["step"] = step
-            if sr:                  # a part of a tensor draws the counters of its elements in the whole tensor
+            steps.append(step)
+        grads = [g if g.is_contiguous() else g.contiguous() for _, g, _ in items]
+        if sr:                      # a part of a tensor draws the counters of its elements in the whole tensor
+            for i, (_, _, st) in enumerate(items):
                 first = pcs[i].elem0 if pcs[i] is not None else 0
-                cols["sr_base"][i] = (sr_base(self._sr_seed(st), step) + first) & 0xFFFFFFFFFFFFFFFF
-            sc = self._step_scalars(group, step)
+                cols["sr_base"][i] = (sr_base(self._sr_seed(st), steps[i]) + first) & 0xFFFFFFFFFFFFFFFF
+        uniform = steps.count(steps[0]) == n          # the usual case: every tensor of the group is at the same step
+        for i in ([0] if uniform else range(n)):
+            where = slice(None) if uniform else i
+            sc = self._step_scalars(group, steps[i])
             alpha, decay = self._alpha_decay(group, sc)
-            cols["decay"][i], cols["alpha"][i] = decay, alpha
-            cols["v_w"][i] = f32(sc["beta_val"])
-            cols["m_w"][i] = f32(1.0 - group["beta1"]) if group.get("beta1") is not None else f32(0.0)
-            cols["c_w"][i] = f32(1.0 - group["beta3"]) if group.get("beta3") is not None else f32(0.0)
-            cols["eps1"][i] = f32(sc["eps1"])
-            cols["eps_came"][i] = f32(group.get("eps_came", 1e-16))
+            cols["decay"][where], cols["alpha"][where] = decay, alpha
+            cols["v_w"][where] = f32(sc["beta_val"])
+            cols["m_w"][where] = f32(1.0 - group["beta1"]) if group.get("beta1") is not None else f32(0.0)
+            cols["c_w"][where] = f32(1.0 - group["beta3"]) if group.get("beta3") is not None else f32(0.0)
+            cols["eps1"][where] = f32(sc["eps1"])
+            cols["eps_came"][where] = f32(group.get("eps_came", 1e-16))
             if scale is not None:
-                self._fill_scale(scale, i, group, sc)
-            grads.append(g if g.is_contiguous() else g.contiguous())
+                self._fill_scale(scale, where, group, sc)
         d, fira, lag = float(group["d"]), bool(group.get("enable_fira_for_adafactor", False)), bool(group.get("lag_norm", False))
         return (factored_exchanges(came, d, fira, lag), device,
                 plan.stages(grads, cols, d=d, fira=fira, fira_margin=float(group.get("fira_margin", 0.01)), scale=scale, lag=lag))
@@ -986,36 +1035,44 @@ class Adafactor8Bit(Optimizer):
         cols = {k: np.empty(n, dtype=f32) for k in _FULLRANK_COLS}
         if sr:
             cols["sr_base"] = np.zeros(n, dtype=np.uint64)
-        cache = {}
-        grads = []
-        for i, (p, g, st) in enumerate(items):
-            step = st["step"] + 1
-            st["step"] = step
-            if sr:                  # a part of a tensor draws the counters of its elements in the whole tensor
-                first = pcs[i].elem0 if pcs[i] is not None else 0
-                cols["sr_base"][i] = (sr_base(self._sr_seed(st), step) + first) & 0xFFFFFFFFFFFFFFFF
-            vals = cache.get(step)
-            if vals is None:
-                sc = self._step_scalars(group, step)
-                alpha, decay = self._alpha_decay(group, sc)
-                bv = sc["beta_val"]
-                keep = f32(1.0 - group["beta1"]) if (sgd and group.get("beta1") is not None) else f32(1.0 - bv)
-                vals = (decay, alpha, f32(bv), keep, f32(bv * sc["eps_gradsq"]),
+        def row_values(step):
+            sc = self._step_scalars(group, step)
+            alpha, decay = self._alpha_decay(group, sc)
+            bv = sc["beta_val"]
+            keep = f32(1.0 - group["beta1"]) if (sgd and group.get("beta1") is not None) else f32(1.0 - bv)
+            return sc, (decay, alpha, f32(bv), keep, f32(bv * sc["eps_gradsq"]),
                         f32(1.0 - group["beta1"]) if group.get("beta1") is not None else f32(0.0),
                         f32(sc["eps_gradsq"]), f32(sc["eps_denom"]), f32(sc["eps_sq"]))
-                cache[step] = vals
+
+        steps = []
+        for _, _, st in items:
+            step = st["step"] + 1
+            st["step"] = step
+            steps.append(step)
+        grads = [g if g.is_contiguous() else g.contiguous() for _, g, _ in items]
+        if sr:                      # a part of a tensor draws the counters of its elements in the whole tensor
+            for i, (_, _, st) in enumerate(items):
+                first = pcs[i].elem0 if pcs[i] is not None else 0
+                cols["sr_base"][i] = (sr_base(self._sr_seed(st), steps[i]) + first) & 0xFFFFFFFFFFFFFFFF
+        cache = {}
+        uniform = steps.count(steps[0]) == n          # the usual case: every tensor of the group is at the same step
+        for i in ([0] if uniform else range(n)):
+            step = steps[i]
+            got = cache.get(step)
+            if got is None:
+                got = cache[step] = row_values(step)
+            sc, vals = got
+            where = slice(None) if uniform else i
             for k, v in zip(_FULLRANK_COLS, vals):
-                cols[k][i] = v
+                cols[k][where] = v
             if scale is not None:
-                sc = self._step_scalars(group, step)
-                scale["rho"][i] = sc["rho"]
-                scale["eps2"][i] = f32(sc["eps2"])
-                scale["weight_decay"][i] = f32(group["weight_decay"])
+                scale["rho"][where] = sc["rho"]
+                scale["eps2"][where] = f32(sc["eps2"])
+                scale["weight_decay"][where] = f32(group["weight_decay"])
                 if sc["bc_mul"] is not None:
-                    scale["bc"][i], scale["bc_mode"][i] = sc["bc_mul"], 1
+                    scale["bc"][where], scale["bc_mode"][where] = sc["bc_mul"], 1
                 elif sc["bc_div"] is not None:
-                    scale["bc"][i], scale["bc_mode"][i] = sc["bc_div"], 2
-            grads.append(g if g.is_contiguous() else g.contiguous())
+                    scale["bc"][where], scale["bc_mode"][where] = sc["bc_div"], 2
         d, fira, lag = float(group["d"]), bool(group.get("enable_fira_for_adafactor", False)), bool(group.get("lag_norm", False))
         return (fullrank_exchanges(scale is not None, d, fira, bool(plan.cfg.momentum_only), lag), device,
                 plan.stages(grads, cols, d=d, fira=fira, fira_margin=float(group.get("fira_margin", 0.01)), scale=scale, lag=lag))

@@ -372,6 +372,10 @@ class ShardedAdafactor8Bit:
             self.inner._apollo_seed_map = {id(pc): seeds[id(all_params[i])] for (i, lo, hi, k, pc) in local
                                            if id(all_params[i]) in seeds}
             self.inner._apollo_seed_counter = nxt
+        self._bound = {}
+        self._local_by_tensor = {}
+        for (i, lo, hi, k, pc) in local:
+            self._local_by_tensor.setdefault(i, []).append((lo, hi, pc))
         self.gather_stream = None
         self._push_streams, self._pushed = None, False
         self._fence = torch.zeros(1, dtype=torch.float32, device=dev) if self.peer_flat is not None else None
@@ -395,21 +399,28 @@ class ShardedAdafactor8Bit:
                 p.grad.zero_()
         for (_, _, _, _, pc) in self._local:
             pc.grad = None
+        self._bound = {}
 
     # -- the step -------------------------------------------------------------------------------------
     def _bind_grads(self):
-        """Every piece takes the matching stretch of its tensor's gradient (a view, no copy)."""
-        flat_grads = {}
-        for (i, lo, hi, k, pc) in self._local:
+        """Every piece takes the matching stretch of its tensor's gradient (a view, no copy).  Pieces of
+        a tensor whose gradient is the same tensor at the same address as at the last step keep theirs."""
+        bound = self._bound
+        for i, pcs in self._local_by_tensor.items():
             g = self.all_params[i].grad
             if g is None:
-                pc.grad = None
+                if bound.get(i) is not None:
+                    for (lo, hi, pc) in pcs:
+                        pc.grad = None
+                    bound[i] = None
                 continue
-            fg = flat_grads.get(i)
-            if fg is None:
-                fg = (g if g.is_contiguous() else g.contiguous()).view(-1)
-                flat_grads[i] = fg
-            pc.grad = fg[lo:hi].view(pc.shape)
+            was = bound.get(i)
+            if was is not None and was[0] is g and was[1] == g.data_ptr():
+                continue
+            fg = (g if g.is_contiguous() else g.contiguous()).view(-1)
+            for (lo, hi, pc) in pcs:
+                pc.grad = fg[lo:hi].view(pc.shape)
+            bound[i] = (g, g.data_ptr()) if g.is_contiguous() else None
 
     def local_step(self, closure=None):
         """Update the pieces this rank owns.  With the native optimizer and cut tensors this includes

@@ -435,3 +435,38 @@ def test_step_waits_for_gradients_arriving_on_another_stream():
         assert torch.equal(p.detach(), q.detach())
     with pytest.raises(ValueError):
         oa.step(grad_ready=[None])
+
+
+def test_step_follows_a_parameter_whose_storage_was_replaced(oracle):
+    """p.data = <another tensor> keeps the parameter's identity but moves its storage (module.to(),
+    flat-parameter wrappers, manual re-materialisation do this).  The launch tables must follow:
+    the new storage is updated, the old one is left alone."""
+    from adafactor8bit import Adafactor8Bit
+    hp = dict(cases.CASES["adamw_fira_bf16"]["hp"])
+    shapes = [(96, 200), (4096,)]
+    p0 = [cases.make_param(s, 800 + i) for i, s in enumerate(shapes)]
+    params = [torch.nn.Parameter(torch.from_numpy(p.copy()).cuda()) for p in p0]
+    for p in params:
+        p.grad_dtype = None
+    opt = Adafactor8Bit(params, **hp)
+    ohp = oracle.hyper(**hp)
+    ostates = [oracle.init_state(s, ohp) for s in shapes]
+    oparams = [p.copy() for p in p0]
+    old = None
+    for t in range(1, 4):
+        grads = [cases.make_grad(s, 850 + i, t, cases.CASES["adamw_fira_bf16"]["grad"]) for i, s in enumerate(shapes)]
+        if t == 2:
+            old = [p.data for p in params]
+            snapshot = [x.clone() for x in old]
+            for p in params:
+                p.data = p.data.clone()
+        for p, g in zip(params, grads):
+            p.grad = to_cuda_grad(g, p.shape)
+        opt.step()
+        torch.cuda.synchronize()
+        for i in range(len(shapes)):
+            oracle.fullrank_step(oparams[i].reshape(-1), grads[i].reshape(-1), ostates[i], ohp)
+        for i, p in enumerate(params):
+            parity.assert_params(p.detach().cpu().numpy(), oparams[i], f"step {t} param {i}")
+        if t >= 2:
+            assert all(torch.equal(a, b) for a, b in zip(old, snapshot)), "the replaced storage was written"
