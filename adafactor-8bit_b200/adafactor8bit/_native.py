@@ -137,6 +137,8 @@ PROTOTYPES = {
     "af8_last_error": (ctypes.c_char_p, []),
     "af8_struct_size": (ctypes.c_int32, [ctypes.c_int32]),
     "af8_device_status": (_c_i, [ctypes.POINTER(ctypes.c_int32), _c_p]),
+    "af8_device_status_clear": (_c_i, [_c_p]),
+    "af8_selftest_bounded_wait": (_c_i, [_c_p, _c_l, _c_p, _c_p]),
     "af8_set_qmap": (_c_i, [_c_p, _c_p, _c_p]),
     "af8_fullrank_step": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
     "af8_fullrank_upload": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_p, _c_i, _c_l, _c_p]),
@@ -220,6 +222,10 @@ def device_status(stream=None):
     out = ctypes.c_int32(0)
     check(lib().af8_device_status(ctypes.byref(out), stream), "af8_device_status")
     return out.value
+
+
+def clear_device_status(stream=None):
+    check(lib().af8_device_status_clear(stream), "af8_device_status_clear")
 
 
 def version():

@@ -219,6 +219,8 @@ class Adafactor8Bit(Optimizer):
     # checkpointing (optimizer.py:1463-1553)
     # ------------------------------------------------------------------
     def state_dict(self):
+        if torch.cuda.is_available() and any(p.is_cuda for g in self.param_groups for p in g["params"]):
+            self.check_device()
         sd = super().state_dict()
         sd["_apollo_seed_counter"] = self._apollo_seed_counter
         sd["_sr_seed_counter"] = self._sr_seed_counter
@@ -229,8 +231,19 @@ class Adafactor8Bit(Optimizer):
         self._cfg_seen.clear()       # loaded states are checked against the group options at the next step
         self._plans.clear()
         self._group_cache.clear()
-        self._apollo_seed_counter = state_dict.pop("_apollo_seed_counter", self._apollo_seed_counter)
-        self._sr_seed_counter = state_dict.pop("_sr_seed_counter", self._sr_seed_counter)
+        # APOLLO keeps its momentum in the projected space: full-size momentum left in an APOLLO state is
+        # dropped before the base loader would move it to the device (optimizer.py:1472-1480)
+        state_dict["state"] = {
+            idx: ({k: v for k, v in st.items() if k not in ("m", "m_q", "m_scale")}
+                  if isinstance(st, dict) and "apollo_seed" in st else st)
+            for idx, st in state_dict.get("state", {}).items()}
+        # counters a checkpoint does not carry start from 0 (optimizer.py:1502-1503)
+        self._apollo_seed_counter = state_dict.pop("_apollo_seed_counter", 0)
+        self._sr_seed_counter = state_dict.pop("_sr_seed_counter", 0)
+        # groups saved without a stochastic-rounding policy keep the current one (optimizer.py:1505-1520)
+        current_sr = [g.get("stochastic_round_writeback", False) for g in self.param_groups]
+        sr_missing = [("stochastic_round_writeback" not in sg) if isinstance(sg, dict) else True
+                      for sg in state_dict.get("param_groups", [])]
         # torch's loader casts floating-point state to the parameter's dtype and
         # moves everything to its device; remember the saved dtypes and restore
         # them afterwards (the reference does the same, optimizer.py:1482-1539)
@@ -243,6 +256,10 @@ class Adafactor8Bit(Optimizer):
         saved_plain = {idx: {k: v for k, v in st.items() if not isinstance(v, Tensor)}
                        for idx, st in state_dict["state"].items()}
         super().load_state_dict(state_dict)
+        if len(self.param_groups) == len(sr_missing):
+            for group, missing, policy in zip(self.param_groups, sr_missing, current_sr):
+                if missing:
+                    group["stochastic_round_writeback"] = policy
         idx_of = {}
         i = 0
         for g in self.param_groups:
@@ -272,7 +289,21 @@ class Adafactor8Bit(Optimizer):
         per tensor of every launch plan (zeros where no norm was needed).  Reads
         them back from the device, so it synchronises."""
         out = [plan.norms() for plan in self._plans.values()]
+        self.check_device()
         return np.concatenate(out) if out else np.zeros(0, dtype=np.float32)
+
+    def check_device(self):
+        """Raise if a kernel of this library gave up a bounded wait on any device this optimizer steps on
+        (an asynchronous copy that never completed: the launch skipped its stores, so parameters and
+        states of that step are incomplete).  Synchronises; called where the host synchronises anyway
+        (update_norms, state_dict)."""
+        devices = {p.device for g in self.param_groups for p in g["params"] if p.is_cuda}
+        for dev in devices:
+            with torch.cuda.device(dev):
+                code = N.device_status(torch.cuda.current_stream(dev).cuda_stream)
+            if code != 0:
+                raise RuntimeError(f"libaf8 reported device error {code} on {dev}: a kernel gave up waiting for an "
+                                   f"asynchronous copy; the step that ran then is incomplete")
 
     # ------------------------------------------------------------------
     # lazy state creation (first-step branch of _init_group, optimizer.py:1711-1773)

@@ -350,6 +350,51 @@ extern "C" int af8_device_status(int32_t *status_out, void *stream)
     return AF8_OK;
 }
 
+namespace af8 {
+// Self-test of the bounded wait: one thread arms an mbarrier for 64 bytes, copies 32 (that copy
+// completes; nothing stays in flight) and waits with the given limit.  The phase can never complete,
+// so the wait must give up after the limit and record the time-out exactly as the step kernels do.
+__global__ void bounded_wait_selftest_kernel(const unsigned char *src, uint64_t limit_ns, int *gave_up)
+{
+    __shared__ __align__(128) unsigned char s_dst[64];
+    __shared__ __align__(8) uint64_t s_bar;
+    if (threadIdx.x != 0) return;
+    mbar_init(&s_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+    mbar_expect_tx(&s_bar, 64);
+    bulk_g2s(s_dst, src, 32, &s_bar);
+    const bool done = mbar_wait_bounded(&s_bar, 0, limit_ns);
+    if (!done) atomicExch(&g_device_error, DEVERR_COPY_TIMEOUT);
+    *gave_up = done ? 0 : 1;
+    // the 32-byte copy has landed long before the limit ran out; give it a (bounded) moment anyway
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 20000ull) { }
+}
+}  // namespace af8
+
+extern "C" int af8_selftest_bounded_wait(const void *src32, int64_t limit_ns, int32_t *gave_up_dev, void *stream)
+{
+    using namespace af8;
+    if (!src32 || !gave_up_dev) return fail(AF8_ERR_INVALID, "af8_selftest_bounded_wait: null argument");
+    if (!aligned16(src32)) return fail(AF8_ERR_INVALID, "af8_selftest_bounded_wait: the source must be 16-byte aligned");
+    if (limit_ns <= 0 || limit_ns > 1000000000ll) return fail(AF8_ERR_INVALID, "af8_selftest_bounded_wait: the limit must be 1 ns .. 1 s");
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const unsigned char *>(src32), (uint64_t)limit_ns, gave_up_dev);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+extern "C" int af8_device_status_clear(void *stream)
+{
+    using namespace af8;
+    const int zero = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    AF8_CUDA_TRY(cudaMemcpyToSymbolAsync(g_device_error, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st));
+    AF8_CUDA_TRY(cudaStreamSynchronize(st));
+    return AF8_OK;
+}
+
 extern "C" int af8_lag_scalars(const af8_lag_tensor *tensors, int32_t n_tensors, int32_t phase, const void *block_sumsq,
                                af8_dyn_scalars *dyn, void *stream)
 {

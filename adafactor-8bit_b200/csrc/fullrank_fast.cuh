@@ -216,9 +216,9 @@ __device__ __forceinline__ uint64_t global_timer_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Wait for a phase of the barrier for at most two seconds of wall time (a block's
-// copies take microseconds).  Returns false when the time ran out.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity)
+// Wait for a phase of the barrier for at most `limit_ns` of wall time (two seconds unless told
+// otherwise; a block's copies take microseconds).  Returns false when the time ran out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint64_t limit_ns = 2000000000ull)
 {
     uint64_t t0 = 0;
     for (uint32_t i = 0;; ++i) {
@@ -226,7 +226,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
         if ((i & 0xffu) == 0xffu) {
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > 2000000000ull) return false;
+            else if (now - t0 > limit_ns) return false;
         }
     }
 }

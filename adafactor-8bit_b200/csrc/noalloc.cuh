@@ -96,6 +96,7 @@ extern "C" int af8_fullrank_limited_step_noalloc(const af8_fullrank_cfg *cfg, co
     if (!cfg || !host_tensor) return fail(AF8_ERR_INVALID, "af8_fullrank_limited_step_noalloc: null cfg or tensor");
     af8_fullrank_cfg c = *cfg;
     if (c.param_dtype != AF8_F32) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_limited_step_noalloc: only fp32 parameters are supported");
+    if (c.stochastic_round) return fail(AF8_ERR_INVALID, "af8_fullrank_limited_step_noalloc: stochastic rounding applies to bf16 / fp16 parameters only");
     if (c.grad_dtype != AF8_F32 && c.grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_fullrank_limited_step_noalloc: gradients must be fp32 or bf16");
     if (c.v_fmt != AF8_V_FP32 && c.v_fmt != AF8_V_AL8 && c.v_fmt != AF8_V_AL16) return fail(AF8_ERR_INVALID, "af8_fullrank_limited_step_noalloc: bad v_fmt %d", c.v_fmt);
     if (c.m_fmt < AF8_M_NONE || c.m_fmt > AF8_M_FP32) return fail(AF8_ERR_INVALID, "af8_fullrank_limited_step_noalloc: bad m_fmt %d", c.m_fmt);

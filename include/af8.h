@@ -87,6 +87,14 @@ AF8_API int32_t af8_struct_size(int32_t index);
  * device in *status_out: 0 = healthy, 1 = an asynchronous copy never completed
  * (results of that launch are invalid).  No counterpart in the reference. */
 AF8_API int af8_device_status(int32_t *status_out, void *stream);
+/* Reset that flag to 0 (synchronises `stream`).  No counterpart in the reference. */
+AF8_API int af8_device_status_clear(void *stream);
+/* Self-test of the bounded waits: a one-thread kernel arms an mbarrier for more bytes than the single
+ * 32-byte copy from `src32` (device memory, 16-byte aligned) delivers and waits for at most limit_ns
+ * (1 .. 1e9).  Nothing stays in flight and nothing faults; the wait has to give up, writes 1 to
+ * *gave_up_dev (device int32) and raises the device flag with the code of a copy time-out, which
+ * af8_device_status then reports until af8_device_status_clear.  No counterpart in the reference. */
+AF8_API int af8_selftest_bounded_wait(const void *src32, int64_t limit_ns, int32_t *gave_up_dev, void *stream);
 
 /* Upload the signed dynamic-map codebooks (256 and 16 sorted entries) used by
  * the d8 / d4 momentum formats to the current device.
