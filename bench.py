@@ -439,6 +439,10 @@ def run_gpu_arm(args):
         # a bf16 compute copy written by the update kernels; the fp32 masters stay with their owner.
         copy_dtype = torch.bfloat16 if (pdtype == torch.float32 and not args.fp32_gather) else None
         opt = ShardedAdafactor8Bit(groups, compute_dtype=copy_dtype, **wl["hp"])
+        # the sharded optimizer numbers the tensors group by group: follow its order from here on
+        shape_of = {id(p): entry for (_, p), entry in zip(named, shapes)}
+        params = list(opt.all_params)
+        shapes = [shape_of[id(p)] for p in params]
         owned = sorted({i for (i, lo, hi, k, pc) in opt._local})      # tensors of which this rank updates a piece
     else:
         opt = Adafactor8Bit(groups, **wl["hp"])
