@@ -993,10 +993,13 @@ class ApolloPlan:
             self._low_plans[key] = plan
         return plan
 
-    def run(self, grads, pts, per_tensor, lowrank_scalars, first_flags, floor_later, stream=None):
+    def run(self, grads, pts, per_tensor, lowrank_scalars, first_flags, floor_later, stream=None, params=None):
         """per_tensor: list of dicts with the ApolloScalarsIn fields, decay, has_decay and the
-        device scalar `fira_prev` (or None).  lowrank_scalars: v_w, m_w, apollo_eps."""
+        device scalar `fira_prev` (or None).  lowrank_scalars: v_w, m_w, apollo_eps.
+        params: this step's 2-D views of the parameters (their storage may have been replaced)."""
         stream = stream or torch.cuda.current_stream(self.device)
+        if params is not None:
+            self.params = list(params)
         lib = N.lib()
         s = stream.cuda_stream
         log = LAUNCH_LOG
@@ -1027,7 +1030,8 @@ class ApolloPlan:
             k = len(idx)
             cols = dict(decay=np.zeros(k, np.float32), alpha=np.full(k, -1.0, np.float32),
                         v_w=np.full(k, lowrank_scalars["v_w"], np.float32),
-                        v_keep=np.full(k, lowrank_scalars["v_keep"], np.float32), v_eps_add=np.zeros(k, np.float32),
+                        v_keep=np.full(k, -1.0 if self.v_fmt == "fp32" else lowrank_scalars["v_keep"], np.float32),   # fp32 V: lerp_
+                        v_eps_add=np.zeros(k, np.float32),
                         m_w=np.full(k, lowrank_scalars["m_w"], np.float32), eps_gradsq=np.zeros(k, np.float32),
                         eps_denom=np.full(k, lowrank_scalars["apollo_eps"], np.float32),
                         eps_sq=np.full(k, 1.17549435e-38, np.float32))

@@ -813,9 +813,7 @@ class Adafactor8Bit(Optimizer):
                 fullrank.setdefault(key, []).append(ent)
                 continue
             if apollo_rank > 0 and "apollo_seed" in st:
-                if g.dim() != 2:
-                    raise NotImplementedError("APOLLO tensors with more than two dimensions are not available in this build")
-                apollo_items.append(ent)
+                apollo_items.append(ent)        # more than two dimensions: stepped as (shape[0], -1), optimizer.py:2634-2639
                 continue
             quant = st.get("is_quantized", False)
             if group.get("beta1") is not None:
@@ -889,9 +887,12 @@ class Adafactor8Bit(Optimizer):
         quant0 = items[0][2].get("is_quantized", False)
         v_fmt = items[0][2].get("v_quant_type", "al8") if quant0 else "fp32"
         m_fmt = ((items[0][2].get("m_quant_type", "uf8") if quant0 else "fp32") if beta1 is not None else None)
-        if v_fmt == "fp32" or m_fmt == "fp32":
-            raise NotImplementedError("APOLLO with fp32 low-rank states is not available in this build")
-        ids = tuple(id(p) for p, _, _ in items)
+        # tensors of more than two dimensions are stepped as (shape[0], -1) matrices (optimizer.py:2634-2639);
+        # fp16 gradients are widened first, as the reference widens every gradient (optimizer.py:2601)
+        pcs = [self._pieces.get(id(p)) for p, _, _ in items]
+        items = [(p if p.dim() == 2 else p.view(p.shape[0], -1),
+                  (g.float() if g.dtype == torch.float16 else g).reshape(g.shape[0], -1), st) for p, g, st in items]
+        ids = tuple(p.data_ptr() for p, _, _ in items)     # (also follows a parameter whose storage was replaced)
         pkey = (gi, "apollo", items[0][1].dtype, items[0][0].dtype, v_fmt, m_fmt, rank, bool(group["maximize"]))
         sr = bool(group.get("stochastic_round_writeback", False)) and items[0][0].dtype in (torch.bfloat16, torch.float16)
         plan = self._plans.get(pkey)
@@ -916,11 +917,11 @@ class Adafactor8Bit(Optimizer):
                     st["v_low_shape"] = torch.Size([nl])
             if beta1 is not None and st.get("m_low_q") is None and st.get("m_low") is None:
                 tmp = {}
-                _new_m_state(tmp, nl, st.get("m_block_size", m_block), m_fmt, p.device, (nl,), prefix="m_low")
+                low_shape = (R, rank) if R >= C else (rank, C)             # an fp32 momentum has the projected gradient's shape
+                _new_m_state(tmp, nl, st.get("m_block_size", m_block), m_fmt, p.device, low_shape, prefix="m_low")
                 tmp.pop("m_quant_type", None)
                 st.update(tmp)
         if plan is None or plan.ids != ids:
-            pcs = [self._pieces.get(id(p)) for p, _, _ in items]
             plan = ApolloPlan(device, items[0][1].dtype, v_fmt, m_fmt, block, m_block, group["maximize"],
                               [p for p, _, _ in items], [s for _, _, s in items], rank,
                               copies=[pc.copy if pc is not None else None for pc in pcs])
@@ -969,7 +970,7 @@ class Adafactor8Bit(Optimizer):
                    apollo_eps=f32(apollo_eps))
         floor_later = math.log2(max(apollo_eps * apollo_eps, _FLOOR))                  # optimizer.py:2766-2767
         def passes():
-            plan.run(grads, pts, per_tensor, low, first_flags, floor_later)
+            plan.run(grads, pts, per_tensor, low, first_flags, floor_later, params=[p for p, _, _ in items])
             return
             yield                                                                       # (no exchange points)
         return 0, device, passes()

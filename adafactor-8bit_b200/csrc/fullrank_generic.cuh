@@ -157,6 +157,9 @@ fullrank_generic_kernel(const FullrankLaunch L, const GenericCfg C)
                     const float v_old = al_decode(code, v_scale, v_min_log, qm1);
                     const float g2 = __fadd_rn(__fmul_rn(gj, gj), sT.eps_gradsq);
                     vj = lerp_t(v_old, g2, sT.v_w);
+                } else if (sT.v_keep < 0.0f) {   // fp32 state updated with Tensor.lerp_ (APOLLO's low-rank V, optimizer.py:2797-2799)
+                    vj = lerp_t(sT.v_f32[base + i], __fadd_rn(__fmul_rn(gj, gj), sT.eps_gradsq), sT.v_w);
+                    if (writes) sT.v_f32[base + i] = vj;
                 } else {         // optimizer.py:2186-2189
                     const float keep = __fmul_rn(sT.v_f32[base + i], sT.v_keep);
                     vj = __fmaf_rn(__fmul_rn(sT.v_w, gj), gj, keep);

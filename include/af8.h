@@ -136,7 +136,9 @@ typedef struct af8_fullrank_tensor {
     float decay;            /* 1 - wd_mult*wd; 1.0 when weight_decay == 0 */
     float alpha;            /* step size with bias correction folded in */
     float v_w;              /* second-moment EMA weight beta_val */
-    float v_keep;           /* float(1 - beta_val), used by the fp32 V state; with AF8_V_NONE:
+    float v_keep;           /* float(1 - beta_val), used by the fp32 V state (v*v_keep + v_w*g*g, the mul_ / addcmul_
+                               form of optimizer.py:2186-2189); a negative value selects Tensor.lerp_(g*g, v_w)
+                               instead (APOLLO's fp32 low-rank state, optimizer.py:2797-2799); with AF8_V_NONE:
                                float(1 - beta1), the divisor of the momentum */
     float v_eps_add;        /* float(beta_val * eps_for_grad_sq), fp32 V state */
     float m_w;              /* float(1 - beta1) */

@@ -222,6 +222,16 @@ CASES["apollo_bf16p"] = dict(shapes=[(256, 128), (64, 384), (4096,)], steps=5, s
                              hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=16, apollo_update_proj_gap=3,
                                      m_quant_type="uf8", v_quant_type="al8", block_size=2048))
 CASES["apollo_sr_bf16p"] = dict(CASES["apollo_bf16p"], seed=48, hp=dict(CASES["apollo_bf16p"]["hp"], stochastic_round_writeback=True))
+# APOLLO with fp32 low-rank states (quantize=False: Tensor.lerp_ on both moments, momentum kept in the projected
+# gradient's shape), and on a tensor of three dimensions (stepped as (shape[0], -1)) with fp16 gradients
+CASES["apollo_fp32_states"] = dict(shapes=[(96, 64), (32, 160)], steps=5, seed=49,
+                                   grad=dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="bf16"),
+                                   hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=8, apollo_update_proj_gap=3,
+                                           quantize=False))
+CASES["apollo_3d_f16g"] = dict(shapes=[(12, 8, 16), (40, 4, 6)], steps=5, seed=50,
+                               grad=dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="f16"),
+                               hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=8, apollo_update_proj_gap=3,
+                                       m_quant_type="uf8", v_quant_type="al8", block_size=256, min_8bit_size=64))
 MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
 
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]

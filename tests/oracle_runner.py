@@ -22,7 +22,8 @@ class OracleRun:
         self.hp = o.hyper(**self.case["hp"], param_dtype=self.case.get("param_dtype", "f32"))
         self.params0, self.grads = cases.case_inputs(self.case)
         self.params = [p.copy() for p in self.params0]
-        self.states = [o.init_state(p.shape, self.hp) for p in self.params]
+        # an APOLLO tensor of more than two dimensions is stepped as a (shape[0], -1) matrix (optimizer.py:2634-2639)
+        self.states = [o.init_state(self._matrix_shape(p.shape), self.hp) for p in self.params]
         seed = 1                                 # optimizer-level counter (optimizer.py:1460, 1727-1728)
         for st in self.states:
             if "apollo_seed" in st:
@@ -33,10 +34,16 @@ class OracleRun:
                 st["sr_seed"] = k + 1
         self.t = 0
 
+    def _matrix_shape(self, shape):
+        if self.hp["apollo_rank"] > 0 and len(shape) > 2:
+            return (shape[0], int(np.prod(shape[1:])))
+        return tuple(shape)
+
     def step_param(self, i, p, g, st):
         shape = p.shape
         if self.hp["apollo_rank"] > 0 and len(shape) >= 2:
-            return o.apollo_step(p, g, st, self.hp)
+            m = self._matrix_shape(shape)
+            return o.apollo_step(p.reshape(m), g.reshape(m), st, self.hp)      # (views: the update lands in p)
         if len(shape) >= 2 and self.hp["factored"] and not o.is_sgd(self.hp):
             return o.factored_step(p, g, st, self.hp)
         return o.fullrank_step(p.reshape(-1), g.reshape(-1), st, self.hp)

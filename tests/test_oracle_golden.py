@@ -210,6 +210,32 @@ def test_apollo_oracle_against_reference(oracle, name):
                 parity.assert_codes(st["m_q"], ref["m_q"], what + " m_q", zero_reserved=False)
 
 
+@pytest.mark.parametrize("name", ["apollo_fp32_states", "apollo_3d_f16g"])
+def test_apollo_variants_against_reference(oracle, name):
+    """APOLLO with fp32 low-rank states (quantize=False: both moments by Tensor.lerp_, no codes), and on
+    tensors of three dimensions (stepped as (shape[0], -1) matrices) with fp16 gradients.  Bounds as in the
+    test above: the reference's float32 GEMM rounds the projected gradient differently."""
+    run = OracleRun(name)
+    gold = load_golden(name)
+    assert str(gold["digest"]) == cases.inputs_digest(run.params0, run.grads)
+    for t in range(1, run.case["steps"] + 1):
+        run.step()
+        for i, (p, st) in enumerate(zip(run.params, run.states)):
+            ref = golden_entries(gold, t, i)
+            what = f"{name} step {t} param {i}"
+            parity.assert_params(p, ref["param"], what, tol=5e-5)
+            if "apollo_proj_matrix_T" in ref:
+                assert np.array_equal(st["apollo_proj_matrix_T"].reshape(-1), ref["apollo_proj_matrix_T"]), what
+            for key in ("v_low", "m_low"):
+                if key in ref:
+                    assert st[key].size == ref[key].size, what
+                    assert parity.rel_l2(st[key], ref[key]) <= 2e-5, (what, key, parity.rel_l2(st[key], ref[key]))
+            if "m_low_q" in ref:
+                s = parity.code_stats(st["m_low_q"], ref["m_low_q"])
+                assert s["max"] <= 1 and s["neq"] <= max(2, 2e-3 * s["n"]), (what, s)
+            assert parity.rel_l2(st["scaled_grad_norm_prev"], ref["scaled_grad_norm_prev"]) <= 1e-4, what
+
+
 # ---------------------------------------------------------------------------
 # bf16 / fp16 parameters, nearest and stochastic rounding (optimizer.py:162-292, 866-881)
 # ---------------------------------------------------------------------------
