@@ -29,6 +29,9 @@ constexpr int STAT_THREADS = 256;
 #ifndef AF8_STAT_UNROLL
 #define AF8_STAT_UNROLL 4
 #endif
+#ifndef AF8_STAT_PREFETCH
+#define AF8_STAT_PREFETCH 0      /* measured on the TinyLlama set: 0.972 ms with the requests, 0.955 ms without */
+#endif
 #define AF8_PRAGMA_(x) _Pragma(#x)
 #define AF8_UNROLL_(n) AF8_PRAGMA_(unroll n)
 
@@ -99,6 +102,22 @@ fullrank_stat_kernel(const FullrankLaunch L)
         const int64_t b = blk - cur_first;
         const int64_t base = b * FAST_VBLOCK;
         const int64_t rem = numel - base;
+#if AF8_STAT_PREFETCH
+        // Optional: ask L2 for this warp's next block (same tensor, a full block) while this one is worked
+        // on: the gradient is 32 lines of 128 bytes (one per lane), the two code arrays 16 lines each.
+        {
+            const int64_t nb = b + warps;
+            if (blk + warps < cur_end && (nb + 1) * FAST_VBLOCK <= numel) {
+                const int64_t nbase = nb * FAST_VBLOCK;
+                constexpr int GBYTES = std::is_same<GradT, float>::value ? 4 : 2;
+                const char *gp = static_cast<const char *>(grad) + nbase * GBYTES;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(gp + lane * 128));
+                if (GBYTES == 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(gp + 4096 + lane * 128));
+                const uint8_t *cp = (lane < 16 ? mq : vq) + nbase + (lane & 15) * 128;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(cp));
+            }
+        }
+#endif
         // decode v = 2^((code-1)*scale/254 + min_log) as 2^(code*a + c)
         const float sc = __ldg(v_scale + b), ml = __ldg(v_min_log + b);
         const float a = sc * (1.0f / 254.0f);
