@@ -462,6 +462,9 @@ apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, 
     }
 }
 
+#ifndef AF8_APOLLO_APPLY_PREFETCH
+#define AF8_APOLLO_APPLY_PREFETCH 0     /* iterations ahead that the write-back requests from L2; 0: off */
+#endif
 // the same with 8 consecutive elements per thread and 128-bit accesses (cols % 8 == 0,
 // 16-byte aligned arrays, fewer than 2^34 elements)
 // LOWP: the parameter is bf16 / fp16 (8 of them in one 128-bit word); P is ignored otherwise
@@ -480,6 +483,18 @@ apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ gra
     for (uint32_t grp = blockIdx.x * 256u + threadIdx.x; grp < ngroups; grp += gridDim.x * 256u) {
         const uint32_t row = grp / gpr, c8 = (grp - row * gpr) << 3;
         const int64_t idx = (int64_t)grp << 3;
+#if AF8_APOLLO_APPLY_PREFETCH > 0
+        {   // ask L2 for what this thread reads a few iterations on: one request per 128-byte line
+            const uint64_t ahead = (uint64_t)grp + (uint64_t)AF8_APOLLO_APPLY_PREFETCH * gridDim.x * 256u;
+            if (ahead < ngroups) {
+                const int64_t pidx = (int64_t)ahead << 3;
+                if ((threadIdx.x & (BF16 ? 7 : 3)) == 0)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(grad) + pidx * (BF16 ? 2 : 4)));
+                if ((threadIdx.x & (LOWP ? 7 : 3)) == 0)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(param_v) + pidx * (LOWP ? 2 : 4)));
+            }
+        }
+#endif
         float g[8], f[8], pv[8];
         if (BF16) {
             const uint4 a = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(grad) + idx));

@@ -133,6 +133,10 @@ WORKLOADS = {
         shapes=lambda: llama_shapes(4, 2048, 5632, 256, 32000)[1:-2], grad="bf16", bytes_per_param=14,
         hp=dict(_ADAMW, lr=1e-3, weight_decay=0.01, block_size=2048, m_block_size=256,
                 m_quant_type="uf8", v_quant_type="al8", enable_fira_for_adafactor=True, fira_margin=0.01, lag_norm=True)),
+    # four TinyLlama decoder layers with factored Adafactor (constructor defaults): small case for profiler captures
+    "tinyllama_4layers_adafactor": dict(
+        shapes=lambda: llama_shapes(4, 2048, 5632, 256, 32000)[1:-2], grad="bf16", bytes_per_param=10,
+        hp=dict(block_size=256)),
     # one 4096x4096 fp32 parameter with fp32 gradients
     "single_4096_adamw": dict(
         shapes=lambda: [("w", (4096, 4096))], grad="f32", bytes_per_param=16,
