@@ -465,6 +465,9 @@ apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, 
 #ifndef AF8_APOLLO_APPLY_PREFETCH
 #define AF8_APOLLO_APPLY_PREFETCH 0     /* iterations ahead that the write-back requests from L2; 0: off */
 #endif
+#ifndef AF8_APOLLO_APPLY_RUNS
+#define AF8_APOLLO_APPLY_RUNS 0         /* 1: a CTA walks one contiguous run of chunks; 0: grid-stride */
+#endif
 // the same with 8 consecutive elements per thread and 128-bit accesses (cols % 8 == 0,
 // 16-byte aligned arrays, fewer than 2^34 elements)
 // LOWP: the parameter is bf16 / fp16 (8 of them in one 128-bit word); P is ignored otherwise
@@ -480,13 +483,22 @@ apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ gra
     const uint32_t gpr = (uint32_t)(cols >> 3);                 // groups of 8 per row
     const uint32_t ngroups = (uint32_t)((rows * cols) >> 3);
     const float st = scale_tensor ? __ldg(sf) : 0.0f;
-    for (uint32_t grp = blockIdx.x * 256u + threadIdx.x; grp < ngroups; grp += gridDim.x * 256u) {
+#if AF8_APOLLO_APPLY_RUNS
+    // every CTA takes one contiguous run of 2048-element chunks
+    const uint32_t nchunks = (ngroups + 255u) / 256u;
+    const uint32_t per_cta = (nchunks + gridDim.x - 1) / gridDim.x;
+    const uint32_t limit = min((uint64_t)ngroups, (uint64_t)(blockIdx.x + 1) * per_cta * 256u);
+    const uint32_t first = blockIdx.x * per_cta * 256u + threadIdx.x, stride = 256u;
+#else
+    const uint32_t limit = ngroups, first = blockIdx.x * 256u + threadIdx.x, stride = gridDim.x * 256u;
+#endif
+    for (uint32_t grp = first; grp < limit; grp += stride) {
         const uint32_t row = grp / gpr, c8 = (grp - row * gpr) << 3;
         const int64_t idx = (int64_t)grp << 3;
 #if AF8_APOLLO_APPLY_PREFETCH > 0
         {   // ask L2 for what this thread reads a few iterations on: one request per 128-byte line
-            const uint64_t ahead = (uint64_t)grp + (uint64_t)AF8_APOLLO_APPLY_PREFETCH * gridDim.x * 256u;
-            if (ahead < ngroups) {
+            const uint64_t ahead = (uint64_t)grp + (uint64_t)AF8_APOLLO_APPLY_PREFETCH * stride;
+            if (ahead < limit) {
                 const int64_t pidx = (int64_t)ahead << 3;
                 if ((threadIdx.x & (BF16 ? 7 : 3)) == 0)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(grad) + pidx * (BF16 ? 2 : 4)));

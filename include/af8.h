@@ -13,9 +13,12 @@
  *   - every function returns AF8_OK (0) or an AF8_ERR_* code; af8_last_error()
  *     returns the message of the calling thread's last failure;
  *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and
- *     no entry point synchronises the device;
- *   - the caller owns all memory; the library keeps nothing between calls
- *     except the two dynamic-map codebooks in constant memory;
+ *     no entry point synchronises the device (except af8_device_status and
+ *     af8_device_status_clear, which say so);
+ *   - the caller owns all memory.  What the library keeps on a device between calls:
+ *     the two dynamic-map codebooks in constant memory, the sticky error flag that
+ *     af8_device_status reads, and the fixed 1 MiB array of
+ *     af8_fullrank_limited_step_noalloc;
  *   - tensor tables (`af8_*_tensor` arrays) live in DEVICE memory; they are
  *     filled on the host and copied by the caller;
  *   - the current device must be the one that owns the pointers.

@@ -294,3 +294,45 @@ def test_full_state_dict_matches_single_process_layout():
     for rank in range(world):
         for a, b in zip(out[rank][1], ref3):
             assert torch.equal(a, b.detach())
+
+
+def test_merging_and_cutting_of_native_state_entries():
+    """full_state_dict / load_full_state_dict on the optimizer's own state layout, without a GPU: the states
+    of the pieces of a cut tensor (code arrays padded to the block, per-block ranges, packed 4-bit momentum,
+    row / column states kept by every owner) put together give the whole tensor's state, and cutting that
+    again gives the pieces back."""
+    from adafactor8bit.zero import ShardedAdafactor8Bit
+
+    class Fake(ShardedAdafactor8Bit):
+        def __init__(self, shape):
+            self.all_params = [torch.zeros(shape)]
+
+    block, m_block = 256, 64
+    # a full-rank tensor of 1000 elements cut at 512 (both multiples of the blocks), packed uf4 momentum
+    whole = {"step": 3, "block_size": block, "m_block_size": m_block, "m_quant_type": "uf4", "v_quant_type": "al8",
+             "variance_q": torch.arange(1024, dtype=torch.int32).to(torch.uint8), "variance_scale": torch.arange(4.0),
+             "variance_min_log": -torch.arange(4.0), "variance_shape": torch.Size([1000]), "variance_pad": 24,
+             "m_q": torch.arange(512, dtype=torch.int32).to(torch.uint8), "m_scale": torch.arange(16.0),
+             "fira_prev_norm": torch.tensor(0.5)}
+    z = Fake((1000,))
+    a = z._slice(0, 0, 512, (512,), whole)
+    b = z._slice(0, 512, 1000, (488,), whole)
+    assert a["variance_q"].numel() == 512 and b["variance_q"].numel() == 512 and b["variance_pad"] == 24 and a["variance_pad"] == 0
+    assert a["m_q"].numel() == 256 and b["m_q"].numel() == 256 and a["m_scale"].numel() == 8 and b["m_scale"].numel() == 8
+    assert tuple(b["variance_shape"]) == (488,) and float(b["fira_prev_norm"]) == 0.5
+    merged = z._merge(0, [(512, 1000, (488,), b), (0, 512, (512,), a)])
+    assert sorted(merged) == sorted(whole)
+    for k, v in whole.items():
+        assert torch.equal(merged[k], v) if isinstance(v, torch.Tensor) else merged[k] == v, k
+    # a factored tensor cut by rows: fp32 momentum follows the rows, the row / column states are shared
+    shape = (8, 64)
+    whole = {"step": 1, "block_size": block, "m_block_size": m_block, "m": torch.arange(512.0).reshape(shape),
+             "row_var_q": torch.arange(256, dtype=torch.int32).to(torch.uint8), "row_var_scale": torch.ones(1),
+             "col_var": torch.arange(64.0).reshape(1, 64)}
+    z = Fake(shape)
+    a = z._slice(0, 0, 128, (2, 64), whole)
+    b = z._slice(0, 128, 512, (6, 64), whole)
+    assert tuple(a["m"].shape) == (2, 64) and tuple(b["m"].shape) == (6, 64) and torch.equal(b["row_var_q"], whole["row_var_q"])
+    merged = z._merge(0, [(0, 128, (2, 64), a), (128, 512, (6, 64), b)])
+    for k, v in whole.items():
+        assert torch.equal(merged[k], v) if isinstance(v, torch.Tensor) else merged[k] == v, k
