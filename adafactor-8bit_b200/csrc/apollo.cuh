@@ -553,19 +553,20 @@ apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ gra
         float4 *pp = reinterpret_cast<float4 *>(param + idx);
         const float4 p0 = pp[0], p1 = pp[1];
         pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
+        // pairs of elements in packed binary32 arithmetic (each component rounds like the scalar operation)
+        const float2 fs2 = bc2(fs), ss2 = bc2(sqrt_scale), us2 = bc2(us), decay2 = bc2(decay);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            float ge = g[e];
-            if (!isfinite(ge)) ge = 0.0f;                                    // optimizer.py:2606
-            if (negate) ge = -ge;
-            float fe = f[e];
-            if (fira) fe = __fmul_rn(fe, fs);                                // optimizer.py:2994
-            if (!front) fe = __fmul_rn(fe, sqrt_scale);                      // optimizer.py:3000
-            float x = pv[e];
-            if (has_decay) x = __fmul_rn(x, decay);                          // optimizer.py:3075
-            if (scale_tensor) x = __fmaf_rn(__fmul_rn(us, fe), ge, x);       // optimizer.py:3079
-            else x = __fmaf_rn(__fmul_rn(us, ge), fe, x);                    // optimizer.py:3077
-            pv[e] = x;
+        for (int e = 0; e < 8; e += 2) {
+            float2 ge = make_float2(isfinite(g[e]) ? g[e] : 0.0f, isfinite(g[e + 1]) ? g[e + 1] : 0.0f);   // optimizer.py:2606
+            if (negate) ge = make_float2(-ge.x, -ge.y);
+            float2 fe = make_float2(f[e], f[e + 1]);
+            if (fira) fe = __fmul2_rn(fe, fs2);                              // optimizer.py:2994
+            if (!front) fe = __fmul2_rn(fe, ss2);                            // optimizer.py:3000
+            float2 x = make_float2(pv[e], pv[e + 1]);
+            if (has_decay) x = __fmul2_rn(x, decay2);                        // optimizer.py:3075
+            if (scale_tensor) x = __ffma2_rn(__fmul2_rn(us2, fe), ge, x);    // optimizer.py:3079
+            else x = __ffma2_rn(__fmul2_rn(us2, ge), fe, x);                 // optimizer.py:3077
+            pv[e] = x.x; pv[e + 1] = x.y;
         }
         pp[0] = make_float4(pv[0], pv[1], pv[2], pv[3]);
         pp[1] = make_float4(pv[4], pv[5], pv[6], pv[7]);

@@ -139,6 +139,31 @@ __device__ __forceinline__ uint32_t uf8_encode_fast(float m, const DivBy &A)
     return (uint32_t)(k - 0x4b400000 + 128);
 }
 
+// The same helpers on pairs of elements with Blackwell's packed binary32 instructions (one
+// instruction per pair; each component rounds exactly like the scalar operation).
+__device__ __forceinline__ float2 div_by2(float2 x, const DivBy &D)
+{
+    if (D.one) return x;
+    const float2 r2 = bc2(D.rcp);
+    const float2 q = __fmul2_rn(x, r2);
+    const float2 q2 = __ffma2_rn(__ffma2_rn(q, bc2(D.nd), x), r2, q);
+    return make_float2(fabsf(q.x) <= 3.402823466e38f ? q2.x : q.x, fabsf(q.y) <= 3.402823466e38f ? q2.y : q.y);
+}
+__device__ __forceinline__ float2 lerp_w2(float2 s, float2 e, const LerpW &l)
+{
+    return __ffma2_rn(bc2(l.ww), sub2(e, s), l.small ? s : e);
+}
+// two UF8 codes, the first in the low byte
+__device__ __forceinline__ uint32_t uf8_encode_fast2(float2 m, const DivBy &A)
+{
+    const float2 r2 = bc2(A.rcp);
+    const float2 q = __fmul2_rn(m, r2);
+    const float2 q2 = __ffma2_rn(__ffma2_rn(q, bc2(A.nd), m), r2, q);
+    const float2 kf = __ffma2_rn(q2, bc2(128.0f), bc2(12582912.0f));
+    const int k0 = min(__float_as_int(kf.x), 0x4b400000 + 127), k1 = min(__float_as_int(kf.y), 0x4b400000 + 127);
+    return (uint32_t)(k0 - 0x4b400000 + 128) | ((uint32_t)(k1 - 0x4b400000 + 128) << 8);
+}
+
 // ---------------------------------------------------------------------------
 // statistics
 // ---------------------------------------------------------------------------
@@ -584,20 +609,26 @@ __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_fa
             float x[8];
             if (!RESIDUAL) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(g[k][j], g[k][j]);
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 gj = make_float2(g[k][j], g[k][j + 1]);
+                    const float2 xx = __fmul2_rn(gj, gj);
+                    x[j] = xx.x; x[j + 1] = xx.y;
+                }
             } else if (live) {
                 const int64_t flat = r * C + c;
-                const float ir = sT.inv_row[r];
+                const float2 ir2 = bc2(sT.inv_row[r]);
                 const DivBy D = make_div(pre_div);
                 const LerpW LW = make_lerp(sT.m_w);
+                const float2 eps2 = bc2(sT.eps_came);
                 float mo[8];
                 m_old8(sT, L.m_fmt, L.m_block, flat, mo);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float u = u_clipped_fast(g[k][j], ir, ic[j], D);
-                    const float m = lerp_w(mo[j], u, LW);
-                    const float df = __fsub_rn(u, m);
-                    x[j] = __fadd_rn(__fmul_rn(df, df), sT.eps_came);
+                for (int j = 0; j < 8; j += 2) {       // pairs in packed binary32 arithmetic (bit-identical to element-wise)
+                    const float2 u = div_by2(__fmul2_rn(__fmul2_rn(make_float2(g[k][j], g[k][j + 1]), ir2), make_float2(ic[j], ic[j + 1])), D);
+                    const float2 m = lerp_w2(make_float2(mo[j], mo[j + 1]), u, LW);
+                    const float2 df = sub2(u, m);
+                    const float2 xx = __fadd2_rn(__fmul2_rn(df, df), eps2);
+                    x[j] = xx.x; x[j + 1] = xx.y;
                 }
             } else {
 #pragma unroll
@@ -861,36 +892,53 @@ factored_update_vec_kernel(const FactoredLaunch L)
             cg.unpack(L.negate_grad, g);
             load_f8_ro(sT.inv_col + col, ic);
             const float ir = __ldg(sT.inv_row + row);
+            // pairs of elements in packed binary32 arithmetic (bit-identical to the element-wise form)
+            const float2 ir2 = bc2(ir);
             if (L.came) {
                 if (L.mode == AF8_FUPD_SUMSQ_U) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) u[j] = u_clipped(g[j], ir, ic[j], 1.0f);
+                    for (int j = 0; j < 8; j += 2) {
+                        const float2 uj = __fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1]));
+                        u[j] = uj.x; u[j + 1] = uj.y;
+                    }
                 } else {
                     float mo[8], icc[8];
                     m_old8(sT, L.m_fmt, L.m_block, flat, mo, pre_m, cm);
                     load_f8_ro(sT.inv_col_conf + col, icc);
-                    const float irc = __ldg(sT.inv_row_conf + row);
+                    const float2 irc2 = bc2(__ldg(sT.inv_row_conf + row));
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        mj[j] = lerp_w(mo[j], u_clipped_fast(g[j], ir, ic[j], D), LW);
-                        u[j] = __fmul_rn(__fmul_rn(mj[j], irc), icc[j]);
+                    for (int j = 0; j < 8; j += 2) {
+                        const float2 ut = div_by2(__fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1])), D);
+                        const float2 mm = lerp_w2(make_float2(mo[j], mo[j + 1]), ut, LW);
+                        const float2 uj = __fmul2_rn(__fmul2_rn(mm, irc2), make_float2(icc[j], icc[j + 1]));
+                        mj[j] = mm.x; mj[j + 1] = mm.y; u[j] = uj.x; u[j + 1] = uj.y;
                     }
                 }
             } else if (has_m) {
                 float mo[8];
                 m_old8(sT, L.m_fmt, L.m_block, flat, mo, pre_m, cm);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    mj[j] = lerp_w(mo[j], g[j], LW);
-                    u[j] = __fmul_rn(__fmul_rn(mj[j], ir), ic[j]);
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 mm = lerp_w2(make_float2(mo[j], mo[j + 1]), make_float2(g[j], g[j + 1]), LW);
+                    const float2 uj = __fmul2_rn(__fmul2_rn(mm, ir2), make_float2(ic[j], ic[j + 1]));
+                    mj[j] = mm.x; mj[j + 1] = mm.y; u[j] = uj.x; u[j + 1] = uj.y;
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) u[j] = __fmul_rn(__fmul_rn(g[j], ir), ic[j]);
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 uj = __fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1]));
+                    u[j] = uj.x; u[j + 1] = uj.y;
+                }
             }
             if (SUMS) {
+                // The thread's eight squares are added in binary32 (two packed chains) and enter the binary64
+                // partial as one number: the sum only feeds a norm (clip divisor, limiter), where a relative
+                // 1e-7 is far below what the parameters can show, and it saves seven conversions and seven
+                // binary64 additions per chunk.
+                float2 a2 = __fmul2_rn(make_float2(u[0], u[1]), make_float2(u[0], u[1]));
 #pragma unroll
-                for (int j = 0; j < 8; ++j) part += (double)__fmul_rn(u[j], u[j]);
+                for (int j = 2; j < 8; j += 2) a2 = __ffma2_rn(make_float2(u[j], u[j + 1]), make_float2(u[j], u[j + 1]), a2);
+                part += (double)__fadd_rn(a2.x, a2.y);
             }
             if (writes) {
                 if (lowp) {
@@ -910,11 +958,12 @@ factored_update_vec_kernel(const FactoredLaunch L)
                 } else {
                     float *pp = pbase + flat;
                     float p[8] = {cp0.x, cp0.y, cp0.z, cp0.w, cp1.x, cp1.y, cp1.z, cp1.w};
+                    const float2 decay2 = bc2(sT.decay), step2 = bc2(step_mul), fira2 = bc2(fira);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float pj = __fmul_rn(p[j], sT.decay);
-                        if (!zero_upd) pj = __fmaf_rn(step_mul, __fmul_rn(u[j], fira), pj);
-                        p[j] = pj;
+                    for (int j = 0; j < 8; j += 2) {
+                        float2 pj = __fmul2_rn(make_float2(p[j], p[j + 1]), decay2);
+                        if (!zero_upd) pj = __ffma2_rn(step2, __fmul2_rn(make_float2(u[j], u[j + 1]), fira2), pj);
+                        p[j] = pj.x; p[j + 1] = pj.y;
                     }
                     *reinterpret_cast<float4 *>(pp) = make_float4(p[0], p[1], p[2], p[3]);
                     *reinterpret_cast<float4 *>(pp + 4) = make_float4(p[4], p[5], p[6], p[7]);
@@ -945,12 +994,8 @@ factored_update_vec_kernel(const FactoredLaunch L)
             if (w0 < numel) {
                 if (L.m_fmt == AF8_M_UF8) {
                     const DivBy A = make_div(am);
-                    uint32_t o0 = 0, o1 = 0;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        o0 |= uf8_encode_fast(mj[j], A) << (8 * j);
-                        o1 |= uf8_encode_fast(mj[j + 4], A) << (8 * j);
-                    }
+                    const uint32_t o0 = uf8_encode_fast2(make_float2(mj[0], mj[1]), A) | (uf8_encode_fast2(make_float2(mj[2], mj[3]), A) << 16);
+                    const uint32_t o1 = uf8_encode_fast2(make_float2(mj[4], mj[5]), A) | (uf8_encode_fast2(make_float2(mj[6], mj[7]), A) << 16);
                     if (ok) *reinterpret_cast<uint2 *>(sT.m_q + flat) = make_uint2(o0, o1);
                 } else if (L.m_fmt == AF8_M_D8) {
                     uint32_t o0 = 0, o1 = 0;
