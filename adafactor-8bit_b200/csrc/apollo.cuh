@@ -342,40 +342,66 @@ __device__ __forceinline__ int find_finish_tensor(const af8_apollo_finish_tensor
     return lo;
 }
 
-// unit = 8 channels of one tensor, one warp per channel (as apollo_scales_kernel)
+// unit = 8 channels of one tensor.  Right case (a channel is a row of rank contiguous values): one
+// warp per channel.  Left case (a channel is a column of the rank x cols array): the 8 channels of the
+// unit are 32 contiguous bytes of every row, so 8 lanes take one row and the 32 groups of a CTA walk
+// the rows together; the sums of a channel are then added over the groups in a fixed order.
 __global__ void __launch_bounds__(256)
 apollo_scales_multi_kernel(const af8_apollo_finish_tensor *__restrict__ T, int n, int64_t total_units)
 {
     __shared__ double s_part[8];
+    __shared__ double s_nu[8][8], s_ng[8][8];        // left case: [warp][channel of the unit]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int64_t unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         const af8_apollo_finish_tensor *t = T + find_finish_tensor(T, n, unit);
         const int64_t rows = __ldg(&t->rows), cols = __ldg(&t->cols), rank = __ldg(&t->rank);
         const bool right = rows >= cols;
         const int64_t nch = right ? rows : cols;
-        const int64_t ch = (unit - __ldg(&t->first_unit)) * 8 + warp;
+        const int64_t ch0 = (unit - __ldg(&t->first_unit)) * 8;
+        const int64_t ch = ch0 + warp;
         const float *upd = t->upd, *g_low = t->g_low;
         double local = 0.0;
-        if (ch < nch) {
-            double nu = 0.0, ng = 0.0;
-            for (int64_t k = lane; k < rank; k += 32) {
-                const int64_t idx = right ? ch * rank + k : k * nch + ch;
-                const float u = upd[idx], g = g_low[idx];
-                nu += (double)__fmul_rn(u, u);
-                ng += (double)__fmul_rn(g, g);
+        double nu = 0.0, ng = 0.0;
+        if (right) {
+            if (ch < nch) {
+                for (int64_t k = lane; k < rank; k += 32) {
+                    const int64_t idx = ch * rank + k;
+                    const float u = upd[idx], g = g_low[idx];
+                    nu += (double)__fmul_rn(u, u);
+                    ng += (double)__fmul_rn(g, g);
+                }
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
                 nu += __shfl_xor_sync(0xffffffffu, nu, o);
                 ng += __shfl_xor_sync(0xffffffffu, ng, o);
             }
-            if (lane == 0) {
-                float s = __fdiv_rn(__double2float_rn(sqrt(nu)), __fadd_rn(__double2float_rn(sqrt(ng)), 1e-8f));   // optimizer.py:2964
-                if (__ldg(&t->in.scale_front)) s = __fmul_rn(s, __ldg(&t->in.sqrt_scale));                       // optimizer.py:2969-2971
-                t->sf[ch] = s;
-                const float nG = __double2float_rn(sqrt(t->chan_g2[ch]));
-                local = (double)__fmul_rn(__fmul_rn(nG, nG), __fmul_rn(s, s));                                   // optimizer.py:2975-2982
+        } else {
+            const int64_t c = ch0 + (lane & 7);
+            if (c < nch) {
+                for (int64_t k = warp * 4 + (lane >> 3); k < rank; k += 32) {
+                    const int64_t idx = k * nch + c;
+                    const float u = upd[idx], g = g_low[idx];
+                    nu += (double)__fmul_rn(u, u);
+                    ng += (double)__fmul_rn(g, g);
+                }
             }
+            nu += __shfl_xor_sync(0xffffffffu, nu, 8);  ng += __shfl_xor_sync(0xffffffffu, ng, 8);
+            nu += __shfl_xor_sync(0xffffffffu, nu, 16); ng += __shfl_xor_sync(0xffffffffu, ng, 16);
+            if (lane < 8) { s_nu[warp][lane] = nu; s_ng[warp][lane] = ng; }
+            __syncthreads();
+            nu = ng = 0.0;
+            if (lane == 0) {
+#pragma unroll
+                for (int w = 0; w < 8; ++w) { nu += s_nu[w][warp]; ng += s_ng[w][warp]; }
+            }
+        }
+        if (lane == 0 && ch < nch) {
+            float s = __fdiv_rn(__double2float_rn(sqrt(nu)), __fadd_rn(__double2float_rn(sqrt(ng)), 1e-8f));   // optimizer.py:2964
+            if (__ldg(&t->in.scale_front)) s = __fmul_rn(s, __ldg(&t->in.sqrt_scale));                       // optimizer.py:2969-2971
+            t->sf[ch] = s;
+            const float nG = __double2float_rn(sqrt(t->chan_g2[ch]));
+            local = (double)__fmul_rn(__fmul_rn(nG, nG), __fmul_rn(s, s));                                   // optimizer.py:2975-2982
         }
         __syncthreads();
         if (lane == 0) s_part[warp] = local;
@@ -646,7 +672,8 @@ inline int apollo_project_exact(const af8_apollo_proj_desc &d, int32_t grad_dtyp
     return apollo_channel_norms(d.grad, grad_dtype, d.rows, d.cols, d.chan_g2, nullptr, st);
 }
 
-// tensor-core path, per tensor: non-finite flag + channel norms, bf16 planes of Pt; fills the task
+// tensor-core path, per tensor: bf16 planes of Pt (and, for the mma.sync kernel, the non-finite flag and the
+// channel norms; the tcgen05 kernel produces both itself); fills the task
 // true: this projection runs on tcgen05 (right case, rank a multiple of 16 up to 256)
 // bytes of the transposed gradient that a left-case tensor needs on the tcgen05 path
 inline int64_t apollo_transpose_need(const af8_apollo_proj_desc &d)
@@ -668,9 +695,11 @@ inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dt
 {
     int *flag = static_cast<int *>(d.workspace);
     __nv_bfloat16 *planes = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(d.workspace) + APOLLO_WS_HEADER);
-    AF8_CUDA_TRY(cudaMemsetAsync(flag, 0, sizeof(int), st));
-    int rc = apollo_channel_norms(d.grad, grad_dtype, d.rows, d.cols, d.chan_g2, flag, st);
-    if (rc) return rc;
+    if (!umma) {       // the tcgen05 kernel finds non-finite entries and sums the channel norms itself
+        AF8_CUDA_TRY(cudaMemsetAsync(flag, 0, sizeof(int), st));
+        int rc = apollo_channel_norms(d.grad, grad_dtype, d.rows, d.cols, d.chan_g2, flag, st);
+        if (rc) return rc;
+    }
     const bool right = d.rows >= d.cols;
     const int64_t kdim = right ? d.cols : d.rows;
     const int64_t pn = kdim * d.rank;
@@ -815,6 +844,7 @@ extern "C" int af8_apollo_project_ws(const void *grad, int32_t grad_dtype, int32
         UmmaTask u;
         memset(&u, 0, sizeof(u));
         u.t = task;
+        u.chan_g2 = chan_g2;
         rc = apollo_umma_maps(u);
         if (rc) return rc;
         AF8_CUDA_TRY(cudaMemcpyAsync(slot, &u, sizeof(UmmaTask), cudaMemcpyHostToDevice, st));
@@ -880,6 +910,7 @@ extern "C" int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32
             memset(&u, 0, sizeof(u));
             rc = apollo_project_prepare(descs[i], grad_dtype, u.t, tiles_u, true, st, need > 0 ? static_cast<char *>(transpose_scratch) + t_off : nullptr);
             t_off += need;
+            u.chan_g2 = descs[i].chan_g2;
             if (!rc) rc = apollo_umma_maps(u);
         } else {
             rc = apollo_project_prepare(descs[i], grad_dtype, host_m[im++], tiles_m, false, st);

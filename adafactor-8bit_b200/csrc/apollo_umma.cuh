@@ -11,12 +11,15 @@
 // arrive with one three-dimensional copy per stage.
 //
 // CTA = 320 threads, one CTA per SM, persistent over (task, M tile) pairs:
-//   warps 0-7  drain the accumulator: warp w owns TMEM lanes 32 (w % 4) .. +31 and columns
-//              128 (w / 4) .. +127, 128 totals per thread; then store g_low.  When the
-//              gradient holds non-finite values they also clean each stage before its MMAs.
+//   warps 0-7  read every gradient tile from shared memory before its MMAs: they add up the
+//              squares of each row (the channel norms ||G_row||^2 that the scaling step needs,
+//              so the gradient is read from memory once) and zero non-finite entries; then
+//              drain the accumulator: warp w owns TMEM lanes 32 (w % 4) .. +31 and columns
+//              128 (w / 4) .. +127, 128 totals per thread; then store g_low and the norms.
 //   warp 8     allocates / frees TMEM; its lane 0 issues the MMAs and the commits
 //   warp 9     lane 0 issues the copies
-// Four 56 KB stages; a "full" barrier completes on the copies' transaction bytes, an "empty"
+// Four 56 KB stages; a "full" barrier completes on the copies' transaction bytes, a "clean"
+// barrier when the 256 workers have read (and, rarely, repaired) the gradient tile, an "empty"
 // barrier on tcgen05.commit.
 //
 // The tensor cores add into their binary32 accumulators with truncation, whose error grows
@@ -55,7 +58,8 @@ struct __align__(64) UmmaTask {
     CUtensorMap map_a;       // G as [M][K], box 128 x 32
     CUtensorMap map_b;       // planes as [3][N][K], box 3 x N x 32
     ProjTask t;
-    unsigned char pad[384 - 2 * sizeof(CUtensorMap) - sizeof(ProjTask)];
+    double *chan_g2;         // [M] sums of squares of the rows of G (non-finite entries count as zero)
+    unsigned char pad[384 - 2 * sizeof(CUtensorMap) - sizeof(ProjTask) - sizeof(double *)];
 };
 static_assert(sizeof(CUtensorMap) == 128 && sizeof(UmmaTask) == 384, "task layout");
 
@@ -155,6 +159,39 @@ apollo_split_transposed_kernel(const float *__restrict__ p, int K, int N, __nv_b
 
 __device__ __forceinline__ int volatile_load(const int *p) { return *reinterpret_cast<const volatile int *>(p); }
 
+// Sum of squares of the 8 bf16 values of a 16-byte chunk of a staged gradient tile.  The common
+// case is eight binary32 multiply-adds; when that sum is not finite (a NaN or an infinity in the
+// chunk, or squares beyond binary32) the non-finite entries are zeroed in shared memory, as the
+// reference zeroes them in the gradient (optimizer.py:2606), and the sum is redone in binary64.
+__device__ __forceinline__ double umma_chunk_sumsq(unsigned char *p, bool &wrote)
+{
+    uint4 v = *reinterpret_cast<uint4 *>(p);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xffff0000u);
+        s = __fmaf_rn(lo, lo, s);
+        s = __fmaf_rn(hi, hi, s);
+    }
+    if (s <= 3.0e38f) return (double)s;                          // false for NaN and infinity
+    bool changed = false;
+    double d = 0.0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if ((w[i] & 0x7f80u) == 0x7f80u) { w[i] &= 0xffff0000u; changed = true; }
+        if ((w[i] & 0x7f800000u) == 0x7f800000u) { w[i] &= 0x0000ffffu; changed = true; }
+        const double lo = (double)__uint_as_float(w[i] << 16), hi = (double)__uint_as_float(w[i] & 0xffff0000u);
+        d += lo * lo;
+        d += hi * hi;
+    }
+    if (changed) {
+        *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+        wrote = true;
+    }
+    return d;
+}
+
 __global__ void __launch_bounds__(UM_THREADS, 1)
 apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int total_tiles)
 {
@@ -184,11 +221,8 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
     // Running counters, advanced identically by every thread: stage fills and accumulator
     // chunks since the kernel started.  Use number n of a barrier = counter / ring size; the
     // consumer of use n waits for phase parity n & 1, the producer of use n >= 1 for (n-1) & 1.
-    // s_clean is only used by tiles of a tensor with non-finite entries; bit s of clean_phase
-    // is the parity its next consumer waits for.
     int fills = 0, gchunk = 0;
     int issued = 0;                 // producer only: stage fills issued so far
-    uint32_t clean_phase = 0;
 
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         if (volatile_load(&s_abort)) break;
@@ -203,7 +237,6 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
         const int m0 = (tile - __ldg(&T->first_tile)) * UM_BM;
         const int ksteps = (K + UM_BK - 1) / UM_BK;
         const int nchunks = (ksteps + UM_FLUSH - 1) / UM_FLUSH;
-        const bool dirty = __ldg(T->nonfinite_flag) != 0;      // rare: non-finite gradient entries count as zero
         const int plane_bytes = N * UM_ROW_BYTES;
         bool failed = false;
 
@@ -238,26 +271,30 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
                 mbar_arrive(&s_acc_empty[buf]);
                 return true;
             };
-            // dirty gradients: zero the non-finite entries of the stages of chunk c before their MMAs
-            auto clean = [&](int c) -> bool {
+            // The 8 KB gradient tile of a stage is 512 chunks of 16 bytes, two per thread; chunk i lies in
+            // row i / 4 of the tile (the swizzle permutes chunks within a row).  rs0 / rs1: this thread's
+            // share of the squared norms of rows tid / 4 and 64 + tid / 4, over all of K.
+            double rs0 = 0.0, rs1 = 0.0;
+            auto scan = [&](int c) -> bool {
                 const int k_end = min(ksteps, (c + 1) * UM_FLUSH);
                 for (int ks = c * UM_FLUSH; ks < k_end; ++ks) {
                     const int f = fills + ks, slot = f % UM_STAGES;
                     if (!mbar_wait_bounded(&s_full[slot], (uint32_t)(f / UM_STAGES) & 1u)) return false;
                     unsigned char *st = um_smem + slot * UM_STAGE_BYTES;
-                    clean_chunk(st + tid * 16);                  // the 8 KB gradient tile: two 16-byte chunks per thread
-                    clean_chunk(st + (tid + UM_WORKERS) * 16);
-                    fence_proxy_async();
+                    bool wrote = false;
+                    rs0 += umma_chunk_sumsq(st + tid * 16, wrote);
+                    rs1 += umma_chunk_sumsq(st + (tid + UM_WORKERS) * 16, wrote);
+                    if (wrote) fence_proxy_async();              // repaired entries must be visible to the MMAs
                     mbar_arrive(&s_clean[slot]);
                 }
                 return true;
             };
             for (int c = 0; c < nchunks && !failed; ++c) {
-                if (dirty && !clean(c)) { failed = true; break; }
-                if (dirty) { if (c >= 1 && !flush(c - 1)) failed = true; }
-                else if (!flush(c)) failed = true;
+                if (!scan(c)) { failed = true; break; }
+                if (c >= 1 && !flush(c - 1)) failed = true;
             }
-            if (dirty && !failed && !flush(nchunks - 1)) failed = true;
+            if (!failed && !flush(nchunks - 1)) failed = true;
+            failed = __any_sync(0xffffffffu, failed);            // uniform over the warp from here on
             // ---------------- epilogue: the totals to g_low ----------------
             if (!failed) {
                 const int m = m0 + row;
@@ -280,11 +317,19 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
                         if (n < N) out[(int64_t)n * M + m] = sgn * total[e];
                     }
                 }
+                // the four threads that share a row add their parts; one of them stores the norm
+                rs0 += __shfl_xor_sync(0xffffffffu, rs0, 1); rs0 += __shfl_xor_sync(0xffffffffu, rs0, 2);
+                rs1 += __shfl_xor_sync(0xffffffffu, rs1, 1); rs1 += __shfl_xor_sync(0xffffffffu, rs1, 2);
+                double *__restrict__ chan = U->chan_g2;
+                if ((tid & 3) == 0 && chan != nullptr) {
+                    const int ra = m0 + (tid >> 2), rb = ra + 64;
+                    if (ra < M) chan[ra] = rs0;
+                    if (rb < M) chan[rb] = rs1;
+                }
             }
         } else if (warp == UM_MMA_WARP && lane == 0) {
             // ---------------- MMA issuer ----------------
             const uint32_t idesc = umma_instr_desc(N);
-            uint32_t cph = clean_phase;
             for (int ks = 0; ks < ksteps; ++ks) {
                 const int g = gchunk + ks / UM_FLUSH, buf = g & 1;
                 const bool chunk_start = (ks % UM_FLUSH) == 0;
@@ -293,10 +338,9 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
                     tc_fence_after();
                 }
                 const int f = fills + ks, slot = f % UM_STAGES, use = f / UM_STAGES;
-                bool ok;
-                if (dirty) { ok = mbar_wait_bounded(&s_clean[slot], (cph >> slot) & 1u); cph ^= 1u << slot; }
-                else ok = mbar_wait_bounded(&s_full[slot], (uint32_t)use & 1u);
-                if (!ok) { failed = true; break; }
+                // the workers have read this stage (which also means that its copies have landed)
+                if (!mbar_wait_bounded(&s_clean[slot], (uint32_t)use & 1u)) { failed = true; break; }
+                if (!mbar_wait_bounded(&s_full[slot], (uint32_t)use & 1u)) { failed = true; break; }   // complete already: orders the copies before the MMAs in this thread
                 tc_fence_after();
                 const uint32_t a0 = smem_base + slot * UM_STAGE_BYTES;
                 const uint32_t d = tmem + (uint32_t)(buf * UM_MAXN);
@@ -339,8 +383,6 @@ apollo_project_umma_kernel(const UmmaTask *__restrict__ tasks, int n_tasks, int 
                 }
             break;
         }
-        if (dirty)
-            for (int ks = 0; ks < ksteps; ++ks) clean_phase ^= 1u << ((fills + ks) % UM_STAGES);
         fills += ksteps;
         gchunk += nchunks;
     }

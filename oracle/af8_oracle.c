@@ -991,6 +991,56 @@ typedef struct {
  * (2906-2953) states, update_low (2959), scaling factor (2961-2966), global norm
  * (2973-2988), Fira (2990-2996), write-back for fp32 parameters (3073-3079).
  * pt is proj_matrix_T: (cols, rank) when rows >= cols ("right"), else (rank, rows). */
+/* Further low-rank state rules of _update_param_apollo, selected by the next af8o_apollo_step
+ * after af8o_apollo_set_extra (cleared by that call):
+ *   factorize            row / column factors of the projected gradient's squares instead of
+ *                        v_low (optimizer.py:2688-2760), optionally with CAME's confidence
+ *                        vectors on top (2708-2750);
+ *   came, not factorize  CAME over the projected gradient: instability state res_low shaped
+ *                        like it (optimizer.py:2801-2903, the pure-PyTorch branch 2869-2894). */
+typedef struct {
+    int32_t factorize;        /* apollo_factorize */
+    int32_t came;             /* beta3 is not None */
+    int32_t c_fmt;            /* AF8O_V_* of conf_row_low / conf_col_low / res_low */
+    int32_t first_factor;     /* row_var_low does not exist yet (optimizer.py:2695) */
+    float v_keep;             /* float(1 - beta_val) */
+    float c_w;                /* float(1 - beta3) */
+    float eps_came;
+    float eps_sq;             /* max(apollo_eps^2, FLT_MIN) */
+    float d;                  /* clip threshold of U_t (the low-rank one, optimizer.py:2716-2718) */
+    float reserved;
+    float *row_var_low;       /* fp32 [LR] */
+    float *col_var_low;       /* fp32 [LC] */
+    af8o_small_state conf_row, conf_col;      /* factorize + CAME */
+    af8o_small_state res;                     /* CAME without factorisation: n = LR*LC */
+} af8o_apollo_extra;
+static const af8o_apollo_extra *apollo_extra = NULL;
+AF8O_API void af8o_apollo_set_extra(const af8o_apollo_extra *x) { apollo_extra = x; }
+
+/* U_t / clamp(rms(U_t)/d, 1) (optimizer.py:2716-2718, 2872-2874) */
+static void clip_low(float *u, int64_t n, float d)
+{
+    if (d > 0.0f) {
+        float rms = norm2_f64(u, n) / (float)sqrt((double)n);
+        float cf = rms / d;
+        if (cf < 1.0f) cf = 1.0f;
+        for (int64_t i = 0; i < n; ++i) u[i] = u[i] / cf;
+    }
+}
+
+/* the low-rank momentum (optimizer.py:714-729, 690-700): m receives the un-requantised values */
+static int low_m_ema(const af8o_apollo_cfg *c, const float *x, int64_t nl, uint8_t *m_q, float *m_scale, float *m_f32,
+                     const float *map, float *m)
+{
+    if (c->m_fmt != AF8O_M_FP32) {
+        af8o_m_dequantize(m_q, m_scale, nl, c->m_block, c->m_fmt, map, m);
+        for (int64_t i = 0; i < nl; ++i) m[i] = lerp_t(m[i], x[i], c->m_w);
+        return af8o_m_quantize(m, nl, c->m_block, c->m_fmt, map, m_q, m_scale);
+    }
+    for (int64_t i = 0; i < nl; ++i) { m_f32[i] = lerp_t(m_f32[i], x[i], c->m_w); m[i] = m_f32[i]; }
+    return 0;
+}
+
 /* Test hook: the next af8o_apollo_step takes this projected gradient (rows x rank or rank x cols
  * floats) instead of computing G*Pt, so that everything after the contraction can be compared
  * with a device run that started from the same projected values.  Cleared by that call. */
@@ -1060,6 +1110,58 @@ AF8O_API int af8o_apollo_step(const af8o_apollo_cfg *c, float *p, const void *gr
             free(acc);
         }
     }
+    const af8o_apollo_extra *x = apollo_extra;
+    apollo_extra = NULL;
+    int rc = 0;
+    if (x && x->factorize) {
+        /* optimizer.py:2688-2760.  update_low ends up in m. */
+        float *sq = v;                                       /* grad_low.square() */
+        float *rmean = (float *)malloc((size_t)LR * sizeof(float)), *cmean = (float *)malloc((size_t)LC * sizeof(float));
+        float *crow = (float *)malloc((size_t)LR * sizeof(float)), *ccol = (float *)malloc((size_t)LC * sizeof(float));
+        if (!rmean || !cmean || !crow || !ccol) return 2;
+        for (int64_t i = 0; i < nl; ++i) sq[i] = gl[i] * gl[i];
+        row_col_means(sq, LR, LC, rmean, cmean);             /* optimizer.py:2691-2692 */
+        float *rv = x->row_var_low, *cv = x->col_var_low;
+        for (int64_t i = 0; i < LR; ++i) {
+            const float t = rmean[i] + LOG_QUANT_FLOOR;
+            rv[i] = x->first_factor ? t * c->v_w : fmaf(c->v_w, t, rv[i] * x->v_keep);      /* optimizer.py:2695-2700 */
+        }
+        for (int64_t j = 0; j < LC; ++j) {
+            const float t = cmean[j] + LOG_QUANT_FLOOR;
+            cv[j] = x->first_factor ? t * c->v_w : fmaf(c->v_w, t, cv[j] * x->v_keep);
+        }
+        const float rvm = mean_f64(rv, LR);                  /* row_var.mean(dim=-2) */
+        if (has_m && x->came) {                              /* optimizer.py:2708-2750 */
+            float rmv = rvm < LOG_QUANT_FLOOR ? LOG_QUANT_FLOOR : rvm;
+            for (int64_t i = 0; i < LR; ++i) crow[i] = rsqrt_t(rv[i] / rmv);               /* _factored_inv_std */
+            for (int64_t j = 0; j < LC; ++j) ccol[j] = rsqrt_t(cv[j]);
+            float *U = sq;
+            for (int64_t i = 0; i < nl; ++i) { float t = gl[i] * crow[i / LC]; U[i] = t * ccol[i % LC]; }
+            clip_low(U, nl, x->d);
+            rc = low_m_ema(c, U, nl, m_q, m_scale, m_f32, map, m);
+            for (int64_t i = 0; i < nl; ++i) { float t = U[i] - m[i]; t = t * t; U[i] = t + x->eps_came; }
+            row_col_means(U, LR, LC, rmean, cmean);
+            af8o_small_state cr = x->conf_row, cc = x->conf_col;
+            small_state_ema(&cr, rmean, x->c_w, c->block, -126.0f, crow);
+            small_state_ema(&cc, cmean, x->c_w, c->block, -126.0f, ccol);
+            float cm = mean_f64(crow, LR);
+            if (cm < LOG_QUANT_FLOOR) cm = LOG_QUANT_FLOOR;
+            for (int64_t i = 0; i < LR; ++i) crow[i] = rsqrt_t(crow[i] / cm);
+            for (int64_t j = 0; j < LC; ++j) ccol[j] = rsqrt_t(ccol[j]);
+            for (int64_t i = 0; i < nl; ++i) { float t = m[i] * crow[i / LC]; m[i] = t * ccol[i % LC]; }   /* optimizer.py:2750 */
+        } else {
+            const float div = rvm < c->apollo_eps ? c->apollo_eps : rvm;                    /* optimizer.py:2705 */
+            if (has_m) rc = low_m_ema(c, gl, nl, m_q, m_scale, m_f32, map, m);              /* optimizer.py:2753-2757 */
+            else memcpy(m, gl, (size_t)nl * sizeof(float));
+            for (int64_t i = 0; i < nl; ++i) {
+                float ve = rv[i / LC] * cv[i % LC];
+                ve = ve / div;
+                m[i] = m[i] / (sqrtf(ve) + c->apollo_eps);   /* optimizer.py:2758, 2760 */
+            }
+        }
+        free(rmean); free(cmean); free(crow); free(ccol);
+        goto scaling;
+    }
     /* low-rank second moment */
     if (c->first_step) {                                     /* optimizer.py:2770-2779 */
         for (int64_t i = 0; i < nl; ++i) { float t = gl[i] * gl[i]; v[i] = t * c->v_w; }
@@ -1072,8 +1174,37 @@ AF8O_API int af8o_apollo_step(const af8o_apollo_cfg *c, float *p, const void *gr
     } else {                                                 /* optimizer.py:2797-2799 */
         for (int64_t i = 0; i < nl; ++i) { v_f32[i] = lerp_t(v_f32[i], gl[i] * gl[i], c->v_w); v[i] = v_f32[i]; }
     }
+    if (x && x->came) {
+        /* optimizer.py:2801-2903, pure-PyTorch branch; update_low ends up in m */
+        float *U = (float *)malloc((size_t)nl * sizeof(float));
+        if (!U) return 2;
+        for (int64_t i = 0; i < nl; ++i) {
+            const float vc = v[i] < x->eps_sq ? x->eps_sq : v[i];
+            U[i] = gl[i] * rsqrt_t(vc);                      /* optimizer.py:2871, 2898 */
+        }
+        clip_low(U, nl, x->d);
+        if (has_m) {
+            rc = low_m_ema(c, U, nl, m_q, m_scale, m_f32, map, m);
+            for (int64_t i = 0; i < nl; ++i) { float t = U[i] - m[i]; t = t * t; U[i] = t + x->eps_came; }   /* optimizer.py:2881 */
+            af8o_small_state rs = x->res;
+            if (rs.fmt == AF8O_V_FP32) {
+                for (int64_t i = 0; i < nl; ++i) { rs.f32[i] = lerp_t(rs.f32[i], U[i], x->c_w); U[i] = rs.f32[i]; }
+            } else {                                         /* optimizer.py:2884-2889: the requantised values are used */
+                float *t2 = v;
+                small_state_ema(&rs, U, x->c_w, c->block, -126.0f, t2);
+                af8o_al_dequantize(rs.q, rs.scale, rs.min_log, nl, c->block, rs.fmt, U);
+            }
+            for (int64_t i = 0; i < nl; ++i) {
+                const float rc_ = U[i] < x->eps_sq ? x->eps_sq : U[i];
+                m[i] = m[i] * rsqrt_t(rc_);                  /* optimizer.py:2894 */
+            }
+        } else {
+            memcpy(m, U, (size_t)nl * sizeof(float));        /* optimizer.py:2902 */
+        }
+        free(U);
+        goto scaling;
+    }
     /* low-rank momentum and update_low (optimizer.py:2906-2959) */
-    int rc = 0;
     if (has_m) {
         if (m_quant) {
             af8o_m_dequantize(m_q, m_scale, nl, c->m_block, c->m_fmt, map, m);
@@ -1087,6 +1218,7 @@ AF8O_API int af8o_apollo_step(const af8o_apollo_cfg *c, float *p, const void *gr
     }
     for (int64_t i = 0; i < nl; ++i) m[i] = m[i] / (sqrtf(v[i]) + c->apollo_eps);   /* update_low in m */
 
+scaling:;
     /* scaling factor (optimizer.py:2961-2966) and squared channel norms of G (2975-2979) */
     double total = 0.0;
     float norm_unscaled = 0.0f;

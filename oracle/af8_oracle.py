@@ -643,9 +643,17 @@ def apollo_projection(state, shape, step, rank, gap):
     return pt
 
 
+class ApolloExtra(ctypes.Structure):
+    _fields_ = [("factorize", c_i), ("came", c_i), ("c_fmt", c_i), ("first_factor", c_i),
+                ("v_keep", c_f), ("c_w", c_f), ("eps_came", c_f), ("eps_sq", c_f), ("d", c_f), ("reserved", c_f),
+                ("row_var_low", c_p), ("col_var_low", c_p),
+                ("conf_row", SmallState), ("conf_col", SmallState), ("res", SmallState)]
+
+
 def apollo_step(p, g, state, hp, g_low=None):
-    """_update_param_apollo (optimizer.py:2587-3084) for 2-D fp32 parameters, without
-    factorisation and without CAME.  g_low: a projected gradient (float32, rows x rank or
+    """_update_param_apollo (optimizer.py:2587-3084) for 2-D fp32 parameters: the plain rule,
+    apollo_factorize (2688-2760) and CAME over the projected gradient (2801-2903, the
+    pure-PyTorch branch).  g_low: a projected gradient (float32, rows x rank or
     rank x cols) to use instead of computing G @ Pt: everything after the contraction then
     starts from the same values as a device run whose projection was copied here."""
     assert p.dtype == f32 and p.ndim == 2 and p.flags.c_contiguous
@@ -677,8 +685,40 @@ def apollo_step(p, g, state, hp, g_low=None):
     nl = max(R, C) * rank
     block = state["block_size"]
     m_block = state.get("m_block_size", hp["m_block_size"])
+    factorize = bool(hp.get("apollo_factorize", False))
+    beta3 = hp.get("beta3")
     first = state.get("v_low_q") is None and state.get("v_low") is None
-    if first:
+    extra = None
+    if factorize or beta3 is not None:
+        LR, LC = (R, rank) if R >= C else (rank, C)
+        cqt = (state.get("c_quant_type", state["v_quant_type"]) if quant else "fp32")
+        extra = ApolloExtra()
+        extra.factorize, extra.came = int(factorize), int(beta3 is not None)
+        extra.c_fmt = V_FMT[cqt]
+        extra.v_keep = float(f32(1.0 - beta_val))
+        extra.c_w = float(f32(1.0 - beta3)) if beta3 is not None else 0.0
+        extra.eps_came = float(f32(hp["eps_came"]))
+        extra.eps_sq = float(f32(max(hp["apollo_eps"] * hp["apollo_eps"], LOG_QUANT_FLOOR)))
+        extra.d = float(f32(hp["d"]))
+        if factorize:
+            extra.first_factor = int("row_var_low" not in state)
+            if extra.first_factor:
+                state["row_var_low"] = np.zeros(LR, dtype=f32)
+                state["col_var_low"] = np.zeros(LC, dtype=f32)
+            extra.row_var_low, extra.col_var_low = _ptr(state["row_var_low"]), _ptr(state["col_var_low"])
+            if has_m and beta3 is not None:
+                if state.get("conf_row_low_q") is None and state.get("conf_row_low") is None:
+                    _init_al(state, "conf_row_low", LR, block, cqt)
+                    _init_al(state, "conf_col_low", LC, block, cqt)
+                extra.conf_row = _small(state, "conf_row_low", LR, cqt)
+                extra.conf_col = _small(state, "conf_col_low", LC, cqt)
+        elif has_m:
+            if state.get("res_low_q") is None and state.get("res_low") is None:
+                _init_al(state, "res_low", nl, block, cqt)
+            extra.res = _small(state, "res_low", nl, cqt)
+    if factorize:
+        first = False                 # no v_low state in this mode
+    elif first:
         if vqt == "fp32":
             state["v_low"] = np.zeros(nl, dtype=f32)
         else:
@@ -724,6 +764,9 @@ def apollo_step(p, g, state, hp, g_low=None):
         assert g_low.size == nl
         lib_.af8o_apollo_override_g_low.argtypes = [c_p]
         lib_.af8o_apollo_override_g_low(_ptr(g_low))
+    if extra is not None:
+        lib_.af8o_apollo_set_extra.argtypes = [ctypes.POINTER(ApolloExtra)]
+        lib_.af8o_apollo_set_extra(ctypes.byref(extra))
     with param_format(hp, state, state["step"]):
         rc = lib_.af8o_apollo_step(
             ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), _ptr(pt),

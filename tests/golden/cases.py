@@ -232,6 +232,24 @@ CASES["apollo_3d_f16g"] = dict(shapes=[(12, 8, 16), (40, 4, 6)], steps=5, seed=5
                                grad=dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="f16"),
                                hp=dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=8, apollo_update_proj_gap=3,
                                        m_quant_type="uf8", v_quant_type="al8", block_size=256, min_8bit_size=64))
+# APOLLO's further low-rank rules: factored second moment of the projected gradient (apollo_factorize), the same
+# with CAME's confidence vectors, CAME over the projected gradient with its instability state shaped like it
+# (quantised AL8 and fp32), and the momentum-free factorised form (beta3 without beta1 is refused by the constructor)
+_APOLLO_X = dict(_APOLLO, lr=1e-3, weight_decay=0.01, apollo_rank=8, apollo_update_proj_gap=3, m_quant_type="uf8",
+                 v_quant_type="al8", block_size=256, m_block_size=256, min_8bit_size=64, eps_came=1e-16)
+_G_APX = dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="bf16")
+CASES["apollo_factorize"] = dict(shapes=[(96, 64), (32, 160)], steps=5, seed=51, grad=_G_APX,
+                                 hp=dict(_APOLLO_X, apollo_factorize=True))
+CASES["apollo_factorize_came"] = dict(shapes=[(96, 64), (32, 160)], steps=5, seed=52, grad=_G_APX,
+                                      hp=dict(_APOLLO_X, apollo_factorize=True, beta3=0.9999, d=1.0))
+CASES["apollo_came"] = dict(shapes=[(96, 64), (32, 160)], steps=5, seed=53, grad=_G_APX,
+                            hp=dict(_APOLLO_X, beta3=0.9999, d=1.0))
+CASES["apollo_came_fp32"] = dict(shapes=[(96, 64), (32, 160)], steps=5, seed=54, grad=_G_APX,
+                                 hp=dict(_APOLLO_X, beta3=0.9999, d=1.0, quantize=False))
+CASES["apollo_factorize_nomom"] = dict(shapes=[(96, 64), (32, 160)], steps=4, seed=55, grad=_G_APX,
+                                       hp=dict(_APOLLO_X, apollo_factorize=True, beta1=None))
+APOLLO_RULE_CASES = ["apollo_factorize", "apollo_factorize_came", "apollo_came", "apollo_came_fp32",
+                     "apollo_factorize_nomom"]
 MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
 
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]

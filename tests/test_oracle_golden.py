@@ -236,6 +236,39 @@ def test_apollo_variants_against_reference(oracle, name):
             assert parity.rel_l2(st["scaled_grad_norm_prev"], ref["scaled_grad_norm_prev"]) <= 1e-4, what
 
 
+@pytest.mark.parametrize("name", cases.APOLLO_RULE_CASES)
+def test_apollo_lowrank_rules_against_reference(oracle, name):
+    """APOLLO's other low-rank rules, free-running against the reference: apollo_factorize (fp32 row / column
+    factors of the projected gradient's squares, optimizer.py:2688-2760), the same with CAME's confidence
+    vectors (2708-2750), CAME over the projected gradient with its instability state res_low, AL8-coded and
+    fp32 (2801-2903, pure-PyTorch branch), and factorisation without momentum.  Codes agree to one step on a
+    few elements (the float32 GEMM of the reference rounds the projected gradient differently), fp32 states
+    and block ranges to 1e-4 relative."""
+    run = OracleRun(name)
+    gold = load_golden(name)
+    assert str(gold["digest"]) == cases.inputs_digest(run.params0, run.grads)
+    for t in range(1, run.case["steps"] + 1):
+        run.step()
+        for i, (p, st) in enumerate(zip(run.params, run.states)):
+            ref = golden_entries(gold, t, i)
+            what = f"{name} step {t} param {i}"
+            parity.assert_params(p, ref["param"], what, tol=5e-5)
+            seen = 0
+            for key, want in ref.items():
+                if key in ("param", "apollo_proj_matrix_T"):
+                    continue
+                assert st.get(key) is not None, (what, key)
+                have = np.asarray(st[key]).reshape(-1)
+                seen += 1
+                if have.dtype in (np.uint8, np.uint16):
+                    s = parity.code_stats(have[:want.size], want)
+                    assert s["max"] <= 1 and s["neq"] <= max(2, 2e-3 * s["n"]), (what, key, s)
+                else:
+                    assert have.size >= want.size, (what, key)
+                    assert parity.rel_l2(have[:want.size], want) <= 1e-4, (what, key, parity.rel_l2(have[:want.size], want))
+            assert seen >= 3, (what, sorted(ref))
+
+
 # ---------------------------------------------------------------------------
 # bf16 / fp16 parameters, nearest and stochastic rounding (optimizer.py:162-292, 866-881)
 # ---------------------------------------------------------------------------
