@@ -909,9 +909,13 @@ class ApolloPlan:
     projection, one batched low-rank state update (the full-rank kernel run on the
     projected gradients), per-tensor scaling and write-back."""
 
-    def __init__(self, device, grad_dtype, v_fmt, m_fmt, block, m_block, negate, params, states, rank, copies=None):
+    def __init__(self, device, grad_dtype, v_fmt, m_fmt, block, m_block, negate, params, states, rank, copies=None,
+                 rule=None, c_fmt="fp32"):
         """copies: optional list with a bf16 tensor (or None) per parameter that receives the updated
-        parameter rounded to nearest (the compute copy of a mixed-precision run)."""
+        parameter rounded to nearest (the compute copy of a mixed-precision run).
+        rule: None for the plain Adam rule over the projected gradient, or dict(factorize=, came=) for
+        apollo_factorize and / or CAME (optimizer.py:2688-2760, 2801-2903); c_fmt: format of their
+        confidence / instability states."""
         self.device = torch.device(device)
         self.params, self.states = list(params), list(states)
         self.n = len(self.params)
@@ -920,6 +924,7 @@ class ApolloPlan:
         self.v_fmt, self.m_fmt, self.block, self.m_block = v_fmt, m_fmt, int(block), int(m_block) if m_block else 0
         self.negate = int(bool(negate))
         self.rank = int(rank)
+        self.rule, self.c_fmt = rule, c_fmt
         for p in self.params:
             if p.dtype not in _GRAD_DT or p.dtype != self.params[0].dtype or not p.is_contiguous() or p.dim() != 2:
                 raise RuntimeError("the APOLLO kernels update contiguous 2-D fp32, bf16 or fp16 parameters, one dtype per group")
@@ -959,6 +964,12 @@ class ApolloPlan:
         self.sums = torch.zeros(3 * self.n, dtype=torch.float64, device=dev)
         self.out = torch.zeros(4 * self.n, dtype=torch.float32, device=dev)
         self._low_plans = {}
+        if rule is not None:          # one work area, sized for the largest tensor (stream order makes its reuse safe)
+            shapes = [((r, self.rank) if r >= c else (self.rank, c)) for r, c in zip(self.rows, self.cols)]
+            self.low_shapes = shapes
+            self.rule_bytes = max(int(lib.af8_apollo_rule_workspace(a, b)) for a, b in shapes)
+            self.rule_work = torch.empty(self.rule_bytes + 256, dtype=torch.uint8, device=dev)
+            self.rule_ptr = (self.rule_work.data_ptr() + 255) // 256 * 256
         # table of the batched scaling-factor / scalar-chain launches (static part)
         fs = np.zeros(self.n, dtype=N.APOLLO_FINISH_TENSOR)
         units = [(n + 7) // 8 for n in self.nch]
@@ -1021,7 +1032,9 @@ class ApolloPlan:
         if log is not None:
             ev[1].record(stream)
         self.upd_all.zero_()        # the low-rank step writes p*0 + u into it; stale NaNs must not survive
-        for first in (True, False):
+        if self.rule is not None:
+            self._run_rule(lowrank_scalars, first_flags, floor_later, s)
+        for first in ((True, False) if self.rule is None else ()):
             idx = [i for i in range(self.n) if bool(first_flags[i]) == first]
             if not idx:
                 continue
@@ -1078,6 +1091,50 @@ class ApolloPlan:
             ev[3].record(stream)
             log.append(("apollo_project", self.total_numel, ev[0], ev[1]))
             log.append(("apollo_scales_apply", self.total_numel, ev[2], ev[3]))
+
+    def _run_rule(self, sc, first_flags, floor_later, s):
+        """update_low of every tensor under apollo_factorize and / or CAME: one af8_apollo_rule_step each."""
+        lib = N.lib()
+
+        def ptr(t):
+            return t.data_ptr() if t is not None else None
+
+        def rule_state(st, prefix, n, fmt):
+            rs = N.ApolloRuleState()
+            rs.n, rs.fmt = n, N.V_FMT[fmt]
+            if fmt == "fp32":
+                rs.f32 = ptr(st[prefix])
+            else:
+                rs.q, rs.scale, rs.min_log = ptr(st[prefix + "_q"]), ptr(st[prefix + "_scale"]), ptr(st[prefix + "_min_log"])
+            return rs
+
+        for i in range(self.n):
+            st = self.states[i]
+            lr, lc = self.low_shapes[i]
+            r = N.ApolloRule()
+            r.g_low, r.upd, r.work, r.work_bytes = self.g_low[i].data_ptr(), self.upd[i].data_ptr(), self.rule_ptr, self.rule_bytes
+            r.lr_rows, r.lr_cols = lr, lc
+            r.factorize, r.came = int(self.rule["factorize"]), int(self.rule["came"])
+            r.m_fmt, r.m_block, r.block = N.M_FMT[self.m_fmt], self.m_block, self.block
+            r.first_factor = int(bool(first_flags[i]) and self.rule["factorize"])
+            r.first_v = int(bool(first_flags[i]) and not self.rule["factorize"])
+            for k in ("v_w", "v_keep", "m_w", "c_w", "eps_came", "eps_sq", "apollo_eps", "d"):
+                setattr(r, k, float(sc[k]))
+            r.v_floor_later = float(floor_later)
+            if self.m_fmt is not None:
+                if self.m_fmt == "fp32":
+                    r.m_f32 = ptr(st["m_low"])
+                else:
+                    r.m_q, r.m_scale = ptr(st["m_low_q"]), ptr(st["m_low_scale"])
+            if self.rule["factorize"]:
+                r.row_var_low, r.col_var_low = ptr(st["row_var_low"]), ptr(st["col_var_low"])
+                if self.rule["came"]:
+                    r.conf_row = rule_state(st, "conf_row_low", lr, self.c_fmt)
+                    r.conf_col = rule_state(st, "conf_col_low", lc, self.c_fmt)
+            else:
+                r.v = rule_state(st, "v_low", lr * lc, self.v_fmt)
+                r.res = rule_state(st, "res_low", lr * lc, self.c_fmt)
+            N.check(lib.af8_apollo_rule_step(ctypes.byref(r), s), "af8_apollo_rule_step")
 
     def norms(self):
         return self.out.cpu().numpy().reshape(self.n, 4)[:, 2].copy()

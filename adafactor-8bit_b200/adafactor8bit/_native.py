@@ -123,6 +123,26 @@ class ApolloScalarsIn(ctypes.Structure):
     ]
 
 
+class ApolloRuleState(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("scale", ctypes.c_void_p), ("min_log", ctypes.c_void_p), ("f32", ctypes.c_void_p),
+                ("n", ctypes.c_int64), ("fmt", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class ApolloRule(ctypes.Structure):
+    _fields_ = [
+        ("g_low", ctypes.c_void_p), ("upd", ctypes.c_void_p), ("work", ctypes.c_void_p), ("work_bytes", ctypes.c_int64),
+        ("lr_rows", ctypes.c_int64), ("lr_cols", ctypes.c_int64),
+        ("factorize", ctypes.c_int32), ("came", ctypes.c_int32), ("m_fmt", ctypes.c_int32), ("m_block", ctypes.c_int32),
+        ("block", ctypes.c_int32), ("first_factor", ctypes.c_int32), ("first_v", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("v_w", ctypes.c_float), ("v_keep", ctypes.c_float), ("m_w", ctypes.c_float), ("c_w", ctypes.c_float),
+        ("eps_came", ctypes.c_float), ("eps_sq", ctypes.c_float), ("apollo_eps", ctypes.c_float), ("d", ctypes.c_float),
+        ("v_floor_later", ctypes.c_float), ("reserved2", ctypes.c_float),
+        ("row_var_low", ctypes.c_void_p), ("col_var_low", ctypes.c_void_p),
+        ("m_q", ctypes.c_void_p), ("m_scale", ctypes.c_void_p), ("m_f32", ctypes.c_void_p),
+        ("v", ApolloRuleState), ("res", ApolloRuleState), ("conf_row", ApolloRuleState), ("conf_col", ApolloRuleState),
+    ]
+
+
 FSTAT_GRADSQ, FSTAT_RESIDUAL = 0, 1
 FUPD_SUMSQ_U, FUPD_SUMSQ, FUPD_APPLY, FUPD_LAG = 0, 1, 2, 3
 
@@ -159,6 +179,8 @@ PROTOTYPES = {
                                  _c_p, _c_p]),
     "af8_apollo_apply": (_c_i, [_c_p, _c_i, _c_i, ctypes.c_uint64, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l,
                                 ctypes.POINTER(ApolloScalarsIn), _c_f, _c_i, _c_p, _c_p]),
+    "af8_apollo_rule_workspace": (ctypes.c_int64, [_c_l, _c_l]),
+    "af8_apollo_rule_step": (_c_i, [ctypes.POINTER(ApolloRule), _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
     "af8_lag_scalars": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p]),
     "af8_fullrank_limited_step_noalloc": (_c_i, [ctypes.POINTER(FullrankCfg), _c_p, _c_f, _c_i, _c_f, _c_p, _c_i, _c_p, _c_p]),
@@ -201,7 +223,7 @@ def lib():
         mirrors = [FULLRANK_TENSOR.itemsize, DYN_SCALARS.itemsize, ctypes.sizeof(FullrankCfg), NORM_TENSOR.itemsize,
                    SCALE_TENSOR.itemsize, SMALL_STATE.itemsize, FACTORED_TENSOR.itemsize, ctypes.sizeof(FactoredCfg),
                    ctypes.sizeof(ApolloScalarsIn), 16, APOLLO_PROJ_DESC.itemsize, APOLLO_FINISH_TENSOR.itemsize,
-                   LAG_TENSOR.itemsize]
+                   LAG_TENSOR.itemsize, ctypes.sizeof(ApolloRule)]
         for i, mine in enumerate(mirrors):
             theirs = handle.af8_struct_size(i)
             if theirs != mine:

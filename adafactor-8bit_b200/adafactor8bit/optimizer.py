@@ -877,10 +877,12 @@ class Adafactor8Bit(Optimizer):
     def _run_apollo(self, gi, group, key, items):
         if group["scale_parameter"]:
             raise NotImplementedError("APOLLO with scale_parameter=True is not available in this build")
-        if group.get("apollo_factorize", False) or group.get("beta3") is not None:
-            raise NotImplementedError("apollo_factorize and APOLLO+CAME are not available in this build")
         rank = int(group["apollo_rank"])
         beta1, beta2 = group.get("beta1"), group["beta2"]
+        beta3 = group.get("beta3")
+        factorize = bool(group.get("apollo_factorize", False))
+        came = beta3 is not None and beta1 is not None
+        rule = dict(factorize=factorize, came=came) if (factorize or came) else None
         block = group.get("block_size", 2048)
         m_block = group.get("m_block_size", 256)
         device = items[0][0].device
@@ -893,7 +895,8 @@ class Adafactor8Bit(Optimizer):
         items = [(p if p.dim() == 2 else p.view(p.shape[0], -1),
                   (g.float() if g.dtype == torch.float16 else g).reshape(g.shape[0], -1), st) for p, g, st in items]
         ids = tuple(p.data_ptr() for p, _, _ in items)     # (also follows a parameter whose storage was replaced)
-        pkey = (gi, "apollo", items[0][1].dtype, items[0][0].dtype, v_fmt, m_fmt, rank, bool(group["maximize"]))
+        c_fmt = items[0][2].get("c_quant_type", items[0][2].get("v_quant_type", "al8")) if quant0 else "fp32"
+        pkey = (gi, "apollo", items[0][1].dtype, items[0][0].dtype, v_fmt, m_fmt, rank, bool(group["maximize"]), factorize, came, c_fmt)
         sr = bool(group.get("stochastic_round_writeback", False)) and items[0][0].dtype in (torch.bfloat16, torch.float16)
         plan = self._plans.get(pkey)
         first_flags, pts, per_tensor, grads = [], [], [], []
@@ -906,8 +909,23 @@ class Adafactor8Bit(Optimizer):
             R, C = p.shape
             nl = max(R, C) * rank
             first = st.get("v_low_q") is None and st.get("v_low") is None
+            low_shape = (R, rank) if R >= C else (rank, C)
+            if factorize:                               # fp32 factors instead of v_low (optimizer.py:2688-2700)
+                first = "row_var_low" not in st
+                if first:
+                    st["row_var_low"] = torch.zeros((low_shape[0], 1), dtype=torch.float32, device=p.device)
+                    st["col_var_low"] = torch.zeros((1, low_shape[1]), dtype=torch.float32, device=p.device)
+                if came and st.get("conf_row_low_q") is None and st.get("conf_row_low") is None:      # optimizer.py:2729-2744
+                    for prefix, shp in (("conf_row_low", (low_shape[0], 1)), ("conf_col_low", (1, low_shape[1]))):
+                        tmp = {}
+                        _new_al_state(tmp, prefix, shp, st.get("block_size", block), p.device, c_fmt)
+                        st.update(tmp)
+            elif came and st.get("res_low_q") is None and st.get("res_low") is None:                   # optimizer.py:2806-2810
+                tmp = {}
+                _new_al_state(tmp, "res_low", low_shape, st.get("block_size", block), p.device, c_fmt)
+                st.update(tmp)
             first_flags.append(first)
-            if first:
+            if first and not factorize:
                 tmp = {}
                 _new_al_state(tmp, "v_low", (nl,), st.get("block_size", block), p.device, v_fmt)
                 for k in ("v_low_q", "v_low_scale", "v_low_min_log", "v_low_shape", "v_low_pad", "v_low"):
@@ -924,7 +942,7 @@ class Adafactor8Bit(Optimizer):
         if plan is None or plan.ids != ids:
             plan = ApolloPlan(device, items[0][1].dtype, v_fmt, m_fmt, block, m_block, group["maximize"],
                               [p for p, _, _ in items], [s for _, _, s in items], rank,
-                              copies=[pc.copy if pc is not None else None for pc in pcs])
+                              copies=[pc.copy if pc is not None else None for pc in pcs], rule=rule, c_fmt=c_fmt)
             plan.ids = ids
             self._plans[pkey] = plan
         step_any = None
@@ -967,7 +985,8 @@ class Adafactor8Bit(Optimizer):
         sc = self._step_scalars(group, step_any)
         bv = sc["beta_val"]
         low = dict(v_w=f32(bv), v_keep=f32(1.0 - bv), m_w=f32(1.0 - beta1) if beta1 is not None else f32(0.0),
-                   apollo_eps=f32(apollo_eps))
+                   apollo_eps=f32(apollo_eps), c_w=f32(1.0 - beta3) if beta3 is not None else f32(0.0),
+                   eps_came=f32(group.get("eps_came", 1e-16)), eps_sq=f32(max(apollo_eps * apollo_eps, _FLOOR)), d=f32(group["d"]))
         floor_later = math.log2(max(apollo_eps * apollo_eps, _FLOOR))                  # optimizer.py:2766-2767
         def passes():
             plan.run(grads, pts, per_tensor, low, first_flags, floor_later, params=[p for p, _, _ in items])

@@ -9,6 +9,7 @@
 #include "scale.cuh"
 #include "factored.cuh"
 #include "apollo.cuh"
+#include "apollo_rules.cuh"
 #include "noalloc.cuh"
 
 extern "C" int af8_version(void) { return AF8_VERSION; }
@@ -22,7 +23,7 @@ extern "C" int32_t af8_struct_size(int32_t index)
         (int32_t)sizeof(af8_norm_tensor), (int32_t)sizeof(af8_scale_tensor), (int32_t)sizeof(af8_small_state),
         (int32_t)sizeof(af8_factored_tensor), (int32_t)sizeof(af8_factored_cfg),
         (int32_t)sizeof(af8_apollo_scalars_in), (int32_t)sizeof(af8_apollo_scalars), (int32_t)sizeof(af8_apollo_proj_desc),
-        (int32_t)sizeof(af8_apollo_finish_tensor), (int32_t)sizeof(af8_lag_tensor),
+        (int32_t)sizeof(af8_apollo_finish_tensor), (int32_t)sizeof(af8_lag_tensor), (int32_t)sizeof(af8_apollo_rule),
     };
     if (index < 0 || index >= (int32_t)(sizeof(sizes) / sizeof(sizes[0]))) return -1;
     return sizes[index];

@@ -488,7 +488,7 @@ __device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefe
 #ifndef AF8_FUPD_PREFETCH_AHEAD
 #define AF8_FUPD_PREFETCH_AHEAD 3      /* chunks ahead that the momentum-free write pass requests from L2; 0: off */
 #endif
-template <typename GradT> __device__ __forceinline__ constexpr int sizeof_grad() { return std::is_same<GradT, float>::value ? 4 : 2; }
+template <typename GradT> __host__ __device__ constexpr int sizeof_grad() { return std::is_same<GradT, float>::value ? 4 : 2; }
 
 template <typename GradT>
 __device__ __forceinline__ void load_g8(const void *grad, int64_t off, int negate, float (&g)[8])
@@ -511,6 +511,10 @@ template <> struct GradRaw8<float> {
         const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(grad) + off);
         a = __ldcs(p); b = __ldcs(p + 1);
     }
+    __device__ __forceinline__ void from_shared(const unsigned char *p)
+    {
+        a = *reinterpret_cast<const float4 *>(p); b = *reinterpret_cast<const float4 *>(p + 16);
+    }
     __device__ __forceinline__ void unpack(int negate, float (&g)[8]) const
     {
         g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
@@ -527,6 +531,7 @@ template <> struct GradRaw8<bf16_tag> {
     {
         a = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(grad) + off));
     }
+    __device__ __forceinline__ void from_shared(const unsigned char *p) { a = *reinterpret_cast<const uint4 *>(p); }
     __device__ __forceinline__ void unpack(int negate, float (&g)[8]) const
     {
         const uint32_t w[4] = {a.x, a.y, a.z, a.w};
@@ -1019,6 +1024,199 @@ factored_update_vec_kernel(const FactoredLaunch L)
     if (SUMS && run_first >= 0) flush_sums(id_end);
 }
 
+// ---------------------------------------------------------------------------
+// The APPLY pass for fp32 parameters with a UF8 momentum (CAME, Adafactor with beta1), inputs
+// through per-warp rings of bulk asynchronous copies.
+//
+// The register-pipelined kernel above has one chunk in flight per thread and was measured
+// latency-bound in this configuration (CAME apply: half of the copy peak, long-scoreboard
+// stalls on top).  Here a warp still owns one momentum block per chunk (256 consecutive
+// elements: gradient, parameter and momentum codes are three contiguous runs of 512 or 1024,
+// 1024 and 256 bytes), but its lane 0 requests them FRING_STAGES - 1 chunks ahead with
+// cp.async.bulk into the warp's own ring; completion is an mbarrier per stage.  Warps do not
+// synchronise with one another except when the CTA moves to its next tensor.  Copies never
+// cross a tensor, and the (at most one) partial chunk at a tensor's end is loaded directly.
+// Same arithmetic, element for element, as factored_update_vec_kernel.
+// ---------------------------------------------------------------------------
+#ifndef AF8_FRING_STAGES
+#define AF8_FRING_STAGES 4
+#endif
+constexpr int FRING_STAGES = AF8_FRING_STAGES;
+constexpr int DEVERR_FRING_TIMEOUT = 3;
+template <typename GradT> __host__ __device__ constexpr int fring_stage_bytes() { return 256 * sizeof_grad<GradT>() + 1024 + 256; }
+template <typename GradT> constexpr size_t fring_smem_bytes() { return (size_t)(FUPD_THREADS / 32) * FRING_STAGES * fring_stage_bytes<GradT>(); }
+
+template <typename GradT, int CTAS>
+__global__ void __launch_bounds__(FUPD_THREADS, CTAS)
+factored_apply_ring_kernel(const FactoredLaunch L)
+{
+    constexpr int GB = sizeof_grad<GradT>();
+    constexpr int P_OFF = 256 * GB, M_OFF = P_OFF + 1024, STAGE = fring_stage_bytes<GradT>(), NS = FRING_STAGES;
+    extern __shared__ __align__(128) unsigned char fr_smem[];
+    __shared__ af8_factored_tensor sT;
+    __shared__ __align__(8) uint64_t s_full[FUPD_THREADS / 32][NS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    unsigned char *const ring = fr_smem + (size_t)warp * NS * STAGE;
+    if (lane == 0) {
+        for (int k = 0; k < NS; ++k) mbar_init(&s_full[warp][k], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int64_t per_cta = (L.total_units + gridDim.x - 1) / gridDim.x;
+    const int64_t id_begin = (int64_t)blockIdx.x * per_cta;
+    const int64_t id_end = min(id_begin + per_cta, L.total_units);
+    int cur_t = -1;
+    int64_t next_first = 0, full_end = 0, flat = 0, row = 0, col = 0;
+    float pre_div = 1.0f, step_mul = 0.0f, fira = 1.0f;
+    bool zero_upd = false;
+    DivBy D = make_div(1.0f);
+    uint32_t cons = 0;            // chunks this warp has taken from its ring
+    int inflight = 0;             // chunks from the current one on whose copies are issued
+
+    for (int64_t id = id_begin; id < id_end; ++id) {
+        if (cur_t < 0 || id >= next_first) {
+            int tn = cur_t;
+            if (tn < 0) tn = find_factored_chunk(L.tensors, L.n_tensors, id);
+            else while (tn + 1 < L.n_tensors && __ldg(&L.tensors[tn + 1].first_chunk) <= id) ++tn;
+            __syncthreads();
+            if (tid < (int)(sizeof(af8_factored_tensor) / 4))
+                reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + tn) + tid);
+            cur_t = tn;
+            __syncthreads();
+            next_first = tn + 1 < L.n_tensors ? __ldg(&L.tensors[tn + 1].first_chunk) : L.total_units;
+            full_end = min(id_end, sT.first_chunk + (sT.rows * sT.cols) / 2048);     // chunk ids below it are whole chunks of this tensor
+            flat = (id - sT.first_chunk) * 2048 + tid * 8;
+            row = flat / sT.cols;
+            col = flat - row * sT.cols;
+            pre_div = 1.0f; step_mul = -sT.alpha; fira = 1.0f; zero_upd = false;
+            if (L.dyn != nullptr) {
+                const af8_dyn_scalars ds = L.dyn[tn];
+                if (L.came) pre_div = ds.pre_div;
+                step_mul = ds.step; fira = ds.fira; zero_upd = ds.zero != 0.0f;
+            }
+            D = make_div(pre_div);
+            inflight = 0;                                            // (copies never cross a tensor)
+        } else {
+            flat += 2048;
+            col += 2048;
+            if (sT.cols >= 2048) {
+                if (col >= sT.cols) { col -= sT.cols; ++row; }
+            } else {
+                const uint32_t q = (uint32_t)col / (uint32_t)sT.cols;
+                row += q;
+                col -= (int64_t)q * sT.cols;
+            }
+        }
+        const int64_t numel = sT.rows * sT.cols;
+        const bool full = id < full_end;
+        const bool ok = flat < numel;
+        float *const pbase = static_cast<float *>(sT.param);
+
+        // ---- request the chunks id .. id + NS - 1 that are whole chunks of this tensor ----
+        int want = (int)min((int64_t)NS, full_end - id);
+        if (want < 0) want = 0;
+        if (lane == 0 && inflight < want) {
+            fence_proxy_async();                                     // this warp's reads of the slots came first
+            const unsigned char *gp = static_cast<const unsigned char *>(sT.grad);
+            const unsigned char *pp = static_cast<const unsigned char *>(sT.param);
+            for (int k = inflight; k < want; ++k) {
+                const int64_t off = (id + k - sT.first_chunk) * 2048 + warp * 256;      // first element of the warp's run
+                const int sl = (int)((cons + (uint32_t)k) % NS);
+                unsigned char *dst = ring + sl * STAGE;
+                mbar_expect_tx(&s_full[warp][sl], (uint32_t)STAGE);
+                bulk_g2s(dst + P_OFF, pp + off * 4, 1024, &s_full[warp][sl]);
+                bulk_g2s(dst, gp + off * GB, 256 * GB, &s_full[warp][sl]);
+                bulk_g2s(dst + M_OFF, sT.m_q + off, 256, &s_full[warp][sl]);
+            }
+        }
+        inflight = want > 0 ? want - 1 : 0;                          // as seen from the next chunk
+
+        GradRaw8<GradT> cg;
+        float4 cp0 = make_float4(0.f, 0.f, 0.f, 0.f), cp1 = cp0;
+        uint2 cm = make_uint2(0u, 0u);
+        if (full) {
+            const int sl = (int)(cons % NS);
+            const bool landed = mbar_wait_bounded(&s_full[warp][sl], (cons / NS) & 1u);
+            if (!__all_sync(0xffffffffu, landed)) {                  // (uniform over the warp)
+                atomicExch(&g_device_error, DEVERR_FRING_TIMEOUT);
+                return;                                              // the other warps go on: nothing waits for this one
+            }
+            const unsigned char *st = ring + sl * STAGE;
+            cg.from_shared(st + lane * (8 * GB));
+            cp0 = *reinterpret_cast<const float4 *>(st + P_OFF + lane * 32);
+            cp1 = *reinterpret_cast<const float4 *>(st + P_OFF + lane * 32 + 16);
+            cm = *reinterpret_cast<const uint2 *>(st + M_OFF + lane * 8);
+            ++cons;
+            __syncwarp();                                            // the slot may be refilled from the next iteration on
+        } else if (ok) {
+            cg.load(sT.grad, flat);
+            cp0 = *reinterpret_cast<const float4 *>(pbase + flat);
+            cp1 = *reinterpret_cast<const float4 *>(pbase + flat + 4);
+            cm = *reinterpret_cast<const uint2 *>(sT.m_q + flat);
+        } else cg.zero();
+
+        float mj[8];
+        if (ok) {
+            float g[8], ic[8], u[8], mo[8];
+            const LerpW LW = make_lerp(sT.m_w);
+            cg.unpack(L.negate_grad, g);
+            load_f8_ro(sT.inv_col + col, ic);
+            const float2 ir2 = bc2(__ldg(sT.inv_row + row));
+            m_old8(sT, AF8_M_UF8, 256, flat, mo, true, cm);
+            if (L.came) {
+                float icc[8];
+                load_f8_ro(sT.inv_col_conf + col, icc);
+                const float2 irc2 = bc2(__ldg(sT.inv_row_conf + row));
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 ut = div_by2(__fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1])), D);
+                    const float2 mm = lerp_w2(make_float2(mo[j], mo[j + 1]), ut, LW);
+                    const float2 uj = __fmul2_rn(__fmul2_rn(mm, irc2), make_float2(icc[j], icc[j + 1]));
+                    mj[j] = mm.x; mj[j + 1] = mm.y; u[j] = uj.x; u[j + 1] = uj.y;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 mm = lerp_w2(make_float2(mo[j], mo[j + 1]), make_float2(g[j], g[j + 1]), LW);
+                    const float2 uj = __fmul2_rn(__fmul2_rn(mm, ir2), make_float2(ic[j], ic[j + 1]));
+                    mj[j] = mm.x; mj[j + 1] = mm.y; u[j] = uj.x; u[j + 1] = uj.y;
+                }
+            }
+            float *pp = pbase + flat;
+            float p[8] = {cp0.x, cp0.y, cp0.z, cp0.w, cp1.x, cp1.y, cp1.z, cp1.w};
+            const float2 decay2 = bc2(sT.decay), step2 = bc2(step_mul), fira2 = bc2(fira);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                float2 pj = __fmul2_rn(make_float2(p[j], p[j + 1]), decay2);
+                if (!zero_upd) pj = __ffma2_rn(step2, __fmul2_rn(make_float2(u[j], u[j + 1]), fira2), pj);
+                p[j] = pj.x; p[j + 1] = pj.y;
+            }
+            *reinterpret_cast<float4 *>(pp) = make_float4(p[0], p[1], p[2], p[3]);
+            *reinterpret_cast<float4 *>(pp + 4) = make_float4(p[4], p[5], p[6], p[7]);
+            if (sT.param_copy != nullptr)                                    // bf16 compute copy
+                *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(sT.param_copy) + flat) =
+                    make_uint4(bf16x2_rn(p[0], p[1]), bf16x2_rn(p[2], p[3]), bf16x2_rn(p[4], p[5]), bf16x2_rn(p[6], p[7]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mj[j] = 0.0f;
+        }
+        // one warp = one momentum block of 256 (the block exists iff its first element does)
+        const int64_t w0 = (id - sT.first_chunk) * 2048 + warp * 256;
+        float am = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(mj[j]));
+        am = fmaxf(warp_max(am), 1e-12f);
+        if (w0 < numel) {
+            const DivBy A = make_div(am);
+            const uint32_t o0 = uf8_encode_fast2(make_float2(mj[0], mj[1]), A) | (uf8_encode_fast2(make_float2(mj[2], mj[3]), A) << 16);
+            const uint32_t o1 = uf8_encode_fast2(make_float2(mj[4], mj[5]), A) | (uf8_encode_fast2(make_float2(mj[6], mj[7]), A) << 16);
+            if (ok) *reinterpret_cast<uint2 *>(sT.m_q + flat) = make_uint2(o0, o1);
+            if (lane == 0) sT.m_scale[w0 / 256] = am;
+        }
+    }
+}
+
 inline int factored_chunk_for(int m_block)
 {
     if (m_block <= 0) return 2048;
@@ -1206,6 +1404,20 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     cudaStream_t cst = static_cast<cudaStream_t>(stream);
     const bool bf = cfg->grad_dtype == AF8_BF16;
     const bool no_m = cfg->m_fmt == AF8_M_NONE;
+    static const bool ring_off = getenv("AF8_NO_FACTORED_RING") != nullptr;
+    if (vec && cfg->mode == AF8_FUPD_APPLY && cfg->m_fmt == AF8_M_UF8 && cfg->param_dtype == AF8_F32 && !ring_off) {
+        // fp32 parameters, UF8 momentum: inputs through per-warp rings of bulk copies
+        if (bf) {
+            AF8_CUDA_TRY(cudaFuncSetAttribute(factored_apply_ring_kernel<bf16_tag, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fring_smem_bytes<bf16_tag>()));
+            factored_apply_ring_kernel<bf16_tag, 3><<<(int)grid, FUPD_THREADS, fring_smem_bytes<bf16_tag>(), cst>>>(L);
+        } else {
+            grid = std::min<int64_t>((int64_t)sm_count() * 2, total_chunks);
+            AF8_CUDA_TRY(cudaFuncSetAttribute(factored_apply_ring_kernel<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fring_smem_bytes<float>()));
+            factored_apply_ring_kernel<float, 2><<<(int)grid, FUPD_THREADS, fring_smem_bytes<float>(), cst>>>(L);
+        }
+        AF8_CUDA_TRY(cudaGetLastError());
+        return AF8_OK;
+    }
 #define AF8_LAUNCH_FUPD(G, P, C) factored_update_vec_kernel<G, P, C><<<(int)grid, FUPD_THREADS, 0, cst>>>(L)
     if (vec && bf && lag) { if (no_m) AF8_LAUNCH_FUPD(bf16_tag, 2, 2); else AF8_LAUNCH_FUPD(bf16_tag, 2, 3); }
     else if (vec && lag) { if (no_m) AF8_LAUNCH_FUPD(float, 2, 2); else AF8_LAUNCH_FUPD(float, 2, 3); }

@@ -512,6 +512,67 @@ AF8_API int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stochasti
                              void *stream);
 
 /* ------------------------------------------------------------------------ */
+/* APOLLO: further low-rank state rules                                      */
+/* ------------------------------------------------------------------------ */
+
+/* An AL-coded (q / scale / min_log) or fp32 state of n values. */
+typedef struct af8_apollo_rule_state {
+    void *q;            /* uint8 (AL8) / uint16 (AL16) codes, padded to the block; NULL for fp32 */
+    float *scale;
+    float *min_log;
+    float *f32;         /* fp32 state when fmt == AF8_V_FP32 */
+    int64_t n;
+    int32_t fmt;        /* AF8_V_* */
+    int32_t reserved;
+} af8_apollo_rule_state;
+
+/* update_low of one tensor under apollo_factorize and / or CAME (beta3), from the projected
+ * gradient that af8_apollo_project* produced.  Replaces the corresponding branches of
+ * _update_param_apollo (optimizer.py:2688-2760 factorised second moment, 2708-2750 its CAME form,
+ * 2801-2903 CAME over the projected gradient; the arithmetic of the pure-PyTorch branches) and the
+ * kernels compute_apollo_came_rms / apollo_came_compute_m_res / apollo_came_compute_update_norms
+ * (kernels.cu:2455-2566).  The plain rule (neither flag) runs through af8_fullrank_step.
+ * lr_rows x lr_cols is the projected shape: (rows, rank) when rows >= cols, else (rank, cols). */
+typedef struct af8_apollo_rule {
+    const float *g_low;         /* lr_rows * lr_cols */
+    float *upd;                 /* out: update_low */
+    void *work;                 /* af8_apollo_rule_workspace(lr_rows, lr_cols) bytes, 256-byte aligned */
+    int64_t work_bytes;
+    int64_t lr_rows, lr_cols;
+    int32_t factorize;          /* apollo_factorize */
+    int32_t came;               /* beta3 is not None (needs a momentum) */
+    int32_t m_fmt;              /* AF8_M_*; AF8_M_NONE when beta1 is None */
+    int32_t m_block;
+    int32_t block;              /* AL block of v_low / res_low / conf_*_low */
+    int32_t first_factor;       /* factorize: row_var_low / col_var_low hold no history yet (optimizer.py:2695) */
+    int32_t first_v;            /* CAME without factorize: v_low holds no history yet (optimizer.py:2763) */
+    int32_t reserved;
+    float v_w;                  /* beta_val */
+    float v_keep;               /* float(1 - beta_val) */
+    float m_w;                  /* float(1 - beta1) */
+    float c_w;                  /* float(1 - beta3) */
+    float eps_came;
+    float eps_sq;               /* max(apollo_eps^2, FLT_MIN) */
+    float apollo_eps;
+    float d;                    /* clip threshold of the low-rank U_t; <= 0: none */
+    float v_floor_later;        /* log2(eps_sq): min_log floor of v_low after its first step */
+    float reserved2;
+    float *row_var_low;         /* factorize: fp32 [lr_rows] */
+    float *col_var_low;         /* factorize: fp32 [lr_cols] */
+    uint8_t *m_q;               /* momentum of the projected space: codes ... */
+    float *m_scale;
+    float *m_f32;               /* ... or fp32 */
+    af8_apollo_rule_state v;            /* CAME without factorize: v_low, n = lr_rows * lr_cols */
+    af8_apollo_rule_state res;          /* CAME without factorize: res_low, n = lr_rows * lr_cols */
+    af8_apollo_rule_state conf_row;     /* factorize + CAME: conf_row_low, n = lr_rows */
+    af8_apollo_rule_state conf_col;     /* factorize + CAME: conf_col_low, n = lr_cols */
+} af8_apollo_rule;
+
+AF8_API int64_t af8_apollo_rule_workspace(int64_t lr_rows, int64_t lr_cols);
+/* rule: HOST pointer.  Everything runs on `stream`; no host synchronisation. */
+AF8_API int af8_apollo_rule_step(const af8_apollo_rule *rule, void *stream);
+
+/* ------------------------------------------------------------------------ */
 /* Step without caller-provided working memory                               */
 /* ------------------------------------------------------------------------ */
 

@@ -196,7 +196,7 @@ def test_tensor_core_projection_at_k4096(rows, cols):
     rms = float(np.sqrt((err ** 2).mean()) / np.sqrt((want ** 2).mean()))
     assert rms <= 2e-6, rms                           # the class of a binary32 product, not of a truncating accumulator
     want_ch = (gc ** 2).astype(f32).astype(np.float64).sum(axis=1 if right else 0)
-    assert np.allclose(chan.cpu().numpy(), want_ch, rtol=1e-12)
+    assert np.allclose(chan.cpu().numpy(), want_ch, rtol=1e-6)      # 8 neighbouring squares are added in binary32 first
 
 
 def test_apollo_tensor_core_step_teacher_forced_on_g_low(oracle):
