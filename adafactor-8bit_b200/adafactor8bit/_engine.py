@@ -1004,15 +1004,39 @@ class ApolloPlan:
             self._low_plans[key] = plan
         return plan
 
-    def run(self, grads, pts, per_tensor, lowrank_scalars, first_flags, floor_later, stream=None, params=None):
+    def _alpha_decay(self, scale, stream):
+        """scale_parameter=True: alpha_t = max(RMS(p), eps2) * rho and the decay factor of every tensor, computed on
+        the device from the parameters as they are before the update (optimizer.py:850-853, 3007-3013), into
+        self.alpha_decay ([n][2] floats) for the finaliser and the write-back."""
+        lib = N.lib()
+        chunk = lib.af8_scale_chunk()
+        numel = np.array([r * c for r, c in zip(self.rows, self.cols)], dtype=np.int64)
+        nchunks = (numel + chunk - 1) // chunk
+        if getattr(self, "alpha_decay", None) is None:
+            self.alpha_decay = torch.zeros(self.n, 2, dtype=torch.float32, device=self.device)
+            self.h_scale = _PinnedRing(self.n * N.SCALE_TENSOR.itemsize)
+            self.d_scale = torch.empty(self.n * N.SCALE_TENSOR.itemsize, dtype=torch.uint8, device=self.device)
+            self.d_chunks = torch.empty(int(nchunks.sum()), dtype=torch.float32, device=self.device)
+        hb = self.h_scale.next()
+        t = hb.numpy()[: self.n * N.SCALE_TENSOR.itemsize].view(N.SCALE_TENSOR)
+        fill_scale_table(t, self.params, numel, numel, nchunks, self.param_dtype, scale)
+        N.check(lib.af8_param_scale(hb.data_ptr(), self.d_scale.data_ptr(), self.n, self.d_chunks.data_ptr(),
+                                    self.alpha_decay.data_ptr(), 8, 0, 4, stream.cuda_stream), "af8_param_scale")
+        self.h_scale.mark(stream)
+
+    def run(self, grads, pts, per_tensor, lowrank_scalars, first_flags, floor_later, stream=None, params=None, scale=None):
         """per_tensor: list of dicts with the ApolloScalarsIn fields, decay, has_decay and the
         device scalar `fira_prev` (or None).  lowrank_scalars: v_w, m_w, apollo_eps.
-        params: this step's 2-D views of the parameters (their storage may have been replaced)."""
+        params: this step's 2-D views of the parameters (their storage may have been replaced).
+        scale: per-tensor inputs of af8_param_scale when the step size follows the parameters' RMS
+        (scale_parameter=True); alpha and the decay factor then come from the device."""
         stream = stream or torch.cuda.current_stream(self.device)
         if params is not None:
             self.params = list(params)
         lib = N.lib()
         s = stream.cuda_stream
+        if scale is not None:
+            self._alpha_decay(scale, stream)
         log = LAUNCH_LOG
         ev = None
         if log is not None:
@@ -1066,7 +1090,8 @@ class ApolloPlan:
                 N.check(lib.af8_apollo_scales(self.upd[i].data_ptr(), self.g_low[i].data_ptr(), self.chan_g2[i].data_ptr(),
                                               self.rows[i], self.cols[i], self.rank, ctypes.byref(sin), self.sf[i].data_ptr(),
                                               self.sums.data_ptr() + 24 * i, prev.data_ptr() if prev is not None else None,
-                                              self.out.data_ptr() + 16 * i, s), "af8_apollo_scales")
+                                              self.out.data_ptr() + 16 * i,
+                                              self.alpha_decay.data_ptr() + 8 * i if scale is not None else None, s), "af8_apollo_scales")
         else:                                       # channel-wise scaling: all tensors in two launches
             h = self.h_finish.next()
             ft = np.frombuffer(h.numpy(), dtype=N.APOLLO_FINISH_TENSOR, count=self.n)
@@ -1074,6 +1099,7 @@ class ApolloPlan:
             for i, sin in enumerate(sins):
                 prev = per_tensor[i].get("fira_prev")
                 ft["fira_prev"][i] = prev.data_ptr() if prev is not None else 0
+                ft["alpha_decay"][i] = self.alpha_decay.data_ptr() + 8 * i if scale is not None else 0
                 for k in ("alpha", "bc", "d", "clip_div", "fira_margin1", "sqrt_scale", "bc_mode", "fira", "fira_has_prev",
                           "scale_tensor", "scale_front"):
                     ft[k][i] = getattr(sin, k)
@@ -1085,7 +1111,7 @@ class ApolloPlan:
             N.check(lib.af8_apollo_apply(self.params[i].data_ptr(), self.param_dtype, int(t.get("sr", False)), int(t.get("sr_base", 0)),
                                          grads[i].data_ptr(), self.grad_dtype, self.negate,
                                          self.sf[i].data_ptr(), self.out.data_ptr() + 16 * i, self.rows[i], self.cols[i],
-                                         ctypes.byref(sin), float(t["decay"]), int(t["has_decay"]),
+                                         ctypes.byref(sin), float(t["decay"]), 2 if scale is not None else int(t["has_decay"]),
                                          self.copies[i].data_ptr() if self.copies[i] is not None else None, s), "af8_apollo_apply")
         if log is not None:
             ev[3].record(stream)

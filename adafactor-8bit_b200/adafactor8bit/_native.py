@@ -66,7 +66,7 @@ APOLLO_FINISH_TENSOR = np.dtype(
     [(n, np.int64) for n in ("rows", "cols", "rank", "first_unit")] +
     [(n, np.float32) for n in ("alpha", "bc", "d", "clip_div", "fira_margin1", "sqrt_scale")] +
     [(n, np.int32) for n in ("bc_mode", "fira", "fira_has_prev", "scale_tensor", "scale_front", "in_reserved")] +
-    [("reserved", np.int64)], align=True)     # af8_apollo_finish_tensor, 144 B
+    [("alpha_decay", np.uint64)], align=True)     # af8_apollo_finish_tensor, 144 B
 
 SMALL_STATE = np.dtype([
     ("q", _P), ("scale", _P), ("min_log", _P), ("f32", _P), ("fmt", np.int32), ("block", np.int32),
@@ -176,7 +176,7 @@ PROTOTYPES = {
     "af8_apollo_project_batch": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_p, _c_p, _c_l, _c_p]),
     "af8_apollo_scales_batch": (_c_i, [_c_p, _c_p, _c_i, _c_l, _c_p]),
     "af8_apollo_scales": (_c_i, [_c_p, _c_p, _c_p, _c_l, _c_l, _c_l, ctypes.POINTER(ApolloScalarsIn), _c_p, _c_p, _c_p,
-                                 _c_p, _c_p]),
+                                 _c_p, _c_p, _c_p]),
     "af8_apollo_apply": (_c_i, [_c_p, _c_i, _c_i, ctypes.c_uint64, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l,
                                 ctypes.POINTER(ApolloScalarsIn), _c_f, _c_i, _c_p, _c_p]),
     "af8_apollo_rule_workspace": (ctypes.c_int64, [_c_l, _c_l]),

@@ -875,8 +875,6 @@ class Adafactor8Bit(Optimizer):
         return proj_t
 
     def _run_apollo(self, gi, group, key, items):
-        if group["scale_parameter"]:
-            raise NotImplementedError("APOLLO with scale_parameter=True is not available in this build")
         rank = int(group["apollo_rank"])
         beta1, beta2 = group.get("beta1"), group["beta2"]
         beta3 = group.get("beta3")
@@ -988,8 +986,15 @@ class Adafactor8Bit(Optimizer):
                    apollo_eps=f32(apollo_eps), c_w=f32(1.0 - beta3) if beta3 is not None else f32(0.0),
                    eps_came=f32(group.get("eps_came", 1e-16)), eps_sq=f32(max(apollo_eps * apollo_eps, _FLOOR)), d=f32(group["d"]))
         floor_later = math.log2(max(apollo_eps * apollo_eps, _FLOOR))                  # optimizer.py:2766-2767
+        scale = None
+        if group["scale_parameter"]:                     # alpha_t from the parameters' RMS, on the device (optimizer.py:850-853)
+            scale = self._scale_inputs(group, len(items))
+            for i, (p, g, st) in enumerate(items):
+                self._fill_scale(scale, i, group, self._step_scalars(group, st["step"]))
+            scale["bc_mode"][:] = 0                      # the bias correction enters the update scale (optimizer.py:3015-3023)
+
         def passes():
-            plan.run(grads, pts, per_tensor, low, first_flags, floor_later, params=[p for p, _, _ in items])
+            plan.run(grads, pts, per_tensor, low, first_flags, floor_later, params=[p for p, _, _ in items], scale=scale)
             return
             yield                                                                       # (no exchange points)
         return 0, device, passes()

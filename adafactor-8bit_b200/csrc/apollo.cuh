@@ -283,8 +283,10 @@ apollo_tensor_sums_kernel(const float *upd, const float *g_low, int64_t nl, cons
 // ---------------------------------------------------------------------------
 // 4. scalar chain of one tensor (one thread)
 // ---------------------------------------------------------------------------
+// alpha_decay: optional device pair (alpha_t, decay factor) from af8_param_scale (scale_parameter=True,
+// optimizer.py:850-853, 3007-3013); NULL: in.alpha, and the decay travels as a kernel argument
 __device__ __forceinline__ void apollo_finalize_one(const af8_apollo_scalars_in &in, const double *sums, float *sf_tensor,
-                                                    float *fira_prev, af8_apollo_scalars *out)
+                                                    float *fira_prev, af8_apollo_scalars *out, const float *alpha_decay = nullptr)
 {
     float norm, s_tensor = 0.0f;
     if (in.scale_tensor) {
@@ -314,19 +316,20 @@ __device__ __forceinline__ void apollo_finalize_one(const af8_apollo_scalars_in 
         const float x = __fdiv_rn(norm, in.clip_div);
         denom = (x >= 1.0f || isnan(x)) ? x : 1.0f;
     }
-    float us = __fdiv_rn(-in.alpha, denom);                                 // optimizer.py:3013
+    const float alpha = alpha_decay ? alpha_decay[0] : in.alpha;
+    float us = __fdiv_rn(-alpha, denom);                                    // optimizer.py:3013
     if (in.bc_mode == 1) us = __fmul_rn(us, in.bc);                         // optimizer.py:3021
     else if (in.bc_mode == 2) us = __fdiv_rn(us, in.bc);                    // optimizer.py:3023
     out->update_scale = us;
     out->fira = fs;
     out->norm = norm;
-    out->reserved = 0.0f;
+    out->decay = alpha_decay ? alpha_decay[1] : 1.0f;
 }
 
-__global__ void apollo_finalize_kernel(const af8_apollo_scalars_in in, const double *sums, float *sf_tensor,
+__global__ void apollo_finalize_kernel(const float *alpha_decay, const af8_apollo_scalars_in in, const double *sums, float *sf_tensor,
                                        float *fira_prev, af8_apollo_scalars *out)
 {
-    apollo_finalize_one(in, sums, sf_tensor, fira_prev, out);
+    apollo_finalize_one(in, sums, sf_tensor, fira_prev, out, alpha_decay);
 }
 
 // ---------------------------------------------------------------------------
@@ -419,7 +422,7 @@ __global__ void apollo_finalize_multi_kernel(const af8_apollo_finish_tensor *T, 
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         const af8_apollo_scalars_in in = T[i].in;
-        apollo_finalize_one(in, T[i].sums, T[i].sf, T[i].fira_prev, T[i].out);
+        apollo_finalize_one(in, T[i].sums, T[i].sf, T[i].fira_prev, T[i].out, T[i].alpha_decay);
     }
 }
 
@@ -451,6 +454,7 @@ apollo_apply_lowp_kernel(void *param, const void *grad, int grad_dtype, int nega
                          int fira, int front, float sqrt_scale, float decay, int has_decay, const ApolloLowp P)
 {
     const float us = sc->update_scale, fs = sc->fira;
+    if (has_decay == 2) decay = sc->decay;               // computed on the device (parameter-scaled step)
     const int64_t n = rows * cols;
     for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * 256) {
         const float g = apollo_grad(grad, grad_dtype, idx, negate);
@@ -468,6 +472,7 @@ apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, 
                     int fira, int front, float sqrt_scale, float decay, int has_decay, uint16_t *param_copy)
 {
     const float us = sc->update_scale, fs = sc->fira;
+    if (has_decay == 2) decay = sc->decay;               // computed on the device (parameter-scaled step)
     const int64_t n = rows * cols;
     for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * 1024) {
 #pragma unroll
@@ -506,6 +511,7 @@ apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ gra
 {
     float *const param = static_cast<float *>(param_v);
     const float us = sc->update_scale, fs = sc->fira;
+    if (has_decay == 2) decay = sc->decay;               // computed on the device (parameter-scaled step)
     const uint32_t gpr = (uint32_t)(cols >> 3);                 // groups of 8 per row
     const uint32_t ngroups = (uint32_t)((rows * cols) >> 3);
     const float st = scale_tensor ? __ldg(sf) : 0.0f;
@@ -929,7 +935,8 @@ extern "C" int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32
 
 extern "C" int af8_apollo_scales(const float *upd, const float *g_low, const double *chan_g2, int64_t rows,
                                  int64_t cols, int64_t rank, const af8_apollo_scalars_in *in, float *sf,
-                                 double *sums, float *fira_prev, af8_apollo_scalars *out, void *stream)
+                                 double *sums, float *fira_prev, af8_apollo_scalars *out, const float *alpha_decay,
+                                 void *stream)
 {
     using namespace af8;
     if (!upd || !g_low || !chan_g2 || !in || !sf || !sums || !out) return fail(AF8_ERR_INVALID, "af8_apollo_scales: null argument");
@@ -949,7 +956,7 @@ extern "C" int af8_apollo_scales(const float *upd, const float *g_low, const dou
         apollo_scales_kernel<<<(int)g, 256, 0, st>>>(upd, g_low, chan_g2, nch, rank, right, in->scale_front, in->sqrt_scale, sf, sums);
     }
     AF8_CUDA_TRY(cudaGetLastError());
-    apollo_finalize_kernel<<<1, 1, 0, st>>>(*in, sums, sf, fira_prev, out);
+    apollo_finalize_kernel<<<1, 1, 0, st>>>(alpha_decay, *in, sums, sf, fira_prev, out);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }

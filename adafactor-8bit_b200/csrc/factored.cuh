@@ -33,6 +33,7 @@ namespace af8 {
 constexpr int FSTAT_ROWS = 512;
 constexpr int FSTAT_COLS = 256;
 constexpr int FUPD_THREADS = 256;
+constexpr int DEVERR_SRING_TIMEOUT = 4;      // a bulk copy of the statistic pass's input ring did not land
 
 struct FactoredLaunch {
     const af8_factored_tensor *tensors;
@@ -680,6 +681,132 @@ __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_fa
     }
 }
 
+// The same rows with the inputs of every row slice (256 columns: 512 or 1024 bytes of gradient and,
+// for the residual, 256 momentum codes) requested SR_STAGES slices ahead by the warp's lane 0 with
+// cp.async.bulk into the warp's own ring (one mbarrier per stage).  Needs cols % 256 == 0 (whole
+// slices, 16-byte aligned runs) and, for the residual, a UF8 momentum.  NB rows are consumed per
+// iteration so that their row sums are reduced jointly, as above.  Returns false after a time-out.
+template <typename GradT> __host__ __device__ constexpr int sring_stages() { return sizeof_grad<GradT>() == 2 ? 8 : 4; }
+template <typename GradT, bool RESIDUAL> __host__ __device__ constexpr int sring_stage_bytes() { return 256 * sizeof_grad<GradT>() + (RESIDUAL ? 256 : 0); }
+template <typename GradT, bool RESIDUAL> __host__ __device__ constexpr size_t sring_smem_bytes() { return (size_t)8 * sring_stages<GradT>() * sring_stage_bytes<GradT, RESIDUAL>(); }
+
+template <typename GradT, int NB, bool RESIDUAL>
+__device__ __forceinline__ bool stats_rows_ring(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t c0,
+                                                float pre_div, const float (&ic)[8], double (&cacc)[8],
+                                                unsigned char *ring, uint64_t *full, uint32_t &cons)
+{
+    constexpr int GB = sizeof_grad<GradT>(), NS = sring_stages<GradT>(), STAGE = sring_stage_bytes<GradT, RESIDUAL>();
+    static_assert(NS % NB == 0, "a ring holds whole groups of rows");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t R = sT.rows, C = sT.cols;
+    const int64_t c = c0 + lane * 8;
+    const int64_t r_end = min(R, r0 + (int64_t)FSTAT_ROWS);
+    const int nrows = r0 + warp < r_end ? (int)((r_end - (r0 + warp) + 7) / 8) : 0;       // rows r0 + warp + 8 k of this warp
+    const unsigned char *gp = static_cast<const unsigned char *>(sT.grad);
+    auto issue = [&](int k) {                                    // lane 0: row slice k into its stage
+        const int64_t off = (r0 + warp + 8 * (int64_t)k) * C + c0;
+        const int sl = (int)((cons + (uint32_t)k) % NS);         // (cons counts the slices consumed before this tile)
+        unsigned char *dst = ring + sl * STAGE;
+        mbar_expect_tx(&full[sl], (uint32_t)STAGE);
+        bulk_g2s(dst, gp + off * GB, 256 * GB, &full[sl]);
+        if (RESIDUAL) bulk_g2s(dst + 256 * GB, sT.m_q + off, 256, &full[sl]);
+    };
+    if (lane == 0 && nrows > 0) {
+        fence_proxy_async();
+        for (int k = 0; k < min(NS, nrows); ++k) issue(k);
+    }
+    const DivBy D = make_div(pre_div);
+    const LerpW LW = make_lerp(sT.m_w);
+    const float2 eps2 = bc2(sT.eps_came);
+    for (int k0 = 0; k0 < nrows; k0 += NB) {
+        GradRaw8<GradT> cur[NB];
+        uint2 cm[NB];
+        bool landed = true;
+#pragma unroll
+        for (int k = 0; k < NB; ++k) {
+            cm[k] = make_uint2(0u, 0u);
+            if (k0 + k < nrows) {
+                const uint32_t n = cons + (uint32_t)(k0 + k);
+                const int sl = (int)(n % NS);
+                landed = landed && mbar_wait_bounded(&full[sl], (n / NS) & 1u);
+                const unsigned char *st = ring + sl * STAGE;
+                cur[k].from_shared(st + lane * (8 * GB));
+                if (RESIDUAL) cm[k] = *reinterpret_cast<const uint2 *>(st + 256 * GB + lane * 8);
+            } else cur[k].zero();
+        }
+        if (!__all_sync(0xffffffffu, landed)) return false;
+        __syncwarp();                                            // the stages were read: they may be refilled
+        if (lane == 0) {
+            fence_proxy_async();
+#pragma unroll
+            for (int k = 0; k < NB; ++k)
+                if (k0 + k + NS < nrows) issue(k0 + k + NS);
+        }
+        double rsum[NB];
+#pragma unroll
+        for (int k = 0; k < NB; ++k) {
+            const int64_t r = r0 + warp + 8 * (int64_t)(k0 + k);
+            const bool live = k0 + k < nrows;
+            float g[8], x[8];
+            cur[k].unpack(L.negate_grad, g);
+            if (!RESIDUAL) {
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 gj = make_float2(g[j], g[j + 1]);
+                    const float2 xx = __fmul2_rn(gj, gj);
+                    x[j] = xx.x; x[j + 1] = xx.y;
+                }
+            } else if (live) {
+                const int64_t flat = r * C + c;
+                const float2 ir2 = bc2(sT.inv_row[r]);
+                float mo[8];
+                m_old8(sT, L.m_fmt, L.m_block, flat, mo, true, cm[k]);
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 u = div_by2(__fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1])), D);
+                    const float2 m = lerp_w2(make_float2(mo[j], mo[j + 1]), u, LW);
+                    const float2 df = sub2(u, m);
+                    const float2 xx = __fadd2_rn(__fmul2_rn(df, df), eps2);
+                    x[j] = xx.x; x[j + 1] = xx.y;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] = 0.0f;
+            }
+            double racc = 0.0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const double xd = (double)x[j];
+                racc += xd;
+                cacc[j] += xd;
+            }
+            rsum[k] = racc;
+        }
+        static_assert(NB == 2 || NB == 4, "row-sum reduction is written for 2 or 4 rows");
+        double v;
+        if (NB == 4) {
+            const bool hi = lane & 16;
+            const double r0x = __shfl_xor_sync(0xffffffffu, hi ? rsum[0] : rsum[2], 16);
+            const double r1x = __shfl_xor_sync(0xffffffffu, hi ? rsum[1] : rsum[NB - 1], 16);
+            const double k0v = (hi ? rsum[2] : rsum[0]) + r0x;
+            const double k1v = (hi ? rsum[NB - 1] : rsum[1]) + r1x;
+            const bool h2 = lane & 8;
+            v = (h2 ? k1v : k0v) + __shfl_xor_sync(0xffffffffu, h2 ? k0v : k1v, 8);
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if ((lane & 7) == 0 && k0 + (lane >> 3) < nrows) atomicAdd(sT.row_sum + r0 + warp + 8 * (int64_t)(k0 + (lane >> 3)), v);
+        } else {
+            const bool hi = lane & 16;
+            v = (hi ? rsum[1] : rsum[0]) + __shfl_xor_sync(0xffffffffu, hi ? rsum[0] : rsum[1], 16);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if ((lane & 15) == 0 && k0 + (lane >> 4) < nrows) atomicAdd(sT.row_sum + r0 + warp + 8 * (int64_t)(k0 + (lane >> 4)), v);
+        }
+    }
+    cons += (uint32_t)nrows;
+    return true;
+}
+
 // RESIDUAL: CAME's (U - M)^2 + eps statistic; otherwise g^2 (separate instantiations, so that
 // the lighter one keeps its lower register count)
 // resident CTAs asked of the compiler (measured on B200: 3 for both passes; the g*g pass went
@@ -698,12 +825,22 @@ __device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_fa
 #endif
 template <typename GradT, bool RESIDUAL>
 __global__ void __launch_bounds__(256, RESIDUAL ? AF8_FSTAT_MIN_CTAS_RES : AF8_FSTAT_MIN_CTAS)
-factored_stats_vec_kernel(const FactoredLaunch L)
+factored_stats_vec_kernel(const FactoredLaunch L, const int use_ring)
 {
     __shared__ double s_col[8][FSTAT_COLS];      // [warp][j * 32 + lane]
     __shared__ af8_factored_tensor sT;
+    extern __shared__ __align__(128) unsigned char sr_smem[];            // the warps' input rings (use_ring)
+    __shared__ __align__(8) uint64_t s_full[8][sring_stages<GradT>()];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int cur_t = -1;
+    uint32_t cons = 0;                           // row slices this warp has taken from its ring
+    if (use_ring) {
+        if (lane == 0) {
+            for (int k = 0; k < sring_stages<GradT>(); ++k) mbar_init(&s_full[warp][k], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+    }
 
     for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
         int t = cur_t;
@@ -734,7 +871,18 @@ factored_stats_vec_kernel(const FactoredLaunch L)
         double cacc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) cacc[j] = 0.0;
-        if (!RESIDUAL) stats_rows<GradT, 4, true, false>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
+        // residual: whole 256-column slices of the gradient and the UF8 codes come through the warp's ring
+        // (measured on Llama-2-7B: 11.9 -> 11.4 ms; the g*g pass and the sum passes, which only read the
+        // gradient, were slower through a ring - 3.0 -> 4.3 ms and 4.6 -> 5.9 ms - and load directly)
+        const bool ring_ok = RESIDUAL && use_ring && (C % FSTAT_COLS) == 0 && L.m_fmt == AF8_M_UF8;
+        if (ring_ok) {
+            unsigned char *ring = sr_smem + (size_t)warp * sring_stages<GradT>() * sring_stage_bytes<GradT, RESIDUAL>();
+            if (!stats_rows_ring<GradT, RESIDUAL ? AF8_FSTAT_RES_NB : 4, RESIDUAL>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)) {
+                atomicExch(&g_device_error, DEVERR_SRING_TIMEOUT);
+                return;                          // (the whole warp; the others finish their rows and leave at the next barrier)
+            }
+        }
+        else if (!RESIDUAL) stats_rows<GradT, 4, true, false>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
         else stats_rows<GradT, AF8_FSTAT_RES_NB, AF8_FSTAT_RES_PREFETCH, true>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
 #pragma unroll
         for (int j = 0; j < 8; ++j) s_col[warp][j * 32 + lane] = cacc[j];
@@ -1349,10 +1497,17 @@ extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factore
     if (grid > tiles) grid = tiles;
     const bool bf = cfg->grad_dtype == AF8_BF16, res = cfg->mode == AF8_FSTAT_RESIDUAL;
     const bool vec = cfg->aligned8 && cfg->grad_dtype != AF8_F16;      // fp16 gradients take the general kernels
-    if (vec && bf && res) factored_stats_vec_kernel<bf16_tag, true><<<(int)grid, 256, 0, st>>>(L);
-    else if (vec && bf) factored_stats_vec_kernel<bf16_tag, false><<<(int)grid, 256, 0, st>>>(L);
-    else if (vec && res) factored_stats_vec_kernel<float, true><<<(int)grid, 256, 0, st>>>(L);
-    else if (vec) factored_stats_vec_kernel<float, false><<<(int)grid, 256, 0, st>>>(L);
+    static const bool ring_off = getenv("AF8_NO_FACTORED_RING") != nullptr;
+    const int ring = (ring_off || !res) ? 0 : 1;
+#define AF8_LAUNCH_FSTAT(G, RES) do { \
+        const size_t sm = ring ? sring_smem_bytes<G, RES>() : 0; \
+        if (sm > 0) AF8_CUDA_TRY(cudaFuncSetAttribute(factored_stats_vec_kernel<G, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)); \
+        factored_stats_vec_kernel<G, RES><<<(int)grid, 256, sm, st>>>(L, ring); } while (0)
+    if (vec && bf && res) AF8_LAUNCH_FSTAT(bf16_tag, true);
+    else if (vec && bf) AF8_LAUNCH_FSTAT(bf16_tag, false);
+    else if (vec && res) AF8_LAUNCH_FSTAT(float, true);
+    else if (vec) AF8_LAUNCH_FSTAT(float, false);
+#undef AF8_LAUNCH_FSTAT
     else factored_stats_kernel<<<(int)grid, 256, 0, st>>>(L);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;

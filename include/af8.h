@@ -416,7 +416,7 @@ typedef struct af8_apollo_scalars {
     float update_scale;     /* -alpha/denom with bias correction */
     float fira;             /* Fira scale */
     float norm;             /* the global norm that was limited */
-    float reserved;
+    float decay;            /* weight-decay factor when it was computed on the device (alpha_decay), else 1 */
 } af8_apollo_scalars;
 
 /* g_low = G @ Pt (rows >= cols; Pt is cols x rank, g_low rows x rank) or Pt @ G
@@ -470,12 +470,14 @@ AF8_API int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32_t 
 /* Scaling factors sf[channel] = ||update_low|| / (||g_low|| + 1e-8) (one entry
  * for the tensor-wide variant), the global norm, the Fira limiter, the clip
  * and the bias correction.  sums: 3 doubles of scratch.  fira_prev: device
- * scalar of the state key "scaled_grad_norm_prev".
+ * scalar of the state key "scaled_grad_norm_prev".  alpha_decay: as
+ * af8_apollo_finish_tensor.alpha_decay, or NULL.
  * Replaces compute_apollo_norms (kernels.cu:2441-2453), fira_scalar and the
  * torch glue of optimizer.py:2961-3023. */
 AF8_API int af8_apollo_scales(const float *upd, const float *g_low, const double *chan_g2, int64_t rows,
                               int64_t cols, int64_t rank, const af8_apollo_scalars_in *in, float *sf,
-                              double *sums, float *fira_prev, af8_apollo_scalars *out, void *stream);
+                              double *sums, float *fira_prev, af8_apollo_scalars *out, const float *alpha_decay,
+                              void *stream);
 
 /* p = p*decay + (update_scale * G) * (sf[channel] * fira * sqrt_scale) for fp32
  * parameters.  Replaces the apollo_apply_* kernels (kernels.cu:2834-3000) and the
@@ -494,7 +496,9 @@ typedef struct af8_apollo_finish_tensor {
     int64_t rows, cols, rank;
     int64_t first_unit;
     af8_apollo_scalars_in in;
-    int64_t reserved;
+    const float *alpha_decay;   /* optional device pair {alpha_t, decay factor} written by af8_param_scale for
+                                   scale_parameter=True (optimizer.py:850-853, 3007-3013): replaces in.alpha, and the
+                                   decay factor is handed on in af8_apollo_scalars.decay; NULL: in.alpha */
 } af8_apollo_finish_tensor;
 AF8_API int af8_apollo_scales_batch(const af8_apollo_finish_tensor *host_tensors, af8_apollo_finish_tensor *dev_tensors,
                                     int32_t n, int64_t total_units, void *stream);
@@ -504,7 +508,8 @@ AF8_API int af8_apollo_scales_batch(const af8_apollo_finish_tensor *host_tensors
  * and rounded stochastically with the counter generator at sr_base (see af8_fullrank_tensor.sr_base;
  * optimizer.py:3043-3079, apollo_apply_{bf16,fp16}_{sr,det}).
  * param_copy: optional bf16 copy of the updated fp32 parameter (rows*cols 16-bit words, 16-byte aligned),
- * as af8_fullrank_tensor.param_copy; NULL for none. */
+ * as af8_fullrank_tensor.param_copy; NULL for none.
+ * has_decay: 0 none, 1 multiply by `decay`, 2 multiply by scalars->decay (computed on the device). */
 AF8_API int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stochastic_round, uint64_t sr_base,
                              const void *grad, int32_t grad_dtype, int32_t negate, const float *sf,
                              const af8_apollo_scalars *scalars, int64_t rows, int64_t cols,

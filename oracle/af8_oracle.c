@@ -845,23 +845,33 @@ static float mean_f64(const float *x, int64_t n)
  * (optimizer.py:2202-2253 statistics, 2394-2399 / 2543-2549 dispatch),
  * _factored_inv_std (optimizer.py:818-821), _compute_ut_clipped
  * (optimizer.py:824-829) and _fallback_2d_update (optimizer.py:920-970). */
+/* The next af8o_factored_step treats its tensor as a batch of this many rows x cols matrices. */
+static int64_t factored_batch = 1;
+AF8O_API void af8o_factored_set_batch(int64_t b) { factored_batch = b; }
+
 AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void *grad,
                                 af8o_small_state *row_var, af8o_small_state *col_var,
                                 af8o_small_state *conf_row, af8o_small_state *conf_col,
                                 uint8_t *m_q, float *m_scale, float *m_f32, const float *map,
                                 int *fira_has_prev, float *fira_prev, float *norm_out)
 {
-    const int64_t R = c->rows, C = c->cols, n = R * C;
+    /* a tensor of more than two dimensions is a batch of B matrices (optimizer.py:2203-2207): rows / cols
+     * describe one of them, the row states hold B*R values, the column states B*C, the means that
+     * normalise the row factor are taken per matrix (row_var.mean(dim=-2)), norms over the whole tensor */
+    const int64_t B = factored_batch > 0 ? factored_batch : 1;
+    factored_batch = 1;
+    const int64_t R = c->rows, C = c->cols, RC = R * C, n = B * RC;
+#define COLI(i) (((i) / RC) * C + (i) % C)
     const int has_m = c->m_fmt != AF8O_M_NONE;
     const int m_quant = has_m && c->m_fmt != AF8O_M_FP32;
     float *g = (float *)malloc((size_t)n * sizeof(float));
     float *u = (float *)malloc((size_t)n * sizeof(float));
-    float *rmean = (float *)malloc((size_t)R * sizeof(float));
-    float *cmean = (float *)malloc((size_t)C * sizeof(float));
-    float *row = (float *)malloc((size_t)R * sizeof(float));
-    float *col = (float *)malloc((size_t)C * sizeof(float));
-    float *inv_r = (float *)malloc((size_t)R * sizeof(float));
-    float *inv_c = (float *)malloc((size_t)C * sizeof(float));
+    float *rmean = (float *)malloc((size_t)(B * R) * sizeof(float));
+    float *cmean = (float *)malloc((size_t)(B * C) * sizeof(float));
+    float *row = (float *)malloc((size_t)(B * R) * sizeof(float));
+    float *col = (float *)malloc((size_t)(B * C) * sizeof(float));
+    float *inv_r = (float *)malloc((size_t)(B * R) * sizeof(float));
+    float *inv_c = (float *)malloc((size_t)(B * C) * sizeof(float));
     if (!g || !u || !rmean || !cmean || !row || !col || !inv_r || !inv_c) return 2;
 
     note_decay(c->has_decay, c->decay);
@@ -871,17 +881,19 @@ AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void
         p[i] = decay_param(p[i], c->has_decay, c->decay);          /* optimizer.py:2039 */
         u[i] = g[i] * g[i];                                /* optimizer.py:2221 */
     }
-    row_col_means(u, R, C, rmean, cmean);                  /* optimizer.py:2222-2223 */
-    for (int64_t i = 0; i < R; ++i) rmean[i] = rmean[i] + c->eps1;
-    for (int64_t j = 0; j < C; ++j) cmean[j] = cmean[j] + c->eps1;
+    for (int64_t b = 0; b < B; ++b) row_col_means(u + b * RC, R, C, rmean + b * R, cmean + b * C);   /* optimizer.py:2222-2223 */
+    for (int64_t i = 0; i < B * R; ++i) rmean[i] = rmean[i] + c->eps1;
+    for (int64_t j = 0; j < B * C; ++j) cmean[j] = cmean[j] + c->eps1;
 
     /* optimizer.py:2232-2238 / 2248-2252 */
     small_state_ema(row_var, rmean, c->v_w, c->block, c->v_floor, row);
     small_state_ema(col_var, cmean, c->v_w, c->block, c->v_floor, col);
-    float rm = mean_f64(row, R);
-    if (rm < c->eps1) rm = c->eps1;
-    for (int64_t i = 0; i < R; ++i) inv_r[i] = rsqrt_t(row[i] / rm);   /* optimizer.py:819 */
-    for (int64_t j = 0; j < C; ++j) inv_c[j] = rsqrt_t(col[j]);        /* optimizer.py:820 */
+    for (int64_t b = 0; b < B; ++b) {
+        float rm = mean_f64(row + b * R, R);
+        if (rm < c->eps1) rm = c->eps1;
+        for (int64_t i = b * R; i < (b + 1) * R; ++i) inv_r[i] = rsqrt_t(row[i] / rm);   /* optimizer.py:819 */
+    }
+    for (int64_t j = 0; j < B * C; ++j) inv_c[j] = rsqrt_t(col[j]);    /* optimizer.py:820 */
 
     float norm = -1.0f;
     int rc = 0;
@@ -890,7 +902,7 @@ AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < n; ++i) {
             float t = g[i] * inv_r[i / C];                 /* optimizer.py:825 */
-            g[i] = t * inv_c[i % C];
+            g[i] = t * inv_c[COLI(i)];
         }
         if (c->d > 0.0f) {                                 /* optimizer.py:826-828 */
             float rms = norm2_f64(g, n) / c->sqrt_n;
@@ -911,18 +923,20 @@ AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void
             t = t * t;
             g[i] = t + c->eps_came;
         }
-        row_col_means(g, R, C, rmean, cmean);              /* optimizer.py:933-934 */
+        for (int64_t b = 0; b < B; ++b) row_col_means(g + b * RC, R, C, rmean + b * R, cmean + b * C);   /* optimizer.py:933-934 */
         small_state_ema(conf_row, rmean, c->c_w, c->block, c->v_floor, row);   /* optimizer.py:937-946 */
         small_state_ema(conf_col, cmean, c->c_w, c->block, c->v_floor, col);
-        float cm = mean_f64(row, R);                       /* optimizer.py:948 */
-        if (cm < c->eps1) cm = c->eps1;
-        for (int64_t i = 0; i < R; ++i) inv_r[i] = rsqrt_t(row[i] / cm);
-        for (int64_t j = 0; j < C; ++j) inv_c[j] = rsqrt_t(col[j]);
+        for (int64_t b = 0; b < B; ++b) {
+            float cm = mean_f64(row + b * R, R);           /* optimizer.py:948 */
+            if (cm < c->eps1) cm = c->eps1;
+            for (int64_t i = b * R; i < (b + 1) * R; ++i) inv_r[i] = rsqrt_t(row[i] / cm);
+        }
+        for (int64_t j = 0; j < B * C; ++j) inv_c[j] = rsqrt_t(col[j]);
         if (!m_quant) memcpy(u, m, (size_t)n * sizeof(float));
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < n; ++i) {                  /* optimizer.py:952, 955 */
             float t = u[i] * inv_r[i / C];
-            u[i] = t * inv_c[i % C];
+            u[i] = t * inv_c[COLI(i)];
         }
         norm = apply_update(p, u, n, c->alpha, 0.0f, c->clip_div, c->fira, c->fira_margin1,
                             fira_has_prev, fira_prev);
@@ -937,7 +951,7 @@ AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < n; ++i) {
             float t = u[i] * inv_r[i / C];
-            u[i] = t * inv_c[i % C];
+            u[i] = t * inv_c[COLI(i)];
         }
         norm = apply_update(p, u, n, c->alpha, c->d, c->clip_div, c->fira, c->fira_margin1,
                             fira_has_prev, fira_prev);
@@ -946,13 +960,14 @@ AF8O_API int af8o_factored_step(const af8o_factored_cfg *c, float *p, const void
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < n; ++i) {
             float t = g[i] * inv_r[i / C];
-            u[i] = t * inv_c[i % C];
+            u[i] = t * inv_c[COLI(i)];
         }
         norm = apply_update(p, u, n, c->alpha, c->d, c->clip_div, c->fira, c->fira_margin1,
                             fira_has_prev, fira_prev);
     }
     if (norm_out) *norm_out = norm;
     free(g); free(u); free(rmean); free(cmean); free(row); free(col); free(inv_r); free(inv_c);
+#undef COLI
     return rc;
 }
 

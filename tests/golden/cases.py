@@ -248,8 +248,14 @@ CASES["apollo_came_fp32"] = dict(shapes=[(96, 64), (32, 160)], steps=5, seed=54,
                                  hp=dict(_APOLLO_X, beta3=0.9999, d=1.0, quantize=False))
 CASES["apollo_factorize_nomom"] = dict(shapes=[(96, 64), (32, 160)], steps=4, seed=55, grad=_G_APX,
                                        hp=dict(_APOLLO_X, apollo_factorize=True, beta1=None))
+# the step size follows the parameters' RMS (scale_parameter=True), weight decay scaled with it
+CASES["apollo_scale_param"] = dict(shapes=[(96, 64), (32, 160)], steps=5, seed=57, grad=_G_APX,
+                                   hp=dict(_APOLLO_X, lr=1e-2, scale_parameter=True, scale_weight_decay=True))
+CASES["apollo_scale_param_tensor"] = dict(shapes=[(96, 64), (32, 160)], steps=4, seed=59, grad=_G_APX,
+                                          hp=dict(_APOLLO_X, lr=1e-2, scale_parameter=True, scale_weight_decay=False,
+                                                  relative_step=True, apollo_scale_type="tensor"))
 APOLLO_RULE_CASES = ["apollo_factorize", "apollo_factorize_came", "apollo_came", "apollo_came_fp32",
-                     "apollo_factorize_nomom"]
+                     "apollo_factorize_nomom", "apollo_scale_param", "apollo_scale_param_tensor"]
 MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
 
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]
