@@ -593,18 +593,25 @@ class FactoredPlan:
         self.cfg.v_floor = -126.0
         if m_fmt in ("d8", "d4"):
             ensure_qmap(self.device)
-        for p in self.params:
-            if not p.is_contiguous() or p.dim() != 2:
-                raise RuntimeError("the factored kernels update contiguous 2-D parameters")
-        self.rows = np.array([p.shape[0] for p in self.params], dtype=np.int64)
-        self.cols = np.array([p.shape[1] for p in self.params], dtype=np.int64)
-        self.full_rows = np.array([(pc.full_rows or p.shape[0]) if pc is not None else p.shape[0]
-                                   for p, pc in zip(self.params, self.pieces)], dtype=np.int64)
+        for p, pc in zip(self.params, self.pieces):
+            if not p.is_contiguous() or p.dim() < 2:
+                raise RuntimeError("the factored kernels update contiguous parameters of two or more dimensions")
+            if p.dim() > 2 and pc is not None and pc.slots is not None:
+                raise RuntimeError("a tensor of more than two dimensions is not cut")
+        # a tensor of more than two dimensions is a batch of matrices over its last two (optimizer.py:2203-2207):
+        # rows counts the rows of all of them, mat_rows those of one, the column vectors hold batch * cols values
+        self.cols = np.array([p.shape[-1] for p in self.params], dtype=np.int64)
+        self.rows = np.array([p.numel() // p.shape[-1] for p in self.params], dtype=np.int64)
+        self.mat_rows = np.array([p.shape[-2] for p in self.params], dtype=np.int64)
+        self.batch = self.rows // self.mat_rows
+        self.full_rows = np.array([(pc.full_rows or r) if pc is not None else r
+                                   for r, pc in zip(self.rows.tolist(), self.pieces)], dtype=np.int64)
         self.row0 = np.array([pc.row0 if pc is not None else 0 for pc in self.pieces], dtype=np.int64)
         self.numel = self.rows * self.cols
         self.full_numel = self.full_rows * self.cols
         self.total_numel = int(self.numel.sum())
-        self.cfg.aligned8 = int(bool((self.cols % 8 == 0).all()))
+        # (batches of matrices take the general kernels; the optimizer keeps them in plans of their own)
+        self.cfg.aligned8 = int(bool((self.cols % 8 == 0).all()) and not bool((self.batch > 1).any()))
         lib = N.lib()
         m_quant = m_fmt not in (None, "fp32")
         self.chunk = lib.af8_factored_chunk(self.cfg.m_block if m_quant else 0)
@@ -613,7 +620,7 @@ class FactoredPlan:
         self.first_chunk = np.concatenate([[0], np.cumsum(self.nchunks)[:-1]]).astype(np.int64)
         self.total_chunks = int(self.nchunks.sum())
         # row sums (of the whole tensor's rows) then column sums of every tensor, each vector on a 16-byte boundary
-        self._vec_len = ((self.full_rows + 3) // 4 * 4) + ((self.cols + 3) // 4 * 4)
+        self._vec_len = ((self.full_rows + 3) // 4 * 4) + ((self.batch * self.cols + 3) // 4 * 4)
         rc = int(self._vec_len.sum())
         self.d_sums = torch.zeros(rc, dtype=torch.float64, device=self.device)
         self.d_inv = torch.empty(rc * (2 if self.came else 1), dtype=torch.float32, device=self.device)
@@ -699,10 +706,12 @@ class FactoredPlan:
         for k in range(self.n_tables):
             rows = self.rows if k == 0 else self.full_rows
             t[k]["rows"], t[k]["cols"] = rows, self.cols
+            t[k]["batch_rows"] = np.where(self.batch > 1, self.mat_rows, 0)
+            mat_rows = np.where(self.batch > 1, self.mat_rows, rows)
             t[k]["first_chunk"] = self._running((rows * self.cols + self.chunk - 1) // self.chunk)
-            t[k]["first_tile"] = self._running(((rows + tr - 1) // tr) * ((self.cols + tc - 1) // tc))
+            t[k]["first_tile"] = self._running(self.batch * ((mat_rows + tr - 1) // tr) * ((self.cols + tc - 1) // tc))
             # units of the small-state launch: the quantisation blocks of the row state, then of the column state
-            units = (rows + sb - 1) // sb + (self.cols + sb - 1) // sb
+            units = (rows + sb - 1) // sb + (self.batch * self.cols + sb - 1) // sb
             t[k]["first_small"] = self._running(units)
             if k == self.n_tables - 1:
                 self.small_units = int(units.sum())

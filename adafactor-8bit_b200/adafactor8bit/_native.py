@@ -81,9 +81,9 @@ FACTORED_TENSOR = np.dtype([
     ("rows", np.int64), ("cols", np.int64), ("first_chunk", np.int64), ("first_tile", np.int64),
     ("decay", np.float32), ("alpha", np.float32), ("v_w", np.float32), ("m_w", np.float32),
     ("c_w", np.float32), ("eps1", np.float32), ("eps_came", np.float32), ("first_small", np.int32),
-    ("sr_base", np.uint64), ("param_copy", _P),
+    ("sr_base", np.uint64), ("param_copy", _P), ("batch_rows", np.int64),
 ], align=True)
-assert FACTORED_TENSOR.itemsize == 328
+assert FACTORED_TENSOR.itemsize == 336
 
 SCALE_TENSOR = np.dtype([
     ("param", _P), ("numel", np.int64), ("first_chunk", np.int64),

@@ -822,10 +822,8 @@ class Adafactor8Bit(Optimizer):
             else:
                 m_fmt, m_block = None, 0
             if g.dim() >= 2 and factored:
-                if g.dim() != 2:
-                    raise NotImplementedError("factored tensors with more than two dimensions are not available in this build")
                 came = group.get("beta3") is not None and group.get("beta1") is not None
-                key = (p.device, g.dtype, m_fmt, m_block, came, p.dtype)
+                key = (p.device, g.dtype, m_fmt, m_block, came, p.dtype, g.dim() > 2)    # batches of matrices: a plan of their own
                 factored_items.setdefault(key, []).append(ent)
                 continue
             v_fmt = st.get("v_quant_type", "al8") if quant else "fp32"
@@ -1015,7 +1013,7 @@ class Adafactor8Bit(Optimizer):
             scale["bc"][i], scale["bc_mode"][i] = sc["bc_div"], 2
 
     def _run_factored(self, gi, group, key, items):
-        device, gdtype, m_fmt, m_block, came, pdtype = key
+        device, gdtype, m_fmt, m_block, came, pdtype = key[:6]
         sr = bool(group.get("stochastic_round_writeback", False)) and pdtype in (torch.bfloat16, torch.float16)
         ids = tuple(id(p) for p, _, _ in items)
         pkey = (gi, "factored", key, bool(group["maximize"]), sr)

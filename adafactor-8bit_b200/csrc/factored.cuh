@@ -65,6 +65,19 @@ __device__ __forceinline__ int find_factored_chunk(const af8_factored_tensor *t,
     return lo;
 }
 
+// batches of matrices (batch_rows > 0): number of matrices, rows of one, and the stat tiles of one
+__host__ __device__ __forceinline__ int64_t fact_mat_rows(const af8_factored_tensor &t) { return t.batch_rows > 0 ? t.batch_rows : t.rows; }
+__host__ __device__ __forceinline__ int64_t fact_batch(const af8_factored_tensor &t) { return t.batch_rows > 0 ? t.rows / t.batch_rows : 1; }
+__host__ __device__ __forceinline__ int64_t fact_tiles(const af8_factored_tensor &t)
+{
+    return fact_batch(t) * ((fact_mat_rows(t) + FSTAT_ROWS - 1) / FSTAT_ROWS) * ((t.cols + FSTAT_COLS - 1) / FSTAT_COLS);
+}
+// first entry of the column arrays for the matrix that holds row `row`
+__device__ __forceinline__ int64_t fact_col_base(const af8_factored_tensor &t, int64_t row)
+{
+    return t.batch_rows > 0 ? (row / t.batch_rows) * t.cols : 0;
+}
+
 __device__ __forceinline__ float load_grad_any(const void *g, int dtype, int64_t i)
 {
     if (dtype == AF8_F32) return static_cast<const float *>(g)[i];
@@ -182,11 +195,16 @@ factored_stats_kernel(const FactoredLaunch L)
             reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
         s_col[tid] = 0.0;
         __syncthreads();
-        const int64_t R = sT.rows, C = sT.cols;
+        const int64_t C = sT.cols;
         const int64_t ntc = (C + FSTAT_COLS - 1) / FSTAT_COLS;
+        const int64_t mr = fact_mat_rows(sT);                              // a tile lies inside one matrix of a batch
+        const int64_t tpm = ((mr + FSTAT_ROWS - 1) / FSTAT_ROWS) * ntc;
         const int64_t local = id - sT.first_tile;
-        const int64_t r0 = (local / ntc) * FSTAT_ROWS;
-        const int64_t c0 = (local % ntc) * FSTAT_COLS;
+        const int64_t mat = local / tpm, lt = local - mat * tpm;
+        const int64_t r0 = mat * mr + (lt / ntc) * FSTAT_ROWS;
+        const int64_t R = (mat + 1) * mr;                                  // end of the matrix's rows
+        const int64_t c0 = (lt % ntc) * FSTAT_COLS;
+        const int64_t cb = sT.batch_rows > 0 ? mat * C : 0;               // the matrix's part of the column arrays
         float pre_div = 1.0f;
         if (L.mode == AF8_FSTAT_RESIDUAL) pre_div = L.dyn[t].pre_div;
 
@@ -196,7 +214,7 @@ factored_stats_kernel(const FactoredLaunch L)
         for (int k = 0; k < FSTAT_COLS / 32; ++k) {
             cacc[k] = 0.0;
             const int64_t c = c0 + lane + 32 * k;
-            icv[k] = (L.mode == AF8_FSTAT_RESIDUAL && c < C) ? sT.inv_col[c] : 0.0f;
+            icv[k] = (L.mode == AF8_FSTAT_RESIDUAL && c < C) ? sT.inv_col[cb + c] : 0.0f;
         }
         for (int rr = warp; rr < FSTAT_ROWS; rr += 8) {
             const int64_t r = r0 + rr;
@@ -231,7 +249,7 @@ factored_stats_kernel(const FactoredLaunch L)
 #pragma unroll
         for (int k = 0; k < FSTAT_COLS / 32; ++k) atomicAdd(&s_col[lane + 32 * k], cacc[k]);
         __syncthreads();
-        if (c0 + tid < C) atomicAdd(sT.col_sum + c0 + tid, s_col[tid]);
+        if (c0 + tid < C) atomicAdd(sT.col_sum + cb + c0 + tid, s_col[tid]);
     }
 }
 
@@ -325,11 +343,13 @@ factored_small_kernel(const af8_factored_tensor *tensors, int n_tensors, int con
     const float w = conf ? T.c_w : T.v_w;
     const float eps_add = conf ? 0.0f : T.eps1;                 // optimizer.py:2222-2223 vs 933-934
     double part;
+    // a batch of matrices: the states are flat over the batch (their blocks run across the matrices); a
+    // column value is the mean over the rows of its own matrix
     if (is_row)
         part = small_state_block(conf ? T.conf_row : T.row_var, T.row_sum, (double)T.cols, T.rows, b, eps_add, w, floor_log,
                                  conf ? T.inv_row_conf : T.inv_row, s_l, s_red);
     else
-        part = small_state_block(conf ? T.conf_col : T.col_var, T.col_sum, (double)T.rows, T.cols, b, eps_add, w, floor_log,
+        part = small_state_block(conf ? T.conf_col : T.col_var, T.col_sum, (double)fact_mat_rows(T), fact_batch(T) * T.cols, b, eps_add, w, floor_log,
                                  conf ? T.inv_col_conf : T.inv_col, s_l, s_red);
     if (!is_row) return;
     // the block's share of the mean of the row state goes where its first row sum was
@@ -355,6 +375,30 @@ factored_inv_kernel(const af8_factored_tensor *tensors, int conf)
     float *inv_r = conf ? T.inv_row_conf : T.inv_row;
     float *inv_c = conf ? T.inv_col_conf : T.inv_col;
     const int block = (conf ? T.conf_row : T.row_var).block;
+    const int64_t stride = (int64_t)blockDim.x * gridDim.y;
+    const int64_t first = (int64_t)blockIdx.y * blockDim.x + tid;
+    if (T.batch_rows > 0) {
+        // a batch: the mean of each matrix's own row values (row_var.mean(dim=-2)), matrices dealt out to the
+        // slices; the values are read before any of them is overwritten by this CTA's own threads
+        __shared__ double s_red[8];
+        const int64_t mr = T.batch_rows, nb = T.rows / mr;
+        for (int64_t m = blockIdx.y; m < nb; m += gridDim.y) {
+            double part = 0.0;
+            for (int64_t i = tid; i < mr; i += blockDim.x) part += (double)inv_r[m * mr + i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            __syncthreads();
+            if ((tid & 31) == 0) s_red[tid >> 5] = part;
+            __syncthreads();
+            double s = 0.0;
+            for (int k = 0; k < 8; ++k) s += s_red[k];
+            float rm = __double2float_rn(s / (double)mr);
+            if (rm < T.eps1) rm = T.eps1;
+            for (int64_t i = tid; i < mr; i += blockDim.x) inv_r[m * mr + i] = rsqrt_t(__fdiv_rn(inv_r[m * mr + i], rm));
+        }
+        for (int64_t j = first; j < nb * T.cols; j += stride) inv_c[j] = rsqrt_t(inv_c[j]);
+        return;
+    }
     if (tid == 0) {
         double s = 0.0;
         for (int64_t e = 0; e < T.rows; e += block) s += T.row_sum[e];      // fixed order
@@ -364,8 +408,6 @@ factored_inv_kernel(const af8_factored_tensor *tensors, int conf)
     }
     __syncthreads();
     const float rm = s_rm;
-    const int64_t stride = (int64_t)blockDim.x * gridDim.y;
-    const int64_t first = (int64_t)blockIdx.y * blockDim.x + tid;
     for (int64_t i = first; i < T.rows; i += stride) inv_r[i] = rsqrt_t(__fdiv_rn(inv_r[i], rm));
     for (int64_t j = first; j < T.cols; j += stride) inv_c[j] = rsqrt_t(inv_c[j]);
 }
@@ -412,7 +454,8 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
                 const int64_t flat = base + i;
                 float g = load_grad_any(sT.grad, L.grad_dtype, flat);
                 if (L.negate_grad) g = -g;
-                const float ir = sT.inv_row[row], ic = sT.inv_col[col];
+                const int64_t cb = fact_col_base(sT, row);                         // (a batch of matrices: that matrix's columns)
+                const float ir = sT.inv_row[row], ic = sT.inv_col[cb + col];
                 float u;
                 if (L.came) {
                     const float uc = u_clipped(g, ir, ic, pre_div);                  // optimizer.py:929
@@ -420,7 +463,7 @@ factored_update_kernel(const FactoredLaunch L, int chunk)
                         u = uc;
                     } else {
                         mj = lerp_t(m_old_at(sT, L.m_fmt, L.m_block, flat), uc, sT.m_w);   // optimizer.py:930
-                        u = __fmul_rn(__fmul_rn(mj, sT.inv_row_conf[row]), sT.inv_col_conf[col]);   // optimizer.py:952
+                        u = __fmul_rn(__fmul_rn(mj, sT.inv_row_conf[row]), sT.inv_col_conf[cb + col]);   // optimizer.py:952
                     }
                 } else if (has_m) {
                     mj = lerp_t(m_old_at(sT, L.m_fmt, L.m_block, flat), g, sT.m_w);        // optimizer.py:959
@@ -581,11 +624,11 @@ __device__ __forceinline__ void m_old8(const af8_factored_tensor &T, int m_fmt, 
 // Rows r0 + warp + 8k of the tile, NB at a time so that NB independent 128-bit loads per lane
 // are in flight.  Column partials go to a per-warp shared array (no shared-memory atomics).
 template <typename GradT, int NB, bool PREFETCH, bool RESIDUAL>
-__device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t c,
+__device__ __forceinline__ void stats_rows(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t row_end, int64_t c,
                                            bool col_ok, float pre_div, const float (&ic)[8], double (&cacc)[8])
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t R = sT.rows, C = sT.cols;
+    const int64_t R = row_end, C = sT.cols;          // row_end: end of the tile's matrix (the tensor's rows unless it is a batch)
     // PREFETCH: the loads of the next NB rows are issued before the current ones are processed
     GradRaw8<GradT> cur[NB], nxt[NB];
     auto fetch = [&](GradRaw8<GradT> (&dst)[NB], int k0) {
@@ -691,14 +734,14 @@ template <typename GradT, bool RESIDUAL> __host__ __device__ constexpr int sring
 template <typename GradT, bool RESIDUAL> __host__ __device__ constexpr size_t sring_smem_bytes() { return (size_t)8 * sring_stages<GradT>() * sring_stage_bytes<GradT, RESIDUAL>(); }
 
 template <typename GradT, int NB, bool RESIDUAL>
-__device__ __forceinline__ bool stats_rows_ring(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t c0,
+__device__ __forceinline__ bool stats_rows_ring(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t row_end, int64_t c0,
                                                 float pre_div, const float (&ic)[8], double (&cacc)[8],
                                                 unsigned char *ring, uint64_t *full, uint32_t &cons)
 {
     constexpr int GB = sizeof_grad<GradT>(), NS = sring_stages<GradT>(), STAGE = sring_stage_bytes<GradT, RESIDUAL>();
     static_assert(NS % NB == 0, "a ring holds whole groups of rows");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t R = sT.rows, C = sT.cols;
+    const int64_t R = row_end, C = sT.cols;
     const int64_t c = c0 + lane * 8;
     const int64_t r_end = min(R, r0 + (int64_t)FSTAT_ROWS);
     const int nrows = r0 + warp < r_end ? (int)((r_end - (r0 + warp) + 7) / 8) : 0;       // rows r0 + warp + 8 k of this warp
@@ -855,8 +898,9 @@ factored_stats_vec_kernel(const FactoredLaunch L, const int use_ring)
         }
         const int64_t C = sT.cols;
         const int64_t ntc = (C + FSTAT_COLS - 1) / FSTAT_COLS;
-        const int64_t local = id - sT.first_tile;
+        const int64_t local = id - sT.first_tile;                  // (batches of matrices take the general kernel)
         const int64_t r0 = (local / ntc) * FSTAT_ROWS;
+        const int64_t row_end = sT.rows;
         const int64_t c0 = (local % ntc) * FSTAT_COLS;
         const int64_t c = c0 + lane * 8;                           // this lane's 8 columns
         const bool col_ok = c < C;                                 // C % 8 == 0: all 8 or none
@@ -877,13 +921,13 @@ factored_stats_vec_kernel(const FactoredLaunch L, const int use_ring)
         const bool ring_ok = RESIDUAL && use_ring && (C % FSTAT_COLS) == 0 && L.m_fmt == AF8_M_UF8;
         if (ring_ok) {
             unsigned char *ring = sr_smem + (size_t)warp * sring_stages<GradT>() * sring_stage_bytes<GradT, RESIDUAL>();
-            if (!stats_rows_ring<GradT, RESIDUAL ? AF8_FSTAT_RES_NB : 4, RESIDUAL>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)) {
+            if (!stats_rows_ring<GradT, RESIDUAL ? AF8_FSTAT_RES_NB : 4, RESIDUAL>(L, sT, r0, row_end, c0, pre_div, ic, cacc, ring, s_full[warp], cons)) {
                 atomicExch(&g_device_error, DEVERR_SRING_TIMEOUT);
                 return;                          // (the whole warp; the others finish their rows and leave at the next barrier)
             }
         }
-        else if (!RESIDUAL) stats_rows<GradT, 4, true, false>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
-        else stats_rows<GradT, AF8_FSTAT_RES_NB, AF8_FSTAT_RES_PREFETCH, true>(L, sT, r0, c, col_ok, pre_div, ic, cacc);
+        else if (!RESIDUAL) stats_rows<GradT, 4, true, false>(L, sT, r0, row_end, c, col_ok, pre_div, ic, cacc);
+        else stats_rows<GradT, AF8_FSTAT_RES_NB, AF8_FSTAT_RES_PREFETCH, true>(L, sT, r0, row_end, c, col_ok, pre_div, ic, cacc);
 #pragma unroll
         for (int j = 0; j < 8; ++j) s_col[warp][j * 32 + lane] = cacc[j];
         __syncthreads();
@@ -1398,12 +1442,16 @@ inline int validate_factored(const af8_factored_cfg &c, const af8_factored_tenso
         if (t.first_chunk != next_chunk) return fail(AF8_ERR_INVALID, "factored tensor %d: first_chunk %lld, expected %lld", i, (long long)t.first_chunk, (long long)next_chunk);
         if (t.first_tile != next_tile) return fail(AF8_ERR_INVALID, "factored tensor %d: first_tile %lld, expected %lld", i, (long long)t.first_tile, (long long)next_tile);
         next_chunk += (t.rows * t.cols + chunk - 1) / chunk;
-        next_tile += ((t.rows + FSTAT_ROWS - 1) / FSTAT_ROWS) * ((t.cols + FSTAT_COLS - 1) / FSTAT_COLS);
+        if (t.batch_rows < 0 || (t.batch_rows > 0 && t.rows % t.batch_rows != 0))
+            return fail(AF8_ERR_INVALID, "factored tensor %d: batch_rows %lld does not divide rows %lld", i, (long long)t.batch_rows, (long long)t.rows);
+        if (t.batch_rows > 0 && c.aligned8)
+            return fail(AF8_ERR_INVALID, "factored tensor %d: a batch of matrices takes the general kernels (cfg.aligned8 = 0)", i);
+        next_tile += fact_tiles(t);
         const af8_small_state *ss[4] = {&t.row_var, &t.col_var, &t.conf_row, &t.conf_col};
         const int sb = t.row_var.block;
         if (sb <= 0) return fail(AF8_ERR_INVALID, "factored tensor %d: small-state block must be positive", i);
         if (t.first_small != next_small) return fail(AF8_ERR_INVALID, "factored tensor %d: first_small %d, expected %lld", i, t.first_small, (long long)next_small);
-        next_small += (t.rows + sb - 1) / sb + (t.cols + sb - 1) / sb;
+        next_small += (t.rows + sb - 1) / sb + (fact_batch(t) * t.cols + sb - 1) / sb;
         if (next_small > 0x7fffffff) return fail(AF8_ERR_UNSUPPORTED, "factored table: too many small-state blocks");
         for (int k = 0; k < (c.came ? 4 : 2); ++k) {
             const af8_small_state &s = *ss[k];
@@ -1482,14 +1530,14 @@ extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factore
     for (int i = 0; i < n_tensors; ++i) {
         const af8_factored_tensor &t = host_tensors[i];
         char *const ptr[2] = {reinterpret_cast<char *>(t.row_sum), reinterpret_cast<char *>(t.col_sum)};
-        const size_t len[2] = {sizeof(double) * (size_t)t.rows, sizeof(double) * (size_t)t.cols};
+        const size_t len[2] = {sizeof(double) * (size_t)t.rows, sizeof(double) * (size_t)(fact_batch(t) * t.cols)};
         for (int k = 0; k < 2; ++k) {
             if (ptr[k] == run_end) { run_end += len[k]; continue; }
             if (run_end != run_begin) AF8_CUDA_TRY(cudaMemsetAsync(run_begin, 0, (size_t)(run_end - run_begin), st));
             run_begin = ptr[k];
             run_end = ptr[k] + len[k];
         }
-        tiles += ((t.rows + FSTAT_ROWS - 1) / FSTAT_ROWS) * ((t.cols + FSTAT_COLS - 1) / FSTAT_COLS);
+        tiles += fact_tiles(t);
     }
     if (run_end != run_begin) AF8_CUDA_TRY(cudaMemsetAsync(run_begin, 0, (size_t)(run_end - run_begin), st));
     FactoredLaunch L = make_factored_launch(*cfg, dev_tensors, n_tensors, tiles, dyn, nullptr);

@@ -292,7 +292,12 @@ typedef struct af8_small_state {
     int32_t block;      /* AL block size of this state */
 } af8_small_state;
 
-/* One 2-D tensor (rows x cols, row-major) of a factored launch. */
+/* One tensor of a factored launch: a rows x cols matrix (row-major) or, with batch_rows > 0, a batch of
+ * rows / batch_rows matrices of batch_rows x cols one after another (a tensor of more than two dimensions,
+ * factored over its last two: optimizer.py:2203-2207).  For a batch the row arrays (row_sum, inv_row*, the row
+ * states) still hold `rows` values, the column arrays (col_sum, inv_col*, the column states) hold
+ * (rows / batch_rows) * cols values, matrix after matrix, and the mean that normalises the row factor is
+ * taken per matrix.  Batches run through the general kernels: launch them with cfg.aligned8 = 0. */
 typedef struct af8_factored_tensor {
     void *param;                /* rows*cols elements of cfg.param_dtype */
     const void *grad;           /* fp32 or bf16 */
@@ -309,7 +314,8 @@ typedef struct af8_factored_tensor {
     af8_small_state conf_row, conf_col;    /* CAME confidence states */
     int64_t rows, cols;
     int64_t first_chunk;        /* running sum of ceil(rows*cols / chunk) (update passes) */
-    int64_t first_tile;         /* running sum of stat tiles (af8_factored_stats) */
+    int64_t first_tile;         /* running sum of stat tiles (af8_factored_stats): per matrix
+                                   ceil(its rows / af8_factored_tile_rows()) * ceil(cols / af8_factored_tile_cols()) */
     float decay;                /* 1 - wd_mult*wd, 1.0 without weight decay */
     float alpha;
     float v_w;                  /* second-moment EMA weight beta_val */
@@ -317,11 +323,12 @@ typedef struct af8_factored_tensor {
     float c_w;                  /* float(1 - beta3) */
     float eps1;
     float eps_came;
-    int32_t first_small;        /* running sum of ceil(rows / B) + ceil(cols / B), B = row_var.block: this tensor's
-                                   first unit in af8_factored_small (its row blocks, then its column blocks) */
+    int32_t first_small;        /* running sum of ceil(rows / B) + ceil(column values / B), B = row_var.block: this
+                                   tensor's first unit in af8_factored_small (its row blocks, then its column blocks) */
     uint64_t sr_base;           /* stochastic rounding counter origin, as af8_fullrank_tensor.sr_base;
                                    element r*cols + c draws from counter sr_base + r*cols + c */
     void *param_copy;           /* optional bf16 copy of the updated fp32 parameter, as af8_fullrank_tensor.param_copy */
+    int64_t batch_rows;         /* 0: one matrix; else the rows of one matrix of the batch (divides rows) */
 } af8_factored_tensor;
 
 enum {

@@ -299,15 +299,14 @@ def init_state(shape, hp):
         return st
     if factored:
         R, C = shape[-2], shape[-1]
-        batch = numel // (R * C)
-        assert batch == 1, "oracle covers 2-D factored tensors"
-        _init_al(st, "row_var", R, hp["block_size"], v_fmt)
-        _init_al(st, "col_var", C, hp["block_size"], v_fmt)
+        batch = numel // (R * C)           # more than two dimensions: a batch of matrices (optimizer.py:1750-1760)
+        _init_al(st, "row_var", batch * R, hp["block_size"], v_fmt)
+        _init_al(st, "col_var", batch * C, hp["block_size"], v_fmt)
         if hp["beta1"] is not None:
             _init_m(st, numel, hp["m_block_size"], m_fmt)
         if hp["beta3"] is not None:
-            _init_al(st, "conf_row", R, hp["block_size"], c_fmt)
-            _init_al(st, "conf_col", C, hp["block_size"], c_fmt)
+            _init_al(st, "conf_row", batch * R, hp["block_size"], c_fmt)
+            _init_al(st, "conf_col", batch * C, hp["block_size"], c_fmt)
     else:
         _init_al(st, "variance", numel, hp["block_size"], v_fmt)
         if hp["beta1"] is not None:
@@ -532,8 +531,9 @@ def _small(state, prefix, n, fmt):
 
 
 def factored_step(p, g, state, hp, sc=None):
-    """Factored branch of _update_param_8bit (optimizer.py:2202-2552, pure route)."""
-    assert p.dtype == f32 and p.ndim == 2 and p.flags.c_contiguous
+    """Factored branch of _update_param_8bit (optimizer.py:2202-2552, pure route); a tensor of more
+    than two dimensions is a batch of matrices over its last two."""
+    assert p.dtype == f32 and p.ndim >= 2 and p.flags.c_contiguous
     lib_ = lib()
     if not hasattr(lib_, "_factored_ready"):
         lib_.af8o_factored_step.argtypes = [ctypes.POINTER(FactoredCfg), c_p, c_p] + \
@@ -542,8 +542,9 @@ def factored_step(p, g, state, hp, sc=None):
         lib_._factored_ready = True
     if sc is None:
         sc = prologue(p, state, hp)
-    R, C = p.shape
-    n = R * C
+    R, C = p.shape[-2:]
+    n = p.size
+    B = n // (R * C)
     g, gdt = _grad_args(g)
     quant = state["is_quantized"]
     vqt = state["v_quant_type"] if quant else "fp32"
@@ -573,14 +574,16 @@ def factored_step(p, g, state, hp, sc=None):
     cfg.clip_div = float(f32(math.sqrt(n) * hp["d"]))
     cfg.fira_margin1 = float(f32(1.0 + hp["fira_margin"]))
     cfg.v_floor = -126.0
-    row = _small(state, "row_var", R, vqt)
-    col = _small(state, "col_var", C, vqt)
-    crow = _small(state, "conf_row", R, cqt) if came else SmallState()
-    ccol = _small(state, "conf_col", C, cqt) if came else SmallState()
+    row = _small(state, "row_var", B * R, vqt)
+    col = _small(state, "col_var", B * C, vqt)
+    crow = _small(state, "conf_row", B * R, cqt) if came else SmallState()
+    ccol = _small(state, "conf_col", B * C, cqt) if came else SmallState()
     has_prev = c_i(1 if "fira_prev_norm" in state else 0)
     prev = c_f(float(state.get("fira_prev_norm", 0.0)))
     norm = c_f(-1.0)
     lag = lag_mode(state, hp, bool(hp["lag_norm"]) and (cfg.fira or hp["d"] > 0) and not came)
+    lib_.af8o_factored_set_batch.argtypes = [c_l]
+    lib_.af8o_factored_set_batch(B)
     with param_format(hp, state, sc["step"]), lag:
         rc = lib_.af8o_factored_step(
             ctypes.byref(cfg), _ptr(p), _ptr(g.reshape(-1)), ctypes.byref(row), ctypes.byref(col),

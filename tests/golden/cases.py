@@ -256,6 +256,16 @@ CASES["apollo_scale_param_tensor"] = dict(shapes=[(96, 64), (32, 160)], steps=4,
                                                   relative_step=True, apollo_scale_type="tensor"))
 APOLLO_RULE_CASES = ["apollo_factorize", "apollo_factorize_came", "apollo_came", "apollo_came_fp32",
                      "apollo_factorize_nomom", "apollo_scale_param", "apollo_scale_param_tensor"]
+# factored tensors of more than two dimensions: a batch of matrices over the last two dimensions, with row / column
+# states whose quantisation blocks run across the batch entries (3 x 40 x 72: 120 row values, 216 column values in
+# blocks of 128) -- Adafactor without and CAME with momentum
+CASES["adafactor_3d"] = dict(shapes=[(3, 40, 72), (2, 2, 24, 16)], steps=5, seed=60, grad=_G_BF16,
+                             hp=dict(lr=1e-3, block_size=128, min_8bit_size=64, relative_step=False, scale_parameter=True,
+                                     weight_decay=0.01))
+CASES["came_3d"] = dict(shapes=[(3, 40, 72), (2, 2, 24, 16)], steps=5, seed=61, grad=_G_BF16,
+                        hp=dict(_CAME, lr=1e-4, m_quant_type="uf8", v_quant_type="al8", block_size=128, m_block_size=64,
+                                min_8bit_size=64, enable_fira_for_adafactor=True))
+FACTORED_3D_CASES = ["adafactor_3d", "came_3d"]
 MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
 
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]

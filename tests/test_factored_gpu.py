@@ -76,7 +76,7 @@ EXTRA_CASES.update({
 })
 
 
-@pytest.mark.parametrize("name", FACTORED_CASES + sorted(EXTRA_CASES))
+@pytest.mark.parametrize("name", FACTORED_CASES + cases.FACTORED_3D_CASES + sorted(EXTRA_CASES))
 def test_factored_free_running_matches_oracle(name, oracle):
     run = OracleRun(name, EXTRA_CASES.get(name))
     params, opt = make_optimizer(run)
@@ -99,7 +99,7 @@ def test_factored_free_running_matches_oracle(name, oracle):
     assert _native.device_status(torch.cuda.current_stream().cuda_stream) == 0
 
 
-@pytest.mark.parametrize("name", ["adafactor_factored", "adafactor_factored_m"])
+@pytest.mark.parametrize("name", ["adafactor_factored", "adafactor_factored_m"] + cases.FACTORED_3D_CASES)
 def test_factored_matches_reference_golden(name, oracle):
     run = OracleRun(name)
     gold = load_golden(name)
@@ -112,7 +112,10 @@ def test_factored_matches_reference_golden(name, oracle):
     torch.cuda.synchronize()
     for i, p in enumerate(params):
         ref = golden_entries(gold, steps, i)
-        parity.assert_params(p.detach().cpu().numpy(), ref["param"], f"{name} final p{i} vs reference", tol=1e-6)
+        # (CAME with the limiter: torch's float32 norm puts the reference's limiter state 2e-5 off the accurately
+        # summed one, which the parameters then carry)
+        parity.assert_params(p.detach().cpu().numpy(), ref["param"], f"{name} final p{i} vs reference",
+                             tol=5e-5 if name == "came_3d" else 1e-6)
         for key in CODE_KEYS:
             if key in ref:
                 parity.assert_codes(state_np(opt.state[p], key), ref[key], f"{name} final p{i} {key} vs reference",

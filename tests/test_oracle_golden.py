@@ -236,6 +236,36 @@ def test_apollo_variants_against_reference(oracle, name):
             assert parity.rel_l2(st["scaled_grad_norm_prev"], ref["scaled_grad_norm_prev"]) <= 1e-4, what
 
 
+@pytest.mark.parametrize("name", cases.FACTORED_3D_CASES)
+def test_factored_batches_against_reference(oracle, name):
+    """Factored tensors of more than two dimensions (batches of matrices over the last two dimensions,
+    optimizer.py:2203-2253): Adafactor with a parameter-scaled step and CAME with momentum and the limiter,
+    free-running against the reference.  The row / column states are flat over the batch, so their
+    quantisation blocks run across the matrices; codes must agree exactly up to two single steps."""
+    run = OracleRun(name)
+    gold = load_golden(name)
+    assert str(gold["digest"]) == cases.inputs_digest(run.params0, run.grads)
+    for t in range(1, run.case["steps"] + 1):
+        run.step()
+        for i, (p, st) in enumerate(zip(run.params, run.states)):
+            ref = golden_entries(gold, t, i)
+            what = f"{name} step {t} param {i}"
+            parity.assert_params(p, ref["param"], what, tol=2e-5)
+            seen = 0
+            for key, want in ref.items():
+                if key == "param":
+                    continue
+                assert st.get(key) is not None, (what, key)
+                have = np.asarray(st[key]).reshape(-1)
+                seen += 1
+                if have.dtype in (np.uint8, np.uint16):
+                    s = parity.code_stats(have[:want.size], want)
+                    assert s["max"] <= 1 and s["neq"] <= 2, (what, key, s)
+                else:
+                    assert parity.rel_l2(have[:want.size], want) <= 1e-4, (what, key)
+            assert seen >= 6, (what, sorted(ref))
+
+
 @pytest.mark.parametrize("name", cases.APOLLO_RULE_CASES)
 def test_apollo_lowrank_rules_against_reference(oracle, name):
     """APOLLO's other low-rank rules, free-running against the reference: apollo_factorize (fp32 row / column
