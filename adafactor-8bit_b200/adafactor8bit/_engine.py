@@ -973,6 +973,7 @@ class ApolloPlan:
         self.sums = torch.zeros(3 * self.n, dtype=torch.float64, device=dev)
         self.out = torch.zeros(4 * self.n, dtype=torch.float32, device=dev)
         self._low_plans = {}
+        self._plane_version = [None] * self.n
         if rule is not None:          # one work area, sized for the largest tensor (stream order makes its reuse safe)
             shapes = [((r, self.rank) if r >= c else (self.rank, c)) for r, c in zip(self.rows, self.cols)]
             self.low_shapes = shapes
@@ -1033,12 +1034,15 @@ class ApolloPlan:
                                     self.alpha_decay.data_ptr(), 8, 0, 4, stream.cuda_stream), "af8_param_scale")
         self.h_scale.mark(stream)
 
-    def run(self, grads, pts, per_tensor, lowrank_scalars, first_flags, floor_later, stream=None, params=None, scale=None):
+    def run(self, grads, pts, per_tensor, lowrank_scalars, first_flags, floor_later, stream=None, params=None, scale=None,
+            versions=None):
         """per_tensor: list of dicts with the ApolloScalarsIn fields, decay, has_decay and the
         device scalar `fira_prev` (or None).  lowrank_scalars: v_w, m_w, apollo_eps.
         params: this step's 2-D views of the parameters (their storage may have been replaced).
         scale: per-tensor inputs of af8_param_scale when the step size follows the parameters' RMS
-        (scale_parameter=True); alpha and the decay factor then come from the device."""
+        (scale_parameter=True); alpha and the decay factor then come from the device.
+        versions: one hashable per tensor that changes whenever its projection matrix does; while it stays
+        the same the bf16 planes of the matrix are kept in the workspace instead of being rebuilt."""
         stream = stream or torch.cuda.current_stream(self.device)
         if params is not None:
             self.params = list(params)
@@ -1058,6 +1062,9 @@ class ApolloPlan:
             d["workspace"][i] = 0 if EXACT_PROJECTION else self.ws_ptr[i]
             d["workspace_bytes"][i] = 0 if EXACT_PROJECTION else self.ws_bytes[i]
             d["rows"][i], d["cols"][i], d["rank"][i], d["negate"][i] = self.rows[i], self.cols[i], self.rank, self.negate
+            ver = (versions[i], pts[i].data_ptr()) if versions is not None and not EXACT_PROJECTION else None
+            d["planes_valid"][i] = int(ver is not None and self._plane_version[i] == ver)
+            self._plane_version[i] = ver
         h_tasks = self.h_tasks.next()
         N.check(lib.af8_apollo_project_batch(d.ctypes.data, self.n, self.grad_dtype, h_tasks.data_ptr(),
                                              self.d_tasks.data_ptr(), self.t_ptr, self.t_bytes, s), "af8_apollo_project_batch")

@@ -59,7 +59,7 @@ assert LAG_TENSOR.itemsize == 80
 
 APOLLO_PROJ_DESC = np.dtype([(n, np.uint64) for n in ("grad", "pt", "g_low", "chan_g2", "workspace")] +
                             [(n, np.int64) for n in ("workspace_bytes", "rows", "cols", "rank")] +
-                            [("negate", np.int32), ("reserved", np.int32)], align=True)     # af8_apollo_proj_desc, 80 B
+                            [("negate", np.int32), ("planes_valid", np.int32)], align=True)     # af8_apollo_proj_desc, 80 B
 
 APOLLO_FINISH_TENSOR = np.dtype(
     [(n, np.uint64) for n in ("upd", "g_low", "chan_g2", "sf", "sums", "fira_prev", "out")] +

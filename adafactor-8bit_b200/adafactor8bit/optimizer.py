@@ -984,6 +984,8 @@ class Adafactor8Bit(Optimizer):
                    apollo_eps=f32(apollo_eps), c_w=f32(1.0 - beta3) if beta3 is not None else f32(0.0),
                    eps_came=f32(group.get("eps_came", 1e-16)), eps_sq=f32(max(apollo_eps * apollo_eps, _FLOOR)), d=f32(group["d"]))
         floor_later = math.log2(max(apollo_eps * apollo_eps, _FLOOR))                  # optimizer.py:2766-2767
+        # the projection matrix of a tensor changes every apollo_update_proj_gap steps only (optimizer.py:2557-2584)
+        versions = [(st.get("last_proj_step"), st.get("current_proj_seed")) for _, _, st in items]
         scale = None
         if group["scale_parameter"]:                     # alpha_t from the parameters' RMS, on the device (optimizer.py:850-853)
             scale = self._scale_inputs(group, len(items))
@@ -992,7 +994,8 @@ class Adafactor8Bit(Optimizer):
             scale["bc_mode"][:] = 0                      # the bias correction enters the update scale (optimizer.py:3015-3023)
 
         def passes():
-            plan.run(grads, pts, per_tensor, low, first_flags, floor_later, params=[p for p, _, _ in items], scale=scale)
+            plan.run(grads, pts, per_tensor, low, first_flags, floor_later, params=[p for p, _, _ in items], scale=scale,
+                     versions=versions)
             return
             yield                                                                       # (no exchange points)
         return 0, device, passes()

@@ -709,7 +709,9 @@ inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dt
     const bool right = d.rows >= d.cols;
     const int64_t kdim = right ? d.cols : d.rows;
     const int64_t pn = kdim * d.rank;
-    if (umma && right) {                                     // planes transposed to [rank][cols]
+    if (d.planes_valid) {
+        // the planes of this pt are in the workspace already (same layout: it follows from the shape and the path)
+    } else if (umma && right) {                              // planes transposed to [rank][cols]
         dim3 grid((unsigned)((kdim + 31) / 32), (unsigned)((d.rank + 31) / 32));
         apollo_split_transposed_kernel<<<grid, 256, 0, st>>>(d.pt, (int)kdim, (int)d.rank, planes);
     } else {                                                 // Pt is [rank][rows] already in the left case

@@ -151,6 +151,9 @@ DEFAULT_WORKLOAD = "tinyllama_adamw_fira"
 NCU_TRAFFIC_BPP = {
     ("fullrank_fast_apply", "bf16"): (13.72, "profiles/fullrank_fast_apply_tinyllama_4layers.txt"),
     ("fullrank_stat", "bf16"): (4.12, "profiles/fullrank_stat_tinyllama_4layers.txt"),
+    # the factored write pass: without momentum (Adafactor, 10 B/param) and with a UF8 momentum (CAME, 12 B/param)
+    ("factored_apply", "bf16", 10): (9.68, "profiles/factored_update_nomomentum_tinyllama_4layers.txt"),
+    ("factored_apply", "bf16", 12): (11.77, "profiles/factored_kernels_llama2_layer_came.txt"),
 }
 
 
@@ -565,7 +568,9 @@ def run_gpu_arm(args):
         # DRAM bytes per parameter (read + write) of this kernel: a constant from the committed profiler
         # capture on the four-layer case; every block is independent, so traffic scales with the
         # parameter count.  No entry for the kernel: traffic is null and the note says so.
-        entry = NCU_TRAFFIC_BPP.get((dom, wl["grad"])) if (wl.get("param", "f32") == "f32" and copy_dtype is None) else None
+        entry = None
+        if wl.get("param", "f32") == "f32" and copy_dtype is None:
+            entry = NCU_TRAFFIC_BPP.get((dom, wl["grad"])) or NCU_TRAFFIC_BPP.get((dom, wl["grad"], bpp))
         traffic = None if entry is None else entry[0] * units / launches
         traffic_note = ("no profiler capture of this kernel and configuration is committed" if entry is None else
                         f"bytes per launch = {entry[0]} B/param from {entry[1]} x parameters of the launch "

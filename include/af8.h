@@ -467,7 +467,9 @@ typedef struct af8_apollo_proj_desc {
     int64_t workspace_bytes;
     int64_t rows, cols, rank;
     int32_t negate;
-    int32_t reserved;
+    int32_t planes_valid;   /* 1: the workspace still holds the bf16 planes of this same pt from an earlier call
+                               (the projection matrix changes every apollo_update_proj_gap steps only): they are
+                               not rebuilt */
 } af8_apollo_proj_desc;
 AF8_API int32_t af8_apollo_project_task_bytes(void);
 AF8_API int af8_apollo_project_batch(const af8_apollo_proj_desc *descs, int32_t n, int32_t grad_dtype,

@@ -48,6 +48,39 @@ def _pdt(variant):
     return torch.bfloat16 if variant == "bf16_sr" else torch.float32
 
 
+def _plain(x, path="state_dict"):
+    """A checkpoint as plain Python / numpy objects (what travels between the processes of this test);
+    every tensor must already be on the CPU."""
+    if isinstance(x, torch.Tensor):
+        assert x.device.type == "cpu", f"{path} is on {x.device}"
+        a = x.detach().contiguous()
+        return ["tensor", str(a.dtype), tuple(a.shape), a.view(torch.int16).numpy().copy() if a.dtype == torch.bfloat16 else a.numpy().copy()]
+    if isinstance(x, torch.Size):
+        return ["size"] + list(x)
+    if isinstance(x, dict):
+        return {k: _plain(v, f"{path}[{k!r}]") for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return [_plain(v, f"{path}[{i}]") for i, v in enumerate(x)]
+    assert x is None or isinstance(x, (bool, int, float, str)), f"{path} holds a {type(x).__name__}"
+    return x
+
+
+def _same(a, b, path="state_dict"):
+    if isinstance(a, dict):
+        assert isinstance(b, dict) and sorted(a) == sorted(b), (path, sorted(a), sorted(b) if isinstance(b, dict) else b)
+        for k in a:
+            _same(a[k], b[k], f"{path}[{k!r}]")
+    elif isinstance(a, list) and len(a) == 4 and a[0] == "tensor":
+        assert isinstance(b, list) and b[:3] == a[:3], (path, a[:3], b[:3] if isinstance(b, list) else b)
+        assert np.array_equal(a[3], b[3]), path
+    elif isinstance(a, list):
+        assert isinstance(b, list) and len(a) == len(b), path
+        for i, (x, y) in enumerate(zip(a, b)):
+            _same(x, y, f"{path}[{i}]")
+    else:
+        assert a == b, (path, a, b)
+
+
 def _worker(rank, world, port, out, variant):
     sys.path.insert(0, os.path.join(ROOT, "adafactor-8bit_b200"))
     import torch.distributed as dist
@@ -83,7 +116,7 @@ def _worker(rank, world, port, out, variant):
                 out["masters"] = [m.numpy().copy() for m in masters]
         full = opt.full_state_dict(dst=0)          # the merged checkpoint, in the unsharded layout
         if rank == 0:
-            out["full"] = full
+            out["full"] = _plain(full)
     finally:
         dist.destroy_process_group()
 
@@ -120,15 +153,11 @@ def test_two_gpu_sharded_step_is_bit_identical_to_one_gpu(variant):
         for a, p in zip(out["masters"], params):
             assert np.array_equal(a, p.detach().cpu().numpy())
     # the merged checkpoint equals the one-GPU optimizer's, entry by entry
-    full, want = out["full"], opt.state_dict()
+    full = out["full"]
+    want = opt.state_dict()
+    want = _plain({k: ({i: {kk: (vv.cpu() if isinstance(vv, torch.Tensor) else vv) for kk, vv in st.items()} for i, st in v.items()}
+                       if k == "state" else v) for k, v in want.items()})
     assert sorted(full["state"]) == sorted(want["state"])
     assert full["_sr_seed_counter"] == want["_sr_seed_counter"]
     assert [g["params"] for g in full["param_groups"]] == [g["params"] for g in want["param_groups"]]
-    for idx, st in want["state"].items():
-        got = full["state"][idx]
-        assert sorted(got) == sorted(st), (idx, sorted(got), sorted(st))
-        for k, v in st.items():
-            if isinstance(v, torch.Tensor):
-                assert torch.equal(got[k], v.cpu()), (idx, k)
-            else:
-                assert got[k] == v, (idx, k, got[k], v)
+    _same(want["state"], full["state"], "state")
