@@ -43,6 +43,7 @@ the update kernels write the rounded copy straight into the gather buffer next t
 all-gather then moves 2 bytes per parameter instead of 4.
 """
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -283,6 +284,10 @@ class ShardedAdafactor8Bit:
         if self.flat is None:
             self.flat = torch.zeros(n_cells * cell, dtype=gather_dtype, device=dev)
         self.exchange = "push" if self.peer_flat is not None else "nccl"
+        # order of a rank's peer copies: "shift" (one at a time, to rank + 1, rank + 2, ...) or "concurrent" (one stream per peer)
+        self.push_order = os.environ.get("AF8_PUSH_ORDER", "shift" if self.world > 2 else "concurrent")
+        if self.push_order not in ("shift", "concurrent"):
+            raise ValueError("AF8_PUSH_ORDER must be 'shift' or 'concurrent'")
         self.master = (torch.zeros(self.parts * cell, dtype=torch.float32, device=dev) if compute_dtype is not None else None)
         owned_numel = 0
         local = []                       # (tensor, lo, hi, part, piece parameter)
@@ -487,13 +492,24 @@ class ShardedAdafactor8Bit:
         ev = torch.cuda.Event()
         ev.record(cur)
         mine = self.flat[a:a + self.cell]
-        for r in range(self.world):
-            if r == self.rank:
-                continue
-            st = self._push_streams[r]
+        if self.push_order == "shift":
+            # one copy at a time, to rank + 1, rank + 2, ...: while the ranks move in step every rank sends to one
+            # peer and receives from one, each pair at the full rate of a single peer copy (several copies running
+            # at once from one GPU were measured at half that in total on 4 GPUs)
+            st = self._push_streams[0]
             with torch.cuda.stream(st):
                 st.wait_event(ev)
-                self.peer_flat[r][a:a + self.cell].copy_(mine, non_blocking=True)     # a copy-engine transfer over NVLink
+                for j in range(1, self.world):
+                    r = (self.rank + j) % self.world
+                    self.peer_flat[r][a:a + self.cell].copy_(mine, non_blocking=True)     # a copy-engine transfer over NVLink
+        else:
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                st = self._push_streams[r]
+                with torch.cuda.stream(st):
+                    st.wait_event(ev)
+                    self.peer_flat[r][a:a + self.cell].copy_(mine, non_blocking=True)
         self._pushed = True
 
     def _gather_fence(self):
