@@ -239,7 +239,9 @@ class ShardedAdafactor8Bit:
                  for i in range(len(all_params))]
         total = sum(_pad(n, UNIT) for n in numels)
         if parts is None:
-            parts = max(1, min(4, total // max(1, self.world) // (32 << 20))) if self.world > 1 else 1
+            # a part should keep a GPU busy for longer than its launches take to issue (about half a millisecond of
+            # host time per part): 256 M parameters per rank and part, at most 4 parts
+            parts = max(1, min(4, total // max(1, self.world) // (256 << 20))) if self.world > 1 else 1
         self.parts = parts = max(1, int(parts))
         n_cells = self.parts * self.world
         self.cell, offsets = plan_layout([(numels[i], rules[i][0], rules[i][1]) for i in range(len(numels))], n_cells)
@@ -384,6 +386,8 @@ class ShardedAdafactor8Bit:
         self.gather_stream = None
         self._push_streams, self._pushed = None, False
         self._fence = torch.zeros(1, dtype=torch.float32, device=dev) if self.peer_flat is not None else None
+        self._start = torch.zeros(1, dtype=torch.float32, device=dev) if self.peer_flat is not None else None
+        self.push_sync = self.push_order == "shift" and os.environ.get("AF8_PUSH_SYNC", "1") != "0"
         self._pipelined = self._in_step = False
         self.gather_log = []          # units in the order this rank gathered them during the last step
 
@@ -499,6 +503,12 @@ class ShardedAdafactor8Bit:
             st = self._push_streams[0]
             with torch.cuda.stream(st):
                 st.wait_event(ev)
+                if self.push_sync:
+                    # the shifted order only avoids two senders at one receiver while the ranks move in step; ranks
+                    # whose parts take different times (whole tensors of unequal cost) drift apart, and a drifted
+                    # sender halves the rate of the receiver it shares.  A tiny all-reduce lines the ranks up
+                    # before every unit; every rank issues it at the same place of its sequence of collectives.
+                    dist.all_reduce(self._start, group=self.group)
                 for j in range(1, self.world):
                     r = (self.rank + j) % self.world
                     self.peer_flat[r][a:a + self.cell].copy_(mine, non_blocking=True)     # a copy-engine transfer over NVLink
