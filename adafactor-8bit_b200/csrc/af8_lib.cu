@@ -3,7 +3,6 @@
 //   nvcc -gencode arch=compute_100a,code=sm_100a -fmad=false ... af8_lib.cu
 #include "common.cuh"
 #include "fullrank_fast.cuh"
-#include "fullrank_warp.cuh"
 #include "fullrank_generic.cuh"
 #include "fullrank_api.cuh"
 #include "codec.cuh"

@@ -217,40 +217,10 @@ inline int dispatch_generic(int mode, const FullrankLaunch &L, const GenericCfg 
     }
 }
 
-template <typename GradT, int MODE>
-inline int launch_warp(const FullrankLaunch &L, cudaStream_t st)
-{
-    using Ring = FwRing<GradT>;
-    auto kernel = fullrank_warp_kernel<GradT, MODE>;
-    AF8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring::SMEM_BYTES));
-    AF8_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                      (int)cudaSharedmemCarveoutMaxShared));
-    int grid = 0;
-    int rc = persistent_grid(kernel, FW_THREADS, Ring::SMEM_BYTES, (L.total_blocks + FW_WARPS - 1) / FW_WARPS, &grid);
-    if (rc) return rc;
-    kernel<<<grid, FW_THREADS, Ring::SMEM_BYTES, st>>>(L);
-    AF8_CUDA_TRY(cudaGetLastError());
-    return AF8_OK;
-}
-
-// fp32 parameters: the update passes with one warp per V block (fullrank_warp.cuh) unless AF8_FULLRANK_WARP=0
-inline bool use_warp_kernel()
-{
-    static const bool on = []() { const char *e = getenv("AF8_FULLRANK_WARP"); return e ? atoi(e) != 0 : AF8_FULLRANK_WARP_DEFAULT != 0; }();
-    return on;
-}
-
 // the specialised kernels (AdamW UF8/AL8 layout): statistic pass, or the update pass for ParamT
 template <typename GradT, typename ParamT>
 inline int dispatch_fast(int mode, const FullrankLaunch &L, cudaStream_t st)
 {
-    if (std::is_same<ParamT, float>::value && mode != AF8_MODE_SUMSQ && use_warp_kernel()) {
-        switch (mode) {
-        case AF8_MODE_NOCLIP: return launch_warp<GradT, AF8_MODE_NOCLIP>(L, st);
-        case AF8_MODE_LAG: return launch_warp<GradT, AF8_MODE_LAG>(L, st);
-        default: return launch_warp<GradT, AF8_MODE_APPLY>(L, st);
-        }
-    }
     switch (mode) {
     case AF8_MODE_NOCLIP: return launch_fast<GradT, ParamT, AF8_MODE_NOCLIP>(L, st);
     case AF8_MODE_SUMSQ: return launch_stat<GradT>(L, st);
