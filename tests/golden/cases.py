@@ -265,7 +265,11 @@ CASES["adafactor_3d"] = dict(shapes=[(3, 40, 72), (2, 2, 24, 16)], steps=5, seed
 CASES["came_3d"] = dict(shapes=[(3, 40, 72), (2, 2, 24, 16)], steps=5, seed=61, grad=_G_BF16,
                         hp=dict(_CAME, lr=1e-4, m_quant_type="uf8", v_quant_type="al8", block_size=128, m_block_size=64,
                                 min_8bit_size=64, enable_fira_for_adafactor=True))
-FACTORED_3D_CASES = ["adafactor_3d", "came_3d"]
+# odd sizes: columns that are no multiple of 8, rows and matrices that straddle the state blocks, a momentum
+CASES["adafactor_3d_odd"] = dict(shapes=[(2, 5, 12), (3, 33, 7)], steps=4, seed=62, grad=_G_CFG0,
+                                 hp=dict(lr=1e-3, beta1=0.9, block_size=128, m_block_size=64, min_8bit_size=16, relative_step=False,
+                                         weight_decay=0.01, d=1.0))
+FACTORED_3D_CASES = ["adafactor_3d", "came_3d", "adafactor_3d_odd"]
 MIGRATION_CASES = ["migrate_quantize_off_on", "migrate_formats", "migrate_came_toggle", "migrate_factored_off"]
 
 LOWP_FULLRANK_CASES = ["adamw_bf16p", "adamw_f16p", "adamw_sr_bf16p", "adamw_sr_f16p"]
