@@ -104,27 +104,44 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
 }
 
 // G[R][C] (bf16) -> G^T[C][R], non-finite entries replaced by zero (optimizer.py:2606).
-// 64 x 64 tiles through shared memory, two elements per thread and access.  R and C even.
+// 64 x 64 tiles.  A thread transposes 2 x 2 blocks in registers (two 32-bit loads from neighbouring
+// rows become the two 32-bit words of neighbouring output rows), so shared memory only moves whole
+// words through two 32 x 33 arrays, without bank conflicts; every global access of a warp is a
+// contiguous run of 128 bytes.  R and C even.
 __global__ void __launch_bounds__(256)
 apollo_transpose_bf16_kernel(const uint16_t *__restrict__ in, int R, int C, uint16_t *__restrict__ out)
 {
-    __shared__ uint16_t tile[64][66];
+    __shared__ uint32_t t0[32][33], t1[32][33];       // [block column][block row]: output rows 2 bc and 2 bc + 1
     const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;     // 32 pairs x 8 rows
-    for (int i = ty; i < 64; i += 8) {
-        const int r = r0 + i, c = c0 + 2 * tx;
-        uint32_t w = 0;
-        if (r < R && c < C) w = __ldg(reinterpret_cast<const uint32_t *>(in + (int64_t)r * C + c));
-        if ((w & 0x7f80u) == 0x7f80u) w &= 0xffff0000u;
-        if ((w & 0x7f800000u) == 0x7f800000u) w &= 0x0000ffffu;
-        tile[i][2 * tx] = (uint16_t)w;
-        tile[i][2 * tx + 1] = (uint16_t)(w >> 16);
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    uint32_t a[4], b[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {                      // block (row ty + 8 k, column tx): rows r, r + 1, columns c, c + 1
+        const int r = r0 + 2 * (ty + 8 * k), c = c0 + 2 * tx;
+        a[k] = b[k] = 0u;
+        if (r < R && c < C) {
+            a[k] = __ldg(reinterpret_cast<const uint32_t *>(in + (int64_t)r * C + c));
+            b[k] = __ldg(reinterpret_cast<const uint32_t *>(in + (int64_t)(r + 1) * C + c));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        uint32_t x = a[k], y = b[k];
+        if ((x & 0x7f80u) == 0x7f80u) x &= 0xffff0000u;
+        if ((x & 0x7f800000u) == 0x7f800000u) x &= 0x0000ffffu;
+        if ((y & 0x7f80u) == 0x7f80u) y &= 0xffff0000u;
+        if ((y & 0x7f800000u) == 0x7f800000u) y &= 0x0000ffffu;
+        t0[tx][ty + 8 * k] = __byte_perm(x, y, 0x5410);          // column c:     (row r, row r + 1)
+        t1[tx][ty + 8 * k] = __byte_perm(x, y, 0x7632);          // column c + 1
     }
     __syncthreads();
-    for (int i = ty; i < 64; i += 8) {
-        const int c = c0 + i, r = r0 + 2 * tx;
-        if (c < C && r < R)
-            *reinterpret_cast<uint32_t *>(out + (int64_t)c * R + r) = (uint32_t)tile[2 * tx][i] | ((uint32_t)tile[2 * tx + 1][i] << 16);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {                      // output rows c, c + 1 of block column ty + 8 k; columns r, r + 1 of block row tx
+        const int c = c0 + 2 * (ty + 8 * k), r = r0 + 2 * tx;
+        if (c < C && r < R) {
+            *reinterpret_cast<uint32_t *>(out + (int64_t)c * R + r) = t0[ty + 8 * k][tx];
+            *reinterpret_cast<uint32_t *>(out + (int64_t)(c + 1) * R + r) = t1[ty + 8 * k][tx];
+        }
     }
 }
 
