@@ -1409,6 +1409,95 @@ factored_apply_ring_kernel(const FactoredLaunch L)
     }
 }
 
+// ---------------------------------------------------------------------------
+// The sum-of-squares pass over u = g * inv_row * inv_col (CAME's first sum, Adafactor without
+// momentum): it only reads the gradient, 2 bytes per parameter, and with one 128-bit load per
+// thread in flight (the kernel above) it was bound by memory latency.  Here a thread takes NE = 16
+// consecutive elements per step of 4096 (8 where the columns are no multiple of 16) and the loads
+// of its next step are issued before the current values are used: four times the bytes in flight.
+// Partial sums as in factored_update_vec_kernel: one binary64 partial per thread over the chunks of
+// a tensor that the CTA processes, reduced once per tensor into the slot of the run's first chunk.
+// ---------------------------------------------------------------------------
+template <typename GradT, int NE>
+__device__ __forceinline__ double sumsq_span(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t e0, int64_t e1)
+{
+    constexpr int NV = NE / 8;                                   // 8-element vectors per thread and step
+    constexpr int64_t STEP = (int64_t)FUPD_THREADS * NE;
+    const int64_t C = sT.cols;
+    double acc = 0.0;
+    int64_t e = e0 + (int64_t)threadIdx.x * NE;
+    if (e >= e1) return acc;
+    int64_t row = e / C, col = e - row * C;
+    GradRaw8<GradT> cur[NV], nxt[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) cur[v].load(sT.grad, e + 8 * v);
+    for (; e < e1; e += STEP) {
+        const bool more = e + STEP < e1;
+        if (more) {
+#pragma unroll
+            for (int v = 0; v < NV; ++v) nxt[v].load(sT.grad, e + STEP + 8 * v);
+        }
+        const float2 ir2 = bc2(__ldg(sT.inv_row + row));
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            float g[8], ic[8];
+            cur[v].unpack(0, g);                                 // (the sign does not matter for the square)
+            load_f8_ro(sT.inv_col + col + 8 * v, ic);
+            float2 a2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const float2 uj = __fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1]));
+                a2 = j == 0 ? __fmul2_rn(uj, uj) : __ffma2_rn(uj, uj, a2);
+            }
+            acc += (double)__fadd_rn(a2.x, a2.y);
+            if (more) cur[v] = nxt[v];
+        }
+        col += STEP;
+        if (col >= C) {
+            if (C >= STEP) { col -= C; ++row; }
+            else { const int64_t q = col / C; row += q; col -= q * C; }
+        }
+    }
+    return acc;
+}
+
+template <typename GradT>
+__global__ void __launch_bounds__(FUPD_THREADS, 4)
+factored_sumsq_wide_kernel(const FactoredLaunch L)
+{
+    __shared__ af8_factored_tensor sT;
+    __shared__ double s_acc2[FUPD_THREADS / 32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int64_t per_cta = (L.total_units + gridDim.x - 1) / gridDim.x;
+    const int64_t id_begin = (int64_t)blockIdx.x * per_cta;
+    const int64_t id_end = min(id_begin + per_cta, L.total_units);
+    int tn = -1;
+    for (int64_t id = id_begin; id < id_end;) {
+        if (tn < 0) tn = find_factored_chunk(L.tensors, L.n_tensors, id);
+        else while (tn + 1 < L.n_tensors && __ldg(&L.tensors[tn + 1].first_chunk) <= id) ++tn;
+        __syncthreads();
+        if (tid < (int)(sizeof(af8_factored_tensor) / 4))
+            reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + tn) + tid);
+        __syncthreads();
+        const int64_t next_first = tn + 1 < L.n_tensors ? __ldg(&L.tensors[tn + 1].first_chunk) : L.total_units;
+        const int64_t run_end = min(id_end, next_first);         // this CTA's chunks of this tensor: id .. run_end - 1
+        const int64_t e0 = (id - sT.first_chunk) * 2048;
+        const int64_t e1 = min((run_end - sT.first_chunk) * 2048, sT.rows * sT.cols);
+        double acc = (sT.cols % 16 == 0) ? sumsq_span<GradT, 16>(L, sT, e0, e1) : sumsq_span<GradT, 8>(L, sT, e0, e1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) s_acc2[warp] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double sum = 0.0;
+            for (int w = 0; w < FUPD_THREADS / 32; ++w) sum += s_acc2[w];
+            L.block_sumsq[id] = sum;
+        }
+        for (int64_t i = id + 1 + tid; i < run_end; i += FUPD_THREADS) L.block_sumsq[i] = 0.0;
+        id = run_end;
+    }
+}
+
 inline int factored_chunk_for(int m_block)
 {
     if (m_block <= 0) return 2048;
@@ -1608,6 +1697,14 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     const bool bf = cfg->grad_dtype == AF8_BF16;
     const bool no_m = cfg->m_fmt == AF8_M_NONE;
     static const bool ring_off = getenv("AF8_NO_FACTORED_RING") != nullptr;
+    static const bool wide_off = getenv("AF8_NO_WIDE_SUMS") != nullptr;
+    if (vec && !apply && !wide_off && cfg->grad_dtype != AF8_F16 && ((cfg->came && cfg->mode == AF8_FUPD_SUMSQ_U) || no_m)) {
+        // the sum only needs the gradient: 16 elements per thread, next step's loads in flight
+        if (bf) factored_sumsq_wide_kernel<bf16_tag><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+        else factored_sumsq_wide_kernel<float><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+        AF8_CUDA_TRY(cudaGetLastError());
+        return AF8_OK;
+    }
     if (vec && cfg->mode == AF8_FUPD_APPLY && cfg->m_fmt == AF8_M_UF8 && cfg->param_dtype == AF8_F32 && !ring_off) {
         // fp32 parameters, UF8 momentum: inputs through per-warp rings of bulk copies
         if (bf) {
