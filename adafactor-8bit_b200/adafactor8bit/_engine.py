@@ -709,7 +709,10 @@ class FactoredPlan:
             t[k]["batch_rows"] = np.where(self.batch > 1, self.mat_rows, 0)
             mat_rows = np.where(self.batch > 1, self.mat_rows, rows)
             t[k]["first_chunk"] = self._running((rows * self.cols + self.chunk - 1) // self.chunk)
-            t[k]["first_tile"] = self._running(self.batch * ((mat_rows + tr - 1) // tr) * ((self.cols + tc - 1) // tc))
+            tiles = self.batch * ((mat_rows + tr - 1) // tr) * ((self.cols + tc - 1) // tc)
+            t[k]["first_tile"] = self._running(tiles)
+            if k == 0:
+                self.cfg.total_tiles = int(tiles.sum())
             # units of the small-state launch: the quantisation blocks of the row state, then of the column state
             units = (rows + sb - 1) // sb + (self.batch * self.cols + sb - 1) // sb
             t[k]["first_small"] = self._running(units)

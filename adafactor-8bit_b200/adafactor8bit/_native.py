@@ -110,7 +110,7 @@ class FactoredCfg(ctypes.Structure):
         ("param_dtype", ctypes.c_int32), ("grad_dtype", ctypes.c_int32), ("m_fmt", ctypes.c_int32),
         ("m_block", ctypes.c_int32), ("came", ctypes.c_int32), ("negate_grad", ctypes.c_int32),
         ("mode", ctypes.c_int32), ("v_floor", ctypes.c_float),
-        ("aligned8", ctypes.c_int32), ("stochastic_round", ctypes.c_int32),
+        ("aligned8", ctypes.c_int32), ("stochastic_round", ctypes.c_int32), ("total_tiles", ctypes.c_int64),
     ]
 
 

@@ -1498,6 +1498,82 @@ factored_sumsq_wide_kernel(const FactoredLaunch L)
     }
 }
 
+// The same sum over the 512 x 256 tiles of the statistic pass: a lane keeps the inverse column factors of
+// its 8 columns in registers while its warp walks the tile's rows (the flat kernel above re-reads them for
+// every element, twice the bytes of the gradient itself through L1), four rows' loads in flight.  A CTA adds
+// its tile's sum to the slot of the tensor's first chunk; the caller clears the slots first.
+template <typename GradT>
+__global__ void __launch_bounds__(256, 4)
+factored_sumsq_tile_kernel(const FactoredLaunch L)
+{
+    constexpr int NB = 4;
+    __shared__ af8_factored_tensor sT;
+    __shared__ double s_acc2[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    int cur_t = -1;
+    for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
+        int t = cur_t;
+        if (t < 0) t = find_factored_tile(L.tensors, L.n_tensors, id);
+        else while (t + 1 < L.n_tensors && __ldg(&L.tensors[t + 1].first_tile) <= id) ++t;
+        __syncthreads();                                           // s_acc2 of the previous tile was read
+        if (t != cur_t) {
+            if (tid < (int)(sizeof(af8_factored_tensor) / 4))
+                reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
+            cur_t = t;
+            __syncthreads();
+        }
+        const int64_t R = sT.rows, C = sT.cols;
+        const int64_t ntc = (C + FSTAT_COLS - 1) / FSTAT_COLS;
+        const int64_t local = id - sT.first_tile;
+        const int64_t r0 = (local / ntc) * FSTAT_ROWS;
+        const int64_t c = (local % ntc) * FSTAT_COLS + lane * 8;   // this lane's 8 columns
+        const bool col_ok = c < C;                                 // C % 8 == 0: all 8 or none
+        float ic[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ic[j] = 0.0f;
+        if (col_ok) load_f8_ro(sT.inv_col + c, ic);
+        double acc = 0.0;
+        GradRaw8<GradT> cur[NB], nxt[NB];
+        auto fetch = [&](GradRaw8<GradT> (&dst)[NB], int k0) {
+#pragma unroll
+            for (int k = 0; k < NB; ++k) {
+                const int64_t r = r0 + warp + 8 * (k0 + k);
+                if (col_ok && r < R && k0 + k < FSTAT_ROWS / 8) dst[k].load(sT.grad, r * C + c);
+                else dst[k].zero();
+            }
+        };
+        fetch(cur, 0);
+        for (int k0 = 0; k0 < FSTAT_ROWS / 8; k0 += NB) {
+            if (r0 + warp + 8 * k0 >= R) break;                    // uniform over the warp
+            fetch(nxt, k0 + NB);
+#pragma unroll
+            for (int k = 0; k < NB; ++k) {
+                const int64_t r = min(r0 + warp + 8 * (int64_t)(k0 + k), R - 1);     // (a row beyond the end carries zeros)
+                const float2 ir2 = bc2(__ldg(sT.inv_row + r));
+                float g[8];
+                cur[k].unpack(0, g);                               // (the sign does not matter for the square)
+                float2 a2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 uj = __fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1]));
+                    a2 = j == 0 ? __fmul2_rn(uj, uj) : __ffma2_rn(uj, uj, a2);
+                }
+                acc += (double)__fadd_rn(a2.x, a2.y);
+                cur[k] = nxt[k];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) s_acc2[warp] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double sum = 0.0;
+            for (int w = 0; w < 8; ++w) sum += s_acc2[w];
+            atomicAdd(L.block_sumsq + sT.first_chunk, sum);
+        }
+    }
+}
+
 inline int factored_chunk_for(int m_block)
 {
     if (m_block <= 0) return 2048;
@@ -1698,6 +1774,20 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
     const bool no_m = cfg->m_fmt == AF8_M_NONE;
     static const bool ring_off = getenv("AF8_NO_FACTORED_RING") != nullptr;
     static const bool wide_off = getenv("AF8_NO_WIDE_SUMS") != nullptr;
+    static const bool tile_off = getenv("AF8_NO_TILE_SUMS") != nullptr;
+    const int64_t total_tiles = cfg->total_tiles;
+    if (vec && !apply && !tile_off && total_tiles > 0 && cfg->grad_dtype != AF8_F16 && ((cfg->came && cfg->mode == AF8_FUPD_SUMSQ_U) || no_m)) {
+        // the sum only needs the gradient: over the statistic tiles, column factors in registers
+        AF8_CUDA_TRY(cudaMemsetAsync(block_sumsq, 0, sizeof(double) * (size_t)total_chunks, cst));
+        FactoredLaunch LT = L;
+        LT.total_units = total_tiles;
+        int64_t tg = (int64_t)sm_count() * 8;
+        if (tg > total_tiles) tg = total_tiles;
+        if (bf) factored_sumsq_tile_kernel<bf16_tag><<<(int)tg, 256, 0, cst>>>(LT);
+        else factored_sumsq_tile_kernel<float><<<(int)tg, 256, 0, cst>>>(LT);
+        AF8_CUDA_TRY(cudaGetLastError());
+        return AF8_OK;
+    }
     if (vec && !apply && !wide_off && cfg->grad_dtype != AF8_F16 && ((cfg->came && cfg->mode == AF8_FUPD_SUMSQ_U) || no_m)) {
         // the sum only needs the gradient: 16 elements per thread, next step's loads in flight
         if (bf) factored_sumsq_wide_kernel<bf16_tag><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);

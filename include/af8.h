@@ -357,6 +357,10 @@ typedef struct af8_factored_cfg {
     int32_t aligned8;       /* 1: every tensor has cols % 8 == 0 and 16-byte aligned arrays
                                (checked by af8_factored_upload); selects the 128-bit kernels */
     int32_t stochastic_round; /* as af8_fullrank_cfg.stochastic_round */
+    int64_t total_tiles;    /* optional: the table's number of statistic tiles (the last tensor's first_tile plus its
+                               own tiles).  With it the sum-of-squares passes that only read the gradient
+                               (AF8_FUPD_SUMSQ_U, AF8_FUPD_SUMSQ without momentum) run over the tiles, with the column
+                               factors in registers; 0: over the flat chunks */
 } af8_factored_cfg;
 
 /* Number of flattened elements per work unit of af8_factored_update for a
