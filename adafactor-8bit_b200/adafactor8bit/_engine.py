@@ -713,6 +713,7 @@ class FactoredPlan:
             t[k]["first_tile"] = self._running(tiles)
             if k == 0:
                 self.cfg.total_tiles = int(tiles.sum())
+                self.cfg.cols_mult256 = int(bool((self.cols % 256 == 0).all()))
             # units of the small-state launch: the quantisation blocks of the row state, then of the column state
             units = (rows + sb - 1) // sb + (self.batch * self.cols + sb - 1) // sb
             t[k]["first_small"] = self._running(units)

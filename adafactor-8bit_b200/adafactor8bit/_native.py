@@ -111,6 +111,7 @@ class FactoredCfg(ctypes.Structure):
         ("m_block", ctypes.c_int32), ("came", ctypes.c_int32), ("negate_grad", ctypes.c_int32),
         ("mode", ctypes.c_int32), ("v_floor", ctypes.c_float),
         ("aligned8", ctypes.c_int32), ("stochastic_round", ctypes.c_int32), ("total_tiles", ctypes.c_int64),
+        ("cols_mult256", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 

@@ -1410,6 +1410,153 @@ factored_apply_ring_kernel(const FactoredLaunch L)
 }
 
 // ---------------------------------------------------------------------------
+// factored_apply_ring_kernel in tile order, for tables whose tensors all have cols % 256 == 0: a CTA takes a
+// 512 x 256 statistic tile, warp w its rows r0 + w, r0 + w + 8, ...; a row slice of 256 columns is 256
+// consecutive elements that start on a multiple of 256, i.e. exactly one momentum block, so the warp still owns
+// its block's absmax.  What changes is that a lane works on the same 8 columns for the whole tile and keeps
+// their inverse column factors (and CAME's confidence factors) in registers instead of loading 32 or 64 bytes
+// of them for every 8 elements.  Ring, arithmetic and stores as in factored_apply_ring_kernel; the copies of
+// a warp run FRING_STAGES - 1 rows ahead inside a tile.
+// ---------------------------------------------------------------------------
+template <typename GradT, int CTAS>
+__global__ void __launch_bounds__(FUPD_THREADS, CTAS)
+factored_apply_tile_kernel(const FactoredLaunch L)
+{
+    constexpr int GB = sizeof_grad<GradT>();
+    constexpr int P_OFF = 256 * GB, M_OFF = P_OFF + 1024, STAGE = fring_stage_bytes<GradT>(), NS = FRING_STAGES;
+    extern __shared__ __align__(128) unsigned char fr_smem[];
+    __shared__ af8_factored_tensor sT;
+    __shared__ __align__(8) uint64_t s_full[FUPD_THREADS / 32][NS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    unsigned char *const ring = fr_smem + (size_t)warp * NS * STAGE;
+    if (lane == 0) {
+        for (int k = 0; k < NS; ++k) mbar_init(&s_full[warp][k], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    int cur_t = -1;
+    float pre_div = 1.0f, step_mul = 0.0f, fira = 1.0f;
+    bool zero_upd = false;
+    DivBy D = make_div(1.0f);
+    uint32_t cons = 0;            // row slices this warp has taken from its ring
+
+    for (int64_t id = blockIdx.x; id < L.total_units; id += gridDim.x) {
+        int t = cur_t;
+        if (t < 0) t = find_factored_tile(L.tensors, L.n_tensors, id);
+        else while (t + 1 < L.n_tensors && __ldg(&L.tensors[t + 1].first_tile) <= id) ++t;
+        if (t != cur_t) {
+            __syncthreads();                                         // every warp has left the previous tensor
+            if (tid < (int)(sizeof(af8_factored_tensor) / 4))
+                reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(L.tensors + t) + tid);
+            cur_t = t;
+            __syncthreads();
+            pre_div = 1.0f; step_mul = -sT.alpha; fira = 1.0f; zero_upd = false;
+            if (L.dyn != nullptr) {
+                const af8_dyn_scalars ds = L.dyn[t];
+                if (L.came) pre_div = ds.pre_div;
+                step_mul = ds.step; fira = ds.fira; zero_upd = ds.zero != 0.0f;
+            }
+            D = make_div(pre_div);
+        }
+        const int64_t R = sT.rows, C = sT.cols;
+        const int64_t ntc = C / FSTAT_COLS;                          // (cols % 256 == 0)
+        const int64_t local = id - sT.first_tile;
+        const int64_t r0 = (local / ntc) * FSTAT_ROWS;
+        const int64_t c0 = (local % ntc) * FSTAT_COLS;
+        const int64_t c = c0 + lane * 8;                             // this lane's 8 columns
+        const int64_t r_end = min(R, r0 + (int64_t)FSTAT_ROWS);
+        const int nrows = r0 + warp < r_end ? (int)((r_end - (r0 + warp) + 7) / 8) : 0;
+        float ic[8], icc[8];
+        load_f8_ro(sT.inv_col + c, ic);
+        if (L.came) load_f8_ro(sT.inv_col_conf + c, icc);
+        float *const pbase = static_cast<float *>(sT.param);
+        const unsigned char *gp = static_cast<const unsigned char *>(sT.grad);
+        const LerpW LW = make_lerp(sT.m_w);
+        const float2 decay2 = bc2(sT.decay), step2 = bc2(step_mul), fira2 = bc2(fira);
+
+        auto issue = [&](int k) {                                    // lane 0: row slice k of this warp into its stage
+            const int64_t off = (r0 + warp + 8 * (int64_t)k) * C + c0;
+            const int sl = (int)((cons + (uint32_t)k) % NS);
+            unsigned char *dst = ring + sl * STAGE;
+            mbar_expect_tx(&s_full[warp][sl], (uint32_t)STAGE);
+            bulk_g2s(dst + P_OFF, reinterpret_cast<const unsigned char *>(pbase) + off * 4, 1024, &s_full[warp][sl]);
+            bulk_g2s(dst, gp + off * GB, 256 * GB, &s_full[warp][sl]);
+            bulk_g2s(dst + M_OFF, sT.m_q + off, 256, &s_full[warp][sl]);
+        };
+        if (lane == 0 && nrows > 0) {
+            fence_proxy_async();                                     // this warp's reads of the slots came first
+            for (int k = 0; k < min(NS, nrows); ++k) issue(k);
+        }
+        for (int k = 0; k < nrows; ++k) {
+            const uint32_t n = cons + (uint32_t)k;
+            const int sl = (int)(n % NS);
+            const bool landed = mbar_wait_bounded(&s_full[warp][sl], (n / NS) & 1u);
+            if (!__all_sync(0xffffffffu, landed)) {                  // (uniform over the warp)
+                atomicExch(&g_device_error, DEVERR_FRING_TIMEOUT);
+                return;
+            }
+            const unsigned char *st = ring + sl * STAGE;
+            GradRaw8<GradT> cg;
+            cg.from_shared(st + lane * (8 * GB));
+            const float4 cp0 = *reinterpret_cast<const float4 *>(st + P_OFF + lane * 32);
+            const float4 cp1 = *reinterpret_cast<const float4 *>(st + P_OFF + lane * 32 + 16);
+            const uint2 cm = *reinterpret_cast<const uint2 *>(st + M_OFF + lane * 8);
+            __syncwarp();                                            // the slot may be refilled
+            if (lane == 0 && k + NS < nrows) { fence_proxy_async(); issue(k + NS); }
+
+            const int64_t row = r0 + warp + 8 * (int64_t)k;
+            const int64_t flat = row * C + c;
+            float g[8], u[8], mo[8], mj[8];
+            cg.unpack(L.negate_grad, g);
+            const float2 ir2 = bc2(__ldg(sT.inv_row + row));
+            m_old8(sT, AF8_M_UF8, 256, flat, mo, true, cm);
+            if (L.came) {
+                const float2 irc2 = bc2(__ldg(sT.inv_row_conf + row));
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 ut = div_by2(__fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1])), D);
+                    const float2 mm = lerp_w2(make_float2(mo[j], mo[j + 1]), ut, LW);
+                    const float2 uj = __fmul2_rn(__fmul2_rn(mm, irc2), make_float2(icc[j], icc[j + 1]));
+                    mj[j] = mm.x; mj[j + 1] = mm.y; u[j] = uj.x; u[j + 1] = uj.y;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 mm = lerp_w2(make_float2(mo[j], mo[j + 1]), make_float2(g[j], g[j + 1]), LW);
+                    const float2 uj = __fmul2_rn(__fmul2_rn(mm, ir2), make_float2(ic[j], ic[j + 1]));
+                    mj[j] = mm.x; mj[j + 1] = mm.y; u[j] = uj.x; u[j + 1] = uj.y;
+                }
+            }
+            float p[8] = {cp0.x, cp0.y, cp0.z, cp0.w, cp1.x, cp1.y, cp1.z, cp1.w};
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                float2 pj = __fmul2_rn(make_float2(p[j], p[j + 1]), decay2);
+                if (!zero_upd) pj = __ffma2_rn(step2, __fmul2_rn(make_float2(u[j], u[j + 1]), fira2), pj);
+                p[j] = pj.x; p[j + 1] = pj.y;
+            }
+            float *pp = pbase + flat;
+            *reinterpret_cast<float4 *>(pp) = make_float4(p[0], p[1], p[2], p[3]);
+            *reinterpret_cast<float4 *>(pp + 4) = make_float4(p[4], p[5], p[6], p[7]);
+            if (sT.param_copy != nullptr)                                    // bf16 compute copy
+                *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(sT.param_copy) + flat) =
+                    make_uint4(bf16x2_rn(p[0], p[1]), bf16x2_rn(p[2], p[3]), bf16x2_rn(p[4], p[5]), bf16x2_rn(p[6], p[7]));
+            // the row slice is one momentum block of 256
+            float am = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(mj[j]));
+            am = fmaxf(warp_max(am), 1e-12f);
+            const DivBy A = make_div(am);
+            const uint32_t o0 = uf8_encode_fast2(make_float2(mj[0], mj[1]), A) | (uf8_encode_fast2(make_float2(mj[2], mj[3]), A) << 16);
+            const uint32_t o1 = uf8_encode_fast2(make_float2(mj[4], mj[5]), A) | (uf8_encode_fast2(make_float2(mj[6], mj[7]), A) << 16);
+            *reinterpret_cast<uint2 *>(sT.m_q + flat) = make_uint2(o0, o1);
+            if (lane == 0) sT.m_scale[(row * C + c0) / 256] = am;
+        }
+        cons += (uint32_t)nrows;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // The sum-of-squares pass over u = g * inv_row * inv_col (CAME's first sum, Adafactor without
 // momentum): it only reads the gradient, 2 bytes per parameter, and with one 128-bit load per
 // thread in flight (the kernel above) it was bound by memory latency.  Here a thread takes NE = 16
@@ -1792,6 +1939,24 @@ extern "C" int af8_factored_update(const af8_factored_cfg *cfg, const af8_factor
         // the sum only needs the gradient: 16 elements per thread, next step's loads in flight
         if (bf) factored_sumsq_wide_kernel<bf16_tag><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
         else factored_sumsq_wide_kernel<float><<<(int)grid, FUPD_THREADS, 0, cst>>>(L);
+        AF8_CUDA_TRY(cudaGetLastError());
+        return AF8_OK;
+    }
+    static const bool tile_apply_off = getenv("AF8_NO_TILE_APPLY") != nullptr;
+    if (vec && cfg->mode == AF8_FUPD_APPLY && cfg->m_fmt == AF8_M_UF8 && cfg->param_dtype == AF8_F32 && !ring_off && !tile_apply_off &&
+        cfg->total_tiles > 0 && cfg->cols_mult256) {
+        // every row slice of 256 columns is one momentum block: tile order, column factors in registers
+        FactoredLaunch LT = L;
+        LT.total_units = cfg->total_tiles;
+        if (bf) {
+            int64_t tg = std::min<int64_t>((int64_t)sm_count() * 3, cfg->total_tiles);
+            AF8_CUDA_TRY(cudaFuncSetAttribute(factored_apply_tile_kernel<bf16_tag, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fring_smem_bytes<bf16_tag>()));
+            factored_apply_tile_kernel<bf16_tag, 3><<<(int)tg, FUPD_THREADS, fring_smem_bytes<bf16_tag>(), cst>>>(LT);
+        } else {
+            int64_t tg = std::min<int64_t>((int64_t)sm_count() * 2, cfg->total_tiles);
+            AF8_CUDA_TRY(cudaFuncSetAttribute(factored_apply_tile_kernel<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fring_smem_bytes<float>()));
+            factored_apply_tile_kernel<float, 2><<<(int)tg, FUPD_THREADS, fring_smem_bytes<float>(), cst>>>(LT);
+        }
         AF8_CUDA_TRY(cudaGetLastError());
         return AF8_OK;
     }

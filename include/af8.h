@@ -361,6 +361,9 @@ typedef struct af8_factored_cfg {
                                own tiles).  With it the sum-of-squares passes that only read the gradient
                                (AF8_FUPD_SUMSQ_U, AF8_FUPD_SUMSQ without momentum) run over the tiles, with the column
                                factors in registers; 0: over the flat chunks */
+    int32_t cols_mult256;   /* 1: every tensor of the table has cols % 256 == 0 (with total_tiles: the write pass with a
+                               UF8 momentum then also runs over the tiles, a row slice being one momentum block) */
+    int32_t reserved;
 } af8_factored_cfg;
 
 /* Number of flattened elements per work unit of af8_factored_update for a
