@@ -733,34 +733,93 @@ template <typename GradT> __host__ __device__ constexpr int sring_stages() { ret
 template <typename GradT, bool RESIDUAL> __host__ __device__ constexpr int sring_stage_bytes() { return 256 * sizeof_grad<GradT>() + (RESIDUAL ? 256 : 0); }
 template <typename GradT, bool RESIDUAL> __host__ __device__ constexpr size_t sring_smem_bytes() { return (size_t)8 * sring_stages<GradT>() * sring_stage_bytes<GradT, RESIDUAL>(); }
 
-template <typename GradT, int NB, bool RESIDUAL>
-__device__ __forceinline__ bool stats_rows_ring(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t row_end, int64_t c0,
-                                                float pre_div, const float (&ic)[8], double (&cacc)[8],
-                                                unsigned char *ring, uint64_t *full, uint32_t &cons)
+// 8 UF8 codes of one momentum block as floats: (code - 128) * mc, two elements per instruction; each
+// component rounds like the scalar form in m_old8
+__device__ __forceinline__ void uf8_decode8(uint2 w, float mc, float2 (&m)[4])
 {
-    constexpr int GB = sizeof_grad<GradT>(), NS = sring_stages<GradT>(), STAGE = sring_stage_bytes<GradT, RESIDUAL>();
-    static_assert(NS % NB == 0, "a ring holds whole groups of rows");
+    const float2 off = bc2(-8388736.0f), mc2 = bc2(mc);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t word = j < 2 ? w.x : w.y;
+        const float2 b = make_float2(__uint_as_float(__byte_perm(word, 0x4b000000u, 0x7540u | (uint32_t)((2 * j) & 3))),
+                                     __uint_as_float(__byte_perm(word, 0x4b000000u, 0x7540u | (uint32_t)((2 * j + 1) & 3))));
+        m[j] = __fmul2_rn(__fadd2_rn(b, off), mc2);
+    }
+}
+
+// CAME's residual (U - M)^2 + eps of 8 elements, M the momentum after this step's EMA.
+// ONE: the clip divisor is 1; SMALL: |momentum weight| < 0.5 (the form of lerp).  The quotient is taken
+// without div_by's test for an infinite product.  The caller guarantees a divisor d >= 1 (or NaN), as the
+// RMS clip produces: then a finite t = g * r * c has a finite product t * fl(1 / d), and an infinite or NaN t
+// ends as x = NaN with the true quotient as well (U and M are both infinite, U - M is NaN).
+template <bool ONE, bool SMALL>
+__device__ __forceinline__ void residual_x8(const float (&g)[8], uint2 codes, float mc, float ir, const float (&ic)[8],
+                                            const DivBy &D, float ww, float eps, float (&x)[8])
+{
+    const float2 ir2 = bc2(ir), r2 = bc2(D.rcp), nd2 = bc2(D.nd), ww2 = bc2(ww), eps2 = bc2(eps);
+    float2 mo[4];
+    uf8_decode8(codes, mc, mo);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 t = __fmul2_rn(__fmul2_rn(make_float2(g[2 * j], g[2 * j + 1]), ir2), make_float2(ic[2 * j], ic[2 * j + 1]));
+        float2 u = t;
+        if (!ONE) {
+            const float2 q = __fmul2_rn(t, r2);
+            u = __ffma2_rn(__ffma2_rn(q, nd2, t), r2, q);
+        }
+        const float2 m = __ffma2_rn(ww2, sub2(u, mo[j]), SMALL ? mo[j] : u);
+        const float2 df = sub2(u, m);
+        const float2 xx = __fadd2_rn(__fmul2_rn(df, df), eps2);
+        x[2 * j] = xx.x; x[2 * j + 1] = xx.y;
+    }
+}
+
+// The residual pass over the rows r0 + warp + 8 k of a tile whose 256-column row slices (gradient and UF8 codes,
+// momentum block 256: a slice is one block) come through the warp's ring.  NB rows are consumed per iteration
+// so that their row sums are reduced jointly.  The per-row scalars (inverse row factor, block absmax) of the
+// next iteration are loaded while the current one computes; the sign of a negated gradient rides on the row
+// factor ((-g) * r == g * (-r) bit for bit).  Returns false after a time-out.
+template <typename GradT, int NB, bool ONE, bool SMALL>
+__device__ __forceinline__ bool residual_rows_ring(const FactoredLaunch &L, const af8_factored_tensor &sT, int64_t r0, int64_t c0,
+                                                   float pre_div, const float (&ic)[8], double (&cacc)[8],
+                                                   unsigned char *ring, uint64_t *full, uint32_t &cons)
+{
+    constexpr int GB = sizeof_grad<GradT>(), NS = sring_stages<GradT>(), STAGE = sring_stage_bytes<GradT, true>();
+    static_assert(NS % NB == 0 && (NS & (NS - 1)) == 0, "a ring holds whole groups of rows");
+    static_assert(NB == 2 || NB == 4, "row-sum reduction is written for 2 or 4 rows");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t R = row_end, C = sT.cols;
-    const int64_t c = c0 + lane * 8;
-    const int64_t r_end = min(R, r0 + (int64_t)FSTAT_ROWS);
-    const int nrows = r0 + warp < r_end ? (int)((r_end - (r0 + warp) + 7) / 8) : 0;       // rows r0 + warp + 8 k of this warp
-    const unsigned char *gp = static_cast<const unsigned char *>(sT.grad);
-    auto issue = [&](int k) {                                    // lane 0: row slice k into its stage
-        const int64_t off = (r0 + warp + 8 * (int64_t)k) * C + c0;
-        const int sl = (int)((cons + (uint32_t)k) % NS);         // (cons counts the slices consumed before this tile)
+    const int64_t C = sT.cols;
+    const int64_t r_end = min(sT.rows, r0 + (int64_t)FSTAT_ROWS);
+    const int64_t row0 = r0 + warp;
+    const int nrows = row0 < r_end ? (int)((r_end - row0 + 7) / 8) : 0;          // rows row0 + 8 k of this warp
+    int64_t eoff = row0 * C + c0;                                // lane 0: the element offset of the next slice to request
+    uint32_t prod = cons;                                        // (cons counts the slices consumed before this tile)
+    auto issue = [&]() {
+        const int sl = (int)(prod & (uint32_t)(NS - 1));
+        ++prod;
         unsigned char *dst = ring + sl * STAGE;
         mbar_expect_tx(&full[sl], (uint32_t)STAGE);
-        bulk_g2s(dst, gp + off * GB, 256 * GB, &full[sl]);
-        if (RESIDUAL) bulk_g2s(dst + 256 * GB, sT.m_q + off, 256, &full[sl]);
+        bulk_g2s(dst, static_cast<const unsigned char *>(sT.grad) + eoff * GB, 256 * GB, &full[sl]);
+        bulk_g2s(dst + 256 * GB, sT.m_q + eoff, 256, &full[sl]);
+        eoff += 8 * sT.cols;
     };
     if (lane == 0 && nrows > 0) {
         fence_proxy_async();
-        for (int k = 0; k < min(NS, nrows); ++k) issue(k);
+        for (int k = 0; k < min(NS, nrows); ++k) issue();
     }
     const DivBy D = make_div(pre_div);
     const LerpW LW = make_lerp(sT.m_w);
-    const float2 eps2 = bc2(sT.eps_came);
+    const float eps = sT.eps_came, sgn = L.negate_grad ? -1.0f : 1.0f;
+    // row row0 + 8 k: inverse row factor at index row0 + 8 k, block absmax at sc0 + k * scstep (both fit 32 bits:
+    // a tensor has fewer than 2^31 rows and momentum blocks)
+    const int scstep = (int)(8 * (C >> 8));
+    const int sc0 = (int)(row0 * (C >> 8) + (c0 >> 8));
+    float nir[NB], nsc[NB];                                      // the scalars of the next NB rows, signed and scaled
+#pragma unroll
+    for (int k = 0; k < NB; ++k) {
+        nir[k] = 0.0f; nsc[k] = 0.0f;
+        if (k < nrows) { nir[k] = __ldg(sT.inv_row + (int)row0 + 8 * k); nsc[k] = __ldg(sT.m_scale + sc0 + k * scstep); }
+    }
     for (int k0 = 0; k0 < nrows; k0 += NB) {
         GradRaw8<GradT> cur[NB];
         uint2 cm[NB];
@@ -770,11 +829,11 @@ __device__ __forceinline__ bool stats_rows_ring(const FactoredLaunch &L, const a
             cm[k] = make_uint2(0u, 0u);
             if (k0 + k < nrows) {
                 const uint32_t n = cons + (uint32_t)(k0 + k);
-                const int sl = (int)(n % NS);
+                const int sl = (int)(n & (uint32_t)(NS - 1));
                 landed = landed && mbar_wait_bounded(&full[sl], (n / NS) & 1u);
                 const unsigned char *st = ring + sl * STAGE;
                 cur[k].from_shared(st + lane * (8 * GB));
-                if (RESIDUAL) cm[k] = *reinterpret_cast<const uint2 *>(st + 256 * GB + lane * 8);
+                cm[k] = *reinterpret_cast<const uint2 *>(st + 256 * GB + lane * 8);
             } else cur[k].zero();
         }
         if (!__all_sync(0xffffffffu, landed)) return false;
@@ -783,49 +842,30 @@ __device__ __forceinline__ bool stats_rows_ring(const FactoredLaunch &L, const a
             fence_proxy_async();
 #pragma unroll
             for (int k = 0; k < NB; ++k)
-                if (k0 + k + NS < nrows) issue(k0 + k + NS);
+                if (k0 + k + NS < nrows) issue();
         }
         double rsum[NB];
 #pragma unroll
         for (int k = 0; k < NB; ++k) {
-            const int64_t r = r0 + warp + 8 * (int64_t)(k0 + k);
-            const bool live = k0 + k < nrows;
-            float g[8], x[8];
-            cur[k].unpack(L.negate_grad, g);
-            if (!RESIDUAL) {
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    const float2 gj = make_float2(g[j], g[j + 1]);
-                    const float2 xx = __fmul2_rn(gj, gj);
-                    x[j] = xx.x; x[j + 1] = xx.y;
-                }
-            } else if (live) {
-                const int64_t flat = r * C + c;
-                const float2 ir2 = bc2(sT.inv_row[r]);
-                float mo[8];
-                m_old8(sT, L.m_fmt, L.m_block, flat, mo, true, cm[k]);
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    const float2 u = div_by2(__fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1])), D);
-                    const float2 m = lerp_w2(make_float2(mo[j], mo[j + 1]), u, LW);
-                    const float2 df = sub2(u, m);
-                    const float2 xx = __fadd2_rn(__fmul2_rn(df, df), eps2);
-                    x[j] = xx.x; x[j + 1] = xx.y;
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) x[j] = 0.0f;
-            }
             double racc = 0.0;
+            if (k0 + k < nrows) {
+                float g[8], x[8];
+                cur[k].unpack(0, g);
+                // fl(scale / 128): a power-of-two divisor, scale >= 1e-12
+                residual_x8<ONE, SMALL>(g, cm[k], __fmul_rn(nsc[k], 0.0078125f), __fmul_rn(nir[k], sgn), ic, D, LW.ww, eps, x);
+                if (k0 + NB + k < nrows) {                       // this row's successor in the next iteration
+                    nir[k] = __ldg(sT.inv_row + (int)row0 + 8 * (k0 + NB + k));
+                    nsc[k] = __ldg(sT.m_scale + sc0 + (k0 + NB + k) * scstep);
+                }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const double xd = (double)x[j];
-                racc += xd;
-                cacc[j] += xd;
+                for (int j = 0; j < 8; ++j) {
+                    const double xd = (double)x[j];
+                    racc += xd;
+                    cacc[j] += xd;
+                }
             }
             rsum[k] = racc;
         }
-        static_assert(NB == 2 || NB == 4, "row-sum reduction is written for 2 or 4 rows");
         double v;
         if (NB == 4) {
             const bool hi = lane & 16;
@@ -837,13 +877,13 @@ __device__ __forceinline__ bool stats_rows_ring(const FactoredLaunch &L, const a
             v = (h2 ? k1v : k0v) + __shfl_xor_sync(0xffffffffu, h2 ? k0v : k1v, 8);
 #pragma unroll
             for (int o = 4; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if ((lane & 7) == 0 && k0 + (lane >> 3) < nrows) atomicAdd(sT.row_sum + r0 + warp + 8 * (int64_t)(k0 + (lane >> 3)), v);
+            if ((lane & 7) == 0 && k0 + (lane >> 3) < nrows) atomicAdd(sT.row_sum + row0 + 8 * (int64_t)(k0 + (lane >> 3)), v);
         } else {
             const bool hi = lane & 16;
             v = (hi ? rsum[1] : rsum[0]) + __shfl_xor_sync(0xffffffffu, hi ? rsum[0] : rsum[1], 16);
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if ((lane & 15) == 0 && k0 + (lane >> 4) < nrows) atomicAdd(sT.row_sum + r0 + warp + 8 * (int64_t)(k0 + (lane >> 4)), v);
+            if ((lane & 15) == 0 && k0 + (lane >> 4) < nrows) atomicAdd(sT.row_sum + row0 + 8 * (int64_t)(k0 + (lane >> 4)), v);
         }
     }
     cons += (uint32_t)nrows;
@@ -918,16 +958,27 @@ factored_stats_vec_kernel(const FactoredLaunch L, const int use_ring)
         // residual: whole 256-column slices of the gradient and the UF8 codes come through the warp's ring
         // (measured on Llama-2-7B: 11.9 -> 11.4 ms; the g*g pass and the sum passes, which only read the
         // gradient, were slower through a ring - 3.0 -> 4.3 ms and 4.6 -> 5.9 ms - and load directly)
-        const bool ring_ok = RESIDUAL && use_ring && (C % FSTAT_COLS) == 0 && L.m_fmt == AF8_M_UF8;
-        if (ring_ok) {
-            unsigned char *ring = sr_smem + (size_t)warp * sring_stages<GradT>() * sring_stage_bytes<GradT, RESIDUAL>();
-            if (!stats_rows_ring<GradT, RESIDUAL ? AF8_FSTAT_RES_NB : 4, RESIDUAL>(L, sT, r0, row_end, c0, pre_div, ic, cacc, ring, s_full[warp], cons)) {
-                atomicExch(&g_device_error, DEVERR_SRING_TIMEOUT);
-                return;                          // (the whole warp; the others finish their rows and leave at the next barrier)
+        // (the ring's quotient wants a clip divisor >= 1 or NaN, which is what the RMS clip produces)
+        bool done = false;
+        if constexpr (RESIDUAL) {
+            if (use_ring && (C % FSTAT_COLS) == 0 && L.m_fmt == AF8_M_UF8 && L.m_block == 256 && !(pre_div < 1.0f)) {
+                done = true;
+                unsigned char *ring = sr_smem + (size_t)warp * sring_stages<GradT>() * sring_stage_bytes<GradT, true>();
+                constexpr int NB = AF8_FSTAT_RES_NB;
+                const bool one = pre_div == 1.0f, small = fabsf(sT.m_w) < 0.5f;  // (uniform over the tensor)
+                bool ok;
+                if (one) ok = small ? residual_rows_ring<GradT, NB, true, true>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)
+                                    : residual_rows_ring<GradT, NB, true, false>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons);
+                else ok = small ? residual_rows_ring<GradT, NB, false, true>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)
+                                : residual_rows_ring<GradT, NB, false, false>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons);
+                if (!ok) {
+                    atomicExch(&g_device_error, DEVERR_SRING_TIMEOUT);
+                    return;                      // (the whole warp; the others finish their rows and leave at the next barrier)
+                }
             }
         }
-        else if (!RESIDUAL) stats_rows<GradT, 4, true, false>(L, sT, r0, row_end, c, col_ok, pre_div, ic, cacc);
-        else stats_rows<GradT, AF8_FSTAT_RES_NB, AF8_FSTAT_RES_PREFETCH, true>(L, sT, r0, row_end, c, col_ok, pre_div, ic, cacc);
+        if (!RESIDUAL) stats_rows<GradT, 4, true, false>(L, sT, r0, row_end, c, col_ok, pre_div, ic, cacc);
+        else if (!done) stats_rows<GradT, AF8_FSTAT_RES_NB, AF8_FSTAT_RES_PREFETCH, true>(L, sT, r0, row_end, c, col_ok, pre_div, ic, cacc);
 #pragma unroll
         for (int j = 0; j < 8; ++j) s_col[warp][j * 32 + lane] = cacc[j];
         __syncthreads();
@@ -1488,6 +1539,18 @@ factored_apply_tile_kernel(const FactoredLaunch L)
             fence_proxy_async();                                     // this warp's reads of the slots came first
             for (int k = 0; k < min(NS, nrows); ++k) issue(k);
         }
+        // the per-row scalars (inverse row factors, block absmax) are loaded one row ahead; the sign of a
+        // negated gradient rides on the row factor ((-g) * r == g * (-r) bit for bit; without CAME the
+        // gradient itself enters the momentum and is negated when unpacked)
+        const int64_t row0 = r0 + warp;
+        const int64_t scstep = 8 * (C >> 8);
+        float *const scp = sT.m_scale + row0 * (C >> 8) + (c0 >> 8);             // + scstep per row of this warp
+        const float sgn = (L.came && L.negate_grad) ? -1.0f : 1.0f;
+        float n_ir = 0.0f, n_irc = 0.0f, n_sc = 0.0f;
+        if (nrows > 0) {
+            n_ir = __ldg(sT.inv_row + row0); n_sc = __ldg(scp);
+            if (L.came) n_irc = __ldg(sT.inv_row_conf + row0);
+        }
         for (int k = 0; k < nrows; ++k) {
             const uint32_t n = cons + (uint32_t)k;
             const int sl = (int)(n % NS);
@@ -1505,25 +1568,29 @@ factored_apply_tile_kernel(const FactoredLaunch L)
             __syncwarp();                                            // the slot may be refilled
             if (lane == 0 && k + NS < nrows) { fence_proxy_async(); issue(k + NS); }
 
-            const int64_t row = r0 + warp + 8 * (int64_t)k;
+            const int64_t row = row0 + 8 * (int64_t)k;
             const int64_t flat = row * C + c;
-            float g[8], u[8], mo[8], mj[8];
-            cg.unpack(L.negate_grad, g);
-            const float2 ir2 = bc2(__ldg(sT.inv_row + row));
-            m_old8(sT, AF8_M_UF8, 256, flat, mo, true, cm);
+            float g[8], u[8], mj[8];
+            float2 mo[4];
+            cg.unpack(L.came ? 0 : L.negate_grad, g);
+            const float2 ir2 = bc2(__fmul_rn(n_ir, sgn)), irc2 = bc2(n_irc);
+            uf8_decode8(cm, __fmul_rn(n_sc, 0.0078125f), mo);                    // fl(scale / 128), scale >= 1e-12
+            if (k + 1 < nrows) {
+                n_ir = __ldg(sT.inv_row + row + 8); n_sc = __ldg(scp + (k + 1) * scstep);
+                if (L.came) n_irc = __ldg(sT.inv_row_conf + row + 8);
+            }
             if (L.came) {
-                const float2 irc2 = bc2(__ldg(sT.inv_row_conf + row));
 #pragma unroll
                 for (int j = 0; j < 8; j += 2) {
                     const float2 ut = div_by2(__fmul2_rn(__fmul2_rn(make_float2(g[j], g[j + 1]), ir2), make_float2(ic[j], ic[j + 1])), D);
-                    const float2 mm = lerp_w2(make_float2(mo[j], mo[j + 1]), ut, LW);
+                    const float2 mm = lerp_w2(mo[j >> 1], ut, LW);
                     const float2 uj = __fmul2_rn(__fmul2_rn(mm, irc2), make_float2(icc[j], icc[j + 1]));
                     mj[j] = mm.x; mj[j + 1] = mm.y; u[j] = uj.x; u[j + 1] = uj.y;
                 }
             } else {
 #pragma unroll
                 for (int j = 0; j < 8; j += 2) {
-                    const float2 mm = lerp_w2(make_float2(mo[j], mo[j + 1]), make_float2(g[j], g[j + 1]), LW);
+                    const float2 mm = lerp_w2(mo[j >> 1], make_float2(g[j], g[j + 1]), LW);
                     const float2 uj = __fmul2_rn(__fmul2_rn(mm, ir2), make_float2(ic[j], ic[j + 1]));
                     mj[j] = mm.x; mj[j + 1] = mm.y; u[j] = uj.x; u[j + 1] = uj.y;
                 }
@@ -1550,7 +1617,7 @@ factored_apply_tile_kernel(const FactoredLaunch L)
             const uint32_t o0 = uf8_encode_fast2(make_float2(mj[0], mj[1]), A) | (uf8_encode_fast2(make_float2(mj[2], mj[3]), A) << 16);
             const uint32_t o1 = uf8_encode_fast2(make_float2(mj[4], mj[5]), A) | (uf8_encode_fast2(make_float2(mj[6], mj[7]), A) << 16);
             *reinterpret_cast<uint2 *>(sT.m_q + flat) = make_uint2(o0, o1);
-            if (lane == 0) sT.m_scale[(row * C + c0) / 256] = am;
+            if (lane == 0) scp[k * scstep] = am;
         }
         cons += (uint32_t)nrows;
     }
