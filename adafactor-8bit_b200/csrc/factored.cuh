@@ -792,18 +792,23 @@ __device__ __forceinline__ bool residual_rows_ring(const FactoredLaunch &L, cons
     const int64_t r_end = min(sT.rows, r0 + (int64_t)FSTAT_ROWS);
     const int64_t row0 = r0 + warp;
     const int nrows = row0 < r_end ? (int)((r_end - row0 + 7) / 8) : 0;          // rows row0 + 8 k of this warp
-    int64_t eoff = row0 * C + c0;                                // lane 0: the element offset of the next slice to request
+    // lanes 0 and 1 request the next slice: lane 0 its gradients (and the bytes to expect), lane 1 its codes,
+    // both with the same instructions (a copy may complete before the bytes are announced: the phase also
+    // needs lane 0's arrival)
+    const int64_t estep = 8 * C;
+    int64_t eoff = row0 * C + c0;                                // element offset of the next slice
+    const unsigned char *src = lane == 0 ? static_cast<const unsigned char *>(sT.grad) : sT.m_q;
+    const int esz = lane == 0 ? GB : 1;
     uint32_t prod = cons;                                        // (cons counts the slices consumed before this tile)
-    auto issue = [&]() {
+    auto issue = [&]() {                                         // lanes 0 and 1
         const int sl = (int)(prod & (uint32_t)(NS - 1));
         ++prod;
         unsigned char *dst = ring + sl * STAGE;
-        mbar_expect_tx(&full[sl], (uint32_t)STAGE);
-        bulk_g2s(dst, static_cast<const unsigned char *>(sT.grad) + eoff * GB, 256 * GB, &full[sl]);
-        bulk_g2s(dst + 256 * GB, sT.m_q + eoff, 256, &full[sl]);
-        eoff += 8 * sT.cols;
+        if (lane == 0) mbar_expect_tx(&full[sl], (uint32_t)STAGE);
+        bulk_g2s(dst + lane * (256 * GB), src + eoff * esz, 256 * esz, &full[sl]);
+        eoff += estep;
     };
-    if (lane == 0 && nrows > 0) {
+    if (lane < 2 && nrows > 0) {
         fence_proxy_async();
         for (int k = 0; k < min(NS, nrows); ++k) issue();
     }
@@ -838,7 +843,7 @@ __device__ __forceinline__ bool residual_rows_ring(const FactoredLaunch &L, cons
         }
         if (!__all_sync(0xffffffffu, landed)) return false;
         __syncwarp();                                            // the stages were read: they may be refilled
-        if (lane == 0) {
+        if (lane < 2) {
             fence_proxy_async();
 #pragma unroll
             for (int k = 0; k < NB; ++k)
@@ -857,12 +862,15 @@ __device__ __forceinline__ bool residual_rows_ring(const FactoredLaunch &L, cons
                     nir[k] = __ldg(sT.inv_row + (int)row0 + 8 * (k0 + NB + k));
                     nsc[k] = __ldg(sT.m_scale + sc0 + (k0 + NB + k) * scstep);
                 }
+                double pr[4];                                   // (pairwise: a short dependency chain)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const double xd = (double)x[j];
-                    racc += xd;
-                    cacc[j] += xd;
+                for (int j = 0; j < 8; j += 2) {
+                    const double xa = (double)x[j], xb = (double)x[j + 1];
+                    cacc[j] += xa;
+                    cacc[j + 1] += xb;
+                    pr[j >> 1] = xa + xb;
                 }
+                racc = (pr[0] + pr[1]) + (pr[2] + pr[3]);
             }
             rsum[k] = racc;
         }
