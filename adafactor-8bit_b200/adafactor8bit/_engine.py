@@ -994,6 +994,17 @@ class ApolloPlan:
             fs["first_unit"][i] = sum(units[:i])
         self._finish_static = fs
         self.finish_units = int(sum(units))
+        # table of the batched write-back (static part): 2048-element chunks numbered across the tensors
+        ap = np.zeros(self.n, dtype=N.APOLLO_APPLY_TENSOR)
+        chunks = [(r * c + 2047) // 2048 for r, c in zip(self.rows, self.cols)]
+        for i in range(self.n):
+            ap["sf"][i], ap["scalars"][i] = self.sf[i].data_ptr(), self.out.data_ptr() + 16 * i
+            ap["param_copy"][i] = self.copies[i].data_ptr() if self.copies[i] is not None else 0
+            ap["rows"][i], ap["cols"][i], ap["first_chunk"][i] = self.rows[i], self.cols[i], sum(chunks[:i])
+        self._apply_static = ap
+        self.apply_chunks = int(sum(chunks))
+        self.h_apply = _PinnedRing(self.n * N.APOLLO_APPLY_TENSOR.itemsize)
+        self.d_apply = torch.empty(self.n * N.APOLLO_APPLY_TENSOR.itemsize, dtype=torch.uint8, device=dev)
         self.h_finish = _PinnedRing(self.n * N.APOLLO_FINISH_TENSOR.itemsize)
         self.d_finish = torch.empty(self.n * N.APOLLO_FINISH_TENSOR.itemsize, dtype=torch.uint8, device=dev)
 
@@ -1126,13 +1137,19 @@ class ApolloPlan:
             N.check(lib.af8_apollo_scales_batch(h.data_ptr(), self.d_finish.data_ptr(), self.n, self.finish_units, s),
                     "af8_apollo_scales_batch")
             self.h_finish.mark(stream)
+        h = self.h_apply.next()                     # the write-back of all tensors: one launch
+        at = np.frombuffer(h.numpy(), dtype=N.APOLLO_APPLY_TENSOR, count=self.n)
+        at[:] = self._apply_static
         for i, sin in enumerate(sins):
             t = per_tensor[i]
-            N.check(lib.af8_apollo_apply(self.params[i].data_ptr(), self.param_dtype, int(t.get("sr", False)), int(t.get("sr_base", 0)),
-                                         grads[i].data_ptr(), self.grad_dtype, self.negate,
-                                         self.sf[i].data_ptr(), self.out.data_ptr() + 16 * i, self.rows[i], self.cols[i],
-                                         ctypes.byref(sin), float(t["decay"]), 2 if scale is not None else int(t["has_decay"]),
-                                         self.copies[i].data_ptr() if self.copies[i] is not None else None, s), "af8_apollo_apply")
+            at["param"][i], at["grad"][i] = self.params[i].data_ptr(), grads[i].data_ptr()   # (this step's storage)
+            at["sr_base"][i], at["stochastic_round"][i] = int(t.get("sr_base", 0)), int(t.get("sr", False))
+            at["decay"][i], at["has_decay"][i] = float(t["decay"]), 2 if scale is not None else int(t["has_decay"])
+            at["sqrt_scale"][i], at["scale_tensor"][i] = sin.sqrt_scale, sin.scale_tensor
+            at["fira"][i], at["scale_front"][i] = sin.fira, sin.scale_front
+        N.check(lib.af8_apollo_apply_batch(h.data_ptr(), self.d_apply.data_ptr(), self.n, self.apply_chunks, self.param_dtype,
+                                           self.grad_dtype, self.negate, s), "af8_apollo_apply_batch")
+        self.h_apply.mark(stream)
         if log is not None:
             ev[3].record(stream)
             log.append(("apollo_project", self.total_numel, ev[0], ev[1]))

@@ -68,6 +68,13 @@ APOLLO_FINISH_TENSOR = np.dtype(
     [(n, np.int32) for n in ("bc_mode", "fira", "fira_has_prev", "scale_tensor", "scale_front", "in_reserved")] +
     [("alpha_decay", np.uint64)], align=True)     # af8_apollo_finish_tensor, 144 B
 
+APOLLO_APPLY_TENSOR = np.dtype(
+    [(n, np.uint64) for n in ("param", "grad", "sf", "scalars", "param_copy")] +
+    [(n, np.int64) for n in ("rows", "cols", "first_chunk")] + [("sr_base", np.uint64)] +
+    [(n, np.float32) for n in ("sqrt_scale", "decay")] +
+    [(n, np.int32) for n in ("scale_tensor", "fira", "scale_front", "has_decay", "stochastic_round", "reserved")],
+    align=True)     # af8_apollo_apply_tensor, 104 B
+
 SMALL_STATE = np.dtype([
     ("q", _P), ("scale", _P), ("min_log", _P), ("f32", _P), ("fmt", np.int32), ("block", np.int32),
 ], align=True)
@@ -180,6 +187,7 @@ PROTOTYPES = {
                                  _c_p, _c_p, _c_p]),
     "af8_apollo_apply": (_c_i, [_c_p, _c_i, _c_i, ctypes.c_uint64, _c_p, _c_i, _c_i, _c_p, _c_p, _c_l, _c_l,
                                 ctypes.POINTER(ApolloScalarsIn), _c_f, _c_i, _c_p, _c_p]),
+    "af8_apollo_apply_batch": (_c_i, [_c_p, _c_p, _c_i, _c_l, _c_i, _c_i, _c_i, _c_p]),
     "af8_apollo_rule_workspace": (ctypes.c_int64, [_c_l, _c_l]),
     "af8_apollo_rule_step": (_c_i, [ctypes.POINTER(ApolloRule), _c_p]),
     "af8_norm_finalize": (_c_i, [_c_p, _c_i, _c_p, _c_p, _c_p]),
@@ -224,7 +232,7 @@ def lib():
         mirrors = [FULLRANK_TENSOR.itemsize, DYN_SCALARS.itemsize, ctypes.sizeof(FullrankCfg), NORM_TENSOR.itemsize,
                    SCALE_TENSOR.itemsize, SMALL_STATE.itemsize, FACTORED_TENSOR.itemsize, ctypes.sizeof(FactoredCfg),
                    ctypes.sizeof(ApolloScalarsIn), 16, APOLLO_PROJ_DESC.itemsize, APOLLO_FINISH_TENSOR.itemsize,
-                   LAG_TENSOR.itemsize, ctypes.sizeof(ApolloRule)]
+                   LAG_TENSOR.itemsize, ctypes.sizeof(ApolloRule), APOLLO_APPLY_TENSOR.itemsize]
         for i, mine in enumerate(mirrors):
             theirs = handle.af8_struct_size(i)
             if theirs != mine:

@@ -24,6 +24,7 @@ extern "C" int32_t af8_struct_size(int32_t index)
         (int32_t)sizeof(af8_factored_tensor), (int32_t)sizeof(af8_factored_cfg),
         (int32_t)sizeof(af8_apollo_scalars_in), (int32_t)sizeof(af8_apollo_scalars), (int32_t)sizeof(af8_apollo_proj_desc),
         (int32_t)sizeof(af8_apollo_finish_tensor), (int32_t)sizeof(af8_lag_tensor), (int32_t)sizeof(af8_apollo_rule),
+        (int32_t)sizeof(af8_apollo_apply_tensor),
     };
     if (index < 0 || index >= (int32_t)(sizeof(sizes) / sizeof(sizes[0]))) return -1;
     return sizes[index];

@@ -493,15 +493,90 @@ apollo_apply_kernel(float *param, const void *grad, int grad_dtype, int negate, 
     }
 }
 
-#ifndef AF8_APOLLO_APPLY_PREFETCH
-#define AF8_APOLLO_APPLY_PREFETCH 0     /* iterations ahead that the write-back requests from L2; 0: off */
-#endif
-#ifndef AF8_APOLLO_APPLY_RUNS
-#define AF8_APOLLO_APPLY_RUNS 0         /* 1: a CTA walks one contiguous run of chunks; 0: grid-stride */
-#endif
-// the same with 8 consecutive elements per thread and 128-bit accesses (cols % 8 == 0,
-// 16-byte aligned arrays, fewer than 2^34 elements)
+// 8 consecutive elements (group grp of the tensor) with 128-bit accesses (cols % 8 == 0, 16-byte aligned arrays,
+// fewer than 2^34 elements); gpr: groups per row, st: the tensor-wise factor
 // LOWP: the parameter is bf16 / fp16 (8 of them in one 128-bit word); P is ignored otherwise
+template <bool BF16, bool LOWP>
+__device__ __forceinline__ void apollo_apply_group(void *__restrict__ param_v, const void *__restrict__ grad, int negate,
+                                                   const float *__restrict__ sf, float st, float us, float fs, uint32_t gpr, uint32_t grp,
+                                                   int right, int scale_tensor, int fira, int front, float sqrt_scale, float decay,
+                                                   int has_decay, const ApolloLowp &P, uint16_t *__restrict__ param_copy)
+{
+    float *const param = static_cast<float *>(param_v);
+    const uint32_t row = grp / gpr, c8 = (grp - row * gpr) << 3;
+    const int64_t idx = (int64_t)grp << 3;
+    float g[8], f[8], pv[8];
+    if (BF16) {
+        const uint4 a = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(grad) + idx));
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { g[2 * k] = __uint_as_float(w[k] << 16); g[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+    } else {
+        const float4 a = __ldcs(reinterpret_cast<const float4 *>(static_cast<const float *>(grad) + idx));
+        const float4 b = __ldcs(reinterpret_cast<const float4 *>(static_cast<const float *>(grad) + idx) + 1);
+        g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+    }
+    if (scale_tensor) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = st;
+    } else if (right) {
+        const float fr = __ldg(sf + row);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = fr;
+    } else {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(sf + c8)), b = __ldg(reinterpret_cast<const float4 *>(sf + c8) + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    if (LOWP) {
+        uint4 *ph = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(param_v) + idx);
+        const uint4 pw = *ph;
+        const uint32_t w[4] = {pw.x, pw.y, pw.z, pw.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const uint32_t h = (e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffffu);
+            const float p = P.dtype == AF8_BF16 ? bf16_bits_to_f32(h) : f16_bits_to_f32(h);
+            float ge = g[e];
+            if (!isfinite(ge)) ge = 0.0f;
+            if (negate) ge = -ge;
+            float fe = f[e];
+            if (fira) fe = __fmul_rn(fe, fs);
+            if (!front) fe = __fmul_rn(fe, sqrt_scale);
+            const uint32_t r = apollo_lowp_bits(p, ge, fe, us, decay, has_decay, scale_tensor, P, idx + e);
+            if (e & 1) o[e >> 1] |= r << 16; else o[e >> 1] = r;
+        }
+        *ph = make_uint4(o[0], o[1], o[2], o[3]);
+        return;
+    }
+    float4 *pp = reinterpret_cast<float4 *>(param + idx);
+    const float4 p0 = pp[0], p1 = pp[1];
+    pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
+    // pairs of elements in packed binary32 arithmetic (each component rounds like the scalar operation)
+    const float2 fs2 = bc2(fs), ss2 = bc2(sqrt_scale), us2 = bc2(us), decay2 = bc2(decay);
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+        float2 ge = make_float2(isfinite(g[e]) ? g[e] : 0.0f, isfinite(g[e + 1]) ? g[e + 1] : 0.0f);   // optimizer.py:2606
+        if (negate) ge = make_float2(-ge.x, -ge.y);
+        float2 fe = make_float2(f[e], f[e + 1]);
+        if (fira) fe = __fmul2_rn(fe, fs2);                              // optimizer.py:2994
+        if (!front) fe = __fmul2_rn(fe, ss2);                            // optimizer.py:3000
+        float2 x = make_float2(pv[e], pv[e + 1]);
+        if (has_decay) x = __fmul2_rn(x, decay2);                        // optimizer.py:3075
+        if (scale_tensor) x = __ffma2_rn(__fmul2_rn(us2, fe), ge, x);    // optimizer.py:3079
+        else x = __ffma2_rn(__fmul2_rn(us2, ge), fe, x);                 // optimizer.py:3077
+        pv[e] = x.x; pv[e + 1] = x.y;
+    }
+    pp[0] = make_float4(pv[0], pv[1], pv[2], pv[3]);
+    pp[1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
+    if (param_copy) {                                                    // bf16 compute copy, round to nearest
+        uint32_t o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = f32_to_bf16_rn_bits(pv[2 * k]) | (f32_to_bf16_rn_bits(pv[2 * k + 1]) << 16);
+        *reinterpret_cast<uint4 *>(param_copy + idx) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// one tensor, grid-stride over its groups
 template <bool BF16, bool LOWP>
 __global__ void __launch_bounds__(256)
 apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ grad, int negate, const float *__restrict__ sf,
@@ -509,105 +584,61 @@ apollo_apply_vec_kernel(void *__restrict__ param_v, const void *__restrict__ gra
                         int fira, int front, float sqrt_scale, float decay, int has_decay, const ApolloLowp P,
                         uint16_t *__restrict__ param_copy)
 {
-    float *const param = static_cast<float *>(param_v);
     const float us = sc->update_scale, fs = sc->fira;
     if (has_decay == 2) decay = sc->decay;               // computed on the device (parameter-scaled step)
     const uint32_t gpr = (uint32_t)(cols >> 3);                 // groups of 8 per row
     const uint32_t ngroups = (uint32_t)((rows * cols) >> 3);
     const float st = scale_tensor ? __ldg(sf) : 0.0f;
-#if AF8_APOLLO_APPLY_RUNS
-    // every CTA takes one contiguous run of 2048-element chunks
-    const uint32_t nchunks = (ngroups + 255u) / 256u;
-    const uint32_t per_cta = (nchunks + gridDim.x - 1) / gridDim.x;
-    const uint32_t limit = min((uint64_t)ngroups, (uint64_t)(blockIdx.x + 1) * per_cta * 256u);
-    const uint32_t first = blockIdx.x * per_cta * 256u + threadIdx.x, stride = 256u;
-#else
-    const uint32_t limit = ngroups, first = blockIdx.x * 256u + threadIdx.x, stride = gridDim.x * 256u;
-#endif
-    for (uint32_t grp = first; grp < limit; grp += stride) {
-        const uint32_t row = grp / gpr, c8 = (grp - row * gpr) << 3;
-        const int64_t idx = (int64_t)grp << 3;
-#if AF8_APOLLO_APPLY_PREFETCH > 0
-        {   // ask L2 for what this thread reads a few iterations on: one request per 128-byte line
-            const uint64_t ahead = (uint64_t)grp + (uint64_t)AF8_APOLLO_APPLY_PREFETCH * stride;
-            if (ahead < limit) {
-                const int64_t pidx = (int64_t)ahead << 3;
-                if ((threadIdx.x & (BF16 ? 7 : 3)) == 0)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(grad) + pidx * (BF16 ? 2 : 4)));
-                if ((threadIdx.x & (LOWP ? 7 : 3)) == 0)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char *>(param_v) + pidx * (LOWP ? 2 : 4)));
-            }
+    for (uint32_t grp = blockIdx.x * 256u + threadIdx.x; grp < ngroups; grp += gridDim.x * 256u)
+        apollo_apply_group<BF16, LOWP>(param_v, grad, negate, sf, st, us, fs, gpr, grp, right, scale_tensor, fira, front, sqrt_scale,
+                                       decay, has_decay, P, param_copy);
+}
+
+// all tensors of a table in one launch: a CTA takes chunks of 2048 elements (256 groups) in grid-stride order over
+// the whole table and keeps the descriptor of its current tensor in shared memory
+__device__ __forceinline__ int find_apply_chunk(const af8_apollo_apply_tensor *t, int n, int64_t id)
+{
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(&t[mid].first_chunk) <= id) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+template <bool BF16, bool LOWP>
+__global__ void __launch_bounds__(256)
+apollo_apply_batch_kernel(const af8_apollo_apply_tensor *__restrict__ tensors, int n, int64_t total_chunks, int negate, int param_dtype)
+{
+    __shared__ af8_apollo_apply_tensor sT;
+    static_assert(sizeof(af8_apollo_apply_tensor) % 4 == 0 && sizeof(af8_apollo_apply_tensor) / 4 <= 256, "descriptor copy");
+    const int tid = threadIdx.x;
+    int cur_t = -1;
+    float us = 0.0f, fs = 0.0f, decay = 0.0f, st = 0.0f;
+    uint32_t gpr = 1, ngroups = 0;
+    int right = 0;
+    ApolloLowp P{param_dtype, 0, 0};
+    for (int64_t id = blockIdx.x; id < total_chunks; id += gridDim.x) {
+        int t = cur_t;
+        if (t < 0) t = find_apply_chunk(tensors, n, id);
+        else while (t + 1 < n && __ldg(&tensors[t + 1].first_chunk) <= id) ++t;
+        if (t != cur_t) {                                        // (uniform over the CTA)
+            __syncthreads();                                     // every thread has left the previous tensor
+            if (tid < (int)(sizeof(af8_apollo_apply_tensor) / 4))
+                reinterpret_cast<uint32_t *>(&sT)[tid] = __ldg(reinterpret_cast<const uint32_t *>(tensors + t) + tid);
+            cur_t = t;
+            __syncthreads();
+            us = sT.scalars->update_scale; fs = sT.scalars->fira;
+            decay = sT.has_decay == 2 ? sT.scalars->decay : sT.decay;    // 2: computed on the device (parameter-scaled step)
+            gpr = (uint32_t)(sT.cols >> 3);
+            ngroups = (uint32_t)((sT.rows * sT.cols) >> 3);
+            right = sT.rows >= sT.cols;
+            st = sT.scale_tensor ? __ldg(sT.sf) : 0.0f;
+            P.sr = sT.stochastic_round; P.sr_base = sT.sr_base;
         }
-#endif
-        float g[8], f[8], pv[8];
-        if (BF16) {
-            const uint4 a = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(grad) + idx));
-            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { g[2 * k] = __uint_as_float(w[k] << 16); g[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
-        } else {
-            const float4 a = __ldcs(reinterpret_cast<const float4 *>(static_cast<const float *>(grad) + idx));
-            const float4 b = __ldcs(reinterpret_cast<const float4 *>(static_cast<const float *>(grad) + idx) + 1);
-            g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
-        }
-        if (scale_tensor) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = st;
-        } else if (right) {
-            const float fr = __ldg(sf + row);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = fr;
-        } else {
-            const float4 a = __ldg(reinterpret_cast<const float4 *>(sf + c8)), b = __ldg(reinterpret_cast<const float4 *>(sf + c8) + 1);
-            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-        }
-        if (LOWP) {
-            uint4 *ph = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(param_v) + idx);
-            const uint4 pw = *ph;
-            const uint32_t w[4] = {pw.x, pw.y, pw.z, pw.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const uint32_t h = (e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffffu);
-                const float p = P.dtype == AF8_BF16 ? bf16_bits_to_f32(h) : f16_bits_to_f32(h);
-                float ge = g[e];
-                if (!isfinite(ge)) ge = 0.0f;
-                if (negate) ge = -ge;
-                float fe = f[e];
-                if (fira) fe = __fmul_rn(fe, fs);
-                if (!front) fe = __fmul_rn(fe, sqrt_scale);
-                const uint32_t r = apollo_lowp_bits(p, ge, fe, us, decay, has_decay, scale_tensor, P, idx + e);
-                if (e & 1) o[e >> 1] |= r << 16; else o[e >> 1] = r;
-            }
-            *ph = make_uint4(o[0], o[1], o[2], o[3]);
-            continue;
-        }
-        float4 *pp = reinterpret_cast<float4 *>(param + idx);
-        const float4 p0 = pp[0], p1 = pp[1];
-        pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
-        // pairs of elements in packed binary32 arithmetic (each component rounds like the scalar operation)
-        const float2 fs2 = bc2(fs), ss2 = bc2(sqrt_scale), us2 = bc2(us), decay2 = bc2(decay);
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-            float2 ge = make_float2(isfinite(g[e]) ? g[e] : 0.0f, isfinite(g[e + 1]) ? g[e + 1] : 0.0f);   // optimizer.py:2606
-            if (negate) ge = make_float2(-ge.x, -ge.y);
-            float2 fe = make_float2(f[e], f[e + 1]);
-            if (fira) fe = __fmul2_rn(fe, fs2);                              // optimizer.py:2994
-            if (!front) fe = __fmul2_rn(fe, ss2);                            // optimizer.py:3000
-            float2 x = make_float2(pv[e], pv[e + 1]);
-            if (has_decay) x = __fmul2_rn(x, decay2);                        // optimizer.py:3075
-            if (scale_tensor) x = __ffma2_rn(__fmul2_rn(us2, fe), ge, x);    // optimizer.py:3079
-            else x = __ffma2_rn(__fmul2_rn(us2, ge), fe, x);                 // optimizer.py:3077
-            pv[e] = x.x; pv[e + 1] = x.y;
-        }
-        pp[0] = make_float4(pv[0], pv[1], pv[2], pv[3]);
-        pp[1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
-        if (param_copy) {                                                    // bf16 compute copy, round to nearest
-            uint32_t o[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) o[k] = f32_to_bf16_rn_bits(pv[2 * k]) | (f32_to_bf16_rn_bits(pv[2 * k + 1]) << 16);
-            *reinterpret_cast<uint4 *>(param_copy + idx) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
+        const uint32_t grp = (uint32_t)(id - sT.first_chunk) * 256u + (uint32_t)tid;
+        if (grp < ngroups)
+            apollo_apply_group<BF16, LOWP>(sT.param, sT.grad, negate, sT.sf, st, us, fs, gpr, grp, right, sT.scale_tensor, sT.fira,
+                                           sT.scale_front, sT.sqrt_scale, decay, sT.has_decay, P, static_cast<uint16_t *>(sT.param_copy));
     }
 }
 
@@ -1042,6 +1073,65 @@ extern "C" int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stocha
     apollo_apply_kernel<<<(int)g, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<float *>(param), grad, grad_dtype, negate, sf, scalars, rows, cols, rows >= cols ? 1 : 0,
         in->scale_tensor, in->fira, in->scale_front, in->sqrt_scale, decay, has_decay, pc);
+    AF8_CUDA_TRY(cudaGetLastError());
+    return AF8_OK;
+}
+
+extern "C" int af8_apollo_apply_batch(const af8_apollo_apply_tensor *host_tensors, af8_apollo_apply_tensor *dev_tensors,
+                                      int32_t n, int64_t total_chunks, int32_t param_dtype, int32_t grad_dtype,
+                                      int32_t negate, void *stream)
+{
+    using namespace af8;
+    if (!host_tensors || !dev_tensors || n <= 0) return fail(AF8_ERR_INVALID, "af8_apollo_apply_batch: null table or n <= 0");
+    if (grad_dtype != AF8_F32 && grad_dtype != AF8_BF16) return fail(AF8_ERR_UNSUPPORTED, "af8_apollo_apply_batch: gradients must be fp32 or bf16");
+    if (param_dtype != AF8_F32 && param_dtype != AF8_BF16 && param_dtype != AF8_F16)
+        return fail(AF8_ERR_INVALID, "af8_apollo_apply_batch: bad param_dtype %d", param_dtype);
+    bool vec = true;
+    int64_t chunks = 0;
+    for (int i = 0; i < n; ++i) {
+        const af8_apollo_apply_tensor &T = host_tensors[i];
+        if (!T.param || !T.grad || !T.sf || !T.scalars || T.rows <= 0 || T.cols <= 0)
+            return fail(AF8_ERR_INVALID, "af8_apollo_apply_batch: tensor %d: null pointer or empty shape", i);
+        if (T.param_copy && (param_dtype != AF8_F32 || !aligned16(T.param_copy)))
+            return fail(AF8_ERR_INVALID, "af8_apollo_apply_batch: tensor %d: param_copy needs fp32 parameters and a 16-byte aligned address", i);
+        if (T.stochastic_round && param_dtype == AF8_F32)
+            return fail(AF8_ERR_INVALID, "af8_apollo_apply_batch: stochastic rounding applies to bf16 / fp16 parameters only");
+        if (T.has_decay < 0 || T.has_decay > 2) return fail(AF8_ERR_INVALID, "af8_apollo_apply_batch: tensor %d: bad has_decay %d", i, T.has_decay);
+        if (T.first_chunk != chunks) return fail(AF8_ERR_INVALID, "af8_apollo_apply_batch: tensor %d: first_chunk out of sequence", i);
+        const int64_t numel = T.rows * T.cols;
+        chunks += (numel + 2047) / 2048;
+        const bool right = T.rows >= T.cols;
+        if (!(T.cols % 8 == 0 && numel < ((int64_t)1 << 34) && aligned16(T.param) && aligned16(T.grad) &&
+              (right || T.scale_tensor || aligned16(T.sf))))
+            vec = false;
+    }
+    if (chunks != total_chunks) return fail(AF8_ERR_INVALID, "af8_apollo_apply_batch: total_chunks does not match the table");
+    if (!vec) {                                  // tensor by tensor
+        for (int i = 0; i < n; ++i) {
+            const af8_apollo_apply_tensor &T = host_tensors[i];
+            af8_apollo_scalars_in in;
+            memset(&in, 0, sizeof(in));
+            in.scale_tensor = T.scale_tensor; in.fira = T.fira; in.scale_front = T.scale_front; in.sqrt_scale = T.sqrt_scale;
+            const int rc = af8_apollo_apply(T.param, param_dtype, T.stochastic_round, T.sr_base, T.grad, grad_dtype, negate, T.sf,
+                                            T.scalars, T.rows, T.cols, &in, T.decay, T.has_decay, T.param_copy, stream);
+            if (rc != AF8_OK) return rc;
+        }
+        return AF8_OK;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    AF8_CUDA_TRY(cudaMemcpyAsync(dev_tensors, host_tensors, sizeof(af8_apollo_apply_tensor) * (size_t)n, cudaMemcpyHostToDevice, st));
+    const bool lowp = param_dtype != AF8_F32;
+    // one wave of resident CTAs, each walking the table in grid-stride order
+#define AF8_APOLLO_APPLY_BATCH(B, L) do { \
+        static int per_sm = 0; \
+        if (per_sm == 0 && (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, apollo_apply_batch_kernel<B, L>, 256, 0) != cudaSuccess || per_sm <= 0)) \
+            per_sm = 4; \
+        const int64_t g = total_chunks < 148 * (int64_t)per_sm ? total_chunks : 148 * (int64_t)per_sm; \
+        apollo_apply_batch_kernel<B, L><<<(int)g, 256, 0, st>>>(dev_tensors, n, total_chunks, negate, param_dtype); \
+    } while (0)
+    if (grad_dtype == AF8_BF16) { if (lowp) AF8_APOLLO_APPLY_BATCH(true, true); else AF8_APOLLO_APPLY_BATCH(true, false); }
+    else { if (lowp) AF8_APOLLO_APPLY_BATCH(false, true); else AF8_APOLLO_APPLY_BATCH(false, false); }
+#undef AF8_APOLLO_APPLY_BATCH
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
 }

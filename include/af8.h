@@ -532,6 +532,29 @@ AF8_API int af8_apollo_apply(void *param, int32_t param_dtype, int32_t stochasti
                              const af8_apollo_scalars_in *in, float decay, int32_t has_decay, void *param_copy,
                              void *stream);
 
+/* af8_apollo_apply for all tensors of a group in one launch (the reference writes back tensor by tensor,
+ * optimizer.py:3043-3079; one launch keeps the memory system busy across the tensors' ends).  Every field as
+ * the argument of the same name of af8_apollo_apply; scale_tensor, fira, scale_front and sqrt_scale as in
+ * af8_apollo_scalars_in.  first_chunk numbers 2048-element chunks across the table, ceil(rows*cols / 2048)
+ * per tensor, and total_chunks is their count.  host_tensors is pinned and stays valid until the copy has
+ * run; dev_tensors holds n entries.  A table with a tensor that the 128-bit path cannot take (cols % 8 != 0,
+ * an unaligned array, 2^34 elements or more) is applied tensor by tensor through af8_apollo_apply. */
+typedef struct af8_apollo_apply_tensor {
+    void *param;
+    const void *grad;
+    const float *sf;
+    const af8_apollo_scalars *scalars;
+    void *param_copy;           /* NULL for none */
+    int64_t rows, cols;
+    int64_t first_chunk;
+    uint64_t sr_base;
+    float sqrt_scale, decay;
+    int32_t scale_tensor, fira, scale_front, has_decay, stochastic_round, reserved;
+} af8_apollo_apply_tensor;
+AF8_API int af8_apollo_apply_batch(const af8_apollo_apply_tensor *host_tensors, af8_apollo_apply_tensor *dev_tensors,
+                                   int32_t n, int64_t total_chunks, int32_t param_dtype, int32_t grad_dtype,
+                                   int32_t negate, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* APOLLO: further low-rank state rules                                      */
 /* ------------------------------------------------------------------------ */

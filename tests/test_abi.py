@@ -49,6 +49,7 @@ def test_struct_sizes_match_header():
     assert _native.NORM_TENSOR.itemsize == 64
     assert _native.SCALE_TENSOR.itemsize == 64
     assert ctypes.sizeof(_native.FullrankCfg) == 48
+    assert _native.APOLLO_APPLY_TENSOR.itemsize == 104
 
 
 def test_bad_arguments_are_rejected_without_a_gpu():

@@ -287,3 +287,77 @@ def test_projection_is_correctly_rounded():
         assert np.array_equal(got, want)
         want_ch = (gc.astype(np.float32).astype(np.float64) ** 2).astype(np.float32).astype(np.float64).sum(axis=1 if right else 0)
         assert np.allclose(chan.cpu().numpy(), want_ch, rtol=1e-12)
+
+
+@pytest.mark.parametrize("param_dtype,grad_dtype", [("f32", "bf16"), ("f32", "f32"), ("bf16", "bf16")])
+@pytest.mark.parametrize("aligned", [True, False], ids=["vector_path", "one_odd_tensor"])
+def test_apply_batch_equals_per_tensor_calls(param_dtype, grad_dtype, aligned):
+    """af8_apollo_apply_batch writes what af8_apollo_apply writes tensor by tensor, bit for bit: right- and
+    left-case tensors, channel- and tensor-wise scaling, every decay mode, a bf16 compute copy, a tensor that
+    ends inside a 2048-element chunk; with one tensor whose columns are no multiple of 8 the table takes the
+    per-tensor route."""
+    import ctypes
+    from adafactor8bit import _native as N
+    lib = N.lib()
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(77)
+    shapes = [(512, 256), (64, 1032), (264, 136), (96, 2048), (40, 72)]
+    if not aligned:
+        shapes[2] = (250, 36)
+    pdt = dict(f32=torch.float32, bf16=torch.bfloat16)[param_dtype]
+    gdt = dict(f32=torch.float32, bf16=torch.bfloat16)[grad_dtype]
+    n = len(shapes)
+    p0 = [torch.randn(s, generator=gen).to(pdt).to(dev) for s in shapes]
+    grads = [(torch.randn(s, generator=gen) * 0.01).to(gdt).to(dev) for s in shapes]
+    grads[0][3, 5] = float("inf")                     # non-finite gradients count as zero
+    sfs = [(torch.rand(max(s), generator=gen) + 0.5).to(dev) for s in shapes]
+    scal = torch.zeros(n, 4, dtype=torch.float32)
+    scal[:, 0] = -torch.rand(n, generator=gen) * 1e-2     # update_scale
+    scal[:, 1] = 0.5 + torch.rand(n, generator=gen)       # fira
+    scal[:, 3] = 0.99                                     # decay computed on the device
+    scal = scal.to(dev)
+    sins = []
+    for i in range(n):
+        sin = N.ApolloScalarsIn()
+        sin.scale_tensor, sin.fira, sin.scale_front, sin.sqrt_scale = int(i == 3), int(i % 2 == 0), int(i == 1), 1.25
+        sins.append(sin)
+    decay = [0.999, 0.0, 0.98, 0.0, 0.97]
+    has_decay = [1, 0, 2, 0, 1]
+    sr = [int(param_dtype != "f32" and i == 4) for i in range(n)]
+    copies = [torch.zeros(s, dtype=torch.bfloat16, device=dev) if (param_dtype == "f32" and i in (0, 3)) else None
+              for i, s in enumerate(shapes)]
+    PD, GD = dict(f32=N.F32, bf16=N.BF16)[param_dtype], dict(f32=N.F32, bf16=N.BF16)[grad_dtype]
+    s = torch.cuda.current_stream(dev).cuda_stream
+
+    want_p = [p.clone() for p in p0]
+    want_c = [c.clone() if c is not None else None for c in copies]
+    for i in range(n):
+        N.check(lib.af8_apollo_apply(want_p[i].data_ptr(), PD, sr[i], 1234 + i, grads[i].data_ptr(), GD, 1, sfs[i].data_ptr(),
+                                     scal.data_ptr() + 16 * i, shapes[i][0], shapes[i][1], ctypes.byref(sins[i]), decay[i],
+                                     has_decay[i], want_c[i].data_ptr() if want_c[i] is not None else None, s), "af8_apollo_apply")
+    got_p = [p.clone() for p in p0]
+    got_c = [c.clone() if c is not None else None for c in copies]
+    host = torch.zeros(n * N.APOLLO_APPLY_TENSOR.itemsize, dtype=torch.uint8).pin_memory()
+    devt = torch.empty(n * N.APOLLO_APPLY_TENSOR.itemsize, dtype=torch.uint8, device=dev)
+    t = np.frombuffer(host.numpy(), dtype=N.APOLLO_APPLY_TENSOR, count=n)
+    first = 0
+    for i in range(n):
+        t["param"][i], t["grad"][i], t["sf"][i] = got_p[i].data_ptr(), grads[i].data_ptr(), sfs[i].data_ptr()
+        t["scalars"][i] = scal.data_ptr() + 16 * i
+        t["param_copy"][i] = got_c[i].data_ptr() if got_c[i] is not None else 0
+        t["rows"][i], t["cols"][i], t["first_chunk"][i] = shapes[i][0], shapes[i][1], first
+        first += (shapes[i][0] * shapes[i][1] + 2047) // 2048
+        t["sr_base"][i], t["stochastic_round"][i] = 1234 + i, sr[i]
+        t["sqrt_scale"][i], t["decay"][i], t["has_decay"][i] = sins[i].sqrt_scale, decay[i], has_decay[i]
+        t["scale_tensor"][i], t["fira"][i], t["scale_front"][i] = sins[i].scale_tensor, sins[i].fira, sins[i].scale_front
+    N.check(lib.af8_apollo_apply_batch(host.data_ptr(), devt.data_ptr(), n, first, PD, GD, 1, s), "af8_apollo_apply_batch")
+    torch.cuda.synchronize(dev)
+    for i in range(n):
+        assert not torch.equal(want_p[i], p0[i])
+        assert torch.equal(got_p[i].view(torch.int16 if pdt == torch.bfloat16 else torch.int32),
+                           want_p[i].view(torch.int16 if pdt == torch.bfloat16 else torch.int32)), shapes[i]
+        if want_c[i] is not None:
+            assert torch.equal(got_c[i].view(torch.int16), want_c[i].view(torch.int16)), shapes[i]
+    # a table whose chunk numbering is wrong is refused before anything is launched
+    t["first_chunk"][1] += 1
+    assert lib.af8_apollo_apply_batch(host.data_ptr(), devt.data_ptr(), n, first, PD, GD, 1, s) == N.ERR_INVALID
