@@ -742,9 +742,21 @@ class FactoredPlan:
     def _stats(self, mode, host_buf, stream, x=None):
         self.cfg.mode = mode
         lib = N.lib()
-        self._log("stats_gradsq" if mode == N.FSTAT_GRADSQ else "stats_residual", lambda: N.check(
-            lib.af8_factored_stats(ctypes.byref(self.cfg), self.d_table.data_ptr(), host_buf.data_ptr(), self.n,
-                                   self.d_dyn.data_ptr(), stream.cuda_stream), "af8_factored_stats"), stream)
+        if mode == N.FSTAT_RESIDUAL:
+            # room for two tensor maps (128 bytes each) per entry: with them the library brings the rows in as boxes
+            if getattr(self, "h_maps", None) is None:
+                self.h_maps = _PinnedRing(self.n * 256)
+                self.d_maps = torch.empty(self.n * 256, dtype=torch.uint8, device=self.device)
+            hm = self.h_maps.next()
+            self._log("stats_residual", lambda: N.check(
+                lib.af8_factored_stats_boxes(ctypes.byref(self.cfg), self.d_table.data_ptr(), host_buf.data_ptr(), self.n,
+                                             self.d_dyn.data_ptr(), hm.data_ptr(), self.d_maps.data_ptr(), stream.cuda_stream),
+                "af8_factored_stats_boxes"), stream)
+            self.h_maps.mark(stream)
+        else:
+            self._log("stats_gradsq", lambda: N.check(
+                lib.af8_factored_stats(ctypes.byref(self.cfg), self.d_table.data_ptr(), host_buf.data_ptr(), self.n,
+                                       self.d_dyn.data_ptr(), stream.cuda_stream), "af8_factored_stats"), stream)
         if x is not None:
             for i in self.cut:                  # the entry's rows and its column partial sums join the whole tensor's
                 a, ln = int(self._sums_off[i]), int(self._vec_len[i])

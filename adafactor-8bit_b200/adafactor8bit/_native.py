@@ -175,6 +175,7 @@ PROTOTYPES = {
     "af8_factored_tile_cols": (_c_i, []),
     "af8_factored_upload": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_p, _c_i, _c_p]),
     "af8_factored_stats": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_p, _c_i, _c_p, _c_p]),
+    "af8_factored_stats_boxes": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_p, _c_i, _c_p, _c_p, _c_p, _c_p]),
     "af8_factored_small": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_i, _c_i, _c_p]),
     "af8_factored_update": (_c_i, [ctypes.POINTER(FactoredCfg), _c_p, _c_i, _c_l, _c_p, _c_p, _c_p]),
     "af8_apollo_project": (_c_i, [_c_p, _c_i, _c_i, _c_p, _c_l, _c_l, _c_l, _c_p, _c_p, _c_p]),

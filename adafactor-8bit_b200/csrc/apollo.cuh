@@ -776,23 +776,6 @@ inline int apollo_project_prepare(const af8_apollo_proj_desc &d, int32_t grad_dt
     return AF8_OK;
 }
 
-// cuTensorMapEncodeTiled, fetched through the runtime so that the library needs no link-time
-// dependency on the driver library
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-inline EncodeTiledFn encode_tiled_fn()
-{
-    static EncodeTiledFn fn = []() -> EncodeTiledFn {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
 // the two tensor maps of a tcgen05 task: G as [M][K] with boxes of 128 x 32, the planes as
 // [3][N][K] with boxes of 3 x N x 32, both with the 64-byte swizzle and zero fill outside
 inline int apollo_umma_maps(UmmaTask &u)

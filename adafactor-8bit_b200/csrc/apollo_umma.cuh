@@ -39,6 +39,7 @@
 
 #include "common.cuh"
 #include "fullrank_fast.cuh"     // mbarrier helpers, g_device_error
+#include "tensormap.cuh"         // tiled bulk tensor copies
 #include "apollo_mma.cuh"        // ProjTask, clean_chunk
 
 namespace af8 {
@@ -91,18 +92,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// tiled bulk tensor copies global -> shared, completion as transaction bytes on `bar`
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
-}
-
 // G[R][C] (bf16) -> G^T[C][R], non-finite entries replaced by zero (optimizer.py:2606).
 // 64 x 64 tiles.  A thread transposes 2 x 2 blocks in registers (two 32-bit loads from neighbouring
 // rows become the two 32-bit words of neighbouring output rows), so shared memory only moves whole

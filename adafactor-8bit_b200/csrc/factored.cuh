@@ -27,6 +27,7 @@
 #include "fullrank_fast.cuh"
 #include "fullrank_generic.cuh"
 #include "fullrank_stat.cuh"
+#include "tensormap.cuh"
 
 namespace af8 {
 
@@ -898,6 +899,108 @@ __device__ __forceinline__ bool residual_rows_ring(const FactoredLaunch &L, cons
     return true;
 }
 
+// The same pass with the input of FBOX_ROWS consecutive rows per copy: one tiled bulk tensor copy brings their
+// 256-column slices of the gradient (tensor map maps[0]: bf16 [rows][cols], box 256 x FBOX_ROWS), one their UF8 codes
+// (maps[1]: bytes, same box) into a stage of the warp's two-stage ring, so that the instructions of a request -
+// about 57 issue slots with one lane active - are spent once per FBOX_ROWS rows instead of once per row.  Warp w
+// takes the row groups r0 + FBOX_ROWS (w + 8 k); rows past the end of the tensor arrive as zeros and are skipped.
+// bf16 gradients only (a stage is 3 KB; the two stages fill the ring's 6 KB per warp).
+constexpr int FBOX_ROWS = 4, FBOX_STAGES = 2;
+constexpr int FBOX_G_BYTES = FBOX_ROWS * 512, FBOX_STAGE_BYTES = FBOX_G_BYTES + FBOX_ROWS * 256;
+static_assert(FBOX_STAGES * FBOX_STAGE_BYTES <= sring_stages<bf16_tag>() * sring_stage_bytes<bf16_tag, true>(), "the boxes use the ring's memory");
+static_assert(FSTAT_ROWS % (8 * FBOX_ROWS) == 0, "whole row groups per warp and tile");
+
+template <bool ONE, bool SMALL>
+__device__ __forceinline__ bool residual_rows_box(const FactoredLaunch &L, const af8_factored_tensor &sT, const CUtensorMap *maps,
+                                                  int64_t r0, int64_t c0, float pre_div, const float (&ic)[8], double (&cacc)[8],
+                                                  unsigned char *ring, uint64_t *full, uint32_t &cons)
+{
+    constexpr int BR = FBOX_ROWS, NS = FBOX_STAGES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t C = sT.cols;
+    const int r_end = (int)min(sT.rows, r0 + (int64_t)FSTAT_ROWS);
+    const int row0 = (int)r0 + BR * warp;                        // first row of this warp's group 0; group g: + 8 * BR * g
+    const int ngroups = row0 < r_end ? (r_end - row0 + 8 * BR - 1) / (8 * BR) : 0;
+    auto issue = [&](int g) {                                    // lane 0: group g into its stage
+        const int sl = (int)((cons + (uint32_t)g) & (uint32_t)(NS - 1));
+        unsigned char *dst = ring + sl * FBOX_STAGE_BYTES;
+        mbar_expect_tx(&full[sl], (uint32_t)FBOX_STAGE_BYTES);
+        tma_load_2d(dst, maps, (int)c0, row0 + 8 * BR * g, &full[sl]);
+        tma_load_2d(dst + FBOX_G_BYTES, maps + 1, (int)c0, row0 + 8 * BR * g, &full[sl]);
+    };
+    if (lane == 0 && ngroups > 0) {
+        fence_proxy_async();
+        for (int g = 0; g < min(NS, ngroups); ++g) issue(g);
+    }
+    const DivBy D = make_div(pre_div);
+    const LerpW LW = make_lerp(sT.m_w);
+    const float eps = sT.eps_came, sgn = L.negate_grad ? -1.0f : 1.0f;
+    // row r: inverse row factor at index r, block absmax at r * (C / 256) + c0 / 256 (both fit 32 bits)
+    const int scrow = (int)(C >> 8), scoff = (int)(c0 >> 8);
+    float nir[2], nsc[2];                                        // the scalars of the next pair of rows
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        nir[k] = 0.0f; nsc[k] = 0.0f;
+        if (row0 + k < r_end) { nir[k] = __ldg(sT.inv_row + row0 + k); nsc[k] = __ldg(sT.m_scale + (row0 + k) * scrow + scoff); }
+    }
+    for (int g = 0; g < ngroups; ++g) {
+        const uint32_t n = cons + (uint32_t)g;
+        const int sl = (int)(n & (uint32_t)(NS - 1));
+        const bool landed = mbar_wait_bounded(&full[sl], (n / NS) & 1u);
+        if (!__all_sync(0xffffffffu, landed)) return false;
+        const unsigned char *st = ring + sl * FBOX_STAGE_BYTES;
+        const int grow = row0 + 8 * BR * g;                      // first row of the group
+#pragma unroll
+        for (int h = 0; h < BR / 2; ++h) {                       // pairs of rows: their row sums are reduced jointly
+            GradRaw8<bf16_tag> cur[2];
+            uint2 cm[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                cur[k].from_shared(st + (2 * h + k) * 512 + lane * 16);
+                cm[k] = *reinterpret_cast<const uint2 *>(st + FBOX_G_BYTES + (2 * h + k) * 256 + lane * 8);
+            }
+            if (h == BR / 2 - 1) {                               // the stage was read: it may be refilled
+                __syncwarp();
+                if (lane == 0 && g + NS < ngroups) { fence_proxy_async(); issue(g + NS); }
+            }
+            double rsum[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int r = grow + 2 * h + k;
+                double racc = 0.0;
+                const float ir = __fmul_rn(nir[k], sgn), mc = __fmul_rn(nsc[k], 0.0078125f);   // fl(scale / 128), scale >= 1e-12
+                {   // this row's successor: the same place of the next pair
+                    const int rn = (h == BR / 2 - 1) ? r + 8 * BR - (BR - 2) : r + 2;
+                    if (rn < r_end) { nir[k] = __ldg(sT.inv_row + rn); nsc[k] = __ldg(sT.m_scale + rn * scrow + scoff); }
+                }
+                if (r < r_end) {
+                    float gg[8], x[8];
+                    cur[k].unpack(0, gg);
+                    residual_x8<ONE, SMALL>(gg, cm[k], mc, ir, ic, D, LW.ww, eps, x);
+                    double pr[4];                               // (pairwise: a short dependency chain)
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {
+                        const double xa = (double)x[j], xb = (double)x[j + 1];
+                        cacc[j] += xa;
+                        cacc[j + 1] += xb;
+                        pr[j >> 1] = xa + xb;
+                    }
+                    racc = (pr[0] + pr[1]) + (pr[2] + pr[3]);
+                }
+                rsum[k] = racc;
+            }
+            const bool hi = lane & 16;
+            double v = (hi ? rsum[1] : rsum[0]) + __shfl_xor_sync(0xffffffffu, hi ? rsum[0] : rsum[1], 16);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            const int rr = grow + 2 * h + (lane >> 4);
+            if ((lane & 15) == 0 && rr < r_end) atomicAdd(sT.row_sum + rr, v);
+        }
+    }
+    cons += (uint32_t)ngroups;
+    return true;
+}
+
 // RESIDUAL: CAME's (U - M)^2 + eps statistic; otherwise g^2 (separate instantiations, so that
 // the lighter one keeps its lower register count)
 // resident CTAs asked of the compiler (measured on B200: 3 for both passes; the g*g pass went
@@ -916,7 +1019,7 @@ __device__ __forceinline__ bool residual_rows_ring(const FactoredLaunch &L, cons
 #endif
 template <typename GradT, bool RESIDUAL>
 __global__ void __launch_bounds__(256, RESIDUAL ? AF8_FSTAT_MIN_CTAS_RES : AF8_FSTAT_MIN_CTAS)
-factored_stats_vec_kernel(const FactoredLaunch L, const int use_ring)
+factored_stats_vec_kernel(const FactoredLaunch L, const int use_ring, const CUtensorMap *__restrict__ maps)
 {
     __shared__ double s_col[8][FSTAT_COLS];      // [warp][j * 32 + lane]
     __shared__ af8_factored_tensor sT;
@@ -974,8 +1077,19 @@ factored_stats_vec_kernel(const FactoredLaunch L, const int use_ring)
                 unsigned char *ring = sr_smem + (size_t)warp * sring_stages<GradT>() * sring_stage_bytes<GradT, true>();
                 constexpr int NB = AF8_FSTAT_RES_NB;
                 const bool one = pre_div == 1.0f, small = fabsf(sT.m_w) < 0.5f;  // (uniform over the tensor)
-                bool ok;
-                if (one) ok = small ? residual_rows_ring<GradT, NB, true, true>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)
+                bool ok = true, boxes = false;
+                if constexpr (std::is_same<GradT, bf16_tag>::value) {
+                if (use_ring == 2) {                                             // boxes of rows through tensor maps
+                    boxes = true;
+                    const CUtensorMap *mp = maps + 2 * t;
+                    if (one) ok = small ? residual_rows_box<true, true>(L, sT, mp, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)
+                                        : residual_rows_box<true, false>(L, sT, mp, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons);
+                    else ok = small ? residual_rows_box<false, true>(L, sT, mp, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)
+                                    : residual_rows_box<false, false>(L, sT, mp, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons);
+                }
+                }
+                if (boxes) { }
+                else if (one) ok = small ? residual_rows_ring<GradT, NB, true, true>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)
                                     : residual_rows_ring<GradT, NB, true, false>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons);
                 else ok = small ? residual_rows_ring<GradT, NB, false, true>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons)
                                 : residual_rows_ring<GradT, NB, false, false>(L, sT, r0, c0, pre_div, ic, cacc, ring, s_full[warp], cons);
@@ -1900,9 +2014,31 @@ extern "C" int af8_factored_upload(const af8_factored_cfg *cfg, const af8_factor
     return AF8_OK;
 }
 
-extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
-                                  const af8_factored_tensor *host_tensors, int32_t n_tensors,
-                                  const af8_dyn_scalars *dyn, void *stream)
+namespace af8 {
+// the two tensor maps of a tensor for residual_rows_box: gradient (bf16) and UF8 codes as [rows][cols], boxes of
+// 256 columns x FBOX_ROWS rows, no swizzle, zeros outside
+inline int factored_box_maps(const af8_factored_tensor &t, CUtensorMap *out)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(AF8_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dim[2] = {(cuuint64_t)t.cols, (cuuint64_t)t.rows};
+    const cuuint32_t box[2] = {256, FBOX_ROWS}, es[2] = {1, 1};
+    const cuuint64_t gstride[1] = {(cuuint64_t)t.cols * 2}, mstride[1] = {(cuuint64_t)t.cols};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(t.grad), dim, gstride, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(AF8_ERR_CUDA, "cuTensorMapEncodeTiled (gradient rows) failed with %d", (int)r);
+    r = enc(out + 1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, t.m_q, dim, mstride, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(AF8_ERR_CUDA, "cuTensorMapEncodeTiled (momentum codes) failed with %d", (int)r);
+    return AF8_OK;
+}
+}  // namespace af8
+
+static int af8_factored_stats_impl(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                                   const af8_factored_tensor *host_tensors, int32_t n_tensors,
+                                   const af8_dyn_scalars *dyn, void *host_maps, void *dev_maps, void *stream)
 {
     using namespace af8;
     int rc = check_factored_cfg(cfg, "af8_factored_stats");
@@ -1933,11 +2069,33 @@ extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factore
     const bool bf = cfg->grad_dtype == AF8_BF16, res = cfg->mode == AF8_FSTAT_RESIDUAL;
     const bool vec = cfg->aligned8 && cfg->grad_dtype != AF8_F16;      // fp16 gradients take the general kernels
     static const bool ring_off = getenv("AF8_NO_FACTORED_RING") != nullptr;
-    const int ring = (ring_off || !res) ? 0 : 1;
+    static const bool box_off = getenv("AF8_NO_FACTORED_BOXES") != nullptr;
+    int ring = (ring_off || !res) ? 0 : 1;
+    // residual pass over bf16 gradients and UF8 codes of tensors with cols % 256 == 0: boxes of rows through
+    // tensor maps, when the caller has given room for the maps
+    const CUtensorMap *maps = nullptr;
+    if (ring && !box_off && vec && bf && host_maps && dev_maps && cfg->m_fmt == AF8_M_UF8 && cfg->m_block == 256 && cfg->cols_mult256) {
+        bool ok = (reinterpret_cast<uintptr_t>(dev_maps) & 63) == 0;
+        for (int i = 0; i < n_tensors && ok; ++i) {
+            const af8_factored_tensor &t = host_tensors[i];
+            ok = fact_batch(t) == 1 && t.rows < ((int64_t)1 << 31) && t.cols < ((int64_t)1 << 31) && (t.cols % 256) == 0 &&
+                 t.rows * (t.cols >> 8) < ((int64_t)1 << 31);
+        }
+        if (ok) {
+            CUtensorMap *hm = static_cast<CUtensorMap *>(host_maps);
+            for (int i = 0; i < n_tensors; ++i) {
+                rc = factored_box_maps(host_tensors[i], hm + 2 * i);
+                if (rc) return rc;
+            }
+            AF8_CUDA_TRY(cudaMemcpyAsync(dev_maps, host_maps, sizeof(CUtensorMap) * 2 * (size_t)n_tensors, cudaMemcpyHostToDevice, st));
+            maps = static_cast<const CUtensorMap *>(dev_maps);
+            ring = 2;
+        }
+    }
 #define AF8_LAUNCH_FSTAT(G, RES) do { \
         const size_t sm = ring ? sring_smem_bytes<G, RES>() : 0; \
         if (sm > 0) AF8_CUDA_TRY(cudaFuncSetAttribute(factored_stats_vec_kernel<G, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm)); \
-        factored_stats_vec_kernel<G, RES><<<(int)grid, 256, sm, st>>>(L, ring); } while (0)
+        factored_stats_vec_kernel<G, RES><<<(int)grid, 256, sm, st>>>(L, ring, maps); } while (0)
     if (vec && bf && res) AF8_LAUNCH_FSTAT(bf16_tag, true);
     else if (vec && bf) AF8_LAUNCH_FSTAT(bf16_tag, false);
     else if (vec && res) AF8_LAUNCH_FSTAT(float, true);
@@ -1946,6 +2104,20 @@ extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factore
     else factored_stats_kernel<<<(int)grid, 256, 0, st>>>(L);
     AF8_CUDA_TRY(cudaGetLastError());
     return AF8_OK;
+}
+
+extern "C" int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                                  const af8_factored_tensor *host_tensors, int32_t n_tensors,
+                                  const af8_dyn_scalars *dyn, void *stream)
+{
+    return af8_factored_stats_impl(cfg, dev_tensors, host_tensors, n_tensors, dyn, nullptr, nullptr, stream);
+}
+
+extern "C" int af8_factored_stats_boxes(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                                        const af8_factored_tensor *host_tensors, int32_t n_tensors,
+                                        const af8_dyn_scalars *dyn, void *host_maps, void *dev_maps, void *stream)
+{
+    return af8_factored_stats_impl(cfg, dev_tensors, host_tensors, n_tensors, dyn, host_maps, dev_maps, stream);
 }
 
 extern "C" int af8_factored_small(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,

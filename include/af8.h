@@ -384,6 +384,15 @@ AF8_API int af8_factored_upload(const af8_factored_cfg *cfg, const af8_factored_
 AF8_API int af8_factored_stats(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
                                const af8_factored_tensor *host_tensors, int32_t n_tensors,
                                const af8_dyn_scalars *dyn, void *stream);
+/* The same with room for two tensor maps (128 bytes each) per tensor: host_maps is pinned, 64-byte aligned and
+ * stays unchanged until its copy has run; dev_maps is device memory, 64-byte aligned.  In RESIDUAL mode over bf16
+ * gradients and a UF8 momentum of block 256 with cfg.cols_mult256 set, the library describes every tensor's
+ * gradient and momentum codes as [rows][cols] arrays for tiled bulk tensor copies (TMA) and the kernel brings
+ * four rows of a 256-column slice in per copy instead of one.  Otherwise, or with NULL maps, it is
+ * af8_factored_stats. */
+AF8_API int af8_factored_stats_boxes(const af8_factored_cfg *cfg, const af8_factored_tensor *dev_tensors,
+                                     const af8_factored_tensor *host_tensors, int32_t n_tensors,
+                                     const af8_dyn_scalars *dyn, void *host_maps, void *dev_maps, void *stream);
 
 /* Per tensor: means from the sums, EMA into the row / column states (second
  * moment when conf == 0, CAME confidence when conf != 0), requantisation, and

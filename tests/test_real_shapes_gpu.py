@@ -126,6 +126,14 @@ def test_came_on_llama2_shapes(oracle):
              3, 7300, _cmp_mixed)
 
 
+def test_came_rows_that_end_inside_a_box(oracle):
+    """The residual pass brings four rows in per copy: row counts that are no multiple of 4, of a warp's 32-row
+    stride or of the 512-row tile (the rows past the end arrive as zeros and must not count), one tile column
+    and several, against the oracle."""
+    run_free(oracle, "came_ragged_rows", [(517, 512), (1030, 256), (3, 768), (33, 256)], cases.CASES["came_al16"]["hp"],
+             cases.CASES["came_al16"]["grad"], 3, 7400, _cmp_mixed)
+
+
 APOLLO_HP = dict(cases.CASES["apollo_r32"]["hp"], apollo_rank=256, apollo_update_proj_gap=200)
 APOLLO_GRAD = dict(dist="normal", std=1e-3, zero_frac=0.0, dtype="bf16")
 
