@@ -63,3 +63,22 @@ def test_bad_arguments_are_rejected_without_a_gpu():
     with pytest.raises(RuntimeError):
         _native.check(rc, "af8_fullrank_step")
     assert lib.af8_fullrank_step(None, None, None, 0, 0, None, None, None) == _native.ERR_INVALID
+
+
+def test_batched_entry_points_reject_empty_tables_without_a_gpu():
+    """The table checks of the multi-tensor entry points run on the host before anything is enqueued."""
+    import numpy as np
+    from adafactor8bit import _native
+    lib = _native.lib()
+    assert lib.af8_apollo_apply_batch(None, None, 0, 0, _native.F32, _native.BF16, 0, None) == _native.ERR_INVALID
+    t = np.zeros(2, dtype=_native.APOLLO_APPLY_TENSOR)
+    for k in ("param", "grad", "sf", "scalars"):
+        t[k] = 256
+    t["rows"], t["cols"] = 64, 64
+    t["first_chunk"] = [0, 5]                 # the second tensor starts at chunk 2, not 5
+    rc = lib.af8_apollo_apply_batch(t.ctypes.data, ctypes.c_void_p(256), 2, 4, _native.F32, _native.BF16, 0, None)
+    assert rc == _native.ERR_INVALID and b"first_chunk" in lib.af8_last_error()
+    t["first_chunk"] = [0, 2]
+    rc = lib.af8_apollo_apply_batch(t.ctypes.data, ctypes.c_void_p(256), 2, 5, _native.F32, _native.BF16, 0, None)
+    assert rc == _native.ERR_INVALID and b"total_chunks" in lib.af8_last_error()
+    assert lib.af8_factored_stats_boxes(None, None, None, 0, None, None, None, None) == _native.ERR_INVALID
